@@ -1,0 +1,82 @@
+"""Second, independent restatement of the five block dequantisers in vectorised numpy.
+
+TEST INFRASTRUCTURE.  It shares no code with ``ggml_quants_oracle.cpp`` and is written from the
+block layouts and packing loops of hf2q's quantizers (q4_0.rs:47-64, q8_0.rs:59-67,
+q4_k.rs:166-215, q5_k.rs:137-158, q6_k.rs:120-143), so a shared misreading of a layout would have
+to be made twice.  All arithmetic is float32 with one operation per numpy call (no fusion).
+"""
+from __future__ import annotations
+
+import numpy as np
+
+Q4_0, Q8_0, Q4_K, Q5_K, Q6_K = 2, 8, 12, 13, 14
+_GEOM = {Q4_0: (32, 18), Q8_0: (32, 34), Q4_K: (256, 144), Q5_K: (256, 176), Q6_K: (256, 210)}
+
+
+def _f16(b: np.ndarray) -> np.ndarray:
+    """Two little-endian bytes per block -> float32 (exact widening)."""
+    return np.ascontiguousarray(b).view("<f2").astype(np.float32).reshape(-1)
+
+
+def _scale_min_k4(s: np.ndarray):
+    """12 packed bytes per block -> (sc[nb,8], m[nb,8]) as float32."""
+    s = s.astype(np.uint8)
+    sc = np.empty((s.shape[0], 8), np.uint8)
+    mn = np.empty((s.shape[0], 8), np.uint8)
+    sc[:, :4] = s[:, 0:4] & 63
+    mn[:, :4] = s[:, 4:8] & 63
+    sc[:, 4:] = (s[:, 8:12] & 0x0F) | ((s[:, 0:4] >> 6) << 4)
+    mn[:, 4:] = (s[:, 8:12] >> 4) | ((s[:, 4:8] >> 6) << 4)
+    return sc.astype(np.float32), mn.astype(np.float32)
+
+
+def dequantize(t: int, raw) -> np.ndarray:
+    be, bb = _GEOM[t]
+    raw = np.ascontiguousarray(raw, dtype=np.uint8).reshape(-1, bb)
+    nb = raw.shape[0]
+    if t == Q4_0:
+        d = _f16(raw[:, 0:2])[:, None]
+        qs = raw[:, 2:18]
+        lo = (qs & 15).astype(np.int32) - 8
+        hi = (qs >> 4).astype(np.int32) - 8
+        q = np.concatenate([lo, hi], axis=1).astype(np.float32)
+        return (q * d).reshape(-1)
+    if t == Q8_0:
+        d = _f16(raw[:, 0:2])[:, None]
+        q = raw[:, 2:34].view(np.int8).astype(np.float32)
+        return (q * d).reshape(-1)
+    if t in (Q4_K, Q5_K):
+        d = _f16(raw[:, 0:2])[:, None]
+        dmin = _f16(raw[:, 2:4])[:, None]
+        sc, mn = _scale_min_k4(raw[:, 4:16])
+        if t == Q4_K:
+            qs = raw[:, 16:144].reshape(nb, 4, 32)
+            lo = (qs & 15).astype(np.float32)
+            hi = (qs >> 4).astype(np.float32)
+        else:
+            qh = raw[:, 16:48]                       # [nb, 32]
+            qs = raw[:, 48:176].reshape(nb, 4, 32)
+            c = np.arange(4, dtype=np.uint8)[None, :, None]
+            b1 = (qh[:, None, :] >> (2 * c)) & 1
+            b2 = (qh[:, None, :] >> (2 * c + 1)) & 1
+            lo = ((qs & 15) + 16 * b1).astype(np.float32)
+            hi = ((qs >> 4) + 16 * b2).astype(np.float32)
+        q = np.stack([lo, hi], axis=2).reshape(nb, 8, 32)      # sub-block j = 2c (+1)
+        d1 = (d * sc)[:, :, None]                               # f32 product, exact
+        m1 = (dmin * mn)[:, :, None]
+        prod = d1 * q
+        return (prod - m1).astype(np.float32).reshape(-1)
+    if t == Q6_K:
+        ql = raw[:, 0:128].reshape(nb, 2, 2, 32)               # [half n][which 32-run][l]
+        qh = raw[:, 128:192].reshape(nb, 2, 32)
+        sc = raw[:, 192:208].view(np.int8).astype(np.float32)  # [nb,16]
+        d = _f16(raw[:, 208:210])[:, None]
+        out = np.empty((nb, 2, 4, 32), np.float32)
+        for k in range(4):
+            lo = (ql[:, :, k, :] & 15) if k < 2 else (ql[:, :, k - 2, :] >> 4)
+            hi = (qh >> (2 * k)) & 3
+            out[:, :, k, :] = ((lo | (hi << 4)).astype(np.int32) - 32).astype(np.float32)
+        q = out.reshape(nb, 16, 16)
+        ds = (d * sc)[:, :, None]
+        return (ds * q).astype(np.float32).reshape(-1)
+    raise ValueError(f"unsupported ggml type {t}")
