@@ -1,0 +1,67 @@
+"""ctypes binding of libhf2q_cuda.so -- the same symbols a Rust ``hf2q-cuda-sys`` crate would bind.
+
+There is no fallback: if the library is missing or a symbol is absent, import fails loudly.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import re
+from pathlib import Path
+
+PKG = Path(__file__).resolve().parent
+LIB_PATH = PKG / "libhf2q_cuda.so"
+HEADER = PKG.parent / "include" / "hf2q_cuda.h"
+
+OK = 0
+ERR_INVALID_ARGUMENT, ERR_UNSUPPORTED_TYPE, ERR_CUDA, ERR_WORKSPACE = 1, 2, 3, 4
+ERR_TIMEOUT, ERR_OUT_OF_MEMORY, ERR_NO_DEVICE = 5, 6, 7
+
+i32, u32, u64, vp = C.c_int32, C.c_uint32, C.c_uint64, C.c_void_p
+pp = C.POINTER(C.c_void_p)
+
+# name -> (restype, argtypes); kept in the order of include/hf2q_cuda.h
+SIGNATURES = {
+    "hf2q_cuda_ctx_create": (i32, [i32, pp]),
+    "hf2q_cuda_ctx_destroy": (i32, [vp]),
+    "hf2q_cuda_strerror": (C.c_char_p, [i32]),
+    "hf2q_cuda_last_error": (C.c_char_p, [vp]),
+    "hf2q_cuda_check_status": (i32, [vp, vp]),
+    "hf2q_cuda_block_geometry": (i32, [u32, C.POINTER(u32), C.POINTER(u32)]),
+    "hf2q_cuda_row_bytes": (i32, [u32, u64, C.POINTER(u64)]),
+    "hf2q_cuda_expert_stride": (i32, [u32, u64, u64, C.POINTER(u64)]),
+    "hf2q_cuda_upload_blocks": (i32, [vp, vp, u64, pp]),
+    "hf2q_cuda_free": (i32, [vp, vp]),
+    "hf2q_cuda_dequantize": (i32, [vp, vp, vp, u32, u64, u64, vp, u32]),
+    "hf2q_cuda_qmatmul": (i32, [vp, vp, vp, u32, vp, vp, u32, u32, u32, u32, vp, u64]),
+    "hf2q_cuda_qmatmul_workspace_bytes": (i32, [u32, u32, u32, u32, u32, C.POINTER(u64)]),
+    "hf2q_cuda_qmatmul_host": (i32, [vp, vp, u32, vp, vp, u32, u32, u32, u32]),
+    "hf2q_cuda_qmatmul_id": (i32, [vp, vp, vp, u32, vp, vp, vp, u32, u32, u32, u32, u32, u64, u32, vp, u64]),
+    "hf2q_cuda_qmatmul_id_scratch_bytes": (i32, [u32, u32, u32, u32, C.POINTER(u64)]),
+    "hf2q_cuda_moe_softmax_topk": (i32, [vp, vp, vp, vp, vp, u32, u32, u32]),
+    "hf2q_cuda_launch_count": (u64, [vp]),
+    "hf2q_cuda_sm_count": (i32, [vp]),
+    "hf2q_cuda_version": (C.c_char_p, []),
+}
+
+
+def declared_symbols() -> list[str]:
+    """Every function name the public header declares."""
+    text = HEADER.read_text()
+    return sorted(set(re.findall(r"HF2Q_API\s+[\w\s\*]+?\b(hf2q_cuda_\w+)\s*\(", text)))
+
+
+_lib = None
+
+
+def load() -> C.CDLL:
+    global _lib
+    if _lib is None:
+        if not LIB_PATH.exists():
+            raise ImportError(f"{LIB_PATH} is missing -- build it with `python -m hf2q_b200.build` "
+                              "(there is no CPU or PyTorch fallback for this library)")
+        lib = C.CDLL(str(LIB_PATH))
+        for name, (res, args) in SIGNATURES.items():
+            fn = getattr(lib, name)          # AttributeError if the symbol is not exported
+            fn.restype, fn.argtypes = res, args
+        _lib = lib
+    return _lib

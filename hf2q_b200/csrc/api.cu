@@ -1,0 +1,353 @@
+// C ABI of the library (see include/hf2q_cuda.h): argument validation, routing between the
+// kernels, status handling.  Host code only; mirrors the checks hf2q performs before it calls
+// mlx-native (shape and type allow-lists, src/inference/models/qwen35/weight_loader.rs:1059-1079;
+// unsupported type is an error, src/serve/forward_mlx.rs:9647-9651).
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <new>
+
+#include "common.cuh"
+#include "kernels.h"
+
+using namespace hf2q;
+
+struct hf2q_ctx {
+    int device = -1;
+    DeviceInfo dev{};
+    uint32_t* status = nullptr;        // device status word
+    uint64_t launches = 0;
+    // staging for the *_host convenience calls
+    void* stage_x = nullptr;  size_t stage_x_bytes = 0;
+    float* stage_y = nullptr; size_t stage_y_bytes = 0;
+    void* pin_x = nullptr;    size_t pin_x_bytes = 0;
+    float* pin_y = nullptr;   size_t pin_y_bytes = 0;
+    void* ws = nullptr;       size_t ws_bytes = 0;
+    cudaStream_t host_stream = nullptr;
+    char err[512] = {0};
+};
+
+namespace {
+
+int32_t fail(hf2q_ctx* ctx, int32_t code, const char* fmt, ...) {
+    if (ctx) {
+        va_list ap;
+        va_start(ap, fmt);
+        vsnprintf(ctx->err, sizeof ctx->err, fmt, ap);
+        va_end(ap);
+    }
+    return code;
+}
+int32_t cuda_fail(hf2q_ctx* ctx, cudaError_t e, const char* what) {
+    const int32_t code = e == cudaErrorMemoryAllocation ? HF2Q_ERR_OUT_OF_MEMORY : HF2Q_ERR_CUDA;
+    return fail(ctx, code, "%s: %s", what, cudaGetErrorString(e));
+}
+
+struct DeviceGuard {
+    int prev = -1;
+    bool ok = false;
+    explicit DeviceGuard(int dev) {
+        if (cudaGetDevice(&prev) != cudaSuccess) prev = -1;
+        ok = cudaSetDevice(dev) == cudaSuccess;
+    }
+    ~DeviceGuard() { if (prev >= 0) cudaSetDevice(prev); }
+};
+
+size_t dtype_size(uint32_t dt) { return dt == HF2Q_DT_F32 ? 4 : 2; }
+
+int32_t check_matmul_shape(hf2q_ctx* ctx, uint32_t type, uint32_t n, uint32_t k, const char* who) {
+    if (!type_supported(type)) return fail(ctx, HF2Q_ERR_UNSUPPORTED_TYPE, "%s: ggml type %u is not one of Q4_0/Q8_0/Q4_K/Q5_K/Q6_K", who, type);
+    const BlockGeom g = block_geom(type);
+    if (n == 0 || k == 0) return fail(ctx, HF2Q_ERR_INVALID_ARGUMENT, "%s: n=%u k=%u must be non-zero", who, n, k);
+    if (k % g.elems) return fail(ctx, HF2Q_ERR_INVALID_ARGUMENT, "%s: k=%u is not a multiple of the %u-element block", who, k, g.elems);
+    return HF2Q_OK;
+}
+
+int32_t grow(hf2q_ctx* ctx, void** p, size_t* have, size_t want, bool pinned) {
+    if (*have >= want) return HF2Q_OK;
+    if (*p) { pinned ? cudaFreeHost(*p) : cudaFree(*p); *p = nullptr; *have = 0; }
+    cudaError_t e = pinned ? cudaMallocHost(p, want) : cudaMalloc(p, want);
+    if (e != cudaSuccess) return cuda_fail(ctx, e, pinned ? "cudaMallocHost" : "cudaMalloc");
+    *have = want;
+    return HF2Q_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+HF2Q_API const char* hf2q_cuda_version(void) { return "hf2q-cuda 0.1 (sm_100a)"; }
+
+HF2Q_API const char* hf2q_cuda_strerror(int32_t s) {
+    switch (s) {
+        case HF2Q_OK: return "ok";
+        case HF2Q_ERR_INVALID_ARGUMENT: return "invalid argument";
+        case HF2Q_ERR_UNSUPPORTED_TYPE: return "unsupported ggml type";
+        case HF2Q_ERR_CUDA: return "CUDA runtime error";
+        case HF2Q_ERR_WORKSPACE: return "workspace missing or too small";
+        case HF2Q_ERR_TIMEOUT: return "device-side wait timed out";
+        case HF2Q_ERR_OUT_OF_MEMORY: return "out of device memory";
+        case HF2Q_ERR_NO_DEVICE: return "no usable CUDA device";
+        default: return "unknown status";
+    }
+}
+
+HF2Q_API const char* hf2q_cuda_last_error(const hf2q_ctx* ctx) { return ctx ? ctx->err : "null context"; }
+
+HF2Q_API int32_t hf2q_cuda_ctx_create(int32_t device, hf2q_ctx** out) {
+    if (!out) return HF2Q_ERR_INVALID_ARGUMENT;
+    *out = nullptr;
+    int count = 0;
+    if (cudaGetDeviceCount(&count) != cudaSuccess || count <= 0) { (void)cudaGetLastError(); return HF2Q_ERR_NO_DEVICE; }
+    if (device < 0 || device >= count) return HF2Q_ERR_INVALID_ARGUMENT;
+    hf2q_ctx* c = new (std::nothrow) hf2q_ctx();
+    if (!c) return HF2Q_ERR_OUT_OF_MEMORY;
+    c->device = device;
+    DeviceGuard g(device);
+    cudaDeviceProp prop{};
+    if (!g.ok || cudaGetDeviceProperties(&prop, device) != cudaSuccess) { delete c; return HF2Q_ERR_CUDA; }
+    if (prop.major < 10) { delete c; return HF2Q_ERR_NO_DEVICE; }   // kernels are sm_100a only
+    c->dev.sm_count = prop.multiProcessorCount;
+    c->dev.max_smem_optin = static_cast<int>(prop.sharedMemPerBlockOptin);
+    if (cudaMalloc(&c->status, 256) != cudaSuccess || cudaMemset(c->status, 0, 256) != cudaSuccess ||
+        cudaStreamCreateWithFlags(&c->host_stream, cudaStreamNonBlocking) != cudaSuccess) {
+        if (c->status) cudaFree(c->status);
+        delete c;
+        return HF2Q_ERR_CUDA;
+    }
+    *out = c;
+    return HF2Q_OK;
+}
+
+HF2Q_API int32_t hf2q_cuda_ctx_destroy(hf2q_ctx* ctx) {
+    if (!ctx) return HF2Q_ERR_INVALID_ARGUMENT;
+    DeviceGuard g(ctx->device);
+    cudaDeviceSynchronize();
+    if (ctx->status) cudaFree(ctx->status);
+    if (ctx->stage_x) cudaFree(ctx->stage_x);
+    if (ctx->stage_y) cudaFree(ctx->stage_y);
+    if (ctx->ws) cudaFree(ctx->ws);
+    if (ctx->pin_x) cudaFreeHost(ctx->pin_x);
+    if (ctx->pin_y) cudaFreeHost(ctx->pin_y);
+    if (ctx->host_stream) cudaStreamDestroy(ctx->host_stream);
+    delete ctx;
+    return HF2Q_OK;
+}
+
+HF2Q_API int32_t hf2q_cuda_check_status(hf2q_ctx* ctx, void* stream) {
+    if (!ctx) return HF2Q_ERR_INVALID_ARGUMENT;
+    DeviceGuard g(ctx->device);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    uint32_t word = 0;
+    cudaError_t e = cudaMemcpyAsync(&word, ctx->status, 4, cudaMemcpyDeviceToHost, st);
+    if (e == cudaSuccess) e = cudaMemsetAsync(ctx->status, 0, 4, st);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(st);
+    if (e != cudaSuccess) return cuda_fail(ctx, e, "status read-back");
+    if (word & STATUS_WAIT_TIMEOUT) return fail(ctx, HF2Q_ERR_TIMEOUT, "a kernel gave up a bounded wait (status 0x%x)", word);
+    if (word & STATUS_BAD_EXPERT_ID) return fail(ctx, HF2Q_ERR_INVALID_ARGUMENT, "ids[] held an expert index >= n_experts (status 0x%x)", word);
+    return HF2Q_OK;
+}
+
+HF2Q_API int32_t hf2q_cuda_block_geometry(uint32_t t, uint32_t* be, uint32_t* bb) {
+    if (!type_supported(t)) return HF2Q_ERR_UNSUPPORTED_TYPE;
+    const BlockGeom g = block_geom(t);
+    if (be) *be = g.elems;
+    if (bb) *bb = g.bytes;
+    return HF2Q_OK;
+}
+
+HF2Q_API int32_t hf2q_cuda_row_bytes(uint32_t t, uint64_t k, uint64_t* out) {
+    if (!out) return HF2Q_ERR_INVALID_ARGUMENT;
+    if (!type_supported(t)) return HF2Q_ERR_UNSUPPORTED_TYPE;
+    const BlockGeom g = block_geom(t);
+    if (k % g.elems) return HF2Q_ERR_INVALID_ARGUMENT;
+    *out = k / g.elems * g.bytes;
+    return HF2Q_OK;
+}
+
+HF2Q_API int32_t hf2q_cuda_expert_stride(uint32_t t, uint64_t rows, uint64_t cols, uint64_t* out) {
+    uint64_t rb = 0;
+    const int32_t rc = hf2q_cuda_row_bytes(t, cols, &rb);
+    if (rc) return rc;
+    *out = rows * rb;
+    return HF2Q_OK;
+}
+
+HF2Q_API int32_t hf2q_cuda_upload_blocks(hf2q_ctx* ctx, const void* host, uint64_t nbytes, void** dev_out) {
+    if (!ctx || !host || !dev_out || nbytes == 0) return fail(ctx, HF2Q_ERR_INVALID_ARGUMENT, "upload_blocks: null pointer or zero length");
+    DeviceGuard g(ctx->device);
+    void* d = nullptr;
+    // 16 spare bytes keep 16-byte vector reads of the final partial chunk inside the allocation
+    cudaError_t e = cudaMalloc(&d, nbytes + 16);
+    if (e != cudaSuccess) return cuda_fail(ctx, e, "upload_blocks: cudaMalloc");
+    e = cudaMemcpy(d, host, nbytes, cudaMemcpyHostToDevice);
+    if (e != cudaSuccess) { cudaFree(d); return cuda_fail(ctx, e, "upload_blocks: cudaMemcpy"); }
+    *dev_out = d;
+    return HF2Q_OK;
+}
+
+HF2Q_API int32_t hf2q_cuda_free(hf2q_ctx* ctx, void* p) {
+    if (!ctx) return HF2Q_ERR_INVALID_ARGUMENT;
+    DeviceGuard g(ctx->device);
+    const cudaError_t e = cudaFree(p);
+    return e == cudaSuccess ? HF2Q_OK : cuda_fail(ctx, e, "cudaFree");
+}
+
+HF2Q_API int32_t hf2q_cuda_dequantize(hf2q_ctx* ctx, void* stream, const void* w, uint32_t type, uint64_t n,
+                                      uint64_t k, void* out, uint32_t out_dtype) {
+    if (!ctx) return HF2Q_ERR_INVALID_ARGUMENT;
+    if (!w || !out) return fail(ctx, HF2Q_ERR_INVALID_ARGUMENT, "dequantize: null pointer");
+    if (!type_supported(type)) return fail(ctx, HF2Q_ERR_UNSUPPORTED_TYPE, "dequantize: ggml type %u unsupported", type);
+    if (out_dtype > HF2Q_DT_BF16) return fail(ctx, HF2Q_ERR_INVALID_ARGUMENT, "dequantize: out_dtype %u", out_dtype);
+    const BlockGeom g = block_geom(type);
+    if (k == 0 || k % g.elems) return fail(ctx, HF2Q_ERR_INVALID_ARGUMENT, "dequantize: k=%llu not a multiple of %u", (unsigned long long)k, g.elems);
+    if (reinterpret_cast<uintptr_t>(w) % 2) return fail(ctx, HF2Q_ERR_INVALID_ARGUMENT, "dequantize: weight pointer must be 2-byte aligned");
+    if (n == 0) return HF2Q_OK;
+    DeviceGuard dg(ctx->device);
+    const cudaError_t e = launch_dequant(type, w, out, out_dtype, n * k, ctx->dev.sm_count, static_cast<cudaStream_t>(stream));
+    if (e != cudaSuccess) return cuda_fail(ctx, e, "dequantize launch");
+    ctx->launches += 1;
+    return HF2Q_OK;
+}
+
+HF2Q_API int32_t hf2q_cuda_qmatmul_workspace_bytes(uint32_t m, uint32_t n, uint32_t k, uint32_t type,
+                                                   uint32_t x_dtype, uint64_t* out) {
+    (void)n; (void)k; (void)x_dtype; (void)m;
+    if (!out) return HF2Q_ERR_INVALID_ARGUMENT;
+    if (!type_supported(type)) return HF2Q_ERR_UNSUPPORTED_TYPE;
+    *out = 0;
+    return HF2Q_OK;
+}
+
+HF2Q_API int32_t hf2q_cuda_qmatmul(hf2q_ctx* ctx, void* stream, const void* x, uint32_t x_dtype, const void* w,
+                                   float* y, uint32_t m, uint32_t n, uint32_t k, uint32_t type,
+                                   void* workspace, uint64_t workspace_bytes) {
+    (void)workspace; (void)workspace_bytes;
+    if (!ctx) return HF2Q_ERR_INVALID_ARGUMENT;
+    if (!x || !w || !y) return fail(ctx, HF2Q_ERR_INVALID_ARGUMENT, "qmatmul: null pointer");
+    if (x_dtype != HF2Q_DT_F32 && x_dtype != HF2Q_DT_BF16) return fail(ctx, HF2Q_ERR_INVALID_ARGUMENT, "qmatmul: x_dtype %u (want F32 or BF16)", x_dtype);
+    int32_t rc = check_matmul_shape(ctx, type, n, k, "qmatmul");
+    if (rc) return rc;
+    if (m == 0) return HF2Q_OK;
+    if (reinterpret_cast<uintptr_t>(w) % 2 || reinterpret_cast<uintptr_t>(x) % dtype_size(x_dtype) || reinterpret_cast<uintptr_t>(y) % 4)
+        return fail(ctx, HF2Q_ERR_INVALID_ARGUMENT, "qmatmul: misaligned buffer");
+    DeviceGuard dg(ctx->device);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    // mat-vec kernel, 8 activation rows per launch
+    for (uint32_t m0 = 0; m0 < m; m0 += 8) {
+        GemvArgs a{};
+        a.w = w;
+        a.x = static_cast<const uint8_t*>(x) + static_cast<size_t>(m0) * k * dtype_size(x_dtype);
+        a.y = y + static_cast<size_t>(m0) * n;
+        a.x_dtype = x_dtype;
+        a.type = type;
+        a.m = (m - m0) < 8 ? (m - m0) : 8;
+        a.n = n; a.k = k;
+        a.slots = 1; a.top_k = 1; a.n_experts = 0;
+        a.status = ctx->status;
+        int nl = 0;
+        const cudaError_t e = launch_gemv(a, ctx->dev, st, &nl);
+        if (e != cudaSuccess) return cuda_fail(ctx, e, "qmatmul launch");
+        ctx->launches += nl;
+    }
+    return HF2Q_OK;
+}
+
+HF2Q_API int32_t hf2q_cuda_qmatmul_host(hf2q_ctx* ctx, const void* x_host, uint32_t x_dtype, const void* w_dev,
+                                        float* y_host, uint32_t m, uint32_t n, uint32_t k, uint32_t type) {
+    if (!ctx) return HF2Q_ERR_INVALID_ARGUMENT;
+    if (!x_host || !w_dev || !y_host) return fail(ctx, HF2Q_ERR_INVALID_ARGUMENT, "qmatmul_host: null pointer");
+    if (x_dtype != HF2Q_DT_F32 && x_dtype != HF2Q_DT_BF16) return fail(ctx, HF2Q_ERR_INVALID_ARGUMENT, "qmatmul_host: x_dtype %u", x_dtype);
+    int32_t rc = check_matmul_shape(ctx, type, n, k, "qmatmul_host");
+    if (rc) return rc;
+    if (m == 0) return HF2Q_OK;
+    DeviceGuard dg(ctx->device);
+    const size_t xb = static_cast<size_t>(m) * k * dtype_size(x_dtype), yb = static_cast<size_t>(m) * n * 4;
+    if ((rc = grow(ctx, &ctx->stage_x, &ctx->stage_x_bytes, xb, false))) return rc;
+    if ((rc = grow(ctx, reinterpret_cast<void**>(&ctx->stage_y), &ctx->stage_y_bytes, yb, false))) return rc;
+    uint64_t wsb = 0;
+    hf2q_cuda_qmatmul_workspace_bytes(m, n, k, type, x_dtype, &wsb);
+    if (wsb && (rc = grow(ctx, &ctx->ws, &ctx->ws_bytes, wsb, false))) return rc;
+    cudaStream_t st = ctx->host_stream;
+    cudaError_t e = cudaMemcpyAsync(ctx->stage_x, x_host, xb, cudaMemcpyHostToDevice, st);
+    if (e != cudaSuccess) return cuda_fail(ctx, e, "qmatmul_host: H2D");
+    rc = hf2q_cuda_qmatmul(ctx, st, ctx->stage_x, x_dtype, w_dev, ctx->stage_y, m, n, k, type, ctx->ws, ctx->ws_bytes);
+    if (rc) return rc;
+    e = cudaMemcpyAsync(y_host, ctx->stage_y, yb, cudaMemcpyDeviceToHost, st);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(st);
+    if (e != cudaSuccess) return cuda_fail(ctx, e, "qmatmul_host: D2H");
+    return HF2Q_OK;
+}
+
+HF2Q_API int32_t hf2q_cuda_qmatmul_id_scratch_bytes(uint32_t n_experts, uint32_t max_rows, uint32_t k,
+                                                    uint32_t x_dtype, uint64_t* out) {
+    (void)n_experts; (void)max_rows; (void)k; (void)x_dtype;
+    if (!out) return HF2Q_ERR_INVALID_ARGUMENT;
+    *out = 0;
+    return HF2Q_OK;
+}
+
+HF2Q_API int32_t hf2q_cuda_qmatmul_id(hf2q_ctx* ctx, void* stream, const void* x, uint32_t x_dtype,
+                                      const void* w_stacked, const uint32_t* ids, float* y, uint32_t n_tokens,
+                                      uint32_t top_k, uint32_t n, uint32_t k, uint32_t n_experts,
+                                      uint64_t expert_stride, uint32_t type, void* scratch, uint64_t scratch_bytes) {
+    (void)scratch; (void)scratch_bytes;
+    if (!ctx) return HF2Q_ERR_INVALID_ARGUMENT;
+    if (!x || !w_stacked || !ids || !y) return fail(ctx, HF2Q_ERR_INVALID_ARGUMENT, "qmatmul_id: null pointer");
+    if (x_dtype != HF2Q_DT_F32 && x_dtype != HF2Q_DT_BF16) return fail(ctx, HF2Q_ERR_INVALID_ARGUMENT, "qmatmul_id: x_dtype %u", x_dtype);
+    int32_t rc = check_matmul_shape(ctx, type, n, k, "qmatmul_id");
+    if (rc) return rc;
+    if (top_k == 0 || n_experts == 0) return fail(ctx, HF2Q_ERR_INVALID_ARGUMENT, "qmatmul_id: top_k=%u n_experts=%u must be non-zero", top_k, n_experts);
+    uint64_t min_stride = 0;
+    hf2q_cuda_expert_stride(type, n, k, &min_stride);
+    if (expert_stride < min_stride) return fail(ctx, HF2Q_ERR_INVALID_ARGUMENT, "qmatmul_id: expert_stride %llu < one [n,k] matrix (%llu bytes)", (unsigned long long)expert_stride, (unsigned long long)min_stride);
+    if (expert_stride % 2 || reinterpret_cast<uintptr_t>(w_stacked) % 2) return fail(ctx, HF2Q_ERR_INVALID_ARGUMENT, "qmatmul_id: weights must be 2-byte aligned");
+    if (n_tokens == 0) return HF2Q_OK;
+    const uint64_t rows = static_cast<uint64_t>(n_tokens) * top_k;
+    DeviceGuard dg(ctx->device);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    // per-row mat-vec, at most 32768 routed rows per launch (grid.y limit is 65535)
+    if (top_k > 32768) return fail(ctx, HF2Q_ERR_INVALID_ARGUMENT, "qmatmul_id: top_k=%u exceeds 32768", top_k);
+    const uint64_t chunk = 32768 / top_k * top_k;
+    for (uint64_t r0 = 0; r0 < rows; ) {
+        const uint64_t cnt = rows - r0 < chunk ? rows - r0 : chunk;
+        GemvArgs a{};
+        a.w = w_stacked;
+        a.x = static_cast<const uint8_t*>(x) + (r0 / top_k) * k * dtype_size(x_dtype);
+        a.y = y + r0 * n;
+        a.ids = ids + r0;
+        a.expert_stride = expert_stride;
+        a.x_dtype = x_dtype;
+        a.type = type;
+        a.m = 1; a.n = n; a.k = k;
+        a.slots = static_cast<uint32_t>(cnt);
+        a.top_k = top_k;
+        a.n_experts = n_experts;
+        a.status = ctx->status;
+        int nl = 0;
+        const cudaError_t e = launch_gemv(a, ctx->dev, st, &nl);
+        if (e != cudaSuccess) return cuda_fail(ctx, e, "qmatmul_id launch");
+        ctx->launches += nl;
+        r0 += cnt;
+    }
+    return HF2Q_OK;
+}
+
+HF2Q_API int32_t hf2q_cuda_moe_softmax_topk(hf2q_ctx* ctx, void* stream, const float* logits, uint32_t* ids,
+                                            float* weights, uint32_t n_tokens, uint32_t n_experts, uint32_t top_k) {
+    if (!ctx) return HF2Q_ERR_INVALID_ARGUMENT;
+    if (!logits || !ids || !weights) return fail(ctx, HF2Q_ERR_INVALID_ARGUMENT, "moe_softmax_topk: null pointer");
+    if (top_k == 0 || top_k > n_experts) return fail(ctx, HF2Q_ERR_INVALID_ARGUMENT, "moe_softmax_topk: top_k=%u must be in 1..n_experts=%u", top_k, n_experts);
+    if (n_experts > 3072) return fail(ctx, HF2Q_ERR_INVALID_ARGUMENT, "moe_softmax_topk: n_experts=%u exceeds 3072", n_experts);
+    if (n_tokens == 0) return HF2Q_OK;
+    DeviceGuard dg(ctx->device);
+    const cudaError_t e = launch_softmax_topk(logits, ids, weights, n_tokens, n_experts, top_k, static_cast<cudaStream_t>(stream));
+    if (e != cudaSuccess) return cuda_fail(ctx, e, "moe_softmax_topk launch");
+    ctx->launches += 1;
+    return HF2Q_OK;
+}
+
+HF2Q_API uint64_t hf2q_cuda_launch_count(const hf2q_ctx* ctx) { return ctx ? ctx->launches : 0; }
+HF2Q_API int32_t hf2q_cuda_sm_count(const hf2q_ctx* ctx) { return ctx ? ctx->dev.sm_count : 0; }
+
+}  // extern "C"

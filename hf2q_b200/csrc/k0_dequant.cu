@@ -1,0 +1,67 @@
+// K0: standalone block dequantisation, W[n,k] blocks -> dense [n,k] (f32 bit-exact, or f16/bf16
+// rounded to nearest even).  One thread per output element so stores coalesce; the block header
+// re-reads hit L1.  Stands in for mlx-native's dequant-to-f16 kernel that hf2q reaches through
+// dequant_to_f16::materialize_f16_shadow (src/serve/forward_mlx.rs:9440) and for the CPU
+// GgufFile::load_tensor_f32 its loaders use.
+#include "common.cuh"
+#include "kernels.h"
+
+namespace hf2q {
+
+template <typename T> __device__ __forceinline__ T cvt_out(float v);
+template <> __device__ __forceinline__ float cvt_out<float>(float v) { return v; }
+template <> __device__ __forceinline__ __half cvt_out<__half>(float v) { return __float2half_rn(v); }
+template <> __device__ __forceinline__ __nv_bfloat16 cvt_out<__nv_bfloat16>(float v) {
+    return __float2bfloat16_rn(v);
+}
+
+template <uint32_t TYPE, typename OUT>
+__global__ void __launch_bounds__(256) dequant_kernel(const uint8_t* __restrict__ w,
+                                                      OUT* __restrict__ out, uint64_t n_elems) {
+    constexpr BlockGeom G = block_geom(TYPE);
+    const uint64_t stride = static_cast<uint64_t>(gridDim.x) * blockDim.x;
+    for (uint64_t i = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n_elems;
+         i += stride) {
+        const uint64_t blk = i / G.elems;
+        const int e = static_cast<int>(i % G.elems);
+        out[i] = cvt_out<OUT>(dequant_elem<TYPE>(w + blk * G.bytes, e));
+    }
+}
+
+template <uint32_t TYPE>
+static cudaError_t launch_dequant_t(const void* w, void* out, uint32_t out_dtype, uint64_t n_elems,
+                                    int sm_count, cudaStream_t st) {
+    const uint64_t want = (n_elems + 255) / 256;
+    const uint64_t cap = static_cast<uint64_t>(sm_count) * 32;
+    const unsigned grid = static_cast<unsigned>(want < cap ? (want ? want : 1) : cap);
+    const uint8_t* wb = static_cast<const uint8_t*>(w);
+    switch (out_dtype) {
+        case HF2Q_DT_F32:
+            dequant_kernel<TYPE, float><<<grid, 256, 0, st>>>(wb, static_cast<float*>(out), n_elems);
+            break;
+        case HF2Q_DT_F16:
+            dequant_kernel<TYPE, __half><<<grid, 256, 0, st>>>(wb, static_cast<__half*>(out), n_elems);
+            break;
+        case HF2Q_DT_BF16:
+            dequant_kernel<TYPE, __nv_bfloat16>
+                <<<grid, 256, 0, st>>>(wb, static_cast<__nv_bfloat16*>(out), n_elems);
+            break;
+        default:
+            return cudaErrorInvalidValue;
+    }
+    return cudaGetLastError();
+}
+
+cudaError_t launch_dequant(uint32_t type, const void* w, void* out, uint32_t out_dtype,
+                           uint64_t n_elems, int sm_count, cudaStream_t st) {
+    switch (type) {
+        case HF2Q_TYPE_Q4_0: return launch_dequant_t<HF2Q_TYPE_Q4_0>(w, out, out_dtype, n_elems, sm_count, st);
+        case HF2Q_TYPE_Q8_0: return launch_dequant_t<HF2Q_TYPE_Q8_0>(w, out, out_dtype, n_elems, sm_count, st);
+        case HF2Q_TYPE_Q4_K: return launch_dequant_t<HF2Q_TYPE_Q4_K>(w, out, out_dtype, n_elems, sm_count, st);
+        case HF2Q_TYPE_Q5_K: return launch_dequant_t<HF2Q_TYPE_Q5_K>(w, out, out_dtype, n_elems, sm_count, st);
+        case HF2Q_TYPE_Q6_K: return launch_dequant_t<HF2Q_TYPE_Q6_K>(w, out, out_dtype, n_elems, sm_count, st);
+        default: return cudaErrorInvalidValue;
+    }
+}
+
+}  // namespace hf2q

@@ -1,0 +1,39 @@
+// Host-side launch interface between the C ABI (api.cu) and the kernel translation units.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace hf2q {
+
+// K0 (k0_dequant.cu)
+cudaError_t launch_dequant(uint32_t type, const void* w, void* out, uint32_t out_dtype,
+                           uint64_t n_elems, int sm_count, cudaStream_t st);
+
+// K1 / K3 (k1_gemv.cu): y[slot*?..] = x . dequant(W)^T for 1..8 activation rows.
+// Dense call: ids == nullptr, top_k == 1, slots == 1, m = activation rows (1..8).
+// Routed call (mul_mv_id): ids != nullptr, one slot per routed output row, m == 1 per slot;
+// slot r reads x row r / top_k and the expert matrix at w + ids[r] * expert_stride.
+struct GemvArgs {
+    const void* w;
+    const void* x;
+    float* y;
+    const uint32_t* ids;
+    uint64_t expert_stride;
+    uint32_t x_dtype;
+    uint32_t type;
+    uint32_t m, n, k;
+    uint32_t slots, top_k, n_experts;
+    uint32_t* status;
+};
+struct DeviceInfo {
+    int sm_count;
+    int max_smem_optin;
+};
+cudaError_t launch_gemv(const GemvArgs& a, const DeviceInfo& dev, cudaStream_t st, int* launches);
+
+// softmax -> top-k -> renormalise (moe_router.cu)
+cudaError_t launch_softmax_topk(const float* logits, uint32_t* ids, float* weights,
+                                uint32_t n_tokens, uint32_t n_experts, uint32_t top_k,
+                                cudaStream_t st);
+
+}  // namespace hf2q

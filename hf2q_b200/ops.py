@@ -1,0 +1,275 @@
+"""Host-side mirror of the op surface hf2q's inference models call on the quantized-matmul path.
+
+Names, argument meaning and error behaviour follow the reference (paths relative to the hf2q
+source tree):
+
+* ``GgmlType``                       src/quantize/ggml_quants/ggml_type.rs:18-54
+* ``GgmlQuantizedMatmulParams``      built at src/inference/models/qwen35/gpu_ffn.rs:1218-1229,
+                                     src/serve/forward_mlx.rs:408-415
+* ``GgmlQuantizedMatmulIdParams``    built at gpu_ffn.rs:2606-2618
+* ``GpuContext``                     src/serve/gpu.rs:19-38
+* ``QuantWeight``/``load_quant_weight``  MlxQWeight + load_gguf_qweight, forward_mlx.rs:364-402,
+                                     9356-9386; load_tensor_with_residency, weight_loader.rs:147-159
+* ``quantized_matmul_ggml``          call sites gpu_ffn.rs:1236-1306, gpu_full_attn.rs:848-855
+* ``quantized_matmul_id_ggml``       quantized_matmul_id_ggml_pooled, gpu_ffn.rs:188-206
+* ``IdMmScratch``                    decode_pool.rs:181-228
+* ``moe_softmax_topk``               dispatch_moe_softmax_topk, gpu_ffn.rs:2551
+
+Everything here forwards to ``libhf2q_cuda.so`` through its C ABI; there is no PyTorch or CPU
+implementation behind these functions.  Ops are enqueued on torch's current CUDA stream and do
+not synchronise, as the reference's ops append to a command encoder and return.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import enum
+from dataclasses import dataclass
+
+import numpy as np
+import torch
+
+from . import _lib
+
+
+class GgmlType(enum.IntEnum):
+    Q4_0 = 2
+    Q8_0 = 8
+    Q4_K = 12
+    Q5_K = 13
+    Q6_K = 14
+
+
+DT_F32, DT_F16, DT_BF16 = 0, 1, 2
+_TORCH_DT = {torch.float32: DT_F32, torch.float16: DT_F16, torch.bfloat16: DT_BF16}
+_DT_TORCH = {v: k for k, v in _TORCH_DT.items()}
+
+
+class Hf2qError(RuntimeError):
+    """A non-zero status from the C ABI (the reference's MlxError)."""
+
+    def __init__(self, status: int, detail: str):
+        self.status = status
+        name = _lib.load().hf2q_cuda_strerror(status).decode()
+        super().__init__(f"{name}: {detail}" if detail else name)
+
+
+@dataclass(frozen=True)
+class GgmlQuantizedMatmulParams:
+    m: int
+    n: int
+    k: int
+    ggml_type: int
+
+
+@dataclass(frozen=True)
+class GgmlQuantizedMatmulIdParams:
+    n_tokens: int
+    top_k: int
+    n: int
+    k: int
+    n_experts: int
+    expert_stride: int
+    ggml_type: int
+
+
+class GpuContext:
+    """One device context (serve/gpu.rs:19-38).  Not shared between threads."""
+
+    def __init__(self, device: int = 0):
+        lib = _lib.load()
+        h = C.c_void_p()
+        rc = lib.hf2q_cuda_ctx_create(device, C.byref(h))
+        if rc:
+            raise Hf2qError(rc, f"ctx_create(device={device})")
+        self._h = h
+        self.device = device
+        self._lib = lib
+
+    def close(self) -> None:
+        if getattr(self, "_h", None):
+            self._lib.hf2q_cuda_ctx_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    # -- helpers --------------------------------------------------------------------------
+    def _check(self, rc: int) -> None:
+        if rc:
+            raise Hf2qError(rc, self._lib.hf2q_cuda_last_error(self._h).decode())
+
+    def _stream(self) -> int:
+        return torch.cuda.current_stream(self.device).cuda_stream
+
+    def check_status(self) -> None:
+        """Synchronises the current stream and raises if a kernel flagged a problem."""
+        self._check(self._lib.hf2q_cuda_check_status(self._h, self._stream()))
+
+    @property
+    def launch_count(self) -> int:
+        return int(self._lib.hf2q_cuda_launch_count(self._h))
+
+    @property
+    def sm_count(self) -> int:
+        return int(self._lib.hf2q_cuda_sm_count(self._h))
+
+
+def row_bytes(ggml_type: int, k: int) -> int:
+    out = C.c_uint64()
+    rc = _lib.load().hf2q_cuda_row_bytes(int(ggml_type), k, C.byref(out))
+    if rc:
+        raise Hf2qError(rc, f"row_bytes(type={int(ggml_type)}, k={k})")
+    return out.value
+
+
+def expert_stride(ggml_type: int, rows: int, cols: int) -> int:
+    out = C.c_uint64()
+    rc = _lib.load().hf2q_cuda_expert_stride(int(ggml_type), rows, cols, C.byref(out))
+    if rc:
+        raise Hf2qError(rc, f"expert_stride(type={int(ggml_type)}, rows={rows}, cols={cols})")
+    return out.value
+
+
+class QuantWeight:
+    """Raw GGUF block bytes resident on the device + (ggml_dtype, rows, cols) -- MlxQWeight."""
+
+    def __init__(self, ctx: GpuContext, ptr: int, nbytes: int, ggml_type: int, rows: int, cols: int,
+                 owner=None, abi_owned: bool = False):
+        self.ctx, self.ptr, self.nbytes = ctx, ptr, nbytes
+        self.ggml_type, self.rows, self.cols = int(ggml_type), rows, cols
+        self._owner, self._abi_owned = owner, abi_owned
+
+    def matmul_params(self, m: int) -> GgmlQuantizedMatmulParams:
+        return GgmlQuantizedMatmulParams(m=m, n=self.rows, k=self.cols, ggml_type=self.ggml_type)
+
+    def row_slice(self, r0: int, r1: int) -> "QuantWeight":
+        """Rows [r0, r1) as a view: rows are contiguous byte ranges, so a shard is a byte slice."""
+        rb = row_bytes(self.ggml_type, self.cols)
+        return QuantWeight(self.ctx, self.ptr + r0 * rb, (r1 - r0) * rb, self.ggml_type, r1 - r0,
+                           self.cols, owner=self)
+
+    def free(self) -> None:
+        if self._abi_owned and self.ptr:
+            self.ctx._lib.hf2q_cuda_free(self.ctx._h, C.c_void_p(self.ptr))
+            self.ptr = 0
+
+    def __del__(self):
+        try:
+            if self.ctx._h:
+                self.free()
+        except Exception:
+            pass
+
+
+def load_quant_weight(ctx: GpuContext, raw, ggml_type: int, rows: int, cols: int) -> QuantWeight:
+    """Uploads raw block bytes unchanged.  ``raw`` is a uint8 numpy array (host) or a uint8 CUDA
+    tensor already on the device (kept alive by the returned object)."""
+    want = rows * row_bytes(ggml_type, cols)
+    if isinstance(raw, torch.Tensor):
+        if raw.dtype != torch.uint8 or not raw.is_cuda or not raw.is_contiguous():
+            raise Hf2qError(_lib.ERR_INVALID_ARGUMENT, "device weight must be a contiguous uint8 CUDA tensor")
+        if raw.numel() != want:
+            raise Hf2qError(_lib.ERR_INVALID_ARGUMENT, f"byte length {raw.numel()} != rows*row_bytes {want}")
+        return QuantWeight(ctx, raw.data_ptr(), want, ggml_type, rows, cols, owner=raw)
+    raw = np.ascontiguousarray(raw, dtype=np.uint8).reshape(-1)
+    if raw.size != want:
+        raise Hf2qError(_lib.ERR_INVALID_ARGUMENT, f"byte length {raw.size} != rows*row_bytes {want}")
+    dev = C.c_void_p()
+    ctx._check(ctx._lib.hf2q_cuda_upload_blocks(ctx._h, raw.ctypes.data, raw.size, C.byref(dev)))
+    return QuantWeight(ctx, dev.value, want, ggml_type, rows, cols, abi_owned=True)
+
+
+def _act(t: torch.Tensor, name: str) -> int:
+    if not t.is_cuda or not t.is_contiguous():
+        raise Hf2qError(_lib.ERR_INVALID_ARGUMENT, f"{name} must be a contiguous CUDA tensor")
+    if t.dtype not in (torch.float32, torch.bfloat16):
+        raise Hf2qError(_lib.ERR_INVALID_ARGUMENT, f"{name} dtype {t.dtype} (want float32 or bfloat16)")
+    return _TORCH_DT[t.dtype]
+
+
+def quantized_matmul_workspace_bytes(params: GgmlQuantizedMatmulParams, x_dtype=torch.bfloat16) -> int:
+    out = C.c_uint64()
+    rc = _lib.load().hf2q_cuda_qmatmul_workspace_bytes(params.m, params.n, params.k, int(params.ggml_type),
+                                                       _TORCH_DT[x_dtype], C.byref(out))
+    if rc:
+        raise Hf2qError(rc, "qmatmul_workspace_bytes")
+    return out.value
+
+
+def quantized_matmul_ggml(ctx: GpuContext, input: torch.Tensor, weight: QuantWeight, out: torch.Tensor,
+                          params: GgmlQuantizedMatmulParams, workspace: torch.Tensor | None = None) -> None:
+    """out[m,n] = input[m,k] . dequant(weight[n,k])^T   (f32 out, fp32 accumulation)."""
+    xdt = _act(input, "input")
+    if out.dtype != torch.float32 or not out.is_cuda or not out.is_contiguous():
+        raise Hf2qError(_lib.ERR_INVALID_ARGUMENT, "out must be a contiguous float32 CUDA tensor")
+    if input.numel() < params.m * params.k or out.numel() < params.m * params.n:
+        raise Hf2qError(_lib.ERR_INVALID_ARGUMENT, "input/out smaller than [m,k] / [m,n]")
+    if weight.rows != params.n or weight.cols != params.k or weight.ggml_type != int(params.ggml_type):
+        raise Hf2qError(_lib.ERR_INVALID_ARGUMENT, "params do not match the weight's (rows, cols, type)")
+    ws_ptr, ws_bytes = (workspace.data_ptr(), workspace.numel() * workspace.element_size()) if workspace is not None else (None, 0)
+    ctx._check(ctx._lib.hf2q_cuda_qmatmul(ctx._h, ctx._stream(), input.data_ptr(), xdt, weight.ptr,
+                                          out.data_ptr(), params.m, params.n, params.k,
+                                          int(params.ggml_type), ws_ptr, ws_bytes))
+
+
+def quantized_matmul_host(ctx: GpuContext, x_host: np.ndarray, weight: QuantWeight, y_host: np.ndarray,
+                          m: int, x_dtype: int = DT_F32) -> None:
+    """Host-buffer form: copies x in, runs, copies y out, waits (hf2q_cuda_qmatmul_host)."""
+    ctx._check(ctx._lib.hf2q_cuda_qmatmul_host(ctx._h, x_host.ctypes.data, x_dtype, weight.ptr,
+                                               y_host.ctypes.data, m, weight.rows, weight.cols,
+                                               weight.ggml_type))
+
+
+class IdMmScratch:
+    """Device scratch of the expert-routed product (decode_pool.rs:181-228)."""
+
+    def __init__(self, ctx: GpuContext, n_experts: int, max_rows: int, k: int = 0, x_dtype=torch.bfloat16):
+        out = C.c_uint64()
+        ctx._check(ctx._lib.hf2q_cuda_qmatmul_id_scratch_bytes(n_experts, max_rows, k, _TORCH_DT[x_dtype], C.byref(out)))
+        self.nbytes = out.value
+        self.buf = torch.empty(max(self.nbytes, 16), dtype=torch.uint8, device=f"cuda:{ctx.device}")
+
+    @classmethod
+    def alloc(cls, ctx: GpuContext, n_experts: int, max_rows: int, k: int = 0, x_dtype=torch.bfloat16) -> "IdMmScratch":
+        return cls(ctx, n_experts, max_rows, k, x_dtype)
+
+
+def quantized_matmul_id_ggml(ctx: GpuContext, input: torch.Tensor, weight_ptr: int, ids: torch.Tensor,
+                             out: torch.Tensor, scratch: IdMmScratch | None,
+                             params: GgmlQuantizedMatmulIdParams) -> None:
+    """out[t*top_k+s, :] = input[t, :] . dequant(W[ids[t*top_k+s]])^T  -- mul_mat_id."""
+    xdt = _act(input, "input")
+    if ids.dtype not in (torch.int32, torch.uint32) or not ids.is_cuda or not ids.is_contiguous():
+        raise Hf2qError(_lib.ERR_INVALID_ARGUMENT, "ids must be a contiguous 32-bit integer CUDA tensor")
+    rows = params.n_tokens * params.top_k
+    if ids.numel() < rows or out.numel() < rows * params.n or input.numel() < params.n_tokens * params.k:
+        raise Hf2qError(_lib.ERR_INVALID_ARGUMENT, "ids/input/out smaller than the params require")
+    if out.dtype != torch.float32 or not out.is_cuda or not out.is_contiguous():
+        raise Hf2qError(_lib.ERR_INVALID_ARGUMENT, "out must be a contiguous float32 CUDA tensor")
+    sp, sb = (scratch.buf.data_ptr(), scratch.nbytes) if scratch is not None else (None, 0)
+    wp = weight_ptr.ptr if isinstance(weight_ptr, QuantWeight) else int(weight_ptr)
+    ctx._check(ctx._lib.hf2q_cuda_qmatmul_id(ctx._h, ctx._stream(), input.data_ptr(), xdt, wp,
+                                             ids.data_ptr(), out.data_ptr(), params.n_tokens, params.top_k,
+                                             params.n, params.k, params.n_experts, params.expert_stride,
+                                             int(params.ggml_type), sp, sb))
+
+
+def dequantize(ctx: GpuContext, weight: QuantWeight, out_dtype=torch.float32) -> torch.Tensor:
+    out = torch.empty((weight.rows, weight.cols), dtype=out_dtype, device=f"cuda:{ctx.device}")
+    ctx._check(ctx._lib.hf2q_cuda_dequantize(ctx._h, ctx._stream(), weight.ptr, weight.ggml_type,
+                                             weight.rows, weight.cols, out.data_ptr(), _TORCH_DT[out_dtype]))
+    return out
+
+
+def moe_softmax_topk(ctx: GpuContext, logits: torch.Tensor, top_k: int):
+    if logits.dtype != torch.float32 or not logits.is_cuda or not logits.is_contiguous() or logits.dim() != 2:
+        raise Hf2qError(_lib.ERR_INVALID_ARGUMENT, "logits must be a contiguous float32 [tokens, experts] CUDA tensor")
+    t, e = logits.shape
+    ids = torch.empty(t * top_k, dtype=torch.int32, device=logits.device)
+    w = torch.empty(t * top_k, dtype=torch.float32, device=logits.device)
+    ctx._check(ctx._lib.hf2q_cuda_moe_softmax_topk(ctx._h, ctx._stream(), logits.data_ptr(), ids.data_ptr(),
+                                                   w.data_ptr(), t, e, top_k))
+    return ids, w

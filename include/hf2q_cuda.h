@@ -1,0 +1,173 @@
+/*
+ * hf2q_cuda.h -- C ABI of the B200 (sm_100a) backend for hf2q's quantized-weight matmul path.
+ *
+ * Every entry point is plain C: pointers, sizes and integer tags only.  The functions are the ones
+ * a `hf2q-cuda-sys` FFI crate would bind in place of the calls hf2q makes today into the external
+ * mlx-native crate; each declaration cites the hf2q call site or type it stands in for (paths are
+ * relative to the hf2q source tree).
+ *
+ * Conventions kept from the reference's op surface
+ *   - enqueue, do not execute: compute calls launch on the caller's stream and return; they never
+ *     synchronise and never allocate (gpu_ffn.rs:1044-1049, 2300-2311; scratch is passed in, as
+ *     with IdMmScratch, decode_pool.rs:181-228).  The *_host convenience calls are the exception
+ *     and say so.
+ *   - buffers are caller-owned; outputs must be pre-sized (gpu_ffn.rs:757-763).
+ *   - unsupported types and malformed shapes are errors, never a silent fallback
+ *     (forward_mlx.rs:9647-9651; weight_loader.rs:1059-1079).
+ *   - a context is bound to one device and may be used from one thread at a time; the library
+ *     keeps no other mutable global state (decode_pool.rs:51-76, serve/gpu.rs:38-39).
+ *
+ * `stream` arguments are `cudaStream_t` passed as `void*` (NULL = the legacy default stream).
+ */
+#ifndef HF2Q_CUDA_H
+#define HF2Q_CUDA_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(__GNUC__)
+#define HF2Q_API __attribute__((visibility("default")))
+#else
+#define HF2Q_API
+#endif
+
+typedef struct hf2q_ctx hf2q_ctx;
+
+/* Status codes (the reference returns Result<(), MlxError>: InvalidArgument, CommandBufferError,
+ * IoError -- gpu_ffn.rs:160, 207). */
+enum {
+    HF2Q_OK = 0,
+    HF2Q_ERR_INVALID_ARGUMENT = 1, /* null pointer, zero or mismatched shape, misaligned buffer   */
+    HF2Q_ERR_UNSUPPORTED_TYPE = 2, /* ggml type outside {Q4_0,Q8_0,Q4_K,Q5_K,Q6_K}                */
+    HF2Q_ERR_CUDA = 3,             /* a CUDA runtime call failed; see hf2q_cuda_last_error        */
+    HF2Q_ERR_WORKSPACE = 4,        /* workspace / scratch missing or too small                    */
+    HF2Q_ERR_TIMEOUT = 5,          /* a bounded device-side wait gave up (status word non-zero)   */
+    HF2Q_ERR_OUT_OF_MEMORY = 6,
+    HF2Q_ERR_NO_DEVICE = 7
+};
+
+/* GGUF numeric type ids (src/quantize/ggml_quants/ggml_type.rs:18-33). */
+enum {
+    HF2Q_TYPE_Q4_0 = 2,
+    HF2Q_TYPE_Q8_0 = 8,
+    HF2Q_TYPE_Q4_K = 12,
+    HF2Q_TYPE_Q5_K = 13,
+    HF2Q_TYPE_Q6_K = 14
+};
+
+/* Element types of activations and of dequantised output. */
+enum { HF2Q_DT_F32 = 0, HF2Q_DT_F16 = 1, HF2Q_DT_BF16 = 2 };
+
+/* ---- context ------------------------------------------------------------------------------ */
+
+/* GpuContext::new (src/serve/gpu.rs:19-38): binds a device, queries its SM count and shared-memory
+ * limits, allocates the 4-byte device status word the bounded waits report through. */
+HF2Q_API int32_t hf2q_cuda_ctx_create(int32_t device, hf2q_ctx** out);
+HF2Q_API int32_t hf2q_cuda_ctx_destroy(hf2q_ctx* ctx);
+
+/* MlxError's Display (gpu_ffn.rs:160): static text for a status code. */
+HF2Q_API const char* hf2q_cuda_strerror(int32_t status);
+/* Detail of the last failure on this context (shape that was rejected, CUDA error string). */
+HF2Q_API const char* hf2q_cuda_last_error(const hf2q_ctx* ctx);
+/* Reads and clears the device status word (synchronises `stream`); HF2Q_ERR_TIMEOUT if a kernel
+ * recorded that a bounded wait ran out.  Stands where the reference learns of a failed command
+ * buffer at commit_and_wait (gpu_ffn.rs:1036-1040). */
+HF2Q_API int32_t hf2q_cuda_check_status(hf2q_ctx* ctx, void* stream);
+
+/* ---- geometry ----------------------------------------------------------------------------- */
+
+/* GgmlType::block_size / type_size (ggml_type.rs:60-127). */
+HF2Q_API int32_t hf2q_cuda_block_geometry(uint32_t ggml_type, uint32_t* block_elems,
+                                          uint32_t* block_bytes);
+/* GgmlType::row_size (ggml_type.rs:131-133): bytes of one row of k elements. */
+HF2Q_API int32_t hf2q_cuda_row_bytes(uint32_t ggml_type, uint64_t k, uint64_t* out);
+/* ggml_type_stride (gpu_ffn.rs:400-412): bytes of one expert's [rows, cols] slice. */
+HF2Q_API int32_t hf2q_cuda_expert_stride(uint32_t ggml_type, uint64_t rows, uint64_t cols,
+                                         uint64_t* out);
+
+/* ---- weight residency --------------------------------------------------------------------- */
+
+/* GgufFile::load_tensor as used by load_tensor_with_residency (weight_loader.rs:147-159) and
+ * load_gguf_qweight (forward_mlx.rs:9356-9386): copies the raw GGUF block bytes to the device
+ * UNCHANGED.  Allocates (load time, not launch path); synchronous.  Free with hf2q_cuda_free. */
+HF2Q_API int32_t hf2q_cuda_upload_blocks(hf2q_ctx* ctx, const void* host_bytes, uint64_t nbytes,
+                                         void** dev_out);
+HF2Q_API int32_t hf2q_cuda_free(hf2q_ctx* ctx, void* dev_ptr);
+
+/* ---- K0: standalone dequantisation -------------------------------------------------------- */
+
+/* dequant_to_f16::materialize_f16_shadow (forward_mlx.rs:9440) and GgufFile::load_tensor_f32
+ * (gpu_full_attn.rs upload helpers): W[n,k] blocks -> dense [n,k] of out_dtype.  F32 output is
+ * bit-exact with the inverse of the quantizers' re-encode step. */
+HF2Q_API int32_t hf2q_cuda_dequantize(hf2q_ctx* ctx, void* stream, const void* w,
+                                      uint32_t ggml_type, uint64_t n, uint64_t k, void* out,
+                                      uint32_t out_dtype);
+
+/* ---- a4: dense quantized matmul ----------------------------------------------------------- */
+
+/* quantized_matmul_ggml(enc, registry, device, input, weight, &mut out,
+ *                       &GgmlQuantizedMatmulParams{m,n,k,ggml_type})
+ * (gpu_ffn.rs:1236-1306, gpu_full_attn.rs:848-855, gpu_delta_net.rs:399-407,
+ *  forward_mlx.rs:9960-9968):  y[m,n] = x[m,k] . dequant(W[n,k])^T, fp32 accumulation.
+ * x is row-major [m,k] of x_dtype (F32 or BF16), y is row-major f32 [m,n], w is the raw block
+ * bytes of W.  m <= 8 takes the mat-vec kernel (the reference's MM_ROUTING_THRESHOLD,
+ * forward_mlx.rs:9800); larger m takes the tensor-core kernel, which needs the workspace reported
+ * by hf2q_cuda_qmatmul_workspace_bytes (0 for m <= 8). */
+HF2Q_API int32_t hf2q_cuda_qmatmul(hf2q_ctx* ctx, void* stream, const void* x, uint32_t x_dtype,
+                                   const void* w, float* y, uint32_t m, uint32_t n, uint32_t k,
+                                   uint32_t ggml_type, void* workspace, uint64_t workspace_bytes);
+HF2Q_API int32_t hf2q_cuda_qmatmul_workspace_bytes(uint32_t m, uint32_t n, uint32_t k,
+                                                   uint32_t ggml_type, uint32_t x_dtype,
+                                                   uint64_t* out);
+
+/* Same product for callers that hold HOST buffers: copies x in, runs, copies y out, waits.
+ * Uses staging buffers the context grows on first use.  Stands for the reference's
+ * `apply_linear_projection_f32` + download pattern in its tests (gpu_ffn.rs:3209-3275). */
+HF2Q_API int32_t hf2q_cuda_qmatmul_host(hf2q_ctx* ctx, const void* x_host, uint32_t x_dtype,
+                                        const void* w_dev, float* y_host, uint32_t m, uint32_t n,
+                                        uint32_t k, uint32_t ggml_type);
+
+/* ---- a6: expert-routed quantized matmul --------------------------------------------------- */
+
+/* quantized_matmul_id_ggml_pooled(enc, registry, device, input, weight, ids, out,
+ *     &mut IdMmScratch, &GgmlQuantizedMatmulIdParams{n_tokens, top_k, n, k, n_experts,
+ *     expert_stride, ggml_type})   (gpu_ffn.rs:188-206, 2606-2618, 2728-2736;
+ *  forward_mlx.rs:5285-5292, 5367-5374; forward_prefill_batched.rs:2692-2707, 2805-2820):
+ *   y[t*top_k+s, :] = x[t, :] . dequant(W_e)^T,  e = ids[t*top_k+s],
+ *   W_e = w_stacked + e*expert_stride (raw blocks of an [n,k] matrix).
+ * x is [n_tokens,k] of x_dtype, ids is u32 [n_tokens*top_k] token-major, y is f32
+ * [n_tokens*top_k, n].  An id >= n_experts makes that output row zero and sets the status word.
+ * Few rows take the per-row mat-vec; many rows take the grouped tensor-core kernel, which sorts
+ * rows by expert on the device inside `scratch` (>= hf2q_cuda_qmatmul_id_scratch_bytes). */
+HF2Q_API int32_t hf2q_cuda_qmatmul_id(hf2q_ctx* ctx, void* stream, const void* x, uint32_t x_dtype,
+                                      const void* w_stacked, const uint32_t* ids, float* y,
+                                      uint32_t n_tokens, uint32_t top_k, uint32_t n, uint32_t k,
+                                      uint32_t n_experts, uint64_t expert_stride,
+                                      uint32_t ggml_type, void* scratch, uint64_t scratch_bytes);
+/* IdMmScratch::alloc(device, n_experts, max_n_tokens) (decode_pool.rs:205-214). */
+HF2Q_API int32_t hf2q_cuda_qmatmul_id_scratch_bytes(uint32_t n_experts, uint32_t max_rows,
+                                                    uint32_t k, uint32_t x_dtype, uint64_t* out);
+
+/* dispatch_moe_softmax_topk (gpu_ffn.rs:2551), semantics of softmax_topk_renorm_cpu
+ * (gpu_ffn.rs:1879-1924): logits f32 [n_tokens, n_experts] -> ids u32 [n_tokens*top_k] (descending
+ * probability, ties to the lower index) and renormalised weights f32 [n_tokens*top_k]. */
+HF2Q_API int32_t hf2q_cuda_moe_softmax_topk(hf2q_ctx* ctx, void* stream, const float* logits,
+                                            uint32_t* ids, float* weights, uint32_t n_tokens,
+                                            uint32_t n_experts, uint32_t top_k);
+
+/* ---- introspection ------------------------------------------------------------------------ */
+
+/* Number of kernels this library has launched through `ctx` since creation (the reference keeps
+ * dispatch counters for the same purpose, forward_mlx.rs:3346). */
+HF2Q_API uint64_t hf2q_cuda_launch_count(const hf2q_ctx* ctx);
+HF2Q_API int32_t hf2q_cuda_sm_count(const hf2q_ctx* ctx);
+HF2Q_API const char* hf2q_cuda_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* HF2Q_CUDA_H */

@@ -1,0 +1,149 @@
+"""CPU tests of the oracle: pinned to the reference's golden fixtures, self-consistency, edge cases."""
+import hashlib
+import json
+from pathlib import Path
+
+import numpy as np
+import pytest
+
+import oracle
+from oracle import np_dequant
+from tests.util import FIXTURES, make_weight_f32, random_finite_blocks
+
+GOLDEN = Path(__file__).resolve().parent / "golden"
+# per-format reconstruction bounds of dequant(expected) vs input on the fixtures (abs, rel-L2)
+BOUNDS = {oracle.Q4_0: (0.12, 0.068), oracle.Q8_0: (0.0043, 0.0038), oracle.Q4_K: (0.107, 0.057),
+          oracle.Q5_K: (0.045, 0.028), oracle.Q6_K: (0.036, 0.014)}
+
+
+def _load(t, variant):
+    name, n = FIXTURES[t]
+    x = np.fromfile(GOLDEN / "ggml_quants" / f"{name}_{n}_{variant}_input.bin", dtype="<f4")
+    e = np.fromfile(GOLDEN / "ggml_quants" / f"{name}_{n}_{variant}_expected.bin", dtype=np.uint8)
+    return x, e, n
+
+
+def test_manifest_matches():
+    man = json.loads((GOLDEN / "MANIFEST.json").read_text())
+    assert len(man) == 20
+    for fn, sha in man.items():
+        assert hashlib.sha256((GOLDEN / "ggml_quants" / fn).read_bytes()).hexdigest() == sha, fn
+
+
+@pytest.mark.parametrize("t", oracle.ALL_TYPES)
+@pytest.mark.parametrize("variant", ["noim", "im"])
+def test_quantizer_bytes_equal_golden(t, variant):
+    """The reference's own byte_cmp_noim / byte_cmp_im tests (q4_k.rs:386-403 and siblings)."""
+    x, expected, n = _load(t, variant)
+    im = oracle.mulberry32_imatrix(n, 2) if variant == "im" else None
+    got = oracle.quantize(t, x, n, im)
+    assert got.shape == expected.shape
+    assert np.array_equal(got, expected)
+
+
+@pytest.mark.parametrize("t", oracle.ALL_TYPES)
+def test_fixture_inputs_are_mulberry32_seed1(t):
+    x, _, n = _load(t, "noim")
+    assert np.array_equal(x, oracle.mulberry32_uniform(2 * n, 1))
+
+
+@pytest.mark.parametrize("t", oracle.ALL_TYPES)
+@pytest.mark.parametrize("variant", ["noim", "im"])
+def test_dequant_of_golden_reconstructs_input(t, variant):
+    x, expected, _ = _load(t, variant)
+    y = oracle.dequantize(t, expected)
+    amax, rel = BOUNDS[t]
+    assert np.abs(y - x).max() <= amax
+    assert np.linalg.norm(y - x) / np.linalg.norm(x) <= rel
+
+
+@pytest.mark.parametrize("t", oracle.ALL_TYPES)
+def test_two_dequant_restatements_agree_bitwise(t):
+    for variant in ("noim", "im"):
+        _, expected, _ = _load(t, variant)
+        a, b = oracle.dequantize(t, expected), np_dequant.dequantize(t, expected)
+        assert np.array_equal(a.view(np.uint32), b.view(np.uint32))
+    raw = random_finite_blocks(t, 512, seed=7)
+    a, b = oracle.dequantize(t, raw), np_dequant.dequantize(t, raw)
+    assert np.array_equal(a.view(np.uint32), b.view(np.uint32))
+    w = oracle.quantize(t, make_weight_f32(16, 1024, seed=3), 1024)
+    a, b = oracle.dequantize(t, w), np_dequant.dequantize(t, w)
+    assert np.array_equal(a.view(np.uint32), b.view(np.uint32))
+
+
+@pytest.mark.parametrize("t", oracle.ALL_TYPES)
+def test_requantizing_dequantized_values_returns_the_same_bytes_for_symmetric_formats(t):
+    """Re-encode identity: dequantised values lie exactly on the grid the block stores."""
+    w = make_weight_f32(8, 1024, seed=11)
+    raw = oracle.quantize(t, w, 1024)
+    y = oracle.dequantize(t, raw)
+    y2 = oracle.dequantize(t, oracle.quantize(t, y, 1024))
+    # the quantizer's scale search may pick another scale for already-quantised data, so compare
+    # values: the round trip must not move any element by more than half a quantisation step
+    step = np.abs(y).max() / {oracle.Q4_0: 7, oracle.Q8_0: 127, oracle.Q4_K: 15, oracle.Q5_K: 31, oracle.Q6_K: 31}[t]
+    assert np.abs(y2 - y).max() <= step
+
+
+def test_nearest_int_is_round_half_even():
+    # common.rs:525-539
+    L = oracle.lib()
+    for v, want in [(0.0, 0), (1.0, 1), (-1.0, -1), (1.4, 1), (1.6, 2), (-1.4, -1), (-1.6, -2),
+                    (0.5, 0), (1.5, 2), (2.5, 2), (3.5, 4)]:
+        assert L.oracle_nearest_int(v) == want
+
+
+def test_f16_conversion_matches_numpy_everywhere():
+    bits = np.arange(65536, dtype=np.uint16)
+    ref = bits.view(np.float16).astype(np.float32)
+    L = oracle.lib()
+    got = np.array([L.oracle_f16_to_f32(int(b)) for b in bits[::7]], dtype=np.float32)
+    assert np.array_equal(got.view(np.uint32)[~np.isnan(ref[::7])], ref[::7].view(np.uint32)[~np.isnan(ref[::7])])
+    rng = np.random.default_rng(0)
+    x = np.concatenate([rng.standard_normal(20000).astype(np.float32) * s for s in (1e-8, 1e-5, 1e-3, 1.0, 1e3, 7e4)])
+    with np.errstate(over="ignore"):
+        want = x.astype(np.float16).astype(np.float32)
+    assert np.array_equal(oracle.f16_round_trip(x).view(np.uint32), want.view(np.uint32))
+
+
+def test_zero_blocks():
+    for t in oracle.ALL_TYPES:
+        raw = oracle.quantize(t, np.zeros(512, np.float32), 512)
+        assert np.all(oracle.dequantize(t, raw) == 0.0)
+
+
+def test_simple_q4_0_encoder_matches_reference_formula():
+    # gpu_full_attn.rs:427-451
+    rng = np.random.default_rng(5)
+    v = rng.standard_normal(64).astype(np.float32)
+    v[32:] = 0.0
+    raw = oracle.encode_q4_0_simple(v).reshape(2, 18)
+    d0 = raw[0, :2].view("<f2")[0]
+    assert d0 == np.float16(np.abs(v[:32]).max() / np.float32(7.0))
+    assert raw[1, :2].view("<f2")[0] == np.float16(1.0) and np.all(raw[1, 2:] == 0x88)
+    y = oracle.dequantize(oracle.Q4_0, raw.reshape(-1))
+    assert np.abs(y[:32] - v[:32]).max() <= float(d0) * 0.51 + 1e-3
+
+
+def test_matmul_and_topk_semantics():
+    rng = np.random.default_rng(2)
+    a = rng.standard_normal((3, 64)).astype(np.float32)
+    b = rng.standard_normal((5, 64)).astype(np.float32)
+    got = oracle.matmul_a_by_bt(a, b)
+    assert np.allclose(got, a @ b.T, rtol=1e-5, atol=1e-5)
+    assert np.allclose(oracle.matmul_f64(a, b), a.astype(np.float64) @ b.T.astype(np.float64))
+    logits = np.array([[0.0, 1.0, 1.0, -1.0, 0.5]], np.float32)
+    ids, w = oracle.softmax_topk_renorm(logits, 3)
+    assert ids.tolist() == [1, 2, 4]          # tie between 1 and 2 keeps the lower index first
+    assert abs(w.sum() - 1.0) < 1e-6 and w[0] == w[1] > w[2]
+
+
+def test_qmatmul_id_oracle_matches_dense_per_row():
+    t, n, k, ne = oracle.Q5_K, 16, 512, 4
+    w = np.concatenate([oracle.quantize(t, make_weight_f32(n, k, seed=20 + e), k) for e in range(ne)])
+    stride = n * oracle.row_bytes(t, k)
+    x = np.random.default_rng(1).standard_normal((3, k)).astype(np.float32)
+    ids = np.array([0, 3, 1, 1, 2, 0], np.uint32)
+    y = oracle.qmatmul_id(t, w, stride, x, ids, 3, 2, n, k, ne)
+    for r, e in enumerate(ids):
+        yd, _, _ = oracle.qmatmul(t, w[e * stride:(e + 1) * stride], x[r // 2:r // 2 + 1], n, k)
+        assert np.array_equal(y[r], yd[0])
