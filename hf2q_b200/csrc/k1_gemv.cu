@@ -20,6 +20,8 @@
 //
 // Rows whose byte length is not a multiple of 16 (e.g. Q6_K with k = 512, Q4_0 with k = 32)
 // cannot be bulk-copied and take the simple warp-per-row kernel at the end of this file.
+#include <mutex>
+
 #include "common.cuh"
 #include "kernels.h"
 
@@ -386,13 +388,30 @@ template <uint32_t TYPE, int M, bool XSMEM>
 cudaError_t launch_stream(const KParams& p, uint32_t slots, size_t smem, const DeviceInfo& dev,
                           cudaStream_t st) {
     auto kern = gemv_stream_kernel<TYPE, M, XSMEM>;
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         static_cast<int>(smem));
-    if (e != cudaSuccess) return e;
-    int per_sm = 1;
-    e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, THREADS, smem);
-    if (e != cudaSuccess) return e;
-    if (per_sm < 1) per_sm = 1;
+    // The opt-in shared-memory limit is raised once per kernel; the occupancy answer is cached for
+    // the last shared-memory size, so the steady-state launch path makes no other runtime call.
+    static std::mutex mu;
+    static bool attr_set = false;
+    static size_t cached_smem = ~static_cast<size_t>(0);
+    static int cached_per_sm = 1;
+    int per_sm;
+    {
+        std::lock_guard<std::mutex> lock(mu);
+        if (!attr_set) {
+            cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                 dev.max_smem_optin);
+            if (e != cudaSuccess) return e;
+            attr_set = true;
+        }
+        if (cached_smem != smem) {
+            int q = 1;
+            cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&q, kern, THREADS, smem);
+            if (e != cudaSuccess) return e;
+            cached_per_sm = q < 1 ? 1 : q;
+            cached_smem = smem;
+        }
+        per_sm = cached_per_sm;
+    }
     uint32_t want = static_cast<uint32_t>(dev.sm_count) * per_sm;
     uint32_t gx = (want + slots - 1) / slots;
     if (gx > p.ngroups) gx = p.ngroups;
