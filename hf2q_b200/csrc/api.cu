@@ -4,6 +4,7 @@
 // unsupported type is an error, src/serve/forward_mlx.rs:9647-9651).
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <new>
 
@@ -17,6 +18,7 @@ struct hf2q_ctx {
     DeviceInfo dev{};
     uint32_t* status = nullptr;        // device status word
     uint64_t launches = 0;
+    bool fp32_matvec = false;          // HF2Q_CUDA_F32_MATVEC=1: CUDA-core fp32 mat-vec instead of the MMA one
     // staging for the *_host convenience calls
     void* stage_x = nullptr;  size_t stage_x_bytes = 0;
     float* stage_y = nullptr; size_t stage_y_bytes = 0;
@@ -72,6 +74,33 @@ int32_t grow(hf2q_ctx* ctx, void** p, size_t* have, size_t want, bool pinned) {
     return HF2Q_OK;
 }
 
+// y[m,n] for m activation rows through the mat-vec kernels, split into as many launches as the
+// chosen kernel needs.  ids == nullptr: dense.
+int32_t run_matvec(hf2q_ctx* ctx, cudaStream_t st, GemvArgs a, uint32_t m_total, const char* who) {
+    const size_t xs = dtype_size(a.x_dtype);
+    const bool mma = !ctx->fp32_matvec && gemv_mma_supported(a);
+    uint32_t step = 8;
+    if (mma) {
+        step = gemv_mma_max_rows(a.type, a.k, a.x_dtype, ctx->dev);
+        if (step == 0) step = 8;
+    }
+    const bool use_mma = mma && gemv_mma_max_rows(a.type, a.k, a.x_dtype, ctx->dev) > 0;
+    const uint8_t* x0 = static_cast<const uint8_t*>(a.x);
+    float* y0 = a.y;
+    for (uint32_t m0 = 0; m0 < m_total; m0 += step) {
+        a.m = (m_total - m0) < step ? (m_total - m0) : step;
+        a.x = x0 + static_cast<size_t>(m0) * a.k * xs;
+        a.y = y0 + static_cast<size_t>(m0) * a.n;
+        cudaError_t e;
+        int nl = 1;
+        if (use_mma) e = launch_gemv_mma(a, ctx->dev, st);
+        else e = launch_gemv(a, ctx->dev, st, &nl);
+        if (e != cudaSuccess) return cuda_fail(ctx, e, who);
+        ctx->launches += nl;
+    }
+    return HF2Q_OK;
+}
+
 }  // namespace
 
 extern "C" {
@@ -115,6 +144,10 @@ HF2Q_API int32_t hf2q_cuda_ctx_create(int32_t device, hf2q_ctx** out) {
         delete c;
         return HF2Q_ERR_CUDA;
     }
+    // one knob, read once here and never on the launch path (the reference has the same kind of
+    // switch for its mat-vec: HF2Q_F32_MATVEC, src/serve/forward_mlx.rs:9835)
+    const char* env = getenv("HF2Q_CUDA_F32_MATVEC");
+    c->fp32_matvec = env && env[0] == '1';
     *out = c;
     return HF2Q_OK;
 }
@@ -145,6 +178,7 @@ HF2Q_API int32_t hf2q_cuda_check_status(hf2q_ctx* ctx, void* stream) {
     if (e != cudaSuccess) return cuda_fail(ctx, e, "status read-back");
     if (word & STATUS_WAIT_TIMEOUT) return fail(ctx, HF2Q_ERR_TIMEOUT, "a kernel gave up a bounded wait (status 0x%x)", word);
     if (word & STATUS_BAD_EXPERT_ID) return fail(ctx, HF2Q_ERR_INVALID_ARGUMENT, "ids[] held an expert index >= n_experts (status 0x%x)", word);
+    if (word & STATUS_X_CLIPPED) return fail(ctx, HF2Q_ERR_INVALID_ARGUMENT, "an activation exceeded 65504 in magnitude and was clipped (status 0x%x)", word);
     return HF2Q_OK;
 }
 
@@ -233,24 +267,13 @@ HF2Q_API int32_t hf2q_cuda_qmatmul(hf2q_ctx* ctx, void* stream, const void* x, u
         return fail(ctx, HF2Q_ERR_INVALID_ARGUMENT, "qmatmul: misaligned buffer");
     DeviceGuard dg(ctx->device);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    // mat-vec kernel, 8 activation rows per launch
-    for (uint32_t m0 = 0; m0 < m; m0 += 8) {
-        GemvArgs a{};
-        a.w = w;
-        a.x = static_cast<const uint8_t*>(x) + static_cast<size_t>(m0) * k * dtype_size(x_dtype);
-        a.y = y + static_cast<size_t>(m0) * n;
-        a.x_dtype = x_dtype;
-        a.type = type;
-        a.m = (m - m0) < 8 ? (m - m0) : 8;
-        a.n = n; a.k = k;
-        a.slots = 1; a.top_k = 1; a.n_experts = 0;
-        a.status = ctx->status;
-        int nl = 0;
-        const cudaError_t e = launch_gemv(a, ctx->dev, st, &nl);
-        if (e != cudaSuccess) return cuda_fail(ctx, e, "qmatmul launch");
-        ctx->launches += nl;
-    }
-    return HF2Q_OK;
+    GemvArgs a{};
+    a.w = w; a.x = x; a.y = y;
+    a.x_dtype = x_dtype; a.type = type;
+    a.n = n; a.k = k;
+    a.slots = 1; a.top_k = 1; a.n_experts = 0;
+    a.status = ctx->status;
+    return run_matvec(ctx, st, a, m, "qmatmul launch");
 }
 
 HF2Q_API int32_t hf2q_cuda_qmatmul_host(hf2q_ctx* ctx, const void* x_host, uint32_t x_dtype, const void* w_dev,
@@ -324,8 +347,12 @@ HF2Q_API int32_t hf2q_cuda_qmatmul_id(hf2q_ctx* ctx, void* stream, const void* x
         a.top_k = top_k;
         a.n_experts = n_experts;
         a.status = ctx->status;
-        int nl = 0;
-        const cudaError_t e = launch_gemv(a, ctx->dev, st, &nl);
+        cudaError_t e;
+        int nl = 1;
+        if (!ctx->fp32_matvec && gemv_mma_supported(a) && gemv_mma_max_rows(type, k, x_dtype, ctx->dev) > 0)
+            e = launch_gemv_mma(a, ctx->dev, st);
+        else
+            e = launch_gemv(a, ctx->dev, st, &nl);
         if (e != cudaSuccess) return cuda_fail(ctx, e, "qmatmul_id launch");
         ctx->launches += nl;
         r0 += cnt;

@@ -19,6 +19,7 @@ constexpr int QK_K = 256;
 enum : uint32_t {
     STATUS_WAIT_TIMEOUT = 1u,   // a bounded mbarrier wait gave up
     STATUS_BAD_EXPERT_ID = 2u,  // ids[] held a value >= n_experts
+    STATUS_X_CLIPPED = 4u,      // an activation exceeded the f16 range (65504) and was clipped
 };
 
 struct BlockGeom { uint32_t elems, bytes; };

@@ -1,0 +1,572 @@
+// K1 / K3 (main variant): dequant-fused mat-vec for 1..8 activation rows, dense and expert-routed.
+//
+//   y[t, r] = sum_k x[t, k] * dequant(W)[r, k]
+//
+// Stands in for mlx-native's kernel_mul_mv_<q>_f32 / kernel_mul_mv_id_<q>_f32 that hf2q reaches
+// through quantized_matmul_ggml (m <= 8; src/inference/models/qwen35/gpu_ffn.rs:1236-1306,
+// src/serve/forward_mlx.rs:9960-9968) and quantized_matmul_id_ggml (few rows; gpu_ffn.rs:188-206,
+// forward_mlx.rs:5285-5292).
+//
+// Why it looks the way it does.  At 6.5 TB/s a B200 SM receives ~25 weight bytes per clock, i.e.
+// 30 (Q6_K) to 44 (Q4_K) weight elements, but issues only 128 lane-instructions per clock: about
+// 3-4 instructions per element, for all activation rows together.  One FMA per element and row
+// already breaks that budget at 4 rows, so the multiply-accumulate goes through the warp-level
+// m16n8k16 MMA (8 weight rows x 16 elements x 8 activation columns per instruction) and the
+// CUDA cores only unpack bits:
+//
+//   * a persistent CTA owns groups of 8 weight rows; a producer warp streams their RAW block
+//     bytes into a shared-memory ring with 1-D bulk copies (cp.async.bulk + mbarrier), 2048
+//     elements per row and stage, so 18/34/210-byte blocks are readable at any 2-byte offset;
+//   * each of 8 consumer warps takes one 256-element chunk of the stage for all 8 rows: lane
+//     (g, t) unpacks row g, four elements at a time, into the A fragment.  The integer codes are
+//     fed as f16 SUBNORMALS (code * 2^-24): a single PRMT turns two packed bytes into an f16x2
+//     operand, with no int->float conversion and no offset to subtract;
+//   * scales stay out of the per-element path: Q4_K/Q5_K multiply the codes by the 6-bit
+//     sub-block scale in f16 (code*scale < 2048, exact) and apply d once per block; Q6_K applies
+//     d*scale to each 16-element MMA result; Q4_0/Q8_0 apply d per block.  Offsets (the -dmin*m
+//     of Q4_K/Q5_K, the -32/-8/-128 code biases) become one small extra MMA (or FMA) per block
+//     against per-sub-block sums of x that every CTA computes once;
+//   * activations live in shared memory as f16 (bf16 input: exact in range; f32 input: split
+//     into hi + lo halves on two MMA columns, ~2^-22 relative);
+//   * partial sums of the 8 warps are combined through shared memory in a fixed order: no
+//     atomics, bit-reproducible.
+//
+// Needs 16-byte aligned rows and k a multiple of 256; other shapes take the fp32 kernel in
+// k1_gemv.cu.
+#include <mutex>
+
+#include "common.cuh"
+#include "kernels.h"
+
+namespace hf2q {
+
+namespace {
+
+constexpr int ROWS = 8;
+constexpr int CWARPS = 8;
+constexpr int CT = CWARPS * 32;
+constexpr int THREADS = CT + 32;
+constexpr int SLICE_ELEMS = 2048;
+constexpr int MAX_STAGES = 4;
+
+struct MParams {
+    const uint8_t* w;
+    const void* x;
+    float* y;
+    const uint32_t* ids;
+    uint64_t expert_stride;
+    uint32_t x_bf16;
+    uint32_t m;            // activation rows of this launch (bf16: <= 8, f32: <= 4)
+    uint32_t nslots;       // MMA columns in use: m (bf16) or 2m (f32 hi/lo split)
+    uint32_t n, k;
+    uint32_t top_k, n_experts;
+    uint32_t row_bytes, slice_bytes, pitch, nslices, ngroups, stages;
+    uint32_t xpitch;       // bytes between activation rows in shared memory
+    uint32_t* status;
+};
+
+__device__ __forceinline__ void mma_16816(float& c0, float& c1, uint32_t a0, uint32_t a2, uint32_t b0,
+                                          uint32_t b1) {
+    float c2 = 0.f, c3 = 0.f;    // rows 8..15 of the tile are unused (their A registers are zero)
+    asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+        "{%0,%1,%2,%3};"
+        : "+f"(c0), "+f"(c1), "+f"(c2), "+f"(c3)
+        : "r"(a0), "r"(0u), "r"(a2), "r"(0u), "r"(b0), "r"(b1));
+}
+// bytes (b0,b1) / (b2,b3) of w as two f16 subnormals each: value = byte * 2^-24
+__device__ __forceinline__ uint32_t sub01(uint32_t w) { return __byte_perm(w, 0u, 0x4140u); }
+__device__ __forceinline__ uint32_t sub23(uint32_t w) { return __byte_perm(w, 0u, 0x4342u); }
+__device__ __forceinline__ uint32_t hmul2_bits(uint32_t a, uint32_t b) {
+    __half2 r = __hmul2(*reinterpret_cast<__half2*>(&a), *reinterpret_cast<__half2*>(&b));
+    return *reinterpret_cast<uint32_t*>(&r);
+}
+__device__ __forceinline__ uint2 ld_x4(const uint8_t* xrow, uint32_t e) {
+    return xrow ? *reinterpret_cast<const uint2*>(xrow + 2 * e) : make_uint2(0u, 0u);
+}
+constexpr float TWO24 = 16777216.0f;
+
+// ---- Q4_K / Q5_K: one 256-element block of row g, lane t owns chunk t (sub-blocks 2t, 2t+1) ----
+template <bool Q5>
+__device__ __forceinline__ void chunk_k45(const uint8_t* blk, uint32_t e0, const uint8_t* xrow,
+                                          const uint8_t* sxblk, int t, float& f0, float& f1) {
+    constexpr int QS = Q5 ? 48 : 16;
+    const uint4 hd = *reinterpret_cast<const uint4*>(blk);
+    const uint4 qa = *reinterpret_cast<const uint4*>(blk + QS + 32 * t);
+    const uint4 qb = *reinterpret_cast<const uint4*>(blk + QS + 32 * t + 16);
+    const uint32_t qv[8] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w};
+    uint32_t gv[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    if constexpr (Q5) {
+        const uint4 ga = *reinterpret_cast<const uint4*>(blk + 16);
+        const uint4 gb = *reinterpret_cast<const uint4*>(blk + 32);
+        gv[0] = ga.x; gv[1] = ga.y; gv[2] = ga.z; gv[3] = ga.w;
+        gv[4] = gb.x; gv[5] = gb.y; gv[6] = gb.z; gv[7] = gb.w;
+    }
+    uint32_t sc1, m1, sc2, m2;
+    scale_min_k4(2 * t, hd.y, hd.z, hd.w, sc1, m1);
+    scale_min_k4(2 * t + 1, hd.y, hd.z, hd.w, sc2, m2);
+    // scale * 2^10 as f16x2 (<= 64512): code*2^-24 * scale*2^10 = code*scale*2^-14, exact
+    const __half2 s1h = __half2half2(__uint2half_rn(sc1 << 10));
+    const __half2 s2h = __half2half2(__uint2half_rn(sc2 << 10));
+    const uint32_t s1 = *reinterpret_cast<const uint32_t*>(&s1h);
+    const uint32_t s2 = *reinterpret_cast<const uint32_t*>(&s2h);
+    float c0 = 0.f, c1 = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        uint32_t lo = qv[i] & 0x0F0F0F0Fu, hi = (qv[i] >> 4) & 0x0F0F0F0Fu;
+        if constexpr (Q5) {
+            lo |= ((gv[i] >> (2 * t)) & 0x01010101u) << 4;
+            hi |= ((gv[i] >> (2 * t + 1)) & 0x01010101u) << 4;
+        }
+        const uint2 xl = ld_x4(xrow, e0 + 64 * t + 4 * i);
+        mma_16816(c0, c1, hmul2_bits(sub01(lo), s1), hmul2_bits(sub23(lo), s1), xl.x, xl.y);
+        const uint2 xh = ld_x4(xrow, e0 + 64 * t + 32 + 4 * i);
+        mma_16816(c0, c1, hmul2_bits(sub01(hi), s2), hmul2_bits(sub23(hi), s2), xh.x, xh.y);
+    }
+    // -dmin * sum_j m_j * Sx_j : columns (2t, 2t+1) x Sx_hi, (2t+8, 2t+9) x Sx_lo
+    const uint32_t am = m1 | (m2 << 16);
+    uint32_t bs0 = 0, bs1 = 0;
+    if (sxblk) {
+        bs0 = *reinterpret_cast<const uint32_t*>(sxblk + 4 * t);
+        bs1 = *reinterpret_cast<const uint32_t*>(sxblk + 16 + 4 * t);
+    }
+    float n0 = 0.f, n1 = 0.f;
+    mma_16816(n0, n1, am, am, bs0, bs1);
+    const float d = f16_bits_to_f32(hd.x & 0xffffu) * 16384.0f;
+    const float dm = f16_bits_to_f32(hd.x >> 16) * TWO24;
+    f0 += d * c0 - dm * n0;
+    f1 += d * c1 - dm * n1;
+}
+
+// ---- Q6_K: one block of row g; every MMA step is one 16-element sub-block ----
+__device__ __forceinline__ void chunk_q6k(const uint8_t* blk, uint32_t e0, const uint8_t* xrow,
+                                          const uint8_t* sxblk, float* scr_row, int t, float& f0, float& f1) {
+    // the four scales this lane converts: sub-blocks 2t, 2t+1, 2t+8, 2t+9
+    const uint32_t packed = (ld_u16(blk + 192 + 2 * t) | (ld_u16(blk + 200 + 2 * t) << 16)) ^ 0x80808080u;
+    const __half2 off = __half2half2(__ushort_as_half(0x6480));          // 1152 = 1024 + 128
+    uint32_t h01 = __byte_perm(packed, 0x64646464u, 0x4140u), h23 = __byte_perm(packed, 0x64646464u, 0x4342u);
+    __half2 s01 = __hsub2(*reinterpret_cast<__half2*>(&h01), off);       // exact signed ints
+    __half2 s23 = __hsub2(*reinterpret_cast<__half2*>(&h23), off);
+    const float d = f16_bits_to_f32(ld_u16(blk + 208));
+    const float d24 = d * TWO24;
+    __syncwarp();                                                        // previous block's reads done
+    *reinterpret_cast<float2*>(scr_row + 2 * t) = make_float2(__low2float(s01) * d24, __high2float(s01) * d24);
+    *reinterpret_cast<float2*>(scr_row + 8 + 2 * t) = make_float2(__low2float(s23) * d24, __high2float(s23) * d24);
+    __syncwarp();
+    float sc[16];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float4 v = *reinterpret_cast<const float4*>(scr_row + 4 * i);
+        sc[4 * i] = v.x; sc[4 * i + 1] = v.y; sc[4 * i + 2] = v.z; sc[4 * i + 3] = v.w;
+    }
+    // bias: sum_s sc_s * Sx_s (hi and lo parts), later scaled by -32 d
+    float b0 = 0.f, b1 = 0.f;
+    {
+        uint32_t h0 = 0, h1 = 0, l0 = 0, l1 = 0;
+        if (sxblk) {                              // operand loads may diverge; the MMAs may not
+            h0 = *reinterpret_cast<const uint32_t*>(sxblk + 4 * t);
+            h1 = *reinterpret_cast<const uint32_t*>(sxblk + 16 + 4 * t);
+            l0 = *reinterpret_cast<const uint32_t*>(sxblk + 32 + 4 * t);
+            l1 = *reinterpret_cast<const uint32_t*>(sxblk + 48 + 4 * t);
+        }
+        const uint32_t a0 = *reinterpret_cast<uint32_t*>(&s01), a2 = *reinterpret_cast<uint32_t*>(&s23);
+        mma_16816(b0, b1, a0, a2, h0, h1);
+        mma_16816(b0, b1, a0, a2, l0, l1);
+    }
+#pragma unroll
+    for (int nh = 0; nh < 4; ++nh) {
+        const int n = nh >> 1, h = nh & 1;
+        const uint32_t qa = ld_u32_a2(blk + 64 * n + 16 * h + 4 * t);
+        const uint32_t qb = ld_u32_a2(blk + 64 * n + 32 + 16 * h + 4 * t);
+        const uint32_t qh = ld_u32_a2(blk + 128 + 32 * n + 16 * h + 4 * t);
+        uint32_t q[4];
+        q[0] = (qa & 0x0F0F0F0Fu) | ((qh << 4) & 0x30303030u);
+        q[1] = (qb & 0x0F0F0F0Fu) | ((qh << 2) & 0x30303030u);
+        q[2] = ((qa >> 4) & 0x0F0F0F0Fu) | (qh & 0x30303030u);
+        q[3] = ((qb >> 4) & 0x0F0F0F0Fu) | ((qh >> 2) & 0x30303030u);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const uint2 xv = ld_x4(xrow, e0 + 128 * n + 32 * k + 16 * h + 4 * t);
+            float c0 = 0.f, c1 = 0.f;
+            mma_16816(c0, c1, sub01(q[k]), sub23(q[k]), xv.x, xv.y);
+            const float s = sc[8 * n + 2 * k + h];
+            f0 += s * c0;
+            f1 += s * c1;
+        }
+    }
+    f0 -= 32.0f * d * b0;
+    f1 -= 32.0f * d * b1;
+}
+
+// ---- Q4_0 / Q8_0: eight 32-element blocks of row g; two MMA steps per block ----
+template <bool Q8>
+__device__ __forceinline__ void chunk_legacy(const uint8_t* blk0, uint32_t e0, const uint8_t* xrow,
+                                             const float* sxf, int t, float& f0, float& f1) {
+    constexpr int BB = Q8 ? 34 : 18;
+#pragma unroll
+    for (int b = 0; b < 8; ++b) {
+        const uint8_t* blk = blk0 + b * BB;
+        const uint32_t e = e0 + 32 * b;
+        const float d = f16_bits_to_f32(ld_u16(blk));
+        uint32_t w0, w1, ea, eb;
+        if constexpr (Q8) {
+            w0 = ld_u32_a2(blk + 2 + 8 * t) ^ 0x80808080u;      // code + 128
+            w1 = ld_u32_a2(blk + 6 + 8 * t) ^ 0x80808080u;
+            ea = e + 8 * t; eb = ea + 4;
+        } else {
+            const uint32_t w = ld_u32_a2(blk + 2 + 4 * t);
+            w0 = w & 0x0F0F0F0Fu;                                // elements 4t..4t+3
+            w1 = (w >> 4) & 0x0F0F0F0Fu;                         // elements 16+4t..
+            ea = e + 4 * t; eb = ea + 16;
+        }
+        const uint2 xa = ld_x4(xrow, ea), xb = ld_x4(xrow, eb);
+        float c0 = 0.f, c1 = 0.f;
+        mma_16816(c0, c1, sub01(w0), sub23(w0), xa.x, xa.y);
+        mma_16816(c0, c1, sub01(w1), sub23(w1), xb.x, xb.y);
+        const float2 sx = *reinterpret_cast<const float2*>(sxf + (e >> 5) * 8 + 2 * t);
+        constexpr float BIAS = Q8 ? 128.0f : 8.0f;
+        f0 += d * (TWO24 * c0 - BIAS * sx.x);
+        f1 += d * (TWO24 * c1 - BIAS * sx.y);
+    }
+}
+
+template <uint32_t TYPE>
+__global__ void __launch_bounds__(THREADS) gemv_mma_kernel(const MParams p) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    constexpr bool K45 = TYPE == HF2Q_TYPE_Q4_K || TYPE == HF2Q_TYPE_Q5_K;
+    constexpr bool Q6 = TYPE == HF2Q_TYPE_Q6_K;
+    constexpr bool LEG = TYPE == HF2Q_TYPE_Q4_0 || TYPE == HF2Q_TYPE_Q8_0;
+    constexpr BlockGeom G = block_geom(TYPE);
+    // bytes of x-sum panel per 256 elements and column: K45 8 x (hi,lo) f16, Q6 16 x (hi,lo) f16;
+    // Q4_0/Q8_0 keep f32 sums for all 8 columns per 32-element block
+    constexpr uint32_t SXB = K45 ? 32 : 64;
+
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem);
+    uint64_t* empty = full + MAX_STAGES;
+    uint8_t* ring = smem + 128;
+    const uint32_t stage_bytes = ROWS * p.pitch;
+    float* red = reinterpret_cast<float*>(ring + p.stages * stage_bytes);        // [2][CWARPS][8][8]
+    float* scr = red + 2 * CWARPS * 64;                                         // [CWARPS][8][16]
+    uint8_t* xh = reinterpret_cast<uint8_t*>(scr + CWARPS * 8 * 16);             // [nslots][xpitch]
+    uint8_t* sxp = xh + p.nslots * p.xpitch;
+    const uint32_t nblk_total = p.k >> 8;
+    const uint32_t sx_slot_bytes = nblk_total * SXB;                            // K45 / Q6 panels
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t slot = blockIdx.y;
+    const uint8_t* wbase = p.w;
+    uint32_t xrow_idx = 0;
+    bool slot_ok = true;
+    if (p.ids) {
+        const uint32_t e = p.ids[slot];
+        slot_ok = e < p.n_experts;
+        if (!slot_ok && threadIdx.x == 0) atomicOr(p.status, STATUS_BAD_EXPERT_ID);
+        wbase += static_cast<uint64_t>(slot_ok ? e : 0) * p.expert_stride;
+        xrow_idx = slot / p.top_k;
+    }
+    float* yout = p.y + static_cast<size_t>(slot) * p.n;
+
+    if (threadIdx.x == 0) {
+        for (uint32_t s = 0; s < p.stages; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], CWARPS); }
+        mbar_fence_init();
+    }
+    __syncthreads();
+
+    if (warp == CWARPS) {
+        // ---------------- producer warp: lane r copies row r of each stage ----------------
+        if (slot_ok) {
+            uint32_t it = 0;
+            bool alive = true;
+            for (uint32_t rg = blockIdx.x; rg < p.ngroups && alive; rg += gridDim.x) {
+                const uint32_t row0 = rg * ROWS;
+                const uint32_t nrows = min(static_cast<uint32_t>(ROWS), p.n - row0);
+                for (uint32_t s = 0; s < p.nslices; ++s, ++it) {
+                    const uint32_t st = it % p.stages;
+                    if (it >= p.stages) {
+                        alive = mbar_wait_bounded(&empty[st], ((it / p.stages) - 1) & 1, p.status);
+                        alive = __all_sync(0xffffffffu, alive);
+                        if (!alive) break;
+                    }
+                    const uint32_t off = s * p.slice_bytes;
+                    const uint32_t bytes = min(p.slice_bytes, p.row_bytes - off);
+                    if (lane == 0) mbar_arrive_expect_tx(&full[st], nrows * bytes);
+                    __syncwarp();
+                    if (static_cast<uint32_t>(lane) < nrows)
+                        bulk_g2s(ring + st * stage_bytes + lane * p.pitch,
+                                 wbase + static_cast<uint64_t>(row0 + lane) * p.row_bytes + off, bytes, &full[st]);
+                }
+            }
+        }
+        return;
+    }
+
+    // ---------------- consumers: build the f16 activation panel and its sub-block sums ------------
+    const int ctid = threadIdx.x;
+    {
+        const uint32_t k8 = p.k >> 3;
+        bool clipped = false;
+        for (uint32_t idx = ctid; idx < p.nslots * k8; idx += CT) {
+            const uint32_t s = idx / k8, e = (idx - s * k8) * 8;
+            float v[8];
+            if (p.x_bf16) {
+                const uint4 r = __ldg(reinterpret_cast<const uint4*>(
+                    static_cast<const __nv_bfloat16*>(p.x) + (static_cast<size_t>(xrow_idx) + s) * p.k + e));
+                const uint32_t rr[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    v[2 * j] = __uint_as_float(rr[j] << 16);
+                    v[2 * j + 1] = __uint_as_float(rr[j] & 0xffff0000u);
+                }
+            } else {
+                const float* src = static_cast<const float*>(p.x) + (static_cast<size_t>(xrow_idx) + (s >> 1)) * p.k + e;
+                const float4 a = __ldg(reinterpret_cast<const float4*>(src));
+                const float4 b = __ldg(reinterpret_cast<const float4*>(src + 4));
+                v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+            }
+            uint32_t out[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                float a = v[2 * j], b = v[2 * j + 1];
+                clipped |= (fabsf(a) > 65504.0f) | (fabsf(b) > 65504.0f);
+                a = fminf(fmaxf(a, -65504.0f), 65504.0f);
+                b = fminf(fmaxf(b, -65504.0f), 65504.0f);
+                __half ha = __float2half_rn(a), hb = __float2half_rn(b);
+                if (!p.x_bf16 && (s & 1)) {          // lo part of the f32 split
+                    ha = __float2half_rn(a - __half2float(ha));
+                    hb = __float2half_rn(b - __half2float(hb));
+                }
+                out[j] = static_cast<uint32_t>(__half_as_ushort(ha)) | (static_cast<uint32_t>(__half_as_ushort(hb)) << 16);
+            }
+            *reinterpret_cast<uint4*>(xh + s * p.xpitch + 2 * e) = make_uint4(out[0], out[1], out[2], out[3]);
+        }
+        if (clipped) atomicOr(p.status, STATUS_X_CLIPPED);
+    }
+    asm volatile("bar.sync 1, %0;" ::"n"(CT));
+    if constexpr (LEG) {
+        float* sxf = reinterpret_cast<float*>(sxp);
+        const uint32_t nb = p.k >> 5;
+        for (uint32_t idx = ctid; idx < nb * 8; idx += CT) {
+            const uint32_t b = idx >> 3, s = idx & 7;
+            float acc = 0.f;
+            if (s < p.nslots) {
+                const uint4* src = reinterpret_cast<const uint4*>(xh + s * p.xpitch + 64 * b);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const uint4 r = src[j];
+                    const uint32_t rr[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) {
+                        const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&rr[q]));
+                        acc += f.x + f.y;
+                    }
+                }
+            }
+            sxf[idx] = acc;
+        }
+    } else {
+        constexpr uint32_t SUB = K45 ? 32 : 16;            // elements per sub-block sum
+        constexpr uint32_t PER = 256 / SUB;                // sums per block: 8 or 16
+        const uint32_t nsub = p.k / SUB;
+        for (uint32_t idx = ctid; idx < p.nslots * nsub; idx += CT) {
+            const uint32_t s = idx / nsub, j = idx - s * nsub;
+            const uint4* src = reinterpret_cast<const uint4*>(xh + s * p.xpitch + 2 * SUB * j);
+            float acc = 0.f;
+#pragma unroll
+            for (uint32_t v = 0; v < SUB / 8; ++v) {
+                const uint4 r = src[v];
+                const uint32_t rr[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&rr[q]));
+                    acc += f.x + f.y;
+                }
+            }
+            const __half hi = __float2half_rn(acc);
+            const __half lo = __float2half_rn(acc - __half2float(hi));
+            __half* dst = reinterpret_cast<__half*>(sxp + s * sx_slot_bytes + (j / PER) * SXB);
+            dst[j % PER] = hi;
+            dst[PER + j % PER] = lo;
+        }
+    }
+    asm volatile("bar.sync 1, %0;" ::"n"(CT));
+    if (!slot_ok) {
+        for (uint32_t r = ctid; r < p.n; r += CT) yout[r] = 0.f;
+        return;
+    }
+
+    const int g = lane >> 2, t = lane & 3;
+    const bool col_live = static_cast<uint32_t>(g) < p.nslots;
+    const uint8_t* xrow = col_live ? xh + g * p.xpitch : nullptr;
+    const uint8_t* sxslot = col_live ? sxp + g * sx_slot_bytes : nullptr;
+    float* scr_row = scr + (warp * 8 + g) * 16;
+    (void)scr_row; (void)sxslot;
+
+    uint32_t it = 0, grp = 0;
+    bool alive = true;
+    for (uint32_t rg = blockIdx.x; rg < p.ngroups; rg += gridDim.x, ++grp) {
+        float f0 = 0.f, f1 = 0.f;
+        for (uint32_t s = 0; s < p.nslices; ++s, ++it) {
+            const uint32_t st = it % p.stages;
+            // a wait that gives up marks the warp dead; it keeps walking the loops (skipping waits
+            // and work) so the named barriers below are still reached by all 256 consumers
+            if (alive && !mbar_wait_bounded(&full[st], (it / p.stages) & 1, p.status)) alive = false;
+            const uint32_t kbase = s * SLICE_ELEMS;
+            const uint32_t nchunks = min(static_cast<uint32_t>(SLICE_ELEMS), p.k - kbase) >> 8;
+            if (alive && static_cast<uint32_t>(warp) < nchunks) {
+                const uint8_t* rowp = ring + st * stage_bytes + g * p.pitch;
+                const uint32_t e0 = kbase + 256 * warp;
+                if constexpr (K45) {
+                    chunk_k45<TYPE == HF2Q_TYPE_Q5_K>(rowp + warp * G.bytes, e0, xrow,
+                                                      sxslot ? sxslot + (e0 >> 8) * SXB : nullptr, t, f0, f1);
+                } else if constexpr (Q6) {
+                    chunk_q6k(rowp + warp * 210, e0, xrow, sxslot ? sxslot + (e0 >> 8) * SXB : nullptr, scr_row, t, f0, f1);
+                } else {
+                    chunk_legacy<TYPE == HF2Q_TYPE_Q8_0>(rowp + warp * 8 * G.bytes, e0, xrow,
+                                                         reinterpret_cast<const float*>(sxp), t, f0, f1);
+                }
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&empty[st]);
+        }
+        // combine the 8 warps' partial sums in a fixed order; double-buffered so one barrier suffices
+        float* rbuf = red + (grp & 1) * CWARPS * 64;
+        *reinterpret_cast<float2*>(rbuf + warp * 64 + g * 8 + 2 * t) = make_float2(f0, f1);
+        asm volatile("bar.sync 1, %0;" ::"n"(CT));
+        if (ctid < 64) {
+            const uint32_t r = ctid >> 3, c = ctid & 7;
+            const uint32_t row = rg * ROWS + r;
+            float v = 0.f;
+            if (p.x_bf16) {
+#pragma unroll
+                for (int w = 0; w < CWARPS; ++w) v += rbuf[w * 64 + r * 8 + c];
+                if (row < p.n && c < p.m) yout[static_cast<size_t>(c) * p.n + row] = v;
+            } else if (c < 4) {
+#pragma unroll
+                for (int w = 0; w < CWARPS; ++w) v += rbuf[w * 64 + r * 8 + 2 * c] + rbuf[w * 64 + r * 8 + 2 * c + 1];
+                if (row < p.n && c < p.m) yout[static_cast<size_t>(c) * p.n + row] = v;
+            }
+        }
+    }
+}
+
+// shared memory that does not depend on the ring depth
+size_t smem_base_bytes(uint32_t type, uint32_t k, uint32_t nslots) {
+    const bool k45 = type == HF2Q_TYPE_Q4_K || type == HF2Q_TYPE_Q5_K;
+    const bool leg = type == HF2Q_TYPE_Q4_0 || type == HF2Q_TYPE_Q8_0;
+    const size_t fixed = 128 + (2 * CWARPS * 64 + CWARPS * 8 * 16) * 4;
+    const size_t xbytes = static_cast<size_t>(nslots) * (2 * static_cast<size_t>(k) + 32);
+    const size_t sxbytes = leg ? static_cast<size_t>(k / 32) * 8 * 4
+                               : static_cast<size_t>(nslots) * (k / 256) * (k45 ? 32 : 64);
+    return fixed + xbytes + sxbytes;
+}
+size_t stage_bytes_of(uint32_t type, uint32_t k) {
+    const BlockGeom g = block_geom(type);
+    uint32_t slice = SLICE_ELEMS / g.elems * g.bytes;
+    const uint32_t row = k / g.elems * g.bytes;
+    if (slice > row) slice = row;
+    return static_cast<size_t>(ROWS) * (slice + 16);
+}
+
+template <uint32_t TYPE>
+cudaError_t launch_mma_t(MParams p, uint32_t slots, const DeviceInfo& dev, cudaStream_t st) {
+    auto kern = gemv_mma_kernel<TYPE>;
+    const size_t stage = static_cast<size_t>(ROWS) * p.pitch;
+    const size_t limit = static_cast<size_t>(dev.max_smem_optin);
+    const size_t base = smem_base_bytes(TYPE, p.k, p.nslots);
+    if (base + 2 * stage > limit) return cudaErrorInvalidConfiguration;
+    // deepest ring (<= 4 stages) that still lets two CTAs share an SM; else one CTA with 4 stages
+    const size_t half = (limit + 1024) / 2 - 1024;     // per-CTA budget for 2 CTAs/SM (1 KB reserved each)
+    uint32_t stages = 0;
+    for (uint32_t s = MAX_STAGES; s >= 3; --s)
+        if (base + s * stage <= half) { stages = s; break; }
+    if (!stages) {
+        stages = MAX_STAGES;
+        while (base + stages * stage > limit) --stages;
+    }
+    p.stages = stages;
+    const size_t smem = base + stages * stage;
+
+    static std::mutex mu;
+    static bool attr_set = false;
+    static size_t cached_smem = ~static_cast<size_t>(0);
+    static int cached_per_sm = 1;
+    int per_sm;
+    {
+        std::lock_guard<std::mutex> lock(mu);
+        if (!attr_set) {
+            cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, dev.max_smem_optin);
+            if (e != cudaSuccess) return e;
+            attr_set = true;
+        }
+        if (cached_smem != smem) {
+            int q = 1;
+            cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&q, kern, THREADS, smem);
+            if (e != cudaSuccess) return e;
+            cached_per_sm = q < 1 ? 1 : q;
+            cached_smem = smem;
+        }
+        per_sm = cached_per_sm;
+    }
+    const uint32_t want = static_cast<uint32_t>(dev.sm_count) * per_sm;
+    uint32_t gx = (want + slots - 1) / slots;
+    if (gx > p.ngroups) gx = p.ngroups;
+    if (gx < 1) gx = 1;
+    kern<<<dim3(gx, slots), THREADS, smem, st>>>(p);
+    return cudaGetLastError();
+}
+
+}  // namespace
+
+bool gemv_mma_supported(const GemvArgs& a) {
+    const BlockGeom g = block_geom(a.type);
+    const uint64_t row_bytes = static_cast<uint64_t>(a.k) / g.elems * g.bytes;
+    return a.k % 256 == 0 && row_bytes % 16 == 0 && a.expert_stride % 16 == 0 &&
+           reinterpret_cast<uintptr_t>(a.w) % 16 == 0 && reinterpret_cast<uintptr_t>(a.x) % 16 == 0;
+}
+
+// Activation rows one launch can take: 8 MMA columns (bf16: one per row, f32: two per row), capped
+// by what fits in shared memory next to a ring of at least 3 stages.
+uint32_t gemv_mma_max_rows(uint32_t type, uint32_t k, uint32_t x_dtype, const DeviceInfo& dev) {
+    const uint32_t per_row = x_dtype == HF2Q_DT_BF16 ? 1 : 2;
+    uint32_t rows = 8 / per_row;
+    while (rows > 0 && smem_base_bytes(type, k, rows * per_row) + 3 * stage_bytes_of(type, k) >
+                           static_cast<size_t>(dev.max_smem_optin))
+        --rows;
+    return rows;
+}
+
+// One launch: bf16 activations, m <= 8; f32 activations, m <= 4 (hi/lo split on two columns).
+cudaError_t launch_gemv_mma(const GemvArgs& a, const DeviceInfo& dev, cudaStream_t st) {
+    const BlockGeom g = block_geom(a.type);
+    MParams p{};
+    p.w = static_cast<const uint8_t*>(a.w);
+    p.x = a.x;
+    p.y = a.y;
+    p.ids = a.ids;
+    p.expert_stride = a.expert_stride;
+    p.x_bf16 = a.x_dtype == HF2Q_DT_BF16;
+    p.m = a.m;
+    p.nslots = p.x_bf16 ? a.m : 2 * a.m;
+    if (p.nslots > 8) return cudaErrorInvalidValue;
+    p.n = a.n;
+    p.k = a.k;
+    p.top_k = a.top_k ? a.top_k : 1;
+    p.n_experts = a.n_experts;
+    p.row_bytes = a.k / g.elems * g.bytes;
+    p.slice_bytes = SLICE_ELEMS / g.elems * g.bytes;
+    if (p.slice_bytes > p.row_bytes) p.slice_bytes = p.row_bytes;
+    p.pitch = p.slice_bytes + 16;                 // rows land 4 banks apart
+    p.nslices = (a.k + SLICE_ELEMS - 1) / SLICE_ELEMS;
+    p.ngroups = (a.n + ROWS - 1) / ROWS;
+    p.xpitch = 2 * a.k + 32;                      // activation rows land 8 banks apart
+    p.status = a.status;
+    switch (a.type) {
+        case HF2Q_TYPE_Q4_0: return launch_mma_t<HF2Q_TYPE_Q4_0>(p, a.slots, dev, st);
+        case HF2Q_TYPE_Q8_0: return launch_mma_t<HF2Q_TYPE_Q8_0>(p, a.slots, dev, st);
+        case HF2Q_TYPE_Q4_K: return launch_mma_t<HF2Q_TYPE_Q4_K>(p, a.slots, dev, st);
+        case HF2Q_TYPE_Q5_K: return launch_mma_t<HF2Q_TYPE_Q5_K>(p, a.slots, dev, st);
+        case HF2Q_TYPE_Q6_K: return launch_mma_t<HF2Q_TYPE_Q6_K>(p, a.slots, dev, st);
+        default: return cudaErrorInvalidValue;
+    }
+}
+
+}  // namespace hf2q

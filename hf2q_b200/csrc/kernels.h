@@ -31,6 +31,12 @@ struct DeviceInfo {
 };
 cudaError_t launch_gemv(const GemvArgs& a, const DeviceInfo& dev, cudaStream_t st, int* launches);
 
+// Tensor-core (warp MMA) variant of the same product (k1_gemv_mma.cu).  One launch handles up to
+// gemv_mma_max_rows() activation rows; needs 16-byte aligned rows and k % 256 == 0.
+bool gemv_mma_supported(const GemvArgs& a);
+uint32_t gemv_mma_max_rows(uint32_t type, uint32_t k, uint32_t x_dtype, const DeviceInfo& dev);
+cudaError_t launch_gemv_mma(const GemvArgs& a, const DeviceInfo& dev, cudaStream_t st);
+
 // softmax -> top-k -> renormalise (moe_router.cu)
 cudaError_t launch_softmax_topk(const float* logits, uint32_t* ids, float* weights,
                                 uint32_t n_tokens, uint32_t n_experts, uint32_t top_k,
