@@ -362,7 +362,7 @@ def main() -> None:
     roofline = {
         "bound": "hbm", "achieved": round(per_gpu, 1), "peak": peak, "unit": "GB/s",
         "frac": round(per_gpu / peak, 4), "peak_source": f"of {peak_kind}",
-        "kernel": "gemv_stream_kernel<Q6_K, M in {1,4,8}>",
+        "kernel": "gemv_mma_kernel<Q6_K>, m in {1,4,8}",
         "traffic": None if ratio is None else round(ratio * mean_launch_bytes),
         "algorithmic_bytes_per_launch_mean": round(mean_launch_bytes),
         "frac_of_nominal_8TBps": round(per_gpu / 8000.0, 4),

@@ -42,12 +42,12 @@ namespace hf2q {
 
 namespace {
 
-constexpr int ROWS = 8;
-constexpr int CWARPS = 8;
+constexpr int ROWS = 16;               // weight rows per stage = rows of one MMA tile
+constexpr int CWARPS = 16;             // consumer warps; each takes 128 elements x 16 rows per stage
 constexpr int CT = CWARPS * 32;
 constexpr int THREADS = CT + 32;
 constexpr int SLICE_ELEMS = 2048;
-constexpr int MAX_STAGES = 4;
+constexpr int MAX_STAGES = 8;
 
 struct MParams {
     const uint8_t* w;
@@ -65,13 +65,22 @@ struct MParams {
     uint32_t* status;
 };
 
-__device__ __forceinline__ void mma_16816(float& c0, float& c1, uint32_t a0, uint32_t a2, uint32_t b0,
-                                          uint32_t b1) {
-    float c2 = 0.f, c3 = 0.f;    // rows 8..15 of the tile are unused (their A registers are zero)
+// m16n8k16, f16 inputs, f32 accumulate.  Lane (g = lane/4, t = lane%4) holds A for rows g (a0, a2)
+// and g+8 (a1, a3) at k-columns {2t, 2t+1} (a0, a1) and {2t+8, 2t+9} (a2, a3); B for column g at
+// the same k positions; C/D rows g (c[0], c[1]) and g+8 (c[2], c[3]) at columns 2t, 2t+1.
+__device__ __forceinline__ void mma_acc(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                        uint32_t b0, uint32_t b1) {
     asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
         "{%0,%1,%2,%3};"
-        : "+f"(c0), "+f"(c1), "+f"(c2), "+f"(c3)
-        : "r"(a0), "r"(0u), "r"(a2), "r"(0u), "r"(b0), "r"(b1));
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void mma_new(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                        uint32_t b0, uint32_t b1) {
+    asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+        "{%10,%10,%10,%10};"
+        : "=f"(c[0]), "=f"(c[1]), "=f"(c[2]), "=f"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(0.f));
 }
 // bytes (b0,b1) / (b2,b3) of w as two f16 subnormals each: value = byte * 2^-24
 __device__ __forceinline__ uint32_t sub01(uint32_t w) { return __byte_perm(w, 0u, 0x4140u); }
@@ -81,151 +90,191 @@ __device__ __forceinline__ uint32_t hmul2_bits(uint32_t a, uint32_t b) {
     return *reinterpret_cast<uint32_t*>(&r);
 }
 __device__ __forceinline__ uint2 ld_x4(const uint8_t* xrow, uint32_t e) {
-    return xrow ? *reinterpret_cast<const uint2*>(xrow + 2 * e) : make_uint2(0u, 0u);
+    return *reinterpret_cast<const uint2*>(xrow + 2 * e);
 }
 constexpr float TWO24 = 16777216.0f;
 
-// ---- Q4_K / Q5_K: one 256-element block of row g, lane t owns chunk t (sub-blocks 2t, 2t+1) ----
+// ---- Q4_K / Q5_K: half a block (128 elements = chunks 2*half, 2*half+1) of rows g and g+8.
+// Lane t owns 16 bytes of qs per row: chunk c = 2*half + (t>>1), bytes 16*(t&1)..+15, i.e. 16
+// elements of sub-block 2c (low nibbles) and 16 of sub-block 2c+1 (high nibbles).
 template <bool Q5>
-__device__ __forceinline__ void chunk_k45(const uint8_t* blk, uint32_t e0, const uint8_t* xrow,
-                                          const uint8_t* sxblk, int t, float& f0, float& f1) {
-    constexpr int QS = Q5 ? 48 : 16;
-    const uint4 hd = *reinterpret_cast<const uint4*>(blk);
-    const uint4 qa = *reinterpret_cast<const uint4*>(blk + QS + 32 * t);
-    const uint4 qb = *reinterpret_cast<const uint4*>(blk + QS + 32 * t + 16);
-    const uint32_t qv[8] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w};
-    uint32_t gv[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-    if constexpr (Q5) {
-        const uint4 ga = *reinterpret_cast<const uint4*>(blk + 16);
-        const uint4 gb = *reinterpret_cast<const uint4*>(blk + 32);
-        gv[0] = ga.x; gv[1] = ga.y; gv[2] = ga.z; gv[3] = ga.w;
-        gv[4] = gb.x; gv[5] = gb.y; gv[6] = gb.z; gv[7] = gb.w;
-    }
-    uint32_t sc1, m1, sc2, m2;
-    scale_min_k4(2 * t, hd.y, hd.z, hd.w, sc1, m1);
-    scale_min_k4(2 * t + 1, hd.y, hd.z, hd.w, sc2, m2);
-    // scale * 2^10 as f16x2 (<= 64512): code*2^-24 * scale*2^10 = code*scale*2^-14, exact
-    const __half2 s1h = __half2half2(__uint2half_rn(sc1 << 10));
-    const __half2 s2h = __half2half2(__uint2half_rn(sc2 << 10));
-    const uint32_t s1 = *reinterpret_cast<const uint32_t*>(&s1h);
-    const uint32_t s2 = *reinterpret_cast<const uint32_t*>(&s2h);
-    float c0 = 0.f, c1 = 0.f;
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-        uint32_t lo = qv[i] & 0x0F0F0F0Fu, hi = (qv[i] >> 4) & 0x0F0F0F0Fu;
+struct K45Row {
+    uint32_t qv[4], gv[4], s1, s2, am;
+    float d, dm;
+    __device__ __forceinline__ void load(const uint8_t* blk, int c, int hb) {
+        constexpr int QS = Q5 ? 48 : 16;
+        const uint4 hd = *reinterpret_cast<const uint4*>(blk);
+        const uint4 qa = *reinterpret_cast<const uint4*>(blk + QS + 32 * c + 16 * hb);
+        qv[0] = qa.x; qv[1] = qa.y; qv[2] = qa.z; qv[3] = qa.w;
         if constexpr (Q5) {
-            lo |= ((gv[i] >> (2 * t)) & 0x01010101u) << 4;
-            hi |= ((gv[i] >> (2 * t + 1)) & 0x01010101u) << 4;
+            const uint4 ga = *reinterpret_cast<const uint4*>(blk + 16 + 16 * hb);
+            gv[0] = ga.x; gv[1] = ga.y; gv[2] = ga.z; gv[3] = ga.w;
         }
-        const uint2 xl = ld_x4(xrow, e0 + 64 * t + 4 * i);
-        mma_16816(c0, c1, hmul2_bits(sub01(lo), s1), hmul2_bits(sub23(lo), s1), xl.x, xl.y);
-        const uint2 xh = ld_x4(xrow, e0 + 64 * t + 32 + 4 * i);
-        mma_16816(c0, c1, hmul2_bits(sub01(hi), s2), hmul2_bits(sub23(hi), s2), xh.x, xh.y);
+        uint32_t sc1, m1, sc2, m2;
+        scale_min_k4(2 * c, hd.y, hd.z, hd.w, sc1, m1);
+        scale_min_k4(2 * c + 1, hd.y, hd.z, hd.w, sc2, m2);
+        // scale * 2^10 as f16x2 (<= 64512): code*2^-24 * scale*2^10 = code*scale*2^-14, exact
+        const __half2 s1h = __half2half2(__uint2half_rn(sc1 << 10));
+        const __half2 s2h = __half2half2(__uint2half_rn(sc2 << 10));
+        s1 = *reinterpret_cast<const uint32_t*>(&s1h);
+        s2 = *reinterpret_cast<const uint32_t*>(&s2h);
+        am = hb ? 0u : (m1 | (m2 << 16));
+        d = f16_bits_to_f32(hd.x & 0xffffu) * 16384.0f;
+        dm = f16_bits_to_f32(hd.x >> 16) * TWO24;
     }
-    // -dmin * sum_j m_j * Sx_j : columns (2t, 2t+1) x Sx_hi, (2t+8, 2t+9) x Sx_lo
-    const uint32_t am = m1 | (m2 << 16);
-    uint32_t bs0 = 0, bs1 = 0;
-    if (sxblk) {
-        bs0 = *reinterpret_cast<const uint32_t*>(sxblk + 4 * t);
-        bs1 = *reinterpret_cast<const uint32_t*>(sxblk + 16 + 4 * t);
+    __device__ __forceinline__ void codes(int i, int c, uint32_t& lo, uint32_t& hi) const {
+        lo = qv[i] & 0x0F0F0F0Fu;
+        hi = (qv[i] >> 4) & 0x0F0F0F0Fu;
+        if constexpr (Q5) {
+            lo |= ((gv[i] >> (2 * c)) & 0x01010101u) << 4;
+            hi |= ((gv[i] >> (2 * c + 1)) & 0x01010101u) << 4;
+        }
     }
-    float n0 = 0.f, n1 = 0.f;
-    mma_16816(n0, n1, am, am, bs0, bs1);
-    const float d = f16_bits_to_f32(hd.x & 0xffffu) * 16384.0f;
-    const float dm = f16_bits_to_f32(hd.x >> 16) * TWO24;
-    f0 += d * c0 - dm * n0;
-    f1 += d * c1 - dm * n1;
-}
+};
 
-// ---- Q6_K: one block of row g; every MMA step is one 16-element sub-block ----
-__device__ __forceinline__ void chunk_q6k(const uint8_t* blk, uint32_t e0, const uint8_t* xrow,
-                                          const uint8_t* sxblk, float* scr_row, int t, float& f0, float& f1) {
-    // the four scales this lane converts: sub-blocks 2t, 2t+1, 2t+8, 2t+9
-    const uint32_t packed = (ld_u16(blk + 192 + 2 * t) | (ld_u16(blk + 200 + 2 * t) << 16)) ^ 0x80808080u;
-    const __half2 off = __half2half2(__ushort_as_half(0x6480));          // 1152 = 1024 + 128
-    uint32_t h01 = __byte_perm(packed, 0x64646464u, 0x4140u), h23 = __byte_perm(packed, 0x64646464u, 0x4342u);
-    __half2 s01 = __hsub2(*reinterpret_cast<__half2*>(&h01), off);       // exact signed ints
-    __half2 s23 = __hsub2(*reinterpret_cast<__half2*>(&h23), off);
-    const float d = f16_bits_to_f32(ld_u16(blk + 208));
-    const float d24 = d * TWO24;
-    __syncwarp();                                                        // previous block's reads done
-    *reinterpret_cast<float2*>(scr_row + 2 * t) = make_float2(__low2float(s01) * d24, __high2float(s01) * d24);
-    *reinterpret_cast<float2*>(scr_row + 8 + 2 * t) = make_float2(__low2float(s23) * d24, __high2float(s23) * d24);
-    __syncwarp();
-    float sc[16];
+template <bool Q5>
+__device__ __forceinline__ void half_k45(const uint8_t* blk0, const uint8_t* blk1, int half, uint32_t e0,
+                                         const uint8_t* xrow, const uint8_t* sxblk, int t, float (&f)[4]) {
+    const int c = 2 * half + (t >> 1), hb = t & 1;
+    K45Row<Q5> r0, r1;
+    r0.load(blk0, c, hb);
+    r1.load(blk1, c, hb);
+    const uint32_t eb = e0 + 64 * c + 16 * hb;
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
-        const float4 v = *reinterpret_cast<const float4*>(scr_row + 4 * i);
-        sc[4 * i] = v.x; sc[4 * i + 1] = v.y; sc[4 * i + 2] = v.z; sc[4 * i + 3] = v.w;
+        uint32_t lo0, hi0, lo1, hi1;
+        r0.codes(i, c, lo0, hi0);
+        r1.codes(i, c, lo1, hi1);
+        const uint2 xl = ld_x4(xrow, eb + 4 * i);
+        mma_acc(acc, hmul2_bits(sub01(lo0), r0.s1), hmul2_bits(sub01(lo1), r1.s1),
+                hmul2_bits(sub23(lo0), r0.s1), hmul2_bits(sub23(lo1), r1.s1), xl.x, xl.y);
+        const uint2 xh = ld_x4(xrow, eb + 32 + 4 * i);
+        mma_acc(acc, hmul2_bits(sub01(hi0), r0.s2), hmul2_bits(sub01(hi1), r1.s2),
+                hmul2_bits(sub23(hi0), r0.s2), hmul2_bits(sub23(hi1), r1.s2), xh.x, xh.y);
     }
-    // bias: sum_s sc_s * Sx_s (hi and lo parts), later scaled by -32 d
-    float b0 = 0.f, b1 = 0.f;
+    // -dmin * sum_j m_j * Sx_j over this half's four sub-blocks: lanes with (t&1)==0 carry
+    // (m_2c, m_2c+1) against Sx_hi on k-columns (2t, 2t+1) and against Sx_lo on (2t+8, 2t+9);
+    // odd lanes carry zeros.  The panel stores, per block, hi[8] then lo[8] (f16).
+    const uint32_t bs0 = *reinterpret_cast<const uint32_t*>(sxblk + 4 * c);
+    const uint32_t bs1 = *reinterpret_cast<const uint32_t*>(sxblk + 16 + 4 * c);
+    float mn[4];
+    mma_new(mn, r0.am, r1.am, r0.am, r1.am, bs0, bs1);
+    f[0] += r0.d * acc[0] - r0.dm * mn[0];
+    f[1] += r0.d * acc[1] - r0.dm * mn[1];
+    f[2] += r1.d * acc[2] - r1.dm * mn[2];
+    f[3] += r1.d * acc[3] - r1.dm * mn[3];
+}
+
+// ---- Q6_K: half n (128 elements, sub-blocks 8n..8n+7) of one block of rows g and g+8; every MMA
+// step is one 16-element sub-block, so d*scale is applied to each step's result.  ALIGNED: the
+// block starts on a 4-byte boundary (even block index), so 32-bit fields load in one instruction.
+template <bool ALIGNED>
+__device__ __forceinline__ uint32_t ld_w(const uint8_t* p) {
+    if constexpr (ALIGNED) return *reinterpret_cast<const uint32_t*>(p);
+    else return ld_u32_a2(p);
+}
+// converts this lane's two scales (sub-blocks 8n+2t, 8n+2t+1) of one row, publishes d*2^24*scale
+// to the row's scratch line and returns the exact f16x2 scales for the bias MMA
+__device__ __forceinline__ uint32_t q6_scales(const uint8_t* blk, int n, int t, float* scr_row, float& d) {
+    const uint32_t packed = ld_u16(blk + 192 + 8 * n + 2 * t) ^ 0x8080u;
+    const __half2 off = __half2half2(__ushort_as_half(0x6480));          // 1152 = 1024 + 128
+    uint32_t h01 = __byte_perm(packed, 0x64646464u, 0x4140u);
+    __half2 s01 = __hsub2(*reinterpret_cast<__half2*>(&h01), off);       // exact signed ints
+    d = f16_bits_to_f32(ld_u16(blk + 208));
+    const float d24 = d * TWO24;
+    *reinterpret_cast<float2*>(scr_row + 2 * t) = make_float2(__low2float(s01) * d24, __high2float(s01) * d24);
+    return *reinterpret_cast<uint32_t*>(&s01);
+}
+template <bool ALIGNED>
+__device__ __forceinline__ void q6_codes(const uint8_t* blk, int n, int h, int t, uint32_t (&q)[4]) {
+    const uint32_t qa = ld_w<ALIGNED>(blk + 64 * n + 16 * h + 4 * t);
+    const uint32_t qb = ld_w<ALIGNED>(blk + 64 * n + 32 + 16 * h + 4 * t);
+    const uint32_t qh = ld_w<ALIGNED>(blk + 128 + 32 * n + 16 * h + 4 * t);
+    q[0] = (qa & 0x0F0F0F0Fu) | ((qh << 4) & 0x30303030u);
+    q[1] = (qb & 0x0F0F0F0Fu) | ((qh << 2) & 0x30303030u);
+    q[2] = ((qa >> 4) & 0x0F0F0F0Fu) | (qh & 0x30303030u);
+    q[3] = ((qb >> 4) & 0x0F0F0F0Fu) | ((qh >> 2) & 0x30303030u);
+}
+template <bool ALIGNED>
+__device__ __forceinline__ void half_q6k(const uint8_t* blk0, const uint8_t* blk1, int n, uint32_t e0,
+                                         const uint8_t* xrow, const uint8_t* sxblk, float* scr0, float* scr1,
+                                         int t, float (&f)[4]) {
+    float d0, d1;
+    __syncwarp();                                                        // previous reads of scratch done
+    const uint32_t sa0 = q6_scales(blk0, n, t, scr0, d0);
+    const uint32_t sa1 = q6_scales(blk1, n, t, scr1, d1);
+    __syncwarp();
+    float sc0[8], sc1[8];
     {
-        uint32_t h0 = 0, h1 = 0, l0 = 0, l1 = 0;
-        if (sxblk) {                              // operand loads may diverge; the MMAs may not
-            h0 = *reinterpret_cast<const uint32_t*>(sxblk + 4 * t);
-            h1 = *reinterpret_cast<const uint32_t*>(sxblk + 16 + 4 * t);
-            l0 = *reinterpret_cast<const uint32_t*>(sxblk + 32 + 4 * t);
-            l1 = *reinterpret_cast<const uint32_t*>(sxblk + 48 + 4 * t);
-        }
-        const uint32_t a0 = *reinterpret_cast<uint32_t*>(&s01), a2 = *reinterpret_cast<uint32_t*>(&s23);
-        mma_16816(b0, b1, a0, a2, h0, h1);
-        mma_16816(b0, b1, a0, a2, l0, l1);
+        const float4 a = *reinterpret_cast<const float4*>(scr0), b = *reinterpret_cast<const float4*>(scr0 + 4);
+        sc0[0] = a.x; sc0[1] = a.y; sc0[2] = a.z; sc0[3] = a.w; sc0[4] = b.x; sc0[5] = b.y; sc0[6] = b.z; sc0[7] = b.w;
+        const float4 c = *reinterpret_cast<const float4*>(scr1), e = *reinterpret_cast<const float4*>(scr1 + 4);
+        sc1[0] = c.x; sc1[1] = c.y; sc1[2] = c.z; sc1[3] = c.w; sc1[4] = e.x; sc1[5] = e.y; sc1[6] = e.z; sc1[7] = e.w;
     }
+    // bias: sum_s sc_s * Sx_s (hi on k-columns 2t,2t+1; lo on 2t+8,2t+9), later scaled by -32 d.
+    // The panel stores, per block, hi[16] then lo[16] (f16).
+    float bias[4];
+    mma_new(bias, sa0, sa1, sa0, sa1, *reinterpret_cast<const uint32_t*>(sxblk + 16 * n + 4 * t),
+            *reinterpret_cast<const uint32_t*>(sxblk + 32 + 16 * n + 4 * t));
 #pragma unroll
-    for (int nh = 0; nh < 4; ++nh) {
-        const int n = nh >> 1, h = nh & 1;
-        const uint32_t qa = ld_u32_a2(blk + 64 * n + 16 * h + 4 * t);
-        const uint32_t qb = ld_u32_a2(blk + 64 * n + 32 + 16 * h + 4 * t);
-        const uint32_t qh = ld_u32_a2(blk + 128 + 32 * n + 16 * h + 4 * t);
-        uint32_t q[4];
-        q[0] = (qa & 0x0F0F0F0Fu) | ((qh << 4) & 0x30303030u);
-        q[1] = (qb & 0x0F0F0F0Fu) | ((qh << 2) & 0x30303030u);
-        q[2] = ((qa >> 4) & 0x0F0F0F0Fu) | (qh & 0x30303030u);
-        q[3] = ((qb >> 4) & 0x0F0F0F0Fu) | ((qh >> 2) & 0x30303030u);
+    for (int h = 0; h < 2; ++h) {
+        uint32_t q0[4], q1[4];
+        q6_codes<ALIGNED>(blk0, n, h, t, q0);
+        q6_codes<ALIGNED>(blk1, n, h, t, q1);
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
             const uint2 xv = ld_x4(xrow, e0 + 128 * n + 32 * k + 16 * h + 4 * t);
-            float c0 = 0.f, c1 = 0.f;
-            mma_16816(c0, c1, sub01(q[k]), sub23(q[k]), xv.x, xv.y);
-            const float s = sc[8 * n + 2 * k + h];
-            f0 += s * c0;
-            f1 += s * c1;
+            float c[4];
+            mma_new(c, sub01(q0[k]), sub01(q1[k]), sub23(q0[k]), sub23(q1[k]), xv.x, xv.y);
+            f[0] += sc0[2 * k + h] * c[0];
+            f[1] += sc0[2 * k + h] * c[1];
+            f[2] += sc1[2 * k + h] * c[2];
+            f[3] += sc1[2 * k + h] * c[3];
         }
     }
-    f0 -= 32.0f * d * b0;
-    f1 -= 32.0f * d * b1;
+    f[0] -= 32.0f * d0 * bias[0];
+    f[1] -= 32.0f * d0 * bias[1];
+    f[2] -= 32.0f * d1 * bias[2];
+    f[3] -= 32.0f * d1 * bias[3];
 }
 
-// ---- Q4_0 / Q8_0: eight 32-element blocks of row g; two MMA steps per block ----
+// ---- Q4_0 / Q8_0: four 32-element blocks of rows g and g+8; two MMA steps per block ----
 template <bool Q8>
-__device__ __forceinline__ void chunk_legacy(const uint8_t* blk0, uint32_t e0, const uint8_t* xrow,
-                                             const float* sxf, int t, float& f0, float& f1) {
+__device__ __forceinline__ void legacy_codes(const uint8_t* blk, int t, uint32_t& w0, uint32_t& w1) {
+    if constexpr (Q8) {
+        w0 = ld_u32_a2(blk + 2 + 8 * t) ^ 0x80808080u;      // code + 128, elements 8t..8t+3
+        w1 = ld_u32_a2(blk + 6 + 8 * t) ^ 0x80808080u;      // elements 8t+4..8t+7
+    } else {
+        const uint32_t w = ld_u32_a2(blk + 2 + 4 * t);
+        w0 = w & 0x0F0F0F0Fu;                                // elements 4t..4t+3
+        w1 = (w >> 4) & 0x0F0F0F0Fu;                         // elements 16+4t..
+    }
+}
+template <bool Q8>
+__device__ __forceinline__ void half_legacy(const uint8_t* p0, const uint8_t* p1, uint32_t e0,
+                                            const uint8_t* xrow, const float* sxf, int t, float (&f)[4]) {
     constexpr int BB = Q8 ? 34 : 18;
+    constexpr float BIAS = Q8 ? 128.0f : 8.0f;
 #pragma unroll
-    for (int b = 0; b < 8; ++b) {
-        const uint8_t* blk = blk0 + b * BB;
+    for (int b = 0; b < 4; ++b) {
+        const uint8_t* blk0 = p0 + b * BB;
+        const uint8_t* blk1 = p1 + b * BB;
         const uint32_t e = e0 + 32 * b;
-        const float d = f16_bits_to_f32(ld_u16(blk));
-        uint32_t w0, w1, ea, eb;
-        if constexpr (Q8) {
-            w0 = ld_u32_a2(blk + 2 + 8 * t) ^ 0x80808080u;      // code + 128
-            w1 = ld_u32_a2(blk + 6 + 8 * t) ^ 0x80808080u;
-            ea = e + 8 * t; eb = ea + 4;
-        } else {
-            const uint32_t w = ld_u32_a2(blk + 2 + 4 * t);
-            w0 = w & 0x0F0F0F0Fu;                                // elements 4t..4t+3
-            w1 = (w >> 4) & 0x0F0F0F0Fu;                         // elements 16+4t..
-            ea = e + 4 * t; eb = ea + 16;
-        }
+        const float d0 = f16_bits_to_f32(ld_u16(blk0)), d1 = f16_bits_to_f32(ld_u16(blk1));
+        uint32_t u0, u1, v0, v1;
+        legacy_codes<Q8>(blk0, t, u0, u1);
+        legacy_codes<Q8>(blk1, t, v0, v1);
+        const uint32_t ea = Q8 ? e + 8 * t : e + 4 * t, eb = Q8 ? ea + 4 : ea + 16;
         const uint2 xa = ld_x4(xrow, ea), xb = ld_x4(xrow, eb);
-        float c0 = 0.f, c1 = 0.f;
-        mma_16816(c0, c1, sub01(w0), sub23(w0), xa.x, xa.y);
-        mma_16816(c0, c1, sub01(w1), sub23(w1), xb.x, xb.y);
+        float c[4];
+        mma_new(c, sub01(u0), sub01(v0), sub23(u0), sub23(v0), xa.x, xa.y);
+        mma_acc(c, sub01(u1), sub01(v1), sub23(u1), sub23(v1), xb.x, xb.y);
         const float2 sx = *reinterpret_cast<const float2*>(sxf + (e >> 5) * 8 + 2 * t);
-        constexpr float BIAS = Q8 ? 128.0f : 8.0f;
-        f0 += d * (TWO24 * c0 - BIAS * sx.x);
-        f1 += d * (TWO24 * c1 - BIAS * sx.y);
+        f[0] += d0 * (TWO24 * c[0] - BIAS * sx.x);
+        f[1] += d0 * (TWO24 * c[1] - BIAS * sx.y);
+        f[2] += d1 * (TWO24 * c[2] - BIAS * sx.x);
+        f[3] += d1 * (TWO24 * c[3] - BIAS * sx.y);
     }
 }
 
@@ -244,9 +293,9 @@ __global__ void __launch_bounds__(THREADS) gemv_mma_kernel(const MParams p) {
     uint64_t* empty = full + MAX_STAGES;
     uint8_t* ring = smem + 128;
     const uint32_t stage_bytes = ROWS * p.pitch;
-    float* red = reinterpret_cast<float*>(ring + p.stages * stage_bytes);        // [2][CWARPS][8][8]
-    float* scr = red + 2 * CWARPS * 64;                                         // [CWARPS][8][16]
-    uint8_t* xh = reinterpret_cast<uint8_t*>(scr + CWARPS * 8 * 16);             // [nslots][xpitch]
+    float* red = reinterpret_cast<float*>(ring + p.stages * stage_bytes);        // [2][CWARPS][16][8]
+    float* scr = red + 2 * CWARPS * 128;                                        // [CWARPS][16][8]
+    uint8_t* xh = reinterpret_cast<uint8_t*>(scr + CWARPS * 16 * 8);             // [nslots][xpitch]
     uint8_t* sxp = xh + p.nslots * p.xpitch;
     const uint32_t nblk_total = p.k >> 8;
     const uint32_t sx_slot_bytes = nblk_total * SXB;                            // K45 / Q6 panels
@@ -393,55 +442,65 @@ __global__ void __launch_bounds__(THREADS) gemv_mma_kernel(const MParams p) {
         return;
     }
 
+    // Lane (g, t): weight row g, MMA column g.  Columns beyond nslots alias column 0: a column of
+    // the product depends only on its own column of B, and those outputs are never stored.
     const int g = lane >> 2, t = lane & 3;
-    const bool col_live = static_cast<uint32_t>(g) < p.nslots;
-    const uint8_t* xrow = col_live ? xh + g * p.xpitch : nullptr;
-    const uint8_t* sxslot = col_live ? sxp + g * sx_slot_bytes : nullptr;
-    float* scr_row = scr + (warp * 8 + g) * 16;
-    (void)scr_row; (void)sxslot;
+    const uint32_t col = static_cast<uint32_t>(g) < p.nslots ? g : 0;
+    const uint8_t* xrow = xh + col * p.xpitch;
+    const uint8_t* sxslot = sxp + col * sx_slot_bytes;
+    float* scr0 = scr + (warp * 16 + g) * 8;
+    float* scr1 = scr0 + 64;
+    (void)scr0; (void)scr1; (void)sxslot;
 
     uint32_t it = 0, grp = 0;
     bool alive = true;
     for (uint32_t rg = blockIdx.x; rg < p.ngroups; rg += gridDim.x, ++grp) {
-        float f0 = 0.f, f1 = 0.f;
+        float f[4] = {0.f, 0.f, 0.f, 0.f};
         for (uint32_t s = 0; s < p.nslices; ++s, ++it) {
             const uint32_t st = it % p.stages;
             // a wait that gives up marks the warp dead; it keeps walking the loops (skipping waits
-            // and work) so the named barriers below are still reached by all 256 consumers
+            // and work) so the named barriers below are still reached by all consumers
             if (alive && !mbar_wait_bounded(&full[st], (it / p.stages) & 1, p.status)) alive = false;
             const uint32_t kbase = s * SLICE_ELEMS;
-            const uint32_t nchunks = min(static_cast<uint32_t>(SLICE_ELEMS), p.k - kbase) >> 8;
-            if (alive && static_cast<uint32_t>(warp) < nchunks) {
-                const uint8_t* rowp = ring + st * stage_bytes + g * p.pitch;
-                const uint32_t e0 = kbase + 256 * warp;
+            const uint32_t nhalf = min(static_cast<uint32_t>(SLICE_ELEMS), p.k - kbase) >> 7;
+            // which 128-element piece this warp takes rotates with the stage, so that idle warps
+            // (short slices) and the slower unaligned Q6_K blocks spread evenly over the warps
+            const uint32_t hb = (static_cast<uint32_t>(warp) + it) & (CWARPS - 1);
+            if (alive && hb < nhalf) {
+                const uint8_t* r0 = ring + st * stage_bytes + g * p.pitch;
+                const uint8_t* r1 = r0 + 8 * p.pitch;
+                const uint32_t b = hb >> 1, half = hb & 1;
+                const uint32_t e0 = kbase + 256 * b;
                 if constexpr (K45) {
-                    chunk_k45<TYPE == HF2Q_TYPE_Q5_K>(rowp + warp * G.bytes, e0, xrow,
-                                                      sxslot ? sxslot + (e0 >> 8) * SXB : nullptr, t, f0, f1);
+                    half_k45<TYPE == HF2Q_TYPE_Q5_K>(r0 + b * G.bytes, r1 + b * G.bytes, half, e0, xrow,
+                                                     sxslot + (e0 >> 8) * SXB, t, f);
                 } else if constexpr (Q6) {
-                    chunk_q6k(rowp + warp * 210, e0, xrow, sxslot ? sxslot + (e0 >> 8) * SXB : nullptr, scr_row, t, f0, f1);
+                    if (b & 1) half_q6k<false>(r0 + b * 210, r1 + b * 210, half, e0, xrow, sxslot + (e0 >> 8) * SXB, scr0, scr1, t, f);
+                    else half_q6k<true>(r0 + b * 210, r1 + b * 210, half, e0, xrow, sxslot + (e0 >> 8) * SXB, scr0, scr1, t, f);
                 } else {
-                    chunk_legacy<TYPE == HF2Q_TYPE_Q8_0>(rowp + warp * 8 * G.bytes, e0, xrow,
-                                                         reinterpret_cast<const float*>(sxp), t, f0, f1);
+                    half_legacy<TYPE == HF2Q_TYPE_Q8_0>(r0 + hb * 4 * G.bytes, r1 + hb * 4 * G.bytes, kbase + 128 * hb, xrow,
+                                                        reinterpret_cast<const float*>(sxp), t, f);
                 }
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(&empty[st]);
         }
-        // combine the 8 warps' partial sums in a fixed order; double-buffered so one barrier suffices
-        float* rbuf = red + (grp & 1) * CWARPS * 64;
-        *reinterpret_cast<float2*>(rbuf + warp * 64 + g * 8 + 2 * t) = make_float2(f0, f1);
+        // combine the warps' partial sums in a fixed order; double-buffered so one barrier suffices
+        float* rbuf = red + (grp & 1) * CWARPS * 128;
+        *reinterpret_cast<float2*>(rbuf + warp * 128 + g * 8 + 2 * t) = make_float2(f[0], f[1]);
+        *reinterpret_cast<float2*>(rbuf + warp * 128 + (g + 8) * 8 + 2 * t) = make_float2(f[2], f[3]);
         asm volatile("bar.sync 1, %0;" ::"n"(CT));
-        if (ctid < 64) {
+        if (ctid < 128) {
             const uint32_t r = ctid >> 3, c = ctid & 7;
             const uint32_t row = rg * ROWS + r;
             float v = 0.f;
             if (p.x_bf16) {
 #pragma unroll
-                for (int w = 0; w < CWARPS; ++w) v += rbuf[w * 64 + r * 8 + c];
+                for (int w = 0; w < CWARPS; ++w) v += rbuf[w * 128 + r * 8 + c];
                 if (row < p.n && c < p.m) yout[static_cast<size_t>(c) * p.n + row] = v;
             } else if (c < 4) {
 #pragma unroll
-                for (int w = 0; w < CWARPS; ++w) v += rbuf[w * 64 + r * 8 + 2 * c] + rbuf[w * 64 + r * 8 + 2 * c + 1];
+                for (int w = 0; w < CWARPS; ++w) v += rbuf[w * 128 + r * 8 + 2 * c] + rbuf[w * 128 + r * 8 + 2 * c + 1];
                 if (row < p.n && c < p.m) yout[static_cast<size_t>(c) * p.n + row] = v;
             }
         }
@@ -452,7 +511,7 @@ __global__ void __launch_bounds__(THREADS) gemv_mma_kernel(const MParams p) {
 size_t smem_base_bytes(uint32_t type, uint32_t k, uint32_t nslots) {
     const bool k45 = type == HF2Q_TYPE_Q4_K || type == HF2Q_TYPE_Q5_K;
     const bool leg = type == HF2Q_TYPE_Q4_0 || type == HF2Q_TYPE_Q8_0;
-    const size_t fixed = 128 + (2 * CWARPS * 64 + CWARPS * 8 * 16) * 4;
+    const size_t fixed = 128 + (2 * CWARPS * 128 + CWARPS * 16 * 8) * 4;
     const size_t xbytes = static_cast<size_t>(nslots) * (2 * static_cast<size_t>(k) + 32);
     const size_t sxbytes = leg ? static_cast<size_t>(k / 32) * 8 * 4
                                : static_cast<size_t>(nslots) * (k / 256) * (k45 ? 32 : 64);
@@ -473,14 +532,15 @@ cudaError_t launch_mma_t(MParams p, uint32_t slots, const DeviceInfo& dev, cudaS
     const size_t limit = static_cast<size_t>(dev.max_smem_optin);
     const size_t base = smem_base_bytes(TYPE, p.k, p.nslots);
     if (base + 2 * stage > limit) return cudaErrorInvalidConfiguration;
-    // deepest ring (<= 4 stages) that still lets two CTAs share an SM; else one CTA with 4 stages
-    const size_t half = (limit + 1024) / 2 - 1024;     // per-CTA budget for 2 CTAs/SM (1 KB reserved each)
+    // two CTAs per SM when each can still have a ring of >= 4 stages (up to 6), else one CTA with
+    // as deep a ring as fits (up to 8 stages): bytes in flight per SM are what hides HBM latency
+    const size_t half = limit / 2 - 1024;
     uint32_t stages = 0;
-    for (uint32_t s = MAX_STAGES; s >= 3; --s)
+    for (uint32_t s = 6; s >= 4; --s)
         if (base + s * stage <= half) { stages = s; break; }
     if (!stages) {
         stages = MAX_STAGES;
-        while (base + stages * stage > limit) --stages;
+        while (stages > 2 && base + stages * stage > limit) --stages;
     }
     p.stages = stages;
     const size_t smem = base + stages * stage;
