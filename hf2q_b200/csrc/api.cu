@@ -246,17 +246,17 @@ HF2Q_API int32_t hf2q_cuda_dequantize(hf2q_ctx* ctx, void* stream, const void* w
 
 HF2Q_API int32_t hf2q_cuda_qmatmul_workspace_bytes(uint32_t m, uint32_t n, uint32_t k, uint32_t type,
                                                    uint32_t x_dtype, uint64_t* out) {
-    (void)n; (void)k; (void)x_dtype; (void)m;
+    (void)n; (void)x_dtype;
     if (!out) return HF2Q_ERR_INVALID_ARGUMENT;
     if (!type_supported(type)) return HF2Q_ERR_UNSUPPORTED_TYPE;
-    *out = 0;
+    // m <= 8 (mat-vec) needs none; the tensor-core GEMM keeps an f16 copy of the activations
+    *out = m > 8 ? gemm_tc_workspace_bytes(m, k) : 0;
     return HF2Q_OK;
 }
 
 HF2Q_API int32_t hf2q_cuda_qmatmul(hf2q_ctx* ctx, void* stream, const void* x, uint32_t x_dtype, const void* w,
                                    float* y, uint32_t m, uint32_t n, uint32_t k, uint32_t type,
                                    void* workspace, uint64_t workspace_bytes) {
-    (void)workspace; (void)workspace_bytes;
     if (!ctx) return HF2Q_ERR_INVALID_ARGUMENT;
     if (!x || !w || !y) return fail(ctx, HF2Q_ERR_INVALID_ARGUMENT, "qmatmul: null pointer");
     if (x_dtype != HF2Q_DT_F32 && x_dtype != HF2Q_DT_BF16) return fail(ctx, HF2Q_ERR_INVALID_ARGUMENT, "qmatmul: x_dtype %u (want F32 or BF16)", x_dtype);
@@ -267,6 +267,20 @@ HF2Q_API int32_t hf2q_cuda_qmatmul(hf2q_ctx* ctx, void* stream, const void* x, u
         return fail(ctx, HF2Q_ERR_INVALID_ARGUMENT, "qmatmul: misaligned buffer");
     DeviceGuard dg(ctx->device);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
+    // m > 8: tensor-core GEMM (the reference's MM_ROUTING_THRESHOLD, forward_mlx.rs:9800) when the
+    // layout allows tensor-map copies; otherwise the mat-vec kernels, 8 rows at a time
+    if (m > 8 && !ctx->fp32_matvec && gemm_tc_supported(type, w, n, k)) {
+        const uint64_t need = gemm_tc_workspace_bytes(m, k);
+        if (!workspace || workspace_bytes < need)
+            return fail(ctx, HF2Q_ERR_WORKSPACE, "qmatmul: m=%u needs a workspace of %llu bytes (got %llu)", m,
+                        (unsigned long long)need, (unsigned long long)workspace_bytes);
+        if (reinterpret_cast<uintptr_t>(workspace) % 256) return fail(ctx, HF2Q_ERR_INVALID_ARGUMENT, "qmatmul: workspace must be 256-byte aligned");
+        int nl = 0;
+        const cudaError_t e = launch_gemm_tc(type, w, x, x_dtype, y, m, n, k, workspace, ctx->status, ctx->dev.sm_count, st, &nl);
+        if (e != cudaSuccess) return cuda_fail(ctx, e, "qmatmul (tensor-core GEMM) launch");
+        ctx->launches += nl;
+        return HF2Q_OK;
+    }
     GemvArgs a{};
     a.w = w; a.x = x; a.y = y;
     a.x_dtype = x_dtype; a.type = type;

@@ -37,6 +37,13 @@ bool gemv_mma_supported(const GemvArgs& a);
 uint32_t gemv_mma_max_rows(uint32_t type, uint32_t k, uint32_t x_dtype, const DeviceInfo& dev);
 cudaError_t launch_gemv_mma(const GemvArgs& a, const DeviceInfo& dev, cudaStream_t st);
 
+// K2 (k2_gemm_tc.cu): tcgen05 GEMM for many activation rows.  Needs k % 256 == 0, 16-byte aligned
+// rows and a workspace of gemm_tc_workspace_bytes(m, k) for the f16 copy of the activations.
+bool gemm_tc_supported(uint32_t type, const void* w, uint32_t n, uint32_t k);
+uint64_t gemm_tc_workspace_bytes(uint32_t m, uint32_t k);
+cudaError_t launch_gemm_tc(uint32_t type, const void* w, const void* x, uint32_t x_dtype, float* y, uint32_t m, uint32_t n,
+                           uint32_t k, void* workspace, uint32_t* status, int sm_count, cudaStream_t st, int* launches);
+
 // softmax -> top-k -> renormalise (moe_router.cu)
 cudaError_t launch_softmax_topk(const float* logits, uint32_t* ids, float* weights,
                                 uint32_t n_tokens, uint32_t n_experts, uint32_t top_k,

@@ -209,6 +209,15 @@ def quantized_matmul_ggml(ctx: GpuContext, input: torch.Tensor, weight: QuantWei
         raise Hf2qError(_lib.ERR_INVALID_ARGUMENT, "input/out smaller than [m,k] / [m,n]")
     if weight.rows != params.n or weight.cols != params.k or weight.ggml_type != int(params.ggml_type):
         raise Hf2qError(_lib.ERR_INVALID_ARGUMENT, "params do not match the weight's (rows, cols, type)")
+    if workspace is None:
+        # the reference keeps such scratch in per-thread pools (decode_pool.rs:51-76); so does this mirror
+        need = quantized_matmul_workspace_bytes(params, input.dtype)
+        if need:
+            ws = getattr(ctx, "_ws", None)
+            if ws is None or ws.numel() < need:
+                ws = torch.empty(need, dtype=torch.uint8, device=input.device)
+                ctx._ws = ws
+            workspace = ws
     ws_ptr, ws_bytes = (workspace.data_ptr(), workspace.numel() * workspace.element_size()) if workspace is not None else (None, 0)
     ctx._check(ctx._lib.hf2q_cuda_qmatmul(ctx._h, ctx._stream(), input.data_ptr(), xdt, weight.ptr,
                                           out.data_ptr(), params.m, params.n, params.k,

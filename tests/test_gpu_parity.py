@@ -137,6 +137,32 @@ def test_qmatmul_more_than_eight_rows(gpu_ctx):
     assert rel_l2(y.cpu().numpy(), _ref(t, raw, xs, n, k)) < GATE
 
 
+# ---------------------------------------------------------------- K2 tensor-core GEMM
+@pytest.mark.parametrize("t", TYPES)
+def test_gemm_matches_f64_reference(gpu_ctx, t):
+    """m > 8 takes the tcgen05 kernel (f16 operands, fp32 accumulate): gate 1e-3 relative L2."""
+    for (n, k, m, bf16) in [(128, 256, 16, True), (200, 1024, 33, True), (384, 2048, 130, False),
+                            (96, 4096, 300, True), (520, 512, 64, True)]:
+        raw = make_quant_weight(t, n, k, seed=3 * n + k + m)
+        w = hq.load_quant_weight(gpu_ctx, raw, t, n, k)
+        xd, xs = _dev_x(make_x(m, k, seed=m), bf16)
+        y = torch.full((m, n), float("nan"), device="cuda")
+        hq.quantized_matmul_ggml(gpu_ctx, xd, w, y, w.matmul_params(m))
+        gpu_ctx.check_status()
+        err = rel_l2(y.cpu().numpy(), _ref(t, raw, xs, n, k))
+        assert err < GATE, (t, n, k, m, err)
+
+
+def test_gemm_needs_its_workspace(gpu_ctx):
+    t, n, k, m = oracle.Q4_K, 128, 512, 64
+    w = hq.load_quant_weight(gpu_ctx, make_quant_weight(t, n, k, seed=1), t, n, k)
+    x = torch.randn(m, k, device="cuda")
+    y = torch.empty(m, n, device="cuda")
+    lib = _lib.load()
+    rc = lib.hf2q_cuda_qmatmul(gpu_ctx._h, None, x.data_ptr(), 0, w.ptr, y.data_ptr(), m, n, k, t, None, 0)
+    assert rc == _lib.ERR_WORKSPACE
+
+
 def test_row_shard_is_a_byte_slice(gpu_ctx):
     t, n, k = oracle.Q6_K, 64, 4096
     raw = make_quant_weight(t, n, k, seed=6)
