@@ -290,6 +290,35 @@ HF2Q_API int32_t hf2q_cuda_qmatmul(hf2q_ctx* ctx, void* stream, const void* x, u
     return run_matvec(ctx, st, a, m, "qmatmul launch");
 }
 
+HF2Q_API int32_t hf2q_cuda_qmatmul_static(hf2q_ctx* ctx, void* stream, const void* x, uint32_t x_dtype, const void* w,
+                                          float* y, uint32_t m, uint32_t n, uint32_t k, uint32_t type) {
+    if (!ctx) return HF2Q_ERR_INVALID_ARGUMENT;
+    if (!x || !w || !y) return fail(ctx, HF2Q_ERR_INVALID_ARGUMENT, "qmatmul_static: null pointer");
+    if (x_dtype != HF2Q_DT_F32 && x_dtype != HF2Q_DT_BF16) return fail(ctx, HF2Q_ERR_INVALID_ARGUMENT, "qmatmul_static: x_dtype %u (want F32 or BF16)", x_dtype);
+    int32_t rc = check_matmul_shape(ctx, type, n, k, "qmatmul_static");
+    if (rc) return rc;
+    if (m == 0) return HF2Q_OK;
+    if (reinterpret_cast<uintptr_t>(x) % dtype_size(x_dtype) || reinterpret_cast<uintptr_t>(y) % 4)
+        return fail(ctx, HF2Q_ERR_INVALID_ARGUMENT, "qmatmul_static: misaligned buffer");
+    if (!gemm_tc_supported(type, w, n, k))
+        return fail(ctx, HF2Q_ERR_INVALID_ARGUMENT, "qmatmul_static: needs k %% 256 == 0 and 16-byte aligned weight rows (k=%u)", k);
+    const uint64_t need = gemm_tc_workspace_bytes(m, k), have = gemm_tc_static_scratch_bytes();
+    if (need > have)
+        return fail(ctx, HF2Q_ERR_WORKSPACE, "qmatmul_static: m*k = %llu elements needs %llu bytes of scratch, the fixed array holds %llu (m*k <= %llu)",
+                    (unsigned long long)m * k, (unsigned long long)need, (unsigned long long)have, (unsigned long long)(have / 2));
+    DeviceGuard dg(ctx->device);
+    void* scratch = nullptr;
+    cudaError_t e = gemm_tc_static_scratch(ctx->device, &scratch);       // first call per device: cudaGetSymbolAddress
+    if (e != cudaSuccess) return cuda_fail(ctx, e, "qmatmul_static: cudaGetSymbolAddress");
+    int nl = 0;
+    e = launch_gemm_tc(type, w, x, x_dtype, y, m, n, k, scratch, ctx->status, ctx->dev.sm_count, static_cast<cudaStream_t>(stream), &nl);
+    if (e != cudaSuccess) return cuda_fail(ctx, e, "qmatmul_static launch");
+    ctx->launches += nl;
+    return HF2Q_OK;
+}
+
+HF2Q_API uint64_t hf2q_cuda_qmatmul_static_max_elements(void) { return gemm_tc_static_scratch_bytes() / 2; }
+
 HF2Q_API int32_t hf2q_cuda_qmatmul_host(hf2q_ctx* ctx, const void* x_host, uint32_t x_dtype, const void* w_dev,
                                         float* y_host, uint32_t m, uint32_t n, uint32_t k, uint32_t type) {
     if (!ctx) return HF2Q_ERR_INVALID_ARGUMENT;

@@ -547,4 +547,33 @@ cudaError_t launch_gemm_tc(uint32_t type, const void* w, const void* x, uint32_t
     }
 }
 
+
+// ---------------------------------------------------------------- allocation-free variant
+// Scratch for hf2q_cuda_qmatmul_static: the f16 copy of the activations lives in this fixed
+// array instead of a caller workspace.  Every GPU that loads the library holds these 8 MiB until
+// the process exits.  In host code `g_static_x16` is only a handle for the runtime, not a device
+// address; the address a kernel can use comes from cudaGetSymbolAddress, per device.
+constexpr uint64_t STATIC_SCRATCH_BYTES = 8ull << 20;
+static __device__ __align__(256) unsigned char g_static_x16[STATIC_SCRATCH_BYTES];
+
+uint64_t gemm_tc_static_scratch_bytes() { return STATIC_SCRATCH_BYTES; }
+
+// Device address of the scratch array on `device` (which must be the current device).  The first
+// call per device asks the runtime; later calls return the cached pointer.
+cudaError_t gemm_tc_static_scratch(int device, void** out) {
+    constexpr int MAX_DEV = 64;
+    static std::mutex mu;
+    static void* cached[MAX_DEV] = {nullptr};
+    if (device < 0 || device >= MAX_DEV) return cudaErrorInvalidDevice;
+    std::lock_guard<std::mutex> lock(mu);
+    if (!cached[device]) {
+        void* ptr = nullptr;
+        const cudaError_t e = cudaGetSymbolAddress(&ptr, g_static_x16);
+        if (e != cudaSuccess) return e;
+        cached[device] = ptr;
+    }
+    *out = cached[device];
+    return cudaSuccess;
+}
+
 }  // namespace hf2q

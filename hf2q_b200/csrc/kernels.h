@@ -44,6 +44,10 @@ uint64_t gemm_tc_workspace_bytes(uint32_t m, uint32_t k);
 cudaError_t launch_gemm_tc(uint32_t type, const void* w, const void* x, uint32_t x_dtype, float* y, uint32_t m, uint32_t n,
                            uint32_t k, void* workspace, uint32_t* status, int sm_count, cudaStream_t st, int* launches);
 
+// Fixed scratch of the allocation-free GEMM entry (lives in k2_gemm_tc.cu).
+uint64_t gemm_tc_static_scratch_bytes();
+cudaError_t gemm_tc_static_scratch(int device, void** out);
+
 // softmax -> top-k -> renormalise (moe_router.cu)
 cudaError_t launch_softmax_topk(const float* logits, uint32_t* ids, float* weights,
                                 uint32_t n_tokens, uint32_t n_experts, uint32_t top_k,

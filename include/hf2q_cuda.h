@@ -124,6 +124,28 @@ HF2Q_API int32_t hf2q_cuda_qmatmul_workspace_bytes(uint32_t m, uint32_t n, uint3
                                                    uint32_t ggml_type, uint32_t x_dtype,
                                                    uint64_t* out);
 
+/* No counterpart in the reference.  The same product as hf2q_cuda_qmatmul through the tensor-core
+ * GEMM, for callers that cannot hand the library a workspace because they cannot allocate device
+ * memory at all: code that runs after the host application has handed the device to its own
+ * arena or pools (hf2q keeps such arenas for its FFN buffers), plugin or FFI glue
+ * that sees only the tensors of one op, and latency-critical loops where a cudaMalloc would stall
+ * every stream of the device.  The f16 copy of the activations that the GEMM needs is kept in a
+ * fixed array inside the library image instead: 8 MiB per GPU, held from library load to process
+ * exit, so m * k must not exceed hf2q_cuda_qmatmul_static_max_elements() (4 194 304; e.g. 512
+ * rows of k = 8192); larger products fail with HF2Q_ERR_WORKSPACE and a message saying so.
+ * The call allocates nothing (no cudaMalloc / cudaFree, no allocating library routine) and is
+ * enqueued on `stream` like the others.  Needs k % 256 == 0 and 16-byte aligned weight rows.
+ * The FIRST call on each device looks the array's device address up (cudaGetSymbolAddress, with
+ * that device current) and caches it; make that first call before any stream capture begins.
+ * All calls on a device share the one array and it keeps the previous call's contents (every
+ * element a call reads is written by that call first, so nothing needs clearing); two calls whose
+ * kernels can overlap on the GPU -- different streams, or graph branches -- race on it and must be
+ * ordered by the caller. */
+HF2Q_API int32_t hf2q_cuda_qmatmul_static(hf2q_ctx* ctx, void* stream, const void* x, uint32_t x_dtype,
+                                          const void* w, float* y, uint32_t m, uint32_t n, uint32_t k,
+                                          uint32_t ggml_type);
+HF2Q_API uint64_t hf2q_cuda_qmatmul_static_max_elements(void);
+
 /* Same product for callers that hold HOST buffers: copies x in, runs, copies y out, waits.
  * Uses staging buffers the context grows on first use.  Stands for the reference's
  * `apply_linear_projection_f32` + download pattern in its tests (gpu_ffn.rs:3209-3275). */
