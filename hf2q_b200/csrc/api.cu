@@ -18,7 +18,8 @@ struct hf2q_ctx {
     DeviceInfo dev{};
     uint32_t* status = nullptr;        // device status word
     uint64_t launches = 0;
-    bool fp32_matvec = false;          // HF2Q_CUDA_F32_MATVEC=1: CUDA-core fp32 mat-vec instead of the MMA one
+    bool fp32_matvec = false;          // HF2Q_CUDA_F32_MATVEC=1: CUDA-core fp32 mat-vec only
+    bool tc_matvec = false;            // HF2Q_CUDA_TC_MATVEC=1: dense mat-vecs on the tcgen05 kernel (slower today)
     // staging for the *_host convenience calls
     void* stage_x = nullptr;  size_t stage_x_bytes = 0;
     float* stage_y = nullptr; size_t stage_y_bytes = 0;
@@ -78,6 +79,15 @@ int32_t grow(hf2q_ctx* ctx, void** p, size_t* have, size_t want, bool pinned) {
 // chosen kernel needs.  ids == nullptr: dense.
 int32_t run_matvec(hf2q_ctx* ctx, cudaStream_t st, GemvArgs a, uint32_t m_total, const char* who) {
     const size_t xs = dtype_size(a.x_dtype);
+    if (!ctx->fp32_matvec && ctx->tc_matvec && m_total <= 8) {
+        a.m = m_total;
+        if (gemv_tc_supported(a)) {
+            const cudaError_t e = launch_gemv_tc(a, ctx->dev, st);
+            if (e != cudaSuccess) return cuda_fail(ctx, e, who);
+            ctx->launches += 1;
+            return HF2Q_OK;
+        }
+    }
     const bool mma = !ctx->fp32_matvec && gemv_mma_supported(a);
     uint32_t step = 8;
     if (mma) {
@@ -148,6 +158,8 @@ HF2Q_API int32_t hf2q_cuda_ctx_create(int32_t device, hf2q_ctx** out) {
     // switch for its mat-vec: HF2Q_F32_MATVEC, src/serve/forward_mlx.rs:9835)
     const char* env = getenv("HF2Q_CUDA_F32_MATVEC");
     c->fp32_matvec = env && env[0] == '1';
+    env = getenv("HF2Q_CUDA_TC_MATVEC");
+    c->tc_matvec = env && env[0] == '1';
     *out = c;
     return HF2Q_OK;
 }
@@ -345,11 +357,15 @@ HF2Q_API int32_t hf2q_cuda_qmatmul_host(hf2q_ctx* ctx, const void* x_host, uint3
     return HF2Q_OK;
 }
 
+// routed rows above which the grouped tensor-core product is used (the reference's
+// MM_ID_ROUTING_THRESHOLD settled on 32, docs/ADR-013-qwen35-inference.md:1097-1103)
+static constexpr uint32_t MM_ID_ROUTING_THRESHOLD = 32;
+
 HF2Q_API int32_t hf2q_cuda_qmatmul_id_scratch_bytes(uint32_t n_experts, uint32_t max_rows, uint32_t k,
                                                     uint32_t x_dtype, uint64_t* out) {
-    (void)n_experts; (void)max_rows; (void)k; (void)x_dtype;
+    (void)x_dtype;
     if (!out) return HF2Q_ERR_INVALID_ARGUMENT;
-    *out = 0;
+    *out = max_rows > MM_ID_ROUTING_THRESHOLD ? moe_scratch_layout(n_experts, max_rows, k).total : 0;
     return HF2Q_OK;
 }
 
@@ -357,7 +373,6 @@ HF2Q_API int32_t hf2q_cuda_qmatmul_id(hf2q_ctx* ctx, void* stream, const void* x
                                       const void* w_stacked, const uint32_t* ids, float* y, uint32_t n_tokens,
                                       uint32_t top_k, uint32_t n, uint32_t k, uint32_t n_experts,
                                       uint64_t expert_stride, uint32_t type, void* scratch, uint64_t scratch_bytes) {
-    (void)scratch; (void)scratch_bytes;
     if (!ctx) return HF2Q_ERR_INVALID_ARGUMENT;
     if (!x || !w_stacked || !ids || !y) return fail(ctx, HF2Q_ERR_INVALID_ARGUMENT, "qmatmul_id: null pointer");
     if (x_dtype != HF2Q_DT_F32 && x_dtype != HF2Q_DT_BF16) return fail(ctx, HF2Q_ERR_INVALID_ARGUMENT, "qmatmul_id: x_dtype %u", x_dtype);
@@ -372,6 +387,24 @@ HF2Q_API int32_t hf2q_cuda_qmatmul_id(hf2q_ctx* ctx, void* stream, const void* x
     const uint64_t rows = static_cast<uint64_t>(n_tokens) * top_k;
     DeviceGuard dg(ctx->device);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (rows > MM_ID_ROUTING_THRESHOLD && rows / 32 + n_experts <= 65535 && !ctx->fp32_matvec &&
+        gemm_tc_grouped_supported(type, w_stacked, expert_stride, n_experts, k) && reinterpret_cast<uintptr_t>(x) % 16 == 0) {
+        // many rows: sort by expert on the device, gather activations, ONE grouped tensor-core launch
+        const MoeScratch lay = moe_scratch_layout(n_experts, static_cast<uint32_t>(rows), k);
+        if (!scratch || scratch_bytes < lay.total)
+            return fail(ctx, HF2Q_ERR_WORKSPACE, "qmatmul_id: %llu routed rows need %llu bytes of scratch (got %llu)",
+                        (unsigned long long)rows, (unsigned long long)lay.total, (unsigned long long)scratch_bytes);
+        if (reinterpret_cast<uintptr_t>(scratch) % 256) return fail(ctx, HF2Q_ERR_INVALID_ARGUMENT, "qmatmul_id: scratch must be 256-byte aligned");
+        const uint32_t nt = moe_token_tile(static_cast<uint32_t>(rows), n_experts);
+        cudaError_t e = launch_moe_prep(ids, static_cast<uint32_t>(rows), n_experts, top_k, nt, x, x_dtype, k, y, n, scratch, lay,
+                                        ctx->status, ctx->dev.sm_count, st);
+        if (e == cudaSuccess)
+            e = launch_gemm_tc_grouped(type, w_stacked, expert_stride, n_experts, static_cast<uint32_t>(rows), y, n, k, nt, scratch, lay,
+                                       ctx->status, st);
+        if (e != cudaSuccess) return cuda_fail(ctx, e, "qmatmul_id (grouped tensor-core) launch");
+        ctx->launches += 3;
+        return HF2Q_OK;
+    }
     // per-row mat-vec, at most 32768 routed rows per launch (grid.y limit is 65535)
     if (top_k > 32768) return fail(ctx, HF2Q_ERR_INVALID_ARGUMENT, "qmatmul_id: top_k=%u exceeds 32768", top_k);
     const uint64_t chunk = 32768 / top_k * top_k;

@@ -34,8 +34,11 @@
 
 #include "common.cuh"
 #include "kernels.h"
+#include "tc_common.cuh"
 
 namespace hf2q {
+
+using namespace tc;
 
 namespace {
 
@@ -46,230 +49,37 @@ constexpr int raw_stages_of(uint32_t type) { return type == HF2Q_TYPE_Q8_0 ? 2 :
 constexpr int X_STAGES = 4;
 constexpr int GEMM_THREADS = 192;
 
+// One token tile of the grouped (expert-routed) product: rows [start, start+count) of the
+// expert-sorted activation panel belong to expert `expert`.
+struct GroupTile { uint32_t expert, start, count, pad; };
+
 struct GParams {
     float* y;
     uint32_t m, n, k;
+    // grouped mode (mul_mat_id): tile table, its length, and the routed-row index of every sorted row
+    const GroupTile* tiles;
+    const uint32_t* n_tiles;
+    const uint32_t* perm;
     uint32_t boxw;          // bytes per weight row in one raw stage
     uint32_t blk_bytes;     // bytes of one 256-element K-block of a row
     uint32_t* status;
 };
 
-// ---------------------------------------------------------------- PTX wrappers
-__device__ __forceinline__ void tma_2d(void* dst, const CUtensorMap* map, int c0, int c1, uint64_t* bar) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-        ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(c0), "r"(c1), "r"(smem_u32(bar))
-        : "memory");
-}
-__device__ __forceinline__ void tmem_alloc(uint32_t* dst_smem, uint32_t ncols) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(dst_smem)), "r"(ncols) : "memory");
-}
-__device__ __forceinline__ void tmem_relinquish() {
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
-}
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_commit(uint64_t* bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-// D[tmem_d] (+)= A[tmem_a] * B[smem desc]; M = 128, K = 16, f16 inputs, f32 accumulate
-__device__ __forceinline__ void umma_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
-        ::"r"(tmem_d), "r"(tmem_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
-        : "memory");
-}
-__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&v)[32]) {
-    asm volatile(
-        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,"
-        "%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
-        ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]),
-          "r"(v[8]), "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]),
-          "r"(v[16]), "r"(v[17]), "r"(v[18]), "r"(v[19]), "r"(v[20]), "r"(v[21]), "r"(v[22]), "r"(v[23]),
-          "r"(v[24]), "r"(v[25]), "r"(v[26]), "r"(v[27]), "r"(v[28]), "r"(v[29]), "r"(v[30]), "r"(v[31])
-        : "memory");
-}
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
-        "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
-        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
-          "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
-          "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
-          "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
-        : "r"(taddr)
-        : "memory");
-}
-__device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
-__device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-
-// K-major, 128-byte swizzled shared-memory operand: 8-row groups are 1024 bytes apart.
-__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
-    return static_cast<uint64_t>((addr & 0x3FFFFu) >> 4) | (static_cast<uint64_t>(1) << 16) |
-           (static_cast<uint64_t>(1024 >> 4) << 32) | (static_cast<uint64_t>(1) << 46) |
-           (static_cast<uint64_t>(2) << 61);
-}
-
-// ---------------------------------------------------------------- per-row dequantisers
-// Each produces the 64 f16 values of quarter `qd` (elements 64qd .. 64qd+63 of a 256-element
-// K-block, in natural order) packed two per register.
-
-__device__ __forceinline__ uint32_t pack_h2(float a, float b) {
-    __half2 h = __floats2half2_rn(a, b);
-    return *reinterpret_cast<uint32_t*>(&h);
-}
-__device__ __forceinline__ uint32_t h2_bits(__half2 h) { return *reinterpret_cast<uint32_t*>(&h); }
-// two packed bytes -> (1024 + b) as f16x2, then minus `bias` (>= 1024), exact
-__device__ __forceinline__ __half2 codes01(uint32_t w, __half2 bias) {
-    uint32_t h = __byte_perm(w, 0x64646464u, 0x4140u);
-    return __hsub2(*reinterpret_cast<__half2*>(&h), bias);
-}
-__device__ __forceinline__ __half2 codes23(uint32_t w, __half2 bias) {
-    uint32_t h = __byte_perm(w, 0x64646464u, 0x4342u);
-    return __hsub2(*reinterpret_cast<__half2*>(&h), bias);
-}
-
-// Q4_K / Q5_K.  P: the block's 36 / 44 words.  Quarter qd = chunk c: low nibbles are sub-block 2c,
-// high nibbles sub-block 2c+1;  w = f16(d*sc) * q - f16(dmin*m).
-template <bool Q5>
-__device__ __forceinline__ void dq_k45(const uint32_t* P, int c, uint32_t (&out)[32]) {
-    constexpr int QW = Q5 ? 12 : 4;         // first qs word
-    const float d = f16_bits_to_f32(P[0] & 0xffffu), dmin = f16_bits_to_f32(P[0] >> 16);
-    uint32_t sc1, m1, sc2, m2;
-    scale_min_k4(2 * c, P[1], P[2], P[3], sc1, m1);
-    scale_min_k4(2 * c + 1, P[1], P[2], P[3], sc2, m2);
-    const __half2 S1 = __float2half2_rn(d * static_cast<float>(sc1)), M1 = __float2half2_rn(-dmin * static_cast<float>(m1));
-    const __half2 S2 = __float2half2_rn(d * static_cast<float>(sc2)), M2 = __float2half2_rn(-dmin * static_cast<float>(m2));
-    const __half2 k1024 = __half2half2(__ushort_as_half(0x6400));
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-        const uint32_t w = P[QW + 8 * c + i];
-        uint32_t lo = w & 0x0F0F0F0Fu, hi = (w >> 4) & 0x0F0F0F0Fu;
-        if constexpr (Q5) {
-            const uint32_t g = P[4 + i];
-            lo |= ((g >> (2 * c)) & 0x01010101u) << 4;
-            hi |= ((g >> (2 * c + 1)) & 0x01010101u) << 4;
-        }
-        out[2 * i] = h2_bits(__hfma2(codes01(lo, k1024), S1, M1));
-        out[2 * i + 1] = h2_bits(__hfma2(codes23(lo, k1024), S1, M1));
-        out[16 + 2 * i] = h2_bits(__hfma2(codes01(hi, k1024), S2, M2));
-        out[16 + 2 * i + 1] = h2_bits(__hfma2(codes23(hi, k1024), S2, M2));
-    }
-}
-
-// Q6_K.  W(j): logical 32-bit word j of the 210-byte block.  Quarter qd: half n = qd>>1, k in
-// {2*(qd&1), 2*(qd&1)+1}; element 128n + 32k + l comes from ql/qh as in the quantizer's packing.
-template <typename WordFn>
-__device__ __forceinline__ void dq_q6k(WordFn W, int qd, uint32_t (&out)[32]) {
-    const int n = qd >> 1, kp = qd & 1;
-    const float d = f16_bits_to_f32(W(52) & 0xffffu);
-    const uint32_t scw = W(48 + 2 * n + kp);             // scales 8n+4kp .. 8n+4kp+3
-    const __half2 k1056 = __half2half2(__ushort_as_half(0x6420));   // 1024 + 32
-    __half2 S[4];
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-        const float s = static_cast<float>(static_cast<int8_t>((scw >> (8 * j)) & 0xffu));
-        S[j] = __float2half2_rn(d * s);                  // sub-block 8n + 4kp + j = 8n + 2k + (l/16)
-    }
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-        const uint32_t qa = W(16 * n + i), qb = W(16 * n + 8 + i), qh = W(32 + 8 * n + i);
-        uint32_t q0, q1;
-        if (kp == 0) {
-            q0 = (qa & 0x0F0F0F0Fu) | ((qh << 4) & 0x30303030u);
-            q1 = (qb & 0x0F0F0F0Fu) | ((qh << 2) & 0x30303030u);
-        } else {
-            q0 = ((qa >> 4) & 0x0F0F0F0Fu) | (qh & 0x30303030u);
-            q1 = ((qb >> 4) & 0x0F0F0F0Fu) | ((qh >> 2) & 0x30303030u);
-        }
-        const int h = i >> 2;                            // l / 16
-        out[2 * i] = h2_bits(__hmul2(codes01(q0, k1056), S[h]));
-        out[2 * i + 1] = h2_bits(__hmul2(codes23(q0, k1056), S[h]));
-        out[16 + 2 * i] = h2_bits(__hmul2(codes01(q1, k1056), S[2 + h]));
-        out[16 + 2 * i + 1] = h2_bits(__hmul2(codes23(q1, k1056), S[2 + h]));
-    }
-}
-
-// Q4_0 / Q8_0: eight 32-element blocks per K-block; element-wise decode (correct, not tuned).
-template <uint32_t TYPE>
-__device__ __forceinline__ void dq_legacy(const uint8_t* row, int qd, uint32_t (&out)[32]) {
-    constexpr BlockGeom G = block_geom(TYPE);
-#pragma unroll
-    for (int b = 0; b < 2; ++b) {
-        const uint8_t* blk = row + (2 * qd + b) * G.bytes;
-#pragma unroll
-        for (int e = 0; e < 32; e += 2)
-            out[16 * b + e / 2] = pack_h2(dequant_elem<TYPE>(blk, e), dequant_elem<TYPE>(blk, e + 1));
-    }
-}
-
-template <uint32_t TYPE, int OFF>
-__device__ __forceinline__ void dequant_row_to_tmem(const uint8_t* row, uint32_t taddr) {
-    if constexpr (TYPE == HF2Q_TYPE_Q4_K || TYPE == HF2Q_TYPE_Q5_K) {
-        constexpr int NW = TYPE == HF2Q_TYPE_Q4_K ? 36 : 44;
-        uint32_t P[NW];
-#pragma unroll
-        for (int u = 0; u < NW / 4; ++u) {
-            const uint4 v = reinterpret_cast<const uint4*>(row)[u];
-            P[4 * u] = v.x; P[4 * u + 1] = v.y; P[4 * u + 2] = v.z; P[4 * u + 3] = v.w;
-        }
-#pragma unroll
-        for (int qd = 0; qd < 4; ++qd) {
-            uint32_t out[32];
-            dq_k45<TYPE == HF2Q_TYPE_Q5_K>(P, qd, out);
-            tmem_st32(taddr + 32 * qd, out);
-        }
-    } else if constexpr (TYPE == HF2Q_TYPE_Q6_K) {
-        uint32_t P[60];
-#pragma unroll
-        for (int u = 0; u < 15; ++u) {
-            const uint4 v = reinterpret_cast<const uint4*>(row)[u];
-            P[4 * u] = v.x; P[4 * u + 1] = v.y; P[4 * u + 2] = v.z; P[4 * u + 3] = v.w;
-        }
-        auto W = [&](int j) -> uint32_t {
-            if constexpr (OFF % 4 == 0) return P[j + OFF / 4];
-            else return __funnelshift_r(P[j + OFF / 4], P[j + OFF / 4 + 1], 16);
-        };
-#pragma unroll
-        for (int qd = 0; qd < 4; ++qd) {
-            uint32_t out[32];
-            dq_q6k(W, qd, out);
-            tmem_st32(taddr + 32 * qd, out);
-        }
-    } else {
-#pragma unroll 1
-        for (int qd = 0; qd < 4; ++qd) {
-            uint32_t out[32];
-            dq_legacy<TYPE>(row, qd, out);
-            tmem_st32(taddr + 32 * qd, out);
-        }
-    }
-}
-
 template <uint32_t TYPE>
 __device__ __forceinline__ void dequant_dispatch(const uint8_t* row, uint32_t off, uint32_t taddr) {
-    if constexpr (TYPE == HF2Q_TYPE_Q6_K) {
-        switch (off) {   // byte offset of the block inside its 16-byte aligned box; warp-uniform
-            case 0: dequant_row_to_tmem<TYPE, 0>(row, taddr); break;
-            case 2: dequant_row_to_tmem<TYPE, 2>(row, taddr); break;
-            case 4: dequant_row_to_tmem<TYPE, 4>(row, taddr); break;
-            case 6: dequant_row_to_tmem<TYPE, 6>(row, taddr); break;
-            case 8: dequant_row_to_tmem<TYPE, 8>(row, taddr); break;
-            case 10: dequant_row_to_tmem<TYPE, 10>(row, taddr); break;
-            case 12: dequant_row_to_tmem<TYPE, 12>(row, taddr); break;
-            default: dequant_row_to_tmem<TYPE, 14>(row, taddr); break;
+    with_row_block<TYPE>(off, [&](auto rb) {
+        rb.load(row, off);
+#pragma unroll
+        for (int qd = 0; qd < 4; ++qd) {
+            uint32_t out[32];
+            rb.quarter(qd, out);
+            tmem_st32(taddr + 32 * qd, out);
         }
-    } else {
-        dequant_row_to_tmem<TYPE, 0>(row, taddr);
-    }
+    });
 }
 
 // ---------------------------------------------------------------- the kernel
-template <uint32_t TYPE, int NT>
+template <uint32_t TYPE, int NT, bool GROUPED>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x, const GParams p) {
     extern __shared__ uint8_t smem_raw[];
@@ -290,7 +100,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(d_full + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const uint32_t row0 = blockIdx.x * TILE_N, tok0 = blockIdx.y * NT;
+    const uint32_t row0 = blockIdx.x * TILE_N;
+    uint32_t tok0 = blockIdx.y * NT, tok_end = p.m, expert = 0;
+    if constexpr (GROUPED) {
+        if (blockIdx.y >= *p.n_tiles) return;              // the grid is sized for the worst case
+        const GroupTile gt = p.tiles[blockIdx.y];
+        tok0 = gt.start; tok_end = gt.start + gt.count; expert = gt.expert;
+    }
     const uint32_t nkb = p.k / KB;
 
     if (threadIdx.x == 0) {
@@ -318,7 +134,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
                 if (!ok) break;
                 mbar_arrive_expect_tx(&raw_full[rs], raw_stage);
                 const uint32_t byte0 = (kb * p.blk_bytes) & ~15u;       // 16-byte aligned start of the box
-                tma_2d(raw + rs * raw_stage, &tmap_w, static_cast<int>(byte0 >> 1), static_cast<int>(row0), &raw_full[rs]);
+                if constexpr (GROUPED)
+                    tma_3d(raw + rs * raw_stage, &tmap_w, static_cast<int>(byte0 >> 1), static_cast<int>(row0), static_cast<int>(expert), &raw_full[rs]);
+                else
+                    tma_2d(raw + rs * raw_stage, &tmap_w, static_cast<int>(byte0 >> 1), static_cast<int>(row0), &raw_full[rs]);
                 for (uint32_t j = 0; j < KB / XK && ok; ++j) {
                     const uint32_t xi = kb * (KB / XK) + j, st = xi % X_STAGES;
                     if (xi >= X_STAGES) ok = mbar_wait_bounded(&x_empty[st], ((xi / X_STAGES) - 1) & 1, p.status);
@@ -391,7 +210,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
 #pragma unroll
                     for (int j = 0; j < 32; ++j) {
                         const uint32_t tok = tok0 + c0 + j;
-                        if (tok < p.m) p.y[static_cast<size_t>(tok) * p.n + row] = __uint_as_float(v[j]);
+                        if (tok < tok_end) {
+                            const uint32_t dst = GROUPED ? p.perm[tok] : tok;      // scatter back to routed-row order
+                            p.y[static_cast<size_t>(dst) * p.n + row] = __uint_as_float(v[j]);
+                        }
                     }
                 }
             }
@@ -434,20 +256,11 @@ EncodeTiledFn encode_fn() {
     return fn;
 }
 
-uint32_t boxw_of(uint32_t type) {
-    switch (type) {
-        case HF2Q_TYPE_Q4_K: return 144;
-        case HF2Q_TYPE_Q5_K: return 176;
-        case HF2Q_TYPE_Q6_K: return 240;     // 210 bytes at an offset of 0..14, pitch 15 x 16 bytes
-        case HF2Q_TYPE_Q4_0: return 144;     // 8 blocks
-        case HF2Q_TYPE_Q8_0: return 272;     // 8 blocks
-        default: return 0;
-    }
-}
+uint32_t boxw_of(uint32_t type) { return tc_boxw(type); }
 
-template <uint32_t TYPE, int NT>
-cudaError_t launch_gemm_t(const CUtensorMap& tw, const CUtensorMap& tx, const GParams& p, cudaStream_t st) {
-    auto kern = gemm_tc_kernel<TYPE, NT>;
+template <uint32_t TYPE, int NT, bool GROUPED>
+cudaError_t launch_gemm_t(const CUtensorMap& tw, const CUtensorMap& tx, const GParams& p, uint32_t grid_y, cudaStream_t st) {
+    auto kern = gemm_tc_kernel<TYPE, NT, GROUPED>;
     const size_t smem = 1024 + static_cast<size_t>(X_STAGES) * NT * 128 + static_cast<size_t>(raw_stages_of(TYPE)) * TILE_N * p.boxw + 256;
     static std::mutex mu;
     static bool attr_set = false;
@@ -459,18 +272,19 @@ cudaError_t launch_gemm_t(const CUtensorMap& tw, const CUtensorMap& tx, const GP
             attr_set = true;
         }
     }
-    const dim3 grid((p.n + TILE_N - 1) / TILE_N, (p.m + NT - 1) / NT);
+    const dim3 grid((p.n + TILE_N - 1) / TILE_N, grid_y);
     kern<<<grid, GEMM_THREADS, smem, st>>>(tw, tx, p);
     return cudaGetLastError();
 }
 
 template <uint32_t TYPE>
 cudaError_t launch_gemm_nt(const CUtensorMap& tw, const CUtensorMap& tx, const GParams& p, uint32_t nt, cudaStream_t st) {
+    const uint32_t gy = (p.m + nt - 1) / nt;
     switch (nt) {
-        case 32: return launch_gemm_t<TYPE, 32>(tw, tx, p, st);
-        case 64: return launch_gemm_t<TYPE, 64>(tw, tx, p, st);
-        case 128: return launch_gemm_t<TYPE, 128>(tw, tx, p, st);
-        default: return launch_gemm_t<TYPE, 256>(tw, tx, p, st);
+        case 32: return launch_gemm_t<TYPE, 32, false>(tw, tx, p, gy, st);
+        case 64: return launch_gemm_t<TYPE, 64, false>(tw, tx, p, gy, st);
+        case 128: return launch_gemm_t<TYPE, 128, false>(tw, tx, p, gy, st);
+        default: return launch_gemm_t<TYPE, 256, false>(tw, tx, p, gy, st);
     }
 }
 
@@ -547,6 +361,70 @@ cudaError_t launch_gemm_tc(uint32_t type, const void* w, const void* x, uint32_t
     }
 }
 
+
+bool gemm_tc_grouped_supported(uint32_t type, const void* w, uint64_t expert_stride, uint32_t n_experts, uint32_t k) {
+    return gemm_tc_supported(type, w, 0, k) && expert_stride % 16 == 0 && n_experts <= 2048;
+}
+
+template <uint32_t TYPE>
+cudaError_t launch_grouped_nt(const CUtensorMap& tw, const CUtensorMap& tx, const GParams& p, uint32_t nt, uint32_t gy, cudaStream_t st) {
+    switch (nt) {
+        case 32: return launch_gemm_t<TYPE, 32, true>(tw, tx, p, gy, st);
+        case 64: return launch_gemm_t<TYPE, 64, true>(tw, tx, p, gy, st);
+        case 128: return launch_gemm_t<TYPE, 128, true>(tw, tx, p, gy, st);
+        default: return launch_gemm_t<TYPE, 256, true>(tw, tx, p, gy, st);
+    }
+}
+
+// One launch over (weight-row tile, token tile of one expert).  The grid is sized for the largest
+// possible number of token tiles; CTAs past the actual count (read from the scratch header) exit.
+cudaError_t launch_gemm_tc_grouped(uint32_t type, const void* w_stacked, uint64_t expert_stride, uint32_t n_experts, uint32_t rows,
+                                   float* y, uint32_t n, uint32_t k, uint32_t nt, void* scratch, const MoeScratch& lay,
+                                   uint32_t* status, cudaStream_t st) {
+    const BlockGeom g = block_geom(type);
+    const uint64_t row_bytes = static_cast<uint64_t>(k) / g.elems * g.bytes;
+    EncodeTiledFn enc = encode_fn();
+    if (!enc) return cudaErrorNotSupported;
+    uint8_t* base = static_cast<uint8_t*>(scratch);
+    GParams p{};
+    p.y = y; p.m = rows; p.n = n; p.k = k;
+    p.tiles = reinterpret_cast<const GroupTile*>(base + lay.tiles_off);
+    p.n_tiles = reinterpret_cast<const uint32_t*>(base);
+    p.perm = reinterpret_cast<const uint32_t*>(base + lay.perm_off);
+    p.boxw = boxw_of(type);
+    p.blk_bytes = KB / g.elems * g.bytes;
+    p.status = status;
+    alignas(64) CUtensorMap tw, tx;
+    {
+        // stacked experts: [E][n rows][row_bytes] viewed as u16; box = boxw bytes x 128 rows x 1 expert
+        cuuint64_t dims[3] = {row_bytes / 2, n, n_experts};
+        cuuint64_t strides[2] = {row_bytes, expert_stride};
+        cuuint32_t box[3] = {p.boxw / 2, TILE_N, 1};
+        cuuint32_t es[3] = {1, 1, 1};
+        CUresult r = enc(&tw, CU_TENSOR_MAP_DATA_TYPE_UINT16, 3, const_cast<void*>(w_stacked), dims, strides, box, es,
+                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) return cudaErrorInvalidValue;
+    }
+    {
+        cuuint64_t dims[2] = {k, rows};
+        cuuint64_t strides[1] = {static_cast<cuuint64_t>(k) * 2};
+        cuuint32_t box[2] = {XK, nt};
+        cuuint32_t es[2] = {1, 1};
+        CUresult r = enc(&tx, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, base + lay.xg_off, dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                         CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) return cudaErrorInvalidValue;
+    }
+    const uint32_t gy = rows / nt + n_experts;           // >= sum over experts of ceil(count / nt)
+    switch (type) {
+        case HF2Q_TYPE_Q4_0: return launch_grouped_nt<HF2Q_TYPE_Q4_0>(tw, tx, p, nt, gy, st);
+        case HF2Q_TYPE_Q8_0: return launch_grouped_nt<HF2Q_TYPE_Q8_0>(tw, tx, p, nt, gy, st);
+        case HF2Q_TYPE_Q4_K: return launch_grouped_nt<HF2Q_TYPE_Q4_K>(tw, tx, p, nt, gy, st);
+        case HF2Q_TYPE_Q5_K: return launch_grouped_nt<HF2Q_TYPE_Q5_K>(tw, tx, p, nt, gy, st);
+        case HF2Q_TYPE_Q6_K: return launch_grouped_nt<HF2Q_TYPE_Q6_K>(tw, tx, p, nt, gy, st);
+        default: return cudaErrorInvalidValue;
+    }
+}
 
 // ---------------------------------------------------------------- allocation-free variant
 // Scratch for hf2q_cuda_qmatmul_static: the f16 copy of the activations lives in this fixed

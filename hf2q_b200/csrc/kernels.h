@@ -37,12 +37,35 @@ bool gemv_mma_supported(const GemvArgs& a);
 uint32_t gemv_mma_max_rows(uint32_t type, uint32_t k, uint32_t x_dtype, const DeviceInfo& dev);
 cudaError_t launch_gemv_mma(const GemvArgs& a, const DeviceInfo& dev, cudaStream_t st);
 
+// Tensor-memory variant of the mat-vec (k1_gemv_tc.cu): tcgen05 with thread-per-row dequant and a
+// cluster split of k.  Dense calls only, m <= 8.
+bool gemv_tc_supported(const GemvArgs& a);
+cudaError_t launch_gemv_tc(const GemvArgs& a, const DeviceInfo& dev, cudaStream_t st);
+
 // K2 (k2_gemm_tc.cu): tcgen05 GEMM for many activation rows.  Needs k % 256 == 0, 16-byte aligned
 // rows and a workspace of gemm_tc_workspace_bytes(m, k) for the f16 copy of the activations.
 bool gemm_tc_supported(uint32_t type, const void* w, uint32_t n, uint32_t k);
 uint64_t gemm_tc_workspace_bytes(uint32_t m, uint32_t k);
 cudaError_t launch_gemm_tc(uint32_t type, const void* w, const void* x, uint32_t x_dtype, float* y, uint32_t m, uint32_t n,
                            uint32_t k, void* workspace, uint32_t* status, int sm_count, cudaStream_t st, int* launches);
+
+// K4: grouped expert-routed product.  moe_scratch_layout() carves the caller's scratch into header
+// (tile count, sorted-row count), tile table, permutation and the f16 activation panel;
+// launch_moe_prep() sorts routed rows by expert and gathers their activations (k4_moe_prep.cu);
+// launch_gemm_tc_grouped() is the one grouped tensor-core launch (k2_gemm_tc.cu).
+struct MoeScratch {
+    uint64_t tiles_off, perm_off, xg_off, total;
+    uint32_t max_tiles;
+};
+uint32_t moe_token_tile(uint32_t rows, uint32_t n_experts);
+MoeScratch moe_scratch_layout(uint32_t n_experts, uint32_t rows, uint32_t k);
+cudaError_t launch_moe_prep(const uint32_t* ids, uint32_t rows, uint32_t n_experts, uint32_t top_k, uint32_t nt, const void* x,
+                            uint32_t x_dtype, uint32_t k, float* y, uint32_t n, void* scratch, const MoeScratch& lay, uint32_t* status,
+                            int sm_count, cudaStream_t st);
+bool gemm_tc_grouped_supported(uint32_t type, const void* w, uint64_t expert_stride, uint32_t n_experts, uint32_t k);
+cudaError_t launch_gemm_tc_grouped(uint32_t type, const void* w_stacked, uint64_t expert_stride, uint32_t n_experts, uint32_t rows,
+                                   float* y, uint32_t n, uint32_t k, uint32_t nt, void* scratch, const MoeScratch& lay,
+                                   uint32_t* status, cudaStream_t st);
 
 // Fixed scratch of the allocation-free GEMM entry (lives in k2_gemm_tc.cu).
 uint64_t gemm_tc_static_scratch_bytes();
