@@ -11,19 +11,19 @@
 //
 // One CTA computes a tile of 128 weight rows x NT activation rows (tokens):
 //
-//   warp 4 (one lane)   TMA producer.  Per 256-element K-block: one 2-D tensor copy of the RAW block
+//   warp 8 (one lane)   TMA producer.  Per 256-element K-block: one 2-D tensor copy of the RAW block
 //                       bytes of 128 weight rows (box 128 x <=272 B, no swizzle) and four 2-D copies
 //                       of the f16 activations (box NT x 64 elements, 128-byte swizzle) into
 //                       shared-memory rings; completion on mbarriers.
-//   warps 0-3           dequantisers.  Thread r owns weight row r: it reads its own raw bytes from
+//   warps 0-7           dequantisers, two per weight row (one per half K-block).  A thread reads its row's raw bytes from
 //                       shared memory (16-byte vectors, conflict-free pitch), unpacks 256 codes,
 //                       applies d*scale (and -dmin*min) in f16x2 and writes the A operand straight
 //                       into TENSOR MEMORY with tcgen05.st (row = TMEM lane), double-buffered.
 //                       No cross-lane traffic, no shared-memory round trip for the dequantised tile.
-//   warp 5 (one lane)   MMA issuer.  tcgen05.mma.kind::f16, M = 128, N = NT, K = 16, A from TMEM,
+//   warp 9 (one lane)   MMA issuer.  tcgen05.mma.kind::f16, M = 128, N = NT, K = 16, A from TMEM,
 //                       B (activations, K-major, 128B-swizzled) from shared memory, D in TMEM;
 //                       tcgen05.commit releases the activation stages and the A buffers.
-//   warps 0-3 again     epilogue: tcgen05.ld the fp32 accumulators, coalesced stores of y.
+//   warps 0-7 again     epilogue: tcgen05.ld the fp32 accumulators, coalesced stores of y.
 //
 // TMEM: 512 columns = D (<= 256) + 2 x 128 (two A buffers of one K-block each).
 // Every mbarrier wait is bounded; a wait that gives up sets the status word and all roles drain to
@@ -31,6 +31,7 @@
 #include <cuda.h>
 
 #include <mutex>
+#include <type_traits>
 
 #include "common.cuh"
 #include "kernels.h"
@@ -47,7 +48,10 @@ constexpr int KB = 256;          // K elements per block step
 constexpr int XK = 64;           // K elements per activation stage (128 bytes of f16)
 constexpr int raw_stages_of(uint32_t type) { return type == HF2Q_TYPE_Q8_0 ? 2 : 3; }   // 272-byte rows: 2 stages fit
 constexpr int X_STAGES = 4;
-constexpr int GEMM_THREADS = 192;
+constexpr int DEQ_GROUPS = 2;                        // groups of 4 dequantiser warps; group g takes quarters g*2, g*2+1
+constexpr int QPG = 4 / DEQ_GROUPS;                  // quarters (64 elements) of a K-block per group
+constexpr int DEQ_WARPS = 4 * DEQ_GROUPS;
+constexpr int GEMM_THREADS = (DEQ_WARPS + 2) * 32;
 
 // One token tile of the grouped (expert-routed) product: rows [start, start+count) of the
 // expert-sorted activation panel belong to expert `expert`.
@@ -65,17 +69,34 @@ struct GParams {
     uint32_t* status;
 };
 
-template <uint32_t TYPE>
-__device__ __forceinline__ void dequant_dispatch(const uint8_t* row, uint32_t off, uint32_t taddr) {
+// Thread r dequantises quarters [Q0, Q0 + QPG) of its row's K-block into TMEM columns taddr + 32*q.
+template <uint32_t TYPE, int Q0>
+__device__ __forceinline__ void dequant_quarters(const uint8_t* row, uint32_t off, uint32_t taddr) {
     with_row_block<TYPE>(off, [&](auto rb) {
         rb.load(row, off);
 #pragma unroll
-        for (int qd = 0; qd < 4; ++qd) {
+        for (int qd = Q0; qd < Q0 + QPG; ++qd) {
             uint32_t out[32];
             rb.quarter(qd, out);
             tmem_st32(taddr + 32 * qd, out);
         }
     });
+}
+template <uint32_t TYPE>
+__device__ __forceinline__ void dequant_dispatch(uint32_t grp, const uint8_t* row, uint32_t off, uint32_t taddr) {
+    if constexpr (DEQ_GROUPS == 1) {
+        dequant_quarters<TYPE, 0>(row, off, taddr);
+    } else if constexpr (DEQ_GROUPS == 2) {
+        if (grp == 0) dequant_quarters<TYPE, 0>(row, off, taddr);
+        else dequant_quarters<TYPE, 2>(row, off, taddr);
+    } else {
+        switch (grp) {
+            case 0: dequant_quarters<TYPE, 0>(row, off, taddr); break;
+            case 1: dequant_quarters<TYPE, 1>(row, off, taddr); break;
+            case 2: dequant_quarters<TYPE, 2>(row, off, taddr); break;
+            default: dequant_quarters<TYPE, 3>(row, off, taddr); break;
+        }
+    }
 }
 
 // ---------------------------------------------------------------- the kernel
@@ -110,13 +131,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
     const uint32_t nkb = p.k / KB;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < RAW_STAGES; ++s) { mbar_init(&raw_full[s], 1); mbar_init(&raw_empty[s], 4); }
+        for (int s = 0; s < RAW_STAGES; ++s) { mbar_init(&raw_full[s], 1); mbar_init(&raw_empty[s], DEQ_WARPS); }
         for (int s = 0; s < X_STAGES; ++s) { mbar_init(&x_full[s], 1); mbar_init(&x_empty[s], 1); }
-        for (int s = 0; s < 2; ++s) { mbar_init(&a_full[s], 4); mbar_init(&a_empty[s], 1); }
+        for (int s = 0; s < 2; ++s) { mbar_init(&a_full[s], DEQ_WARPS); mbar_init(&a_empty[s], 1); }
         mbar_init(d_full, 1);
         mbar_fence_init();
     }
-    if (warp == 5) { tmem_alloc(tmem_slot, 512); tmem_relinquish(); }
+    if (warp == DEQ_WARPS + 1) { tmem_alloc(tmem_slot, 512); tmem_relinquish(); }
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
@@ -124,7 +145,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
     const uint32_t tmem_d = tmem_base;                 // columns [0, NT)
     const uint32_t tmem_a = tmem_base + 256;           // two buffers of 128 columns
 
-    if (warp == 4) {
+    if (warp == DEQ_WARPS) {
         // ------------------------------ TMA producer
         if (lane == 0) {
             bool ok = true;
@@ -147,7 +168,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
                 }
             }
         }
-    } else if (warp == 5) {
+    } else if (warp == DEQ_WARPS + 1) {
         // ------------------------------ MMA issuer
         if (lane == 0) {
             // instruction descriptor: D f32, A/B f16, both K-major, N = NT, M = 128
@@ -178,8 +199,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
         }
     } else {
         // ------------------------------ dequantisers (thread = weight row), then epilogue
-        const uint32_t r = threadIdx.x;                    // 0..127 == TMEM lane
-        const uint32_t lane_addr = (static_cast<uint32_t>(warp) * 32u) << 16;
+        const uint32_t quad = warp & 3, grp = static_cast<uint32_t>(warp) >> 2;
+        const uint32_t r = quad * 32 + lane;               // weight row of the tile == TMEM lane
+        const uint32_t lane_addr = (quad * 32u) << 16;
         bool ok = true;
         for (uint32_t kb = 0; kb < nkb; ++kb) {
             const uint32_t rs = kb % RAW_STAGES, ab = kb & 1;
@@ -189,7 +211,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
             if (!ok) break;
             tc_fence_after();
             const uint32_t off = (kb * p.blk_bytes) & 15u;
-            dequant_dispatch<TYPE>(raw + rs * raw_stage + r * p.boxw, off, tmem_a + ab * 128 + lane_addr);
+            dequant_dispatch<TYPE>(grp, raw + rs * raw_stage + r * p.boxw, off, tmem_a + ab * 128 + lane_addr);
             tmem_wait_st();
             tc_fence_before();
             __syncwarp();
@@ -202,7 +224,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
             tc_fence_after();
             const uint32_t row = row0 + r;
 #pragma unroll 1
-            for (int c0 = 0; c0 < NT; c0 += 32) {
+            for (int c0 = 32 * static_cast<int>(grp); c0 < NT; c0 += 32 * DEQ_GROUPS) {   // the groups share the columns
                 uint32_t v[32];
                 tmem_ld32(tmem_d + lane_addr + c0, v);
                 tmem_wait_ld();
@@ -221,7 +243,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
     }
     tc_fence_before();
     __syncthreads();
-    if (warp == 5) { tc_fence_after(); tmem_dealloc(tmem_base, 512); }
+    if (warp == DEQ_WARPS + 1) { tc_fence_after(); tmem_dealloc(tmem_base, 512); }
 }
 
 // ---------------------------------------------------------------- activations -> f16 panel

@@ -1,0 +1,92 @@
+"""Multi-GPU wrappers of the quantized-matmul path: one process per GPU, torch.distributed plumbing.
+
+The reference is single-device (no collective exists in hf2q), so both schemes are new:
+
+* dense weights are sharded by OUTPUT ROWS -- a shard is a contiguous byte range of the raw block
+  bytes -- and every product is followed by an all-gather of the output columns;
+* MoE experts are sharded BY EXPERT (E / world per rank); routed rows travel to the rank that owns
+  their expert with an all-to-all, are multiplied there by the local grouped product, and travel
+  back with a second all-to-all.
+
+The functions take the local compute as a callable, so the same host logic runs over NCCL with
+the CUDA library and over gloo on CPU in the tests.  Remote data always lands in local memory
+(the collective's receive buffer) before any kernel reads it; no kernel here touches peer memory.
+"""
+from __future__ import annotations
+
+from typing import Callable, Sequence
+
+import torch
+import torch.distributed as dist
+
+
+def shard_rows(n: int, world: int, rank: int) -> tuple[int, int]:
+    """Rows [r0, r1) of an n-row weight owned by `rank`: contiguous, sizes differ by at most one."""
+    base, rem = divmod(n, world)
+    r0 = rank * base + min(rank, rem)
+    return r0, r0 + base + (1 if rank < rem else 0)
+
+
+def rowshard_matmul(x: torch.Tensor, local_matmul: Callable[[torch.Tensor], torch.Tensor], n: int,
+                    group=None) -> torch.Tensor:
+    """y[m, n] = x . W^T with W sharded by rows: local product, then all-gather of the columns.
+
+    ``local_matmul(x)`` returns this rank's [m, n_local] float32 block (n_local from shard_rows)."""
+    world = dist.get_world_size(group)
+    rank = dist.get_rank(group)
+    y_local = local_matmul(x)
+    m = y_local.shape[0]
+    sizes = [shard_rows(n, world, r)[1] - shard_rows(n, world, r)[0] for r in range(world)]
+    assert y_local.shape[1] == sizes[rank]
+    if world == 1:
+        return y_local
+    pad = max(sizes)
+    if len(set(sizes)) == 1:
+        out = torch.empty((world * m, pad), dtype=y_local.dtype, device=y_local.device)
+        dist.all_gather_into_tensor(out, y_local.contiguous(), group=group)
+        return out.view(world, m, pad).permute(1, 0, 2).reshape(m, n)
+    send = torch.zeros((m, pad), dtype=y_local.dtype, device=y_local.device)
+    send[:, : sizes[rank]] = y_local
+    parts = [torch.empty_like(send) for _ in range(world)]
+    dist.all_gather(parts, send, group=group)
+    return torch.cat([p[:, :s] for p, s in zip(parts, sizes)], dim=1)
+
+
+def expert_owner(ids: torch.Tensor, n_experts: int, world: int) -> torch.Tensor:
+    """Rank that owns each routed row's expert (experts are split into `world` equal ranges)."""
+    assert n_experts % world == 0, "experts must divide evenly over the ranks"
+    return torch.div(ids.to(torch.int64), n_experts // world, rounding_mode="floor")
+
+
+def ep_mul_mat_id(x_rows: torch.Tensor, ids: torch.Tensor, n_experts: int, n_out: int,
+                  local_mul_mat_id: Callable[[torch.Tensor, torch.Tensor], torch.Tensor], group=None) -> torch.Tensor:
+    """Expert-parallel mul_mat_id.
+
+    x_rows: [R, k] activations, one row per routed row held by THIS rank; ids: [R] global expert ids.
+    ``local_mul_mat_id(x, local_ids)`` multiplies rows by this rank's experts (ids relative to the
+    rank's first expert) and returns [rows, n_out] float32.  Returns [R, n_out] in the caller's order.
+    """
+    world = dist.get_world_size(group)
+    rank = dist.get_rank(group)
+    e_local = n_experts // world
+    if world == 1:
+        return local_mul_mat_id(x_rows, ids)
+    owner = expert_owner(ids, n_experts, world)
+    order = torch.sort(owner, stable=True).indices                  # rows grouped by destination rank
+    send_counts = torch.bincount(owner, minlength=world)
+    recv_counts = torch.empty_like(send_counts)
+    dist.all_to_all_single(recv_counts, send_counts, group=group)   # how many rows each peer sends us
+    sc, rc = send_counts.tolist(), recv_counts.tolist()
+    x_send = x_rows.index_select(0, order).contiguous()
+    id_send = (ids.index_select(0, order).to(torch.int64) - owner.index_select(0, order) * e_local).to(torch.int32).contiguous()
+    x_recv = torch.empty((sum(rc), x_rows.shape[1]), dtype=x_rows.dtype, device=x_rows.device)
+    id_recv = torch.empty((sum(rc),), dtype=torch.int32, device=x_rows.device)
+    dist.all_to_all_single(x_recv, x_send, output_split_sizes=rc, input_split_sizes=sc, group=group)
+    dist.all_to_all_single(id_recv, id_send, output_split_sizes=rc, input_split_sizes=sc, group=group)
+    y_recv = local_mul_mat_id(x_recv, id_recv) if x_recv.shape[0] else torch.empty((0, n_out), dtype=torch.float32, device=x_rows.device)
+    y_back = torch.empty((x_rows.shape[0], n_out), dtype=torch.float32, device=x_rows.device)
+    dist.all_to_all_single(y_back, y_recv.contiguous(), output_split_sizes=sc, input_split_sizes=rc, group=group)
+    out = torch.empty_like(y_back)
+    out.index_copy_(0, order, y_back)
+    _ = rank
+    return out
