@@ -46,8 +46,14 @@ namespace {
 constexpr int TILE_N = 128;      // weight rows per CTA (MMA M)
 constexpr int KB = 256;          // K elements per block step
 constexpr int XK = 64;           // K elements per activation stage (128 bytes of f16)
-constexpr int raw_stages_of(uint32_t type) { return type == HF2Q_TYPE_Q8_0 ? 2 : 3; }   // 272-byte rows: 2 stages fit
-constexpr int X_STAGES = 4;
+constexpr int raw_stages_of(uint32_t type, int nt) { return (type == HF2Q_TYPE_Q8_0 || nt >= 256 || nt <= 64) ? 2 : 3; }
+// Tiles of <= 64 tokens run two CTAs per SM (one CTA's fixed latencies hide behind the other's work):
+// one A buffer instead of two and 256 TMEM columns instead of 512.
+constexpr int a_bufs_of(int nt) { return nt <= 64 ? 1 : 2; }
+constexpr uint32_t tmem_cols_of(int nt) { return nt <= 64 ? 256u : 512u; }
+// activation stages: one stage is NT rows x 64 elements; keep ~128 KB of them in flight so that the
+// copies for the next K-blocks are issued long before the MMA warp needs them
+constexpr int x_stages_of(uint32_t type, int nt) { return nt >= 256 ? (type == HF2Q_TYPE_Q8_0 ? 4 : 5) : 8; }
 constexpr int DEQ_GROUPS = 2;                        // groups of 4 dequantiser warps; group g takes quarters g*2, g*2+1
 constexpr int QPG = 4 / DEQ_GROUPS;                  // quarters (64 elements) of a K-block per group
 constexpr int DEQ_WARPS = 4 * DEQ_GROUPS;
@@ -101,13 +107,14 @@ __device__ __forceinline__ void dequant_dispatch(uint32_t grp, const uint8_t* ro
 
 // ---------------------------------------------------------------- the kernel
 template <uint32_t TYPE, int NT, bool GROUPED>
-__global__ void __launch_bounds__(GEMM_THREADS, 1)
+__global__ void __launch_bounds__(GEMM_THREADS, (NT <= 64 ? 2 : 1))
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x, const GParams p) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
     constexpr uint32_t X_STAGE = NT * 128;                       // NT rows x 64 f16, 128B-swizzled
+    constexpr int X_STAGES = x_stages_of(TYPE, NT);
     uint8_t* xs = smem;                                          // X_STAGES x X_STAGE (1024-aligned)
-    constexpr int RAW_STAGES = raw_stages_of(TYPE);
+    constexpr int RAW_STAGES = raw_stages_of(TYPE, NT);
     uint8_t* raw = xs + X_STAGES * X_STAGE;                      // RAW_STAGES x 128 x boxw
     const uint32_t raw_stage = TILE_N * p.boxw;
     uint64_t* bars = reinterpret_cast<uint64_t*>(raw + RAW_STAGES * raw_stage);
@@ -115,6 +122,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
     uint64_t* raw_empty = raw_full + RAW_STAGES;
     uint64_t* x_full = raw_empty + RAW_STAGES;  // [X_STAGES]
     uint64_t* x_empty = x_full + X_STAGES;
+    constexpr int A_BUFS = a_bufs_of(NT);
+    constexpr uint32_t TMEM_COLS = tmem_cols_of(NT);
     uint64_t* a_full = x_empty + X_STAGES;      // [2]
     uint64_t* a_empty = a_full + 2;
     uint64_t* d_full = a_empty + 2;             // [1]
@@ -137,13 +146,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
         mbar_init(d_full, 1);
         mbar_fence_init();
     }
-    if (warp == DEQ_WARPS + 1) { tmem_alloc(tmem_slot, 512); tmem_relinquish(); }
+    if (warp == DEQ_WARPS + 1) { tmem_alloc(tmem_slot, TMEM_COLS); tmem_relinquish(); }
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
     const uint32_t tmem_d = tmem_base;                 // columns [0, NT)
-    const uint32_t tmem_a = tmem_base + 256;           // two buffers of 128 columns
+    const uint32_t tmem_a = tmem_base + (A_BUFS == 1 ? 128 : 256);     // A_BUFS buffers of 128 columns
 
     if (warp == DEQ_WARPS) {
         // ------------------------------ TMA producer
@@ -175,8 +184,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
             constexpr uint32_t IDESC = (1u << 4) | (static_cast<uint32_t>(NT >> 3) << 17) | (static_cast<uint32_t>(128 >> 4) << 24);
             bool ok = true;
             for (uint32_t kb = 0; kb < nkb && ok; ++kb) {
-                const uint32_t ab = kb & 1;
-                ok = mbar_wait_bounded(&a_full[ab], (kb >> 1) & 1, p.status);
+                const uint32_t ab = kb % A_BUFS;
+                ok = mbar_wait_bounded(&a_full[ab], (kb / A_BUFS) & 1, p.status);
                 if (!ok) break;
                 tc_fence_after();
                 for (uint32_t j = 0; j < KB / XK && ok; ++j) {
@@ -204,9 +213,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
         const uint32_t lane_addr = (quad * 32u) << 16;
         bool ok = true;
         for (uint32_t kb = 0; kb < nkb; ++kb) {
-            const uint32_t rs = kb % RAW_STAGES, ab = kb & 1;
+            const uint32_t rs = kb % RAW_STAGES, ab = kb % A_BUFS;
             if (ok) ok = mbar_wait_bounded(&raw_full[rs], (kb / RAW_STAGES) & 1, p.status);
-            if (ok && kb >= 2) ok = mbar_wait_bounded(&a_empty[ab], ((kb >> 1) - 1) & 1, p.status);
+            if (ok && kb >= A_BUFS) ok = mbar_wait_bounded(&a_empty[ab], ((kb / A_BUFS) - 1) & 1, p.status);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
             tc_fence_after();
@@ -243,7 +252,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
     }
     tc_fence_before();
     __syncthreads();
-    if (warp == DEQ_WARPS + 1) { tc_fence_after(); tmem_dealloc(tmem_base, 512); }
+    if (warp == DEQ_WARPS + 1) { tc_fence_after(); tmem_dealloc(tmem_base, TMEM_COLS); }
 }
 
 // ---------------------------------------------------------------- activations -> f16 panel
@@ -283,7 +292,7 @@ uint32_t boxw_of(uint32_t type) { return tc_boxw(type); }
 template <uint32_t TYPE, int NT, bool GROUPED>
 cudaError_t launch_gemm_t(const CUtensorMap& tw, const CUtensorMap& tx, const GParams& p, uint32_t grid_y, cudaStream_t st) {
     auto kern = gemm_tc_kernel<TYPE, NT, GROUPED>;
-    const size_t smem = 1024 + static_cast<size_t>(X_STAGES) * NT * 128 + static_cast<size_t>(raw_stages_of(TYPE)) * TILE_N * p.boxw + 256;
+    const size_t smem = 1024 + static_cast<size_t>(x_stages_of(TYPE, NT)) * NT * 128 + static_cast<size_t>(raw_stages_of(TYPE, NT)) * TILE_N * p.boxw + 512;
     static std::mutex mu;
     static bool attr_set = false;
     {
@@ -323,8 +332,23 @@ uint64_t gemm_tc_workspace_bytes(uint32_t m, uint32_t k) {
     return (static_cast<uint64_t>(m) * k * 2 + 255) & ~static_cast<uint64_t>(255);
 }
 
-// Tokens per CTA tile for m activation rows.
-uint32_t gemm_tc_token_tile(uint32_t m) { return m > 128 ? 256 : m > 64 ? 128 : m > 32 ? 64 : 32; }
+// Tokens per CTA tile for m activation rows over `tiles_n` weight-row tiles: the widest tile whose
+// CTA count still fills the SMs evenly (wide tiles amortise the dequantisation best).
+uint32_t gemm_tc_token_tile(uint32_t m, uint32_t tiles_n, int sms) {
+    if (m <= 32) return 32;
+    if (m <= 64) return 64;
+    uint32_t best = 128;
+    double best_score = -1.0;
+    for (uint32_t nt : {256u, 128u, 64u}) {
+        if (nt / 2 >= m) continue;
+        const uint32_t ctas = tiles_n * ((m + nt - 1) / nt);
+        const uint32_t waves = (ctas + sms - 1) / sms;
+        const double fill = static_cast<double>(ctas) / (static_cast<double>(waves) * sms);
+        const double score = fill * (nt == 256 ? 1.0 : nt == 128 ? 0.78 : 0.55);   // measured relative tile efficiency
+        if (score > best_score) { best_score = score; best = nt; }
+    }
+    return best;
+}
 
 cudaError_t launch_gemm_tc(uint32_t type, const void* w, const void* x, uint32_t x_dtype, float* y, uint32_t m, uint32_t n,
                            uint32_t k, void* workspace, uint32_t* status, int sm_count, cudaStream_t st, int* launches) {
@@ -349,7 +373,7 @@ cudaError_t launch_gemm_tc(uint32_t type, const void* w, const void* x, uint32_t
     p.boxw = boxw_of(type);
     p.blk_bytes = KB / g.elems * g.bytes;
     p.status = status;
-    const uint32_t nt = gemm_tc_token_tile(m);
+    const uint32_t nt = gemm_tc_token_tile(m, (n + TILE_N - 1) / TILE_N, sm_count);
     alignas(64) CUtensorMap tw, tx;
     {
         // weights: [n rows][row_bytes] viewed as u16, box = boxw bytes x 128 rows, no swizzle
