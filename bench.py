@@ -268,8 +268,9 @@ def main() -> None:
     for _ in range(args.warmup):
         step()
     barrier()
-    # One step's launches are captured into a CUDA graph and replayed (what a decode loop does);
-    # with collectives in the step the launches are issued eagerly instead.
+    # One step's launches are captured into a CUDA graph and replayed (what a decode loop does).
+    # With NCCL all-gathers in the step (several GPUs) the launches are issued eagerly: capturing the
+    # collectives into the graph did not complete on this pool (the run had to be killed).
     graph = None
     if world == 1 and not args.no_graph:
         try:
