@@ -186,6 +186,124 @@ def run_reference(args) -> None:
     print(json.dumps(line))
 
 
+def measured_tensor_peak() -> tuple[float, str]:
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        try:
+            return float(json.loads(p.read_text())["bf16_tflops_sustained"]), "measured (sustained)"
+        except Exception:
+            pass
+    return 1400.0, "fallback"
+
+
+def run_secondary(args) -> None:
+    """The other two kernels of the path on one GPU, same timing rules, one JSON line each run.
+
+    gemm: BASELINE config 3 -- Q4_K for 6144x4096, 4096x4096, 28672x4096 and Q6_K for the 4096x14336
+          down projection, bf16 activations, M in {512, 2048, 4096}; metric = TFLOP/s (2*M*N*K).
+    moe:  BASELINE config 4 -- 256 experts, hidden 2048, intermediate 512, top-8, Q5_K; gate, up and
+          down mul_mat_id at T in {1, 2048}; metric = layer time and the two rooflines.
+    Weights here are random block bytes with finite scales (throughput does not depend on the values;
+    parity is what the tests check)."""
+    import torch
+
+    import hf2q_b200 as hq
+    import oracle
+
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    ctx = hq.GpuContext(0)
+
+    def random_weight(t, rows, k):
+        rb = oracle.row_bytes(t, k)
+        raw = torch.randint(0, 256, (rows * rb,), dtype=torch.uint8, device=dev)
+        be, bb = oracle.block_geometry(t)
+        v = raw.view(-1, bb)
+        for o in {2: [1], 8: [1], 12: [1, 3], 13: [1, 3], 14: [209]}[t]:       # high byte of each f16 scale
+            v[:, o] &= 0x3B                                                     # finite, |d| < 1
+        return raw
+
+    def timed(fn, reps):
+        for _ in range(max(3, args.warmup)):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) * 1e-3 / reps
+
+    sampler = ClockSampler(0)
+    sampler.start()
+    l0 = ctx.launch_count
+    if args.workload == "gemm":
+        cases = [(12, 6144, 4096), (12, 4096, 4096), (12, 28672, 4096), (14, 4096, 14336)]
+        toks = [args.tokens] if args.tokens else [512, 2048, 4096]
+        rows, flops, secs = {}, 0.0, 0.0
+        for (t, n, k) in cases:
+            w = hq.load_quant_weight(ctx, random_weight(t, n, k), t, n, k)
+            for m in toks:
+                x = torch.randn(m, k, device=dev).bfloat16()
+                y = torch.empty(m, n, device=dev)
+                prm = hq.GgmlQuantizedMatmulParams(m, n, k, t)
+                dt = timed(lambda: hq.quantized_matmul_ggml(ctx, x, w, y, prm), max(3, min(args.steps, 20)))
+                rows[f"{oracle.TYPE_NAMES[t]}_{n}x{k}_M{m}"] = round(2.0 * m * n * k / dt / 1e12, 1)
+                flops += 2.0 * m * n * k
+                secs += dt
+        peak, kind = measured_tensor_peak()
+        val = flops / secs / 1e12
+        line = {"metric": "prefill dequant-GEMM TFLOP/s", "value": round(val, 1), "unit": "TFLOP/s", "n_gpus": 1,
+                "higher_is_better": True, "dtype": "f16 operands, f32 accumulate", "data": "synthetic",
+                "config": {"workload": "Q4_K_M prefill GEMM sweep (Q4_K x3 shapes, Q6_K 4096x14336), bf16 activations",
+                           "tokens": toks, "timing": "CUDA events, activation conversion kernel included"},
+                "roofline": {"bound": "tensor", "achieved": round(val, 1), "peak": peak, "unit": "TFLOP/s",
+                             "frac": round(val / peak, 4), "peak_source": f"of {kind}", "kernel": "gemm_tc_kernel", "traffic": None},
+                "per_case_TFLOPs": rows}
+    else:
+        t, E, H, I, topk = 13, 256, 2048, 512, 8
+        sg, sd = hq.expert_stride(t, I, H), hq.expert_stride(t, H, I)
+        wg, wu, wd = random_weight(t, E * I, H), random_weight(t, E * I, H), random_weight(t, E * H, I)
+        res = {}
+        for T in ([args.tokens] if args.tokens else [1, 2048]):
+            logits = torch.randn(T, E, device=dev)
+            ids, _ = hq.moe_softmax_topk(ctx, logits, topk)
+            x = torch.randn(T, H, device=dev).bfloat16()
+            R = T * topk
+            g, u = torch.empty(R, I, device=dev), torch.empty(R, I, device=dev)
+            d = torch.empty(R, H, device=dev)
+            act = torch.randn(R, I, device=dev).bfloat16()
+            sc = hq.IdMmScratch.alloc(ctx, E, R, H)
+            pg = hq.GgmlQuantizedMatmulIdParams(T, topk, I, H, E, sg, t)
+            pd = hq.GgmlQuantizedMatmulIdParams(R, 1, H, I, E, sd, t)
+
+            def layer():
+                hq.quantized_matmul_id_ggml(ctx, x, wg.data_ptr(), ids, g, sc, pg)
+                hq.quantized_matmul_id_ggml(ctx, x, wu.data_ptr(), ids, u, sc, pg)
+                hq.quantized_matmul_id_ggml(ctx, act, wd.data_ptr(), ids, d, sc, pd)
+
+            dt = timed(layer, max(3, min(args.steps, 20)))
+            nexp = int(torch.unique(ids).numel())
+            wbytes = nexp * (2 * sg + sd)
+            res[f"T{T}"] = {"us_per_layer": round(dt * 1e6, 1), "TFLOPs": round(2.0 * R * 3 * I * H / dt / 1e12, 2),
+                            "weight_GBps": round(wbytes / dt / 1e9, 1), "experts_touched": nexp}
+        peak_h, kind_h = measured_hbm_peak()
+        last = res[sorted(res)[-1]]
+        line = {"metric": "MoE mul_mat_id layer time", "value": last["us_per_layer"], "unit": "us", "n_gpus": 1,
+                "higher_is_better": False, "dtype": "f16 operands, f32 accumulate", "data": "synthetic",
+                "config": {"workload": "Qwen3-style A3B expert layer: 256 experts, hidden 2048, intermediate 512, top-8, Q5_K; "
+                                       "gate + up + down mul_mat_id (router outputs from the softmax/top-k kernel)"},
+                "roofline": {"bound": "hbm", "achieved": last["weight_GBps"], "peak": peak_h, "unit": "GB/s",
+                             "frac": round(last["weight_GBps"] / peak_h, 4), "peak_source": f"of {kind_h}",
+                             "kernel": "gemm_tc_kernel<grouped> + moe_sort/gather (T=2048), gemv_mma_kernel (T=1)", "traffic": None},
+                "per_case": res}
+    line["gpu_launches"] = int(ctx.launch_count - l0)
+    line["clocks"] = sampler.stop()
+    ctx.check_status()
+    print(json.dumps(line))
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -196,11 +314,18 @@ def main() -> None:
     ap.add_argument("--e2e-steps", type=int, default=0, help="steps of the host-buffer leg (0 = auto)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-graph", action="store_true", help="issue launches eagerly instead of replaying a CUDA graph")
+    ap.add_argument("--workload", default="gemv", choices=["gemv", "gemm", "moe"],
+                    help="gemv: the headline Q6_K decode sweep (default); gemm: Q4_K_M prefill GEMM sweep; "
+                         "moe: Qwen3-style A3B expert layer (Q5_K mul_mat_id)")
+    ap.add_argument("--tokens", type=int, default=0, help="gemm/moe: one token count instead of the sweep")
     args = ap.parse_args()
     if args.warmup < 3:
         args.warmup = 3
     if args.impl == "reference":
         run_reference(args)
+        return
+    if args.workload != "gemv":
+        run_secondary(args)
         return
 
     import torch
