@@ -40,6 +40,9 @@ SIGNATURES = {
     "hf2q_cuda_qmatmul_id": (i32, [vp, vp, vp, u32, vp, vp, vp, u32, u32, u32, u32, u32, u64, u32, vp, u64]),
     "hf2q_cuda_qmatmul_id_scratch_bytes": (i32, [u32, u32, u32, u32, C.POINTER(u64)]),
     "hf2q_cuda_moe_softmax_topk": (i32, [vp, vp, vp, vp, vp, u32, u32, u32]),
+    "hf2q_cuda_silu_mul": (i32, [vp, vp, vp, vp, vp, u64]),
+    "hf2q_cuda_moe_combine": (i32, [vp, vp, vp, vp, vp, vp, vp, vp, u32, u32, u32]),
+    "hf2q_cuda_rowdot": (i32, [vp, vp, vp, vp, vp, u32, u32]),
     "hf2q_cuda_launch_count": (u64, [vp]),
     "hf2q_cuda_sm_count": (i32, [vp]),
     "hf2q_cuda_version": (C.c_char_p, []),

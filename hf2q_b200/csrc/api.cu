@@ -450,6 +450,45 @@ HF2Q_API int32_t hf2q_cuda_moe_softmax_topk(hf2q_ctx* ctx, void* stream, const f
     return HF2Q_OK;
 }
 
+HF2Q_API int32_t hf2q_cuda_silu_mul(hf2q_ctx* ctx, void* stream, const float* gate, const float* up, float* out, uint64_t n) {
+    if (!ctx) return HF2Q_ERR_INVALID_ARGUMENT;
+    if (!gate || !up || !out) return fail(ctx, HF2Q_ERR_INVALID_ARGUMENT, "silu_mul: null pointer");
+    if (n == 0) return HF2Q_OK;
+    DeviceGuard dg(ctx->device);
+    const cudaError_t e = launch_silu_mul(gate, up, out, n, ctx->dev.sm_count, static_cast<cudaStream_t>(stream));
+    if (e != cudaSuccess) return cuda_fail(ctx, e, "silu_mul launch");
+    ctx->launches += 1;
+    return HF2Q_OK;
+}
+
+HF2Q_API int32_t hf2q_cuda_moe_combine(hf2q_ctx* ctx, void* stream, const float* y, const float* weights, const float* shared,
+                                       const float* shared_gate_logit, const float* residual, float* out, uint32_t n_tokens,
+                                       uint32_t top_k, uint32_t hidden) {
+    if (!ctx) return HF2Q_ERR_INVALID_ARGUMENT;
+    if (!y || !weights || !out) return fail(ctx, HF2Q_ERR_INVALID_ARGUMENT, "moe_combine: null pointer");
+    if (top_k == 0 || hidden == 0) return fail(ctx, HF2Q_ERR_INVALID_ARGUMENT, "moe_combine: top_k and hidden must be non-zero");
+    if (n_tokens == 0) return HF2Q_OK;
+    if (n_tokens > 65535) return fail(ctx, HF2Q_ERR_INVALID_ARGUMENT, "moe_combine: n_tokens=%u exceeds 65535 per call", n_tokens);
+    DeviceGuard dg(ctx->device);
+    const cudaError_t e = launch_moe_combine(y, weights, shared, shared_gate_logit, residual, out, n_tokens, top_k, hidden,
+                                             static_cast<cudaStream_t>(stream));
+    if (e != cudaSuccess) return cuda_fail(ctx, e, "moe_combine launch");
+    ctx->launches += 1;
+    return HF2Q_OK;
+}
+
+HF2Q_API int32_t hf2q_cuda_rowdot(hf2q_ctx* ctx, void* stream, const float* x, const float* v, float* out, uint32_t n_tokens,
+                                  uint32_t hidden) {
+    if (!ctx) return HF2Q_ERR_INVALID_ARGUMENT;
+    if (!x || !v || !out) return fail(ctx, HF2Q_ERR_INVALID_ARGUMENT, "rowdot: null pointer");
+    if (n_tokens == 0) return HF2Q_OK;
+    DeviceGuard dg(ctx->device);
+    const cudaError_t e = launch_rowdot(x, v, out, n_tokens, hidden, static_cast<cudaStream_t>(stream));
+    if (e != cudaSuccess) return cuda_fail(ctx, e, "rowdot launch");
+    ctx->launches += 1;
+    return HF2Q_OK;
+}
+
 HF2Q_API uint64_t hf2q_cuda_launch_count(const hf2q_ctx* ctx) { return ctx ? ctx->launches : 0; }
 HF2Q_API int32_t hf2q_cuda_sm_count(const hf2q_ctx* ctx) { return ctx ? ctx->dev.sm_count : 0; }
 

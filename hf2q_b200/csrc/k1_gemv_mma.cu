@@ -293,8 +293,8 @@ __global__ void __launch_bounds__(THREADS) gemv_mma_kernel(const MParams p) {
     uint64_t* empty = full + MAX_STAGES;
     uint8_t* ring = smem + 128;
     const uint32_t stage_bytes = ROWS * p.pitch;
-    float* red = reinterpret_cast<float*>(ring + p.stages * stage_bytes);        // [2][CWARPS][16][8]
-    float* scr = red + 2 * CWARPS * 128;                                        // [CWARPS][16][8]
+    float* red = reinterpret_cast<float*>(ring + p.stages * stage_bytes);        // [CWARPS][16][8]
+    float* scr = red + CWARPS * 128;                                            // [CWARPS][16][8]
     uint8_t* xh = reinterpret_cast<uint8_t*>(scr + CWARPS * 16 * 8);             // [nslots][xpitch]
     uint8_t* sxp = xh + p.nslots * p.xpitch;
     const uint32_t nblk_total = p.k >> 8;
@@ -323,15 +323,14 @@ __global__ void __launch_bounds__(THREADS) gemv_mma_kernel(const MParams p) {
     if (warp == CWARPS) {
         // ---------------- producer warp: lane r copies row r of each stage ----------------
         if (slot_ok) {
-            uint32_t it = 0;
+            uint32_t it = 0, st = 0, ph = 1;      // ring slot and the parity of its previous use
             bool alive = true;
             for (uint32_t rg = blockIdx.x; rg < p.ngroups && alive; rg += gridDim.x) {
                 const uint32_t row0 = rg * ROWS;
                 const uint32_t nrows = min(static_cast<uint32_t>(ROWS), p.n - row0);
-                for (uint32_t s = 0; s < p.nslices; ++s, ++it) {
-                    const uint32_t st = it % p.stages;
+                for (uint32_t s = 0; s < p.nslices; ++s, ++it, st = (st + 1 == p.stages ? 0 : st + 1), ph ^= (st == 0)) {
                     if (it >= p.stages) {
-                        alive = mbar_wait_bounded(&empty[st], ((it / p.stages) - 1) & 1, p.status);
+                        alive = mbar_wait_bounded(&empty[st], ph, p.status);
                         alive = __all_sync(0xffffffffu, alive);
                         if (!alive) break;
                     }
@@ -351,41 +350,61 @@ __global__ void __launch_bounds__(THREADS) gemv_mma_kernel(const MParams p) {
     // ---------------- consumers: build the f16 activation panel and its sub-block sums ------------
     const int ctid = threadIdx.x;
     {
-        const uint32_t k8 = p.k >> 3;
+        // 8 elements per item; four items per thread and pass so that four independent loads are
+        // in flight before the first conversion
+        const uint32_t k8 = p.k >> 3, total = p.nslots * k8;
         bool clipped = false;
-        for (uint32_t idx = ctid; idx < p.nslots * k8; idx += CT) {
-            const uint32_t s = idx / k8, e = (idx - s * k8) * 8;
-            float v[8];
-            if (p.x_bf16) {
-                const uint4 r = __ldg(reinterpret_cast<const uint4*>(
-                    static_cast<const __nv_bfloat16*>(p.x) + (static_cast<size_t>(xrow_idx) + s) * p.k + e));
-                const uint32_t rr[4] = {r.x, r.y, r.z, r.w};
+        for (uint32_t base = ctid; base < total; base += 4 * CT) {
+            uint4 ra[4], rb[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const uint32_t idx = base + u * CT;
+                ra[u] = make_uint4(0, 0, 0, 0); rb[u] = ra[u];
+                if (idx < total) {
+                    const uint32_t s = idx / k8, e = (idx - s * k8) * 8;
+                    if (p.x_bf16) {
+                        ra[u] = __ldg(reinterpret_cast<const uint4*>(
+                            static_cast<const __nv_bfloat16*>(p.x) + (static_cast<size_t>(xrow_idx) + s) * p.k + e));
+                    } else {
+                        const float* src = static_cast<const float*>(p.x) + (static_cast<size_t>(xrow_idx) + (s >> 1)) * p.k + e;
+                        ra[u] = __ldg(reinterpret_cast<const uint4*>(src));
+                        rb[u] = __ldg(reinterpret_cast<const uint4*>(src + 4));
+                    }
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const uint32_t idx = base + u * CT;
+                if (idx >= total) continue;
+                const uint32_t s = idx / k8, e = (idx - s * k8) * 8;
+                float v[8];
+                if (p.x_bf16) {
+                    const uint32_t rr[4] = {ra[u].x, ra[u].y, ra[u].z, ra[u].w};
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        v[2 * j] = __uint_as_float(rr[j] << 16);
+                        v[2 * j + 1] = __uint_as_float(rr[j] & 0xffff0000u);
+                    }
+                } else {
+                    v[0] = __uint_as_float(ra[u].x); v[1] = __uint_as_float(ra[u].y); v[2] = __uint_as_float(ra[u].z); v[3] = __uint_as_float(ra[u].w);
+                    v[4] = __uint_as_float(rb[u].x); v[5] = __uint_as_float(rb[u].y); v[6] = __uint_as_float(rb[u].z); v[7] = __uint_as_float(rb[u].w);
+                }
+                uint32_t out[4];
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
-                    v[2 * j] = __uint_as_float(rr[j] << 16);
-                    v[2 * j + 1] = __uint_as_float(rr[j] & 0xffff0000u);
+                    float a = v[2 * j], b = v[2 * j + 1];
+                    clipped |= (fabsf(a) > 65504.0f) | (fabsf(b) > 65504.0f);
+                    a = fminf(fmaxf(a, -65504.0f), 65504.0f);
+                    b = fminf(fmaxf(b, -65504.0f), 65504.0f);
+                    __half ha = __float2half_rn(a), hb = __float2half_rn(b);
+                    if (!p.x_bf16 && (s & 1)) {          // lo part of the f32 split
+                        ha = __float2half_rn(a - __half2float(ha));
+                        hb = __float2half_rn(b - __half2float(hb));
+                    }
+                    out[j] = static_cast<uint32_t>(__half_as_ushort(ha)) | (static_cast<uint32_t>(__half_as_ushort(hb)) << 16);
                 }
-            } else {
-                const float* src = static_cast<const float*>(p.x) + (static_cast<size_t>(xrow_idx) + (s >> 1)) * p.k + e;
-                const float4 a = __ldg(reinterpret_cast<const float4*>(src));
-                const float4 b = __ldg(reinterpret_cast<const float4*>(src + 4));
-                v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+                *reinterpret_cast<uint4*>(xh + s * p.xpitch + 2 * e) = make_uint4(out[0], out[1], out[2], out[3]);
             }
-            uint32_t out[4];
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                float a = v[2 * j], b = v[2 * j + 1];
-                clipped |= (fabsf(a) > 65504.0f) | (fabsf(b) > 65504.0f);
-                a = fminf(fmaxf(a, -65504.0f), 65504.0f);
-                b = fminf(fmaxf(b, -65504.0f), 65504.0f);
-                __half ha = __float2half_rn(a), hb = __float2half_rn(b);
-                if (!p.x_bf16 && (s & 1)) {          // lo part of the f32 split
-                    ha = __float2half_rn(a - __half2float(ha));
-                    hb = __float2half_rn(b - __half2float(hb));
-                }
-                out[j] = static_cast<uint32_t>(__half_as_ushort(ha)) | (static_cast<uint32_t>(__half_as_ushort(hb)) << 16);
-            }
-            *reinterpret_cast<uint4*>(xh + s * p.xpitch + 2 * e) = make_uint4(out[0], out[1], out[2], out[3]);
         }
         if (clipped) atomicOr(p.status, STATUS_X_CLIPPED);
     }
@@ -452,15 +471,14 @@ __global__ void __launch_bounds__(THREADS) gemv_mma_kernel(const MParams p) {
     float* scr1 = scr0 + 64;
     (void)scr0; (void)scr1; (void)sxslot;
 
-    uint32_t it = 0, grp = 0;
+    uint32_t it = 0, grp = 0, st = 0, ph = 0;     // ring slot and the parity of its current use
     bool alive = true;
     for (uint32_t rg = blockIdx.x; rg < p.ngroups; rg += gridDim.x, ++grp) {
         float f[4] = {0.f, 0.f, 0.f, 0.f};
-        for (uint32_t s = 0; s < p.nslices; ++s, ++it) {
-            const uint32_t st = it % p.stages;
+        for (uint32_t s = 0; s < p.nslices; ++s, ++it, st = (st + 1 == p.stages ? 0 : st + 1), ph ^= (st == 0)) {
             // a wait that gives up marks the warp dead; it keeps walking the loops (skipping waits
             // and work) so the named barriers below are still reached by all consumers
-            if (alive && !mbar_wait_bounded(&full[st], (it / p.stages) & 1, p.status)) alive = false;
+            if (alive && !mbar_wait_bounded(&full[st], ph, p.status)) alive = false;
             const uint32_t kbase = s * SLICE_ELEMS;
             const uint32_t nhalf = min(static_cast<uint32_t>(SLICE_ELEMS), p.k - kbase) >> 7;
             // which 128-element piece this warp takes rotates with the stage, so that idle warps
@@ -485,8 +503,9 @@ __global__ void __launch_bounds__(THREADS) gemv_mma_kernel(const MParams p) {
             __syncwarp();
             if (lane == 0) mbar_arrive(&empty[st]);
         }
-        // combine the warps' partial sums in a fixed order; double-buffered so one barrier suffices
-        float* rbuf = red + (grp & 1) * CWARPS * 128;
+        // combine the warps' partial sums in a fixed order
+        float* rbuf = red;
+        if (grp) asm volatile("bar.sync 1, %0;" ::"n"(CT));      // the previous group's readers are done
         *reinterpret_cast<float2*>(rbuf + warp * 128 + g * 8 + 2 * t) = make_float2(f[0], f[1]);
         *reinterpret_cast<float2*>(rbuf + warp * 128 + (g + 8) * 8 + 2 * t) = make_float2(f[2], f[3]);
         asm volatile("bar.sync 1, %0;" ::"n"(CT));
@@ -511,7 +530,7 @@ __global__ void __launch_bounds__(THREADS) gemv_mma_kernel(const MParams p) {
 size_t smem_base_bytes(uint32_t type, uint32_t k, uint32_t nslots) {
     const bool k45 = type == HF2Q_TYPE_Q4_K || type == HF2Q_TYPE_Q5_K;
     const bool leg = type == HF2Q_TYPE_Q4_0 || type == HF2Q_TYPE_Q8_0;
-    const size_t fixed = 128 + (2 * CWARPS * 128 + CWARPS * 16 * 8) * 4;
+    const size_t fixed = 128 + (CWARPS * 128 + CWARPS * 16 * 8) * 4;
     const size_t xbytes = static_cast<size_t>(nslots) * (2 * static_cast<size_t>(k) + 32);
     const size_t sxbytes = leg ? static_cast<size_t>(k / 32) * 8 * 4
                                : static_cast<size_t>(nslots) * (k / 256) * (k45 ? 32 : 64);
@@ -532,11 +551,12 @@ cudaError_t launch_mma_t(MParams p, uint32_t slots, const DeviceInfo& dev, cudaS
     const size_t limit = static_cast<size_t>(dev.max_smem_optin);
     const size_t base = smem_base_bytes(TYPE, p.k, p.nslots);
     if (base + 2 * stage > limit) return cudaErrorInvalidConfiguration;
-    // two CTAs per SM when each can still have a ring of >= 4 stages (up to 6), else one CTA with
-    // as deep a ring as fits (up to 8 stages): bytes in flight per SM are what hides HBM latency
+    // two CTAs per SM (twice the warps to hide latency) when each can still have a ring of >= 3
+    // stages, else one CTA with as deep a ring as fits (up to 8 stages): bytes in flight per SM are
+    // what hides HBM latency
     const size_t half = limit / 2 - 1024;
     uint32_t stages = 0;
-    for (uint32_t s = 6; s >= 4; --s)
+    for (uint32_t s = 4; s >= 3; --s)
         if (base + s * stage <= half) { stages = s; break; }
     if (!stages) {
         stages = MAX_STAGES;

@@ -76,4 +76,11 @@ cudaError_t launch_softmax_topk(const float* logits, uint32_t* ids, float* weigh
                                 uint32_t n_tokens, uint32_t n_experts, uint32_t top_k,
                                 cudaStream_t st);
 
+
+// element-wise glue of the FFN builders (ffn_elementwise.cu)
+cudaError_t launch_silu_mul(const float* gate, const float* up, float* out, uint64_t n, int sm_count, cudaStream_t st);
+cudaError_t launch_moe_combine(const float* y, const float* w, const float* shared, const float* gate_logit, const float* residual,
+                               float* out, uint32_t n_tokens, uint32_t top_k, uint32_t h, cudaStream_t st);
+cudaError_t launch_rowdot(const float* x, const float* v, float* out, uint32_t n_tokens, uint32_t h, cudaStream_t st);
+
 }  // namespace hf2q

@@ -181,6 +181,27 @@ HF2Q_API int32_t hf2q_cuda_moe_softmax_topk(hf2q_ctx* ctx, void* stream, const f
                                             uint32_t* ids, float* weights, uint32_t n_tokens,
                                             uint32_t n_experts, uint32_t top_k);
 
+/* ---- a8: element-wise glue of the FFN builders ---------------------------------------------- */
+
+/* dispatch_silu_mul as used by build_dense_ffn_layer_gpu_q_into (gpu_ffn.rs:1086-1351), semantics
+ * of dense_swiglu_cpu_ref (ffn.rs:91-112): out[i] = silu(gate[i]) * up[i], silu(x) = x / (1 + e^-x). */
+HF2Q_API int32_t hf2q_cuda_silu_mul(hf2q_ctx* ctx, void* stream, const float* gate, const float* up,
+                                    float* out, uint64_t n);
+/* dispatch_moe_weighted_reduce + shared-expert gate + residual add of
+ * build_moe_ffn_layer_gpu_q_into (gpu_ffn.rs:2313-2802), semantics of moe_ffn_cpu_ref
+ * (ffn.rs:179-336): out[t,:] = sum_s weights[t*top_k+s] * y[t*top_k+s,:]
+ *                             + sigmoid(shared_gate_logit[t]) * shared[t,:]   (if shared != NULL;
+ *                               gate 1 if shared_gate_logit == NULL)
+ *                             + residual[t,:]                                 (if residual != NULL). */
+HF2Q_API int32_t hf2q_cuda_moe_combine(hf2q_ctx* ctx, void* stream, const float* y, const float* weights,
+                                       const float* shared, const float* shared_gate_logit,
+                                       const float* residual, float* out, uint32_t n_tokens,
+                                       uint32_t top_k, uint32_t hidden);
+/* The shared expert's gate logit, a [1, hidden] f32 matrix applied per token (ffn.rs:298-304):
+ * out[t] = sum_i v[i] * x[t,i]. */
+HF2Q_API int32_t hf2q_cuda_rowdot(hf2q_ctx* ctx, void* stream, const float* x, const float* v, float* out,
+                                  uint32_t n_tokens, uint32_t hidden);
+
 /* ---- introspection ------------------------------------------------------------------------ */
 
 /* Number of kernels this library has launched through `ctx` since creation (the reference keeps

@@ -68,6 +68,10 @@ def lib() -> C.CDLL:
         L.oracle_qmatmul_id.argtypes = [u32, vp, u64, vp, vp, i64, i64, i64, i64, i64, vp, ci]
         L.oracle_softmax_topk_renorm.argtypes = [vp, i64, i64, i64, vp, vp]
         L.oracle_softmax_topk_renorm.restype = None
+        L.oracle_dense_swiglu.argtypes = [vp, vp, vp, vp, i64, i64, i64, vp, ci]
+        L.oracle_dense_swiglu.restype = None
+        L.oracle_moe_ffn.argtypes = [vp] * 9 + [i64] * 6 + [vp]
+        L.oracle_moe_ffn.restype = None
         L.oracle_mulberry32_uniform.argtypes = [vp, i64, u32]
         L.oracle_mulberry32_uniform.restype = None
         L.oracle_mulberry32_imatrix.argtypes = [vp, i64, u32]
@@ -215,4 +219,30 @@ def mulberry32_uniform(n: int, seed: int) -> np.ndarray:
 def mulberry32_imatrix(n: int, seed: int) -> np.ndarray:
     out = np.empty(n, dtype=np.float32)
     lib().oracle_mulberry32_imatrix(_p(out), n, seed)
+    return out
+
+
+def dense_swiglu(x, gate, up, down, threads: int = 0) -> np.ndarray:
+    """dense_swiglu_cpu_ref (ffn.rs:91-112) on f32 (dequantised) weights."""
+    x, gate, up, down = _f32(x), _f32(gate), _f32(up), _f32(down)
+    seq, h = x.shape
+    m = gate.shape[0]
+    y = np.empty((seq, h), dtype=np.float32)
+    lib().oracle_dense_swiglu(_p(x), _p(gate), _p(up), _p(down), seq, h, m, _p(y), threads or max_threads())
+    return y
+
+
+def moe_ffn(x, router, eg, eu, ed, topk: int, shared=None) -> np.ndarray:
+    """moe_ffn_cpu_ref (ffn.rs:179-336).  eg/eu: [E, m_moe, h]; ed: [E, h, m_moe];
+    shared = (gate_logit[h], gate[m_sh,h], up[m_sh,h], down[h,m_sh]) or None."""
+    x, router, eg, eu, ed = _f32(x), _f32(router), _f32(eg), _f32(eu), _f32(ed)
+    seq, h = x.shape
+    ne, m_moe = eg.shape[0], eg.shape[1]
+    out = np.empty((seq, h), dtype=np.float32)
+    if shared is not None:
+        sl, sg, su, sd = (_f32(a) for a in shared)
+        m_sh = sg.shape[0]
+        lib().oracle_moe_ffn(_p(x), _p(router), _p(eg), _p(eu), _p(ed), _p(sl), _p(sg), _p(su), _p(sd), seq, h, ne, topk, m_moe, m_sh, _p(out))
+    else:
+        lib().oracle_moe_ffn(_p(x), _p(router), _p(eg), _p(eu), _p(ed), None, None, None, None, seq, h, ne, topk, m_moe, 0, _p(out))
     return out

@@ -810,6 +810,84 @@ void oracle_softmax_topk_renorm(const float* logits, int64_t seq_len, int64_t nu
     }
 }
 
+// ffn.rs:24-30
+static inline float silu_ref(float x) { return x / (1.0f + std::exp(-x)); }
+static inline float sigmoid_ref(float x) { return 1.0f / (1.0f + std::exp(-x)); }
+
+// dense_swiglu_cpu_ref (ffn.rs:91-112): y = down @ (silu(gate @ x) * (up @ x)); all f32, weights
+// [out, in] row-major (already dequantised), x [seq, h], y [seq, h].
+void oracle_dense_swiglu(const float* x, const float* gate, const float* up, const float* down, int64_t seq,
+                         int64_t h, int64_t m, float* y, int threads) {
+    std::vector<float> a((size_t)seq * m), b((size_t)seq * m);
+    oracle_matmul_a_by_bt(x, gate, seq, h, m, a.data(), threads);
+    oracle_matmul_a_by_bt(x, up, seq, h, m, b.data(), threads);
+    for (int64_t i = 0; i < seq * m; ++i) a[i] = silu_ref(a[i]) * b[i];
+    oracle_matmul_a_by_bt(a.data(), down, seq, m, h, y, threads);
+}
+
+// moe_ffn_cpu_ref (ffn.rs:179-336).  Router logits, softmax, stable top-k, renormalise, per-expert
+// SwiGLU, weighted sum; plus the sigmoid-gated shared expert when m_sh > 0.
+void oracle_moe_ffn(const float* x, const float* router, const float* eg, const float* eu, const float* ed,
+                    const float* sh_logit, const float* sg, const float* su, const float* sd, int64_t seq, int64_t h,
+                    int64_t ne, int64_t topk, int64_t m_moe, int64_t m_sh, float* out) {
+    std::vector<float> logits((size_t)ne), ex((size_t)ne), probs((size_t)ne), a((size_t)m_moe), b((size_t)m_moe),
+        yv((size_t)h), moe((size_t)h), as((size_t)(m_sh > 0 ? m_sh : 1)), bs((size_t)(m_sh > 0 ? m_sh : 1));
+    std::vector<int64_t> order((size_t)ne);
+    for (int64_t t = 0; t < seq; ++t) {
+        const float* xt = x + t * h;
+        for (int64_t e = 0; e < ne; ++e) {
+            float acc = 0.0f;
+            for (int64_t i = 0; i < h; ++i) acc += router[e * h + i] * xt[i];
+            logits[e] = acc;
+        }
+        float mx = -INFINITY;
+        for (int64_t e = 0; e < ne; ++e) mx = std::fmax(mx, logits[e]);
+        float denom = 0.0f;
+        for (int64_t e = 0; e < ne; ++e) { ex[e] = std::exp(logits[e] - mx); denom += ex[e]; }
+        for (int64_t e = 0; e < ne; ++e) probs[e] = ex[e] / denom;
+        std::iota(order.begin(), order.end(), 0);
+        std::stable_sort(order.begin(), order.end(), [&](int64_t p, int64_t q) { return probs[q] < probs[p]; });
+        float rs = 0.0f;
+        for (int64_t s = 0; s < topk; ++s) rs += probs[order[s]];
+        std::fill(moe.begin(), moe.end(), 0.0f);
+        for (int64_t s = 0; s < topk; ++s) {
+            const int64_t e = order[s];
+            const float w = rs > 1e-20f ? probs[e] / rs : 1.0f / (float)topk;
+            const float* g = eg + e * m_moe * h; const float* u = eu + e * m_moe * h; const float* d = ed + e * h * m_moe;
+            for (int64_t i = 0; i < m_moe; ++i) {
+                float ga = 0.0f, ua = 0.0f;
+                for (int64_t j = 0; j < h; ++j) ga += g[i * h + j] * xt[j];
+                for (int64_t j = 0; j < h; ++j) ua += u[i * h + j] * xt[j];
+                a[i] = silu_ref(ga) * ua;
+            }
+            for (int64_t i = 0; i < h; ++i) {
+                float acc = 0.0f;
+                for (int64_t j = 0; j < m_moe; ++j) acc += d[i * m_moe + j] * a[j];
+                moe[i] += w * acc;
+            }
+        }
+        if (m_sh > 0) {
+            float lg = 0.0f;
+            for (int64_t i = 0; i < h; ++i) lg += sh_logit[i] * xt[i];
+            const float gv = sigmoid_ref(lg);
+            for (int64_t i = 0; i < m_sh; ++i) {
+                float ga = 0.0f, ua = 0.0f;
+                for (int64_t j = 0; j < h; ++j) ga += sg[i * h + j] * xt[j];
+                for (int64_t j = 0; j < h; ++j) ua += su[i * h + j] * xt[j];
+                as[i] = silu_ref(ga) * ua;
+            }
+            for (int64_t i = 0; i < h; ++i) {
+                float acc = 0.0f;
+                for (int64_t j = 0; j < m_sh; ++j) acc += sd[i * m_sh + j] * as[j];
+                out[t * h + i] = moe[i] + gv * acc;
+            }
+        } else {
+            for (int64_t i = 0; i < h; ++i) out[t * h + i] = moe[i];
+        }
+    }
+    (void)b; (void)bs; (void)yv;
+}
+
 // mulberry32 streams of the fixture generator (scripts/ggml_quants_harness/gen.c:24-50).
 static inline uint32_t mulberry32_step(uint32_t* state) {
     *state += 0x6D2B79F5u;

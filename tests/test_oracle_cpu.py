@@ -147,3 +147,26 @@ def test_qmatmul_id_oracle_matches_dense_per_row():
     for r, e in enumerate(ids):
         yd, _, _ = oracle.qmatmul(t, w[e * stride:(e + 1) * stride], x[r // 2:r // 2 + 1], n, k)
         assert np.array_equal(y[r], yd[0])
+
+
+def test_ffn_oracles_match_numpy():
+    rng = np.random.default_rng(0)
+    seq, h, m, E, k = 3, 32, 64, 4, 2
+    x = rng.standard_normal((seq, h)).astype(np.float32)
+    g, u = (rng.standard_normal((m, h)) * 0.1).astype(np.float32), (rng.standard_normal((m, h)) * 0.1).astype(np.float32)
+    d = (rng.standard_normal((h, m)) * 0.1).astype(np.float32)
+    a, b = x @ g.T, x @ u.T
+    want = ((a / (1 + np.exp(-a))) * b) @ d.T
+    assert np.allclose(oracle.dense_swiglu(x, g, u, d), want, rtol=1e-4, atol=1e-5)
+    router = rng.standard_normal((E, h)).astype(np.float32)
+    eg = (rng.standard_normal((E, m, h)) * 0.1).astype(np.float32)
+    eu = (rng.standard_normal((E, m, h)) * 0.1).astype(np.float32)
+    ed = (rng.standard_normal((E, h, m)) * 0.1).astype(np.float32)
+    got = oracle.moe_ffn(x, router, eg, eu, ed, k)
+    ids, w = oracle.softmax_topk_renorm(x @ router.T, k)
+    ref = np.zeros((seq, h), np.float32)
+    for t in range(seq):
+        for s in range(k):
+            e = int(ids[t * k + s])
+            ref[t] += w[t * k + s] * oracle.dense_swiglu(x[t:t + 1], eg[e], eu[e], ed[e])[0]
+    assert np.allclose(got, ref, rtol=1e-4, atol=1e-5)
