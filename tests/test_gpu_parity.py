@@ -338,3 +338,24 @@ def test_invalid_arguments_are_errors_not_fallbacks(gpu_ctx):
         hq.load_quant_weight(gpu_ctx, np.zeros(100, np.uint8), t, n, k)
     # m == 0 and n_tokens == 0 are no-ops, not errors
     assert lib.hf2q_cuda_qmatmul(gpu_ctx._h, None, x.data_ptr(), 0, w.ptr, y.data_ptr(), 0, n, k, t, None, 0) == 0
+
+
+def test_gguf_file_feeds_the_kernels(gpu_ctx, tmp_path):
+    """GGUF file -> reader -> raw-block upload -> product: the loader contract end to end."""
+    from hf2q_b200 import gguf
+    t, n, k = oracle.Q6_K, 64, 2048
+    raw = make_quant_weight(t, n, k, seed=77)
+    wtr = gguf.GgufWriter()
+    wtr.add_kv("general.architecture", gguf.T_STRING, "test")
+    wtr.add_tensor("blk.0.ffn_down.weight", (n, k), t, raw)
+    path = tmp_path / "w.gguf"
+    wtr.write(path)
+    with gguf.GgufFile(path) as g:
+        w = g.load_quant_weight(gpu_ctx, "blk.0.ffn_down.weight")
+        assert (w.rows, w.cols, w.ggml_type) == (n, k, t)
+        xd, xs = _dev_x(make_x(2, k, seed=1), True)
+        y = torch.empty((2, n), device="cuda")
+        hq.quantized_matmul_ggml(gpu_ctx, xd, w, y, w.matmul_params(2))
+        assert rel_l2(y.cpu().numpy(), _ref(t, raw, xs, n, k)) < 2e-5
+        deq = hq.dequantize(gpu_ctx, w).cpu().numpy()
+        assert np.array_equal(deq.view(np.uint32), oracle.dequantize(t, raw).reshape(n, k).view(np.uint32))
