@@ -6,6 +6,7 @@ the "does it build" check.  The library lands next to this file so it travels wi
 from __future__ import annotations
 
 import os
+import shlex
 import subprocess
 import sys
 from pathlib import Path
@@ -48,7 +49,7 @@ def build(force: bool = False, verbose: bool = False) -> Path:
     objs, procs = [], []
     for src in SOURCES:
         obj = objdir / (src + ".o")
-        cmd = [_nvcc(), *NVCC_FLAGS, "-ccbin", "g++", "-c", str(CSRC / src), "-o", str(obj)]
+        cmd = [_nvcc(), *NVCC_FLAGS, *shlex.split(os.environ.get("HF2Q_NVCC_EXTRA", "")), "-ccbin", "g++", "-c", str(CSRC / src), "-o", str(obj)]
         procs.append((src, subprocess.Popen(cmd, env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)))
         objs.append(str(obj))
     log = []

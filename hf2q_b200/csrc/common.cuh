@@ -146,18 +146,25 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
     return ok != 0;
 }
 // Bounded wait: gives up after ~2^31 clock ticks (about a second), records it in *status and
-// returns false so the caller can leave its loop with the context intact.
-__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity,
-                                                  uint32_t* status) {
-    if (mbar_try_wait(bar, parity)) return true;
+// returns false so the caller can leave its loop with the context intact.  The first probe is
+// checked before the clock is read at all.  SLEEP_NS > 0
+// backs off between probes (for warps whose wake-up latency does not matter).
+template <uint32_t SLEEP_NS>
+__device__ __forceinline__ bool mbar_wait_slow(uint64_t* bar, uint32_t parity, uint32_t* status) {
     const long long t0 = clock64();
-    while (!mbar_try_wait(bar, parity)) {
-        if (clock64() - t0 > (1ll << 31)) {
+    for (uint32_t n = 1;; ++n) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if constexpr (SLEEP_NS > 0) __nanosleep(SLEEP_NS);
+        if ((n & 15u) == 0 && clock64() - t0 > (1ll << 31)) {
             if (status) atomicOr(status, STATUS_WAIT_TIMEOUT);
             return false;
         }
     }
-    return true;
+}
+template <uint32_t SLEEP_NS = 0>
+__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity, uint32_t* status) {
+    if (mbar_try_wait(bar, parity)) return true;
+    return mbar_wait_slow<SLEEP_NS>(bar, parity, status);
 }
 // 1-D bulk copy global -> this CTA's shared memory, completion counted in bytes on `bar`.
 // dst, src and bytes must be multiples of 16.  The copy targets this CTA only.

@@ -11,28 +11,36 @@
 // 30 (Q6_K) to 44 (Q4_K) weight elements, but issues only 128 lane-instructions per clock: about
 // 3-4 instructions per element, for all activation rows together.  One FMA per element and row
 // already breaks that budget at 4 rows, so the multiply-accumulate goes through the warp-level
-// m16n8k16 MMA (8 weight rows x 16 elements x 8 activation columns per instruction) and the
+// m16n8k16 MMA (16 weight rows x 16 elements x 8 activation columns per instruction) and the
 // CUDA cores only unpack bits:
 //
-//   * a persistent CTA owns groups of 8 weight rows; a producer warp streams their RAW block
-//     bytes into a shared-memory ring with 1-D bulk copies (cp.async.bulk + mbarrier), 2048
-//     elements per row and stage, so 18/34/210-byte blocks are readable at any 2-byte offset;
-//   * each of 8 consumer warps takes one 256-element chunk of the stage for all 8 rows: lane
-//     (g, t) unpacks row g, four elements at a time, into the A fragment.  The integer codes are
-//     fed as f16 SUBNORMALS (code * 2^-24): a single PRMT turns two packed bytes into an f16x2
-//     operand, with no int->float conversion and no offset to subtract;
+//   * a persistent CTA (one per SM) owns groups of 16 weight rows; a producer warp streams their
+//     RAW block bytes into a shared-memory ring with 1-D bulk copies (cp.async.bulk + mbarrier),
+//     2048 elements per row and stage, so 18/34/210-byte blocks are readable at any 2-byte offset;
+//   * consumer warps work in teams of 8, one team per ring stage, one warp per 256-element block
+//     of the stage for all 16 rows: lane (g, t) unpacks rows g and g+8, four elements at a time,
+//     into the A fragment.  The integer codes are fed as f16 SUBNORMALS (code * 2^-24): a single
+//     PRMT turns two packed bytes into an f16x2 operand, with no int->float conversion and no
+//     offset to subtract;
 //   * scales stay out of the per-element path: Q4_K/Q5_K multiply the codes by the 6-bit
 //     sub-block scale in f16 (code*scale < 2048, exact) and apply d once per block; Q6_K applies
 //     d*scale to each 16-element MMA result; Q4_0/Q8_0 apply d per block.  Offsets (the -dmin*m
 //     of Q4_K/Q5_K, the -32/-8/-128 code biases) become one small extra MMA (or FMA) per block
 //     against per-sub-block sums of x that every CTA computes once;
 //   * activations live in shared memory as f16 (bf16 input: exact in range; f32 input: split
-//     into hi + lo halves on two MMA columns, ~2^-22 relative);
-//   * partial sums of the 8 warps are combined through shared memory in a fixed order: no
-//     atomics, bit-reproducible.
+//     into hi + lo halves on two MMA columns, ~2^-22 relative); rows too long for that are
+//     handled in k-phases (see the kernel);
+//   * a reducer warp combines the consumer warps' partial sums in a fixed order: no atomics,
+//     bit-reproducible.
+//
+// Measured on B200: the per-block unpack + 9 MMAs of a Q6_K half block issue ~205 instructions
+// per warp, and the legacy warp-level MMA holds its pipe for ~32 cycles per instruction and SM
+// sub-partition, which caps this design at ~28 weight elements per clock and SM, i.e. about the
+// HBM rate for Q6_K.
 //
 // Needs 16-byte aligned rows and k a multiple of 256; other shapes take the fp32 kernel in
 // k1_gemv.cu.
+#include <cstdlib>
 #include <mutex>
 
 #include "common.cuh"
@@ -43,9 +51,8 @@ namespace hf2q {
 namespace {
 
 constexpr int ROWS = 16;               // weight rows per stage = rows of one MMA tile
-constexpr int CWARPS = 16;             // consumer warps; each takes 128 elements x 16 rows per stage
-constexpr int CT = CWARPS * 32;
-constexpr int THREADS = CT + 32;
+constexpr int TEAM = 8;                // consumer warps per stage: one per 256-element block
+constexpr int MAX_TEAMS = 3;
 constexpr int SLICE_ELEMS = 2048;
 constexpr int MAX_STAGES = 8;
 
@@ -62,7 +69,12 @@ struct MParams {
     uint32_t top_k, n_experts;
     uint32_t row_bytes, slice_bytes, pitch, nslices, ngroups, stages;
     uint32_t xpitch;       // bytes between activation rows in shared memory
+    uint32_t phase_base, phase_rem;   // k-phases: the first phase_rem have phase_base + 1 slices, the rest phase_base
+    uint32_t last_nblk;        // 256-element blocks in the last slice of a row
     uint32_t* status;
+#ifdef HF2Q_MMA_PROBE
+    uint32_t debug;            // 1: skip the arithmetic, 2: skip the copies (timing probes, wrong results)
+#endif
 };
 
 // m16n8k16, f16 inputs, f32 accumulate.  Lane (g = lane/4, t = lane%4) holds A for rows g (a0, a2)
@@ -278,27 +290,149 @@ __device__ __forceinline__ void half_legacy(const uint8_t* p0, const uint8_t* p1
     }
 }
 
-template <uint32_t TYPE>
-__global__ void __launch_bounds__(THREADS) gemv_mma_kernel(const MParams p) {
+// Builds the f16 activation panel of elements [k0, k0 + klen) and its sub-block sums; called by
+// all CTH consumer threads.  One item = 8 consecutive elements of one column: converted to f16 (f32
+// input: hi or lo part), stored, and summed; lanes holding the same sub-block combine their sums
+// by shuffle.  A warp's 32 items are 256 consecutive elements of one column.
+template <uint32_t TYPE, int CTH, int U>
+__device__ __forceinline__ void build_panel(const void* x, bool x_bf16, uint32_t nslots, uint32_t k, uint32_t xpitch,
+                                         uint32_t* status, uint8_t* xh, uint8_t* sxp, uint32_t sx_slot_bytes,
+                                         uint32_t xrow_idx, uint32_t k0, uint32_t klen) {
+    constexpr bool K45 = TYPE == HF2Q_TYPE_Q4_K || TYPE == HF2Q_TYPE_Q5_K;
+    constexpr bool LEG = TYPE == HF2Q_TYPE_Q4_0 || TYPE == HF2Q_TYPE_Q8_0;
+    constexpr uint32_t SXB = K45 ? 32 : 64;
+    const uint32_t ctid = threadIdx.x, lane = threadIdx.x & 31;
+    constexpr uint32_t SUB = LEG ? 32 : (K45 ? 32 : 16);      // elements per sub-block sum
+    constexpr uint32_t PER = 256 / SUB;
+    const uint32_t k8 = klen >> 3, total = nslots * k8;
+    bool clipped = false;
+    auto finish = [&](uint32_t idx, const float (&v)[8]) {
+        const uint32_t s = idx / k8, e = (idx - s * k8) * 8;
+        uint32_t out[4];
+        float acc = 0.f;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            float a = v[2 * j], b = v[2 * j + 1];
+            clipped |= (fabsf(a) > 65504.0f) | (fabsf(b) > 65504.0f);
+            a = fminf(fmaxf(a, -65504.0f), 65504.0f);
+            b = fminf(fmaxf(b, -65504.0f), 65504.0f);
+            __half ha = __float2half_rn(a), hb = __float2half_rn(b);
+            if (!x_bf16 && (s & 1)) {          // lo part of the f32 split
+                ha = __float2half_rn(a - __half2float(ha));
+                hb = __float2half_rn(b - __half2float(hb));
+            }
+            acc += __half2float(ha) + __half2float(hb);
+            out[j] = static_cast<uint32_t>(__half_as_ushort(ha)) | (static_cast<uint32_t>(__half_as_ushort(hb)) << 16);
+        }
+        *reinterpret_cast<uint4*>(xh + s * xpitch + 2 * e) = make_uint4(out[0], out[1], out[2], out[3]);
+        acc += __shfl_xor_sync(0xffffffffu, acc, 1);
+        if constexpr (SUB == 32) acc += __shfl_xor_sync(0xffffffffu, acc, 2);
+        if ((lane & (SUB / 8 - 1)) == 0) {
+            const uint32_t j = e / SUB;
+            if constexpr (LEG) {
+                reinterpret_cast<float*>(sxp)[j * 8 + s] = acc;
+            } else {
+                const __half hi = __float2half_rn(acc);
+                const __half lo = __float2half_rn(acc - __half2float(hi));
+                __half* dst = reinterpret_cast<__half*>(sxp + s * sx_slot_bytes + (j / PER) * SXB);
+                dst[j % PER] = hi;
+                dst[PER + j % PER] = lo;
+            }
+        }
+    };
+    if (x_bf16) {
+        for (uint32_t base = ctid; base < total; base += U * CTH) {
+            uint4 ra[U];
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const uint32_t idx = base + u * CTH;
+                if (idx < total) {
+                    const uint32_t s = idx / k8, e = (idx - s * k8) * 8;
+                    ra[u] = __ldg(reinterpret_cast<const uint4*>(
+                        static_cast<const __nv_bfloat16*>(x) + (static_cast<size_t>(xrow_idx) + s) * k + k0 + e));
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const uint32_t idx = base + u * CTH;
+                if (idx >= total) break;
+                const uint32_t rr[4] = {ra[u].x, ra[u].y, ra[u].z, ra[u].w};
+                float v[8];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    v[2 * j] = __uint_as_float(rr[j] << 16);
+                    v[2 * j + 1] = __uint_as_float(rr[j] & 0xffff0000u);
+                }
+                finish(idx, v);
+            }
+        }
+    } else {
+        for (uint32_t base = ctid; base < total; base += 4 * CTH) {
+            float4 ra[4], rb[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const uint32_t idx = base + u * CTH;
+                if (idx < total) {
+                    const uint32_t s = idx / k8, e = (idx - s * k8) * 8;
+                    const float4* src = reinterpret_cast<const float4*>(
+                        static_cast<const float*>(x) + (static_cast<size_t>(xrow_idx) + (s >> 1)) * k + k0 + e);
+                    ra[u] = __ldg(src);
+                    rb[u] = __ldg(src + 1);
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const uint32_t idx = base + u * CTH;
+                if (idx >= total) break;
+                const float v[8] = {ra[u].x, ra[u].y, ra[u].z, ra[u].w, rb[u].x, rb[u].y, rb[u].z, rb[u].w};
+                finish(idx, v);
+            }
+        }
+    }
+    if (clipped) atomicOr(status, STATUS_X_CLIPPED);
+}
+
+// Warp roles.  Consumer warps form NTEAMS teams of TEAM = 8; ring stage i belongs to team
+// i % NTEAMS, whose eight warps each take one 256-element block of the stage for all 16 rows.  So
+// NTEAMS stages are being unpacked at any time while the producer warp refills the others.  A
+// reducer warp adds the consumers' partial sums of a finished row group (fixed order: bit-
+// reproducible) and stores them; the hand-over goes through two mbarrier pairs, so consumers never
+// stop at a CTA-wide barrier inside the main loop.
+//
+// Long rows: the f16 activation panel of all columns must sit in shared memory next to the ring.
+// When it does not fit, k is cut into PHASES of whole slices.  The CTA walks all its row groups
+// once per phase with only that phase's activations resident, and the reducer adds the phase's
+// sums to what the previous phase stored (same thread, same address: ordered, no atomics).  Every
+// weight byte is still read exactly once.
+// PHASED = false compiles the single-phase case without the phase loop (fewer live registers in
+// the main loop).
+template <uint32_t TYPE, int NTEAMS, bool PHASED>
+__global__ void __launch_bounds__((NTEAMS * TEAM + 2) * 32, 1) gemv_mma_kernel(const MParams p) {
     extern __shared__ __align__(128) uint8_t smem[];
     constexpr bool K45 = TYPE == HF2Q_TYPE_Q4_K || TYPE == HF2Q_TYPE_Q5_K;
     constexpr bool Q6 = TYPE == HF2Q_TYPE_Q6_K;
     constexpr bool LEG = TYPE == HF2Q_TYPE_Q4_0 || TYPE == HF2Q_TYPE_Q8_0;
     constexpr BlockGeom G = block_geom(TYPE);
+    constexpr int CW = NTEAMS * TEAM;          // consumer warps
+    constexpr int CTH = CW * 32;
     // bytes of x-sum panel per 256 elements and column: K45 8 x (hi,lo) f16, Q6 16 x (hi,lo) f16;
     // Q4_0/Q8_0 keep f32 sums for all 8 columns per 32-element block
     constexpr uint32_t SXB = K45 ? 32 : 64;
 
     uint64_t* full = reinterpret_cast<uint64_t*>(smem);
     uint64_t* empty = full + MAX_STAGES;
-    uint8_t* ring = smem + 128;
-    const uint32_t stage_bytes = ROWS * p.pitch;
-    float* red = reinterpret_cast<float*>(ring + p.stages * stage_bytes);        // [CWARPS][16][8]
-    float* scr = red + CWARPS * 128;                                            // [CWARPS][16][8]
-    uint8_t* xh = reinterpret_cast<uint8_t*>(scr + CWARPS * 16 * 8);             // [nslots][xpitch]
+    uint64_t* red_full = empty + MAX_STAGES;
+    uint64_t* red_empty = red_full + 2;
+    uint8_t* ring = smem + 256;
+    const uint32_t stages = p.stages, pitch = p.pitch, nslices = p.nslices;
+    const uint32_t spp = p.phase_base + (p.phase_rem ? 1u : 0u);              // slices of the longest phase
+    const uint32_t stage_bytes = ROWS * pitch;
+    float* red = reinterpret_cast<float*>(ring + stages * stage_bytes);          // [2][CW][16][8]
+    float* scr = red + 2 * CW * 128;                                            // [CW][16][8]
+    uint8_t* xh = reinterpret_cast<uint8_t*>(scr + CW * 16 * 8);                 // [nslots][xpitch]
     uint8_t* sxp = xh + p.nslots * p.xpitch;
-    const uint32_t nblk_total = p.k >> 8;
-    const uint32_t sx_slot_bytes = nblk_total * SXB;                            // K45 / Q6 panels
+    const uint32_t kphase = min(spp * SLICE_ELEMS, p.k);                        // elements of k resident at a time
+    const uint32_t sx_slot_bytes = (kphase >> 8) * SXB;                         // K45 / Q6 panels
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t slot = blockIdx.y;
@@ -313,156 +447,102 @@ __global__ void __launch_bounds__(THREADS) gemv_mma_kernel(const MParams p) {
         xrow_idx = slot / p.top_k;
     }
     float* yout = p.y + static_cast<size_t>(slot) * p.n;
+    // row groups of this CTA: blockIdx.x, blockIdx.x + gridDim.x, ...
+    const uint32_t gcta = blockIdx.x < p.ngroups ? (p.ngroups - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
 
     if (threadIdx.x == 0) {
-        for (uint32_t s = 0; s < p.stages; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], CWARPS); }
+        for (uint32_t i = 0; i < stages; ++i) { mbar_init(&full[i], 1); mbar_init(&empty[i], TEAM); }
+        // every phase has at least NTEAMS slices unless the whole row has fewer
+        const uint32_t contributing = (nslices < NTEAMS ? nslices : NTEAMS) * TEAM;
+        for (int i = 0; i < 2; ++i) { mbar_init(&red_full[i], contributing); mbar_init(&red_empty[i], 1); }
         mbar_fence_init();
     }
     __syncthreads();
 
-    if (warp == CWARPS) {
+    if (warp == CW) {
         // ---------------- producer warp: lane r copies row r of each stage ----------------
         if (slot_ok) {
             uint32_t it = 0, st = 0, ph = 1;      // ring slot and the parity of its previous use
-            bool alive = true;
-            for (uint32_t rg = blockIdx.x; rg < p.ngroups && alive; rg += gridDim.x) {
-                const uint32_t row0 = rg * ROWS;
-                const uint32_t nrows = min(static_cast<uint32_t>(ROWS), p.n - row0);
-                for (uint32_t s = 0; s < p.nslices; ++s, ++it, st = (st + 1 == p.stages ? 0 : st + 1), ph ^= (st == 0)) {
-                    if (it >= p.stages) {
-                        alive = mbar_wait_bounded(&empty[st], ph, p.status);
-                        alive = __all_sync(0xffffffffu, alive);
-                        if (!alive) break;
+            for (uint32_t s0 = 0, pi = 0; s0 < nslices; ++pi) {
+                const uint32_t s1 = s0 + p.phase_base + (pi < p.phase_rem ? 1u : 0u);
+                for (uint32_t rg = blockIdx.x; rg < p.ngroups; rg += gridDim.x) {
+                    const uint32_t row0 = rg * ROWS;
+                    const uint32_t nrows = min(static_cast<uint32_t>(ROWS), p.n - row0);
+                    for (uint32_t s = s0; s < s1; ++s, ++it, st = (st + 1 == stages ? 0 : st + 1), ph ^= (st == 0)) {
+                        if (it >= stages) {
+                            bool alive = mbar_wait_bounded<20>(&empty[st], ph, p.status);
+                            alive = __all_sync(0xffffffffu, alive);
+                            if (!alive) return;
+                        }
+                        const uint32_t off = s * p.slice_bytes;
+                        const uint32_t bytes = min(p.slice_bytes, p.row_bytes - off);
+#ifdef HF2Q_MMA_PROBE
+                        if (p.debug == 2) { if (lane == 0) mbar_arrive(&full[st]); continue; }
+#endif
+                        if (lane == 0) mbar_arrive_expect_tx(&full[st], nrows * bytes);
+                        __syncwarp();
+                        if (static_cast<uint32_t>(lane) < nrows)
+                            bulk_g2s(ring + st * stage_bytes + lane * pitch,
+                                     wbase + static_cast<uint64_t>(row0 + lane) * p.row_bytes + off, bytes, &full[st]);
                     }
-                    const uint32_t off = s * p.slice_bytes;
-                    const uint32_t bytes = min(p.slice_bytes, p.row_bytes - off);
-                    if (lane == 0) mbar_arrive_expect_tx(&full[st], nrows * bytes);
-                    __syncwarp();
-                    if (static_cast<uint32_t>(lane) < nrows)
-                        bulk_g2s(ring + st * stage_bytes + lane * p.pitch,
-                                 wbase + static_cast<uint64_t>(row0 + lane) * p.row_bytes + off, bytes, &full[st]);
                 }
+                s0 = s1;
             }
         }
         return;
     }
+    if (warp == CW + 1) {
+        // ---------------- reducer warp: lane sums outputs lane, lane+32, lane+64, lane+96 of the
+        // [16 rows][8 columns] tile over the teams that worked on the group, in team order
+        if (!slot_ok) return;
+        const uint32_t nteams = nslices < NTEAMS ? nslices : NTEAMS;
+        uint32_t fl = 0, first = 0;                   // flush counter; team of the group's first stage
+        for (uint32_t s0 = 0, pi = 0; s0 < nslices; ++pi) {
+            const uint32_t nsp = p.phase_base + (pi < p.phase_rem ? 1u : 0u);
+            for (uint32_t rg = blockIdx.x; rg < p.ngroups; rg += gridDim.x, ++fl, first = (first + nsp) % NTEAMS) {
+                const uint32_t rs = fl & 1;
+                if (!mbar_wait_bounded<100>(&red_full[rs], (fl >> 1) & 1, p.status)) return;
+                float v[4] = {0.f, 0.f, 0.f, 0.f};
+                for (uint32_t i = 0, tm = first; i < nteams; ++i, tm = (tm + 1 == NTEAMS ? 0 : tm + 1)) {
+                    const float* rbuf = red + (rs * CW + tm * TEAM) * 128 + lane;
+#pragma unroll
+                    for (int w = 0; w < TEAM; ++w) {
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) v[j] += rbuf[w * 128 + 32 * j];
+                    }
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&red_empty[rs]);
+                const uint32_t c = lane & 7;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const uint32_t row = rg * ROWS + (lane >> 3) + 4 * j;
+                    float out = v[j];
+                    uint32_t tok = c;
+                    if (!p.x_bf16) {                                     // hi + lo column
+                        out += __shfl_xor_sync(0xffffffffu, out, 1);
+                        tok = (c & 1) ? 0xffffffffu : c >> 1;
+                    }
+                    if (row < p.n && tok < p.m) {
+                        float* dst = yout + static_cast<size_t>(tok) * p.n + row;
+                        *dst = s0 ? *dst + out : out;
+                    }
+                }
+            }
+            s0 += nsp;
+        }
+        return;
+    }
 
-    // ---------------- consumers: build the f16 activation panel and its sub-block sums ------------
+    // ---------------- consumers ----------------
     const int ctid = threadIdx.x;
-    {
-        // 8 elements per item; four items per thread and pass so that four independent loads are
-        // in flight before the first conversion
-        const uint32_t k8 = p.k >> 3, total = p.nslots * k8;
-        bool clipped = false;
-        for (uint32_t base = ctid; base < total; base += 4 * CT) {
-            uint4 ra[4], rb[4];
-#pragma unroll
-            for (int u = 0; u < 4; ++u) {
-                const uint32_t idx = base + u * CT;
-                ra[u] = make_uint4(0, 0, 0, 0); rb[u] = ra[u];
-                if (idx < total) {
-                    const uint32_t s = idx / k8, e = (idx - s * k8) * 8;
-                    if (p.x_bf16) {
-                        ra[u] = __ldg(reinterpret_cast<const uint4*>(
-                            static_cast<const __nv_bfloat16*>(p.x) + (static_cast<size_t>(xrow_idx) + s) * p.k + e));
-                    } else {
-                        const float* src = static_cast<const float*>(p.x) + (static_cast<size_t>(xrow_idx) + (s >> 1)) * p.k + e;
-                        ra[u] = __ldg(reinterpret_cast<const uint4*>(src));
-                        rb[u] = __ldg(reinterpret_cast<const uint4*>(src + 4));
-                    }
-                }
-            }
-#pragma unroll
-            for (int u = 0; u < 4; ++u) {
-                const uint32_t idx = base + u * CT;
-                if (idx >= total) continue;
-                const uint32_t s = idx / k8, e = (idx - s * k8) * 8;
-                float v[8];
-                if (p.x_bf16) {
-                    const uint32_t rr[4] = {ra[u].x, ra[u].y, ra[u].z, ra[u].w};
-#pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        v[2 * j] = __uint_as_float(rr[j] << 16);
-                        v[2 * j + 1] = __uint_as_float(rr[j] & 0xffff0000u);
-                    }
-                } else {
-                    v[0] = __uint_as_float(ra[u].x); v[1] = __uint_as_float(ra[u].y); v[2] = __uint_as_float(ra[u].z); v[3] = __uint_as_float(ra[u].w);
-                    v[4] = __uint_as_float(rb[u].x); v[5] = __uint_as_float(rb[u].y); v[6] = __uint_as_float(rb[u].z); v[7] = __uint_as_float(rb[u].w);
-                }
-                uint32_t out[4];
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    float a = v[2 * j], b = v[2 * j + 1];
-                    clipped |= (fabsf(a) > 65504.0f) | (fabsf(b) > 65504.0f);
-                    a = fminf(fmaxf(a, -65504.0f), 65504.0f);
-                    b = fminf(fmaxf(b, -65504.0f), 65504.0f);
-                    __half ha = __float2half_rn(a), hb = __float2half_rn(b);
-                    if (!p.x_bf16 && (s & 1)) {          // lo part of the f32 split
-                        ha = __float2half_rn(a - __half2float(ha));
-                        hb = __float2half_rn(b - __half2float(hb));
-                    }
-                    out[j] = static_cast<uint32_t>(__half_as_ushort(ha)) | (static_cast<uint32_t>(__half_as_ushort(hb)) << 16);
-                }
-                *reinterpret_cast<uint4*>(xh + s * p.xpitch + 2 * e) = make_uint4(out[0], out[1], out[2], out[3]);
-            }
-        }
-        if (clipped) atomicOr(p.status, STATUS_X_CLIPPED);
-    }
-    asm volatile("bar.sync 1, %0;" ::"n"(CT));
-    if constexpr (LEG) {
-        float* sxf = reinterpret_cast<float*>(sxp);
-        const uint32_t nb = p.k >> 5;
-        for (uint32_t idx = ctid; idx < nb * 8; idx += CT) {
-            const uint32_t b = idx >> 3, s = idx & 7;
-            float acc = 0.f;
-            if (s < p.nslots) {
-                const uint4* src = reinterpret_cast<const uint4*>(xh + s * p.xpitch + 64 * b);
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    const uint4 r = src[j];
-                    const uint32_t rr[4] = {r.x, r.y, r.z, r.w};
-#pragma unroll
-                    for (int q = 0; q < 4; ++q) {
-                        const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&rr[q]));
-                        acc += f.x + f.y;
-                    }
-                }
-            }
-            sxf[idx] = acc;
-        }
-    } else {
-        constexpr uint32_t SUB = K45 ? 32 : 16;            // elements per sub-block sum
-        constexpr uint32_t PER = 256 / SUB;                // sums per block: 8 or 16
-        const uint32_t nsub = p.k / SUB;
-        for (uint32_t idx = ctid; idx < p.nslots * nsub; idx += CT) {
-            const uint32_t s = idx / nsub, j = idx - s * nsub;
-            const uint4* src = reinterpret_cast<const uint4*>(xh + s * p.xpitch + 2 * SUB * j);
-            float acc = 0.f;
-#pragma unroll
-            for (uint32_t v = 0; v < SUB / 8; ++v) {
-                const uint4 r = src[v];
-                const uint32_t rr[4] = {r.x, r.y, r.z, r.w};
-#pragma unroll
-                for (int q = 0; q < 4; ++q) {
-                    const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&rr[q]));
-                    acc += f.x + f.y;
-                }
-            }
-            const __half hi = __float2half_rn(acc);
-            const __half lo = __float2half_rn(acc - __half2float(hi));
-            __half* dst = reinterpret_cast<__half*>(sxp + s * sx_slot_bytes + (j / PER) * SXB);
-            dst[j % PER] = hi;
-            dst[PER + j % PER] = lo;
-        }
-    }
-    asm volatile("bar.sync 1, %0;" ::"n"(CT));
     if (!slot_ok) {
-        for (uint32_t r = ctid; r < p.n; r += CT) yout[r] = 0.f;
+        for (uint32_t r = ctid; r < p.n; r += CTH) yout[r] = 0.f;
         return;
     }
 
-    // Lane (g, t): weight row g, MMA column g.  Columns beyond nslots alias column 0: a column of
-    // the product depends only on its own column of B, and those outputs are never stored.
+    // Lane (g, t): weight rows g and g+8, MMA column g.  Columns beyond nslots alias column 0: a
+    // column of the product depends only on its own column of B, and those outputs are never stored.
     const int g = lane >> 2, t = lane & 3;
     const uint32_t col = static_cast<uint32_t>(g) < p.nslots ? g : 0;
     const uint8_t* xrow = xh + col * p.xpitch;
@@ -470,70 +550,100 @@ __global__ void __launch_bounds__(THREADS) gemv_mma_kernel(const MParams p) {
     float* scr0 = scr + (warp * 16 + g) * 8;
     float* scr1 = scr0 + 64;
     (void)scr0; (void)scr1; (void)sxslot;
+    const uint32_t team = static_cast<uint32_t>(warp) / TEAM;
+    const uint8_t* ring_g = ring + g * pitch;                            // this lane's first row in slot 0
+    float* red_w = red + warp * 128 + g * 8 + 2 * t;
+    const uint32_t last_slice = nslices - 1, last_nblk = p.last_nblk;
+#ifdef HF2Q_MMA_PROBE
+    const uint32_t dbg = p.debug;
+#else
+    constexpr uint32_t dbg = 0;
+#endif
+    uint32_t blk = static_cast<uint32_t>(warp) % TEAM;                   // block of the stage this warp takes; rotates
+    uint32_t fl_base = 0;                                                // flushes of earlier phases
 
-    uint32_t it = 0, grp = 0, st = 0, ph = 0;     // ring slot and the parity of its current use
-    bool alive = true;
-    for (uint32_t rg = blockIdx.x; rg < p.ngroups; rg += gridDim.x, ++grp) {
+    for (uint32_t s0 = 0, pi = 0, nsp = 0; s0 < (PHASED ? nslices : 1u); s0 += nsp, ++pi, fl_base += gcta) {
+        nsp = PHASED ? p.phase_base + (pi < p.phase_rem ? 1u : 0u) : nslices;     // slices of this phase
+        if (PHASED && s0) asm volatile("bar.sync 1, %0;" ::"n"(CTH));    // everyone is done with the previous panel
+        const uint32_t k0 = s0 * SLICE_ELEMS;
+        build_panel<TYPE, CTH, (PHASED ? 2 : 8)>(p.x, p.x_bf16 != 0, p.nslots, p.k, p.xpitch, p.status, xh, sxp, sx_slot_bytes, xrow_idx, k0,
+                               min(nsp * SLICE_ELEMS, p.k - k0));
+        asm volatile("bar.sync 1, %0;" ::"n"(CTH));
+
+        // Stages of this phase are numbered it0 .. it0 + gcta * nsp - 1 (group-major); this team
+        // owns those with index = team (mod NTEAMS); stage i sits in ring slot i % stages.
+        const uint32_t it0 = gcta * s0;
+        uint32_t rel = (team + NTEAMS - it0 % NTEAMS) % NTEAMS;          // first own stage, relative to it0
+        uint32_t grp = rel / nsp, s = rel - grp * nsp;
+        uint32_t st = (it0 + rel) % stages, ph = ((it0 + rel) / stages) & 1u;
+        const uint32_t step_s = NTEAMS % nsp, step_g = NTEAMS / nsp;
         float f[4] = {0.f, 0.f, 0.f, 0.f};
-        for (uint32_t s = 0; s < p.nslices; ++s, ++it, st = (st + 1 == p.stages ? 0 : st + 1), ph ^= (st == 0)) {
-            // a wait that gives up marks the warp dead; it keeps walking the loops (skipping waits
-            // and work) so the named barriers below are still reached by all consumers
-            if (alive && !mbar_wait_bounded(&full[st], ph, p.status)) alive = false;
-            const uint32_t kbase = s * SLICE_ELEMS;
-            const uint32_t nhalf = min(static_cast<uint32_t>(SLICE_ELEMS), p.k - kbase) >> 7;
-            // which 128-element piece this warp takes rotates with the stage, so that idle warps
-            // (short slices) and the slower unaligned Q6_K blocks spread evenly over the warps
-            const uint32_t hb = (static_cast<uint32_t>(warp) + it) & (CWARPS - 1);
-            if (alive && hb < nhalf) {
-                const uint8_t* r0 = ring + st * stage_bytes + g * p.pitch;
-                const uint8_t* r1 = r0 + 8 * p.pitch;
-                const uint32_t b = hb >> 1, half = hb & 1;
-                const uint32_t e0 = kbase + 256 * b;
+        while (grp < gcta) {
+            if (!mbar_wait_bounded(&full[st], ph, p.status)) return;
+            // the block a warp takes rotates, so that the slower unaligned (odd) Q6_K blocks and the
+            // idle turns of a short last slice spread evenly over the team
+            blk = (blk + 1) & (TEAM - 1);
+            const uint32_t nblk = s0 + s == last_slice ? last_nblk : static_cast<uint32_t>(TEAM);
+            if (blk < nblk && dbg != 1) {
+                const uint8_t* r0 = ring_g + st * stage_bytes;
+                const uint8_t* r1 = r0 + 8 * pitch;
+                const uint32_t e0 = s * SLICE_ELEMS + 256 * blk;          // element index inside the panel
                 if constexpr (K45) {
-                    half_k45<TYPE == HF2Q_TYPE_Q5_K>(r0 + b * G.bytes, r1 + b * G.bytes, half, e0, xrow,
-                                                     sxslot + (e0 >> 8) * SXB, t, f);
+                    const uint8_t* b0 = r0 + blk * G.bytes;
+                    const uint8_t* b1 = r1 + blk * G.bytes;
+                    const uint8_t* sx = sxslot + (e0 >> 8) * SXB;
+                    half_k45<TYPE == HF2Q_TYPE_Q5_K>(b0, b1, 0, e0, xrow, sx, t, f);
+                    half_k45<TYPE == HF2Q_TYPE_Q5_K>(b0, b1, 1, e0, xrow, sx, t, f);
                 } else if constexpr (Q6) {
-                    if (b & 1) half_q6k<false>(r0 + b * 210, r1 + b * 210, half, e0, xrow, sxslot + (e0 >> 8) * SXB, scr0, scr1, t, f);
-                    else half_q6k<true>(r0 + b * 210, r1 + b * 210, half, e0, xrow, sxslot + (e0 >> 8) * SXB, scr0, scr1, t, f);
+                    const uint8_t* b0 = r0 + blk * 210;
+                    const uint8_t* b1 = r1 + blk * 210;
+                    const uint8_t* sx = sxslot + (e0 >> 8) * SXB;
+                    if (blk & 1) {
+                        half_q6k<false>(b0, b1, 0, e0, xrow, sx, scr0, scr1, t, f);
+                        half_q6k<false>(b0, b1, 1, e0, xrow, sx, scr0, scr1, t, f);
+                    } else {
+                        half_q6k<true>(b0, b1, 0, e0, xrow, sx, scr0, scr1, t, f);
+                        half_q6k<true>(b0, b1, 1, e0, xrow, sx, scr0, scr1, t, f);
+                    }
                 } else {
-                    half_legacy<TYPE == HF2Q_TYPE_Q8_0>(r0 + hb * 4 * G.bytes, r1 + hb * 4 * G.bytes, kbase + 128 * hb, xrow,
-                                                        reinterpret_cast<const float*>(sxp), t, f);
+#pragma unroll
+                    for (uint32_t h = 0; h < 2; ++h)
+                        half_legacy<TYPE == HF2Q_TYPE_Q8_0>(r0 + (2 * blk + h) * 4 * G.bytes, r1 + (2 * blk + h) * 4 * G.bytes,
+                                                            e0 + 128 * h, xrow, reinterpret_cast<const float*>(sxp), t, f);
                 }
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(&empty[st]);
-        }
-        // combine the warps' partial sums in a fixed order
-        float* rbuf = red;
-        if (grp) asm volatile("bar.sync 1, %0;" ::"n"(CT));      // the previous group's readers are done
-        *reinterpret_cast<float2*>(rbuf + warp * 128 + g * 8 + 2 * t) = make_float2(f[0], f[1]);
-        *reinterpret_cast<float2*>(rbuf + warp * 128 + (g + 8) * 8 + 2 * t) = make_float2(f[2], f[3]);
-        asm volatile("bar.sync 1, %0;" ::"n"(CT));
-        if (ctid < 128) {
-            const uint32_t r = ctid >> 3, c = ctid & 7;
-            const uint32_t row = rg * ROWS + r;
-            float v = 0.f;
-            if (p.x_bf16) {
-#pragma unroll
-                for (int w = 0; w < CWARPS; ++w) v += rbuf[w * 128 + r * 8 + c];
-                if (row < p.n && c < p.m) yout[static_cast<size_t>(c) * p.n + row] = v;
-            } else if (c < 4) {
-#pragma unroll
-                for (int w = 0; w < CWARPS; ++w) v += rbuf[w * 128 + r * 8 + 2 * c] + rbuf[w * 128 + r * 8 + 2 * c + 1];
-                if (row < p.n && c < p.m) yout[static_cast<size_t>(c) * p.n + row] = v;
+            st += NTEAMS;
+            if (st >= stages) { st -= stages; ph ^= 1u; }
+            s += step_s;
+            uint32_t dg = step_g;
+            if (s >= nsp) { s -= nsp; ++dg; }
+            if (dg) {
+                // that was this team's last stage of the group: hand the partial sums to the reducer
+                const uint32_t fl = fl_base + grp, rs = fl & 1;
+                if (fl >= 2 && !mbar_wait_bounded(&red_empty[rs], ((fl >> 1) - 1) & 1, p.status)) return;
+                float* rb = red_w + rs * (CW * 128);
+                *reinterpret_cast<float2*>(rb) = make_float2(f[0], f[1]);
+                *reinterpret_cast<float2*>(rb + 64) = make_float2(f[2], f[3]);
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&red_full[rs]);
+                f[0] = f[1] = f[2] = f[3] = 0.f;
+                grp += dg;
             }
         }
     }
 }
 
-// shared memory that does not depend on the ring depth
-size_t smem_base_bytes(uint32_t type, uint32_t k, uint32_t nslots) {
+// shared memory that does not depend on the ring depth; kphase = elements of k resident at a time
+size_t smem_base_bytes(uint32_t type, uint32_t kphase, uint32_t nslots, int teams) {
     const bool k45 = type == HF2Q_TYPE_Q4_K || type == HF2Q_TYPE_Q5_K;
     const bool leg = type == HF2Q_TYPE_Q4_0 || type == HF2Q_TYPE_Q8_0;
-    const size_t fixed = 128 + (CWARPS * 128 + CWARPS * 16 * 8) * 4;
-    const size_t xbytes = static_cast<size_t>(nslots) * (2 * static_cast<size_t>(k) + 32);
-    const size_t sxbytes = leg ? static_cast<size_t>(k / 32) * 8 * 4
-                               : static_cast<size_t>(nslots) * (k / 256) * (k45 ? 32 : 64);
+    const size_t cw = static_cast<size_t>(teams) * TEAM;
+    const size_t fixed = 256 + (2 * cw * 128 + cw * 16 * 8) * 4;
+    const size_t xbytes = static_cast<size_t>(nslots) * (2 * static_cast<size_t>(kphase) + 32);
+    const size_t sxbytes = leg ? static_cast<size_t>(kphase / 32) * 8 * 4
+                               : static_cast<size_t>(nslots) * (kphase / 256) * (k45 ? 32 : 64);
     return fixed + xbytes + sxbytes;
 }
 size_t stage_bytes_of(uint32_t type, uint32_t k) {
@@ -544,32 +654,51 @@ size_t stage_bytes_of(uint32_t type, uint32_t k) {
     return static_cast<size_t>(ROWS) * (slice + 16);
 }
 
-template <uint32_t TYPE>
-cudaError_t launch_mma_t(MParams p, uint32_t slots, const DeviceInfo& dev, cudaStream_t st) {
-    auto kern = gemv_mma_kernel<TYPE>;
-    const size_t stage = static_cast<size_t>(ROWS) * p.pitch;
-    const size_t limit = static_cast<size_t>(dev.max_smem_optin);
-    const size_t base = smem_base_bytes(TYPE, p.k, p.nslots);
-    if (base + 2 * stage > limit) return cudaErrorInvalidConfiguration;
-    // two CTAs per SM (twice the warps to hide latency) when each can still have a ring of >= 3
-    // stages, else one CTA with as deep a ring as fits (up to 8 stages): bytes in flight per SM are
-    // what hides HBM latency
-    const size_t half = limit / 2 - 1024;
-    uint32_t stages = 0;
-    for (uint32_t s = 4; s >= 3; --s)
-        if (base + s * stage <= half) { stages = s; break; }
-    if (!stages) {
-        stages = MAX_STAGES;
-        while (stages > 2 && base + stages * stage > limit) --stages;
-    }
-    p.stages = stages;
-    const size_t smem = base + stages * stage;
+int env_int(const char* name, int dflt) {
+    const char* v = getenv(name);
+    return v && *v ? atoi(v) : dflt;
+}
 
+// How k is cut into phases and how deep the ring is, for `teams` consumer teams.
+struct Plan {
+    uint32_t phase_base = 0, phase_rem = 0, stages = 0;
+    size_t smem = 0;
+};
+// Fewest phases (of nslices / phases slices, the first nslices % phases one longer, none shorter
+// than `teams` unless the row is) whose activation panel leaves room for a ring of teams + 3
+// stages: each team holds one stage while three are in flight.  Failing that, teams + 2, teams + 1.
+Plan make_plan(uint32_t type, uint32_t k, uint32_t nslots, int teams, size_t limit) {
+    const uint32_t nslices = (k + SLICE_ELEMS - 1) / SLICE_ELEMS;
+    const size_t stage = stage_bytes_of(type, k);
+    static const uint32_t min_spare = static_cast<uint32_t>(env_int("HF2Q_CUDA_MMA_MINSPARE", 1));   // tuning aid
+    for (uint32_t spare = 3; spare >= min_spare && spare >= 1; --spare) {
+        for (uint32_t phases = 1; phases <= nslices; ++phases) {
+            const uint32_t base = nslices / phases, rem = nslices % phases;
+            if (phases > 1 && base < static_cast<uint32_t>(teams)) break;
+            const uint32_t longest = base + (rem ? 1 : 0);
+            const uint32_t kphase = longest * SLICE_ELEMS < k ? longest * SLICE_ELEMS : k;
+            const size_t fixed = smem_base_bytes(type, kphase, nslots, teams);
+            if (fixed >= limit) continue;
+            size_t s = (limit - fixed) / stage;
+            if (s > MAX_STAGES) s = MAX_STAGES;
+            if (s >= static_cast<size_t>(teams) + spare) {
+                Plan pl;
+                pl.phase_base = base;
+                pl.phase_rem = rem;
+                pl.stages = static_cast<uint32_t>(s);
+                pl.smem = fixed + s * stage;
+                return pl;
+            }
+        }
+    }
+    return Plan{};
+}
+
+template <uint32_t TYPE, int NTEAMS, bool PHASED>
+cudaError_t launch_mma_tt(MParams p, uint32_t slots, const Plan& pl, const DeviceInfo& dev, cudaStream_t st) {
+    auto kern = gemv_mma_kernel<TYPE, NTEAMS, PHASED>;
     static std::mutex mu;
     static bool attr_set = false;
-    static size_t cached_smem = ~static_cast<size_t>(0);
-    static int cached_per_sm = 1;
-    int per_sm;
     {
         std::lock_guard<std::mutex> lock(mu);
         if (!attr_set) {
@@ -577,21 +706,34 @@ cudaError_t launch_mma_t(MParams p, uint32_t slots, const DeviceInfo& dev, cudaS
             if (e != cudaSuccess) return e;
             attr_set = true;
         }
-        if (cached_smem != smem) {
-            int q = 1;
-            cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&q, kern, THREADS, smem);
-            if (e != cudaSuccess) return e;
-            cached_per_sm = q < 1 ? 1 : q;
-            cached_smem = smem;
-        }
-        per_sm = cached_per_sm;
     }
-    const uint32_t want = static_cast<uint32_t>(dev.sm_count) * per_sm;
-    uint32_t gx = (want + slots - 1) / slots;
+    p.stages = pl.stages;
+    p.phase_base = pl.phase_base;
+    p.phase_rem = pl.phase_rem;
+    const uint32_t longest = pl.phase_base + (pl.phase_rem ? 1 : 0);
+    const uint32_t kphase = longest * SLICE_ELEMS < p.k ? longest * SLICE_ELEMS : p.k;
+    p.xpitch = 2 * kphase + 32;                   // activation rows land 8 banks apart
+    uint32_t gx = (static_cast<uint32_t>(dev.sm_count) + slots - 1) / slots;      // one CTA per SM
     if (gx > p.ngroups) gx = p.ngroups;
     if (gx < 1) gx = 1;
-    kern<<<dim3(gx, slots), THREADS, smem, st>>>(p);
+    kern<<<dim3(gx, slots), (NTEAMS * TEAM + 2) * 32, pl.smem, st>>>(p);
     return cudaGetLastError();
+}
+
+template <uint32_t TYPE>
+cudaError_t launch_mma_t(MParams p, uint32_t slots, const DeviceInfo& dev, cudaStream_t st) {
+    const size_t limit = static_cast<size_t>(dev.max_smem_optin);
+    static const int force_teams = env_int("HF2Q_CUDA_MMA_TEAMS", 2);          // tuning aid
+#ifdef HF2Q_MMA_PROBE
+    p.debug = env_int("HF2Q_CUDA_MMA_DEBUG", 0);
+#endif
+    int teams = force_teams == 3 ? 3 : 2;
+    Plan pl = make_plan(TYPE, p.k, p.nslots, teams, limit);
+    if (!pl.stages && teams == 3) { teams = 2; pl = make_plan(TYPE, p.k, p.nslots, 2, limit); }
+    if (!pl.stages) return cudaErrorInvalidConfiguration;
+    const bool phased = pl.phase_base != p.nslices;
+    if (teams == 3) return phased ? launch_mma_tt<TYPE, 3, true>(p, slots, pl, dev, st) : launch_mma_tt<TYPE, 3, false>(p, slots, pl, dev, st);
+    return phased ? launch_mma_tt<TYPE, 2, true>(p, slots, pl, dev, st) : launch_mma_tt<TYPE, 2, false>(p, slots, pl, dev, st);
 }
 
 }  // namespace
@@ -604,13 +746,11 @@ bool gemv_mma_supported(const GemvArgs& a) {
 }
 
 // Activation rows one launch can take: 8 MMA columns (bf16: one per row, f32: two per row), capped
-// by what fits in shared memory next to a ring of at least 3 stages.
+// by what fits in shared memory next to a ring of at least 4 stages.
 uint32_t gemv_mma_max_rows(uint32_t type, uint32_t k, uint32_t x_dtype, const DeviceInfo& dev) {
     const uint32_t per_row = x_dtype == HF2Q_DT_BF16 ? 1 : 2;
     uint32_t rows = 8 / per_row;
-    while (rows > 0 && smem_base_bytes(type, k, rows * per_row) + 3 * stage_bytes_of(type, k) >
-                           static_cast<size_t>(dev.max_smem_optin))
-        --rows;
+    while (rows > 0 && !make_plan(type, k, rows * per_row, 2, static_cast<size_t>(dev.max_smem_optin)).stages) --rows;
     return rows;
 }
 
@@ -637,7 +777,7 @@ cudaError_t launch_gemv_mma(const GemvArgs& a, const DeviceInfo& dev, cudaStream
     p.pitch = p.slice_bytes + 16;                 // rows land 4 banks apart
     p.nslices = (a.k + SLICE_ELEMS - 1) / SLICE_ELEMS;
     p.ngroups = (a.n + ROWS - 1) / ROWS;
-    p.xpitch = 2 * a.k + 32;                      // activation rows land 8 banks apart
+    p.last_nblk = (a.k - (p.nslices - 1) * SLICE_ELEMS) >> 8;
     p.status = a.status;
     switch (a.type) {
         case HF2Q_TYPE_Q4_0: return launch_mma_t<HF2Q_TYPE_Q4_0>(p, a.slots, dev, st);
