@@ -74,8 +74,22 @@ struct MParams {
     uint32_t* status;
 #ifdef HF2Q_MMA_PROBE
     uint32_t debug;            // 1: skip the arithmetic, 2: skip the copies (timing probes, wrong results)
+    uint32_t launch_id;
 #endif
 };
+
+#ifdef HF2Q_MMA_PROBE
+// timeline probe: [launch parity][CTA][event] global-timer stamps
+__device__ unsigned long long g_probe_ts[2 * 160 * 8];
+__device__ __forceinline__ void probe_stamp(const MParams& p, int ev) {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    if (blockIdx.x < 160 && blockIdx.y == 0) g_probe_ts[((p.launch_id & 1) * 160 + blockIdx.x) * 8 + ev] = t;
+}
+#define PROBE_STAMP(ev) probe_stamp(p, ev)
+#else
+#define PROBE_STAMP(ev)
+#endif
 
 // m16n8k16, f16 inputs, f32 accumulate.  Lane (g = lane/4, t = lane%4) holds A for rows g (a0, a2)
 // and g+8 (a1, a3) at k-columns {2t, 2t+1} (a0, a1) and {2t+8, 2t+9} (a2, a3); B for column g at
@@ -291,9 +305,10 @@ __device__ __forceinline__ void half_legacy(const uint8_t* p0, const uint8_t* p1
 }
 
 // Builds the f16 activation panel of elements [k0, k0 + klen) and its sub-block sums; called by
-// all CTH consumer threads.  One item = 8 consecutive elements of one column: converted to f16 (f32
-// input: hi or lo part), stored, and summed; lanes holding the same sub-block combine their sums
-// by shuffle.  A warp's 32 items are 256 consecutive elements of one column.
+// all CTH consumer threads.  A thread converts 8 consecutive elements (one 16-byte store) of up
+// to U columns per round; lanes holding the same sub-block combine their sums by shuffle (a warp's
+// 32 threads cover 256 consecutive elements).  f32 input yields two columns per activation row:
+// hi = f16(x) and lo = f16(x - hi).  Values beyond the f16 range are clamped and flagged.
 template <uint32_t TYPE, int CTH, int U>
 __device__ __forceinline__ void build_panel(const void* x, bool x_bf16, uint32_t nslots, uint32_t k, uint32_t xpitch,
                                          uint32_t* status, uint8_t* xh, uint8_t* sxp, uint32_t sx_slot_bytes,
@@ -301,34 +316,29 @@ __device__ __forceinline__ void build_panel(const void* x, bool x_bf16, uint32_t
     constexpr bool K45 = TYPE == HF2Q_TYPE_Q4_K || TYPE == HF2Q_TYPE_Q5_K;
     constexpr bool LEG = TYPE == HF2Q_TYPE_Q4_0 || TYPE == HF2Q_TYPE_Q8_0;
     constexpr uint32_t SXB = K45 ? 32 : 64;
-    const uint32_t ctid = threadIdx.x, lane = threadIdx.x & 31;
     constexpr uint32_t SUB = LEG ? 32 : (K45 ? 32 : 16);      // elements per sub-block sum
     constexpr uint32_t PER = 256 / SUB;
-    const uint32_t k8 = klen >> 3, total = nslots * k8;
-    bool clipped = false;
-    auto finish = [&](uint32_t idx, const float (&v)[8]) {
-        const uint32_t s = idx / k8, e = (idx - s * k8) * 8;
-        uint32_t out[4];
-        float acc = 0.f;
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            float a = v[2 * j], b = v[2 * j + 1];
-            clipped |= (fabsf(a) > 65504.0f) | (fabsf(b) > 65504.0f);
-            a = fminf(fmaxf(a, -65504.0f), 65504.0f);
-            b = fminf(fmaxf(b, -65504.0f), 65504.0f);
-            __half ha = __float2half_rn(a), hb = __float2half_rn(b);
-            if (!x_bf16 && (s & 1)) {          // lo part of the f32 split
-                ha = __float2half_rn(a - __half2float(ha));
-                hb = __float2half_rn(b - __half2float(hb));
-            }
-            acc += __half2float(ha) + __half2float(hb);
-            out[j] = static_cast<uint32_t>(__half_as_ushort(ha)) | (static_cast<uint32_t>(__half_as_ushort(hb)) << 16);
-        }
-        *reinterpret_cast<uint4*>(xh + s * xpitch + 2 * e) = make_uint4(out[0], out[1], out[2], out[3]);
+    const uint32_t ctid = threadIdx.x, lane = threadIdx.x & 31;
+    const uint32_t k8 = klen >> 3;
+    uint32_t clipped = 0;
+    const __half2 lim = __half2half2(__ushort_as_half(0x7BFF));          // 65504
+    // f16x2 from two floats, clamped to the finite range; flags a change; adds the values to acc
+    auto pack = [&](float a, float b, float& acc) -> __half2 {
+        const __half2 raw = __floats2half2_rn(a, b);
+        const __half2 h = __hmin2(__hmax2(raw, __hneg2(lim)), lim);
+        clipped |= *reinterpret_cast<const uint32_t*>(&raw) ^ *reinterpret_cast<const uint32_t*>(&h);
+        const float2 f = __half22float2(h);
+        acc += f.x + f.y;
+        return h;
+    };
+    auto store = [&](uint32_t s, uint32_t pos, const __half2 (&h)[4], float acc) {
+        *reinterpret_cast<uint4*>(xh + s * xpitch + 16 * pos) =
+            make_uint4(*reinterpret_cast<const uint32_t*>(&h[0]), *reinterpret_cast<const uint32_t*>(&h[1]),
+                       *reinterpret_cast<const uint32_t*>(&h[2]), *reinterpret_cast<const uint32_t*>(&h[3]));
         acc += __shfl_xor_sync(0xffffffffu, acc, 1);
         if constexpr (SUB == 32) acc += __shfl_xor_sync(0xffffffffu, acc, 2);
         if ((lane & (SUB / 8 - 1)) == 0) {
-            const uint32_t j = e / SUB;
+            const uint32_t j = (8 * pos) / SUB;
             if constexpr (LEG) {
                 reinterpret_cast<float*>(sxp)[j * 8 + s] = acc;
             } else {
@@ -340,52 +350,78 @@ __device__ __forceinline__ void build_panel(const void* x, bool x_bf16, uint32_t
             }
         }
     };
-    if (x_bf16) {
-        for (uint32_t base = ctid; base < total; base += U * CTH) {
-            uint4 ra[U];
+    auto convert_bf16 = [&](const uint4& r, uint32_t s, uint32_t pos) {
+        const uint32_t rr[4] = {r.x, r.y, r.z, r.w};
+        __half2 h[4];
+        float acc = 0.f;
 #pragma unroll
-            for (int u = 0; u < U; ++u) {
-                const uint32_t idx = base + u * CTH;
-                if (idx < total) {
-                    const uint32_t s = idx / k8, e = (idx - s * k8) * 8;
-                    ra[u] = __ldg(reinterpret_cast<const uint4*>(
-                        static_cast<const __nv_bfloat16*>(x) + (static_cast<size_t>(xrow_idx) + s) * k + k0 + e));
+        for (int j = 0; j < 4; ++j)
+            h[j] = pack(__uint_as_float(rr[j] << 16), __uint_as_float(rr[j] & 0xffff0000u), acc);
+        store(s, pos, h, acc);
+    };
+    // k8 is a multiple of 32, so a warp is either wholly inside or wholly outside the loops
+    if (x_bf16 && 2 * nslots <= U) {
+        // few columns: keep U loads in flight by taking U positions of one column per round
+        for (uint32_t s = 0; s < nslots; ++s) {
+            const __nv_bfloat16* src = static_cast<const __nv_bfloat16*>(x) + (static_cast<size_t>(xrow_idx) + s) * k + k0;
+            for (uint32_t pos0 = ctid; pos0 < k8; pos0 += U * CTH) {
+                uint4 ra[U];
+#pragma unroll
+                for (int u = 0; u < U; ++u)
+                    if (pos0 + u * CTH < k8) ra[u] = __ldg(reinterpret_cast<const uint4*>(src + 8 * (pos0 + u * CTH)));
+#pragma unroll
+                for (int u = 0; u < U; ++u) {
+                    if (pos0 + u * CTH >= k8) break;
+                    convert_bf16(ra[u], s, pos0 + u * CTH);
                 }
-            }
-#pragma unroll
-            for (int u = 0; u < U; ++u) {
-                const uint32_t idx = base + u * CTH;
-                if (idx >= total) break;
-                const uint32_t rr[4] = {ra[u].x, ra[u].y, ra[u].z, ra[u].w};
-                float v[8];
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    v[2 * j] = __uint_as_float(rr[j] << 16);
-                    v[2 * j + 1] = __uint_as_float(rr[j] & 0xffff0000u);
-                }
-                finish(idx, v);
             }
         }
-    } else {
-        for (uint32_t base = ctid; base < total; base += 4 * CTH) {
-            float4 ra[4], rb[4];
+    } else
+    for (uint32_t pos = ctid; pos < k8; pos += CTH) {
+        if (x_bf16) {
+            const __nv_bfloat16* src = static_cast<const __nv_bfloat16*>(x) + static_cast<size_t>(xrow_idx) * k + k0 + 8 * pos;
+            for (uint32_t s0 = 0; s0 < nslots; s0 += U) {
+                uint4 ra[U];
 #pragma unroll
-            for (int u = 0; u < 4; ++u) {
-                const uint32_t idx = base + u * CTH;
-                if (idx < total) {
-                    const uint32_t s = idx / k8, e = (idx - s * k8) * 8;
-                    const float4* src = reinterpret_cast<const float4*>(
-                        static_cast<const float*>(x) + (static_cast<size_t>(xrow_idx) + (s >> 1)) * k + k0 + e);
-                    ra[u] = __ldg(src);
-                    rb[u] = __ldg(src + 1);
+                for (int u = 0; u < U; ++u)
+                    if (s0 + u < nslots) ra[u] = __ldg(reinterpret_cast<const uint4*>(src + static_cast<size_t>(s0 + u) * k));
+#pragma unroll
+                for (int u = 0; u < U; ++u) {
+                    if (s0 + u >= nslots) break;
+                    convert_bf16(ra[u], s0 + u, pos);
                 }
             }
+        } else {
+            constexpr int UT = U > 4 ? 4 : (U > 1 ? U / 2 : 1);      // activation rows per round (two float4 each)
+            const float* src = static_cast<const float*>(x) + static_cast<size_t>(xrow_idx) * k + k0 + 8 * pos;
+            const uint32_t ntok = nslots >> 1;
+            for (uint32_t t0 = 0; t0 < ntok; t0 += UT) {
+                float4 ra[UT], rb[UT];
 #pragma unroll
-            for (int u = 0; u < 4; ++u) {
-                const uint32_t idx = base + u * CTH;
-                if (idx >= total) break;
-                const float v[8] = {ra[u].x, ra[u].y, ra[u].z, ra[u].w, rb[u].x, rb[u].y, rb[u].z, rb[u].w};
-                finish(idx, v);
+                for (int u = 0; u < UT; ++u)
+                    if (t0 + u < ntok) {
+                        const float4* q = reinterpret_cast<const float4*>(src + static_cast<size_t>(t0 + u) * k);
+                        ra[u] = __ldg(q);
+                        rb[u] = __ldg(q + 1);
+                    }
+#pragma unroll
+                for (int u = 0; u < UT; ++u) {
+                    if (t0 + u >= ntok) break;
+                    const float v[8] = {ra[u].x, ra[u].y, ra[u].z, ra[u].w, rb[u].x, rb[u].y, rb[u].z, rb[u].w};
+                    __half2 hi[4], lo[4];
+                    float acc_hi = 0.f, acc_lo = 0.f;
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const float a = fminf(fmaxf(v[2 * j], -65504.0f), 65504.0f);
+                        const float b = fminf(fmaxf(v[2 * j + 1], -65504.0f), 65504.0f);
+                        clipped |= static_cast<uint32_t>(a != v[2 * j]) | static_cast<uint32_t>(b != v[2 * j + 1]);
+                        hi[j] = pack(a, b, acc_hi);
+                        const float2 f = __half22float2(hi[j]);
+                        lo[j] = pack(a - f.x, b - f.y, acc_lo);
+                    }
+                    store(2 * (t0 + u), pos, hi, acc_hi);
+                    store(2 * (t0 + u) + 1, pos, lo, acc_lo);
+                }
             }
         }
     }
@@ -440,6 +476,7 @@ __global__ void __launch_bounds__((NTEAMS * TEAM + 2) * 32, 1) gemv_mma_kernel(c
     uint32_t xrow_idx = 0;
     bool slot_ok = true;
     if (p.ids) {
+        asm volatile("griddepcontrol.wait;" ::: "memory");
         const uint32_t e = p.ids[slot];
         slot_ok = e < p.n_experts;
         if (!slot_ok && threadIdx.x == 0) atomicOr(p.status, STATUS_BAD_EXPERT_ID);
@@ -450,17 +487,24 @@ __global__ void __launch_bounds__((NTEAMS * TEAM + 2) * 32, 1) gemv_mma_kernel(c
     // row groups of this CTA: blockIdx.x, blockIdx.x + gridDim.x, ...
     const uint32_t gcta = blockIdx.x < p.ngroups ? (p.ngroups - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
 
-    if (threadIdx.x == 0) {
-        for (uint32_t i = 0; i < stages; ++i) { mbar_init(&full[i], 1); mbar_init(&empty[i], TEAM); }
-        // every phase has at least NTEAMS slices unless the whole row has fewer
-        const uint32_t contributing = (nslices < NTEAMS ? nslices : NTEAMS) * TEAM;
-        for (int i = 0; i < 2; ++i) { mbar_init(&red_full[i], contributing); mbar_init(&red_empty[i], 1); }
-        mbar_fence_init();
-    }
-    __syncthreads();
+    // Programmatic dependent launch: let the next kernel of the stream start its own prologue as soon
+    // as SMs free up, and do not touch anything an earlier kernel may still be writing (activations,
+    // expert ids, outputs) before that kernel has completed.  Weight bytes are immutable, so the
+    // producer of a dense launch starts streaming without waiting.
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
+    // Start-up: the producer warp initialises the ring's barriers itself and issues the first copies
+    // at once; the reducer warp initialises the hand-over barriers; the consumers build the
+    // activation panel.  One CTA-wide barrier then publishes all of that to everyone.
     if (warp == CW) {
         // ---------------- producer warp: lane r copies row r of each stage ----------------
+        if (lane == 0) {
+            PROBE_STAMP(0);
+            for (uint32_t i = 0; i < stages; ++i) { mbar_init(&full[i], 1); mbar_init(&empty[i], TEAM); }
+            mbar_fence_init();
+        }
+        __syncwarp();
+        bool synced = false;
         if (slot_ok) {
             uint32_t it = 0, st = 0, ph = 1;      // ring slot and the parity of its previous use
             for (uint32_t s0 = 0, pi = 0; s0 < nslices; ++pi) {
@@ -469,6 +513,9 @@ __global__ void __launch_bounds__((NTEAMS * TEAM + 2) * 32, 1) gemv_mma_kernel(c
                     const uint32_t row0 = rg * ROWS;
                     const uint32_t nrows = min(static_cast<uint32_t>(ROWS), p.n - row0);
                     for (uint32_t s = s0; s < s1; ++s, ++it, st = (st + 1 == stages ? 0 : st + 1), ph ^= (st == 0)) {
+                        // the copies of the first stage are on their way: meet the other warps (a
+                        // bulk copy can hold its issuing thread while the copy queue is full)
+                        if (it == 1) { __syncthreads(); synced = true; }
                         if (it >= stages) {
                             bool alive = mbar_wait_bounded<20>(&empty[st], ph, p.status);
                             alive = __all_sync(0xffffffffu, alive);
@@ -488,20 +535,28 @@ __global__ void __launch_bounds__((NTEAMS * TEAM + 2) * 32, 1) gemv_mma_kernel(c
                 }
                 s0 = s1;
             }
+            if (lane == 0) PROBE_STAMP(6);
         }
+        if (!synced) __syncthreads();
         return;
     }
     if (warp == CW + 1) {
         // ---------------- reducer warp: lane sums outputs lane, lane+32, lane+64, lane+96 of the
         // [16 rows][8 columns] tile over the teams that worked on the group, in team order
+        const uint32_t nteams = nslices < NTEAMS ? nslices : NTEAMS;      // every phase has at least NTEAMS slices
+        if (lane == 0) {                                                  // unless the whole row has fewer
+            for (int i = 0; i < 2; ++i) { mbar_init(&red_full[i], nteams * TEAM); mbar_init(&red_empty[i], 1); }
+            mbar_fence_init();
+        }
+        __syncthreads();
         if (!slot_ok) return;
-        const uint32_t nteams = nslices < NTEAMS ? nslices : NTEAMS;
+        asm volatile("griddepcontrol.wait;" ::: "memory");                // before the first store to y
         uint32_t fl = 0, first = 0;                   // flush counter; team of the group's first stage
         for (uint32_t s0 = 0, pi = 0; s0 < nslices; ++pi) {
             const uint32_t nsp = p.phase_base + (pi < p.phase_rem ? 1u : 0u);
             for (uint32_t rg = blockIdx.x; rg < p.ngroups; rg += gridDim.x, ++fl, first = (first + nsp) % NTEAMS) {
                 const uint32_t rs = fl & 1;
-                if (!mbar_wait_bounded<100>(&red_full[rs], (fl >> 1) & 1, p.status)) return;
+                if (!mbar_wait_bounded(&red_full[rs], (fl >> 1) & 1, p.status)) return;
                 float v[4] = {0.f, 0.f, 0.f, 0.f};
                 for (uint32_t i = 0, tm = first; i < nteams; ++i, tm = (tm + 1 == NTEAMS ? 0 : tm + 1)) {
                     const float* rbuf = red + (rs * CW + tm * TEAM) * 128 + lane;
@@ -531,12 +586,15 @@ __global__ void __launch_bounds__((NTEAMS * TEAM + 2) * 32, 1) gemv_mma_kernel(c
             }
             s0 += nsp;
         }
+        if (lane == 0) PROBE_STAMP(5);
         return;
     }
 
     // ---------------- consumers ----------------
     const int ctid = threadIdx.x;
+    asm volatile("griddepcontrol.wait;" ::: "memory");                    // before reading x / writing y
     if (!slot_ok) {
+        __syncthreads();
         for (uint32_t r = ctid; r < p.n; r += CTH) yout[r] = 0.f;
         return;
     }
@@ -568,7 +626,9 @@ __global__ void __launch_bounds__((NTEAMS * TEAM + 2) * 32, 1) gemv_mma_kernel(c
         const uint32_t k0 = s0 * SLICE_ELEMS;
         build_panel<TYPE, CTH, (PHASED ? 2 : 8)>(p.x, p.x_bf16 != 0, p.nslots, p.k, p.xpitch, p.status, xh, sxp, sx_slot_bytes, xrow_idx, k0,
                                min(nsp * SLICE_ELEMS, p.k - k0));
-        asm volatile("bar.sync 1, %0;" ::"n"(CTH));
+        if (s0 == 0) __syncthreads();                                    // panel + all barrier initialisations
+        else asm volatile("bar.sync 1, %0;" ::"n"(CTH));
+        if (threadIdx.x == 0 && s0 == 0) PROBE_STAMP(2);
 
         // Stages of this phase are numbered it0 .. it0 + gcta * nsp - 1 (group-major); this team
         // owns those with index = team (mod NTEAMS); stage i sits in ring slot i % stages.
@@ -580,6 +640,9 @@ __global__ void __launch_bounds__((NTEAMS * TEAM + 2) * 32, 1) gemv_mma_kernel(c
         float f[4] = {0.f, 0.f, 0.f, 0.f};
         while (grp < gcta) {
             if (!mbar_wait_bounded(&full[st], ph, p.status)) return;
+#ifdef HF2Q_MMA_PROBE
+            if (threadIdx.x == 0 && s0 == 0 && grp == 0 && s == 0) PROBE_STAMP(3);
+#endif
             // the block a warp takes rotates, so that the slower unaligned (odd) Q6_K blocks and the
             // idle turns of a short last slice spread evenly over the team
             blk = (blk + 1) & (TEAM - 1);
@@ -633,6 +696,7 @@ __global__ void __launch_bounds__((NTEAMS * TEAM + 2) * 32, 1) gemv_mma_kernel(c
             }
         }
     }
+    if (threadIdx.x == 0) PROBE_STAMP(4);
 }
 
 // shared memory that does not depend on the ring depth; kphase = elements of k resident at a time
@@ -716,8 +780,18 @@ cudaError_t launch_mma_tt(MParams p, uint32_t slots, const Plan& pl, const Devic
     uint32_t gx = (static_cast<uint32_t>(dev.sm_count) + slots - 1) / slots;      // one CTA per SM
     if (gx > p.ngroups) gx = p.ngroups;
     if (gx < 1) gx = 1;
-    kern<<<dim3(gx, slots), (NTEAMS * TEAM + 2) * 32, pl.smem, st>>>(p);
-    return cudaGetLastError();
+    static const int pdl = env_int("HF2Q_CUDA_PDL", 1);
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(gx, slots);
+    cfg.blockDim = dim3((NTEAMS * TEAM + 2) * 32);
+    cfg.dynamicSmemBytes = pl.smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kern, p);
 }
 
 template <uint32_t TYPE>
@@ -726,6 +800,8 @@ cudaError_t launch_mma_t(MParams p, uint32_t slots, const DeviceInfo& dev, cudaS
     static const int force_teams = env_int("HF2Q_CUDA_MMA_TEAMS", 2);          // tuning aid
 #ifdef HF2Q_MMA_PROBE
     p.debug = env_int("HF2Q_CUDA_MMA_DEBUG", 0);
+    static uint32_t launch_counter = 0;
+    p.launch_id = launch_counter++;
 #endif
     int teams = force_teams == 3 ? 3 : 2;
     Plan pl = make_plan(TYPE, p.k, p.nslots, teams, limit);
@@ -737,6 +813,12 @@ cudaError_t launch_mma_t(MParams p, uint32_t slots, const DeviceInfo& dev, cudaS
 }
 
 }  // namespace
+
+#ifdef HF2Q_MMA_PROBE
+extern "C" __attribute__((visibility("default"))) int hf2q_probe_read(unsigned long long* host) {
+    return static_cast<int>(cudaMemcpyFromSymbol(host, g_probe_ts, sizeof(g_probe_ts)));
+}
+#endif
 
 bool gemv_mma_supported(const GemvArgs& a) {
     const BlockGeom g = block_geom(a.type);
