@@ -37,6 +37,8 @@ SIGNATURES = {
     "hf2q_cuda_qmatmul_static": (i32, [vp, vp, vp, u32, vp, vp, u32, u32, u32, u32]),
     "hf2q_cuda_qmatmul_static_max_elements": (u64, []),
     "hf2q_cuda_qmatmul_host": (i32, [vp, vp, u32, vp, vp, u32, u32, u32, u32]),
+    "hf2q_cuda_qmatmul_host_async": (i32, [vp, vp, u32, vp, vp, u32, u32, u32, u32]),
+    "hf2q_cuda_host_sync": (i32, [vp]),
     "hf2q_cuda_qmatmul_id": (i32, [vp, vp, vp, u32, vp, vp, vp, u32, u32, u32, u32, u32, u64, u32, vp, u64]),
     "hf2q_cuda_qmatmul_id_scratch_bytes": (i32, [u32, u32, u32, u32, C.POINTER(u64)]),
     "hf2q_cuda_moe_softmax_topk": (i32, [vp, vp, vp, vp, vp, u32, u32, u32]),

@@ -21,8 +21,21 @@ struct hf2q_ctx {
     bool fp32_matvec = false;          // HF2Q_CUDA_F32_MATVEC=1: CUDA-core fp32 mat-vec only
     bool tc_matvec = false;            // HF2Q_CUDA_TC_MATVEC=1: dense mat-vecs on the tcgen05 kernel (slower today)
     // staging for the *_host convenience calls
-    void* stage_x = nullptr;  size_t stage_x_bytes = 0;
-    float* stage_y = nullptr; size_t stage_y_bytes = 0;
+    // A small ring of device staging buffers and two streams: copies on out_stream, kernels on
+    // host_stream.  The copy stream's order is in(0), in(1), out(0), in(2), out(1), ...: the copy-in of
+    // call i+1 and the copy-out of call i-1 run while the kernel of call i does, and because out(i-2)
+    // precedes in(i) on that stream, slot i % HOST_SLOTS is free again when in(i) starts.
+    struct HostSlot {
+        void* x = nullptr;  size_t x_bytes = 0;
+        float* y = nullptr; size_t y_bytes = 0;
+        cudaEvent_t loaded = nullptr, computed = nullptr;
+    };
+    static constexpr int HOST_SLOTS = 4;
+    HostSlot hslot[HOST_SLOTS];
+    uint32_t hnext = 0;
+    cudaStream_t out_stream = nullptr;
+    // copy-out of the latest call, not yet queued
+    HostSlot* pending = nullptr; float* pending_dst = nullptr; size_t pending_bytes = 0;
     void* pin_x = nullptr;    size_t pin_x_bytes = 0;
     float* pin_y = nullptr;   size_t pin_y_bytes = 0;
     void* ws = nullptr;       size_t ws_bytes = 0;
@@ -149,7 +162,8 @@ HF2Q_API int32_t hf2q_cuda_ctx_create(int32_t device, hf2q_ctx** out) {
     c->dev.sm_count = prop.multiProcessorCount;
     c->dev.max_smem_optin = static_cast<int>(prop.sharedMemPerBlockOptin);
     if (cudaMalloc(&c->status, 256) != cudaSuccess || cudaMemset(c->status, 0, 256) != cudaSuccess ||
-        cudaStreamCreateWithFlags(&c->host_stream, cudaStreamNonBlocking) != cudaSuccess) {
+        cudaStreamCreateWithFlags(&c->host_stream, cudaStreamNonBlocking) != cudaSuccess ||
+        cudaStreamCreateWithFlags(&c->out_stream, cudaStreamNonBlocking) != cudaSuccess) {
         if (c->status) cudaFree(c->status);
         delete c;
         return HF2Q_ERR_CUDA;
@@ -169,8 +183,13 @@ HF2Q_API int32_t hf2q_cuda_ctx_destroy(hf2q_ctx* ctx) {
     DeviceGuard g(ctx->device);
     cudaDeviceSynchronize();
     if (ctx->status) cudaFree(ctx->status);
-    if (ctx->stage_x) cudaFree(ctx->stage_x);
-    if (ctx->stage_y) cudaFree(ctx->stage_y);
+    for (auto& hs : ctx->hslot) {
+        if (hs.x) cudaFree(hs.x);
+        if (hs.y) cudaFree(hs.y);
+        if (hs.computed) cudaEventDestroy(hs.computed);
+        if (hs.loaded) cudaEventDestroy(hs.loaded);
+    }
+    if (ctx->out_stream) cudaStreamDestroy(ctx->out_stream);
     if (ctx->ws) cudaFree(ctx->ws);
     if (ctx->pin_x) cudaFreeHost(ctx->pin_x);
     if (ctx->pin_y) cudaFreeHost(ctx->pin_y);
@@ -331,8 +350,19 @@ HF2Q_API int32_t hf2q_cuda_qmatmul_static(hf2q_ctx* ctx, void* stream, const voi
 
 HF2Q_API uint64_t hf2q_cuda_qmatmul_static_max_elements(void) { return gemm_tc_static_scratch_bytes() / 2; }
 
-HF2Q_API int32_t hf2q_cuda_qmatmul_host(hf2q_ctx* ctx, const void* x_host, uint32_t x_dtype, const void* w_dev,
-                                        float* y_host, uint32_t m, uint32_t n, uint32_t k, uint32_t type) {
+namespace {
+// queues the copy-out that the previous host call left pending
+cudaError_t flush_pending(hf2q_ctx* ctx) {
+    if (!ctx->pending) return cudaSuccess;
+    cudaError_t e = cudaStreamWaitEvent(ctx->out_stream, ctx->pending->computed, 0);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(ctx->pending_dst, ctx->pending->y, ctx->pending_bytes, cudaMemcpyDeviceToHost, ctx->out_stream);
+    ctx->pending = nullptr;
+    return e;
+}
+}  // namespace
+
+HF2Q_API int32_t hf2q_cuda_qmatmul_host_async(hf2q_ctx* ctx, const void* x_host, uint32_t x_dtype, const void* w_dev,
+                                              float* y_host, uint32_t m, uint32_t n, uint32_t k, uint32_t type) {
     if (!ctx) return HF2Q_ERR_INVALID_ARGUMENT;
     if (!x_host || !w_dev || !y_host) return fail(ctx, HF2Q_ERR_INVALID_ARGUMENT, "qmatmul_host: null pointer");
     if (x_dtype != HF2Q_DT_F32 && x_dtype != HF2Q_DT_BF16) return fail(ctx, HF2Q_ERR_INVALID_ARGUMENT, "qmatmul_host: x_dtype %u", x_dtype);
@@ -341,20 +371,57 @@ HF2Q_API int32_t hf2q_cuda_qmatmul_host(hf2q_ctx* ctx, const void* x_host, uint3
     if (m == 0) return HF2Q_OK;
     DeviceGuard dg(ctx->device);
     const size_t xb = static_cast<size_t>(m) * k * dtype_size(x_dtype), yb = static_cast<size_t>(m) * n * 4;
-    if ((rc = grow(ctx, &ctx->stage_x, &ctx->stage_x_bytes, xb, false))) return rc;
-    if ((rc = grow(ctx, reinterpret_cast<void**>(&ctx->stage_y), &ctx->stage_y_bytes, yb, false))) return rc;
+    hf2q_ctx::HostSlot& hs = ctx->hslot[ctx->hnext++ % hf2q_ctx::HOST_SLOTS];
     uint64_t wsb = 0;
     hf2q_cuda_qmatmul_workspace_bytes(m, n, k, type, x_dtype, &wsb);
-    if (wsb && (rc = grow(ctx, &ctx->ws, &ctx->ws_bytes, wsb, false))) return rc;
-    cudaStream_t st = ctx->host_stream;
-    cudaError_t e = cudaMemcpyAsync(ctx->stage_x, x_host, xb, cudaMemcpyHostToDevice, st);
-    if (e != cudaSuccess) return cuda_fail(ctx, e, "qmatmul_host: H2D");
-    rc = hf2q_cuda_qmatmul(ctx, st, ctx->stage_x, x_dtype, w_dev, ctx->stage_y, m, n, k, type, ctx->ws, ctx->ws_bytes);
+    cudaError_t e = cudaSuccess;
+    if (hs.x_bytes < xb || hs.y_bytes < yb || ctx->ws_bytes < wsb) {
+        // growing a buffer frees the old one: nothing may still be using it
+        e = flush_pending(ctx);
+        if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->host_stream);
+        if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->out_stream);
+        if (e != cudaSuccess) return cuda_fail(ctx, e, "qmatmul_host: sync before growing staging buffers");
+        if ((rc = grow(ctx, &hs.x, &hs.x_bytes, xb, false))) return rc;
+        if ((rc = grow(ctx, reinterpret_cast<void**>(&hs.y), &hs.y_bytes, yb, false))) return rc;
+        if (wsb && (rc = grow(ctx, &ctx->ws, &ctx->ws_bytes, wsb, false))) return rc;
+    }
+    if (!hs.computed) {
+        e = cudaEventCreateWithFlags(&hs.computed, cudaEventDisableTiming);
+        if (e == cudaSuccess) e = cudaEventCreateWithFlags(&hs.loaded, cudaEventDisableTiming);
+        if (e != cudaSuccess) return cuda_fail(ctx, e, "qmatmul_host: event");
+    }
+    // copy stream: this call's copy-in, then the previous call's copy-out
+    e = cudaMemcpyAsync(hs.x, x_host, xb, cudaMemcpyHostToDevice, ctx->out_stream);
+    if (e == cudaSuccess) e = cudaEventRecord(hs.loaded, ctx->out_stream);
+    if (e == cudaSuccess) e = flush_pending(ctx);
+    if (e != cudaSuccess) return cuda_fail(ctx, e, "qmatmul_host: copies");
+    // kernel stream
+    e = cudaStreamWaitEvent(ctx->host_stream, hs.loaded, 0);
+    if (e != cudaSuccess) return cuda_fail(ctx, e, "qmatmul_host: wait");
+    rc = hf2q_cuda_qmatmul(ctx, ctx->host_stream, hs.x, x_dtype, w_dev, hs.y, m, n, k, type, ctx->ws, ctx->ws_bytes);
     if (rc) return rc;
-    e = cudaMemcpyAsync(y_host, ctx->stage_y, yb, cudaMemcpyDeviceToHost, st);
-    if (e == cudaSuccess) e = cudaStreamSynchronize(st);
-    if (e != cudaSuccess) return cuda_fail(ctx, e, "qmatmul_host: D2H");
+    e = cudaEventRecord(hs.computed, ctx->host_stream);
+    if (e != cudaSuccess) return cuda_fail(ctx, e, "qmatmul_host: record");
+    ctx->pending = &hs;
+    ctx->pending_dst = y_host;
+    ctx->pending_bytes = yb;
     return HF2Q_OK;
+}
+
+HF2Q_API int32_t hf2q_cuda_host_sync(hf2q_ctx* ctx) {
+    if (!ctx) return HF2Q_ERR_INVALID_ARGUMENT;
+    DeviceGuard dg(ctx->device);
+    cudaError_t e = flush_pending(ctx);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->out_stream);      // the last copy-out waited for the last kernel
+    if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->host_stream);
+    if (e != cudaSuccess) return cuda_fail(ctx, e, "host_sync");
+    return HF2Q_OK;
+}
+
+HF2Q_API int32_t hf2q_cuda_qmatmul_host(hf2q_ctx* ctx, const void* x_host, uint32_t x_dtype, const void* w_dev,
+                                        float* y_host, uint32_t m, uint32_t n, uint32_t k, uint32_t type) {
+    const int32_t rc = hf2q_cuda_qmatmul_host_async(ctx, x_host, x_dtype, w_dev, y_host, m, n, k, type);
+    return rc ? rc : hf2q_cuda_host_sync(ctx);
 }
 
 // routed rows above which the grouped tensor-core product is used (the reference's

@@ -145,15 +145,27 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
+// Same probe, but the hardware may park the thread for up to `ns` nanoseconds while the phase is
+// incomplete (it resumes at once when the phase completes): far fewer polling instructions.
+__device__ __forceinline__ bool mbar_try_wait_parked(uint64_t* bar, uint32_t parity, uint32_t ns) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity), "r"(ns)
+        : "memory");
+    return ok != 0;
+}
 // Bounded wait: gives up after ~2^31 clock ticks (about a second), records it in *status and
 // returns false so the caller can leave its loop with the context intact.  The first probe is
-// checked before the clock is read at all.  SLEEP_NS > 0
-// backs off between probes (for warps whose wake-up latency does not matter).
+// checked before the clock is read at all; later probes let the hardware park the thread.
 template <uint32_t SLEEP_NS>
 __device__ __forceinline__ bool mbar_wait_slow(uint64_t* bar, uint32_t parity, uint32_t* status) {
     const long long t0 = clock64();
     for (uint32_t n = 1;; ++n) {
-        if (mbar_try_wait(bar, parity)) return true;
+        if (mbar_try_wait_parked(bar, parity, 2000u)) return true;
         if constexpr (SLEEP_NS > 0) __nanosleep(SLEEP_NS);
         if ((n & 15u) == 0 && clock64() - t0 > (1ll << 31)) {
             if (status) atomicOr(status, STATUS_WAIT_TIMEOUT);

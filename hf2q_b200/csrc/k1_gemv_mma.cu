@@ -42,6 +42,7 @@
 // k1_gemv.cu.
 #include <cstdlib>
 #include <mutex>
+#include <type_traits>
 
 #include "common.cuh"
 #include "kernels.h"
@@ -359,39 +360,39 @@ __device__ __forceinline__ void build_panel(const void* x, bool x_bf16, uint32_t
             h[j] = pack(__uint_as_float(rr[j] << 16), __uint_as_float(rr[j] & 0xffff0000u), acc);
         store(s, pos, h, acc);
     };
-    // k8 is a multiple of 32, so a warp is either wholly inside or wholly outside the loops
-    if (x_bf16 && 2 * nslots <= U) {
-        // few columns: keep U loads in flight by taking U positions of one column per round
-        for (uint32_t s = 0; s < nslots; ++s) {
-            const __nv_bfloat16* src = static_cast<const __nv_bfloat16*>(x) + (static_cast<size_t>(xrow_idx) + s) * k + k0;
-            for (uint32_t pos0 = ctid; pos0 < k8; pos0 += U * CTH) {
-                uint4 ra[U];
+    // k8 is a multiple of 32, so a warp is either wholly inside or wholly outside the loops.
+    // bf16 input: SU columns x PU positions are loaded before any is converted.
+    auto bf16_rounds = [&](auto su_c, auto pu_c) {
+        constexpr int SU = decltype(su_c)::value, PU = decltype(pu_c)::value;
+        const __nv_bfloat16* src = static_cast<const __nv_bfloat16*>(x) + static_cast<size_t>(xrow_idx) * k + k0;
+        for (uint32_t pos0 = ctid; pos0 < k8; pos0 += PU * CTH) {
+            for (uint32_t s0 = 0; s0 < nslots; s0 += SU) {
+                uint4 ra[SU * PU];
 #pragma unroll
-                for (int u = 0; u < U; ++u)
-                    if (pos0 + u * CTH < k8) ra[u] = __ldg(reinterpret_cast<const uint4*>(src + 8 * (pos0 + u * CTH)));
+                for (int a = 0; a < SU; ++a)
 #pragma unroll
-                for (int u = 0; u < U; ++u) {
-                    if (pos0 + u * CTH >= k8) break;
-                    convert_bf16(ra[u], s, pos0 + u * CTH);
-                }
+                    for (int b = 0; b < PU; ++b)
+                        if (s0 + a < nslots && pos0 + b * CTH < k8)
+                            ra[a * PU + b] = __ldg(reinterpret_cast<const uint4*>(src + static_cast<size_t>(s0 + a) * k + 8 * (pos0 + b * CTH)));
+#pragma unroll
+                for (int a = 0; a < SU; ++a)
+#pragma unroll
+                    for (int b = 0; b < PU; ++b)
+                        if (s0 + a < nslots && pos0 + b * CTH < k8) convert_bf16(ra[a * PU + b], s0 + a, pos0 + b * CTH);
             }
+        }
+    };
+    if (x_bf16) {
+        if constexpr (U >= 8) {
+            if (k8 <= CTH) bf16_rounds(std::integral_constant<int, 8>{}, std::integral_constant<int, 1>{});
+            else if (nslots <= 2) bf16_rounds(std::integral_constant<int, 2>{}, std::integral_constant<int, 4>{});
+            else bf16_rounds(std::integral_constant<int, 4>{}, std::integral_constant<int, 2>{});
+        } else {
+            bf16_rounds(std::integral_constant<int, U>{}, std::integral_constant<int, 1>{});
         }
     } else
     for (uint32_t pos = ctid; pos < k8; pos += CTH) {
-        if (x_bf16) {
-            const __nv_bfloat16* src = static_cast<const __nv_bfloat16*>(x) + static_cast<size_t>(xrow_idx) * k + k0 + 8 * pos;
-            for (uint32_t s0 = 0; s0 < nslots; s0 += U) {
-                uint4 ra[U];
-#pragma unroll
-                for (int u = 0; u < U; ++u)
-                    if (s0 + u < nslots) ra[u] = __ldg(reinterpret_cast<const uint4*>(src + static_cast<size_t>(s0 + u) * k));
-#pragma unroll
-                for (int u = 0; u < U; ++u) {
-                    if (s0 + u >= nslots) break;
-                    convert_bf16(ra[u], s0 + u, pos);
-                }
-            }
-        } else {
+        {
             constexpr int UT = U > 4 ? 4 : (U > 1 ? U / 2 : 1);      // activation rows per round (two float4 each)
             const float* src = static_cast<const float*>(x) + static_cast<size_t>(xrow_idx) * k + k0 + 8 * pos;
             const uint32_t ntok = nslots >> 1;
@@ -517,7 +518,7 @@ __global__ void __launch_bounds__((NTEAMS * TEAM + 2) * 32, 1) gemv_mma_kernel(c
                         // bulk copy can hold its issuing thread while the copy queue is full)
                         if (it == 1) { __syncthreads(); synced = true; }
                         if (it >= stages) {
-                            bool alive = mbar_wait_bounded<20>(&empty[st], ph, p.status);
+                            bool alive = mbar_wait_bounded(&empty[st], ph, p.status);
                             alive = __all_sync(0xffffffffu, alive);
                             if (!alive) return;
                         }
@@ -710,12 +711,20 @@ size_t smem_base_bytes(uint32_t type, uint32_t kphase, uint32_t nslots, int team
                                : static_cast<size_t>(nslots) * (kphase / 256) * (k45 ? 32 : 64);
     return fixed + xbytes + sxbytes;
 }
+// Bytes between rows of a stage: the slice plus 0 or 16 bytes of padding such that consecutive
+// rows start 4 banks apart (pitch / 4 = 4 mod 8): lanes (g, t) reading word t of rows g = 0..7 then
+// touch 32 different banks.
+uint32_t row_pitch(uint32_t slice_bytes) {
+    for (uint32_t pad = 0; pad <= 48; pad += 16)
+        if (((slice_bytes + pad) / 4) % 8 == 4) return slice_bytes + pad;
+    return slice_bytes + 16;
+}
 size_t stage_bytes_of(uint32_t type, uint32_t k) {
     const BlockGeom g = block_geom(type);
     uint32_t slice = SLICE_ELEMS / g.elems * g.bytes;
     const uint32_t row = k / g.elems * g.bytes;
     if (slice > row) slice = row;
-    return static_cast<size_t>(ROWS) * (slice + 16);
+    return static_cast<size_t>(ROWS) * row_pitch(slice);
 }
 
 int env_int(const char* name, int dflt) {
@@ -856,7 +865,7 @@ cudaError_t launch_gemv_mma(const GemvArgs& a, const DeviceInfo& dev, cudaStream
     p.row_bytes = a.k / g.elems * g.bytes;
     p.slice_bytes = SLICE_ELEMS / g.elems * g.bytes;
     if (p.slice_bytes > p.row_bytes) p.slice_bytes = p.row_bytes;
-    p.pitch = p.slice_bytes + 16;                 // rows land 4 banks apart
+    p.pitch = row_pitch(p.slice_bytes);
     p.nslices = (a.k + SLICE_ELEMS - 1) / SLICE_ELEMS;
     p.ngroups = (a.n + ROWS - 1) / ROWS;
     p.last_nblk = (a.k - (p.nslices - 1) * SLICE_ELEMS) >> 8;

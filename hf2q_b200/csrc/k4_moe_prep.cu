@@ -7,6 +7,7 @@
 // Here one counting sort produces (a) perm[]: routed-row indices grouped by expert, (b) a table of
 // token tiles (expert, first sorted row, row count) that the grouped GEMM walks with ONE launch,
 // and then the activation rows are gathered into that order as f16.
+#include <cstdlib>
 #include "common.cuh"
 #include "kernels.h"
 
@@ -110,6 +111,8 @@ __global__ void __launch_bounds__(256) moe_gather_kernel(const void* __restrict_
 
 // tokens per tile of the grouped product for `rows` routed rows over `n_experts` experts
 uint32_t moe_token_tile(uint32_t rows, uint32_t n_experts) {
+    static const int forced = [] { const char* v = getenv("HF2Q_CUDA_MOE_NT"); return v && *v ? atoi(v) : 0; }();   // tuning aid
+    if (forced == 32 || forced == 64 || forced == 128 || forced == 256) return static_cast<uint32_t>(forced);
     const uint32_t avg = rows / (n_experts ? n_experts : 1);
     return avg <= 40 ? 32 : avg <= 96 ? 64 : avg <= 192 ? 128 : 256;
 }

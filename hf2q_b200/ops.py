@@ -225,11 +225,18 @@ def quantized_matmul_ggml(ctx: GpuContext, input: torch.Tensor, weight: QuantWei
 
 
 def quantized_matmul_host(ctx: GpuContext, x_host: np.ndarray, weight: QuantWeight, y_host: np.ndarray,
-                          m: int, x_dtype: int = DT_F32) -> None:
-    """Host-buffer form: copies x in, runs, copies y out, waits (hf2q_cuda_qmatmul_host)."""
-    ctx._check(ctx._lib.hf2q_cuda_qmatmul_host(ctx._h, x_host.ctypes.data, x_dtype, weight.ptr,
-                                               y_host.ctypes.data, m, weight.rows, weight.cols,
-                                               weight.ggml_type))
+                          m: int, x_dtype: int = DT_F32, wait: bool = True) -> None:
+    """Host-buffer form: copies x in, runs, copies y out (hf2q_cuda_qmatmul_host).  With
+    ``wait=False`` the call only queues the work (hf2q_cuda_qmatmul_host_async); y_host is valid
+    after ``host_sync(ctx)`` and both arrays must stay alive until then."""
+    fn = ctx._lib.hf2q_cuda_qmatmul_host if wait else ctx._lib.hf2q_cuda_qmatmul_host_async
+    ctx._check(fn(ctx._h, x_host.ctypes.data, x_dtype, weight.ptr, y_host.ctypes.data, m, weight.rows, weight.cols,
+                  weight.ggml_type))
+
+
+def host_sync(ctx: GpuContext) -> None:
+    """Waits for everything queued by ``quantized_matmul_host(..., wait=False)``."""
+    ctx._check(ctx._lib.hf2q_cuda_host_sync(ctx._h))
 
 
 class IdMmScratch:

@@ -152,6 +152,15 @@ HF2Q_API uint64_t hf2q_cuda_qmatmul_static_max_elements(void);
 HF2Q_API int32_t hf2q_cuda_qmatmul_host(hf2q_ctx* ctx, const void* x_host, uint32_t x_dtype,
                                         const void* w_dev, float* y_host, uint32_t m, uint32_t n,
                                         uint32_t k, uint32_t ggml_type);
+/* The same call without the wait: work is queued on the context's own streams (copy-in + kernel
+ * on one, copy-out on another, so the copy-out of one call overlaps the next kernel) and y_host is
+ * valid after hf2q_cuda_host_sync.  x_host and y_host must stay alive until then; pinned memory
+ * keeps the copies asynchronous.  Mirrors the reference's "append to the encoder, commit_and_wait
+ * once" use of its ops (gpu_ffn.rs:1044-1049, 2300-2311). */
+HF2Q_API int32_t hf2q_cuda_qmatmul_host_async(hf2q_ctx* ctx, const void* x_host, uint32_t x_dtype,
+                                        const void* w_dev, float* y_host, uint32_t m, uint32_t n,
+                                        uint32_t k, uint32_t ggml_type);
+HF2Q_API int32_t hf2q_cuda_host_sync(hf2q_ctx* ctx);
 
 /* ---- a6: expert-routed quantized matmul --------------------------------------------------- */
 

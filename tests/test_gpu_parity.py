@@ -197,6 +197,17 @@ def test_host_buffer_call(gpu_ctx):
     y = np.empty((m, n), np.float32)
     hq.ops.quantized_matmul_host(gpu_ctx, x, w, y, m)
     assert rel_l2(y, _ref(t, raw, x, n, k)) < GATE
+    # queued form: more calls than staging slots, different shapes, one wait at the end
+    outs = []
+    for i in range(7):
+        mi = 1 + i % 3
+        xi = make_x(mi, k, seed=20 + i)
+        yi = np.full((mi, n), np.nan, np.float32)
+        hq.ops.quantized_matmul_host(gpu_ctx, xi, w, yi, mi, wait=False)
+        outs.append((xi, yi))
+    hq.ops.host_sync(gpu_ctx)
+    for xi, yi in outs:
+        assert rel_l2(yi, _ref(t, raw, xi, n, k)) < GATE
 
 
 # ---------------------------------------------------------------- K3 routed mat-vec
