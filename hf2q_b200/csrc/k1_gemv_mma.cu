@@ -662,12 +662,13 @@ __global__ void __launch_bounds__((NTEAMS * TEAM + 2) * 32, 1) gemv_mma_kernel(c
                     const uint8_t* b0 = r0 + blk * 210;
                     const uint8_t* b1 = r1 + blk * 210;
                     const uint8_t* sx = sxslot + (e0 >> 8) * SXB;
+                    // (the two halves run as a loop: half the code, which the instruction cache likes)
                     if (blk & 1) {
-                        half_q6k<false>(b0, b1, 0, e0, xrow, sx, scr0, scr1, t, f);
-                        half_q6k<false>(b0, b1, 1, e0, xrow, sx, scr0, scr1, t, f);
+#pragma unroll 1
+                        for (int nh = 0; nh < 2; ++nh) half_q6k<false>(b0, b1, nh, e0, xrow, sx, scr0, scr1, t, f);
                     } else {
-                        half_q6k<true>(b0, b1, 0, e0, xrow, sx, scr0, scr1, t, f);
-                        half_q6k<true>(b0, b1, 1, e0, xrow, sx, scr0, scr1, t, f);
+#pragma unroll 1
+                        for (int nh = 0; nh < 2; ++nh) half_q6k<true>(b0, b1, nh, e0, xrow, sx, scr0, scr1, t, f);
                     }
                 } else {
 #pragma unroll
