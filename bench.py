@@ -15,7 +15,9 @@ weights in L2.  One "step" is one pass over all copies x shapes x token counts.
             of y back to pinned host memory; one hf2q_cuda_host_sync per step waits for all of them
 
 Multi-GPU (torchrun, one rank per GPU): weak scaling.  Each rank holds the shapes above as ITS row
-shard of a matrix G times taller, runs the same local sweep and all-gathers every output over NCCL.
+shard of a matrix G times taller and runs the same sweep; the mat-vec kernel stores its columns into
+every rank's full-width output buffer itself (peer memory over NVLink, arrival counters), so a step
+contains no collective call and is replayed from a CUDA graph like the single-GPU step.
 
 `--impl reference` times the reference's CPU path for the same products (the oracle's port of
 "dequantise to f32, then matmul_a_by_bt") on the host cores, one bounded sample per step.
@@ -290,8 +292,7 @@ def run_secondary(args) -> None:
                 id_sets.append(hq.moe_softmax_topk(ctx, logits, topk)[0])
 
             def layer(ids):
-                hq.quantized_matmul_id_ggml(ctx, x, wg.data_ptr(), ids, g, sc, pg)
-                hq.quantized_matmul_id_ggml(ctx, x, wu.data_ptr(), ids, u, sc, pg)
+                hq.quantized_matmul_id_pair_ggml(ctx, x, wg.data_ptr(), wu.data_ptr(), ids, g, u, sc, pg)   # gate + up
                 hq.quantized_matmul_id_ggml(ctx, act, wd.data_ptr(), ids, d, sc, pd)
 
             def all_sets():
@@ -334,6 +335,8 @@ def main() -> None:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--copies", type=int, default=8, help="distinct device copies of the four matrices")
     ap.add_argument("--e2e-steps", type=int, default=0, help="steps of the host-buffer leg (0 = auto)")
+    ap.add_argument("--no-chain-wait", action="store_true",
+                    help="several GPUs: products do not wait for the previous product's columns (analysis aid)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-graph", action="store_true", help="issue launches eagerly instead of replaying a CUDA graph")
     ap.add_argument("--workload", default="gemv", choices=["gemv", "gemm", "moe"],
@@ -378,9 +381,14 @@ def main() -> None:
     xdev = {key: torch.from_numpy(b.view(np.int16).copy()).to(dev).view(torch.bfloat16).reshape(key[1], key[0])
             for key, b in xbits.items()}
     ydev = {(n, m): torch.empty((m, n), dtype=torch.float32, device=dev) for n, _ in SHAPES for m in TOKENS}
-    ygath = {}
+    # Several GPUs: each rank's shard is rows [rank*n, (rank+1)*n) of a matrix world*n rows tall, and the
+    # kernel itself stores its columns into every rank's full-width output (peer stores + arrival
+    # counters, hf2q_b200.dist.GatherGroup); each product waits for the previous one's columns from
+    # all ranks before it reads its activations, as a decode chain would.
+    gather = None
     if world > 1:
-        ygath = {(n, m): torch.empty((world, m, n), dtype=torch.float32, device=dev) for n, _ in SHAPES for m in TOKENS}
+        from hf2q_b200.dist import GatherGroup
+        gather = GatherGroup(ctx, max(TOKENS), world * max(n for n, _ in SHAPES))
     params = {(n, k, m): hq.GgmlQuantizedMatmulParams(m, n, k, Q6_K) for n, k in SHAPES for m in TOKENS}
 
     launches_per_step = args.copies * len(SHAPES) * len(TOKENS)
@@ -391,9 +399,12 @@ def main() -> None:
         for m in TOKENS:
             for c in range(args.copies):
                 for (n, k), w in zip(SHAPES, weights[c]):
-                    hq.quantized_matmul_ggml(ctx, xdev[(k, m)], w, ydev[(n, m)], params[(n, k, m)])
-                    if world > 1:
-                        dist.all_gather_into_tensor(ygath[(n, m)], ydev[(n, m)])
+                    if gather is None:
+                        hq.quantized_matmul_ggml(ctx, xdev[(k, m)], w, ydev[(n, m)], params[(n, k, m)])
+                    else:
+                        gather.matmul(xdev[(k, m)], w, m, rank * n, wait_previous=not args.no_chain_wait)
+        if gather is not None:
+            gather.wait()           # the step ends when every rank's columns of the last product are here
 
     def barrier():
         if world > 1:
@@ -415,11 +426,11 @@ def main() -> None:
     for _ in range(args.warmup):
         step()
     barrier()
-    # One step's launches are captured into a CUDA graph and replayed (what a decode loop does).
-    # With NCCL all-gathers in the step (several GPUs) the launches are issued eagerly: capturing the
-    # collectives into the graph did not complete on this pool (the run had to be killed).
+    # One step's launches are captured into a CUDA graph and replayed (what a decode loop does); the
+    # multi-GPU step contains no collective call (the all-gather is in the kernels), so it is captured
+    # the same way.
     graph = None
-    if world == 1 and not args.no_graph:
+    if not args.no_graph:
         try:
             g = torch.cuda.CUDAGraph()
             with torch.cuda.graph(g):
@@ -444,7 +455,7 @@ def main() -> None:
     barrier()
     clocks = sampler.stop()
     ms = ev0.elapsed_time(ev1)
-    gpu_launches = (ctx.launch_count - l0) if graph is None else launches_per_step * args.steps
+    gpu_launches = (ctx.launch_count - l0) if graph is None else (launches_per_step + (1 if gather is not None else 0)) * args.steps
     ctx.check_status()
     if world > 1:
         tms = torch.tensor([ms], device=dev)
@@ -546,7 +557,9 @@ def main() -> None:
             "launches_per_step": launches_per_step, "bytes_per_step": bytes_per_step,
             "launch_mode": "CUDA graph replay of one captured step" if graph is not None else "eager launches",
             "parallelism": "single GPU" if world == 1 else
-                           f"row-sharded x{world}, each rank's shard = the listed shapes, NCCL all-gather of every output",
+                           f"row-sharded x{world}, each rank's shard = the listed shapes; the all-gather of every output is "
+                           "in the kernel's epilogue (stores to the peers' buffers over NVLink + arrival counters), each "
+                           "product waits for the previous one's columns from all ranks",
         },
         "gpu_launches": int(gpu_launches),
         "e2e": {"value": round(e2e_val, 1), "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,

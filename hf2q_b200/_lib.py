@@ -39,7 +39,13 @@ SIGNATURES = {
     "hf2q_cuda_qmatmul_host": (i32, [vp, vp, u32, vp, vp, u32, u32, u32, u32]),
     "hf2q_cuda_qmatmul_host_async": (i32, [vp, vp, u32, vp, vp, u32, u32, u32, u32]),
     "hf2q_cuda_host_sync": (i32, [vp]),
+    "hf2q_cuda_ipc_alloc": (i32, [vp, u64, pp, vp]),
+    "hf2q_cuda_ipc_open": (i32, [vp, vp, pp]),
+    "hf2q_cuda_ipc_close": (i32, [vp, vp]),
+    "hf2q_cuda_qmatmul_gather": (i32, [vp, vp, vp, u32, vp, vp, u32, u32, u32, u32]),
+    "hf2q_cuda_gather_wait": (i32, [vp, vp, vp]),
     "hf2q_cuda_qmatmul_id": (i32, [vp, vp, vp, u32, vp, vp, vp, u32, u32, u32, u32, u32, u64, u32, vp, u64]),
+    "hf2q_cuda_qmatmul_id_pair": (i32, [vp, vp, vp, u32, vp, vp, vp, vp, vp, u32, u32, u32, u32, u32, u64, u32, vp, u64]),
     "hf2q_cuda_qmatmul_id_scratch_bytes": (i32, [u32, u32, u32, u32, C.POINTER(u64)]),
     "hf2q_cuda_moe_softmax_topk": (i32, [vp, vp, vp, vp, vp, u32, u32, u32]),
     "hf2q_cuda_silu_mul": (i32, [vp, vp, vp, vp, vp, u64]),

@@ -321,6 +321,86 @@ HF2Q_API int32_t hf2q_cuda_qmatmul(hf2q_ctx* ctx, void* stream, const void* x, u
     return run_matvec(ctx, st, a, m, "qmatmul launch");
 }
 
+// ---- row-sharded mat-vec with the all-gather in its epilogue (several GPUs, one process each) ----
+
+HF2Q_API int32_t hf2q_cuda_ipc_alloc(hf2q_ctx* ctx, uint64_t bytes, void** dev, uint8_t* handle64) {
+    if (!ctx || !dev || !handle64 || bytes == 0) return HF2Q_ERR_INVALID_ARGUMENT;
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
+    DeviceGuard g(ctx->device);
+    void* p = nullptr;
+    cudaError_t e = cudaMalloc(&p, bytes);
+    if (e == cudaSuccess) e = cudaMemset(p, 0, bytes);
+    cudaIpcMemHandle_t h;
+    if (e == cudaSuccess) e = cudaIpcGetMemHandle(&h, p);
+    if (e != cudaSuccess) { if (p) cudaFree(p); return cuda_fail(ctx, e, "ipc_alloc"); }
+    memcpy(handle64, &h, 64);
+    *dev = p;
+    return HF2Q_OK;
+}
+
+HF2Q_API int32_t hf2q_cuda_ipc_open(hf2q_ctx* ctx, const uint8_t* handle64, void** dev) {
+    if (!ctx || !dev || !handle64) return HF2Q_ERR_INVALID_ARGUMENT;
+    DeviceGuard g(ctx->device);
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handle64, 64);
+    void* p = nullptr;
+    const cudaError_t e = cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess);
+    if (e != cudaSuccess) return cuda_fail(ctx, e, "ipc_open (peer access between the two GPUs is required)");
+    *dev = p;
+    return HF2Q_OK;
+}
+
+HF2Q_API int32_t hf2q_cuda_ipc_close(hf2q_ctx* ctx, void* dev) {
+    if (!ctx || !dev) return HF2Q_ERR_INVALID_ARGUMENT;
+    DeviceGuard g(ctx->device);
+    const cudaError_t e = cudaIpcCloseMemHandle(dev);
+    return e == cudaSuccess ? HF2Q_OK : cuda_fail(ctx, e, "ipc_close");
+}
+
+HF2Q_API int32_t hf2q_cuda_qmatmul_gather(hf2q_ctx* ctx, void* stream, const void* x, uint32_t x_dtype, const void* w,
+                                          const hf2q_gather* g, uint32_t m, uint32_t n, uint32_t k, uint32_t type) {
+    if (!ctx) return HF2Q_ERR_INVALID_ARGUMENT;
+    if (!x || !w || !g) return fail(ctx, HF2Q_ERR_INVALID_ARGUMENT, "qmatmul_gather: null pointer");
+    if (x_dtype != HF2Q_DT_F32 && x_dtype != HF2Q_DT_BF16) return fail(ctx, HF2Q_ERR_INVALID_ARGUMENT, "qmatmul_gather: x_dtype %u", x_dtype);
+    int32_t rc = check_matmul_shape(ctx, type, n, k, "qmatmul_gather");
+    if (rc) return rc;
+    if (g->n_ranks < 1 || g->n_ranks > 8 || g->rank >= g->n_ranks || static_cast<uint64_t>(g->col0) + n > g->n_total)
+        return fail(ctx, HF2Q_ERR_INVALID_ARGUMENT, "qmatmul_gather: rank %u of %u, columns [%u, %u) of %u", g->rank, g->n_ranks, g->col0, g->col0 + n, g->n_total);
+    for (uint32_t r = 0; r < g->n_ranks; ++r)
+        if (!g->y_all[r] || !g->flags[r] || reinterpret_cast<uintptr_t>(g->y_all[r]) % 4 || reinterpret_cast<uintptr_t>(g->flags[r]) % 4)
+            return fail(ctx, HF2Q_ERR_INVALID_ARGUMENT, "qmatmul_gather: buffer of rank %u missing or misaligned", r);
+    if (m == 0) return HF2Q_OK;
+    DeviceGuard dg(ctx->device);
+    GemvArgs a{};
+    a.w = w; a.x = x; a.y = static_cast<float*>(g->y_all[g->rank]);
+    a.x_dtype = x_dtype; a.type = type;
+    a.m = m; a.n = n; a.k = k;
+    a.slots = 1; a.top_k = 1; a.n_experts = 0;
+    a.status = ctx->status;
+    // one launch only: every launch bumps the peers' counters once
+    if (m > 8 || ctx->fp32_matvec || !gemv_mma_supported(a) || gemv_mma_max_rows(type, k, x_dtype, ctx->dev) < m)
+        return fail(ctx, HF2Q_ERR_INVALID_ARGUMENT, "qmatmul_gather: needs m <= %u activation rows, 16-byte aligned weight rows and k %% 256 == 0",
+                    gemv_mma_supported(a) ? gemv_mma_max_rows(type, k, x_dtype, ctx->dev) : 8u);
+    GatherArgs ga{};
+    for (uint32_t r = 0; r < g->n_ranks; ++r) { ga.y_all[r] = static_cast<float*>(g->y_all[r]); ga.flags[r] = static_cast<uint32_t*>(g->flags[r]); }
+    ga.n_ranks = g->n_ranks; ga.rank = g->rank; ga.n_total = g->n_total; ga.col0 = g->col0;
+    ga.wait_expected = g->wait_previous;
+    a.gather = &ga;
+    const cudaError_t e = launch_gemv_mma(a, ctx->dev, static_cast<cudaStream_t>(stream));
+    if (e != cudaSuccess) return cuda_fail(ctx, e, "qmatmul_gather launch");
+    ctx->launches += 1;
+    return HF2Q_OK;
+}
+
+HF2Q_API int32_t hf2q_cuda_gather_wait(hf2q_ctx* ctx, void* stream, const void* flag) {
+    if (!ctx || !flag) return HF2Q_ERR_INVALID_ARGUMENT;
+    DeviceGuard dg(ctx->device);
+    const cudaError_t e = launch_gather_wait(static_cast<const uint32_t*>(flag), ctx->status, static_cast<cudaStream_t>(stream));
+    if (e != cudaSuccess) return cuda_fail(ctx, e, "gather_wait launch");
+    ctx->launches += 1;
+    return HF2Q_OK;
+}
+
 HF2Q_API int32_t hf2q_cuda_qmatmul_static(hf2q_ctx* ctx, void* stream, const void* x, uint32_t x_dtype, const void* w,
                                           float* y, uint32_t m, uint32_t n, uint32_t k, uint32_t type) {
     if (!ctx) return HF2Q_ERR_INVALID_ARGUMENT;
@@ -436,51 +516,59 @@ HF2Q_API int32_t hf2q_cuda_qmatmul_id_scratch_bytes(uint32_t n_experts, uint32_t
     return HF2Q_OK;
 }
 
-HF2Q_API int32_t hf2q_cuda_qmatmul_id(hf2q_ctx* ctx, void* stream, const void* x, uint32_t x_dtype,
-                                      const void* w_stacked, const uint32_t* ids, float* y, uint32_t n_tokens,
-                                      uint32_t top_k, uint32_t n, uint32_t k, uint32_t n_experts,
-                                      uint64_t expert_stride, uint32_t type, void* scratch, uint64_t scratch_bytes) {
-    if (!ctx) return HF2Q_ERR_INVALID_ARGUMENT;
-    if (!x || !w_stacked || !ids || !y) return fail(ctx, HF2Q_ERR_INVALID_ARGUMENT, "qmatmul_id: null pointer");
-    if (x_dtype != HF2Q_DT_F32 && x_dtype != HF2Q_DT_BF16) return fail(ctx, HF2Q_ERR_INVALID_ARGUMENT, "qmatmul_id: x_dtype %u", x_dtype);
-    int32_t rc = check_matmul_shape(ctx, type, n, k, "qmatmul_id");
+namespace {
+// mul_mat_id for one stacked expert tensor (w_b == nullptr) or for two of the same geometry that
+// share x and ids (the gate and up projections of an MoE layer).
+int32_t run_mul_mat_id(hf2q_ctx* ctx, void* stream, const void* x, uint32_t x_dtype, const void* w_a, const void* w_b,
+                       const uint32_t* ids, float* y_a, float* y_b, uint32_t n_tokens, uint32_t top_k, uint32_t n, uint32_t k,
+                       uint32_t n_experts, uint64_t expert_stride, uint32_t type, void* scratch, uint64_t scratch_bytes,
+                       const char* who) {
+    if (!x || !w_a || !ids || !y_a || (w_b && !y_b)) return fail(ctx, HF2Q_ERR_INVALID_ARGUMENT, "%s: null pointer", who);
+    if (x_dtype != HF2Q_DT_F32 && x_dtype != HF2Q_DT_BF16) return fail(ctx, HF2Q_ERR_INVALID_ARGUMENT, "%s: x_dtype %u", who, x_dtype);
+    int32_t rc = check_matmul_shape(ctx, type, n, k, who);
     if (rc) return rc;
-    if (top_k == 0 || n_experts == 0) return fail(ctx, HF2Q_ERR_INVALID_ARGUMENT, "qmatmul_id: top_k=%u n_experts=%u must be non-zero", top_k, n_experts);
+    if (top_k == 0 || n_experts == 0) return fail(ctx, HF2Q_ERR_INVALID_ARGUMENT, "%s: top_k=%u n_experts=%u must be non-zero", who, top_k, n_experts);
     uint64_t min_stride = 0;
     hf2q_cuda_expert_stride(type, n, k, &min_stride);
-    if (expert_stride < min_stride) return fail(ctx, HF2Q_ERR_INVALID_ARGUMENT, "qmatmul_id: expert_stride %llu < one [n,k] matrix (%llu bytes)", (unsigned long long)expert_stride, (unsigned long long)min_stride);
-    if (expert_stride % 2 || reinterpret_cast<uintptr_t>(w_stacked) % 2) return fail(ctx, HF2Q_ERR_INVALID_ARGUMENT, "qmatmul_id: weights must be 2-byte aligned");
+    if (expert_stride < min_stride) return fail(ctx, HF2Q_ERR_INVALID_ARGUMENT, "%s: expert_stride %llu < one [n,k] matrix (%llu bytes)", who, (unsigned long long)expert_stride, (unsigned long long)min_stride);
+    if (expert_stride % 2 || reinterpret_cast<uintptr_t>(w_a) % 2 || reinterpret_cast<uintptr_t>(w_b) % 2)
+        return fail(ctx, HF2Q_ERR_INVALID_ARGUMENT, "%s: weights must be 2-byte aligned", who);
     if (n_tokens == 0) return HF2Q_OK;
     const uint64_t rows = static_cast<uint64_t>(n_tokens) * top_k;
     DeviceGuard dg(ctx->device);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     if (rows > MM_ID_ROUTING_THRESHOLD && rows / 32 + n_experts <= 65535 && !ctx->fp32_matvec &&
-        gemm_tc_grouped_supported(type, w_stacked, expert_stride, n_experts, k) && reinterpret_cast<uintptr_t>(x) % 16 == 0) {
-        // many rows: sort by expert on the device, gather activations, ONE grouped tensor-core launch
+        gemm_tc_grouped_supported(type, w_a, expert_stride, n_experts, k) &&
+        (!w_b || gemm_tc_grouped_supported(type, w_b, expert_stride, n_experts, k)) && reinterpret_cast<uintptr_t>(x) % 16 == 0) {
+        // many rows: sort by expert on the device and gather activations ONCE, then one grouped
+        // tensor-core launch per expert tensor
         const MoeScratch lay = moe_scratch_layout(n_experts, static_cast<uint32_t>(rows), k);
         if (!scratch || scratch_bytes < lay.total)
-            return fail(ctx, HF2Q_ERR_WORKSPACE, "qmatmul_id: %llu routed rows need %llu bytes of scratch (got %llu)",
+            return fail(ctx, HF2Q_ERR_WORKSPACE, "%s: %llu routed rows need %llu bytes of scratch (got %llu)", who,
                         (unsigned long long)rows, (unsigned long long)lay.total, (unsigned long long)scratch_bytes);
-        if (reinterpret_cast<uintptr_t>(scratch) % 256) return fail(ctx, HF2Q_ERR_INVALID_ARGUMENT, "qmatmul_id: scratch must be 256-byte aligned");
+        if (reinterpret_cast<uintptr_t>(scratch) % 256) return fail(ctx, HF2Q_ERR_INVALID_ARGUMENT, "%s: scratch must be 256-byte aligned", who);
         const uint32_t nt = moe_token_tile(static_cast<uint32_t>(rows), n_experts);
-        cudaError_t e = launch_moe_prep(ids, static_cast<uint32_t>(rows), n_experts, top_k, nt, x, x_dtype, k, y, n, scratch, lay,
+        cudaError_t e = launch_moe_prep(ids, static_cast<uint32_t>(rows), n_experts, top_k, nt, x, x_dtype, k, y_a, y_b, n, scratch, lay,
                                         ctx->status, ctx->dev.sm_count, st);
         if (e == cudaSuccess)
-            e = launch_gemm_tc_grouped(type, w_stacked, expert_stride, n_experts, static_cast<uint32_t>(rows), y, n, k, nt, scratch, lay,
+            e = launch_gemm_tc_grouped(type, w_a, expert_stride, n_experts, static_cast<uint32_t>(rows), y_a, n, k, nt, scratch, lay,
                                        ctx->status, st);
-        if (e != cudaSuccess) return cuda_fail(ctx, e, "qmatmul_id (grouped tensor-core) launch");
-        ctx->launches += 3;
+        if (e == cudaSuccess && w_b)
+            e = launch_gemm_tc_grouped(type, w_b, expert_stride, n_experts, static_cast<uint32_t>(rows), y_b, n, k, nt, scratch, lay,
+                                       ctx->status, st);
+        if (e != cudaSuccess) return cuda_fail(ctx, e, who);
+        ctx->launches += w_b ? 4 : 3;
         return HF2Q_OK;
     }
-    // per-row mat-vec, at most 32768 routed rows per launch (grid.y limit is 65535)
-    if (top_k > 32768) return fail(ctx, HF2Q_ERR_INVALID_ARGUMENT, "qmatmul_id: top_k=%u exceeds 32768", top_k);
-    const uint64_t chunk = 32768 / top_k * top_k;
+    // per-row mat-vec, at most 32768 routed rows per launch (grid.y limit is 65535); a pair shares the launch
+    if (top_k > 16384) return fail(ctx, HF2Q_ERR_INVALID_ARGUMENT, "%s: top_k=%u exceeds 16384", who, top_k);
+    const uint64_t chunk = (w_b ? 16384 : 32768) / top_k * top_k;
     for (uint64_t r0 = 0; r0 < rows; ) {
         const uint64_t cnt = rows - r0 < chunk ? rows - r0 : chunk;
         GemvArgs a{};
-        a.w = w_stacked;
+        a.w = w_a;
         a.x = static_cast<const uint8_t*>(x) + (r0 / top_k) * k * dtype_size(x_dtype);
-        a.y = y + r0 * n;
+        a.y = y_a + r0 * n;
         a.ids = ids + r0;
         a.expert_stride = expert_stride;
         a.x_dtype = x_dtype;
@@ -492,15 +580,43 @@ HF2Q_API int32_t hf2q_cuda_qmatmul_id(hf2q_ctx* ctx, void* stream, const void* x
         a.status = ctx->status;
         cudaError_t e;
         int nl = 1;
-        if (!ctx->fp32_matvec && gemv_mma_supported(a) && gemv_mma_max_rows(type, k, x_dtype, ctx->dev) > 0)
+        if (!ctx->fp32_matvec && gemv_mma_supported(a) && gemv_mma_max_rows(type, k, x_dtype, ctx->dev) > 0) {
+            if (w_b) { a.w2 = w_b; a.y2 = y_b + r0 * n; }
             e = launch_gemv_mma(a, ctx->dev, st);
-        else
+        } else {
             e = launch_gemv(a, ctx->dev, st, &nl);
-        if (e != cudaSuccess) return cuda_fail(ctx, e, "qmatmul_id launch");
+            if (e == cudaSuccess && w_b) {
+                int nl2 = 1;
+                a.w = w_b; a.y = y_b + r0 * n;
+                e = launch_gemv(a, ctx->dev, st, &nl2);
+                nl += nl2;
+            }
+        }
+        if (e != cudaSuccess) return cuda_fail(ctx, e, who);
         ctx->launches += nl;
         r0 += cnt;
     }
     return HF2Q_OK;
+}
+}  // namespace
+
+HF2Q_API int32_t hf2q_cuda_qmatmul_id(hf2q_ctx* ctx, void* stream, const void* x, uint32_t x_dtype,
+                                      const void* w_stacked, const uint32_t* ids, float* y, uint32_t n_tokens,
+                                      uint32_t top_k, uint32_t n, uint32_t k, uint32_t n_experts,
+                                      uint64_t expert_stride, uint32_t type, void* scratch, uint64_t scratch_bytes) {
+    if (!ctx) return HF2Q_ERR_INVALID_ARGUMENT;
+    return run_mul_mat_id(ctx, stream, x, x_dtype, w_stacked, nullptr, ids, y, nullptr, n_tokens, top_k, n, k, n_experts,
+                          expert_stride, type, scratch, scratch_bytes, "qmatmul_id");
+}
+
+HF2Q_API int32_t hf2q_cuda_qmatmul_id_pair(hf2q_ctx* ctx, void* stream, const void* x, uint32_t x_dtype,
+                                           const void* w_a, const void* w_b, const uint32_t* ids, float* y_a, float* y_b,
+                                           uint32_t n_tokens, uint32_t top_k, uint32_t n, uint32_t k, uint32_t n_experts,
+                                           uint64_t expert_stride, uint32_t type, void* scratch, uint64_t scratch_bytes) {
+    if (!ctx) return HF2Q_ERR_INVALID_ARGUMENT;
+    if (!w_b || !y_b) return fail(ctx, HF2Q_ERR_INVALID_ARGUMENT, "qmatmul_id_pair: null pointer");
+    return run_mul_mat_id(ctx, stream, x, x_dtype, w_a, w_b, ids, y_a, y_b, n_tokens, top_k, n, k, n_experts, expert_stride, type,
+                          scratch, scratch_bytes, "qmatmul_id_pair");
 }
 
 HF2Q_API int32_t hf2q_cuda_moe_softmax_topk(hf2q_ctx* ctx, void* stream, const float* logits, uint32_t* ids,

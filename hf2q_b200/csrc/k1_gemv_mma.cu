@@ -59,8 +59,11 @@ constexpr int MAX_STAGES = 8;
 
 struct MParams {
     const uint8_t* w;
+    const uint8_t* w2;     // second expert tensor of a routed pair (or nullptr): slots >= pair_slots use it and y2
     const void* x;
     float* y;
+    float* y2;
+    uint32_t pair_slots;
     const uint32_t* ids;
     uint64_t expert_stride;
     uint32_t x_bf16;
@@ -72,6 +75,11 @@ struct MParams {
     uint32_t xpitch;       // bytes between activation rows in shared memory
     uint32_t phase_base, phase_rem;   // k-phases: the first phase_rem have phase_base + 1 slices, the rest phase_base
     uint32_t last_nblk;        // 256-element blocks in the last slice of a row
+    uint32_t sub_groups;       // short rows (<= 4 blocks): a stage holds this many 16-row groups, one warp per (group, block)
+    // fused all-gather (row-sharded weights over several GPUs); g_nranks == 0: plain store to y
+    float* g_y[8];
+    uint32_t* g_flag[8];
+    uint32_t g_nranks, g_rank, g_ntotal, g_col0, g_wait;
     uint32_t* status;
 #ifdef HF2Q_MMA_PROBE
     uint32_t debug;            // 1: skip the arithmetic, 2: skip the copies (timing probes, wrong results)
@@ -373,7 +381,7 @@ __device__ __forceinline__ void build_panel(const void* x, bool x_bf16, uint32_t
 #pragma unroll
                     for (int b = 0; b < PU; ++b)
                         if (s0 + a < nslots && pos0 + b * CTH < k8)
-                            ra[a * PU + b] = __ldg(reinterpret_cast<const uint4*>(src + static_cast<size_t>(s0 + a) * k + 8 * (pos0 + b * CTH)));
+                            ra[a * PU + b] = __ldcg(reinterpret_cast<const uint4*>(src + static_cast<size_t>(s0 + a) * k + 8 * (pos0 + b * CTH)));
 #pragma unroll
                 for (int a = 0; a < SU; ++a)
 #pragma unroll
@@ -402,8 +410,8 @@ __device__ __forceinline__ void build_panel(const void* x, bool x_bf16, uint32_t
                 for (int u = 0; u < UT; ++u)
                     if (t0 + u < ntok) {
                         const float4* q = reinterpret_cast<const float4*>(src + static_cast<size_t>(t0 + u) * k);
-                        ra[u] = __ldg(q);
-                        rb[u] = __ldg(q + 1);
+                        ra[u] = __ldcg(q);
+                        rb[u] = __ldcg(q + 1);
                     }
 #pragma unroll
                 for (int u = 0; u < UT; ++u) {
@@ -463,7 +471,8 @@ __global__ void __launch_bounds__((NTEAMS * TEAM + 2) * 32, 1) gemv_mma_kernel(c
     uint8_t* ring = smem + 256;
     const uint32_t stages = p.stages, pitch = p.pitch, nslices = p.nslices;
     const uint32_t spp = p.phase_base + (p.phase_rem ? 1u : 0u);              // slices of the longest phase
-    const uint32_t stage_bytes = ROWS * pitch;
+    const uint32_t nsub = p.sub_groups, stage_rows = ROWS * nsub;       // nsub > 1 only when a row is one short slice
+    const uint32_t stage_bytes = stage_rows * pitch;
     float* red = reinterpret_cast<float*>(ring + stages * stage_bytes);          // [2][CW][16][8]
     float* scr = red + 2 * CW * 128;                                            // [CW][16][8]
     uint8_t* xh = reinterpret_cast<uint8_t*>(scr + CW * 16 * 8);                 // [nslots][xpitch]
@@ -472,8 +481,10 @@ __global__ void __launch_bounds__((NTEAMS * TEAM + 2) * 32, 1) gemv_mma_kernel(c
     const uint32_t sx_slot_bytes = (kphase >> 8) * SXB;                         // K45 / Q6 panels
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const uint32_t slot = blockIdx.y;
+    uint32_t slot = blockIdx.y;
     const uint8_t* wbase = p.w;
+    float* ybase = p.y;
+    if (p.w2 && slot >= p.pair_slots) { slot -= p.pair_slots; wbase = p.w2; ybase = p.y2; }
     uint32_t xrow_idx = 0;
     bool slot_ok = true;
     if (p.ids) {
@@ -484,7 +495,7 @@ __global__ void __launch_bounds__((NTEAMS * TEAM + 2) * 32, 1) gemv_mma_kernel(c
         wbase += static_cast<uint64_t>(slot_ok ? e : 0) * p.expert_stride;
         xrow_idx = slot / p.top_k;
     }
-    float* yout = p.y + static_cast<size_t>(slot) * p.n;
+    float* yout = ybase + static_cast<size_t>(slot) * p.n;
     // row groups of this CTA: blockIdx.x, blockIdx.x + gridDim.x, ...
     const uint32_t gcta = blockIdx.x < p.ngroups ? (p.ngroups - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
 
@@ -511,8 +522,8 @@ __global__ void __launch_bounds__((NTEAMS * TEAM + 2) * 32, 1) gemv_mma_kernel(c
             for (uint32_t s0 = 0, pi = 0; s0 < nslices; ++pi) {
                 const uint32_t s1 = s0 + p.phase_base + (pi < p.phase_rem ? 1u : 0u);
                 for (uint32_t rg = blockIdx.x; rg < p.ngroups; rg += gridDim.x) {
-                    const uint32_t row0 = rg * ROWS;
-                    const uint32_t nrows = min(static_cast<uint32_t>(ROWS), p.n - row0);
+                    const uint32_t row0 = rg * stage_rows;
+                    const uint32_t nrows = min(stage_rows, p.n - row0);
                     for (uint32_t s = s0; s < s1; ++s, ++it, st = (st + 1 == stages ? 0 : st + 1), ph ^= (st == 0)) {
                         // the copies of the first stage are on their way: meet the other warps (a
                         // bulk copy can hold its issuing thread while the copy queue is full)
@@ -529,9 +540,9 @@ __global__ void __launch_bounds__((NTEAMS * TEAM + 2) * 32, 1) gemv_mma_kernel(c
 #endif
                         if (lane == 0) mbar_arrive_expect_tx(&full[st], nrows * bytes);
                         __syncwarp();
-                        if (static_cast<uint32_t>(lane) < nrows)
-                            bulk_g2s(ring + st * stage_bytes + lane * pitch,
-                                     wbase + static_cast<uint64_t>(row0 + lane) * p.row_bytes + off, bytes, &full[st]);
+                        for (uint32_t rr = lane; rr < nrows; rr += 32)
+                            bulk_g2s(ring + st * stage_bytes + rr * pitch,
+                                     wbase + static_cast<uint64_t>(row0 + rr) * p.row_bytes + off, bytes, &full[st]);
                     }
                 }
                 s0 = s1;
@@ -558,36 +569,67 @@ __global__ void __launch_bounds__((NTEAMS * TEAM + 2) * 32, 1) gemv_mma_kernel(c
             for (uint32_t rg = blockIdx.x; rg < p.ngroups; rg += gridDim.x, ++fl, first = (first + nsp) % NTEAMS) {
                 const uint32_t rs = fl & 1;
                 if (!mbar_wait_bounded(&red_full[rs], (fl >> 1) & 1, p.status)) return;
-                float v[4] = {0.f, 0.f, 0.f, 0.f};
-                for (uint32_t i = 0, tm = first; i < nteams; ++i, tm = (tm + 1 == NTEAMS ? 0 : tm + 1)) {
-                    const float* rbuf = red + (rs * CW + tm * TEAM) * 128 + lane;
+                // partial sums sit at [team][block of the stage]; a sub-group's blocks are adjacent
+                const uint32_t nb = nsub > 1 ? p.last_nblk : static_cast<uint32_t>(TEAM);
+                for (uint32_t sg = 0; sg < nsub; ++sg) {
+                    float v[4] = {0.f, 0.f, 0.f, 0.f};
+                    for (uint32_t i = 0, tm = first; i < nteams; ++i, tm = (tm + 1 == NTEAMS ? 0 : tm + 1)) {
+                        const float* rbuf = red + (rs * CW + tm * TEAM + sg * nb) * 128 + lane;
+                        for (uint32_t w = 0; w < nb; ++w) {
 #pragma unroll
-                    for (int w = 0; w < TEAM; ++w) {
-#pragma unroll
-                        for (int j = 0; j < 4; ++j) v[j] += rbuf[w * 128 + 32 * j];
+                            for (int j = 0; j < 4; ++j) v[j] += rbuf[w * 128 + 32 * j];
+                        }
                     }
-                }
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&red_empty[rs]);
-                const uint32_t c = lane & 7;
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    const uint32_t row = rg * ROWS + (lane >> 3) + 4 * j;
-                    float out = v[j];
-                    uint32_t tok = c;
-                    if (!p.x_bf16) {                                     // hi + lo column
-                        out += __shfl_xor_sync(0xffffffffu, out, 1);
-                        tok = (c & 1) ? 0xffffffffu : c >> 1;
+                    if (sg + 1 == nsub) {
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(&red_empty[rs]);
                     }
-                    if (row < p.n && tok < p.m) {
-                        float* dst = yout + static_cast<size_t>(tok) * p.n + row;
-                        *dst = s0 ? *dst + out : out;
+                    const uint32_t c = lane & 7;
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const uint32_t row = rg * stage_rows + sg * ROWS + (lane >> 3) + 4 * j;
+                        float out = v[j];
+                        uint32_t tok = c;
+                        if (!p.x_bf16) {                                     // hi + lo column
+                            out += __shfl_xor_sync(0xffffffffu, out, 1);
+                            tok = (c & 1) ? 0xffffffffu : c >> 1;
+                        }
+                        if (row < p.n && tok < p.m) {
+                            if (p.g_nranks == 0) {
+                                float* dst = yout + static_cast<size_t>(tok) * p.n + row;
+                                *dst = s0 ? *dst + out : out;
+                            } else {
+                                // the own buffer accumulates the phases; the last phase's total goes to every rank
+                                const size_t off = static_cast<size_t>(tok) * p.g_ntotal + p.g_col0 + row;
+                                float* own = p.g_y[p.g_rank] + off;
+                                const float total = s0 ? *own + out : out;
+                                *own = total;
+                                if (s0 + nsp == nslices)
+                                    for (uint32_t r = 0; r < p.g_nranks; ++r)
+                                        if (r != p.g_rank) p.g_y[r][off] = total;
+                            }
+                        }
                     }
                 }
             }
             s0 += nsp;
         }
         if (lane == 0) PROBE_STAMP(5);
+        if (p.g_nranks > 1) {
+            // Tell the other ranks that this CTA's part of the columns has landed: one system-scope
+            // fence after the warp's stores (the warp barrier makes it cover all lanes' stores), then
+            // one fire-and-forget add per peer.  CTA 0 also records how many arrivals this launch adds
+            // to the own counter (every rank launches the same grid).
+            __syncwarp();
+            if (lane == 0) {
+                const uint32_t ctas = gridDim.x * gridDim.y;
+                if (blockIdx.x == 0 && blockIdx.y == 0) atomicAdd(p.g_flag[p.g_rank] + 1, ctas * (p.g_nranks - 1));
+                __threadfence_system();
+                for (uint32_t r = 0; r < p.g_nranks; ++r)
+                    if (r != p.g_rank)
+                        asm volatile("red.relaxed.sys.global.add.u32 [%0], 1;" ::"l"(p.g_flag[r]) : "memory");
+            }
+        }
         return;
     }
 
@@ -611,7 +653,7 @@ __global__ void __launch_bounds__((NTEAMS * TEAM + 2) * 32, 1) gemv_mma_kernel(c
     (void)scr0; (void)scr1; (void)sxslot;
     const uint32_t team = static_cast<uint32_t>(warp) / TEAM;
     const uint8_t* ring_g = ring + g * pitch;                            // this lane's first row in slot 0
-    float* red_w = red + warp * 128 + g * 8 + 2 * t;
+    float* red_t = red + team * (TEAM * 128) + g * 8 + 2 * t;              // + block * 128: this team's partial sums
     const uint32_t last_slice = nslices - 1, last_nblk = p.last_nblk;
 #ifdef HF2Q_MMA_PROBE
     const uint32_t dbg = p.debug;
@@ -625,6 +667,26 @@ __global__ void __launch_bounds__((NTEAMS * TEAM + 2) * 32, 1) gemv_mma_kernel(c
         nsp = PHASED ? p.phase_base + (pi < p.phase_rem ? 1u : 0u) : nslices;     // slices of this phase
         if (PHASED && s0) asm volatile("bar.sync 1, %0;" ::"n"(CTH));    // everyone is done with the previous panel
         const uint32_t k0 = s0 * SLICE_ELEMS;
+        if (s0 == 0 && p.g_wait) {
+            // the activations are another product's gathered output: wait until every rank's part of
+            // it has arrived here (bounded; the peers' kernels run on other GPUs)
+            if (ctid == 0) {
+                // word 0 counts arrivals from the peers' CTAs, word 1 the arrivals that the products
+                // finished HERE stand for (all ranks issue the same launches): everything has arrived once
+                // word 0 has caught up.  The acquire load orders the reads of x after it.
+                const uint32_t* flag = p.g_flag[p.g_rank];
+                const uint32_t want = *reinterpret_cast<const volatile uint32_t*>(flag + 1);
+                const long long t0 = clock64();
+                for (;;) {
+                    uint32_t got;
+                    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(got) : "l"(flag) : "memory");
+                    if (static_cast<int32_t>(got - want) >= 0) break;
+                    if (clock64() - t0 > (1ll << 31)) { atomicOr(p.status, STATUS_WAIT_TIMEOUT); break; }
+                    __nanosleep(50);
+                }
+            }
+            asm volatile("bar.sync 1, %0;" ::"n"(CTH));
+        }
         build_panel<TYPE, CTH, (PHASED ? 2 : 8)>(p.x, p.x_bf16 != 0, p.nslots, p.k, p.xpitch, p.status, xh, sxp, sx_slot_bytes, xrow_idx, k0,
                                min(nsp * SLICE_ELEMS, p.k - k0));
         if (s0 == 0) __syncthreads();                                    // panel + all barrier initialisations
@@ -647,23 +709,25 @@ __global__ void __launch_bounds__((NTEAMS * TEAM + 2) * 32, 1) gemv_mma_kernel(c
             // the block a warp takes rotates, so that the slower unaligned (odd) Q6_K blocks and the
             // idle turns of a short last slice spread evenly over the team
             blk = (blk + 1) & (TEAM - 1);
-            const uint32_t nblk = s0 + s == last_slice ? last_nblk : static_cast<uint32_t>(TEAM);
+            // short rows: the stage holds nsub groups of 16 rows and `blk` counts (group, block) pairs
+            const uint32_t sgi = nsub > 1 ? blk / last_nblk : 0u, bb = nsub > 1 ? blk - sgi * last_nblk : blk;
+            const uint32_t nblk = nsub > 1 ? nsub * last_nblk : (s0 + s == last_slice ? last_nblk : static_cast<uint32_t>(TEAM));
             if (blk < nblk && dbg != 1) {
-                const uint8_t* r0 = ring_g + st * stage_bytes;
+                const uint8_t* r0 = ring_g + st * stage_bytes + sgi * (ROWS * pitch);
                 const uint8_t* r1 = r0 + 8 * pitch;
-                const uint32_t e0 = s * SLICE_ELEMS + 256 * blk;          // element index inside the panel
+                const uint32_t e0 = s * SLICE_ELEMS + 256 * bb;           // element index inside the panel
                 if constexpr (K45) {
-                    const uint8_t* b0 = r0 + blk * G.bytes;
-                    const uint8_t* b1 = r1 + blk * G.bytes;
+                    const uint8_t* b0 = r0 + bb * G.bytes;
+                    const uint8_t* b1 = r1 + bb * G.bytes;
                     const uint8_t* sx = sxslot + (e0 >> 8) * SXB;
                     half_k45<TYPE == HF2Q_TYPE_Q5_K>(b0, b1, 0, e0, xrow, sx, t, f);
                     half_k45<TYPE == HF2Q_TYPE_Q5_K>(b0, b1, 1, e0, xrow, sx, t, f);
                 } else if constexpr (Q6) {
-                    const uint8_t* b0 = r0 + blk * 210;
-                    const uint8_t* b1 = r1 + blk * 210;
+                    const uint8_t* b0 = r0 + bb * 210;
+                    const uint8_t* b1 = r1 + bb * 210;
                     const uint8_t* sx = sxslot + (e0 >> 8) * SXB;
                     // (the two halves run as a loop: half the code, which the instruction cache likes)
-                    if (blk & 1) {
+                    if (bb & 1) {
 #pragma unroll 1
                         for (int nh = 0; nh < 2; ++nh) half_q6k<false>(b0, b1, nh, e0, xrow, sx, scr0, scr1, t, f);
                     } else {
@@ -673,7 +737,7 @@ __global__ void __launch_bounds__((NTEAMS * TEAM + 2) * 32, 1) gemv_mma_kernel(c
                 } else {
 #pragma unroll
                     for (uint32_t h = 0; h < 2; ++h)
-                        half_legacy<TYPE == HF2Q_TYPE_Q8_0>(r0 + (2 * blk + h) * 4 * G.bytes, r1 + (2 * blk + h) * 4 * G.bytes,
+                        half_legacy<TYPE == HF2Q_TYPE_Q8_0>(r0 + (2 * bb + h) * 4 * G.bytes, r1 + (2 * bb + h) * 4 * G.bytes,
                                                             e0 + 128 * h, xrow, reinterpret_cast<const float*>(sxp), t, f);
                 }
             }
@@ -688,7 +752,7 @@ __global__ void __launch_bounds__((NTEAMS * TEAM + 2) * 32, 1) gemv_mma_kernel(c
                 // that was this team's last stage of the group: hand the partial sums to the reducer
                 const uint32_t fl = fl_base + grp, rs = fl & 1;
                 if (fl >= 2 && !mbar_wait_bounded(&red_empty[rs], ((fl >> 1) - 1) & 1, p.status)) return;
-                float* rb = red_w + rs * (CW * 128);
+                float* rb = red_t + rs * (CW * 128) + blk * 128;
                 *reinterpret_cast<float2*>(rb) = make_float2(f[0], f[1]);
                 *reinterpret_cast<float2*>(rb + 64) = make_float2(f[2], f[3]);
                 __syncwarp();
@@ -720,12 +784,18 @@ uint32_t row_pitch(uint32_t slice_bytes) {
         if (((slice_bytes + pad) / 4) % 8 == 4) return slice_bytes + pad;
     return slice_bytes + 16;
 }
+// Rows of at most four 256-element blocks would leave most of a team idle (one warp per block), so a
+// stage then holds several 16-row groups: 8, 4 or 2 for 1, 2 or 3..4 blocks.
+uint32_t sub_groups_of(uint32_t k) {
+    const uint32_t nblk = k >> 8;
+    return nblk == 1 ? 8u : nblk == 2 ? 4u : nblk <= 4 ? 2u : 1u;
+}
 size_t stage_bytes_of(uint32_t type, uint32_t k) {
     const BlockGeom g = block_geom(type);
     uint32_t slice = SLICE_ELEMS / g.elems * g.bytes;
     const uint32_t row = k / g.elems * g.bytes;
     if (slice > row) slice = row;
-    return static_cast<size_t>(ROWS) * row_pitch(slice);
+    return static_cast<size_t>(ROWS) * sub_groups_of(k) * row_pitch(slice);
 }
 
 int env_int(const char* name, int dflt) {
@@ -830,6 +900,28 @@ extern "C" __attribute__((visibility("default"))) int hf2q_probe_read(unsigned l
 }
 #endif
 
+namespace {
+__global__ void gather_wait_kernel(const uint32_t* flag, uint32_t* status) {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    if (threadIdx.x == 0) {
+        const uint32_t want = *reinterpret_cast<const volatile uint32_t*>(flag + 1);
+        const long long t0 = clock64();
+        for (;;) {
+            uint32_t got;
+            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(got) : "l"(flag) : "memory");
+            if (static_cast<int32_t>(got - want) >= 0) break;
+            if (clock64() - t0 > (1ll << 31)) { atomicOr(status, STATUS_WAIT_TIMEOUT); break; }
+            __nanosleep(50);
+        }
+    }
+}
+}  // namespace
+
+cudaError_t launch_gather_wait(const uint32_t* flag, uint32_t* status, cudaStream_t st) {
+    gather_wait_kernel<<<1, 32, 0, st>>>(flag, status);
+    return cudaGetLastError();
+}
+
 bool gemv_mma_supported(const GemvArgs& a) {
     const BlockGeom g = block_geom(a.type);
     const uint64_t row_bytes = static_cast<uint64_t>(a.k) / g.elems * g.bytes;
@@ -851,6 +943,9 @@ cudaError_t launch_gemv_mma(const GemvArgs& a, const DeviceInfo& dev, cudaStream
     const BlockGeom g = block_geom(a.type);
     MParams p{};
     p.w = static_cast<const uint8_t*>(a.w);
+    p.w2 = static_cast<const uint8_t*>(a.w2);
+    p.y2 = a.y2;
+    p.pair_slots = a.slots;
     p.x = a.x;
     p.y = a.y;
     p.ids = a.ids;
@@ -868,15 +963,23 @@ cudaError_t launch_gemv_mma(const GemvArgs& a, const DeviceInfo& dev, cudaStream
     if (p.slice_bytes > p.row_bytes) p.slice_bytes = p.row_bytes;
     p.pitch = row_pitch(p.slice_bytes);
     p.nslices = (a.k + SLICE_ELEMS - 1) / SLICE_ELEMS;
-    p.ngroups = (a.n + ROWS - 1) / ROWS;
+    p.sub_groups = sub_groups_of(a.k);
+    p.ngroups = (a.n + ROWS * p.sub_groups - 1) / (ROWS * p.sub_groups);
     p.last_nblk = (a.k - (p.nslices - 1) * SLICE_ELEMS) >> 8;
     p.status = a.status;
+    if (a.gather) {
+        const GatherArgs& g = *a.gather;
+        if (a.ids || g.n_ranks < 1 || g.n_ranks > 8 || g.rank >= g.n_ranks) return cudaErrorInvalidValue;
+        for (uint32_t r = 0; r < g.n_ranks; ++r) { p.g_y[r] = g.y_all[r]; p.g_flag[r] = g.flags[r]; }
+        p.g_nranks = g.n_ranks; p.g_rank = g.rank; p.g_ntotal = g.n_total; p.g_col0 = g.col0;
+        p.g_wait = g.wait_expected;
+    }
     switch (a.type) {
-        case HF2Q_TYPE_Q4_0: return launch_mma_t<HF2Q_TYPE_Q4_0>(p, a.slots, dev, st);
-        case HF2Q_TYPE_Q8_0: return launch_mma_t<HF2Q_TYPE_Q8_0>(p, a.slots, dev, st);
-        case HF2Q_TYPE_Q4_K: return launch_mma_t<HF2Q_TYPE_Q4_K>(p, a.slots, dev, st);
-        case HF2Q_TYPE_Q5_K: return launch_mma_t<HF2Q_TYPE_Q5_K>(p, a.slots, dev, st);
-        case HF2Q_TYPE_Q6_K: return launch_mma_t<HF2Q_TYPE_Q6_K>(p, a.slots, dev, st);
+        case HF2Q_TYPE_Q4_0: return launch_mma_t<HF2Q_TYPE_Q4_0>(p, a.w2 ? 2 * a.slots : a.slots, dev, st);
+        case HF2Q_TYPE_Q8_0: return launch_mma_t<HF2Q_TYPE_Q8_0>(p, a.w2 ? 2 * a.slots : a.slots, dev, st);
+        case HF2Q_TYPE_Q4_K: return launch_mma_t<HF2Q_TYPE_Q4_K>(p, a.w2 ? 2 * a.slots : a.slots, dev, st);
+        case HF2Q_TYPE_Q5_K: return launch_mma_t<HF2Q_TYPE_Q5_K>(p, a.w2 ? 2 * a.slots : a.slots, dev, st);
+        case HF2Q_TYPE_Q6_K: return launch_mma_t<HF2Q_TYPE_Q6_K>(p, a.w2 ? 2 * a.slots : a.slots, dev, st);
         default: return cudaErrorInvalidValue;
     }
 }

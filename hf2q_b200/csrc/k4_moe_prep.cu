@@ -20,8 +20,8 @@ constexpr int SORT_THREADS = 1024;
 // Single CTA: histogram, exclusive scans, scatter.  Shared memory: 4 arrays of (E+1) u32.
 __global__ void __launch_bounds__(SORT_THREADS) moe_sort_kernel(const uint32_t* __restrict__ ids, uint32_t rows, uint32_t n_experts,
                                                                 uint32_t nt, uint32_t* __restrict__ header, uint4* __restrict__ tiles,
-                                                                uint32_t* __restrict__ perm, float* __restrict__ y, uint32_t n,
-                                                                uint32_t* status) {
+                                                                uint32_t* __restrict__ perm, float* __restrict__ y, float* __restrict__ y2,
+                                                                uint32_t n, uint32_t* status) {
     extern __shared__ uint32_t sm[];
     uint32_t* cnt = sm;                       // [E]
     uint32_t* off = cnt + n_experts;          // [E+1] first sorted row of each expert
@@ -62,7 +62,10 @@ __global__ void __launch_bounds__(SORT_THREADS) moe_sort_kernel(const uint32_t* 
         if (e < n_experts) {
             perm[atomicAdd(&cur[e], 1u)] = r;
         } else {
-            for (uint32_t c = 0; c < n; ++c) y[static_cast<size_t>(r) * n + c] = 0.f;   // rejected row: defined output
+            for (uint32_t c = 0; c < n; ++c) {                                           // rejected row: defined output
+                y[static_cast<size_t>(r) * n + c] = 0.f;
+                if (y2) y2[static_cast<size_t>(r) * n + c] = 0.f;
+            }
         }
     }
 }
@@ -129,15 +132,15 @@ MoeScratch moe_scratch_layout(uint32_t n_experts, uint32_t rows, uint32_t k) {
 }
 
 cudaError_t launch_moe_prep(const uint32_t* ids, uint32_t rows, uint32_t n_experts, uint32_t top_k, uint32_t nt, const void* x,
-                            uint32_t x_dtype, uint32_t k, float* y, uint32_t n, void* scratch, const MoeScratch& lay, uint32_t* status,
-                            int sm_count, cudaStream_t st) {
+                            uint32_t x_dtype, uint32_t k, float* y, float* y2, uint32_t n, void* scratch, const MoeScratch& lay,
+                            uint32_t* status, int sm_count, cudaStream_t st) {
     uint8_t* base = static_cast<uint8_t*>(scratch);
     uint32_t* header = reinterpret_cast<uint32_t*>(base);
     uint4* tiles = reinterpret_cast<uint4*>(base + lay.tiles_off);
     uint32_t* perm = reinterpret_cast<uint32_t*>(base + lay.perm_off);
     __half* xg = reinterpret_cast<__half*>(base + lay.xg_off);
     const size_t smem = (4 * static_cast<size_t>(n_experts) + 2) * 4;
-    moe_sort_kernel<<<1, SORT_THREADS, smem, st>>>(ids, rows, n_experts, nt, header, tiles, perm, y, n, status);
+    moe_sort_kernel<<<1, SORT_THREADS, smem, st>>>(ids, rows, n_experts, nt, header, tiles, perm, y, y2, n, status);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return e;
     const unsigned grid = rows < static_cast<uint32_t>(sm_count) * 8 ? rows : static_cast<uint32_t>(sm_count) * 8;

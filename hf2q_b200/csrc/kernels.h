@@ -13,6 +13,14 @@ cudaError_t launch_dequant(uint32_t type, const void* w, void* out, uint32_t out
 // Dense call: ids == nullptr, top_k == 1, slots == 1, m = activation rows (1..8).
 // Routed call (mul_mv_id): ids != nullptr, one slot per routed output row, m == 1 per slot;
 // slot r reads x row r / top_k and the expert matrix at w + ids[r] * expert_stride.
+// Row-sharded product whose all-gather is part of the kernel: every rank's output buffer
+// [m][n_total] and arrival counter, as mapped into this process (peer memory for the other ranks).
+struct GatherArgs {
+    float* y_all[8];
+    uint32_t* flags[8];
+    uint32_t n_ranks, rank, n_total, col0;   // this rank's rows are columns [col0, col0 + n) of the full output
+    uint32_t wait_expected;                  // != 0: wait for the previous products' columns from all ranks before reading x
+};
 struct GemvArgs {
     const void* w;
     const void* x;
@@ -24,6 +32,11 @@ struct GemvArgs {
     uint32_t m, n, k;
     uint32_t slots, top_k, n_experts;
     uint32_t* status;
+    const GatherArgs* gather = nullptr;      // dense mat-vec only
+    // routed pair (two stacked expert tensors of the same geometry, same x and ids): slots [slots, 2*slots)
+    // read w2 and write y2; nullptr = single product
+    const void* w2 = nullptr;
+    float* y2 = nullptr;
 };
 struct DeviceInfo {
     int sm_count;
@@ -36,6 +49,9 @@ cudaError_t launch_gemv(const GemvArgs& a, const DeviceInfo& dev, cudaStream_t s
 bool gemv_mma_supported(const GemvArgs& a);
 uint32_t gemv_mma_max_rows(uint32_t type, uint32_t k, uint32_t x_dtype, const DeviceInfo& dev);
 cudaError_t launch_gemv_mma(const GemvArgs& a, const DeviceInfo& dev, cudaStream_t st);
+// bounded wait (one warp) until the arrival counter flag[0] has caught up with the expected count flag[1]; a
+// timeout sets STATUS_WAIT_TIMEOUT
+cudaError_t launch_gather_wait(const uint32_t* flag, uint32_t* status, cudaStream_t st);
 
 // Tensor-memory variant of the mat-vec (k1_gemv_tc.cu): tcgen05 with thread-per-row dequant and a
 // cluster split of k.  Dense calls only, m <= 8.
@@ -60,8 +76,8 @@ struct MoeScratch {
 uint32_t moe_token_tile(uint32_t rows, uint32_t n_experts);
 MoeScratch moe_scratch_layout(uint32_t n_experts, uint32_t rows, uint32_t k);
 cudaError_t launch_moe_prep(const uint32_t* ids, uint32_t rows, uint32_t n_experts, uint32_t top_k, uint32_t nt, const void* x,
-                            uint32_t x_dtype, uint32_t k, float* y, uint32_t n, void* scratch, const MoeScratch& lay, uint32_t* status,
-                            int sm_count, cudaStream_t st);
+                            uint32_t x_dtype, uint32_t k, float* y, float* y2, uint32_t n, void* scratch, const MoeScratch& lay,
+                            uint32_t* status, int sm_count, cudaStream_t st);   // y2: second output of a pair call or nullptr
 bool gemm_tc_grouped_supported(uint32_t type, const void* w, uint64_t expert_stride, uint32_t n_experts, uint32_t k);
 cudaError_t launch_gemm_tc_grouped(uint32_t type, const void* w_stacked, uint64_t expert_stride, uint32_t n_experts, uint32_t rows,
                                    float* y, uint32_t n, uint32_t k, uint32_t nt, void* scratch, const MoeScratch& lay,

@@ -9,11 +9,17 @@ The reference is single-device (no collective exists in hf2q), so both schemes a
   back with a second all-to-all.
 
 The functions take the local compute as a callable, so the same host logic runs over NCCL with
-the CUDA library and over gloo on CPU in the tests.  Remote data always lands in local memory
-(the collective's receive buffer) before any kernel reads it; no kernel here touches peer memory.
+the CUDA library and over gloo on CPU in the tests.  With those, remote data always lands in local
+memory (the collective's receive buffer) before any kernel reads it.
+
+``GatherGroup`` is the fused form of the dense scheme for 1..8 activation rows: the mat-vec kernel
+itself stores this rank's columns into every rank's output buffer (peer memory mapped through CUDA
+IPC) and bumps the peers' arrival counters, so a decode step needs no collective call at all and
+can be replayed from a CUDA graph.  Plain stores only: no multicast, no TMA on peer memory.
 """
 from __future__ import annotations
 
+import ctypes as C
 from typing import Callable, Sequence
 
 import torch
@@ -90,3 +96,86 @@ def ep_mul_mat_id(x_rows: torch.Tensor, ids: torch.Tensor, n_experts: int, n_out
     out.index_copy_(0, order, y_back)
     _ = rank
     return out
+
+
+class _Gather(C.Structure):                        # hf2q_gather in include/hf2q_cuda.h
+    _fields_ = [("y_all", C.c_void_p * 8), ("flags", C.c_void_p * 8), ("n_ranks", C.c_uint32), ("rank", C.c_uint32),
+                ("n_total", C.c_uint32), ("col0", C.c_uint32), ("wait_previous", C.c_uint32)]
+
+
+class _DevView:
+    """Lets torch wrap a raw device pointer (zero copy)."""
+
+    def __init__(self, ptr: int, shape, typestr: str):
+        self.__cuda_array_interface__ = {"shape": tuple(shape), "typestr": typestr, "data": (ptr, False), "version": 2}
+
+
+class GatherGroup:
+    """Output buffers [max_m][n_total] and arrival counters of all ranks, mapped into this process.
+
+    Every rank must issue the same sequence of ``matmul`` calls.  ``matmul(..., wait_previous=True)``
+    makes the kernel wait, after it has started prefetching weights, until the previous product's
+    columns from all ranks have arrived here -- what a decode chain needs when x is that output.
+    ``wait()`` queues a tiny kernel that waits for everything issued so far."""
+
+    def __init__(self, ctx, max_m: int, n_total: int, group=None):
+        self.ctx, self.group = ctx, group
+        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        if self.world > 8:
+            raise ValueError("at most 8 ranks")
+        self.max_m, self.n_total = max_m, n_total
+        lib, h = ctx._lib, ctx._h
+        own_y, own_f = C.c_void_p(), C.c_void_p()
+        hy, hf = (C.c_uint8 * 64)(), (C.c_uint8 * 64)()
+        ctx._check(lib.hf2q_cuda_ipc_alloc(h, max_m * n_total * 4, C.byref(own_y), hy))
+        ctx._check(lib.hf2q_cuda_ipc_alloc(h, 256, C.byref(own_f), hf))
+        handles = [None] * self.world
+        dist.all_gather_object(handles, (bytes(hy), bytes(hf)), group=group)
+        self.y_ptrs, self.flag_ptrs, self._opened = [], [], []
+        for r, (by, bf) in enumerate(handles):
+            if r == self.rank:
+                self.y_ptrs.append(own_y.value)
+                self.flag_ptrs.append(own_f.value)
+                continue
+            py, pf = C.c_void_p(), C.c_void_p()
+            ctx._check(lib.hf2q_cuda_ipc_open(h, (C.c_uint8 * 64).from_buffer_copy(by), C.byref(py)))
+            ctx._check(lib.hf2q_cuda_ipc_open(h, (C.c_uint8 * 64).from_buffer_copy(bf), C.byref(pf)))
+            self.y_ptrs.append(py.value)
+            self.flag_ptrs.append(pf.value)
+            self._opened += [py.value, pf.value]
+        dist.barrier(group=group)              # nobody launches before everyone has mapped the buffers
+
+    def _struct(self, col0: int, wait_previous: bool) -> _Gather:
+        g = _Gather()
+        for r in range(self.world):
+            g.y_all[r] = self.y_ptrs[r]
+            g.flags[r] = self.flag_ptrs[r]
+        g.n_ranks, g.rank, g.n_total, g.col0, g.wait_previous = self.world, self.rank, self.n_total, col0, int(wait_previous)
+        return g
+
+    def matmul(self, x: torch.Tensor, weight, m: int, col0: int, wait_previous: bool = False) -> None:
+        """Columns [col0, col0 + weight.rows) of y[m, n_total] = x . dequant(weight)^T on every rank."""
+        from . import ops
+        if m > self.max_m:
+            raise ValueError(f"m={m} exceeds the group's {self.max_m} rows")
+        g = self._struct(col0, wait_previous and self.world > 1)
+        self.ctx._check(self.ctx._lib.hf2q_cuda_qmatmul_gather(
+            self.ctx._h, self.ctx._stream(), x.data_ptr(), ops._act(x, "x"), weight.ptr, C.byref(g), m, weight.rows,
+            weight.cols, weight.ggml_type))
+
+    def wait(self) -> None:
+        if self.world > 1:
+            self.ctx._check(self.ctx._lib.hf2q_cuda_gather_wait(self.ctx._h, self.ctx._stream(), self.flag_ptrs[self.rank]))
+
+    def output(self, m: int) -> torch.Tensor:
+        """This rank's full-width output buffer as a float32 [m, n_total] tensor (no copy)."""
+        return torch.as_tensor(_DevView(self.y_ptrs[self.rank], (m, self.n_total), "<f4"), device=f"cuda:{self.ctx.device}")
+
+    def close(self) -> None:
+        torch.cuda.synchronize()
+        dist.barrier(group=self.group)         # peers may still be storing into our buffers
+        for p in self._opened:
+            self.ctx._lib.hf2q_cuda_ipc_close(self.ctx._h, p)
+        self._opened = []
+        self.ctx._lib.hf2q_cuda_free(self.ctx._h, self.y_ptrs[self.rank])
+        self.ctx._lib.hf2q_cuda_free(self.ctx._h, self.flag_ptrs[self.rank])

@@ -81,8 +81,7 @@ def build_moe_ffn_layer_gpu_q(ctx: ops.GpuContext, x: torch.Tensor, w: MoeFfnWei
     g = torch.empty((rows, inter), dtype=torch.float32, device=x.device)
     u = torch.empty_like(g)
     pg = ops.GgmlQuantizedMatmulIdParams(T, k, inter, hidden, E, sg, w.ggml_type_gate_up)
-    ops.quantized_matmul_id_ggml(ctx, x, w.expert_gate.data_ptr(), ids, g, scratch, pg)
-    ops.quantized_matmul_id_ggml(ctx, x, w.expert_up.data_ptr(), ids, u, scratch, pg)
+    ops.quantized_matmul_id_pair_ggml(ctx, x, w.expert_gate.data_ptr(), w.expert_up.data_ptr(), ids, g, u, scratch, pg)
     act = _silu_mul(ctx, g, u)
     d = torch.empty((rows, hidden), dtype=torch.float32, device=x.device)
     pd = ops.GgmlQuantizedMatmulIdParams(rows, 1, hidden, inter, E, sd, w.ggml_type_down)

@@ -273,6 +273,28 @@ def quantized_matmul_id_ggml(ctx: GpuContext, input: torch.Tensor, weight_ptr: i
                                              int(params.ggml_type), sp, sb))
 
 
+def quantized_matmul_id_pair_ggml(ctx: GpuContext, input: torch.Tensor, weight_a: int, weight_b: int, ids: torch.Tensor,
+                                  out_a: torch.Tensor, out_b: torch.Tensor, scratch: IdMmScratch | None,
+                                  params: GgmlQuantizedMatmulIdParams) -> None:
+    """mul_mat_id against two stacked expert tensors of the same geometry (gate and up) sharing input and ids."""
+    xdt = _act(input, "input")
+    if ids.dtype not in (torch.int32, torch.uint32) or not ids.is_cuda or not ids.is_contiguous():
+        raise Hf2qError(_lib.ERR_INVALID_ARGUMENT, "ids must be a contiguous 32-bit integer CUDA tensor")
+    rows = params.n_tokens * params.top_k
+    if ids.numel() < rows or min(out_a.numel(), out_b.numel()) < rows * params.n or input.numel() < params.n_tokens * params.k:
+        raise Hf2qError(_lib.ERR_INVALID_ARGUMENT, "ids/input/out smaller than the params require")
+    for out in (out_a, out_b):
+        if out.dtype != torch.float32 or not out.is_cuda or not out.is_contiguous():
+            raise Hf2qError(_lib.ERR_INVALID_ARGUMENT, "outputs must be contiguous float32 CUDA tensors")
+    sp, sb = (scratch.buf.data_ptr(), scratch.nbytes) if scratch is not None else (None, 0)
+    wa = weight_a.ptr if isinstance(weight_a, QuantWeight) else int(weight_a)
+    wb = weight_b.ptr if isinstance(weight_b, QuantWeight) else int(weight_b)
+    ctx._check(ctx._lib.hf2q_cuda_qmatmul_id_pair(ctx._h, ctx._stream(), input.data_ptr(), xdt, wa, wb, ids.data_ptr(),
+                                                  out_a.data_ptr(), out_b.data_ptr(), params.n_tokens, params.top_k,
+                                                  params.n, params.k, params.n_experts, params.expert_stride,
+                                                  int(params.ggml_type), sp, sb))
+
+
 def dequantize(ctx: GpuContext, weight: QuantWeight, out_dtype=torch.float32) -> torch.Tensor:
     out = torch.empty((weight.rows, weight.cols), dtype=out_dtype, device=f"cuda:{ctx.device}")
     ctx._check(ctx._lib.hf2q_cuda_dequantize(ctx._h, ctx._stream(), weight.ptr, weight.ggml_type,

@@ -180,6 +180,15 @@ HF2Q_API int32_t hf2q_cuda_qmatmul_id(hf2q_ctx* ctx, void* stream, const void* x
                                       uint32_t n_experts, uint64_t expert_stride,
                                       uint32_t ggml_type, void* scratch, uint64_t scratch_bytes);
 /* IdMmScratch::alloc(device, n_experts, max_n_tokens) (decode_pool.rs:205-214). */
+/* The same product for TWO stacked expert tensors of identical geometry that share x and ids: the
+ * gate and up projections of build_moe_ffn_layer_gpu_q_into (gpu_ffn.rs:2606-2618 builds both with one
+ * parameter block).  Few routed rows: one launch serves both tensors; many: the sort by expert and
+ * the activation gather are done once for both grouped products.  Same scratch as hf2q_cuda_qmatmul_id. */
+HF2Q_API int32_t hf2q_cuda_qmatmul_id_pair(hf2q_ctx* ctx, void* stream, const void* x, uint32_t x_dtype,
+                                           const void* w_a, const void* w_b, const uint32_t* ids,
+                                           float* y_a, float* y_b, uint32_t n_tokens, uint32_t top_k,
+                                           uint32_t n, uint32_t k, uint32_t n_experts, uint64_t expert_stride,
+                                           uint32_t ggml_type, void* scratch, uint64_t scratch_bytes);
 HF2Q_API int32_t hf2q_cuda_qmatmul_id_scratch_bytes(uint32_t n_experts, uint32_t max_rows,
                                                     uint32_t k, uint32_t x_dtype, uint64_t* out);
 
@@ -189,6 +198,38 @@ HF2Q_API int32_t hf2q_cuda_qmatmul_id_scratch_bytes(uint32_t n_experts, uint32_t
 HF2Q_API int32_t hf2q_cuda_moe_softmax_topk(hf2q_ctx* ctx, void* stream, const float* logits,
                                             uint32_t* ids, float* weights, uint32_t n_tokens,
                                             uint32_t n_experts, uint32_t top_k);
+
+/* ---- e: row-sharded mat-vec with the all-gather in its epilogue ------------------------------- *
+ * The reference runs on one device and has no collective; this is the multi-GPU form of
+ * quantized_matmul_ggml for weights sharded by output rows (one process per GPU).  Every rank owns
+ * a full-width output buffer [m][n_total] and an arrival counter, allocated with hf2q_cuda_ipc_alloc
+ * and opened by the other ranks with hf2q_cuda_ipc_open (CUDA IPC; needs peer access, i.e. NVLink
+ * or PCIe P2P between the GPUs).  hf2q_cuda_qmatmul_gather computes this rank's n rows of the
+ * product and stores them into columns [col0, col0 + n) of EVERY rank's buffer (plain stores to
+ * peer memory from the kernel's epilogue); every CTA then adds 1 to every other rank's arrival
+ * counter (word 0 of that rank's 256-byte counter block), and the launch adds the number of arrivals
+ * it stands for to the own expected count (word 1 of the own block).  All ranks issue the same
+ * sequence of calls, so a rank has received everything once its word 0 has caught up with its
+ * word 1.  A consumer waits for that either inside the next product
+ * (wait_previous != 0: the kernel prefetches weights, then waits before it reads x) or with
+ * hf2q_cuda_gather_wait.  Both waits are bounded (about a second; a timeout is reported by
+ * hf2q_cuda_check_status) and depend on device-side counters only, so a captured CUDA graph of such
+ * calls can be replayed.  m <= 8 and the shapes of the tensor-core mat-vec only (16-byte aligned
+ * weight rows, k % 256 == 0); one launch per call. */
+typedef struct hf2q_gather {
+    void* y_all[8];          /* float [m][n_total] of rank 0..n_ranks-1 as mapped in this process */
+    void* flags[8];          /* 256-byte counter block of rank 0..n_ranks-1 */
+    uint32_t n_ranks, rank;
+    uint32_t n_total, col0;
+    uint32_t wait_previous;  /* != 0: wait for all ranks' earlier products before reading x */
+} hf2q_gather;
+HF2Q_API int32_t hf2q_cuda_ipc_alloc(hf2q_ctx* ctx, uint64_t bytes, void** dev, uint8_t* handle64);
+HF2Q_API int32_t hf2q_cuda_ipc_open(hf2q_ctx* ctx, const uint8_t* handle64, void** dev);
+HF2Q_API int32_t hf2q_cuda_ipc_close(hf2q_ctx* ctx, void* dev);
+HF2Q_API int32_t hf2q_cuda_qmatmul_gather(hf2q_ctx* ctx, void* stream, const void* x, uint32_t x_dtype,
+                                          const void* w, const hf2q_gather* g, uint32_t m, uint32_t n,
+                                          uint32_t k, uint32_t ggml_type);
+HF2Q_API int32_t hf2q_cuda_gather_wait(hf2q_ctx* ctx, void* stream, const void* flag);
 
 /* ---- a8: element-wise glue of the FFN builders ---------------------------------------------- */
 

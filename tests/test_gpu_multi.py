@@ -48,6 +48,32 @@ def _rank_main(rank, world, port, ret):
         y = hd.rowshard_matmul(xd, local, n).cpu().numpy()
         want = oracle.matmul_f64(x, oracle.dequantize(t, raw).reshape(n, k))
         ok &= rel_l2(y, want) < 1e-3
+        # --- dense again, all-gather inside the kernel (peer stores + arrival counters), a chain of
+        # products where each waits for the previous one's columns from every rank
+        gg = hd.GatherGroup(ctx, 8, n)
+        xb = make_x(8, k, seed=5)
+        for step, mm in enumerate((1, 4, 8, 3)):
+            xs = torch.from_numpy(xb[:mm] * (step + 1)).cuda().bfloat16()          # bf16: up to 8 rows per launch
+            gg.matmul(xs, w, mm, r0, wait_previous=step > 0)
+            gg.wait()
+            torch.cuda.synchronize()
+            got = gg.output(mm).cpu().numpy()
+            ok &= rel_l2(got, oracle.matmul_f64(xs.float().cpu().numpy(), oracle.dequantize(t, raw).reshape(n, k))) < 1e-3
+            dist.barrier()                      # nobody overwrites the buffers while a peer still reads them
+        # the same chain from a CUDA graph (no collective call inside): replay twice
+        xs = torch.from_numpy(xb[:2]).cuda().bfloat16()
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            gg.matmul(xs, w, 2, r0)
+            gg.matmul(xs, w, 2, r0, wait_previous=True)
+            gg.wait()
+        for _ in range(3):
+            graph.replay()
+        torch.cuda.synchronize()
+        ok &= rel_l2(gg.output(2).cpu().numpy(), oracle.matmul_f64(xs.float().cpu().numpy(), oracle.dequantize(t, raw).reshape(n, k))) < 1e-3
+        dist.barrier()
+        gg.close()
         # --- MoE: experts sharded, routed rows exchanged
         t, E, n, k = oracle.Q5_K, 8, 256, 512
         stride = hq.expert_stride(t, n, k)

@@ -231,6 +231,33 @@ def test_mul_mat_id_small(gpu_ctx, t):
         assert rel_l2(y.cpu().numpy(), want) < 2e-5
 
 
+@pytest.mark.parametrize("t", [oracle.Q5_K, oracle.Q6_K, oracle.Q8_0])
+def test_mul_mat_id_pair_matches_two_single_calls(gpu_ctx, t):
+    """gate + up in one call: few rows (one routed mat-vec launch for both tensors) and many rows
+    (sort/gather once, two grouped products); bad ids zero the rows of both outputs."""
+    ne, n, k, top_k = 8, 128, 2048 if t == oracle.Q6_K else 512, 2
+    stride = hq.expert_stride(t, n, k)
+    raws = [np.concatenate([make_quant_weight(t, n, k, seed=s0 + e) for e in range(ne)]) for s0 in (300, 400)]
+    wa, wb = (torch.from_numpy(r).cuda() for r in raws)
+    for n_tokens in (1, 5, 40):
+        rows = n_tokens * top_k
+        ids = np.random.default_rng(n_tokens).integers(0, ne, size=rows).astype(np.uint32)
+        xd, xs = _dev_x(make_x(n_tokens, k, seed=9), True)
+        p = hq.GgmlQuantizedMatmulIdParams(n_tokens, top_k, n, k, ne, stride, t)
+        scratch = hq.IdMmScratch.alloc(gpu_ctx, ne, rows, k)
+        idd = torch.from_numpy(ids.view(np.int32)).cuda()
+        ya, yb = (torch.full((rows, n), float("nan"), device="cuda") for _ in range(2))
+        hq.quantized_matmul_id_pair_ggml(gpu_ctx, xd, wa.data_ptr(), wb.data_ptr(), idd, ya, yb, scratch, p)
+        gpu_ctx.check_status()
+        for y, w, raw in ((ya, wa, raws[0]), (yb, wb, raws[1])):
+            single = torch.full((rows, n), float("nan"), device="cuda")
+            hq.quantized_matmul_id_ggml(gpu_ctx, xd, w.data_ptr(), idd, single, scratch, p)
+            assert torch.equal(y, single)                                   # same kernels, same order of sums
+            want = oracle.qmatmul_id(t, raw, stride, xs, ids, n_tokens, top_k, n, k, ne)
+            assert rel_l2(y.cpu().numpy(), want) < GATE
+        gpu_ctx.check_status()
+
+
 def test_mul_mat_id_down_projection_form(gpu_ctx):
     """down: n_tokens = T*top_k, top_k = 1, one activation row per routed slot (forward_mlx.rs:5324-5375)."""
     t, ne, n, k = oracle.Q5_K, 8, 256, 512
