@@ -75,6 +75,7 @@ struct MParams {
     uint32_t xpitch;       // bytes between activation rows in shared memory
     uint32_t phase_base, phase_rem;   // k-phases: the first phase_rem have phase_base + 1 slices, the rest phase_base
     uint32_t last_nblk;        // 256-element blocks in the last slice of a row
+    uint32_t dense_stage;      // != 0: a row is one slice and rows sit back to back in the stage, one bulk copy per stage
     uint32_t sub_groups;       // short rows (<= 4 blocks): a stage holds this many 16-row groups, one warp per (group, block)
     // fused all-gather (row-sharded weights over several GPUs); g_nranks == 0: plain store to y
     float* g_y[8];
@@ -450,8 +451,9 @@ __device__ __forceinline__ void build_panel(const void* x, bool x_bf16, uint32_t
 // sums to what the previous phase stored (same thread, same address: ordered, no atomics).  Every
 // weight byte is still read exactly once.
 // PHASED = false compiles the single-phase case without the phase loop (fewer live registers in
-// the main loop).
-template <uint32_t TYPE, int NTEAMS, bool PHASED>
+// the main loop); SUBG = false compiles out the stacked row groups of short rows; EXT = false the
+// fused all-gather and the routed pair.
+template <uint32_t TYPE, int NTEAMS, bool PHASED, bool SUBG, bool EXT>
 __global__ void __launch_bounds__((NTEAMS * TEAM + 2) * 32, 1) gemv_mma_kernel(const MParams p) {
     extern __shared__ __align__(128) uint8_t smem[];
     constexpr bool K45 = TYPE == HF2Q_TYPE_Q4_K || TYPE == HF2Q_TYPE_Q5_K;
@@ -471,7 +473,8 @@ __global__ void __launch_bounds__((NTEAMS * TEAM + 2) * 32, 1) gemv_mma_kernel(c
     uint8_t* ring = smem + 256;
     const uint32_t stages = p.stages, pitch = p.pitch, nslices = p.nslices;
     const uint32_t spp = p.phase_base + (p.phase_rem ? 1u : 0u);              // slices of the longest phase
-    const uint32_t nsub = p.sub_groups, stage_rows = ROWS * nsub;       // nsub > 1 only when a row is one short slice
+    // SUBG: a row is one short slice and a stage holds p.sub_groups groups of 16 rows
+    const uint32_t nsub = SUBG ? p.sub_groups : 1u, stage_rows = ROWS * nsub;
     const uint32_t stage_bytes = stage_rows * pitch;
     float* red = reinterpret_cast<float*>(ring + stages * stage_bytes);          // [2][CW][16][8]
     float* scr = red + 2 * CW * 128;                                            // [CW][16][8]
@@ -484,7 +487,7 @@ __global__ void __launch_bounds__((NTEAMS * TEAM + 2) * 32, 1) gemv_mma_kernel(c
     uint32_t slot = blockIdx.y;
     const uint8_t* wbase = p.w;
     float* ybase = p.y;
-    if (p.w2 && slot >= p.pair_slots) { slot -= p.pair_slots; wbase = p.w2; ybase = p.y2; }
+    if (EXT && p.w2 && slot >= p.pair_slots) { slot -= p.pair_slots; wbase = p.w2; ybase = p.y2; }
     uint32_t xrow_idx = 0;
     bool slot_ok = true;
     if (p.ids) {
@@ -540,9 +543,15 @@ __global__ void __launch_bounds__((NTEAMS * TEAM + 2) * 32, 1) gemv_mma_kernel(c
 #endif
                         if (lane == 0) mbar_arrive_expect_tx(&full[st], nrows * bytes);
                         __syncwarp();
-                        for (uint32_t rr = lane; rr < nrows; rr += 32)
-                            bulk_g2s(ring + st * stage_bytes + rr * pitch,
-                                     wbase + static_cast<uint64_t>(row0 + rr) * p.row_bytes + off, bytes, &full[st]);
+                        if (p.dense_stage) {
+                            // whole rows, contiguous in memory and in the stage: one copy
+                            if (lane == 0)
+                                bulk_g2s(ring + st * stage_bytes, wbase + static_cast<uint64_t>(row0) * p.row_bytes, nrows * bytes, &full[st]);
+                        } else {
+                            for (uint32_t rr = lane; rr < nrows; rr += 32)
+                                bulk_g2s(ring + st * stage_bytes + rr * pitch,
+                                         wbase + static_cast<uint64_t>(row0 + rr) * p.row_bytes + off, bytes, &full[st]);
+                        }
                     }
                 }
                 s0 = s1;
@@ -575,9 +584,17 @@ __global__ void __launch_bounds__((NTEAMS * TEAM + 2) * 32, 1) gemv_mma_kernel(c
                     float v[4] = {0.f, 0.f, 0.f, 0.f};
                     for (uint32_t i = 0, tm = first; i < nteams; ++i, tm = (tm + 1 == NTEAMS ? 0 : tm + 1)) {
                         const float* rbuf = red + (rs * CW + tm * TEAM + sg * nb) * 128 + lane;
-                        for (uint32_t w = 0; w < nb; ++w) {
+                        if (nsub == 1) {
 #pragma unroll
-                            for (int j = 0; j < 4; ++j) v[j] += rbuf[w * 128 + 32 * j];
+                            for (int w = 0; w < TEAM; ++w) {
+#pragma unroll
+                                for (int j = 0; j < 4; ++j) v[j] += rbuf[w * 128 + 32 * j];
+                            }
+                        } else {
+                            for (uint32_t w = 0; w < nb; ++w) {
+#pragma unroll
+                                for (int j = 0; j < 4; ++j) v[j] += rbuf[w * 128 + 32 * j];
+                            }
                         }
                     }
                     if (sg + 1 == nsub) {
@@ -595,7 +612,7 @@ __global__ void __launch_bounds__((NTEAMS * TEAM + 2) * 32, 1) gemv_mma_kernel(c
                             tok = (c & 1) ? 0xffffffffu : c >> 1;
                         }
                         if (row < p.n && tok < p.m) {
-                            if (p.g_nranks == 0) {
+                            if (!EXT || p.g_nranks == 0) {
                                 float* dst = yout + static_cast<size_t>(tok) * p.n + row;
                                 *dst = s0 ? *dst + out : out;
                             } else {
@@ -615,7 +632,7 @@ __global__ void __launch_bounds__((NTEAMS * TEAM + 2) * 32, 1) gemv_mma_kernel(c
             s0 += nsp;
         }
         if (lane == 0) PROBE_STAMP(5);
-        if (p.g_nranks > 1) {
+        if (EXT && p.g_nranks > 1) {
             // Tell the other ranks that this CTA's part of the columns has landed: one system-scope
             // fence after the warp's stores (the warp barrier makes it cover all lanes' stores), then
             // one fire-and-forget add per peer.  CTA 0 also records how many arrivals this launch adds
@@ -667,7 +684,7 @@ __global__ void __launch_bounds__((NTEAMS * TEAM + 2) * 32, 1) gemv_mma_kernel(c
         nsp = PHASED ? p.phase_base + (pi < p.phase_rem ? 1u : 0u) : nslices;     // slices of this phase
         if (PHASED && s0) asm volatile("bar.sync 1, %0;" ::"n"(CTH));    // everyone is done with the previous panel
         const uint32_t k0 = s0 * SLICE_ELEMS;
-        if (s0 == 0 && p.g_wait) {
+        if (EXT && s0 == 0 && p.g_wait) {
             // the activations are another product's gathered output: wait until every rank's part of
             // it has arrived here (bounded; the peers' kernels run on other GPUs)
             if (ctid == 0) {
@@ -790,12 +807,20 @@ uint32_t sub_groups_of(uint32_t k) {
     const uint32_t nblk = k >> 8;
     return nblk == 1 ? 8u : nblk == 2 ? 4u : nblk <= 4 ? 2u : 1u;
 }
+// A row that fits one slice can be staged without padding -- the rows of a stage are then one
+// contiguous range of memory and arrive with a single bulk copy instead of one per row -- unless that
+// pitch puts rows 0 or 16 banks apart (8- and 4-way conflicts on every weight load).
+bool dense_stage_ok(uint32_t row_bytes, uint32_t k) {
+    const uint32_t words = row_bytes / 4;
+    return k <= SLICE_ELEMS && words % 16 != 0;
+}
 size_t stage_bytes_of(uint32_t type, uint32_t k) {
     const BlockGeom g = block_geom(type);
     uint32_t slice = SLICE_ELEMS / g.elems * g.bytes;
     const uint32_t row = k / g.elems * g.bytes;
     if (slice > row) slice = row;
-    return static_cast<size_t>(ROWS) * sub_groups_of(k) * row_pitch(slice);
+    const uint32_t pitch = dense_stage_ok(row, k) ? row : row_pitch(slice);
+    return static_cast<size_t>(ROWS) * sub_groups_of(k) * pitch;
 }
 
 int env_int(const char* name, int dflt) {
@@ -838,9 +863,9 @@ Plan make_plan(uint32_t type, uint32_t k, uint32_t nslots, int teams, size_t lim
     return Plan{};
 }
 
-template <uint32_t TYPE, int NTEAMS, bool PHASED>
+template <uint32_t TYPE, int NTEAMS, bool PHASED, bool SUBG, bool EXT>
 cudaError_t launch_mma_tt(MParams p, uint32_t slots, const Plan& pl, const DeviceInfo& dev, cudaStream_t st) {
-    auto kern = gemv_mma_kernel<TYPE, NTEAMS, PHASED>;
+    auto kern = gemv_mma_kernel<TYPE, NTEAMS, PHASED, SUBG, EXT>;
     static std::mutex mu;
     static bool attr_set = false;
     {
@@ -877,19 +902,21 @@ cudaError_t launch_mma_tt(MParams p, uint32_t slots, const Plan& pl, const Devic
 template <uint32_t TYPE>
 cudaError_t launch_mma_t(MParams p, uint32_t slots, const DeviceInfo& dev, cudaStream_t st) {
     const size_t limit = static_cast<size_t>(dev.max_smem_optin);
-    static const int force_teams = env_int("HF2Q_CUDA_MMA_TEAMS", 2);          // tuning aid
 #ifdef HF2Q_MMA_PROBE
     p.debug = env_int("HF2Q_CUDA_MMA_DEBUG", 0);
     static uint32_t launch_counter = 0;
     p.launch_id = launch_counter++;
 #endif
-    int teams = force_teams == 3 ? 3 : 2;
-    Plan pl = make_plan(TYPE, p.k, p.nslots, teams, limit);
-    if (!pl.stages && teams == 3) { teams = 2; pl = make_plan(TYPE, p.k, p.nslots, 2, limit); }
+    // two teams: a third (26 warps, 72 registers) measured no faster
+    const Plan pl = make_plan(TYPE, p.k, p.nslots, 2, limit);
     if (!pl.stages) return cudaErrorInvalidConfiguration;
     const bool phased = pl.phase_base != p.nslices;
-    if (teams == 3) return phased ? launch_mma_tt<TYPE, 3, true>(p, slots, pl, dev, st) : launch_mma_tt<TYPE, 3, false>(p, slots, pl, dev, st);
-    return phased ? launch_mma_tt<TYPE, 2, true>(p, slots, pl, dev, st) : launch_mma_tt<TYPE, 2, false>(p, slots, pl, dev, st);
+    const bool ext = p.g_nranks != 0 || p.w2 != nullptr;
+    if (p.sub_groups > 1)                                                                          // one short slice per row
+        return ext ? launch_mma_tt<TYPE, 2, false, true, true>(p, slots, pl, dev, st) : launch_mma_tt<TYPE, 2, false, true, false>(p, slots, pl, dev, st);
+    if (phased)
+        return ext ? launch_mma_tt<TYPE, 2, true, false, true>(p, slots, pl, dev, st) : launch_mma_tt<TYPE, 2, true, false, false>(p, slots, pl, dev, st);
+    return ext ? launch_mma_tt<TYPE, 2, false, false, true>(p, slots, pl, dev, st) : launch_mma_tt<TYPE, 2, false, false, false>(p, slots, pl, dev, st);
 }
 
 }  // namespace
@@ -961,7 +988,8 @@ cudaError_t launch_gemv_mma(const GemvArgs& a, const DeviceInfo& dev, cudaStream
     p.row_bytes = a.k / g.elems * g.bytes;
     p.slice_bytes = SLICE_ELEMS / g.elems * g.bytes;
     if (p.slice_bytes > p.row_bytes) p.slice_bytes = p.row_bytes;
-    p.pitch = row_pitch(p.slice_bytes);
+    p.dense_stage = dense_stage_ok(p.row_bytes, a.k) ? 1u : 0u;
+    p.pitch = p.dense_stage ? p.row_bytes : row_pitch(p.slice_bytes);
     p.nslices = (a.k + SLICE_ELEMS - 1) / SLICE_ELEMS;
     p.sub_groups = sub_groups_of(a.k);
     p.ngroups = (a.n + ROWS * p.sub_groups - 1) / (ROWS * p.sub_groups);
