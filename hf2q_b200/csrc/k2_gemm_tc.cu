@@ -30,6 +30,8 @@
 // the final barrier, where TMEM is freed.  No cluster launch, no multicast.
 #include <cuda.h>
 
+#include <cstdlib>
+
 #include <mutex>
 #include <type_traits>
 
@@ -70,6 +72,7 @@ struct GParams {
     const GroupTile* tiles;
     const uint32_t* n_tiles;
     const uint32_t* perm;
+    uint32_t tiles_per_cta; // weight-row tiles (of 128 rows) one CTA walks, re-using its barriers, TMEM and token tile
     uint32_t boxw;          // bytes per weight row in one raw stage
     uint32_t blk_bytes;     // bytes of one 256-element K-block of a row
     uint32_t* status;
@@ -105,6 +108,20 @@ __device__ __forceinline__ void dequant_dispatch(uint32_t grp, const uint8_t* ro
     }
 }
 
+#ifdef HF2Q_TC_PROBE
+// timeline probe: [CTA (first 512 of the grid, linear)][event] global-timer stamps
+__device__ unsigned long long g_tc_ts[512 * 8];
+__device__ __forceinline__ void tc_stamp(int ev) {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    const uint32_t id = blockIdx.y * gridDim.x + blockIdx.x;
+    if (id < 512) g_tc_ts[id * 8 + ev] = t;
+}
+#define TC_STAMP(ev) tc_stamp(ev)
+#else
+#define TC_STAMP(ev)
+#endif
+
 // ---------------------------------------------------------------- the kernel
 template <uint32_t TYPE, int NT, bool GROUPED>
 __global__ void __launch_bounds__(GEMM_THREADS, (NT <= 64 ? 2 : 1))
@@ -127,10 +144,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
     uint64_t* a_full = x_empty + X_STAGES;      // [2]
     uint64_t* a_empty = a_full + 2;
     uint64_t* d_full = a_empty + 2;             // [1]
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(d_full + 1);
+    uint64_t* d_empty = d_full + 1;             // [1]
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(d_empty + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const uint32_t row0 = blockIdx.x * TILE_N;
+    // this CTA's weight-row tiles: [tile0, tile0 + ntile)
+    const uint32_t n_row_tiles = (p.n + TILE_N - 1) / TILE_N;
+    const uint32_t tile0 = blockIdx.x * p.tiles_per_cta;
+    const uint32_t ntile = min(p.tiles_per_cta, n_row_tiles - tile0);
     uint32_t tok0 = blockIdx.y * NT, tok_end = p.m, expert = 0;
     if constexpr (GROUPED) {
         if (blockIdx.y >= *p.n_tiles) return;              // the grid is sized for the worst case
@@ -138,12 +159,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
         tok0 = gt.start; tok_end = gt.start + gt.count; expert = gt.expert;
     }
     const uint32_t nkb = p.k / KB;
+    if (threadIdx.x == 0) TC_STAMP(0);
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < RAW_STAGES; ++s) { mbar_init(&raw_full[s], 1); mbar_init(&raw_empty[s], DEQ_WARPS); }
         for (int s = 0; s < X_STAGES; ++s) { mbar_init(&x_full[s], 1); mbar_init(&x_empty[s], 1); }
         for (int s = 0; s < 2; ++s) { mbar_init(&a_full[s], DEQ_WARPS); mbar_init(&a_empty[s], 1); }
         mbar_init(d_full, 1);
+        mbar_init(d_empty, DEQ_WARPS);
         mbar_fence_init();
     }
     if (warp == DEQ_WARPS + 1) { tmem_alloc(tmem_slot, TMEM_COLS); tmem_relinquish(); }
@@ -151,6 +174,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    if (threadIdx.x == 0) TC_STAMP(1);
     const uint32_t tmem_d = tmem_base;                 // columns [0, NT)
     const uint32_t tmem_a = tmem_base + (A_BUFS == 1 ? 128 : 256);     // A_BUFS buffers of 128 columns
 
@@ -158,22 +182,25 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
         // ------------------------------ TMA producer
         if (lane == 0) {
             bool ok = true;
-            for (uint32_t kb = 0; kb < nkb && ok; ++kb) {
-                const uint32_t rs = kb % RAW_STAGES;
-                if (kb >= RAW_STAGES) ok = mbar_wait_bounded(&raw_empty[rs], ((kb / RAW_STAGES) - 1) & 1, p.status);
-                if (!ok) break;
-                mbar_arrive_expect_tx(&raw_full[rs], raw_stage);
-                const uint32_t byte0 = (kb * p.blk_bytes) & ~15u;       // 16-byte aligned start of the box
-                if constexpr (GROUPED)
-                    tma_3d(raw + rs * raw_stage, &tmap_w, static_cast<int>(byte0 >> 1), static_cast<int>(row0), static_cast<int>(expert), &raw_full[rs]);
-                else
-                    tma_2d(raw + rs * raw_stage, &tmap_w, static_cast<int>(byte0 >> 1), static_cast<int>(row0), &raw_full[rs]);
-                for (uint32_t j = 0; j < KB / XK && ok; ++j) {
-                    const uint32_t xi = kb * (KB / XK) + j, st = xi % X_STAGES;
-                    if (xi >= X_STAGES) ok = mbar_wait_bounded(&x_empty[st], ((xi / X_STAGES) - 1) & 1, p.status);
+            for (uint32_t tl = 0, gk = 0; tl < ntile && ok; ++tl) {           // gk: K-block count over all tiles
+                const uint32_t row0 = (tile0 + tl) * TILE_N;
+                for (uint32_t kb = 0; kb < nkb && ok; ++kb, ++gk) {
+                    const uint32_t rs = gk % RAW_STAGES;
+                    if (gk >= RAW_STAGES) ok = mbar_wait_bounded(&raw_empty[rs], ((gk / RAW_STAGES) - 1) & 1, p.status);
                     if (!ok) break;
-                    mbar_arrive_expect_tx(&x_full[st], X_STAGE);
-                    tma_2d(xs + st * X_STAGE, &tmap_x, static_cast<int>(kb * KB + j * XK), static_cast<int>(tok0), &x_full[st]);
+                    mbar_arrive_expect_tx(&raw_full[rs], raw_stage);
+                    const uint32_t byte0 = (kb * p.blk_bytes) & ~15u;       // 16-byte aligned start of the box
+                    if constexpr (GROUPED)
+                        tma_3d(raw + rs * raw_stage, &tmap_w, static_cast<int>(byte0 >> 1), static_cast<int>(row0), static_cast<int>(expert), &raw_full[rs]);
+                    else
+                        tma_2d(raw + rs * raw_stage, &tmap_w, static_cast<int>(byte0 >> 1), static_cast<int>(row0), &raw_full[rs]);
+                    for (uint32_t j = 0; j < KB / XK && ok; ++j) {
+                        const uint32_t xi = gk * (KB / XK) + j, st = xi % X_STAGES;
+                        if (xi >= X_STAGES) ok = mbar_wait_bounded(&x_empty[st], ((xi / X_STAGES) - 1) & 1, p.status);
+                        if (!ok) break;
+                        mbar_arrive_expect_tx(&x_full[st], X_STAGE);
+                        tma_2d(xs + st * X_STAGE, &tmap_x, static_cast<int>(kb * KB + j * XK), static_cast<int>(tok0), &x_full[st]);
+                    }
                 }
             }
         }
@@ -183,28 +210,32 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
             // instruction descriptor: D f32, A/B f16, both K-major, N = NT, M = 128
             constexpr uint32_t IDESC = (1u << 4) | (static_cast<uint32_t>(NT >> 3) << 17) | (static_cast<uint32_t>(128 >> 4) << 24);
             bool ok = true;
-            for (uint32_t kb = 0; kb < nkb && ok; ++kb) {
-                const uint32_t ab = kb % A_BUFS;
-                ok = mbar_wait_bounded(&a_full[ab], (kb / A_BUFS) & 1, p.status);
-                if (!ok) break;
-                tc_fence_after();
-                for (uint32_t j = 0; j < KB / XK && ok; ++j) {
-                    const uint32_t xi = kb * (KB / XK) + j, st = xi % X_STAGES;
-                    ok = mbar_wait_bounded(&x_full[st], (xi / X_STAGES) & 1, p.status);
+            for (uint32_t tl = 0, gk = 0; tl < ntile && ok; ++tl) {
+                // the previous tile's accumulators must have been read before they are overwritten
+                if (tl) ok = mbar_wait_bounded(d_empty, (tl - 1) & 1, p.status);
+                for (uint32_t kb = 0; kb < nkb && ok; ++kb, ++gk) {
+                    const uint32_t ab = gk % A_BUFS;
+                    ok = mbar_wait_bounded(&a_full[ab], (gk / A_BUFS) & 1, p.status);
                     if (!ok) break;
                     tc_fence_after();
-                    const uint64_t bdesc = smem_desc_sw128(smem_u32(xs + st * X_STAGE));
+                    for (uint32_t j = 0; j < KB / XK && ok; ++j) {
+                        const uint32_t xi = gk * (KB / XK) + j, st = xi % X_STAGES;
+                        ok = mbar_wait_bounded(&x_full[st], (xi / X_STAGES) & 1, p.status);
+                        if (!ok) break;
+                        tc_fence_after();
+                        const uint64_t bdesc = smem_desc_sw128(smem_u32(xs + st * X_STAGE));
 #pragma unroll
-                    for (uint32_t kk = 0; kk < XK / 16; ++kk) {
-                        // A: 8 columns (16 f16) per K step; B: +32 bytes inside the swizzled row
-                        umma_ts(tmem_d, tmem_a + ab * 128 + (j * (XK / 16) + kk) * 8, bdesc + 2 * kk, IDESC,
-                                (kb | j | kk) != 0 ? 1u : 0u);
+                        for (uint32_t kk = 0; kk < XK / 16; ++kk) {
+                            // A: 8 columns (16 f16) per K step; B: +32 bytes inside the swizzled row
+                            umma_ts(tmem_d, tmem_a + ab * 128 + (j * (XK / 16) + kk) * 8, bdesc + 2 * kk, IDESC,
+                                    (kb | j | kk) != 0 ? 1u : 0u);
+                        }
+                        tc_commit(&x_empty[st]);       // activation stage free once these MMAs retire
                     }
-                    tc_commit(&x_empty[st]);       // activation stage free once these MMAs retire
+                    if (ok) tc_commit(&a_empty[ab]);
                 }
-                if (ok) tc_commit(&a_empty[ab]);
+                if (ok) tc_commit(d_full);
             }
-            if (ok) tc_commit(d_full);
         }
     } else {
         // ------------------------------ dequantisers (thread = weight row), then epilogue
@@ -212,25 +243,31 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
         const uint32_t r = quad * 32 + lane;               // weight row of the tile == TMEM lane
         const uint32_t lane_addr = (quad * 32u) << 16;
         bool ok = true;
-        for (uint32_t kb = 0; kb < nkb; ++kb) {
-            const uint32_t rs = kb % RAW_STAGES, ab = kb % A_BUFS;
-            if (ok) ok = mbar_wait_bounded(&raw_full[rs], (kb / RAW_STAGES) & 1, p.status);
-            if (ok && kb >= A_BUFS) ok = mbar_wait_bounded(&a_empty[ab], ((kb / A_BUFS) - 1) & 1, p.status);
+        for (uint32_t tl = 0, gk = 0; tl < ntile && ok; ++tl) {
+            const uint32_t row0 = (tile0 + tl) * TILE_N;
+            for (uint32_t kb = 0; kb < nkb; ++kb, ++gk) {
+                const uint32_t rs = gk % RAW_STAGES, ab = gk % A_BUFS;
+                if (ok) ok = mbar_wait_bounded(&raw_full[rs], (gk / RAW_STAGES) & 1, p.status);
+                if (ok && gk >= A_BUFS) ok = mbar_wait_bounded(&a_empty[ab], ((gk / A_BUFS) - 1) & 1, p.status);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+                tc_fence_after();
+                if (threadIdx.x == 0 && gk == 0) TC_STAMP(2);
+                const uint32_t off = (kb * p.blk_bytes) & 15u;
+                dequant_dispatch<TYPE>(grp, raw + rs * raw_stage + r * p.boxw, off, tmem_a + ab * 128 + lane_addr);
+                tmem_wait_st();
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) { mbar_arrive(&a_full[ab]); mbar_arrive(&raw_empty[rs]); }
+                if (threadIdx.x == 0 && gk == 0) TC_STAMP(3);
+                if (threadIdx.x == 0 && gk == nkb - 1) TC_STAMP(4);
+            }
+            // epilogue of this tile
+            if (ok) ok = mbar_wait_bounded(d_full, tl & 1, p.status);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
             tc_fence_after();
-            const uint32_t off = (kb * p.blk_bytes) & 15u;
-            dequant_dispatch<TYPE>(grp, raw + rs * raw_stage + r * p.boxw, off, tmem_a + ab * 128 + lane_addr);
-            tmem_wait_st();
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) { mbar_arrive(&a_full[ab]); mbar_arrive(&raw_empty[rs]); }
-        }
-        // epilogue
-        if (ok) ok = mbar_wait_bounded(d_full, 0, p.status);
-        ok = __all_sync(0xffffffffu, ok);
-        if (ok) {
-            tc_fence_after();
+            if (threadIdx.x == 0 && tl == 0) TC_STAMP(5);
             const uint32_t row = row0 + r;
 #pragma unroll 1
             for (int c0 = 32 * static_cast<int>(grp); c0 < NT; c0 += 32 * DEQ_GROUPS) {   // the groups share the columns
@@ -248,10 +285,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
                     }
                 }
             }
+            // this warp is done reading the accumulators: the next tile's MMAs may overwrite them
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(d_empty);
+            if (threadIdx.x == 0 && tl == 0) TC_STAMP(6);
         }
     }
     tc_fence_before();
     __syncthreads();
+    if (threadIdx.x == 0) TC_STAMP(7);
     if (warp == DEQ_WARPS + 1) { tc_fence_after(); tmem_dealloc(tmem_base, TMEM_COLS); }
 }
 
@@ -303,7 +346,8 @@ cudaError_t launch_gemm_t(const CUtensorMap& tw, const CUtensorMap& tx, const GP
             attr_set = true;
         }
     }
-    const dim3 grid((p.n + TILE_N - 1) / TILE_N, grid_y);
+    const uint32_t row_tiles = (p.n + TILE_N - 1) / TILE_N;
+    const dim3 grid((row_tiles + p.tiles_per_cta - 1) / p.tiles_per_cta, grid_y);
     kern<<<grid, GEMM_THREADS, smem, st>>>(tw, tx, p);
     return cudaGetLastError();
 }
@@ -320,6 +364,12 @@ cudaError_t launch_gemm_nt(const CUtensorMap& tw, const CUtensorMap& tx, const G
 }
 
 }  // namespace
+
+#ifdef HF2Q_TC_PROBE
+extern "C" __attribute__((visibility("default"))) int hf2q_tc_probe_read(unsigned long long* host) {
+    return static_cast<int>(cudaMemcpyFromSymbol(host, g_tc_ts, sizeof(g_tc_ts)));
+}
+#endif
 
 bool gemm_tc_supported(uint32_t type, const void* w, uint32_t n, uint32_t k) {
     (void)n;
@@ -370,6 +420,7 @@ cudaError_t launch_gemm_tc(uint32_t type, const void* w, const void* x, uint32_t
     // 2. tensor maps
     GParams p{};
     p.y = y; p.m = m; p.n = n; p.k = k;
+    p.tiles_per_cta = 1;
     p.boxw = boxw_of(type);
     p.blk_bytes = KB / g.elems * g.bytes;
     p.status = status;
@@ -434,6 +485,16 @@ cudaError_t launch_gemm_tc_grouped(uint32_t type, const void* w_stacked, uint64_
     uint8_t* base = static_cast<uint8_t*>(scratch);
     GParams p{};
     p.y = y; p.m = rows; p.n = n; p.k = k;
+    {
+        // One CTA walks several weight-row tiles of its (expert, token tile): barriers, tensor memory and the
+        // first copies' latency are paid once.  Keep about two CTAs per resident slot (2 per SM) in the grid.
+        static const int forced = [] { const char* v = getenv("HF2Q_CUDA_MOE_TPC"); return v && *v ? atoi(v) : 0; }();   // tuning aid
+        const uint32_t row_tiles = (n + TILE_N - 1) / TILE_N, token_tiles = rows / nt + n_experts / 2;
+        uint32_t tpc = static_cast<uint32_t>(static_cast<uint64_t>(row_tiles) * token_tiles / (4 * 148 * 2));
+        if (forced > 0) tpc = static_cast<uint32_t>(forced);
+        p.tiles_per_cta = tpc < 1 ? 1 : tpc > 8 ? 8 : tpc;
+        if (p.tiles_per_cta > row_tiles) p.tiles_per_cta = row_tiles;
+    }
     p.tiles = reinterpret_cast<const GroupTile*>(base + lay.tiles_off);
     p.n_tiles = reinterpret_cast<const uint32_t*>(base);
     p.perm = reinterpret_cast<const uint32_t*>(base + lay.perm_off);
