@@ -388,7 +388,14 @@ def main() -> None:
     gather = None
     if world > 1:
         from hf2q_b200.dist import GatherGroup
-        gather = GatherGroup(ctx, max(TOKENS), world * max(n for n, _ in SHAPES))
+        try:
+            gather = GatherGroup(ctx, max(TOKENS), world * max(n for n, _ in SHAPES))
+        except RuntimeError as exc:          # raised on every rank or on none
+            if rank == 0:
+                print(f"[bench] {exc}; using NCCL all-gathers after each product (eager launches)", file=sys.stderr)
+    ygath = {}
+    if world > 1 and gather is None:
+        ygath = {(n, m): torch.empty((world, m, n), dtype=torch.float32, device=dev) for n, _ in SHAPES for m in TOKENS}
     params = {(n, k, m): hq.GgmlQuantizedMatmulParams(m, n, k, Q6_K) for n, k in SHAPES for m in TOKENS}
 
     launches_per_step = args.copies * len(SHAPES) * len(TOKENS)
@@ -401,6 +408,8 @@ def main() -> None:
                 for (n, k), w in zip(SHAPES, weights[c]):
                     if gather is None:
                         hq.quantized_matmul_ggml(ctx, xdev[(k, m)], w, ydev[(n, m)], params[(n, k, m)])
+                        if world > 1:
+                            dist.all_gather_into_tensor(ygath[(n, m)], ydev[(n, m)])
                     else:
                         gather.matmul(xdev[(k, m)], w, m, rank * n, wait_previous=not args.no_chain_wait)
         if gather is not None:
@@ -430,7 +439,7 @@ def main() -> None:
     # multi-GPU step contains no collective call (the all-gather is in the kernels), so it is captured
     # the same way.
     graph = None
-    if not args.no_graph:
+    if not args.no_graph and (world == 1 or gather is not None):     # NCCL calls are not captured
         try:
             g = torch.cuda.CUDAGraph()
             with torch.cuda.graph(g):
@@ -557,9 +566,10 @@ def main() -> None:
             "launches_per_step": launches_per_step, "bytes_per_step": bytes_per_step,
             "launch_mode": "CUDA graph replay of one captured step" if graph is not None else "eager launches",
             "parallelism": "single GPU" if world == 1 else
-                           f"row-sharded x{world}, each rank's shard = the listed shapes; the all-gather of every output is "
-                           "in the kernel's epilogue (stores to the peers' buffers over NVLink + arrival counters), each "
-                           "product waits for the previous one's columns from all ranks",
+                           (f"row-sharded x{world}, each rank's shard = the listed shapes; the all-gather of every output is "
+                            "in the kernel's epilogue (stores to the peers' buffers over NVLink + arrival counters), each "
+                            "product waits for the previous one's columns from all ranks") if gather is not None else
+                           f"row-sharded x{world}, each rank's shard = the listed shapes; NCCL all-gather after every product",
         },
         "gpu_launches": int(gpu_launches),
         "e2e": {"value": round(e2e_val, 1), "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,

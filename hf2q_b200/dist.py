@@ -127,23 +127,42 @@ class GatherGroup:
         lib, h = ctx._lib, ctx._h
         own_y, own_f = C.c_void_p(), C.c_void_p()
         hy, hf = (C.c_uint8 * 64)(), (C.c_uint8 * 64)()
-        ctx._check(lib.hf2q_cuda_ipc_alloc(h, max_m * n_total * 4, C.byref(own_y), hy))
-        ctx._check(lib.hf2q_cuda_ipc_alloc(h, 256, C.byref(own_f), hf))
-        handles = [None] * self.world
-        dist.all_gather_object(handles, (bytes(hy), bytes(hf)), group=group)
         self.y_ptrs, self.flag_ptrs, self._opened = [], [], []
-        for r, (by, bf) in enumerate(handles):
-            if r == self.rank:
-                self.y_ptrs.append(own_y.value)
-                self.flag_ptrs.append(own_f.value)
-                continue
-            py, pf = C.c_void_p(), C.c_void_p()
-            ctx._check(lib.hf2q_cuda_ipc_open(h, (C.c_uint8 * 64).from_buffer_copy(by), C.byref(py)))
-            ctx._check(lib.hf2q_cuda_ipc_open(h, (C.c_uint8 * 64).from_buffer_copy(bf), C.byref(pf)))
-            self.y_ptrs.append(py.value)
-            self.flag_ptrs.append(pf.value)
-            self._opened += [py.value, pf.value]
-        dist.barrier(group=group)              # nobody launches before everyone has mapped the buffers
+        # Every rank takes part in both exchanges even if something failed locally, so that a failure
+        # (no peer access, IPC not permitted) raises on all ranks instead of leaving some of them waiting.
+        err = None
+        try:
+            ctx._check(lib.hf2q_cuda_ipc_alloc(h, max_m * n_total * 4, C.byref(own_y), hy))
+            ctx._check(lib.hf2q_cuda_ipc_alloc(h, 256, C.byref(own_f), hf))
+        except Exception as exc:                      # noqa: BLE001
+            err = exc
+        handles = [None] * self.world
+        dist.all_gather_object(handles, None if err else (bytes(hy), bytes(hf)), group=group)
+        if err is None and all(hd is not None for hd in handles):
+            try:
+                for r, (by, bf) in enumerate(handles):
+                    if r == self.rank:
+                        self.y_ptrs.append(own_y.value)
+                        self.flag_ptrs.append(own_f.value)
+                        continue
+                    py, pf = C.c_void_p(), C.c_void_p()
+                    ctx._check(lib.hf2q_cuda_ipc_open(h, (C.c_uint8 * 64).from_buffer_copy(by), C.byref(py)))
+                    self._opened.append(py.value)
+                    ctx._check(lib.hf2q_cuda_ipc_open(h, (C.c_uint8 * 64).from_buffer_copy(bf), C.byref(pf)))
+                    self._opened.append(pf.value)
+                    self.y_ptrs.append(py.value)
+                    self.flag_ptrs.append(pf.value)
+            except Exception as exc:                  # noqa: BLE001
+                err = exc
+        oks = [None] * self.world
+        dist.all_gather_object(oks, err is None, group=group)     # also: nobody launches before everyone has mapped the buffers
+        if not all(oks):
+            for ptr in self._opened:
+                lib.hf2q_cuda_ipc_close(h, ptr)
+            for own in (own_y, own_f):
+                if own.value:
+                    lib.hf2q_cuda_free(h, own.value)
+            raise RuntimeError(f"GatherGroup: peer buffers could not be set up on every rank (this rank: {err})")
 
     def _struct(self, col0: int, wait_previous: bool) -> _Gather:
         g = _Gather()
