@@ -633,18 +633,19 @@ __global__ void __launch_bounds__((NTEAMS * TEAM + 2) * 32, 1) gemv_mma_kernel(c
         }
         if (lane == 0) PROBE_STAMP(5);
         if (EXT && p.g_nranks > 1) {
-            // Tell the other ranks that this CTA's part of the columns has landed: one system-scope
-            // fence after the warp's stores (the warp barrier makes it cover all lanes' stores), then
-            // one fire-and-forget add per peer.  CTA 0 also records how many arrivals this launch adds
+            // Tell the other ranks that this CTA's part of the columns has landed: one fire-and-forget
+            // add with release semantics per peer.  CTA 0 also records how many arrivals this launch adds
             // to the own counter (every rank launches the same grid).
             __syncwarp();
             if (lane == 0) {
                 const uint32_t ctas = gridDim.x * gridDim.y;
                 if (blockIdx.x == 0 && blockIdx.y == 0) atomicAdd(p.g_flag[p.g_rank] + 1, ctas * (p.g_nranks - 1));
-                __threadfence_system();
+                // release at system scope: the adds become visible after this warp's stores (the warp
+                // barrier above makes the release cover all lanes' stores) without stalling the warp the
+                // way a separate fence does
                 for (uint32_t r = 0; r < p.g_nranks; ++r)
                     if (r != p.g_rank)
-                        asm volatile("red.relaxed.sys.global.add.u32 [%0], 1;" ::"l"(p.g_flag[r]) : "memory");
+                        asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(p.g_flag[r]) : "memory");
             }
         }
         return;

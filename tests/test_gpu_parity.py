@@ -397,3 +397,38 @@ def test_gguf_file_feeds_the_kernels(gpu_ctx, tmp_path):
         assert rel_l2(y.cpu().numpy(), _ref(t, raw, xs, n, k)) < 2e-5
         deq = hq.dequantize(gpu_ctx, w).cpu().numpy()
         assert np.array_equal(deq.view(np.uint32), oracle.dequantize(t, raw).reshape(n, k).view(np.uint32))
+
+
+def test_gather_entry_single_rank(gpu_ctx):
+    """hf2q_cuda_qmatmul_gather with one rank: columns land at col0 of a wider buffer, the wait kernel
+    and the in-kernel wait pass at once, phases (long rows) accumulate in the buffer."""
+    import ctypes as C
+    from hf2q_b200.dist import _Gather
+    lib, h = gpu_ctx._lib, gpu_ctx._h
+    t = oracle.Q6_K
+    for (n, k, m) in ((48, 2048, 3), (32, 14336, 8)):
+        raw = make_quant_weight(t, n, k, seed=n + k)
+        w = hq.load_quant_weight(gpu_ctx, raw, t, n, k)
+        n_total, col0 = n + 40, 24
+        ybuf, fbuf = C.c_void_p(), C.c_void_p()
+        hy, hf = (C.c_uint8 * 64)(), (C.c_uint8 * 64)()
+        gpu_ctx._check(lib.hf2q_cuda_ipc_alloc(h, m * n_total * 4, C.byref(ybuf), hy))
+        gpu_ctx._check(lib.hf2q_cuda_ipc_alloc(h, 256, C.byref(fbuf), hf))
+        g = _Gather()
+        g.y_all[0], g.flags[0] = ybuf.value, fbuf.value
+        g.n_ranks, g.rank, g.n_total, g.col0, g.wait_previous = 1, 0, n_total, col0, 1
+        xd, xs = _dev_x(make_x(m, k, seed=3), True)
+        for _ in range(2):        # the second call waits (trivially) for the first
+            gpu_ctx._check(lib.hf2q_cuda_qmatmul_gather(h, gpu_ctx._stream(), xd.data_ptr(), hq.ops.DT_BF16, w.ptr, C.byref(g),
+                                                        m, n, k, t))
+        gpu_ctx._check(lib.hf2q_cuda_gather_wait(h, gpu_ctx._stream(), fbuf.value))
+        gpu_ctx.check_status()
+        from hf2q_b200.dist import _DevView
+        y = torch.as_tensor(_DevView(ybuf.value, (m, n_total), "<f4"), device="cuda").cpu().numpy()
+        assert rel_l2(y[:, col0:col0 + n], _ref(t, raw, xs, n, k)) < 2e-5
+        assert not y[:, :col0].any() and not y[:, col0 + n:].any()          # nothing outside the rank's columns
+        lib.hf2q_cuda_free(h, ybuf.value)
+        lib.hf2q_cuda_free(h, fbuf.value)
+    # argument checks
+    g = _Gather()
+    assert lib.hf2q_cuda_qmatmul_gather(h, None, xd.data_ptr(), hq.ops.DT_BF16, w.ptr, C.byref(g), 1, n, k, t) == _lib.ERR_INVALID_ARGUMENT
