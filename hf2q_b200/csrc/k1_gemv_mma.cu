@@ -41,8 +41,11 @@
 // Needs 16-byte aligned rows and k a multiple of 256; other shapes take the fp32 kernel in
 // k1_gemv.cu.
 #include <cstdlib>
+#include <cstring>
 #include <mutex>
 #include <type_traits>
+
+#include <cuda.h>
 
 #include "common.cuh"
 #include "kernels.h"
@@ -75,6 +78,7 @@ struct MParams {
     uint32_t xpitch;       // bytes between activation rows in shared memory
     uint32_t phase_base, phase_rem;   // k-phases: the first phase_rem have phase_base + 1 slices, the rest phase_base
     uint32_t last_nblk;        // 256-element blocks in the last slice of a row
+    uint32_t use_tmap;         // != 0: a stage (16 rows x one slice) arrives with ONE 2-D tensor copy (dense launches)
     uint32_t dense_stage;      // != 0: a row is one slice and rows sit back to back in the stage, one bulk copy per stage
     uint32_t sub_groups;       // short rows (<= 4 blocks): a stage holds this many 16-row groups, one warp per (group, block)
     // fused all-gather (row-sharded weights over several GPUs); g_nranks == 0: plain store to y
@@ -454,7 +458,7 @@ __device__ __forceinline__ void build_panel(const void* x, bool x_bf16, uint32_t
 // the main loop); SUBG = false compiles out the stacked row groups of short rows; EXT = false the
 // fused all-gather and the routed pair.
 template <uint32_t TYPE, int NTEAMS, bool PHASED, bool SUBG, bool EXT>
-__global__ void __launch_bounds__((NTEAMS * TEAM + 2) * 32, 1) gemv_mma_kernel(const MParams p) {
+__global__ void __launch_bounds__((NTEAMS * TEAM + 2) * 32, 1) gemv_mma_kernel(const __grid_constant__ CUtensorMap tmap_w, const MParams p) {
     extern __shared__ __align__(128) uint8_t smem[];
     constexpr bool K45 = TYPE == HF2Q_TYPE_Q4_K || TYPE == HF2Q_TYPE_Q5_K;
     constexpr bool Q6 = TYPE == HF2Q_TYPE_Q6_K;
@@ -539,10 +543,32 @@ __global__ void __launch_bounds__((NTEAMS * TEAM + 2) * 32, 1) gemv_mma_kernel(c
                         const uint32_t off = s * p.slice_bytes;
                         const uint32_t bytes = min(p.slice_bytes, p.row_bytes - off);
 #ifdef HF2Q_MMA_PROBE
-                        if (p.debug == 2) { if (lane == 0) mbar_arrive(&full[st]); continue; }
+                        if (p.debug & 2u) { if (lane == 0) mbar_arrive(&full[st]); continue; }
 #endif
+                        if (p.use_tmap) {
+                            // one tensor copy for the whole stage: the copy engine spends ~15 cycles per copy
+                            // descriptor, which 16 per-row copies per stage made 15 % of the streaming time.
+                            // Rows past n and bytes past the row end are zero-filled and count as transferred.
+                            if (lane == 0) {
+                                mbar_arrive_expect_tx(&full[st], stage_bytes);
+                                asm volatile(
+                                    "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                                    ::"r"(smem_u32(ring + st * stage_bytes)), "l"(reinterpret_cast<uint64_t>(&tmap_w)),
+                                      "r"(static_cast<int>(s * (p.slice_bytes >> 3))), "r"(static_cast<int>(row0)), "r"(smem_u32(&full[st]))
+                                    : "memory");
+                            }
+                            continue;
+                        }
                         if (lane == 0) mbar_arrive_expect_tx(&full[st], nrows * bytes);
                         __syncwarp();
+#ifdef HF2Q_MMA_PROBE
+                        if (p.debug & 4u) {       // timing probe: the stage's bytes as ONE contiguous copy (wrong data)
+                            if (lane == 0)
+                                bulk_g2s(ring + st * stage_bytes, wbase + static_cast<uint64_t>(row0) * p.row_bytes + (s - s0) * nrows * bytes,
+                                         nrows * bytes, &full[st]);
+                            continue;
+                        }
+#endif
                         if (p.dense_stage) {
                             // whole rows, contiguous in memory and in the stage: one copy
                             if (lane == 0)
@@ -730,7 +756,7 @@ __global__ void __launch_bounds__((NTEAMS * TEAM + 2) * 32, 1) gemv_mma_kernel(c
             // short rows: the stage holds nsub groups of 16 rows and `blk` counts (group, block) pairs
             const uint32_t sgi = nsub > 1 ? blk / last_nblk : 0u, bb = nsub > 1 ? blk - sgi * last_nblk : blk;
             const uint32_t nblk = nsub > 1 ? nsub * last_nblk : (s0 + s == last_slice ? last_nblk : static_cast<uint32_t>(TEAM));
-            if (blk < nblk && dbg != 1) {
+            if (blk < nblk && !(dbg & 1u)) {
                 const uint8_t* r0 = ring_g + st * stage_bytes + sgi * (ROWS * pitch);
                 const uint8_t* r1 = r0 + 8 * pitch;
                 const uint32_t e0 = s * SLICE_ELEMS + 256 * bb;           // element index inside the panel
@@ -864,6 +890,37 @@ Plan make_plan(uint32_t type, uint32_t k, uint32_t nslots, int teams, size_t lim
     return Plan{};
 }
 
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* ptr = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(ptr);
+    });
+    return fn;
+}
+
+// Tensor map over a dense weight matrix viewed as 8-byte elements: box = one stage (16 rows x the
+// padded slice).  False if the shape does not fit a box (inner extent > 256 elements: Q8_0).
+bool make_stage_map(CUtensorMap* map, const MParams& p) {
+    EncodeTiledFn enc = encode_fn();
+    if (!enc || p.ids || p.sub_groups > 1 || p.dense_stage || p.pitch % 8 || p.pitch / 8 > 256 || p.slice_bytes % 16 || p.row_bytes % 16) return false;
+    static const bool off = [] { const char* v = getenv("HF2Q_CUDA_MMA_TMAP"); return v && v[0] == '0'; }();      // tuning aid
+    if (off) return false;
+    cuuint64_t dims[2] = {p.row_bytes / 8, p.n};
+    cuuint64_t strides[1] = {p.row_bytes};
+    cuuint32_t box[2] = {p.pitch / 8, ROWS};
+    cuuint32_t es[2] = {1, 1};
+    return enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT64, 2, const_cast<uint8_t*>(p.w), dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
+               CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 template <uint32_t TYPE, int NTEAMS, bool PHASED, bool SUBG, bool EXT>
 cudaError_t launch_mma_tt(MParams p, uint32_t slots, const Plan& pl, const DeviceInfo& dev, cudaStream_t st) {
     auto kern = gemv_mma_kernel<TYPE, NTEAMS, PHASED, SUBG, EXT>;
@@ -897,7 +954,10 @@ cudaError_t launch_mma_tt(MParams p, uint32_t slots, const Plan& pl, const Devic
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = pdl ? 1 : 0;
-    return cudaLaunchKernelEx(&cfg, kern, p);
+    alignas(64) CUtensorMap tmap;
+    memset(&tmap, 0, sizeof tmap);
+    p.use_tmap = make_stage_map(&tmap, p) ? 1u : 0u;
+    return cudaLaunchKernelEx(&cfg, kern, tmap, p);
 }
 
 template <uint32_t TYPE>
