@@ -323,10 +323,12 @@ __device__ __forceinline__ void half_legacy(const uint8_t* p0, const uint8_t* p1
 // to U columns per round; lanes holding the same sub-block combine their sums by shuffle (a warp's
 // 32 threads cover 256 consecutive elements).  f32 input yields two columns per activation row:
 // hi = f16(x) and lo = f16(x - hi).  Values beyond the f16 range are clamped and flagged.
-template <uint32_t TYPE, int CTH, int U>
+// INPLACE (bf16 input, used by the k-phase variant, whose main loop leaves no registers for loads in
+// flight): the raw rows are bulk-copied into the panel's own place and converted there.
+template <uint32_t TYPE, int CTH, int U, bool INPLACE>
 __device__ __forceinline__ void build_panel(const void* x, bool x_bf16, uint32_t nslots, uint32_t k, uint32_t xpitch,
                                          uint32_t* status, uint8_t* xh, uint8_t* sxp, uint32_t sx_slot_bytes,
-                                         uint32_t xrow_idx, uint32_t k0, uint32_t klen) {
+                                         uint32_t xrow_idx, uint32_t k0, uint32_t klen, uint64_t* xbar, uint32_t xparity) {
     constexpr bool K45 = TYPE == HF2Q_TYPE_Q4_K || TYPE == HF2Q_TYPE_Q5_K;
     constexpr bool LEG = TYPE == HF2Q_TYPE_Q4_0 || TYPE == HF2Q_TYPE_Q8_0;
     constexpr uint32_t SXB = K45 ? 32 : 64;
@@ -395,7 +397,19 @@ __device__ __forceinline__ void build_panel(const void* x, bool x_bf16, uint32_t
             }
         }
     };
-    if (x_bf16) {
+    if (x_bf16 && INPLACE) {
+        // bf16 and f16 are both two bytes: the raw rows are bulk-copied into the panel's own place
+        // (one asynchronous copy per column, all in flight at once) and converted there
+        if (ctid < nslots) {
+            if (ctid == 0) mbar_arrive_expect_tx(xbar, nslots * klen * 2);
+            __syncwarp(__activemask());
+            bulk_g2s(xh + ctid * xpitch, static_cast<const __nv_bfloat16*>(x) + (static_cast<size_t>(xrow_idx) + ctid) * k + k0, klen * 2, xbar);
+        }
+        if (!mbar_wait_bounded(xbar, xparity, status)) return;
+        for (uint32_t pos = ctid; pos < k8; pos += CTH)
+            for (uint32_t sl = 0; sl < nslots; ++sl)
+                convert_bf16(*reinterpret_cast<const uint4*>(xh + sl * xpitch + 16 * pos), sl, pos);
+    } else if (x_bf16) {
         if constexpr (U >= 8) {
             if (k8 <= CTH) bf16_rounds(std::integral_constant<int, 8>{}, std::integral_constant<int, 1>{});
             else if (nslots <= 2) bf16_rounds(std::integral_constant<int, 2>{}, std::integral_constant<int, 4>{});
@@ -474,6 +488,7 @@ __global__ void __launch_bounds__((NTEAMS * TEAM + 2) * 32, 1) gemv_mma_kernel(c
     uint64_t* empty = full + MAX_STAGES;
     uint64_t* red_full = empty + MAX_STAGES;
     uint64_t* red_empty = red_full + 2;
+    uint64_t* xbar = red_empty + 2;                    // completion of the activation rows' bulk copies
     uint8_t* ring = smem + 256;
     const uint32_t stages = p.stages, pitch = p.pitch, nslices = p.nslices;
     const uint32_t spp = p.phase_base + (p.phase_rem ? 1u : 0u);              // slices of the longest phase
@@ -680,6 +695,10 @@ __global__ void __launch_bounds__((NTEAMS * TEAM + 2) * 32, 1) gemv_mma_kernel(c
     // ---------------- consumers ----------------
     const int ctid = threadIdx.x;
     asm volatile("griddepcontrol.wait;" ::: "memory");                    // before reading x / writing y
+    if constexpr (PHASED) {
+        if (ctid == 0) { mbar_init(xbar, 1); mbar_fence_init(); }
+        asm volatile("bar.sync 1, %0;" ::"n"(CTH));
+    }
     if (!slot_ok) {
         __syncthreads();
         for (uint32_t r = ctid; r < p.n; r += CTH) yout[r] = 0.f;
@@ -731,8 +750,8 @@ __global__ void __launch_bounds__((NTEAMS * TEAM + 2) * 32, 1) gemv_mma_kernel(c
             }
             asm volatile("bar.sync 1, %0;" ::"n"(CTH));
         }
-        build_panel<TYPE, CTH, (PHASED ? 2 : 8)>(p.x, p.x_bf16 != 0, p.nslots, p.k, p.xpitch, p.status, xh, sxp, sx_slot_bytes, xrow_idx, k0,
-                               min(nsp * SLICE_ELEMS, p.k - k0));
+        build_panel<TYPE, CTH, (PHASED ? 2 : 8), PHASED>(p.x, p.x_bf16 != 0, p.nslots, p.k, p.xpitch, p.status, xh, sxp, sx_slot_bytes, xrow_idx, k0,
+                               min(nsp * SLICE_ELEMS, p.k - k0), xbar, pi & 1u);
         if (s0 == 0) __syncthreads();                                    // panel + all barrier initialisations
         else asm volatile("bar.sync 1, %0;" ::"n"(CTH));
         if (threadIdx.x == 0 && s0 == 0) PROBE_STAMP(2);
@@ -861,13 +880,14 @@ struct Plan {
     size_t smem = 0;
 };
 // Fewest phases (of nslices / phases slices, the first nslices % phases one longer, none shorter
-// than `teams` unless the row is) whose activation panel leaves room for a ring of teams + 3
-// stages: each team holds one stage while three are in flight.  Failing that, teams + 2, teams + 1.
+// than `teams` unless the row is) whose activation panel leaves room for a ring of teams + 2
+// stages: each team holds one stage while two are in flight (measured: fewer phases beat a deeper
+// ring).  Failing that, teams + 1.
 Plan make_plan(uint32_t type, uint32_t k, uint32_t nslots, int teams, size_t limit) {
     const uint32_t nslices = (k + SLICE_ELEMS - 1) / SLICE_ELEMS;
     const size_t stage = stage_bytes_of(type, k);
-    static const uint32_t min_spare = static_cast<uint32_t>(env_int("HF2Q_CUDA_MMA_MINSPARE", 1));   // tuning aid
-    for (uint32_t spare = 3; spare >= min_spare && spare >= 1; --spare) {
+    static const uint32_t first_spare = static_cast<uint32_t>(env_int("HF2Q_CUDA_MMA_SPARE", 2));   // tuning aid
+    for (uint32_t spare = first_spare; spare >= 1; --spare) {
         for (uint32_t phases = 1; phases <= nslices; ++phases) {
             const uint32_t base = nslices / phases, rem = nslices % phases;
             if (phases > 1 && base < static_cast<uint32_t>(teams)) break;
