@@ -55,6 +55,7 @@ namespace hf2q {
 namespace {
 
 constexpr int ROWS = 16;               // weight rows per stage = rows of one MMA tile
+constexpr uint32_t PRE_STAGES = 3;     // ring stages requested before the previous kernel has completed
 constexpr int TEAM = 8;                // consumer warps per stage: one per 256-element block
 constexpr int MAX_TEAMS = 3;
 constexpr int SLICE_ELEMS = 2048;
@@ -104,6 +105,20 @@ __device__ __forceinline__ void probe_stamp(const MParams& p, int ev) {
 #else
 #define PROBE_STAMP(ev)
 #endif
+
+// The one CTA-wide barrier (id 0).  The producer warp arrives and carries on, the other warps
+// wait.  Every participant names the thread count: a barrier whose participants disagree on the
+// count (as the count-less form would once the producer warp has exited) is an error; and the warp
+// must be converged, which the producer's per-lane copy loops do not guarantee by themselves.
+template <int NTHREADS>
+__device__ __forceinline__ void cta_arrive_n() {
+    __syncwarp();
+    asm volatile("bar.arrive 0, %0;" ::"n"(NTHREADS) : "memory");
+}
+template <int NTHREADS>
+__device__ __forceinline__ void cta_sync_n() {
+    asm volatile("bar.sync 0, %0;" ::"n"(NTHREADS) : "memory");
+}
 
 // m16n8k16, f16 inputs, f32 accumulate.  Lane (g = lane/4, t = lane%4) holds A for rows g (a0, a2)
 // and g+8 (a1, a3) at k-columns {2t, 2t+1} (a0, a1) and {2t+8, 2t+9} (a2, a3); B for column g at
@@ -547,9 +562,16 @@ __global__ void __launch_bounds__((NTEAMS * TEAM + 2) * 32, 1) gemv_mma_kernel(c
                     const uint32_t row0 = rg * stage_rows;
                     const uint32_t nrows = min(stage_rows, p.n - row0);
                     for (uint32_t s = s0; s < s1; ++s, ++it, st = (st + 1 == stages ? 0 : st + 1), ph ^= (st == 0)) {
-                        // the copies of the first stage are on their way: meet the other warps (a
-                        // bulk copy can hold its issuing thread while the copy queue is full)
-                        if (it == 1) { __syncthreads(); synced = true; }
+                        // The copies of the first stage are on their way: tell the other warps that the
+                        // ring's barriers exist, WITHOUT waiting for them -- the consumers may sit in
+                        // their dependency wait for microseconds, which is when the ring should fill.
+                        if (it == 1) { cta_arrive_n<(NTEAMS * TEAM + 2) * 32>(); synced = true; }
+                        // Ahead of the previous kernel's completion only PRE_STAGES stages are requested:
+                        // enough for both teams to start at once, while a whole ring per CTA, requested
+                        // by the CTAs that start last, was measured to delay the completion itself (and
+                        // with it every CTA's activation panel) by ~1.4 us on long launches.  The wait also
+                        // means that the bounded waits below only ever measure this kernel's own consumers.
+                        if (it == PRE_STAGES) asm volatile("griddepcontrol.wait;" ::: "memory");
                         if (it >= stages) {
                             bool alive = mbar_wait_bounded(&empty[st], ph, p.status);
                             alive = __all_sync(0xffffffffu, alive);
@@ -599,18 +621,18 @@ __global__ void __launch_bounds__((NTEAMS * TEAM + 2) * 32, 1) gemv_mma_kernel(c
             }
             if (lane == 0) PROBE_STAMP(6);
         }
-        if (!synced) __syncthreads();
+        if (!synced) cta_arrive_n<(NTEAMS * TEAM + 2) * 32>();
         return;
     }
     if (warp == CW + 1) {
-        // ---------------- reducer warp: lane sums outputs lane, lane+32, lane+64, lane+96 of the
-        // [16 rows][8 columns] tile over the teams that worked on the group, in team order
+        // ---------------- reducer warp: lane sums outputs 4*lane .. 4*lane+3 of the [16 rows][8 columns]
+        // tile (row lane/2, columns 4*(lane%2)..+3) over the teams that worked on the group, in team order
         const uint32_t nteams = nslices < NTEAMS ? nslices : NTEAMS;      // every phase has at least NTEAMS slices
         if (lane == 0) {                                                  // unless the whole row has fewer
             for (int i = 0; i < 2; ++i) { mbar_init(&red_full[i], nteams * TEAM); mbar_init(&red_empty[i], 1); }
             mbar_fence_init();
         }
-        __syncthreads();
+        cta_sync_n<(NTEAMS * TEAM + 2) * 32>();
         if (!slot_ok) return;
         asm volatile("griddepcontrol.wait;" ::: "memory");                // before the first store to y
         uint32_t fl = 0, first = 0;                   // flush counter; team of the group's first stage
@@ -619,22 +641,23 @@ __global__ void __launch_bounds__((NTEAMS * TEAM + 2) * 32, 1) gemv_mma_kernel(c
             for (uint32_t rg = blockIdx.x; rg < p.ngroups; rg += gridDim.x, ++fl, first = (first + nsp) % NTEAMS) {
                 const uint32_t rs = fl & 1;
                 if (!mbar_wait_bounded(&red_full[rs], (fl >> 1) & 1, p.status)) return;
+                if (lane == 0) PROBE_STAMP(7);
                 // partial sums sit at [team][block of the stage]; a sub-group's blocks are adjacent
                 const uint32_t nb = nsub > 1 ? p.last_nblk : static_cast<uint32_t>(TEAM);
                 for (uint32_t sg = 0; sg < nsub; ++sg) {
                     float v[4] = {0.f, 0.f, 0.f, 0.f};
                     for (uint32_t i = 0, tm = first; i < nteams; ++i, tm = (tm + 1 == NTEAMS ? 0 : tm + 1)) {
-                        const float* rbuf = red + (rs * CW + tm * TEAM + sg * nb) * 128 + lane;
+                        const float4* rbuf = reinterpret_cast<const float4*>(red + (rs * CW + tm * TEAM + sg * nb) * 128) + lane;
                         if (nsub == 1) {
 #pragma unroll
                             for (int w = 0; w < TEAM; ++w) {
-#pragma unroll
-                                for (int j = 0; j < 4; ++j) v[j] += rbuf[w * 128 + 32 * j];
+                                const float4 a = rbuf[w * 32];
+                                v[0] += a.x; v[1] += a.y; v[2] += a.z; v[3] += a.w;
                             }
                         } else {
                             for (uint32_t w = 0; w < nb; ++w) {
-#pragma unroll
-                                for (int j = 0; j < 4; ++j) v[j] += rbuf[w * 128 + 32 * j];
+                                const float4 a = rbuf[w * 32];
+                                v[0] += a.x; v[1] += a.y; v[2] += a.z; v[3] += a.w;
                             }
                         }
                     }
@@ -642,17 +665,17 @@ __global__ void __launch_bounds__((NTEAMS * TEAM + 2) * 32, 1) gemv_mma_kernel(c
                         __syncwarp();
                         if (lane == 0) mbar_arrive(&red_empty[rs]);
                     }
-                    const uint32_t c = lane & 7;
+                    const uint32_t row = rg * stage_rows + sg * ROWS + (lane >> 1);
+                    if (!p.x_bf16) {                                         // (hi, lo) column pairs
+                        v[0] += v[1];
+                        v[1] = v[2] + v[3];
+                    }
+                    const uint32_t ncol = p.x_bf16 ? 4u : 2u, tok0 = (lane & 1u) * ncol;
 #pragma unroll
                     for (int j = 0; j < 4; ++j) {
-                        const uint32_t row = rg * stage_rows + sg * ROWS + (lane >> 3) + 4 * j;
-                        float out = v[j];
-                        uint32_t tok = c;
-                        if (!p.x_bf16) {                                     // hi + lo column
-                            out += __shfl_xor_sync(0xffffffffu, out, 1);
-                            tok = (c & 1) ? 0xffffffffu : c >> 1;
-                        }
-                        if (row < p.n && tok < p.m) {
+                        const uint32_t tok = tok0 + j;
+                        const float out = v[j];
+                        if (static_cast<uint32_t>(j) < ncol && row < p.n && tok < p.m) {
                             if (!EXT || p.g_nranks == 0) {
                                 float* dst = yout + static_cast<size_t>(tok) * p.n + row;
                                 *dst = s0 ? *dst + out : out;
@@ -700,7 +723,7 @@ __global__ void __launch_bounds__((NTEAMS * TEAM + 2) * 32, 1) gemv_mma_kernel(c
         asm volatile("bar.sync 1, %0;" ::"n"(CTH));
     }
     if (!slot_ok) {
-        __syncthreads();
+        cta_sync_n<(NTEAMS * TEAM + 2) * 32>();
         for (uint32_t r = ctid; r < p.n; r += CTH) yout[r] = 0.f;
         return;
     }
@@ -752,17 +775,32 @@ __global__ void __launch_bounds__((NTEAMS * TEAM + 2) * 32, 1) gemv_mma_kernel(c
         }
         build_panel<TYPE, CTH, (PHASED ? 2 : 8), PHASED>(p.x, p.x_bf16 != 0, p.nslots, p.k, p.xpitch, p.status, xh, sxp, sx_slot_bytes, xrow_idx, k0,
                                min(nsp * SLICE_ELEMS, p.k - k0), xbar, pi & 1u);
-        if (s0 == 0) __syncthreads();                                    // panel + all barrier initialisations
+        if (s0 == 0) cta_sync_n<(NTEAMS * TEAM + 2) * 32>();             // panel + all barrier initialisations
         else asm volatile("bar.sync 1, %0;" ::"n"(CTH));
         if (threadIdx.x == 0 && s0 == 0) PROBE_STAMP(2);
 
         // Stages of this phase are numbered it0 .. it0 + gcta * nsp - 1 (group-major); this team
-        // owns those with index = team (mod NTEAMS); stage i sits in ring slot i % stages.
+        // owns those with index = team (mod NTEAMS); stage i sits in ring slot i % stages.  (No
+        // divisions in the common cases: their latency sits between the panel barrier and the
+        // first block.)
         const uint32_t it0 = gcta * s0;
-        uint32_t rel = (team + NTEAMS - it0 % NTEAMS) % NTEAMS;          // first own stage, relative to it0
-        uint32_t grp = rel / nsp, s = rel - grp * nsp;
-        uint32_t st = (it0 + rel) % stages, ph = ((it0 + rel) / stages) & 1u;
-        const uint32_t step_s = NTEAMS % nsp, step_g = NTEAMS / nsp;
+        const uint32_t rel = (team + NTEAMS - it0 % NTEAMS) % NTEAMS;    // first own stage, relative to it0
+        uint32_t grp, s, st, ph, step_s, step_g;
+        if constexpr (NTEAMS == 2) {                                     // rel is 0 or 1
+            const bool one = nsp == 1;
+            grp = one ? rel : 0u;
+            s = one ? 0u : rel;
+        } else {
+            grp = rel / nsp; s = rel - grp * nsp;
+        }
+        step_s = NTEAMS % nsp; step_g = NTEAMS / nsp;
+        if constexpr (PHASED) {
+            st = (it0 + rel) % stages; ph = ((it0 + rel) / stages) & 1u;
+        } else {                                                         // it0 = 0 and rel < NTEAMS <= 2 * stages
+            const bool wrap = rel >= stages;
+            st = wrap ? rel - stages : rel;
+            ph = wrap ? 1u : 0u;
+        }
         float f[4] = {0.f, 0.f, 0.f, 0.f};
         while (grp < gcta) {
             if (!mbar_wait_bounded(&full[st], ph, p.status)) return;
@@ -826,6 +864,7 @@ __global__ void __launch_bounds__((NTEAMS * TEAM + 2) * 32, 1) gemv_mma_kernel(c
         }
     }
     if (threadIdx.x == 0) PROBE_STAMP(4);
+    if (threadIdx.x == CTH - 32) PROBE_STAMP(1);
 }
 
 // shared memory that does not depend on the ring depth; kphase = elements of k resident at a time
