@@ -79,6 +79,7 @@ struct MParams {
     uint32_t xpitch;       // bytes between activation rows in shared memory
     uint32_t phase_base, phase_rem;   // k-phases: the first phase_rem have phase_base + 1 slices, the rest phase_base
     uint32_t last_nblk;        // 256-element blocks in the last slice of a row
+    uint32_t w_evict_first;    // != 0: weight copies carry the L2 evict-first policy
     uint32_t use_tmap;         // != 0: a stage (16 rows x one slice) arrives with ONE 2-D tensor copy (dense launches)
     uint32_t dense_stage;      // != 0: a row is one slice and rows sit back to back in the stage, one bulk copy per stage
     uint32_t sub_groups;       // short rows (<= 4 blocks): a stage holds this many 16-row groups, one warp per (group, block)
@@ -555,6 +556,9 @@ __global__ void __launch_bounds__((NTEAMS * TEAM + 2) * 32, 1) gemv_mma_kernel(c
         __syncwarp();
         bool synced = false;
         if (slot_ok) {
+            // weight bytes are read once per launch: first in line for eviction, so that streaming them
+            // leaves activations and outputs (which the next launches re-read) in L2
+            const uint64_t wpolicy = p.w_evict_first ? l2_policy_evict_first() : l2_policy_evict_normal();
             uint32_t it = 0, st = 0, ph = 1;      // ring slot and the parity of its previous use
             for (uint32_t s0 = 0, pi = 0; s0 < nslices; ++pi) {
                 const uint32_t s1 = s0 + p.phase_base + (pi < p.phase_rem ? 1u : 0u);
@@ -589,9 +593,10 @@ __global__ void __launch_bounds__((NTEAMS * TEAM + 2) * 32, 1) gemv_mma_kernel(c
                             if (lane == 0) {
                                 mbar_arrive_expect_tx(&full[st], stage_bytes);
                                 asm volatile(
-                                    "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                                    "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%2, %3}], [%4], %5;"
                                     ::"r"(smem_u32(ring + st * stage_bytes)), "l"(reinterpret_cast<uint64_t>(&tmap_w)),
-                                      "r"(static_cast<int>(s * (p.slice_bytes >> 3))), "r"(static_cast<int>(row0)), "r"(smem_u32(&full[st]))
+                                      "r"(static_cast<int>(s * (p.slice_bytes >> 3))), "r"(static_cast<int>(row0)), "r"(smem_u32(&full[st])),
+                                      "l"(wpolicy)
                                     : "memory");
                             }
                             continue;
@@ -609,11 +614,11 @@ __global__ void __launch_bounds__((NTEAMS * TEAM + 2) * 32, 1) gemv_mma_kernel(c
                         if (p.dense_stage) {
                             // whole rows, contiguous in memory and in the stage: one copy
                             if (lane == 0)
-                                bulk_g2s(ring + st * stage_bytes, wbase + static_cast<uint64_t>(row0) * p.row_bytes, nrows * bytes, &full[st]);
+                                bulk_g2s_hint(ring + st * stage_bytes, wbase + static_cast<uint64_t>(row0) * p.row_bytes, nrows * bytes, &full[st], wpolicy);
                         } else {
                             for (uint32_t rr = lane; rr < nrows; rr += 32)
-                                bulk_g2s(ring + st * stage_bytes + rr * pitch,
-                                         wbase + static_cast<uint64_t>(row0 + rr) * p.row_bytes + off, bytes, &full[st]);
+                                bulk_g2s_hint(ring + st * stage_bytes + rr * pitch,
+                                              wbase + static_cast<uint64_t>(row0 + rr) * p.row_bytes + off, bytes, &full[st], wpolicy);
                         }
                     }
                 }
@@ -1015,6 +1020,8 @@ cudaError_t launch_mma_tt(MParams p, uint32_t slots, const Plan& pl, const Devic
     cfg.numAttrs = pdl ? 1 : 0;
     alignas(64) CUtensorMap tmap;
     memset(&tmap, 0, sizeof tmap);
+    static const bool evict_first = env_int("HF2Q_CUDA_MMA_EVICT_FIRST", 1) != 0;      // tuning aid
+    p.w_evict_first = evict_first ? 1u : 0u;
     p.use_tmap = make_stage_map(&tmap, p) ? 1u : 0u;
     return cudaLaunchKernelEx(&cfg, kern, tmap, p);
 }
