@@ -110,10 +110,12 @@ int32_t run_matvec(hf2q_ctx* ctx, cudaStream_t st, GemvArgs a, uint32_t m_total,
     const bool use_mma = mma && gemv_mma_max_rows(a.type, a.k, a.x_dtype, ctx->dev) > 0;
     const uint8_t* x0 = static_cast<const uint8_t*>(a.x);
     float* y0 = a.y;
+    const float* r0 = a.residual;
     for (uint32_t m0 = 0; m0 < m_total; m0 += step) {
         a.m = (m_total - m0) < step ? (m_total - m0) : step;
         a.x = x0 + static_cast<size_t>(m0) * a.k * xs;
         a.y = y0 + static_cast<size_t>(m0) * a.n;
+        if (r0) a.residual = r0 + static_cast<size_t>(m0) * a.n;
         cudaError_t e;
         int nl = 1;
         if (use_mma) e = launch_gemv_mma(a, ctx->dev, st);
@@ -319,6 +321,75 @@ HF2Q_API int32_t hf2q_cuda_qmatmul(hf2q_ctx* ctx, void* stream, const void* x, u
     a.slots = 1; a.top_k = 1; a.n_experts = 0;
     a.status = ctx->status;
     return run_matvec(ctx, st, a, m, "qmatmul launch");
+}
+
+// ---- dense FFN fusions: SwiGLU in the gate/up launch, residual add in the down launch ----
+// (the reference's dense builder issues gate, up, dispatch_silu_mul, down and an optional
+// elementwise_add of the residual: src/inference/models/qwen35/gpu_ffn.rs:896-960)
+
+HF2Q_API int32_t hf2q_cuda_qmatmul_swiglu_supported(hf2q_ctx* ctx, uint32_t m, uint32_t n, uint32_t k, uint32_t type, uint32_t x_dtype) {
+    if (!ctx || !type_supported(type) || n == 0 || k == 0 || ctx->fp32_matvec) return 0;
+    const BlockGeom g = block_geom(type);
+    if (k % g.elems || (static_cast<uint64_t>(k) / g.elems * g.bytes) % 16) return 0;
+    return gemv_mma_swiglu_ok(type, k, m, x_dtype, ctx->dev) ? 1 : 0;
+}
+
+HF2Q_API int32_t hf2q_cuda_qmatmul_swiglu(hf2q_ctx* ctx, void* stream, const void* x, uint32_t x_dtype, const void* w_gate,
+                                          const void* w_up, float* y, uint32_t m, uint32_t n, uint32_t k, uint32_t type) {
+    if (!ctx) return HF2Q_ERR_INVALID_ARGUMENT;
+    if (!x || !w_gate || !w_up || !y) return fail(ctx, HF2Q_ERR_INVALID_ARGUMENT, "qmatmul_swiglu: null pointer");
+    if (x_dtype != HF2Q_DT_F32 && x_dtype != HF2Q_DT_BF16) return fail(ctx, HF2Q_ERR_INVALID_ARGUMENT, "qmatmul_swiglu: x_dtype %u (want F32 or BF16)", x_dtype);
+    int32_t rc = check_matmul_shape(ctx, type, n, k, "qmatmul_swiglu");
+    if (rc) return rc;
+    if (m == 0) return HF2Q_OK;
+    GemvArgs a{};
+    a.w = w_gate; a.w2 = w_up; a.x = x; a.y = y;
+    a.x_dtype = x_dtype; a.type = type;
+    a.m = m; a.n = n; a.k = k;
+    a.slots = 1; a.top_k = 1; a.n_experts = 0;
+    a.swiglu = true;
+    a.status = ctx->status;
+    GemvArgs up = a;
+    up.w = w_up;
+    if (!hf2q_cuda_qmatmul_swiglu_supported(ctx, m, n, k, type, x_dtype) || !gemv_mma_supported(a) || !gemv_mma_supported(up))
+        return fail(ctx, HF2Q_ERR_INVALID_ARGUMENT,
+                    "qmatmul_swiglu: m=%u k=%u does not fit one fused launch (ask hf2q_cuda_qmatmul_swiglu_supported; needs 16-byte aligned rows, "
+                    "k %% 256 == 0, k > 1024 and all activations resident)", m, k);
+    DeviceGuard dg(ctx->device);
+    const cudaError_t e = launch_gemv_mma(a, ctx->dev, static_cast<cudaStream_t>(stream));
+    if (e != cudaSuccess) return cuda_fail(ctx, e, "qmatmul_swiglu launch");
+    ctx->launches += 1;
+    return HF2Q_OK;
+}
+
+HF2Q_API int32_t hf2q_cuda_qmatmul_add_supported(hf2q_ctx* ctx, uint32_t n, uint32_t k, uint32_t type, uint32_t x_dtype) {
+    if (!ctx || !type_supported(type) || n == 0 || k == 0 || ctx->fp32_matvec) return 0;
+    const BlockGeom g = block_geom(type);
+    if (k % 256 || (static_cast<uint64_t>(k) / g.elems * g.bytes) % 16) return 0;
+    return gemv_mma_max_rows(type, k, x_dtype, ctx->dev) > 0 ? 1 : 0;
+}
+
+HF2Q_API int32_t hf2q_cuda_qmatmul_add(hf2q_ctx* ctx, void* stream, const void* x, uint32_t x_dtype, const void* w,
+                                       const float* residual, float* y, uint32_t m, uint32_t n, uint32_t k, uint32_t type) {
+    if (!ctx) return HF2Q_ERR_INVALID_ARGUMENT;
+    if (!x || !w || !y || !residual) return fail(ctx, HF2Q_ERR_INVALID_ARGUMENT, "qmatmul_add: null pointer");
+    if (x_dtype != HF2Q_DT_F32 && x_dtype != HF2Q_DT_BF16) return fail(ctx, HF2Q_ERR_INVALID_ARGUMENT, "qmatmul_add: x_dtype %u (want F32 or BF16)", x_dtype);
+    int32_t rc = check_matmul_shape(ctx, type, n, k, "qmatmul_add");
+    if (rc) return rc;
+    if (m == 0) return HF2Q_OK;
+    if (reinterpret_cast<uintptr_t>(residual) % 4 || reinterpret_cast<uintptr_t>(y) % 4)
+        return fail(ctx, HF2Q_ERR_INVALID_ARGUMENT, "qmatmul_add: misaligned buffer");
+    GemvArgs a{};
+    a.w = w; a.x = x; a.y = y;
+    a.x_dtype = x_dtype; a.type = type;
+    a.n = n; a.k = k;
+    a.slots = 1; a.top_k = 1; a.n_experts = 0;
+    a.status = ctx->status;
+    a.residual = residual;
+    if (ctx->fp32_matvec || !gemv_mma_supported(a) || gemv_mma_max_rows(type, k, x_dtype, ctx->dev) == 0)
+        return fail(ctx, HF2Q_ERR_INVALID_ARGUMENT, "qmatmul_add: needs the warp-MMA mat-vec (16-byte aligned rows, k %% 256 == 0)");
+    DeviceGuard dg(ctx->device);
+    return run_matvec(ctx, static_cast<cudaStream_t>(stream), a, m, "qmatmul_add launch");
 }
 
 // ---- row-sharded mat-vec with the all-gather in its epilogue (several GPUs, one process each) ----

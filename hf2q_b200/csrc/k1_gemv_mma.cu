@@ -80,6 +80,8 @@ struct MParams {
     uint32_t phase_base, phase_rem;   // k-phases: the first phase_rem have phase_base + 1 slices, the rest phase_base
     uint32_t last_nblk;        // 256-element blocks in the last slice of a row
     uint32_t w_evict_first;    // != 0: weight copies carry the L2 evict-first policy
+    uint32_t swiglu;           // != 0 (EXT): w = gate, w2 = up; a CTA's row groups alternate gate, up and y = silu(gate) * up
+    const float* residual;     // != nullptr: y = residual + product (may alias y)
     uint32_t use_tmap;         // != 0: a stage (16 rows x one slice) arrives with ONE 2-D tensor copy (dense launches)
     uint32_t dense_stage;      // != 0: a row is one slice and rows sit back to back in the stage, one bulk copy per stage
     uint32_t sub_groups;       // short rows (<= 4 blocks): a stage holds this many 16-row groups, one warp per (group, block)
@@ -488,7 +490,8 @@ __device__ __forceinline__ void build_panel(const void* x, bool x_bf16, uint32_t
 // the main loop); SUBG = false compiles out the stacked row groups of short rows; EXT = false the
 // fused all-gather and the routed pair.
 template <uint32_t TYPE, int NTEAMS, bool PHASED, bool SUBG, bool EXT>
-__global__ void __launch_bounds__((NTEAMS * TEAM + 2) * 32, 1) gemv_mma_kernel(const __grid_constant__ CUtensorMap tmap_w, const MParams p) {
+__global__ void __launch_bounds__((NTEAMS * TEAM + 2) * 32, 1) gemv_mma_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_w2,
+                                                                               const MParams p) {
     extern __shared__ __align__(128) uint8_t smem[];
     constexpr bool K45 = TYPE == HF2Q_TYPE_Q4_K || TYPE == HF2Q_TYPE_Q5_K;
     constexpr bool Q6 = TYPE == HF2Q_TYPE_Q6_K;
@@ -535,7 +538,10 @@ __global__ void __launch_bounds__((NTEAMS * TEAM + 2) * 32, 1) gemv_mma_kernel(c
     }
     float* yout = ybase + static_cast<size_t>(slot) * p.n;
     // row groups of this CTA: blockIdx.x, blockIdx.x + gridDim.x, ...
-    const uint32_t gcta = blockIdx.x < p.ngroups ? (p.ngroups - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+    const uint32_t own = blockIdx.x < p.ngroups ? (p.ngroups - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+    // fused SwiGLU: every row group is walked twice in a row, first in the gate matrix, then in the up matrix
+    const bool sw = EXT && p.swiglu;
+    const uint32_t gcta = sw ? 2 * own : own;
 
     // Programmatic dependent launch: let the next kernel of the stream start its own prologue as soon
     // as SMs free up, and do not touch anything an earlier kernel may still be writing (activations,
@@ -562,7 +568,11 @@ __global__ void __launch_bounds__((NTEAMS * TEAM + 2) * 32, 1) gemv_mma_kernel(c
             uint32_t it = 0, st = 0, ph = 1;      // ring slot and the parity of its previous use
             for (uint32_t s0 = 0, pi = 0; s0 < nslices; ++pi) {
                 const uint32_t s1 = s0 + p.phase_base + (pi < p.phase_rem ? 1u : 0u);
-                for (uint32_t rg = blockIdx.x; rg < p.ngroups; rg += gridDim.x) {
+                for (uint32_t gi = 0; gi < gcta; ++gi) {
+                    const uint32_t rg = blockIdx.x + (sw ? gi >> 1 : gi) * gridDim.x;
+                    const bool second = sw && (gi & 1u);
+                    const uint8_t* wsrc = second ? p.w2 : wbase;
+                    const CUtensorMap* tmap = second ? &tmap_w2 : &tmap_w;
                     const uint32_t row0 = rg * stage_rows;
                     const uint32_t nrows = min(stage_rows, p.n - row0);
                     for (uint32_t s = s0; s < s1; ++s, ++it, st = (st + 1 == stages ? 0 : st + 1), ph ^= (st == 0)) {
@@ -594,7 +604,7 @@ __global__ void __launch_bounds__((NTEAMS * TEAM + 2) * 32, 1) gemv_mma_kernel(c
                                 mbar_arrive_expect_tx(&full[st], stage_bytes);
                                 asm volatile(
                                     "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%2, %3}], [%4], %5;"
-                                    ::"r"(smem_u32(ring + st * stage_bytes)), "l"(reinterpret_cast<uint64_t>(&tmap_w)),
+                                    ::"r"(smem_u32(ring + st * stage_bytes)), "l"(reinterpret_cast<uint64_t>(tmap)),
                                       "r"(static_cast<int>(s * (p.slice_bytes >> 3))), "r"(static_cast<int>(row0)), "r"(smem_u32(&full[st])),
                                       "l"(wpolicy)
                                     : "memory");
@@ -606,7 +616,7 @@ __global__ void __launch_bounds__((NTEAMS * TEAM + 2) * 32, 1) gemv_mma_kernel(c
 #ifdef HF2Q_MMA_PROBE
                         if (p.debug & 4u) {       // timing probe: the stage's bytes as ONE contiguous copy (wrong data)
                             if (lane == 0)
-                                bulk_g2s(ring + st * stage_bytes, wbase + static_cast<uint64_t>(row0) * p.row_bytes + (s - s0) * nrows * bytes,
+                                bulk_g2s(ring + st * stage_bytes, wsrc + static_cast<uint64_t>(row0) * p.row_bytes + (s - s0) * nrows * bytes,
                                          nrows * bytes, &full[st]);
                             continue;
                         }
@@ -614,11 +624,11 @@ __global__ void __launch_bounds__((NTEAMS * TEAM + 2) * 32, 1) gemv_mma_kernel(c
                         if (p.dense_stage) {
                             // whole rows, contiguous in memory and in the stage: one copy
                             if (lane == 0)
-                                bulk_g2s_hint(ring + st * stage_bytes, wbase + static_cast<uint64_t>(row0) * p.row_bytes, nrows * bytes, &full[st], wpolicy);
+                                bulk_g2s_hint(ring + st * stage_bytes, wsrc + static_cast<uint64_t>(row0) * p.row_bytes, nrows * bytes, &full[st], wpolicy);
                         } else {
                             for (uint32_t rr = lane; rr < nrows; rr += 32)
                                 bulk_g2s_hint(ring + st * stage_bytes + rr * pitch,
-                                              wbase + static_cast<uint64_t>(row0 + rr) * p.row_bytes + off, bytes, &full[st], wpolicy);
+                                              wsrc + static_cast<uint64_t>(row0 + rr) * p.row_bytes + off, bytes, &full[st], wpolicy);
                         }
                     }
                 }
@@ -641,9 +651,12 @@ __global__ void __launch_bounds__((NTEAMS * TEAM + 2) * 32, 1) gemv_mma_kernel(c
         if (!slot_ok) return;
         asm volatile("griddepcontrol.wait;" ::: "memory");                // before the first store to y
         uint32_t fl = 0, first = 0;                   // flush counter; team of the group's first stage
+        float gate[4] = {0.f, 0.f, 0.f, 0.f};         // fused SwiGLU: the gate sums wait here for the up sums
         for (uint32_t s0 = 0, pi = 0; s0 < nslices; ++pi) {
             const uint32_t nsp = p.phase_base + (pi < p.phase_rem ? 1u : 0u);
-            for (uint32_t rg = blockIdx.x; rg < p.ngroups; rg += gridDim.x, ++fl, first = (first + nsp) % NTEAMS) {
+            for (uint32_t gi = 0; gi < gcta; ++gi, ++fl, first = (first + nsp) % NTEAMS) {
+                const uint32_t rg = blockIdx.x + (sw ? gi >> 1 : gi) * gridDim.x;
+                const bool second = sw && (gi & 1u);
                 const uint32_t rs = fl & 1;
                 if (!mbar_wait_bounded(&red_full[rs], (fl >> 1) & 1, p.status)) return;
                 if (lane == 0) PROBE_STAMP(7);
@@ -681,9 +694,14 @@ __global__ void __launch_bounds__((NTEAMS * TEAM + 2) * 32, 1) gemv_mma_kernel(c
                         const uint32_t tok = tok0 + j;
                         const float out = v[j];
                         if (static_cast<uint32_t>(j) < ncol && row < p.n && tok < p.m) {
-                            if (!EXT || p.g_nranks == 0) {
+                            if (EXT && sw) {
+                                if (!second) gate[j] = out;
+                                else yout[static_cast<size_t>(tok) * p.n + row] = gate[j] / (1.0f + expf(-gate[j])) * out;
+                            } else if (!EXT || p.g_nranks == 0) {
                                 float* dst = yout + static_cast<size_t>(tok) * p.n + row;
-                                *dst = s0 ? *dst + out : out;
+                                float o = out;
+                                if (s0 == 0 && p.residual) o += p.residual[static_cast<size_t>(slot) * p.n + static_cast<size_t>(tok) * p.n + row];
+                                *dst = s0 ? *dst + o : o;
                             } else {
                                 // the own buffer accumulates the phases; the last phase's total goes to every rank
                                 const size_t off = static_cast<size_t>(tok) * p.g_ntotal + p.g_col0 + row;
@@ -972,7 +990,7 @@ EncodeTiledFn encode_fn() {
 
 // Tensor map over a dense weight matrix viewed as 8-byte elements: box = one stage (16 rows x the
 // padded slice).  False if the shape does not fit a box (inner extent > 256 elements: Q8_0).
-bool make_stage_map(CUtensorMap* map, const MParams& p) {
+bool make_stage_map(CUtensorMap* map, const MParams& p, const uint8_t* w) {
     EncodeTiledFn enc = encode_fn();
     if (!enc || p.ids || p.sub_groups > 1 || p.dense_stage || p.pitch % 8 || p.pitch / 8 > 256 || p.slice_bytes % 16 || p.row_bytes % 16) return false;
     static const bool off = [] { const char* v = getenv("HF2Q_CUDA_MMA_TMAP"); return v && v[0] == '0'; }();      // tuning aid
@@ -981,7 +999,7 @@ bool make_stage_map(CUtensorMap* map, const MParams& p) {
     cuuint64_t strides[1] = {p.row_bytes};
     cuuint32_t box[2] = {p.pitch / 8, ROWS};
     cuuint32_t es[2] = {1, 1};
-    return enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT64, 2, const_cast<uint8_t*>(p.w), dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
+    return enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT64, 2, const_cast<uint8_t*>(w), dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
                CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
@@ -1018,12 +1036,13 @@ cudaError_t launch_mma_tt(MParams p, uint32_t slots, const Plan& pl, const Devic
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = pdl ? 1 : 0;
-    alignas(64) CUtensorMap tmap;
+    alignas(64) CUtensorMap tmap, tmap2;
     memset(&tmap, 0, sizeof tmap);
+    memset(&tmap2, 0, sizeof tmap2);
     static const bool evict_first = env_int("HF2Q_CUDA_MMA_EVICT_FIRST", 1) != 0;      // tuning aid
     p.w_evict_first = evict_first ? 1u : 0u;
-    p.use_tmap = make_stage_map(&tmap, p) ? 1u : 0u;
-    return cudaLaunchKernelEx(&cfg, kern, tmap, p);
+    p.use_tmap = make_stage_map(&tmap, p, p.w) && (!p.swiglu || make_stage_map(&tmap2, p, p.w2)) ? 1u : 0u;
+    return cudaLaunchKernelEx(&cfg, kern, tmap, tmap2, p);
 }
 
 template <uint32_t TYPE>
@@ -1038,6 +1057,7 @@ cudaError_t launch_mma_t(MParams p, uint32_t slots, const DeviceInfo& dev, cudaS
     const Plan pl = make_plan(TYPE, p.k, p.nslots, 2, limit);
     if (!pl.stages) return cudaErrorInvalidConfiguration;
     const bool phased = pl.phase_base != p.nslices;
+    if (phased && p.swiglu) return cudaErrorInvalidConfiguration;       // the gate sums cannot wait across phases
     const bool ext = p.g_nranks != 0 || p.w2 != nullptr;
     if (p.sub_groups > 1)                                                                          // one short slice per row
         return ext ? launch_mma_tt<TYPE, 2, false, true, true>(p, slots, pl, dev, st) : launch_mma_tt<TYPE, 2, false, true, false>(p, slots, pl, dev, st);
@@ -1092,6 +1112,13 @@ uint32_t gemv_mma_max_rows(uint32_t type, uint32_t k, uint32_t x_dtype, const De
     return rows;
 }
 
+bool gemv_mma_swiglu_ok(uint32_t type, uint32_t k, uint32_t m, uint32_t x_dtype, const DeviceInfo& dev) {
+    const uint32_t nslots = x_dtype == HF2Q_DT_BF16 ? m : 2 * m;
+    if (m == 0 || nslots > 8 || k % 256 || sub_groups_of(k) > 1) return false;
+    const Plan pl = make_plan(type, k, nslots, 2, static_cast<size_t>(dev.max_smem_optin));
+    return pl.stages && pl.phase_base == (k + SLICE_ELEMS - 1) / SLICE_ELEMS;
+}
+
 // One launch: bf16 activations, m <= 8; f32 activations, m <= 4 (hi/lo split on two columns).
 cudaError_t launch_gemv_mma(const GemvArgs& a, const DeviceInfo& dev, cudaStream_t st) {
     const BlockGeom g = block_geom(a.type);
@@ -1099,7 +1126,9 @@ cudaError_t launch_gemv_mma(const GemvArgs& a, const DeviceInfo& dev, cudaStream
     p.w = static_cast<const uint8_t*>(a.w);
     p.w2 = static_cast<const uint8_t*>(a.w2);
     p.y2 = a.y2;
-    p.pair_slots = a.slots;
+    p.pair_slots = a.swiglu ? 0xffffffffu : a.slots;
+    p.swiglu = a.swiglu ? 1u : 0u;
+    p.residual = a.residual;
     p.x = a.x;
     p.y = a.y;
     p.ids = a.ids;
@@ -1129,12 +1158,14 @@ cudaError_t launch_gemv_mma(const GemvArgs& a, const DeviceInfo& dev, cudaStream
         p.g_nranks = g.n_ranks; p.g_rank = g.rank; p.g_ntotal = g.n_total; p.g_col0 = g.col0;
         p.g_wait = g.wait_expected;
     }
+    if (a.swiglu && (!a.w2 || a.ids || a.gather || a.residual || p.sub_groups > 1)) return cudaErrorInvalidValue;
+    const uint32_t slots = a.w2 && !a.swiglu ? 2 * a.slots : a.slots;
     switch (a.type) {
-        case HF2Q_TYPE_Q4_0: return launch_mma_t<HF2Q_TYPE_Q4_0>(p, a.w2 ? 2 * a.slots : a.slots, dev, st);
-        case HF2Q_TYPE_Q8_0: return launch_mma_t<HF2Q_TYPE_Q8_0>(p, a.w2 ? 2 * a.slots : a.slots, dev, st);
-        case HF2Q_TYPE_Q4_K: return launch_mma_t<HF2Q_TYPE_Q4_K>(p, a.w2 ? 2 * a.slots : a.slots, dev, st);
-        case HF2Q_TYPE_Q5_K: return launch_mma_t<HF2Q_TYPE_Q5_K>(p, a.w2 ? 2 * a.slots : a.slots, dev, st);
-        case HF2Q_TYPE_Q6_K: return launch_mma_t<HF2Q_TYPE_Q6_K>(p, a.w2 ? 2 * a.slots : a.slots, dev, st);
+        case HF2Q_TYPE_Q4_0: return launch_mma_t<HF2Q_TYPE_Q4_0>(p, slots, dev, st);
+        case HF2Q_TYPE_Q8_0: return launch_mma_t<HF2Q_TYPE_Q8_0>(p, slots, dev, st);
+        case HF2Q_TYPE_Q4_K: return launch_mma_t<HF2Q_TYPE_Q4_K>(p, slots, dev, st);
+        case HF2Q_TYPE_Q5_K: return launch_mma_t<HF2Q_TYPE_Q5_K>(p, slots, dev, st);
+        case HF2Q_TYPE_Q6_K: return launch_mma_t<HF2Q_TYPE_Q6_K>(p, slots, dev, st);
         default: return cudaErrorInvalidValue;
     }
 }

@@ -37,6 +37,10 @@ struct GemvArgs {
     // read w2 and write y2; nullptr = single product
     const void* w2 = nullptr;
     float* y2 = nullptr;
+    // dense fused SwiGLU: w = gate, w2 = up (same geometry), y = silu(x gate^T) * (x up^T) in one launch
+    bool swiglu = false;
+    // y = residual + product (dense and routed mat-vec; may alias y); nullptr = plain product
+    const float* residual = nullptr;
 };
 struct DeviceInfo {
     int sm_count;
@@ -49,6 +53,8 @@ cudaError_t launch_gemv(const GemvArgs& a, const DeviceInfo& dev, cudaStream_t s
 bool gemv_mma_supported(const GemvArgs& a);
 uint32_t gemv_mma_max_rows(uint32_t type, uint32_t k, uint32_t x_dtype, const DeviceInfo& dev);
 cudaError_t launch_gemv_mma(const GemvArgs& a, const DeviceInfo& dev, cudaStream_t st);
+// whether one launch can take m activation rows with the SwiGLU epilogue (all of k resident, k > 1024)
+bool gemv_mma_swiglu_ok(uint32_t type, uint32_t k, uint32_t m, uint32_t x_dtype, const DeviceInfo& dev);
 // bounded wait (one warp) until the arrival counter flag[0] has caught up with the expected count flag[1]; a
 // timeout sets STATUS_WAIT_TIMEOUT
 cudaError_t launch_gather_wait(const uint32_t* flag, uint32_t* status, cudaStream_t st);

@@ -47,16 +47,27 @@ def _silu_mul(ctx, gate, up):
 
 
 def build_dense_ffn_layer_gpu_q(ctx: ops.GpuContext, x: torch.Tensor, w: DenseFfnWeightsGpuQ,
-                                residual: torch.Tensor | None = None) -> torch.Tensor:
-    """y = down @ (silu(gate @ x) * (up @ x)) (+ residual); x [m, hidden] f32/bf16, y f32 [m, hidden]."""
+                                residual: torch.Tensor | None = None, fused: bool = True) -> torch.Tensor:
+    """y = down @ (silu(gate @ x) * (up @ x)) (+ residual); x [m, hidden] f32/bf16, y f32 [m, hidden].
+
+    With ``fused`` (default) and a shape the fused kernels take, this is two launches: gate/up with
+    the SwiGLU in the epilogue, down with the residual add in the epilogue.  Otherwise the
+    reference's sequence: gate, up, silu_mul, down, add (gpu_ffn.rs:896-960)."""
     m = x.shape[0]
     inter, hidden = w.gate_q.rows, w.gate_q.cols
-    a = torch.empty((m, inter), dtype=torch.float32, device=x.device)
-    b = torch.empty_like(a)
-    ops.quantized_matmul_ggml(ctx, x, w.gate_q, a, w.gate_q.matmul_params(m))
-    ops.quantized_matmul_ggml(ctx, x, w.up_q, b, w.up_q.matmul_params(m))
-    c = _silu_mul(ctx, a, b)
+    if fused and ops.quantized_matmul_swiglu_supported(ctx, m, w.gate_q, x.dtype):
+        c = torch.empty((m, inter), dtype=torch.float32, device=x.device)
+        ops.quantized_matmul_swiglu(ctx, x, w.gate_q, w.up_q, c, m)
+    else:
+        a = torch.empty((m, inter), dtype=torch.float32, device=x.device)
+        b = torch.empty_like(a)
+        ops.quantized_matmul_ggml(ctx, x, w.gate_q, a, w.gate_q.matmul_params(m))
+        ops.quantized_matmul_ggml(ctx, x, w.up_q, b, w.up_q.matmul_params(m))
+        c = _silu_mul(ctx, a, b)
     y = torch.empty((m, hidden), dtype=torch.float32, device=x.device)
+    if residual is not None and fused and m <= 8 and ops.quantized_matmul_add_supported(ctx, w.down_q, c.dtype):
+        ops.quantized_matmul_add(ctx, c, w.down_q, residual.contiguous().float(), y, m)
+        return y
     ops.quantized_matmul_ggml(ctx, c, w.down_q, y, w.down_q.matmul_params(m))
     if residual is not None:
         y += residual

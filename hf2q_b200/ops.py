@@ -224,6 +224,40 @@ def quantized_matmul_ggml(ctx: GpuContext, input: torch.Tensor, weight: QuantWei
                                           int(params.ggml_type), ws_ptr, ws_bytes))
 
 
+def quantized_matmul_swiglu_supported(ctx: GpuContext, m: int, weight: QuantWeight, x_dtype=torch.bfloat16) -> bool:
+    """Whether gate and up products of shape `weight` with m activation rows fit the one fused launch."""
+    xdt = DT_BF16 if x_dtype == torch.bfloat16 else DT_F32
+    return bool(ctx._lib.hf2q_cuda_qmatmul_swiglu_supported(ctx._h, m, weight.rows, weight.cols, weight.ggml_type, xdt))
+
+
+def quantized_matmul_swiglu(ctx: GpuContext, input: torch.Tensor, gate: QuantWeight, up: QuantWeight, out: torch.Tensor, m: int) -> None:
+    """out[m,n] = silu(input . gate^T) * (input . up^T) in one launch (gpu_ffn.rs:896-935: gate, up, dispatch_silu_mul)."""
+    xdt = _act(input, "input")
+    if out.dtype != torch.float32 or not out.is_cuda or not out.is_contiguous() or out.numel() < m * gate.rows:
+        raise Hf2qError(_lib.ERR_INVALID_ARGUMENT, "out must be a contiguous float32 CUDA tensor of [m, n]")
+    if (gate.rows, gate.cols, gate.ggml_type) != (up.rows, up.cols, up.ggml_type) or input.numel() < m * gate.cols:
+        raise Hf2qError(_lib.ERR_INVALID_ARGUMENT, "gate and up must share (rows, cols, type); input must hold [m, k]")
+    ctx._check(ctx._lib.hf2q_cuda_qmatmul_swiglu(ctx._h, ctx._stream(), input.data_ptr(), xdt, gate.ptr, up.ptr, out.data_ptr(),
+                                                 m, gate.rows, gate.cols, gate.ggml_type))
+
+
+def quantized_matmul_add_supported(ctx: GpuContext, weight: QuantWeight, x_dtype=torch.float32) -> bool:
+    xdt = DT_BF16 if x_dtype == torch.bfloat16 else DT_F32
+    return bool(ctx._lib.hf2q_cuda_qmatmul_add_supported(ctx._h, weight.rows, weight.cols, weight.ggml_type, xdt))
+
+
+def quantized_matmul_add(ctx: GpuContext, input: torch.Tensor, weight: QuantWeight, residual: torch.Tensor, out: torch.Tensor, m: int) -> None:
+    """out[m,n] = residual + input . weight^T (gpu_ffn.rs:947-960: the optional add_residual of the dense builder)."""
+    xdt = _act(input, "input")
+    for t, name in ((residual, "residual"), (out, "out")):
+        if t.dtype != torch.float32 or not t.is_cuda or not t.is_contiguous() or t.numel() < m * weight.rows:
+            raise Hf2qError(_lib.ERR_INVALID_ARGUMENT, f"{name} must be a contiguous float32 CUDA tensor of [m, n]")
+    if input.numel() < m * weight.cols:
+        raise Hf2qError(_lib.ERR_INVALID_ARGUMENT, "input smaller than [m, k]")
+    ctx._check(ctx._lib.hf2q_cuda_qmatmul_add(ctx._h, ctx._stream(), input.data_ptr(), xdt, weight.ptr, residual.data_ptr(),
+                                              out.data_ptr(), m, weight.rows, weight.cols, weight.ggml_type))
+
+
 def quantized_matmul_host(ctx: GpuContext, x_host: np.ndarray, weight: QuantWeight, y_host: np.ndarray,
                           m: int, x_dtype: int = DT_F32, wait: bool = True) -> None:
     """Host-buffer form: copies x in, runs, copies y out (hf2q_cuda_qmatmul_host).  With

@@ -146,6 +146,31 @@ HF2Q_API int32_t hf2q_cuda_qmatmul_static(hf2q_ctx* ctx, void* stream, const voi
                                           uint32_t ggml_type);
 HF2Q_API uint64_t hf2q_cuda_qmatmul_static_max_elements(void);
 
+/* Dense SwiGLU FFN fusions for 1..8 activation rows.  The reference's dense builder
+ * (build_dense_ffn_layer_gpu_q, src/inference/models/qwen35/gpu_ffn.rs:896-960) issues the gate and
+ * up products, dispatch_silu_mul, the down product and, with `add_residual`, an elementwise_add;
+ * here that is two launches:
+ *   hf2q_cuda_qmatmul_swiglu: y[m][n] = silu(x * Wgate^T) .* (x * Wup^T), silu(v) = v / (1 + exp(-v));
+ *     every CTA walks a row group first in the gate and then in the up tensor (same geometry, both
+ *     raw-block uploads) and its reducer applies the activation, so neither product is ever stored.
+ *     One launch only: hf2q_cuda_qmatmul_swiglu_supported() returns 1 when (m, k, type, x_dtype) fits
+ *     (k % 256 == 0, k > 1024, 16-byte aligned rows, all m activation rows resident: bf16 m <= 8,
+ *     f32 m <= 4, smaller for very long rows); otherwise the call fails with
+ *     HF2Q_ERR_INVALID_ARGUMENT and the caller issues the three separate ops.
+ *   hf2q_cuda_qmatmul_add: y = residual + x * W^T (residual [m][n] f32, may be y itself); mat-vec
+ *     path only (k % 256 == 0, 16-byte aligned rows: hf2q_cuda_qmatmul_add_supported() returns 1),
+ *     any m (8 rows per launch); other shapes fail with HF2Q_ERR_INVALID_ARGUMENT. */
+HF2Q_API int32_t hf2q_cuda_qmatmul_swiglu_supported(hf2q_ctx* ctx, uint32_t m, uint32_t n, uint32_t k,
+                                                    uint32_t ggml_type, uint32_t x_dtype);
+HF2Q_API int32_t hf2q_cuda_qmatmul_swiglu(hf2q_ctx* ctx, void* stream, const void* x, uint32_t x_dtype,
+                                          const void* w_gate, const void* w_up, float* y, uint32_t m,
+                                          uint32_t n, uint32_t k, uint32_t ggml_type);
+HF2Q_API int32_t hf2q_cuda_qmatmul_add_supported(hf2q_ctx* ctx, uint32_t n, uint32_t k, uint32_t ggml_type,
+                                                 uint32_t x_dtype);
+HF2Q_API int32_t hf2q_cuda_qmatmul_add(hf2q_ctx* ctx, void* stream, const void* x, uint32_t x_dtype,
+                                       const void* w, const float* residual, float* y, uint32_t m,
+                                       uint32_t n, uint32_t k, uint32_t ggml_type);
+
 /* Same product for callers that hold HOST buffers: copies x in, runs, copies y out, waits.
  * Uses staging buffers the context grows on first use.  Stands for the reference's
  * `apply_linear_projection_f32` + download pattern in its tests (gpu_ffn.rs:3209-3275). */

@@ -36,6 +36,62 @@ def test_dense_ffn_builder(gpu_ctx, t, m):
     assert rel_l2(got - res, want - res) < 3e-3
 
 
+@pytest.mark.parametrize("t", list(oracle.ALL_TYPES))
+@pytest.mark.parametrize("bf16", [False, True])
+def test_dense_ffn_fused_launches_equal_the_separate_ops(gpu_ctx, t, bf16):
+    """gate/up with the SwiGLU epilogue and down with the residual epilogue: the same arithmetic in the
+    same order as gate, up, silu_mul, down, add -- bit-identical outputs, and close to the oracle."""
+    from hf2q_b200 import ops
+    hidden, inter = 2048, 1536 + 48                   # inter: a partial last row group of the gate/up tensors
+    gq, gf = _qw(gpu_ctx, t, inter, hidden, 21)
+    uq, uf = _qw(gpu_ctx, t, inter, hidden, 22)
+    dq, df = _qw(gpu_ctx, t, hidden, 2048, 23)
+    for m in (1, 3, 4) + ((8,) if bf16 else ()):
+        x = make_x(m, hidden, seed=30 + m)
+        xd = torch.from_numpy(x).cuda()
+        if bf16:
+            xd = xd.bfloat16()
+            x = xd.float().cpu().numpy()
+        assert ops.quantized_matmul_swiglu_supported(gpu_ctx, m, gq, xd.dtype)
+        a = torch.empty((m, inter), device="cuda")
+        b = torch.empty_like(a)
+        ops.quantized_matmul_ggml(gpu_ctx, xd, gq, a, gq.matmul_params(m))
+        ops.quantized_matmul_ggml(gpu_ctx, xd, uq, b, uq.matmul_params(m))
+        sep = ffn._silu_mul(gpu_ctx, a, b)
+        fused = torch.full((m, inter), float("nan"), device="cuda")
+        ops.quantized_matmul_swiglu(gpu_ctx, xd, gq, uq, fused, m)
+        gpu_ctx.check_status()
+        assert torch.equal(fused, sep), (t, m)
+        g64, u64 = x.astype(np.float64) @ gf.T.astype(np.float64), x.astype(np.float64) @ uf.T.astype(np.float64)
+        want = g64 / (1.0 + np.exp(-g64)) * u64
+        assert rel_l2(fused.cpu().numpy(), want) < 1e-3
+        # down + residual (in place: the residual stream is updated where it lives)
+        c = torch.from_numpy(make_x(m, 2048, seed=40 + m)).cuda()
+        res = torch.from_numpy(make_x(m, hidden, seed=50 + m)).cuda()
+        y = torch.empty((m, hidden), device="cuda")
+        ops.quantized_matmul_ggml(gpu_ctx, c, dq, y, dq.matmul_params(m))
+        want_y = y + res
+        got = res.clone()
+        ops.quantized_matmul_add(gpu_ctx, c, dq, got, got, m)
+        gpu_ctx.check_status()
+        assert torch.equal(got, want_y), (t, m)
+
+
+def test_swiglu_fusion_declines_what_does_not_fit_one_launch(gpu_ctx):
+    from hf2q_b200 import ops
+    t = oracle.Q6_K
+    long_rows = hq.load_quant_weight(gpu_ctx, make_quant_weight(t, 32, 14336, seed=1), t, 32, 14336)
+    assert ops.quantized_matmul_swiglu_supported(gpu_ctx, 1, long_rows, torch.bfloat16)
+    assert not ops.quantized_matmul_swiglu_supported(gpu_ctx, 8, long_rows, torch.bfloat16)      # k-phases
+    assert not ops.quantized_matmul_swiglu_supported(gpu_ctx, 5, long_rows, torch.float32)       # more than 4 f32 rows
+    short_rows = hq.load_quant_weight(gpu_ctx, make_quant_weight(t, 32, 512, seed=2), t, 32, 512)
+    assert not ops.quantized_matmul_swiglu_supported(gpu_ctx, 1, short_rows, torch.bfloat16)     # stacked row groups
+    x = torch.zeros((8, 14336), device="cuda", dtype=torch.bfloat16)
+    y = torch.empty((8, 32), device="cuda")
+    with pytest.raises(hq.Hf2qError):
+        ops.quantized_matmul_swiglu(gpu_ctx, x, long_rows, long_rows, y, 8)
+
+
 @pytest.mark.parametrize("T", [1, 3, 70])
 def test_moe_ffn_builder(gpu_ctx, T):
     t, hidden, inter, E, k, m_sh = oracle.Q5_K, 512, 256, 8, 2, 256
