@@ -690,6 +690,52 @@ HF2Q_API int32_t hf2q_cuda_qmatmul_id_pair(hf2q_ctx* ctx, void* stream, const vo
                           scratch, scratch_bytes, "qmatmul_id_pair");
 }
 
+// gate and up of an MoE layer with the SwiGLU in the epilogue: few routed rows only (the mat-vec path)
+HF2Q_API int32_t hf2q_cuda_qmatmul_id_swiglu_supported(hf2q_ctx* ctx, uint32_t n_tokens, uint32_t top_k, uint32_t n, uint32_t k,
+                                                       uint32_t type, uint32_t x_dtype) {
+    if (!ctx || !type_supported(type) || n == 0 || k == 0 || top_k == 0 || ctx->fp32_matvec) return 0;
+    if (static_cast<uint64_t>(n_tokens) * top_k > MM_ID_ROUTING_THRESHOLD) return 0;
+    const BlockGeom g = block_geom(type);
+    if (k % g.elems || (static_cast<uint64_t>(k) / g.elems * g.bytes) % 16) return 0;
+    return gemv_mma_swiglu_ok(type, k, 1, x_dtype, ctx->dev) ? 1 : 0;
+}
+
+HF2Q_API int32_t hf2q_cuda_qmatmul_id_swiglu(hf2q_ctx* ctx, void* stream, const void* x, uint32_t x_dtype,
+                                             const void* w_gate, const void* w_up, const uint32_t* ids, float* y,
+                                             uint32_t n_tokens, uint32_t top_k, uint32_t n, uint32_t k, uint32_t n_experts,
+                                             uint64_t expert_stride, uint32_t type) {
+    if (!ctx) return HF2Q_ERR_INVALID_ARGUMENT;
+    const char* who = "qmatmul_id_swiglu";
+    if (!x || !w_gate || !w_up || !ids || !y) return fail(ctx, HF2Q_ERR_INVALID_ARGUMENT, "%s: null pointer", who);
+    if (x_dtype != HF2Q_DT_F32 && x_dtype != HF2Q_DT_BF16) return fail(ctx, HF2Q_ERR_INVALID_ARGUMENT, "%s: x_dtype %u", who, x_dtype);
+    int32_t rc = check_matmul_shape(ctx, type, n, k, who);
+    if (rc) return rc;
+    if (top_k == 0 || n_experts == 0) return fail(ctx, HF2Q_ERR_INVALID_ARGUMENT, "%s: top_k=%u n_experts=%u must be non-zero", who, top_k, n_experts);
+    uint64_t min_stride = 0;
+    hf2q_cuda_expert_stride(type, n, k, &min_stride);
+    if (expert_stride < min_stride) return fail(ctx, HF2Q_ERR_INVALID_ARGUMENT, "%s: expert_stride %llu < one [n,k] matrix (%llu bytes)", who, (unsigned long long)expert_stride, (unsigned long long)min_stride);
+    if (n_tokens == 0) return HF2Q_OK;
+    GemvArgs a{};
+    a.w = w_gate; a.w2 = w_up; a.swiglu = true;
+    a.x = x; a.y = y; a.ids = ids;
+    a.expert_stride = expert_stride;
+    a.x_dtype = x_dtype; a.type = type;
+    a.m = 1; a.n = n; a.k = k;
+    a.slots = n_tokens * top_k;
+    a.top_k = top_k; a.n_experts = n_experts;
+    a.status = ctx->status;
+    GemvArgs up = a;
+    up.w = w_up;
+    if (!hf2q_cuda_qmatmul_id_swiglu_supported(ctx, n_tokens, top_k, n, k, type, x_dtype) || !gemv_mma_supported(a) || !gemv_mma_supported(up))
+        return fail(ctx, HF2Q_ERR_INVALID_ARGUMENT, "%s: %u routed rows of k=%u do not fit the fused launch (ask hf2q_cuda_qmatmul_id_swiglu_supported)",
+                    who, n_tokens * top_k, k);
+    DeviceGuard dg(ctx->device);
+    const cudaError_t e = launch_gemv_mma(a, ctx->dev, static_cast<cudaStream_t>(stream));
+    if (e != cudaSuccess) return cuda_fail(ctx, e, "qmatmul_id_swiglu launch");
+    ctx->launches += 1;
+    return HF2Q_OK;
+}
+
 HF2Q_API int32_t hf2q_cuda_moe_softmax_topk(hf2q_ctx* ctx, void* stream, const float* logits, uint32_t* ids,
                                             float* weights, uint32_t n_tokens, uint32_t n_experts, uint32_t top_k) {
     if (!ctx) return HF2Q_ERR_INVALID_ARGUMENT;

@@ -525,6 +525,7 @@ __global__ void __launch_bounds__((NTEAMS * TEAM + 2) * 32, 1) gemv_mma_kernel(c
     uint32_t slot = blockIdx.y;
     const uint8_t* wbase = p.w;
     float* ybase = p.y;
+    const uint8_t* wbase2 = EXT ? p.w2 : nullptr;     // fused SwiGLU: the up tensor (of the same expert)
     if (EXT && p.w2 && slot >= p.pair_slots) { slot -= p.pair_slots; wbase = p.w2; ybase = p.y2; }
     uint32_t xrow_idx = 0;
     bool slot_ok = true;
@@ -534,6 +535,7 @@ __global__ void __launch_bounds__((NTEAMS * TEAM + 2) * 32, 1) gemv_mma_kernel(c
         slot_ok = e < p.n_experts;
         if (!slot_ok && threadIdx.x == 0) atomicOr(p.status, STATUS_BAD_EXPERT_ID);
         wbase += static_cast<uint64_t>(slot_ok ? e : 0) * p.expert_stride;
+        if (EXT && p.w2) wbase2 += static_cast<uint64_t>(slot_ok ? e : 0) * p.expert_stride;
         xrow_idx = slot / p.top_k;
     }
     float* yout = ybase + static_cast<size_t>(slot) * p.n;
@@ -571,7 +573,7 @@ __global__ void __launch_bounds__((NTEAMS * TEAM + 2) * 32, 1) gemv_mma_kernel(c
                 for (uint32_t gi = 0; gi < gcta; ++gi) {
                     const uint32_t rg = blockIdx.x + (sw ? gi >> 1 : gi) * gridDim.x;
                     const bool second = sw && (gi & 1u);
-                    const uint8_t* wsrc = second ? p.w2 : wbase;
+                    const uint8_t* wsrc = second ? wbase2 : wbase;
                     const CUtensorMap* tmap = second ? &tmap_w2 : &tmap_w;
                     const uint32_t row0 = rg * stage_rows;
                     const uint32_t nrows = min(stage_rows, p.n - row0);
@@ -1158,7 +1160,7 @@ cudaError_t launch_gemv_mma(const GemvArgs& a, const DeviceInfo& dev, cudaStream
         p.g_nranks = g.n_ranks; p.g_rank = g.rank; p.g_ntotal = g.n_total; p.g_col0 = g.col0;
         p.g_wait = g.wait_expected;
     }
-    if (a.swiglu && (!a.w2 || a.ids || a.gather || a.residual || p.sub_groups > 1)) return cudaErrorInvalidValue;
+    if (a.swiglu && (!a.w2 || a.gather || a.residual || p.sub_groups > 1)) return cudaErrorInvalidValue;
     const uint32_t slots = a.w2 && !a.swiglu ? 2 * a.slots : a.slots;
     switch (a.type) {
         case HF2Q_TYPE_Q4_0: return launch_mma_t<HF2Q_TYPE_Q4_0>(p, slots, dev, st);

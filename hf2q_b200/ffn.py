@@ -75,7 +75,7 @@ def build_dense_ffn_layer_gpu_q(ctx: ops.GpuContext, x: torch.Tensor, w: DenseFf
 
 
 def build_moe_ffn_layer_gpu_q(ctx: ops.GpuContext, x: torch.Tensor, w: MoeFfnWeightsGpuQ,
-                              residual: torch.Tensor | None = None) -> torch.Tensor:
+                              residual: torch.Tensor | None = None, fused: bool = True) -> torch.Tensor:
     """Router -> softmax/top-k/renorm -> expert gate, up (mul_mat_id) -> SwiGLU -> expert down
     (mul_mat_id, one activation row per routed slot) -> weighted sum over the slots, plus the
     sigmoid-gated shared expert and the residual.  x f32 [T, hidden]; returns f32 [T, hidden]."""
@@ -89,11 +89,16 @@ def build_moe_ffn_layer_gpu_q(ctx: ops.GpuContext, x: torch.Tensor, w: MoeFfnWei
     sg = ops.expert_stride(w.ggml_type_gate_up, inter, hidden)
     sd = ops.expert_stride(w.ggml_type_down, hidden, inter)
     scratch = ops.IdMmScratch.alloc(ctx, E, rows, max(hidden, inter))
-    g = torch.empty((rows, inter), dtype=torch.float32, device=x.device)
-    u = torch.empty_like(g)
     pg = ops.GgmlQuantizedMatmulIdParams(T, k, inter, hidden, E, sg, w.ggml_type_gate_up)
-    ops.quantized_matmul_id_pair_ggml(ctx, x, w.expert_gate.data_ptr(), w.expert_up.data_ptr(), ids, g, u, scratch, pg)
-    act = _silu_mul(ctx, g, u)
+    if fused and ops.quantized_matmul_id_swiglu_supported(ctx, pg, x.dtype):
+        # few routed rows: gate, up and the SwiGLU in one launch
+        act = torch.empty((rows, inter), dtype=torch.float32, device=x.device)
+        ops.quantized_matmul_id_swiglu_ggml(ctx, x, w.expert_gate.data_ptr(), w.expert_up.data_ptr(), ids, act, pg)
+    else:
+        g = torch.empty((rows, inter), dtype=torch.float32, device=x.device)
+        u = torch.empty_like(g)
+        ops.quantized_matmul_id_pair_ggml(ctx, x, w.expert_gate.data_ptr(), w.expert_up.data_ptr(), ids, g, u, scratch, pg)
+        act = _silu_mul(ctx, g, u)
     d = torch.empty((rows, hidden), dtype=torch.float32, device=x.device)
     pd = ops.GgmlQuantizedMatmulIdParams(rows, 1, hidden, inter, E, sd, w.ggml_type_down)
     ops.quantized_matmul_id_ggml(ctx, act, w.expert_down.data_ptr(), ids, d, scratch, pd)

@@ -329,6 +329,30 @@ def quantized_matmul_id_pair_ggml(ctx: GpuContext, input: torch.Tensor, weight_a
                                                   int(params.ggml_type), sp, sb))
 
 
+def quantized_matmul_id_swiglu_supported(ctx: GpuContext, params: GgmlQuantizedMatmulIdParams, x_dtype=torch.float32) -> bool:
+    xdt = DT_BF16 if x_dtype == torch.bfloat16 else DT_F32
+    return bool(ctx._lib.hf2q_cuda_qmatmul_id_swiglu_supported(ctx._h, params.n_tokens, params.top_k, params.n, params.k,
+                                                               int(params.ggml_type), xdt))
+
+
+def quantized_matmul_id_swiglu_ggml(ctx: GpuContext, input: torch.Tensor, weight_gate: int, weight_up: int, ids: torch.Tensor,
+                                    out: torch.Tensor, params: GgmlQuantizedMatmulIdParams) -> None:
+    """out[row] = silu(gate_e . x) * (up_e . x) for few routed rows in one launch (gpu_ffn.rs:2606-2760)."""
+    xdt = _act(input, "input")
+    if ids.dtype not in (torch.int32, torch.uint32) or not ids.is_cuda or not ids.is_contiguous():
+        raise Hf2qError(_lib.ERR_INVALID_ARGUMENT, "ids must be a contiguous 32-bit integer CUDA tensor")
+    rows = params.n_tokens * params.top_k
+    if ids.numel() < rows or out.numel() < rows * params.n or input.numel() < params.n_tokens * params.k:
+        raise Hf2qError(_lib.ERR_INVALID_ARGUMENT, "ids/input/out smaller than the params require")
+    if out.dtype != torch.float32 or not out.is_cuda or not out.is_contiguous():
+        raise Hf2qError(_lib.ERR_INVALID_ARGUMENT, "out must be a contiguous float32 CUDA tensor")
+    wg = weight_gate.ptr if isinstance(weight_gate, QuantWeight) else int(weight_gate)
+    wu = weight_up.ptr if isinstance(weight_up, QuantWeight) else int(weight_up)
+    ctx._check(ctx._lib.hf2q_cuda_qmatmul_id_swiglu(ctx._h, ctx._stream(), input.data_ptr(), xdt, wg, wu, ids.data_ptr(),
+                                                    out.data_ptr(), params.n_tokens, params.top_k, params.n, params.k,
+                                                    params.n_experts, params.expert_stride, int(params.ggml_type)))
+
+
 def dequantize(ctx: GpuContext, weight: QuantWeight, out_dtype=torch.float32) -> torch.Tensor:
     out = torch.empty((weight.rows, weight.cols), dtype=out_dtype, device=f"cuda:{ctx.device}")
     ctx._check(ctx._lib.hf2q_cuda_dequantize(ctx._h, ctx._stream(), weight.ptr, weight.ggml_type,

@@ -214,6 +214,22 @@ HF2Q_API int32_t hf2q_cuda_qmatmul_id_pair(hf2q_ctx* ctx, void* stream, const vo
                                            float* y_a, float* y_b, uint32_t n_tokens, uint32_t top_k,
                                            uint32_t n, uint32_t k, uint32_t n_experts, uint64_t expert_stride,
                                            uint32_t ggml_type, void* scratch, uint64_t scratch_bytes);
+
+/* Gate and up of an MoE layer with the SwiGLU in the epilogue, for few routed rows (n_tokens * top_k
+ * <= 32, the mat-vec path): y[row][n] = silu(x_tok * Wgate[e]^T) .* (x_tok * Wup[e]^T), e = ids[row].
+ * Replaces the two quantized_matmul_id_ggml_pooled calls and the dispatch_silu_mul between them
+ * (src/inference/models/qwen35/gpu_ffn.rs:2606-2760) with one launch; hf2q_cuda_qmatmul_id_swiglu_supported
+ * returns 1 when the shape fits (k % 256 == 0, k > 1024, 16-byte aligned rows and expert stride),
+ * otherwise the call fails with HF2Q_ERR_INVALID_ARGUMENT and the caller uses hf2q_cuda_qmatmul_id_pair
+ * + hf2q_cuda_silu_mul.  Rows whose expert index is out of range are zero-filled and flagged. */
+HF2Q_API int32_t hf2q_cuda_qmatmul_id_swiglu_supported(hf2q_ctx* ctx, uint32_t n_tokens, uint32_t top_k,
+                                                       uint32_t n, uint32_t k, uint32_t ggml_type,
+                                                       uint32_t x_dtype);
+HF2Q_API int32_t hf2q_cuda_qmatmul_id_swiglu(hf2q_ctx* ctx, void* stream, const void* x, uint32_t x_dtype,
+                                             const void* w_gate, const void* w_up, const uint32_t* ids,
+                                             float* y, uint32_t n_tokens, uint32_t top_k, uint32_t n,
+                                             uint32_t k, uint32_t n_experts, uint64_t expert_stride,
+                                             uint32_t ggml_type);
 HF2Q_API int32_t hf2q_cuda_qmatmul_id_scratch_bytes(uint32_t n_experts, uint32_t max_rows,
                                                     uint32_t k, uint32_t x_dtype, uint64_t* out);
 

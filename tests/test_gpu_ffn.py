@@ -92,6 +92,41 @@ def test_swiglu_fusion_declines_what_does_not_fit_one_launch(gpu_ctx):
         ops.quantized_matmul_swiglu(gpu_ctx, x, long_rows, long_rows, y, 8)
 
 
+@pytest.mark.parametrize("t", [oracle.Q4_0, oracle.Q5_K, oracle.Q6_K])
+@pytest.mark.parametrize("bf16", [False, True])
+def test_routed_swiglu_launch_equals_pair_plus_silu_mul(gpu_ctx, t, bf16):
+    from hf2q_b200 import ops
+    hidden, inter, E, top_k = 2048, 256 + 16, 6, 3
+    stride = hq.expert_stride(t, inter, hidden)
+    gate = torch.from_numpy(np.concatenate([make_quant_weight(t, inter, hidden, seed=60 + e) for e in range(E)])).cuda()
+    up = torch.from_numpy(np.concatenate([make_quant_weight(t, inter, hidden, seed=70 + e) for e in range(E)])).cuda()
+    for T in (1, 4):
+        x = torch.from_numpy(make_x(T, hidden, seed=80 + T)).cuda()
+        if bf16:
+            x = x.bfloat16()
+        rng = np.random.default_rng(T)
+        ids = torch.from_numpy(np.stack([rng.permutation(E)[:top_k] for _ in range(T)]).astype(np.int32).reshape(-1)).cuda()
+        p = hq.GgmlQuantizedMatmulIdParams(T, top_k, inter, hidden, E, stride, t)
+        assert ops.quantized_matmul_id_swiglu_supported(gpu_ctx, p, x.dtype)
+        g = torch.empty((T * top_k, inter), device="cuda")
+        u = torch.empty_like(g)
+        hq.quantized_matmul_id_pair_ggml(gpu_ctx, x, gate.data_ptr(), up.data_ptr(), ids, g, u, None, p)
+        sep = ffn._silu_mul(gpu_ctx, g, u)
+        fused = torch.full((T * top_k, inter), float("nan"), device="cuda")
+        ops.quantized_matmul_id_swiglu_ggml(gpu_ctx, x, gate.data_ptr(), up.data_ptr(), ids, fused, p)
+        gpu_ctx.check_status()
+        assert torch.equal(fused, sep), (t, T)
+    # an expert index out of range: that row is zero-filled and the status word says so
+    bad = ids.clone()
+    bad[1] = E
+    ops.quantized_matmul_id_swiglu_ggml(gpu_ctx, x, gate.data_ptr(), up.data_ptr(), bad, fused, p)
+    with pytest.raises(hq.Hf2qError):
+        gpu_ctx.check_status()
+    assert torch.count_nonzero(fused[1]) == 0 and torch.equal(fused[0], sep[0])
+    big = hq.GgmlQuantizedMatmulIdParams(64, top_k, inter, hidden, E, stride, t)
+    assert not ops.quantized_matmul_id_swiglu_supported(gpu_ctx, big, x.dtype)       # many rows: the grouped GEMM's job
+
+
 @pytest.mark.parametrize("T", [1, 3, 70])
 def test_moe_ffn_builder(gpu_ctx, T):
     t, hidden, inter, E, k, m_sh = oracle.Q5_K, 512, 256, 8, 2, 256
