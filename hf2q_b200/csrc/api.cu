@@ -21,21 +21,21 @@ struct hf2q_ctx {
     bool fp32_matvec = false;          // HF2Q_CUDA_F32_MATVEC=1: CUDA-core fp32 mat-vec only
     bool tc_matvec = false;            // HF2Q_CUDA_TC_MATVEC=1: dense mat-vecs on the tcgen05 kernel (slower today)
     // staging for the *_host convenience calls
-    // A small ring of device staging buffers and two streams: copies on out_stream, kernels on
-    // host_stream.  The copy stream's order is in(0), in(1), out(0), in(2), out(1), ...: the copy-in of
-    // call i+1 and the copy-out of call i-1 run while the kernel of call i does, and because out(i-2)
-    // precedes in(i) on that stream, slot i % HOST_SLOTS is free again when in(i) starts.
+    // A ring of device staging buffers and three streams: copy-in on in_stream, kernels on
+    // host_stream, copy-out on out_stream, so that the copy-in of later calls, the kernel of call i
+    // and the copy-out of earlier calls all overlap (the two copy directions use different copy
+    // engines).  Slot i % HOST_SLOTS is reused by call i + HOST_SLOTS: its copy-in waits for the
+    // slot's previous kernel (`computed`), its kernel for the slot's previous copy-out (`drained`).
     struct HostSlot {
         void* x = nullptr;  size_t x_bytes = 0;
         float* y = nullptr; size_t y_bytes = 0;
-        cudaEvent_t loaded = nullptr, computed = nullptr;
+        cudaEvent_t loaded = nullptr, computed = nullptr, drained = nullptr;
+        bool used = false;
     };
-    static constexpr int HOST_SLOTS = 4;
+    static constexpr int HOST_SLOTS = 8;
     HostSlot hslot[HOST_SLOTS];
     uint32_t hnext = 0;
-    cudaStream_t out_stream = nullptr;
-    // copy-out of the latest call, not yet queued
-    HostSlot* pending = nullptr; float* pending_dst = nullptr; size_t pending_bytes = 0;
+    cudaStream_t out_stream = nullptr, in_stream = nullptr;
     void* pin_x = nullptr;    size_t pin_x_bytes = 0;
     float* pin_y = nullptr;   size_t pin_y_bytes = 0;
     void* ws = nullptr;       size_t ws_bytes = 0;
@@ -165,7 +165,8 @@ HF2Q_API int32_t hf2q_cuda_ctx_create(int32_t device, hf2q_ctx** out) {
     c->dev.max_smem_optin = static_cast<int>(prop.sharedMemPerBlockOptin);
     if (cudaMalloc(&c->status, 256) != cudaSuccess || cudaMemset(c->status, 0, 256) != cudaSuccess ||
         cudaStreamCreateWithFlags(&c->host_stream, cudaStreamNonBlocking) != cudaSuccess ||
-        cudaStreamCreateWithFlags(&c->out_stream, cudaStreamNonBlocking) != cudaSuccess) {
+        cudaStreamCreateWithFlags(&c->out_stream, cudaStreamNonBlocking) != cudaSuccess ||
+        cudaStreamCreateWithFlags(&c->in_stream, cudaStreamNonBlocking) != cudaSuccess) {
         if (c->status) cudaFree(c->status);
         delete c;
         return HF2Q_ERR_CUDA;
@@ -190,8 +191,10 @@ HF2Q_API int32_t hf2q_cuda_ctx_destroy(hf2q_ctx* ctx) {
         if (hs.y) cudaFree(hs.y);
         if (hs.computed) cudaEventDestroy(hs.computed);
         if (hs.loaded) cudaEventDestroy(hs.loaded);
+        if (hs.drained) cudaEventDestroy(hs.drained);
     }
     if (ctx->out_stream) cudaStreamDestroy(ctx->out_stream);
+    if (ctx->in_stream) cudaStreamDestroy(ctx->in_stream);
     if (ctx->ws) cudaFree(ctx->ws);
     if (ctx->pin_x) cudaFreeHost(ctx->pin_x);
     if (ctx->pin_y) cudaFreeHost(ctx->pin_y);
@@ -501,16 +504,6 @@ HF2Q_API int32_t hf2q_cuda_qmatmul_static(hf2q_ctx* ctx, void* stream, const voi
 
 HF2Q_API uint64_t hf2q_cuda_qmatmul_static_max_elements(void) { return gemm_tc_static_scratch_bytes() / 2; }
 
-namespace {
-// queues the copy-out that the previous host call left pending
-cudaError_t flush_pending(hf2q_ctx* ctx) {
-    if (!ctx->pending) return cudaSuccess;
-    cudaError_t e = cudaStreamWaitEvent(ctx->out_stream, ctx->pending->computed, 0);
-    if (e == cudaSuccess) e = cudaMemcpyAsync(ctx->pending_dst, ctx->pending->y, ctx->pending_bytes, cudaMemcpyDeviceToHost, ctx->out_stream);
-    ctx->pending = nullptr;
-    return e;
-}
-}  // namespace
 
 HF2Q_API int32_t hf2q_cuda_qmatmul_host_async(hf2q_ctx* ctx, const void* x_host, uint32_t x_dtype, const void* w_dev,
                                               float* y_host, uint32_t m, uint32_t n, uint32_t k, uint32_t type) {
@@ -528,7 +521,7 @@ HF2Q_API int32_t hf2q_cuda_qmatmul_host_async(hf2q_ctx* ctx, const void* x_host,
     cudaError_t e = cudaSuccess;
     if (hs.x_bytes < xb || hs.y_bytes < yb || ctx->ws_bytes < wsb) {
         // growing a buffer frees the old one: nothing may still be using it
-        e = flush_pending(ctx);
+        e = cudaStreamSynchronize(ctx->in_stream);
         if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->host_stream);
         if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->out_stream);
         if (e != cudaSuccess) return cuda_fail(ctx, e, "qmatmul_host: sync before growing staging buffers");
@@ -539,32 +532,35 @@ HF2Q_API int32_t hf2q_cuda_qmatmul_host_async(hf2q_ctx* ctx, const void* x_host,
     if (!hs.computed) {
         e = cudaEventCreateWithFlags(&hs.computed, cudaEventDisableTiming);
         if (e == cudaSuccess) e = cudaEventCreateWithFlags(&hs.loaded, cudaEventDisableTiming);
+        if (e == cudaSuccess) e = cudaEventCreateWithFlags(&hs.drained, cudaEventDisableTiming);
         if (e != cudaSuccess) return cuda_fail(ctx, e, "qmatmul_host: event");
     }
-    // copy stream: this call's copy-in, then the previous call's copy-out
-    e = cudaMemcpyAsync(hs.x, x_host, xb, cudaMemcpyHostToDevice, ctx->out_stream);
-    if (e == cudaSuccess) e = cudaEventRecord(hs.loaded, ctx->out_stream);
-    if (e == cudaSuccess) e = flush_pending(ctx);
-    if (e != cudaSuccess) return cuda_fail(ctx, e, "qmatmul_host: copies");
-    // kernel stream
-    e = cudaStreamWaitEvent(ctx->host_stream, hs.loaded, 0);
-    if (e != cudaSuccess) return cuda_fail(ctx, e, "qmatmul_host: wait");
+    // copy-in: after the slot's previous kernel has read its activations
+    if (hs.used) e = cudaStreamWaitEvent(ctx->in_stream, hs.computed, 0);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(hs.x, x_host, xb, cudaMemcpyHostToDevice, ctx->in_stream);
+    if (e == cudaSuccess) e = cudaEventRecord(hs.loaded, ctx->in_stream);
+    // kernel: after the copy-in, and after the slot's previous copy-out has read its results
+    if (e == cudaSuccess) e = cudaStreamWaitEvent(ctx->host_stream, hs.loaded, 0);
+    if (e == cudaSuccess && hs.used) e = cudaStreamWaitEvent(ctx->host_stream, hs.drained, 0);
+    if (e != cudaSuccess) return cuda_fail(ctx, e, "qmatmul_host: copy-in");
     rc = hf2q_cuda_qmatmul(ctx, ctx->host_stream, hs.x, x_dtype, w_dev, hs.y, m, n, k, type, ctx->ws, ctx->ws_bytes);
     if (rc) return rc;
     e = cudaEventRecord(hs.computed, ctx->host_stream);
-    if (e != cudaSuccess) return cuda_fail(ctx, e, "qmatmul_host: record");
-    ctx->pending = &hs;
-    ctx->pending_dst = y_host;
-    ctx->pending_bytes = yb;
+    // copy-out
+    if (e == cudaSuccess) e = cudaStreamWaitEvent(ctx->out_stream, hs.computed, 0);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(y_host, hs.y, yb, cudaMemcpyDeviceToHost, ctx->out_stream);
+    if (e == cudaSuccess) e = cudaEventRecord(hs.drained, ctx->out_stream);
+    if (e != cudaSuccess) return cuda_fail(ctx, e, "qmatmul_host: copy-out");
+    hs.used = true;
     return HF2Q_OK;
 }
 
 HF2Q_API int32_t hf2q_cuda_host_sync(hf2q_ctx* ctx) {
     if (!ctx) return HF2Q_ERR_INVALID_ARGUMENT;
     DeviceGuard dg(ctx->device);
-    cudaError_t e = flush_pending(ctx);
-    if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->out_stream);      // the last copy-out waited for the last kernel
+    cudaError_t e = cudaStreamSynchronize(ctx->out_stream);      // every copy-out waited for its kernel, which waited for its copy-in
     if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->host_stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->in_stream);
     if (e != cudaSuccess) return cuda_fail(ctx, e, "host_sync");
     return HF2Q_OK;
 }

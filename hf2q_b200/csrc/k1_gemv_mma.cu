@@ -44,6 +44,8 @@
 #include <cstring>
 #include <mutex>
 #include <type_traits>
+#include <unordered_map>
+#include <vector>
 
 #include <cuda.h>
 
@@ -947,7 +949,7 @@ struct Plan {
 // than `teams` unless the row is) whose activation panel leaves room for a ring of teams + 2
 // stages: each team holds one stage while two are in flight (measured: fewer phases beat a deeper
 // ring).  Failing that, teams + 1.
-Plan make_plan(uint32_t type, uint32_t k, uint32_t nslots, int teams, size_t limit) {
+Plan make_plan_uncached(uint32_t type, uint32_t k, uint32_t nslots, int teams, size_t limit) {
     const uint32_t nslices = (k + SLICE_ELEMS - 1) / SLICE_ELEMS;
     const size_t stage = stage_bytes_of(type, k);
     static const uint32_t first_spare = static_cast<uint32_t>(env_int("HF2Q_CUDA_MMA_SPARE", 2));   // tuning aid
@@ -974,6 +976,20 @@ Plan make_plan(uint32_t type, uint32_t k, uint32_t nslots, int teams, size_t lim
     return Plan{};
 }
 
+// The plan depends on five small numbers and is asked for several times per launch: remember it.
+Plan make_plan(uint32_t type, uint32_t k, uint32_t nslots, int teams, size_t limit) {
+    struct Entry { uint32_t type, k, nslots; int teams; size_t limit; Plan plan; };
+    static std::mutex mu;
+    static std::vector<Entry> cache;
+    std::lock_guard<std::mutex> lock(mu);
+    for (const Entry& e : cache)
+        if (e.type == type && e.k == k && e.nslots == nslots && e.teams == teams && e.limit == limit) return e.plan;
+    const Plan pl = make_plan_uncached(type, k, nslots, teams, limit);
+    if (cache.size() >= 256) cache.clear();
+    cache.push_back(Entry{type, k, nslots, teams, limit, pl});
+    return pl;
+}
+
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -997,12 +1013,31 @@ bool make_stage_map(CUtensorMap* map, const MParams& p, const uint8_t* w) {
     if (!enc || p.ids || p.sub_groups > 1 || p.dense_stage || p.pitch % 8 || p.pitch / 8 > 256 || p.slice_bytes % 16 || p.row_bytes % 16) return false;
     static const bool off = [] { const char* v = getenv("HF2Q_CUDA_MMA_TMAP"); return v && v[0] == '0'; }();      // tuning aid
     if (off) return false;
+    // Encoding takes about a microsecond of host time and weights stay where they are: remember the
+    // maps by (address, geometry).  A map holds nothing but those, so a stale entry cannot be wrong.
+    struct Entry { const uint8_t* w; uint32_t row_bytes, n, pitch; CUtensorMap map; };
+    static std::mutex mu;
+    static std::unordered_map<uint64_t, Entry> cache;
+    const uint64_t hkey = reinterpret_cast<uint64_t>(w) ^ (static_cast<uint64_t>(p.n) << 40) ^ (static_cast<uint64_t>(p.pitch) << 52);
+    {
+        std::lock_guard<std::mutex> lock(mu);
+        const auto it = cache.find(hkey);
+        if (it != cache.end() && it->second.w == w && it->second.row_bytes == p.row_bytes && it->second.n == p.n && it->second.pitch == p.pitch) {
+            *map = it->second.map;
+            return true;
+        }
+    }
     cuuint64_t dims[2] = {p.row_bytes / 8, p.n};
     cuuint64_t strides[1] = {p.row_bytes};
     cuuint32_t box[2] = {p.pitch / 8, ROWS};
     cuuint32_t es[2] = {1, 1};
-    return enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT64, 2, const_cast<uint8_t*>(w), dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
-               CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+    if (enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT64, 2, const_cast<uint8_t*>(w), dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
+            CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+        return false;
+    std::lock_guard<std::mutex> lock(mu);
+    if (cache.size() >= 8192) cache.clear();
+    cache[hkey] = Entry{w, p.row_bytes, p.n, p.pitch, *map};
+    return true;
 }
 
 template <uint32_t TYPE, int NTEAMS, bool PHASED, bool SUBG, bool EXT>
