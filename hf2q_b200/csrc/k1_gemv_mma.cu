@@ -175,7 +175,8 @@ struct K45Row {
         scale_min_k4(2 * c + 1, hd.y, hd.z, hd.w, sc2, m2);
         // scale * 2^10 as f16x2 (<= 64512): code*2^-24 * scale*2^10 = code*scale*2^-14, exact
         const __half2 s1h = __half2half2(__uint2half_rn(sc1 << 10));
-        const __half2 s2h = __half2half2(__uint2half_rn(sc2 << 10));
+        // (Q4_K takes the high nibbles where they are, i.e. as 16 * code, and folds the 1/16 into this scale)
+        const __half2 s2h = __half2half2(__uint2half_rn(sc2 << (Q5 ? 10 : 6)));
         s1 = *reinterpret_cast<const uint32_t*>(&s1h);
         s2 = *reinterpret_cast<const uint32_t*>(&s2h);
         am = hb ? 0u : (m1 | (m2 << 16));
@@ -184,7 +185,8 @@ struct K45Row {
     }
     __device__ __forceinline__ void codes(int i, int c, uint32_t& lo, uint32_t& hi) const {
         lo = qv[i] & 0x0F0F0F0Fu;
-        hi = (qv[i] >> 4) & 0x0F0F0F0Fu;
+        if constexpr (!Q5) hi = qv[i] & 0xF0F0F0F0u;
+        else hi = (qv[i] >> 4) & 0x0F0F0F0Fu;
         if constexpr (Q5) {
             lo |= ((gv[i] >> (2 * c)) & 0x01010101u) << 4;
             hi |= ((gv[i] >> (2 * c + 1)) & 0x01010101u) << 4;

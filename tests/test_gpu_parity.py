@@ -199,8 +199,8 @@ def test_host_buffer_call(gpu_ctx):
     assert rel_l2(y, _ref(t, raw, x, n, k)) < GATE
     # queued form: more calls than staging slots, different shapes, one wait at the end
     outs = []
-    for i in range(7):
-        mi = 1 + i % 3
+    for i in range(21):                    # 8 staging slots: every slot is reused, and grows when a larger m arrives
+        mi = (1 + i % 3) if i != 13 else 12
         xi = make_x(mi, k, seed=20 + i)
         yi = np.full((mi, n), np.nan, np.float32)
         hq.ops.quantized_matmul_host(gpu_ctx, xi, w, yi, mi, wait=False)
