@@ -201,17 +201,17 @@ __device__ __forceinline__ void half_k45(const uint8_t* blk0, const uint8_t* blk
     K45Row<Q5> r0, r1;
     r0.load(blk0, c, hb);
     r1.load(blk1, c, hb);
-    const uint32_t eb = e0 + 64 * c + 16 * hb;
+    const uint32_t xb = e0 + 128 * half + 4 * t;          // the panel's half blocks are permuted: 64 hi + 16 i + 4 t
     float acc[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
         uint32_t lo0, hi0, lo1, hi1;
         r0.codes(i, c, lo0, hi0);
         r1.codes(i, c, lo1, hi1);
-        const uint2 xl = ld_x4(xrow, eb + 4 * i);
+        const uint2 xl = ld_x4(xrow, xb + 16 * i);
         mma_acc(acc, hmul2_bits(sub01(lo0), r0.s1), hmul2_bits(sub01(lo1), r1.s1),
                 hmul2_bits(sub23(lo0), r0.s1), hmul2_bits(sub23(lo1), r1.s1), xl.x, xl.y);
-        const uint2 xh = ld_x4(xrow, eb + 32 + 4 * i);
+        const uint2 xh = ld_x4(xrow, xb + 64 + 16 * i);
         mma_acc(acc, hmul2_bits(sub01(hi0), r0.s2), hmul2_bits(sub01(hi1), r1.s2),
                 hmul2_bits(sub23(hi0), r0.s2), hmul2_bits(sub23(hi1), r1.s2), xh.x, xh.y);
     }
@@ -370,9 +370,23 @@ __device__ __forceinline__ void build_panel(const void* x, bool x_bf16, uint32_t
         return h;
     };
     auto store = [&](uint32_t s, uint32_t pos, const __half2 (&h)[4], float acc) {
-        *reinterpret_cast<uint4*>(xh + s * xpitch + 16 * pos) =
-            make_uint4(*reinterpret_cast<const uint32_t*>(&h[0]), *reinterpret_cast<const uint32_t*>(&h[1]),
-                       *reinterpret_cast<const uint32_t*>(&h[2]), *reinterpret_cast<const uint32_t*>(&h[3]));
+        if constexpr (K45) {
+            // Q4_K / Q5_K lanes (g, t) take the elements 64 (t>>1) + 32 hi + 16 (t&1) + 4 i .. +3 of a
+            // 128-element half block in MMA step (i, hi): the panel keeps every half block permuted in
+            // 4-element granules to  64 hi + 16 i + 4 t, so that the four lanes of a step read 32
+            // consecutive bytes (the natural order puts lanes 0/2 and 1/3 on the same banks, and all
+            // eight columns on a quarter of the banks).  This thread's 8 elements are two granules
+            // with the same (t, hi) and i = 2 (pos & 1), + 1.
+            const uint32_t p4 = pos & 15u;
+            const uint32_t g0 = ((p4 >> 2) & 1u) << 4 | (p4 & 1u) << 3 | (p4 >> 3) << 1 | ((p4 >> 1) & 1u);
+            uint8_t* dst = xh + s * xpitch + 16 * (pos & ~15u) + 8 * g0;
+            *reinterpret_cast<uint2*>(dst) = make_uint2(*reinterpret_cast<const uint32_t*>(&h[0]), *reinterpret_cast<const uint32_t*>(&h[1]));
+            *reinterpret_cast<uint2*>(dst + 32) = make_uint2(*reinterpret_cast<const uint32_t*>(&h[2]), *reinterpret_cast<const uint32_t*>(&h[3]));
+        } else {
+            *reinterpret_cast<uint4*>(xh + s * xpitch + 16 * pos) =
+                make_uint4(*reinterpret_cast<const uint32_t*>(&h[0]), *reinterpret_cast<const uint32_t*>(&h[1]),
+                           *reinterpret_cast<const uint32_t*>(&h[2]), *reinterpret_cast<const uint32_t*>(&h[3]));
+        }
         acc += __shfl_xor_sync(0xffffffffu, acc, 1);
         if constexpr (SUB == 32) acc += __shfl_xor_sync(0xffffffffu, acc, 2);
         if ((lane & (SUB / 8 - 1)) == 0) {
@@ -429,8 +443,12 @@ __device__ __forceinline__ void build_panel(const void* x, bool x_bf16, uint32_t
         }
         if (!mbar_wait_bounded(xbar, xparity, status)) return;
         for (uint32_t pos = ctid; pos < k8; pos += CTH)
-            for (uint32_t sl = 0; sl < nslots; ++sl)
-                convert_bf16(*reinterpret_cast<const uint4*>(xh + sl * xpitch + 16 * pos), sl, pos);
+            for (uint32_t sl = 0; sl < nslots; ++sl) {
+                const uint4 raw = *reinterpret_cast<const uint4*>(xh + sl * xpitch + 16 * pos);
+                if constexpr (K45) __syncwarp();          // the permuted stores land in other lanes' sources (same half block, same warp)
+                convert_bf16(raw, sl, pos);
+                if constexpr (K45) __syncwarp();
+            }
     } else if (x_bf16) {
         if constexpr (U >= 8) {
             if (k8 <= CTH) bf16_rounds(std::integral_constant<int, 8>{}, std::integral_constant<int, 1>{});
@@ -523,7 +541,7 @@ __global__ void __launch_bounds__((NTEAMS * TEAM + 2) * 32, 1) gemv_mma_kernel(c
     uint8_t* xh = reinterpret_cast<uint8_t*>(scr + CW * 16 * 8);                 // [nslots][xpitch]
     uint8_t* sxp = xh + p.nslots * p.xpitch;
     const uint32_t kphase = min(spp * SLICE_ELEMS, p.k);                        // elements of k resident at a time
-    const uint32_t sx_slot_bytes = (kphase >> 8) * SXB;                         // K45 / Q6 panels
+    const uint32_t sx_slot_bytes = (kphase >> 8) * SXB + 16;                    // K45 / Q6 panels; +16: columns 4 banks apart
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     uint32_t slot = blockIdx.y;
@@ -904,7 +922,7 @@ size_t smem_base_bytes(uint32_t type, uint32_t kphase, uint32_t nslots, int team
     const size_t fixed = 256 + (2 * cw * 128 + cw * 16 * 8) * 4;
     const size_t xbytes = static_cast<size_t>(nslots) * (2 * static_cast<size_t>(kphase) + 32);
     const size_t sxbytes = leg ? static_cast<size_t>(kphase / 32) * 8 * 4
-                               : static_cast<size_t>(nslots) * (kphase / 256) * (k45 ? 32 : 64);
+                               : static_cast<size_t>(nslots) * ((kphase / 256) * (k45 ? 32 : 64) + 16);
     return fixed + xbytes + sxbytes;
 }
 // Bytes between rows of a stage: the slice plus 0 or 16 bytes of padding such that consecutive
