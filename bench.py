@@ -439,6 +439,29 @@ def main() -> None:
         if not err < 1e-3:
             raise SystemExit(f"parity check failed before timing: rel L2 {err}")
 
+    # Several GPUs: one trial step of the fused form.  A rank whose bounded waits ran out (a peer's
+    # columns never arrived) or whose step took implausibly long votes to drop it, and then every rank
+    # uses NCCL all-gathers instead: the bench must end either way.
+    if gather is not None:
+        barrier()
+        t_trial = time.perf_counter()
+        step()
+        torch.cuda.synchronize()
+        bad = time.perf_counter() - t_trial > 0.5
+        try:
+            ctx.check_status()
+        except hq.Hf2qError:
+            bad = True
+        vote = torch.tensor([1.0 if bad else 0.0], device=dev)
+        dist.all_reduce(vote, op=dist.ReduceOp.MAX)
+        if float(vote.item()) > 0:
+            if rank == 0:
+                print("[bench] the fused gather did not complete its trial step; using NCCL all-gathers after each product (eager launches)",
+                      file=sys.stderr)
+            gather.close()
+            gather = None
+            ygath = {(n, m): torch.empty((world, m, n), dtype=torch.float32, device=dev) for n, _ in SHAPES for m in TOKENS}
+
     for _ in range(args.warmup):
         step()
     barrier()
