@@ -154,78 +154,91 @@ __device__ __forceinline__ uint2 ld_x4(const uint8_t* xrow, uint32_t e) {
 }
 constexpr float TWO24 = 16777216.0f;
 
-// ---- Q4_K / Q5_K: half a block (128 elements = chunks 2*half, 2*half+1) of rows g and g+8.
-// Lane t owns 16 bytes of qs per row: chunk c = 2*half + (t>>1), bytes 16*(t&1)..+15, i.e. 16
-// elements of sub-block 2c (low nibbles) and 16 of sub-block 2c+1 (high nibbles).
-template <bool Q5>
-struct K45Row {
-    uint32_t qv[4], gv[4], s1, s2, am;
-    float d, dm;
-    __device__ __forceinline__ void load(const uint8_t* blk, int c, int hb) {
-        constexpr int QS = Q5 ? 48 : 16;
-        const uint4 hd = *reinterpret_cast<const uint4*>(blk);
-        const uint4 qa = *reinterpret_cast<const uint4*>(blk + QS + 32 * c + 16 * hb);
-        qv[0] = qa.x; qv[1] = qa.y; qv[2] = qa.z; qv[3] = qa.w;
-        if constexpr (Q5) {
-            const uint4 ga = *reinterpret_cast<const uint4*>(blk + 16 + 16 * hb);
-            gv[0] = ga.x; gv[1] = ga.y; gv[2] = ga.z; gv[3] = ga.w;
-        }
-        uint32_t sc1, m1, sc2, m2;
-        scale_min_k4(2 * c, hd.y, hd.z, hd.w, sc1, m1);
-        scale_min_k4(2 * c + 1, hd.y, hd.z, hd.w, sc2, m2);
-        // scale * 2^10 as f16x2 (<= 64512): code*2^-24 * scale*2^10 = code*scale*2^-14, exact
-        const __half2 s1h = __half2half2(__uint2half_rn(sc1 << 10));
-        // (Q4_K takes the high nibbles where they are, i.e. as 16 * code, and folds the 1/16 into this scale)
-        const __half2 s2h = __half2half2(__uint2half_rn(sc2 << (Q5 ? 10 : 6)));
-        s1 = *reinterpret_cast<const uint32_t*>(&s1h);
-        s2 = *reinterpret_cast<const uint32_t*>(&s2h);
-        am = hb ? 0u : (m1 | (m2 << 16));
-        d = f16_bits_to_f32(hd.x & 0xffffu) * 16384.0f;
-        dm = f16_bits_to_f32(hd.x >> 16) * TWO24;
-    }
-    __device__ __forceinline__ void codes(int i, int c, uint32_t& lo, uint32_t& hi) const {
-        lo = qv[i] & 0x0F0F0F0Fu;
-        if constexpr (!Q5) hi = qv[i] & 0xF0F0F0F0u;
-        else hi = (qv[i] >> 4) & 0x0F0F0F0Fu;
-        if constexpr (Q5) {
-            lo |= ((gv[i] >> (2 * c)) & 0x01010101u) << 4;
-            hi |= ((gv[i] >> (2 * c + 1)) & 0x01010101u) << 4;
-        }
-    }
-};
-
+// ---- Q4_K / Q5_K: half a block (128 elements = chunks 2*half, 2*half+1 = sub-blocks 4*half..+3) of
+// rows g and g+8.  A chunk is 32 bytes whose low nibbles are sub-block 2c and whose high nibbles are
+// sub-block 2c+1.  Lane t takes words t and t+4 of each chunk, so an MMA step (sub-block, j) covers
+// the 16 consecutive elements 16j..16j+15 of ONE sub-block (lane t: 16j+4t..+3): the four lanes read
+// 32 consecutive bytes of activations, and the sub-block's scale is applied to the sum of its two
+// steps in f32 instead of to every code.  Lane t decodes the scale and min of sub-block 4*half+t for
+// both rows and hands the scales to the other lanes through the warp's scratch.
 template <bool Q5>
 __device__ __forceinline__ void half_k45(const uint8_t* blk0, const uint8_t* blk1, int half, uint32_t e0,
-                                         const uint8_t* xrow, const uint8_t* sxblk, int t, float (&f)[4]) {
-    const int c = 2 * half + (t >> 1), hb = t & 1;
-    K45Row<Q5> r0, r1;
-    r0.load(blk0, c, hb);
-    r1.load(blk1, c, hb);
-    const uint32_t xb = e0 + 128 * half + 4 * t;          // the panel's half blocks are permuted: 64 hi + 16 i + 4 t
-    float acc[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        uint32_t lo0, hi0, lo1, hi1;
-        r0.codes(i, c, lo0, hi0);
-        r1.codes(i, c, lo1, hi1);
-        const uint2 xl = ld_x4(xrow, xb + 16 * i);
-        mma_acc(acc, hmul2_bits(sub01(lo0), r0.s1), hmul2_bits(sub01(lo1), r1.s1),
-                hmul2_bits(sub23(lo0), r0.s1), hmul2_bits(sub23(lo1), r1.s1), xl.x, xl.y);
-        const uint2 xh = ld_x4(xrow, xb + 64 + 16 * i);
-        mma_acc(acc, hmul2_bits(sub01(hi0), r0.s2), hmul2_bits(sub01(hi1), r1.s2),
-                hmul2_bits(sub23(hi0), r0.s2), hmul2_bits(sub23(hi1), r1.s2), xh.x, xh.y);
-    }
-    // -dmin * sum_j m_j * Sx_j over this half's four sub-blocks: lanes with (t&1)==0 carry
-    // (m_2c, m_2c+1) against Sx_hi on k-columns (2t, 2t+1) and against Sx_lo on (2t+8, 2t+9);
-    // odd lanes carry zeros.  The panel stores, per block, hi[8] then lo[8] (f16).
-    const uint32_t bs0 = *reinterpret_cast<const uint32_t*>(sxblk + 4 * c);
-    const uint32_t bs1 = *reinterpret_cast<const uint32_t*>(sxblk + 16 + 4 * c);
+                                         const uint8_t* xrow, const uint8_t* sxblk, float* scrw, int g, int t, float (&f)[4]) {
+    constexpr int QS = Q5 ? 48 : 16;
+    const int sb = 4 * half + t;
+    const uint4 h0 = *reinterpret_cast<const uint4*>(blk0), h1 = *reinterpret_cast<const uint4*>(blk1);
+    uint32_t sc0, m0, sc1, m1;
+    scale_min_k4(sb, h0.y, h0.z, h0.w, sc0, m0);
+    scale_min_k4(sb, h1.y, h1.z, h1.w, sc1, m1);
+    // codes enter the MMA as f16 subnormals code * 2^-24; Q4_K takes the high nibbles (odd sub-blocks)
+    // where they are, i.e. as 16 * code.  d * 2^k * scale is exact in f32.
+    const float unit = (!Q5 && (t & 1)) ? 1048576.0f : TWO24;
+    const float s0 = f16_bits_to_f32(h0.x & 0xffffu) * unit * static_cast<float>(sc0);
+    const float s1 = f16_bits_to_f32(h1.x & 0xffffu) * unit * static_cast<float>(sc1);
+    __syncwarp();                                                        // previous reads of scratch done
+    *reinterpret_cast<float2*>(scrw + 2 * (8 * t + g)) = make_float2(s0, s1);
+    __syncwarp();
+    // -dmin * sum_j m_j * Sx_j over the half's four sub-blocks: lane t carries m of ITS sub-block as
+    // the integer subnormal on k-column 2t (against the hi part of Sx) and 2t+8 (lo part); the
+    // neighbouring columns are zero on the A side.  The panel stores, per block, hi[8] then lo[8] (f16).
     float mn[4];
-    mma_new(mn, r0.am, r1.am, r0.am, r1.am, bs0, bs1);
-    f[0] += r0.d * acc[0] - r0.dm * mn[0];
-    f[1] += r0.d * acc[1] - r0.dm * mn[1];
-    f[2] += r1.d * acc[2] - r1.dm * mn[2];
-    f[3] += r1.d * acc[3] - r1.dm * mn[3];
+    mma_new(mn, m0, m1, m0, m1, ld_u16(sxblk + 2 * sb), ld_u16(sxblk + 16 + 2 * sb));
+    const float dm0 = f16_bits_to_f32(h0.x >> 16) * TWO24, dm1 = f16_bits_to_f32(h1.x >> 16) * TWO24;
+    const uint8_t* q0 = blk0 + QS + 64 * half + 4 * t;
+    const uint8_t* q1 = blk1 + QS + 64 * half + 4 * t;
+    uint32_t gv0[2] = {0u, 0u}, gv1[2] = {0u, 0u};
+    if constexpr (Q5) {
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+            gv0[j] = *reinterpret_cast<const uint32_t*>(blk0 + 16 + 16 * j + 4 * t);
+            gv1[j] = *reinterpret_cast<const uint32_t*>(blk1 + 16 + 16 * j + 4 * t);
+        }
+    }
+    const float* sread = scrw + 2 * g;
+#pragma unroll
+    for (int c = 0; c < 2; ++c) {
+        uint32_t w0[2], w1[2];
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+            w0[j] = *reinterpret_cast<const uint32_t*>(q0 + 32 * c + 16 * j);
+            w1[j] = *reinterpret_cast<const uint32_t*>(q1 + 32 * c + 16 * j);
+        }
+#pragma unroll
+        for (int nib = 0; nib < 2; ++nib) {
+            float acc[4];
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+                uint32_t c0, c1;
+                if (nib == 0) {
+                    c0 = w0[j] & 0x0F0F0F0Fu;
+                    c1 = w1[j] & 0x0F0F0F0Fu;
+                } else if constexpr (Q5) {
+                    c0 = (w0[j] >> 4) & 0x0F0F0F0Fu;
+                    c1 = (w1[j] >> 4) & 0x0F0F0F0Fu;
+                } else {
+                    c0 = w0[j] & 0xF0F0F0F0u;
+                    c1 = w1[j] & 0xF0F0F0F0u;
+                }
+                if constexpr (Q5) {
+                    const int bit = 2 * (2 * half + c) + nib;
+                    c0 |= ((gv0[j] >> bit) & 0x01010101u) << 4;
+                    c1 |= ((gv1[j] >> bit) & 0x01010101u) << 4;
+                }
+                const uint2 xv = ld_x4(xrow, e0 + 128 * half + 64 * c + 32 * nib + 16 * j + 4 * t);
+                if (j == 0) mma_new(acc, sub01(c0), sub01(c1), sub23(c0), sub23(c1), xv.x, xv.y);
+                else mma_acc(acc, sub01(c0), sub01(c1), sub23(c0), sub23(c1), xv.x, xv.y);
+            }
+            const float2 sc = *reinterpret_cast<const float2*>(sread + 16 * (2 * c + nib));
+            f[0] += sc.x * acc[0];
+            f[1] += sc.x * acc[1];
+            f[2] += sc.y * acc[2];
+            f[3] += sc.y * acc[3];
+        }
+    }
+    f[0] -= dm0 * mn[0];
+    f[1] -= dm0 * mn[1];
+    f[2] -= dm1 * mn[2];
+    f[3] -= dm1 * mn[3];
 }
 
 // ---- Q6_K: half n (128 elements, sub-blocks 8n..8n+7) of one block of rows g and g+8; every MMA
@@ -370,23 +383,9 @@ __device__ __forceinline__ void build_panel(const void* x, bool x_bf16, uint32_t
         return h;
     };
     auto store = [&](uint32_t s, uint32_t pos, const __half2 (&h)[4], float acc) {
-        if constexpr (K45) {
-            // Q4_K / Q5_K lanes (g, t) take the elements 64 (t>>1) + 32 hi + 16 (t&1) + 4 i .. +3 of a
-            // 128-element half block in MMA step (i, hi): the panel keeps every half block permuted in
-            // 4-element granules to  64 hi + 16 i + 4 t, so that the four lanes of a step read 32
-            // consecutive bytes (the natural order puts lanes 0/2 and 1/3 on the same banks, and all
-            // eight columns on a quarter of the banks).  This thread's 8 elements are two granules
-            // with the same (t, hi) and i = 2 (pos & 1), + 1.
-            const uint32_t p4 = pos & 15u;
-            const uint32_t g0 = ((p4 >> 2) & 1u) << 4 | (p4 & 1u) << 3 | (p4 >> 3) << 1 | ((p4 >> 1) & 1u);
-            uint8_t* dst = xh + s * xpitch + 16 * (pos & ~15u) + 8 * g0;
-            *reinterpret_cast<uint2*>(dst) = make_uint2(*reinterpret_cast<const uint32_t*>(&h[0]), *reinterpret_cast<const uint32_t*>(&h[1]));
-            *reinterpret_cast<uint2*>(dst + 32) = make_uint2(*reinterpret_cast<const uint32_t*>(&h[2]), *reinterpret_cast<const uint32_t*>(&h[3]));
-        } else {
-            *reinterpret_cast<uint4*>(xh + s * xpitch + 16 * pos) =
-                make_uint4(*reinterpret_cast<const uint32_t*>(&h[0]), *reinterpret_cast<const uint32_t*>(&h[1]),
-                           *reinterpret_cast<const uint32_t*>(&h[2]), *reinterpret_cast<const uint32_t*>(&h[3]));
-        }
+        *reinterpret_cast<uint4*>(xh + s * xpitch + 16 * pos) =
+            make_uint4(*reinterpret_cast<const uint32_t*>(&h[0]), *reinterpret_cast<const uint32_t*>(&h[1]),
+                       *reinterpret_cast<const uint32_t*>(&h[2]), *reinterpret_cast<const uint32_t*>(&h[3]));
         acc += __shfl_xor_sync(0xffffffffu, acc, 1);
         if constexpr (SUB == 32) acc += __shfl_xor_sync(0xffffffffu, acc, 2);
         if ((lane & (SUB / 8 - 1)) == 0) {
@@ -444,10 +443,7 @@ __device__ __forceinline__ void build_panel(const void* x, bool x_bf16, uint32_t
         if (!mbar_wait_bounded(xbar, xparity, status)) return;
         for (uint32_t pos = ctid; pos < k8; pos += CTH)
             for (uint32_t sl = 0; sl < nslots; ++sl) {
-                const uint4 raw = *reinterpret_cast<const uint4*>(xh + sl * xpitch + 16 * pos);
-                if constexpr (K45) __syncwarp();          // the permuted stores land in other lanes' sources (same half block, same warp)
-                convert_bf16(raw, sl, pos);
-                if constexpr (K45) __syncwarp();
+                convert_bf16(*reinterpret_cast<const uint4*>(xh + sl * xpitch + 16 * pos), sl, pos);
             }
     } else if (x_bf16) {
         if constexpr (U >= 8) {
@@ -868,8 +864,8 @@ __global__ void __launch_bounds__((NTEAMS * TEAM + 2) * 32, 1) gemv_mma_kernel(c
                     const uint8_t* b0 = r0 + bb * G.bytes;
                     const uint8_t* b1 = r1 + bb * G.bytes;
                     const uint8_t* sx = sxslot + (e0 >> 8) * SXB;
-                    half_k45<TYPE == HF2Q_TYPE_Q5_K>(b0, b1, 0, e0, xrow, sx, t, f);
-                    half_k45<TYPE == HF2Q_TYPE_Q5_K>(b0, b1, 1, e0, xrow, sx, t, f);
+                    half_k45<TYPE == HF2Q_TYPE_Q5_K>(b0, b1, 0, e0, xrow, sx, scr0 - 8 * g, g, t, f);
+                    half_k45<TYPE == HF2Q_TYPE_Q5_K>(b0, b1, 1, e0, xrow, sx, scr0 - 8 * g, g, t, f);
                 } else if constexpr (Q6) {
                     const uint8_t* b0 = r0 + bb * 210;
                     const uint8_t* b1 = r1 + bb * 210;
