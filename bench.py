@@ -264,6 +264,45 @@ def run_secondary(args) -> None:
                 "roofline": {"bound": "tensor", "achieved": round(val, 1), "peak": peak, "unit": "TFLOP/s",
                              "frac": round(val / peak, 4), "peak_source": f"of {kind}", "kernel": "gemm_tc_kernel", "traffic": None},
                 "per_case_TFLOPs": rows}
+    elif args.workload == "matvec":
+        # every block format on the decode shapes: per-launch time from a CUDA graph that walks 8
+        # distinct copies of the matrix (so weights come from HBM), bf16 activations
+        peak_h, kind_h = measured_hbm_peak()
+        shapes = [(6144, 4096), (4096, 4096), (28672, 4096), (4096, 14336)]
+        per, tot_b, tot_s = {}, 0.0, 0.0
+        for t in ([int(args.qtype)] if args.qtype else [2, 8, 12, 13, 14]):
+            for n, k in shapes:
+                ws = [hq.load_quant_weight(ctx, random_weight(t, n, k), t, n, k) for _ in range(8)]
+                rb = oracle.row_bytes(t, k)
+                for m in (1, 4, 8):
+                    x = torch.randn(m, k, device=dev).bfloat16()
+                    y = torch.empty(m, n, device=dev)
+                    pr = hq.GgmlQuantizedMatmulParams(m, n, k, t)
+
+                    def walk():
+                        for w in ws:
+                            hq.quantized_matmul_ggml(ctx, x, w, y, pr)
+
+                    for _ in range(3):
+                        walk()
+                    torch.cuda.synchronize()
+                    graph = torch.cuda.CUDAGraph()
+                    with torch.cuda.graph(graph):
+                        walk()
+                    dt = timed(graph.replay, max(3, min(args.steps, 20))) / len(ws)
+                    b = n * rb + 2 * m * k + 4 * m * n
+                    per[f"{oracle.TYPE_NAMES[t]}_{n}x{k}_m{m}"] = {"us": round(dt * 1e6, 2), "GBps": round(b / dt / 1e9, 1)}
+                    tot_b += b
+                    tot_s += dt
+                del ws
+        val = tot_b / tot_s / 1e9
+        line = {"metric": "dequant-GEMV HBM GB/s (all block formats)", "value": round(val, 1), "unit": "GB/s", "n_gpus": 1,
+                "higher_is_better": True, "dtype": "f32", "data": "synthetic",
+                "config": {"workload": "decode mat-vec, 4 shapes x m in {1,4,8} x block formats, bf16 activations; "
+                                       "CUDA graph over 8 copies of each matrix (inputs larger than L2)"},
+                "roofline": {"bound": "hbm", "achieved": round(val, 1), "peak": peak_h, "unit": "GB/s", "frac": round(val / peak_h, 4),
+                             "peak_source": f"of {kind_h}", "kernel": "gemv_mma_kernel", "traffic": None},
+                "per_launch": per}
     else:
         t, E, H, I, topk = 13, 256, 2048, 512, 8
         sg, sd = hq.expert_stride(t, I, H), hq.expert_stride(t, H, I)
@@ -346,7 +385,8 @@ def main() -> None:
                     help="several GPUs: products do not wait for the previous product's columns (analysis aid)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-graph", action="store_true", help="issue launches eagerly instead of replaying a CUDA graph")
-    ap.add_argument("--workload", default="gemv", choices=["gemv", "gemm", "moe"],
+    ap.add_argument("--qtype", default="", help="matvec: one ggml type number (2, 8, 12, 13, 14) instead of all five")
+    ap.add_argument("--workload", default="gemv", choices=["gemv", "gemm", "moe", "matvec"],
                     help="gemv: the headline Q6_K decode sweep (default); gemm: Q4_K_M prefill GEMM sweep; "
                          "moe: Qwen3-style A3B expert layer (Q5_K mul_mat_id)")
     ap.add_argument("--tokens", type=int, default=0, help="gemm/moe: one token count instead of the sweep")
