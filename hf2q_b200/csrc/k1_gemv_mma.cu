@@ -101,10 +101,12 @@ struct MParams {
 #ifdef HF2Q_MMA_PROBE
 // timeline probe: [launch parity][CTA][event] global-timer stamps
 __device__ unsigned long long g_probe_ts[2 * 160 * 8];
+__device__ uint32_t g_probe_parity;
 __device__ __forceinline__ void probe_stamp(const MParams& p, int ev) {
     unsigned long long t;
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
     if (blockIdx.x < 160 && blockIdx.y == 0) g_probe_ts[((p.launch_id & 1) * 160 + blockIdx.x) * 8 + ev] = t;
+    if (ev == 0 && blockIdx.x == 0) g_probe_parity = p.launch_id;
 }
 #define PROBE_STAMP(ev) probe_stamp(p, ev)
 #else
@@ -401,13 +403,21 @@ __device__ __forceinline__ void build_panel(const void* x, bool x_bf16, uint32_t
             }
         }
     };
+    // bf16 -> f16 is exact inside the f16 normal range, so the sub-block sums are taken from the f32
+    // values; out-of-range values are clamped, and noticed through a running maximum of |raw f16|
+    __half2 seen = __float2half2_rn(0.f);
     auto convert_bf16 = [&](const uint4& r, uint32_t s, uint32_t pos) {
         const uint32_t rr[4] = {r.x, r.y, r.z, r.w};
         __half2 h[4];
         float acc = 0.f;
 #pragma unroll
-        for (int j = 0; j < 4; ++j)
-            h[j] = pack(__uint_as_float(rr[j] << 16), __uint_as_float(rr[j] & 0xffff0000u), acc);
+        for (int j = 0; j < 4; ++j) {
+            const float a = __uint_as_float(rr[j] << 16), b = __uint_as_float(rr[j] & 0xffff0000u);
+            const __half2 raw = __floats2half2_rn(a, b);
+            seen = __hmax2(seen, __habs2(raw));
+            h[j] = __hmin2(__hmax2(raw, __hneg2(lim)), lim);
+            acc += a + b;
+        }
         store(s, pos, h, acc);
     };
     // k8 is a multiple of 32, so a warp is either wholly inside or wholly outside the loops.
@@ -415,8 +425,16 @@ __device__ __forceinline__ void build_panel(const void* x, bool x_bf16, uint32_t
     auto bf16_rounds = [&](auto su_c, auto pu_c) {
         constexpr int SU = decltype(su_c)::value, PU = decltype(pu_c)::value;
         const __nv_bfloat16* src = static_cast<const __nv_bfloat16*>(x) + static_cast<size_t>(xrow_idx) * k + k0;
+        asm volatile("griddepcontrol.wait;" ::: "memory");               // x may be an earlier kernel's output
         for (uint32_t pos0 = ctid; pos0 < k8; pos0 += PU * CTH) {
             for (uint32_t s0 = 0; s0 < nslots; s0 += SU) {
+#ifdef HF2Q_MMA_PROBE
+                if (threadIdx.x == 0 && pos0 == 0 && s0 == 0 && k0 == 0) {
+                    unsigned long long tnow;
+                    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(tnow));
+                    if (blockIdx.x < 160 && blockIdx.y == 0) g_probe_ts[((g_probe_parity & 1) * 160 + blockIdx.x) * 8 + 7] = tnow;
+                }
+#endif
                 uint4 ra[SU * PU];
 #pragma unroll
                 for (int a = 0; a < SU; ++a)
@@ -429,12 +447,20 @@ __device__ __forceinline__ void build_panel(const void* x, bool x_bf16, uint32_t
 #pragma unroll
                     for (int b = 0; b < PU; ++b)
                         if (s0 + a < nslots && pos0 + b * CTH < k8) convert_bf16(ra[a * PU + b], s0 + a, pos0 + b * CTH);
+#ifdef HF2Q_MMA_PROBE
+                if (threadIdx.x == 0 && pos0 == 0 && s0 == 0 && k0 == 0) {
+                    unsigned long long tnow;
+                    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(tnow));
+                    if (blockIdx.x < 160 && blockIdx.y == 0) g_probe_ts[((g_probe_parity & 1) * 160 + blockIdx.x) * 8 + 1] = tnow + (*reinterpret_cast<volatile uint32_t*>(xh) & 0u);
+                }
+#endif
             }
         }
     };
     if (x_bf16 && INPLACE) {
         // bf16 and f16 are both two bytes: the raw rows are bulk-copied into the panel's own place
         // (one asynchronous copy per column, all in flight at once) and converted there
+        asm volatile("griddepcontrol.wait;" ::: "memory");               // x may be an earlier kernel's output
         if (ctid < nslots) {
             if (ctid == 0) mbar_arrive_expect_tx(xbar, nslots * klen * 2);
             __syncwarp(__activemask());
@@ -453,7 +479,8 @@ __device__ __forceinline__ void build_panel(const void* x, bool x_bf16, uint32_t
         } else {
             bf16_rounds(std::integral_constant<int, U>{}, std::integral_constant<int, 1>{});
         }
-    } else
+    } else {
+    asm volatile("griddepcontrol.wait;" ::: "memory");                   // x may be an earlier kernel's output
     for (uint32_t pos = ctid; pos < k8; pos += CTH) {
         {
             constexpr int UT = U > 4 ? 4 : (U > 1 ? U / 2 : 1);      // activation rows per round (two float4 each)
@@ -489,6 +516,9 @@ __device__ __forceinline__ void build_panel(const void* x, bool x_bf16, uint32_t
             }
         }
     }
+    }
+    // (a NaN in `seen` fails the comparison as well)
+    if (!(__hle(__low2half(seen), __low2half(lim)) && __hle(__high2half(seen), __low2half(lim)))) clipped = 1;
     if (clipped) atomicOr(status, STATUS_X_CLIPPED);
 }
 
@@ -654,7 +684,6 @@ __global__ void __launch_bounds__((NTEAMS * TEAM + 2) * 32, 1) gemv_mma_kernel(c
                 }
                 s0 = s1;
             }
-            if (lane == 0) PROBE_STAMP(6);
         }
         if (!synced) cta_arrive_n<(NTEAMS * TEAM + 2) * 32>();
         return;
@@ -679,7 +708,6 @@ __global__ void __launch_bounds__((NTEAMS * TEAM + 2) * 32, 1) gemv_mma_kernel(c
                 const bool second = sw && (gi & 1u);
                 const uint32_t rs = fl & 1;
                 if (!mbar_wait_bounded(&red_full[rs], (fl >> 1) & 1, p.status)) return;
-                if (lane == 0) PROBE_STAMP(7);
                 // partial sums sit at [team][block of the stage]; a sub-group's blocks are adjacent
                 const uint32_t nb = nsub > 1 ? p.last_nblk : static_cast<uint32_t>(TEAM);
                 for (uint32_t sg = 0; sg < nsub; ++sg) {
@@ -760,12 +788,21 @@ __global__ void __launch_bounds__((NTEAMS * TEAM + 2) * 32, 1) gemv_mma_kernel(c
 
     // ---------------- consumers ----------------
     const int ctid = threadIdx.x;
-    asm volatile("griddepcontrol.wait;" ::: "memory");                    // before reading x / writing y
+    // Ahead of the dependency wait: ask for the activations' lines (and their address translation).
+    // A prefetch returns no data, so it may run while the previous kernel is still writing them.
+    if (!p.ids) {
+        const uint32_t xbytes = p.k * (p.x_bf16 ? 2u : 4u), m_rows = p.x_bf16 ? p.nslots : p.nslots >> 1;
+        for (uint32_t off = static_cast<uint32_t>(ctid) * 128u; off < m_rows * xbytes; off += CTH * 128u)
+            asm volatile("prefetch.global.L2 [%0];" ::"l"(static_cast<const uint8_t*>(p.x) + off));
+    }
+    // (the consumers' dependency wait sits inside build_panel, directly in front of the first load of
+    // the activations: everything up to there is set-up that does not touch what an earlier kernel writes)
     if constexpr (PHASED) {
         if (ctid == 0) { mbar_init(xbar, 1); mbar_fence_init(); }
         asm volatile("bar.sync 1, %0;" ::"n"(CTH));
     }
     if (!slot_ok) {
+        asm volatile("griddepcontrol.wait;" ::: "memory");                // before writing y
         cta_sync_n<(NTEAMS * TEAM + 2) * 32>();
         for (uint32_t r = ctid; r < p.n; r += CTH) yout[r] = 0.f;
         return;
@@ -799,6 +836,7 @@ __global__ void __launch_bounds__((NTEAMS * TEAM + 2) * 32, 1) gemv_mma_kernel(c
         if (EXT && s0 == 0 && p.g_wait) {
             // the activations are another product's gathered output: wait until every rank's part of
             // it has arrived here (bounded; the peers' kernels run on other GPUs)
+            asm volatile("griddepcontrol.wait;" ::: "memory");            // the counters belong to earlier kernels too
             if (ctid == 0) {
                 // word 0 counts arrivals from the peers' CTAs, word 1 the arrivals that the products
                 // finished HERE stand for (all ranks issue the same launches): everything has arrived once
@@ -907,7 +945,6 @@ __global__ void __launch_bounds__((NTEAMS * TEAM + 2) * 32, 1) gemv_mma_kernel(c
         }
     }
     if (threadIdx.x == 0) PROBE_STAMP(4);
-    if (threadIdx.x == CTH - 32) PROBE_STAMP(1);
 }
 
 // shared memory that does not depend on the ring depth; kphase = elements of k resident at a time
