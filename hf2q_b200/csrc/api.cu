@@ -62,9 +62,11 @@ int32_t cuda_fail(hf2q_ctx* ctx, cudaError_t e, const char* what) {
 struct DeviceGuard {
     int prev = -1;
     bool ok = false;
+    // (switching costs about a microsecond even to the current device, so it is done only when needed)
     explicit DeviceGuard(int dev) {
         if (cudaGetDevice(&prev) != cudaSuccess) prev = -1;
-        ok = cudaSetDevice(dev) == cudaSuccess;
+        if (prev == dev) { ok = true; prev = -1; }
+        else ok = cudaSetDevice(dev) == cudaSuccess;
     }
     ~DeviceGuard() { if (prev >= 0) cudaSetDevice(prev); }
 };
