@@ -775,12 +775,18 @@ __global__ void __launch_bounds__((NTEAMS * TEAM + 2) * 32, 1) gemv_mma_kernel(c
             if (lane == 0) {
                 const uint32_t ctas = gridDim.x * gridDim.y;
                 if (blockIdx.x == 0 && blockIdx.y == 0) atomicAdd(p.g_flag[p.g_rank] + 1, ctas * (p.g_nranks - 1));
-                // release at system scope: the adds become visible after this warp's stores (the warp
-                // barrier above makes the release cover all lanes' stores) without stalling the warp the
-                // way a separate fence does
-                for (uint32_t r = 0; r < p.g_nranks; ++r)
-                    if (r != p.g_rank)
-                        asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(p.g_flag[r]) : "memory");
+                // Release at system scope: the adds become visible after this warp's stores (the warp
+                // barrier above makes it cover all lanes' stores).  One peer: a releasing add.  Several
+                // peers: ONE fence and then relaxed adds, so that the wait for the stores' acknowledgement
+                // is paid once and not once per peer.
+                if (p.g_nranks == 2) {
+                    asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(p.g_flag[p.g_rank ^ 1u]) : "memory");
+                } else {
+                    asm volatile("fence.acq_rel.sys;" ::: "memory");
+                    for (uint32_t r = 0; r < p.g_nranks; ++r)
+                        if (r != p.g_rank)
+                            asm volatile("red.relaxed.sys.global.add.u32 [%0], 1;" ::"l"(p.g_flag[r]) : "memory");
+                }
             }
         }
         return;
