@@ -50,6 +50,7 @@ SIGNATURES = {
     "hf2q_cuda_ipc_close": (i32, [vp, vp]),
     "hf2q_cuda_qmatmul_gather": (i32, [vp, vp, vp, u32, vp, vp, u32, u32, u32, u32]),
     "hf2q_cuda_gather_wait": (i32, [vp, vp, vp]),
+    "hf2q_cuda_set_wait_limit": (i32, [vp, u64]),
     "hf2q_cuda_qmatmul_id": (i32, [vp, vp, vp, u32, vp, vp, vp, u32, u32, u32, u32, u32, u64, u32, vp, u64]),
     "hf2q_cuda_qmatmul_id_pair": (i32, [vp, vp, vp, u32, vp, vp, vp, vp, vp, u32, u32, u32, u32, u32, u64, u32, vp, u64]),
     "hf2q_cuda_qmatmul_id_scratch_bytes": (i32, [u32, u32, u32, u32, C.POINTER(u64)]),

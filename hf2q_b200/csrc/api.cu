@@ -19,7 +19,7 @@ struct hf2q_ctx {
     uint32_t* status = nullptr;        // device status word
     uint64_t launches = 0;
     bool fp32_matvec = false;          // HF2Q_CUDA_F32_MATVEC=1: CUDA-core fp32 mat-vec only
-    bool tc_matvec = false;            // HF2Q_CUDA_TC_MATVEC=1: dense mat-vecs on the tcgen05 kernel (slower today)
+    long long wait_limit = 1ll << 31;  // clock ticks a device-side wait for another GPU may take (about a second)
     // staging for the *_host convenience calls
     // A ring of device staging buffers and three streams: copy-in on in_stream, kernels on
     // host_stream, copy-out on out_stream, so that the copy-in of later calls, the kernel of call i
@@ -94,15 +94,6 @@ int32_t grow(hf2q_ctx* ctx, void** p, size_t* have, size_t want, bool pinned) {
 // chosen kernel needs.  ids == nullptr: dense.
 int32_t run_matvec(hf2q_ctx* ctx, cudaStream_t st, GemvArgs a, uint32_t m_total, const char* who) {
     const size_t xs = dtype_size(a.x_dtype);
-    if (!ctx->fp32_matvec && ctx->tc_matvec && m_total <= 8) {
-        a.m = m_total;
-        if (gemv_tc_supported(a)) {
-            const cudaError_t e = launch_gemv_tc(a, ctx->dev, st);
-            if (e != cudaSuccess) return cuda_fail(ctx, e, who);
-            ctx->launches += 1;
-            return HF2Q_OK;
-        }
-    }
     const bool mma = !ctx->fp32_matvec && gemv_mma_supported(a);
     uint32_t step = 8;
     if (mma) {
@@ -177,8 +168,6 @@ HF2Q_API int32_t hf2q_cuda_ctx_create(int32_t device, hf2q_ctx** out) {
     // switch for its mat-vec: HF2Q_F32_MATVEC, src/serve/forward_mlx.rs:9835)
     const char* env = getenv("HF2Q_CUDA_F32_MATVEC");
     c->fp32_matvec = env && env[0] == '1';
-    env = getenv("HF2Q_CUDA_TC_MATVEC");
-    c->tc_matvec = env && env[0] == '1';
     *out = c;
     return HF2Q_OK;
 }
@@ -445,6 +434,18 @@ HF2Q_API int32_t hf2q_cuda_qmatmul_gather(hf2q_ctx* ctx, void* stream, const voi
     for (uint32_t r = 0; r < g->n_ranks; ++r)
         if (!g->y_all[r] || !g->flags[r] || reinterpret_cast<uintptr_t>(g->y_all[r]) % 4 || reinterpret_cast<uintptr_t>(g->flags[r]) % 4)
             return fail(ctx, HF2Q_ERR_INVALID_ARGUMENT, "qmatmul_gather: buffer of rank %u missing or misaligned", r);
+    {
+        // the shards must tile the output: every rank derives the others' arrival counts from n_rows[]
+        uint64_t sum = 0, before = 0;
+        for (uint32_t r = 0; r < g->n_ranks; ++r) {
+            if (g->n_rows[r] == 0) return fail(ctx, HF2Q_ERR_INVALID_ARGUMENT, "qmatmul_gather: n_rows[%u] is zero", r);
+            if (r < g->rank) before += g->n_rows[r];
+            sum += g->n_rows[r];
+        }
+        if (g->n_rows[g->rank] != n || sum > g->n_total || before != g->col0)
+            return fail(ctx, HF2Q_ERR_INVALID_ARGUMENT, "qmatmul_gather: n_rows[] (sum %llu, %llu before rank %u) does not match n=%u, col0=%u, n_total=%u",
+                        (unsigned long long)sum, (unsigned long long)before, g->rank, n, g->col0, g->n_total);
+    }
     if (m == 0) return HF2Q_OK;
     DeviceGuard dg(ctx->device);
     GemvArgs a{};
@@ -461,6 +462,8 @@ HF2Q_API int32_t hf2q_cuda_qmatmul_gather(hf2q_ctx* ctx, void* stream, const voi
     for (uint32_t r = 0; r < g->n_ranks; ++r) { ga.y_all[r] = static_cast<float*>(g->y_all[r]); ga.flags[r] = static_cast<uint32_t*>(g->flags[r]); }
     ga.n_ranks = g->n_ranks; ga.rank = g->rank; ga.n_total = g->n_total; ga.col0 = g->col0;
     ga.wait_expected = g->wait_previous;
+    for (uint32_t r = 0; r < g->n_ranks; ++r) ga.peer_ctas[r] = gemv_mma_grid_x(g->n_rows[r], k, ctx->dev);
+    ga.wait_limit = ctx->wait_limit;
     a.gather = &ga;
     const cudaError_t e = launch_gemv_mma(a, ctx->dev, static_cast<cudaStream_t>(stream));
     if (e != cudaSuccess) return cuda_fail(ctx, e, "qmatmul_gather launch");
@@ -468,12 +471,21 @@ HF2Q_API int32_t hf2q_cuda_qmatmul_gather(hf2q_ctx* ctx, void* stream, const voi
     return HF2Q_OK;
 }
 
-HF2Q_API int32_t hf2q_cuda_gather_wait(hf2q_ctx* ctx, void* stream, const void* flag) {
-    if (!ctx || !flag) return HF2Q_ERR_INVALID_ARGUMENT;
+HF2Q_API int32_t hf2q_cuda_gather_wait(hf2q_ctx* ctx, void* stream, const hf2q_gather* g) {
+    if (!ctx || !g) return HF2Q_ERR_INVALID_ARGUMENT;
+    if (g->n_ranks < 1 || g->n_ranks > 8 || g->rank >= g->n_ranks || !g->flags[g->rank])
+        return fail(ctx, HF2Q_ERR_INVALID_ARGUMENT, "gather_wait: rank %u of %u", g->rank, g->n_ranks);
     DeviceGuard dg(ctx->device);
-    const cudaError_t e = launch_gather_wait(static_cast<const uint32_t*>(flag), ctx->status, static_cast<cudaStream_t>(stream));
+    const cudaError_t e = launch_gather_wait(static_cast<const uint32_t*>(g->flags[g->rank]), g->n_ranks, g->rank, ctx->wait_limit, ctx->status,
+                                             static_cast<cudaStream_t>(stream));
     if (e != cudaSuccess) return cuda_fail(ctx, e, "gather_wait launch");
     ctx->launches += 1;
+    return HF2Q_OK;
+}
+
+HF2Q_API int32_t hf2q_cuda_set_wait_limit(hf2q_ctx* ctx, uint64_t clock_ticks) {
+    if (!ctx || clock_ticks == 0 || clock_ticks > (1ull << 40)) return HF2Q_ERR_INVALID_ARGUMENT;
+    ctx->wait_limit = static_cast<long long>(clock_ticks);
     return HF2Q_OK;
 }
 

@@ -388,29 +388,28 @@ template <uint32_t TYPE, int M, bool XSMEM>
 cudaError_t launch_stream(const KParams& p, uint32_t slots, size_t smem, const DeviceInfo& dev,
                           cudaStream_t st) {
     auto kern = gemv_stream_kernel<TYPE, M, XSMEM>;
-    // The opt-in shared-memory limit is raised once per kernel; the occupancy answer is cached for
-    // the last shared-memory size, so the steady-state launch path makes no other runtime call.
+    // The opt-in shared-memory limit is raised once per kernel and device; the occupancy answer is
+    // cached per device for the last shared-memory size, so the steady-state launch path makes no
+    // other runtime call.
+    static PerDeviceFlag attr;
+    if (const cudaError_t e = ensure_max_dynamic_smem(kern, dev.max_smem_optin, attr); e != cudaSuccess) return e;
     static std::mutex mu;
-    static bool attr_set = false;
-    static size_t cached_smem = ~static_cast<size_t>(0);
-    static int cached_per_sm = 1;
-    int per_sm;
+    static size_t cached_smem[MAX_DEVICES];
+    static int cached_per_sm[MAX_DEVICES];
+    static bool cached[MAX_DEVICES] = {};
+    int per_sm, cur = 0;
+    if (const cudaError_t e = cudaGetDevice(&cur); e != cudaSuccess) return e;
     {
         std::lock_guard<std::mutex> lock(mu);
-        if (!attr_set) {
-            cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                                 dev.max_smem_optin);
-            if (e != cudaSuccess) return e;
-            attr_set = true;
-        }
-        if (cached_smem != smem) {
+        if (!cached[cur] || cached_smem[cur] != smem) {
             int q = 1;
             cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&q, kern, THREADS, smem);
             if (e != cudaSuccess) return e;
-            cached_per_sm = q < 1 ? 1 : q;
-            cached_smem = smem;
+            cached_per_sm[cur] = q < 1 ? 1 : q;
+            cached_smem[cur] = smem;
+            cached[cur] = true;
         }
-        per_sm = cached_per_sm;
+        per_sm = cached_per_sm[cur];
     }
     uint32_t want = static_cast<uint32_t>(dev.sm_count) * per_sm;
     uint32_t gx = (want + slots - 1) / slots;

@@ -22,11 +22,11 @@
 //     into the A fragment.  The integer codes are fed as f16 SUBNORMALS (code * 2^-24): a single
 //     PRMT turns two packed bytes into an f16x2 operand, with no int->float conversion and no
 //     offset to subtract;
-//   * scales stay out of the per-element path: Q4_K/Q5_K multiply the codes by the 6-bit
-//     sub-block scale in f16 (code*scale < 2048, exact) and apply d once per block; Q6_K applies
-//     d*scale to each 16-element MMA result; Q4_0/Q8_0 apply d per block.  Offsets (the -dmin*m
-//     of Q4_K/Q5_K, the -32/-8/-128 code biases) become one small extra MMA (or FMA) per block
-//     against per-sub-block sums of x that every CTA computes once;
+//   * scales stay out of the per-element path: Q4_K/Q5_K apply d*scale (f32, exact) to the sum of
+//     each 32-element sub-block's two MMA steps; Q6_K applies d*scale to each 16-element MMA
+//     result; Q4_0/Q8_0 apply d per block.  Offsets (the -dmin*m of Q4_K/Q5_K, the -32/-8/-128
+//     code biases) become one small extra MMA (or FMA) per block against per-sub-block sums of x
+//     that every CTA computes once;
 //   * activations live in shared memory as f16 (bf16 input: exact in range; f32 input: split
 //     into hi + lo halves on two MMA columns, ~2^-22 relative); rows too long for that are
 //     handled in k-phases (see the kernel);
@@ -90,28 +90,12 @@ struct MParams {
     // fused all-gather (row-sharded weights over several GPUs); g_nranks == 0: plain store to y
     float* g_y[8];
     uint32_t* g_flag[8];
+    uint32_t g_peer_ctas[8];   // CTAs of the same product on every rank (their arrivals at this rank)
     uint32_t g_nranks, g_rank, g_ntotal, g_col0, g_wait;
+    long long wait_limit;      // clock ticks a wait for other ranks may take before it gives up
     uint32_t* status;
-#ifdef HF2Q_MMA_PROBE
-    uint32_t debug;            // 1: skip the arithmetic, 2: skip the copies (timing probes, wrong results)
-    uint32_t launch_id;
-#endif
 };
 
-#ifdef HF2Q_MMA_PROBE
-// timeline probe: [launch parity][CTA][event] global-timer stamps
-__device__ unsigned long long g_probe_ts[2 * 160 * 8];
-__device__ uint32_t g_probe_parity;
-__device__ __forceinline__ void probe_stamp(const MParams& p, int ev) {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    if (blockIdx.x < 160 && blockIdx.y == 0) g_probe_ts[((p.launch_id & 1) * 160 + blockIdx.x) * 8 + ev] = t;
-    if (ev == 0 && blockIdx.x == 0) g_probe_parity = p.launch_id;
-}
-#define PROBE_STAMP(ev) probe_stamp(p, ev)
-#else
-#define PROBE_STAMP(ev)
-#endif
 
 // The one CTA-wide barrier (id 0).  The producer warp arrives and carries on, the other warps
 // wait.  Every participant names the thread count: a barrier whose participants disagree on the
@@ -155,6 +139,22 @@ __device__ __forceinline__ uint2 ld_x4(const uint8_t* xrow, uint32_t e) {
     return *reinterpret_cast<const uint2*>(xrow + 2 * e);
 }
 constexpr float TWO24 = 16777216.0f;
+
+// Bounded wait until source rank `src` has delivered everything the products launched here so far
+// expect from it: arrival counter flag[src] against the expected count flag[8 + src] (written by
+// earlier kernels of this stream, which have completed).  The acquire load orders the reads of the
+// gathered columns after it.  Gives up after `limit` clock ticks and records that in *status.
+__device__ __forceinline__ void gather_wait_source(const uint32_t* flag, uint32_t src, long long limit, uint32_t* status) {
+    const uint32_t want = *reinterpret_cast<const volatile uint32_t*>(flag + 8 + src);
+    const long long t0 = clock64();
+    for (;;) {
+        uint32_t got;
+        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(got) : "l"(flag + src) : "memory");
+        if (static_cast<int32_t>(got - want) >= 0) break;
+        if (clock64() - t0 > limit) { atomicOr(status, STATUS_WAIT_TIMEOUT); break; }
+        __nanosleep(50);
+    }
+}
 
 // ---- Q4_K / Q5_K: half a block (128 elements = chunks 2*half, 2*half+1 = sub-blocks 4*half..+3) of
 // rows g and g+8.  A chunk is 32 bytes whose low nibbles are sub-block 2c and whose high nibbles are
@@ -428,13 +428,6 @@ __device__ __forceinline__ void build_panel(const void* x, bool x_bf16, uint32_t
         asm volatile("griddepcontrol.wait;" ::: "memory");               // x may be an earlier kernel's output
         for (uint32_t pos0 = ctid; pos0 < k8; pos0 += PU * CTH) {
             for (uint32_t s0 = 0; s0 < nslots; s0 += SU) {
-#ifdef HF2Q_MMA_PROBE
-                if (threadIdx.x == 0 && pos0 == 0 && s0 == 0 && k0 == 0) {
-                    unsigned long long tnow;
-                    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(tnow));
-                    if (blockIdx.x < 160 && blockIdx.y == 0) g_probe_ts[((g_probe_parity & 1) * 160 + blockIdx.x) * 8 + 7] = tnow;
-                }
-#endif
                 uint4 ra[SU * PU];
 #pragma unroll
                 for (int a = 0; a < SU; ++a)
@@ -447,13 +440,6 @@ __device__ __forceinline__ void build_panel(const void* x, bool x_bf16, uint32_t
 #pragma unroll
                     for (int b = 0; b < PU; ++b)
                         if (s0 + a < nslots && pos0 + b * CTH < k8) convert_bf16(ra[a * PU + b], s0 + a, pos0 + b * CTH);
-#ifdef HF2Q_MMA_PROBE
-                if (threadIdx.x == 0 && pos0 == 0 && s0 == 0 && k0 == 0) {
-                    unsigned long long tnow;
-                    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(tnow));
-                    if (blockIdx.x < 160 && blockIdx.y == 0) g_probe_ts[((g_probe_parity & 1) * 160 + blockIdx.x) * 8 + 1] = tnow + (*reinterpret_cast<volatile uint32_t*>(xh) & 0u);
-                }
-#endif
             }
         }
     };
@@ -464,6 +450,9 @@ __device__ __forceinline__ void build_panel(const void* x, bool x_bf16, uint32_t
         if (ctid < nslots) {
             if (ctid == 0) mbar_arrive_expect_tx(xbar, nslots * klen * 2);
             __syncwarp(__activemask());
+            // x may have been written by other GPUs' plain stores that this CTA only ordered through an
+            // acquire load and a barrier: make the asynchronous copy below observe them as well
+            asm volatile("fence.proxy.async;" ::: "memory");
             bulk_g2s(xh + ctid * xpitch, static_cast<const __nv_bfloat16*>(x) + (static_cast<size_t>(xrow_idx) + ctid) * k + k0, klen * 2, xbar);
         }
         if (!mbar_wait_bounded(xbar, xparity, status)) return;
@@ -605,7 +594,6 @@ __global__ void __launch_bounds__((NTEAMS * TEAM + 2) * 32, 1) gemv_mma_kernel(c
     if (warp == CW) {
         // ---------------- producer warp: lane r copies row r of each stage ----------------
         if (lane == 0) {
-            PROBE_STAMP(0);
             for (uint32_t i = 0; i < stages; ++i) { mbar_init(&full[i], 1); mbar_init(&empty[i], TEAM); }
             mbar_fence_init();
         }
@@ -643,9 +631,6 @@ __global__ void __launch_bounds__((NTEAMS * TEAM + 2) * 32, 1) gemv_mma_kernel(c
                         }
                         const uint32_t off = s * p.slice_bytes;
                         const uint32_t bytes = min(p.slice_bytes, p.row_bytes - off);
-#ifdef HF2Q_MMA_PROBE
-                        if (p.debug & 2u) { if (lane == 0) mbar_arrive(&full[st]); continue; }
-#endif
                         if (p.use_tmap) {
                             // one tensor copy for the whole stage: the copy engine spends ~15 cycles per copy
                             // descriptor, which 16 per-row copies per stage made 15 % of the streaming time.
@@ -663,14 +648,6 @@ __global__ void __launch_bounds__((NTEAMS * TEAM + 2) * 32, 1) gemv_mma_kernel(c
                         }
                         if (lane == 0) mbar_arrive_expect_tx(&full[st], nrows * bytes);
                         __syncwarp();
-#ifdef HF2Q_MMA_PROBE
-                        if (p.debug & 4u) {       // timing probe: the stage's bytes as ONE contiguous copy (wrong data)
-                            if (lane == 0)
-                                bulk_g2s(ring + st * stage_bytes, wsrc + static_cast<uint64_t>(row0) * p.row_bytes + (s - s0) * nrows * bytes,
-                                         nrows * bytes, &full[st]);
-                            continue;
-                        }
-#endif
                         if (p.dense_stage) {
                             // whole rows, contiguous in memory and in the stage: one copy
                             if (lane == 0)
@@ -766,27 +743,24 @@ __global__ void __launch_bounds__((NTEAMS * TEAM + 2) * 32, 1) gemv_mma_kernel(c
             }
             s0 += nsp;
         }
-        if (lane == 0) PROBE_STAMP(5);
         if (EXT && p.g_nranks > 1) {
-            // Tell the other ranks that this CTA's part of the columns has landed: one fire-and-forget
-            // add with release semantics per peer.  CTA 0 also records how many arrivals this launch adds
-            // to the own counter (every rank launches the same grid).
+            // Tell the other ranks that this CTA's part of the columns has landed.  Rank r's counter
+            // block holds one arrival counter per SOURCE rank (words 0..7) and, next to it, how many
+            // arrivals the products launched HERE so far stand for from each source (words 8..15):
+            // a source's columns of every earlier product are complete once its counter has caught up,
+            // whatever the other sources have delivered and however many CTAs each rank's shard needs.
             __syncwarp();
             if (lane == 0) {
-                const uint32_t ctas = gridDim.x * gridDim.y;
-                if (blockIdx.x == 0 && blockIdx.y == 0) atomicAdd(p.g_flag[p.g_rank] + 1, ctas * (p.g_nranks - 1));
-                // Release at system scope: the adds become visible after this warp's stores (the warp
-                // barrier above makes it cover all lanes' stores).  One peer: a releasing add.  Several
-                // peers: ONE fence and then relaxed adds, so that the wait for the stores' acknowledgement
-                // is paid once and not once per peer.
-                if (p.g_nranks == 2) {
-                    asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(p.g_flag[p.g_rank ^ 1u]) : "memory");
-                } else {
-                    asm volatile("fence.acq_rel.sys;" ::: "memory");
+                if (blockIdx.x == 0 && blockIdx.y == 0)
                     for (uint32_t r = 0; r < p.g_nranks; ++r)
-                        if (r != p.g_rank)
-                            asm volatile("red.relaxed.sys.global.add.u32 [%0], 1;" ::"l"(p.g_flag[r]) : "memory");
-                }
+                        if (r != p.g_rank) atomicAdd(p.g_flag[p.g_rank] + 8 + r, p.g_peer_ctas[r]);
+                // Release at system scope: the adds become visible after this warp's stores (the warp
+                // barrier above makes it cover all lanes' stores).  ONE fence and then relaxed adds, so
+                // that the wait for the stores' acknowledgement is paid once and not once per peer.
+                asm volatile("fence.acq_rel.sys;" ::: "memory");
+                for (uint32_t r = 0; r < p.g_nranks; ++r)
+                    if (r != p.g_rank)
+                        asm volatile("red.relaxed.sys.global.add.u32 [%0], 1;" ::"l"(p.g_flag[r] + p.g_rank) : "memory");
             }
         }
         return;
@@ -827,11 +801,6 @@ __global__ void __launch_bounds__((NTEAMS * TEAM + 2) * 32, 1) gemv_mma_kernel(c
     const uint8_t* ring_g = ring + g * pitch;                            // this lane's first row in slot 0
     float* red_t = red + team * (TEAM * 128) + g * 8 + 2 * t;              // + block * 128: this team's partial sums
     const uint32_t last_slice = nslices - 1, last_nblk = p.last_nblk;
-#ifdef HF2Q_MMA_PROBE
-    const uint32_t dbg = p.debug;
-#else
-    constexpr uint32_t dbg = 0;
-#endif
     uint32_t blk = static_cast<uint32_t>(warp) % TEAM;                   // block of the stage this warp takes; rotates
     uint32_t fl_base = 0;                                                // flushes of earlier phases
 
@@ -843,28 +812,14 @@ __global__ void __launch_bounds__((NTEAMS * TEAM + 2) * 32, 1) gemv_mma_kernel(c
             // the activations are another product's gathered output: wait until every rank's part of
             // it has arrived here (bounded; the peers' kernels run on other GPUs)
             asm volatile("griddepcontrol.wait;" ::: "memory");            // the counters belong to earlier kernels too
-            if (ctid == 0) {
-                // word 0 counts arrivals from the peers' CTAs, word 1 the arrivals that the products
-                // finished HERE stand for (all ranks issue the same launches): everything has arrived once
-                // word 0 has caught up.  The acquire load orders the reads of x after it.
-                const uint32_t* flag = p.g_flag[p.g_rank];
-                const uint32_t want = *reinterpret_cast<const volatile uint32_t*>(flag + 1);
-                const long long t0 = clock64();
-                for (;;) {
-                    uint32_t got;
-                    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(got) : "l"(flag) : "memory");
-                    if (static_cast<int32_t>(got - want) >= 0) break;
-                    if (clock64() - t0 > (1ll << 31)) { atomicOr(p.status, STATUS_WAIT_TIMEOUT); break; }
-                    __nanosleep(50);
-                }
-            }
+            if (static_cast<uint32_t>(ctid) < p.g_nranks && static_cast<uint32_t>(ctid) != p.g_rank)
+                gather_wait_source(p.g_flag[p.g_rank], ctid, p.wait_limit, p.status);
             asm volatile("bar.sync 1, %0;" ::"n"(CTH));
         }
         build_panel<TYPE, CTH, (PHASED ? 2 : 8), PHASED>(p.x, p.x_bf16 != 0, p.nslots, p.k, p.xpitch, p.status, xh, sxp, sx_slot_bytes, xrow_idx, k0,
                                min(nsp * SLICE_ELEMS, p.k - k0), xbar, pi & 1u);
         if (s0 == 0) cta_sync_n<(NTEAMS * TEAM + 2) * 32>();             // panel + all barrier initialisations
         else asm volatile("bar.sync 1, %0;" ::"n"(CTH));
-        if (threadIdx.x == 0 && s0 == 0) PROBE_STAMP(2);
 
         // Stages of this phase are numbered it0 .. it0 + gcta * nsp - 1 (group-major); this team
         // owns those with index = team (mod NTEAMS); stage i sits in ring slot i % stages.  (No
@@ -891,16 +846,13 @@ __global__ void __launch_bounds__((NTEAMS * TEAM + 2) * 32, 1) gemv_mma_kernel(c
         float f[4] = {0.f, 0.f, 0.f, 0.f};
         while (grp < gcta) {
             if (!mbar_wait_bounded(&full[st], ph, p.status)) return;
-#ifdef HF2Q_MMA_PROBE
-            if (threadIdx.x == 0 && s0 == 0 && grp == 0 && s == 0) PROBE_STAMP(3);
-#endif
             // the block a warp takes rotates, so that the slower unaligned (odd) Q6_K blocks and the
             // idle turns of a short last slice spread evenly over the team
             blk = (blk + 1) & (TEAM - 1);
             // short rows: the stage holds nsub groups of 16 rows and `blk` counts (group, block) pairs
             const uint32_t sgi = nsub > 1 ? blk / last_nblk : 0u, bb = nsub > 1 ? blk - sgi * last_nblk : blk;
             const uint32_t nblk = nsub > 1 ? nsub * last_nblk : (s0 + s == last_slice ? last_nblk : static_cast<uint32_t>(TEAM));
-            if (blk < nblk && !(dbg & 1u)) {
+            if (blk < nblk) {
                 const uint8_t* r0 = ring_g + st * stage_bytes + sgi * (ROWS * pitch);
                 const uint8_t* r1 = r0 + 8 * pitch;
                 const uint32_t e0 = s * SLICE_ELEMS + 256 * bb;           // element index inside the panel
@@ -950,7 +902,6 @@ __global__ void __launch_bounds__((NTEAMS * TEAM + 2) * 32, 1) gemv_mma_kernel(c
             }
         }
     }
-    if (threadIdx.x == 0) PROBE_STAMP(4);
 }
 
 // shared memory that does not depend on the ring depth; kphase = elements of k resident at a time
@@ -1102,16 +1053,8 @@ bool make_stage_map(CUtensorMap* map, const MParams& p, const uint8_t* w) {
 template <uint32_t TYPE, int NTEAMS, bool PHASED, bool SUBG, bool EXT>
 cudaError_t launch_mma_tt(MParams p, uint32_t slots, const Plan& pl, const DeviceInfo& dev, cudaStream_t st) {
     auto kern = gemv_mma_kernel<TYPE, NTEAMS, PHASED, SUBG, EXT>;
-    static std::mutex mu;
-    static bool attr_set = false;
-    {
-        std::lock_guard<std::mutex> lock(mu);
-        if (!attr_set) {
-            cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, dev.max_smem_optin);
-            if (e != cudaSuccess) return e;
-            attr_set = true;
-        }
-    }
+    static PerDeviceFlag smem_attr;
+    if (const cudaError_t e = ensure_max_dynamic_smem(kern, dev.max_smem_optin, smem_attr); e != cudaSuccess) return e;
     p.stages = pl.stages;
     p.phase_base = pl.phase_base;
     p.phase_rem = pl.phase_rem;
@@ -1144,11 +1087,6 @@ cudaError_t launch_mma_tt(MParams p, uint32_t slots, const Plan& pl, const Devic
 template <uint32_t TYPE>
 cudaError_t launch_mma_t(MParams p, uint32_t slots, const DeviceInfo& dev, cudaStream_t st) {
     const size_t limit = static_cast<size_t>(dev.max_smem_optin);
-#ifdef HF2Q_MMA_PROBE
-    p.debug = env_int("HF2Q_CUDA_MMA_DEBUG", 0);
-    static uint32_t launch_counter = 0;
-    p.launch_id = launch_counter++;
-#endif
     // two teams: a third (26 warps, 72 registers) measured no faster
     const Plan pl = make_plan(TYPE, p.k, p.nslots, 2, limit);
     if (!pl.stages) return cudaErrorInvalidConfiguration;
@@ -1164,32 +1102,24 @@ cudaError_t launch_mma_t(MParams p, uint32_t slots, const DeviceInfo& dev, cudaS
 
 }  // namespace
 
-#ifdef HF2Q_MMA_PROBE
-extern "C" __attribute__((visibility("default"))) int hf2q_probe_read(unsigned long long* host) {
-    return static_cast<int>(cudaMemcpyFromSymbol(host, g_probe_ts, sizeof(g_probe_ts)));
-}
-#endif
 
 namespace {
-__global__ void gather_wait_kernel(const uint32_t* flag, uint32_t* status) {
+__global__ void gather_wait_kernel(const uint32_t* flag, uint32_t n_ranks, uint32_t rank, long long limit, uint32_t* status) {
     asm volatile("griddepcontrol.wait;" ::: "memory");
-    if (threadIdx.x == 0) {
-        const uint32_t want = *reinterpret_cast<const volatile uint32_t*>(flag + 1);
-        const long long t0 = clock64();
-        for (;;) {
-            uint32_t got;
-            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(got) : "l"(flag) : "memory");
-            if (static_cast<int32_t>(got - want) >= 0) break;
-            if (clock64() - t0 > (1ll << 31)) { atomicOr(status, STATUS_WAIT_TIMEOUT); break; }
-            __nanosleep(50);
-        }
-    }
+    if (threadIdx.x < n_ranks && threadIdx.x != rank) gather_wait_source(flag, threadIdx.x, limit, status);
 }
 }  // namespace
 
-cudaError_t launch_gather_wait(const uint32_t* flag, uint32_t* status, cudaStream_t st) {
-    gather_wait_kernel<<<1, 32, 0, st>>>(flag, status);
+cudaError_t launch_gather_wait(const uint32_t* flag, uint32_t n_ranks, uint32_t rank, long long limit, uint32_t* status, cudaStream_t st) {
+    gather_wait_kernel<<<1, 32, 0, st>>>(flag, n_ranks, rank, limit, status);
     return cudaGetLastError();
+}
+
+uint32_t gemv_mma_grid_x(uint32_t n, uint32_t k, const DeviceInfo& dev) {
+    const uint32_t rows = ROWS * sub_groups_of(k);
+    const uint32_t ngroups = (n + rows - 1) / rows;
+    const uint32_t gx = static_cast<uint32_t>(dev.sm_count) < ngroups ? static_cast<uint32_t>(dev.sm_count) : ngroups;
+    return gx < 1 ? 1 : gx;
 }
 
 bool gemv_mma_supported(const GemvArgs& a) {
@@ -1250,9 +1180,10 @@ cudaError_t launch_gemv_mma(const GemvArgs& a, const DeviceInfo& dev, cudaStream
     if (a.gather) {
         const GatherArgs& g = *a.gather;
         if (a.ids || g.n_ranks < 1 || g.n_ranks > 8 || g.rank >= g.n_ranks) return cudaErrorInvalidValue;
-        for (uint32_t r = 0; r < g.n_ranks; ++r) { p.g_y[r] = g.y_all[r]; p.g_flag[r] = g.flags[r]; }
+        for (uint32_t r = 0; r < g.n_ranks; ++r) { p.g_y[r] = g.y_all[r]; p.g_flag[r] = g.flags[r]; p.g_peer_ctas[r] = g.peer_ctas[r]; }
         p.g_nranks = g.n_ranks; p.g_rank = g.rank; p.g_ntotal = g.n_total; p.g_col0 = g.col0;
         p.g_wait = g.wait_expected;
+        p.wait_limit = g.wait_limit;
     }
     if (a.swiglu && (!a.w2 || a.gather || a.residual || p.sub_groups > 1)) return cudaErrorInvalidValue;
     const uint32_t slots = a.w2 && !a.swiglu ? 2 * a.slots : a.slots;

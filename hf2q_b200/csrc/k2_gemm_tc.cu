@@ -108,19 +108,6 @@ __device__ __forceinline__ void dequant_dispatch(uint32_t grp, const uint8_t* ro
     }
 }
 
-#ifdef HF2Q_TC_PROBE
-// timeline probe: [CTA (first 512 of the grid, linear)][event] global-timer stamps
-__device__ unsigned long long g_tc_ts[512 * 8];
-__device__ __forceinline__ void tc_stamp(int ev) {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    const uint32_t id = blockIdx.y * gridDim.x + blockIdx.x;
-    if (id < 512) g_tc_ts[id * 8 + ev] = t;
-}
-#define TC_STAMP(ev) tc_stamp(ev)
-#else
-#define TC_STAMP(ev)
-#endif
 
 // ---------------------------------------------------------------- the kernel
 template <uint32_t TYPE, int NT, bool GROUPED>
@@ -159,7 +146,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
         tok0 = gt.start; tok_end = gt.start + gt.count; expert = gt.expert;
     }
     const uint32_t nkb = p.k / KB;
-    if (threadIdx.x == 0) TC_STAMP(0);
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < RAW_STAGES; ++s) { mbar_init(&raw_full[s], 1); mbar_init(&raw_empty[s], DEQ_WARPS); }
@@ -174,7 +160,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
-    if (threadIdx.x == 0) TC_STAMP(1);
     const uint32_t tmem_d = tmem_base;                 // columns [0, NT)
     const uint32_t tmem_a = tmem_base + (A_BUFS == 1 ? 128 : 256);     // A_BUFS buffers of 128 columns
 
@@ -252,22 +237,18 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
                 tc_fence_after();
-                if (threadIdx.x == 0 && gk == 0) TC_STAMP(2);
                 const uint32_t off = (kb * p.blk_bytes) & 15u;
                 dequant_dispatch<TYPE>(grp, raw + rs * raw_stage + r * p.boxw, off, tmem_a + ab * 128 + lane_addr);
                 tmem_wait_st();
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) { mbar_arrive(&a_full[ab]); mbar_arrive(&raw_empty[rs]); }
-                if (threadIdx.x == 0 && gk == 0) TC_STAMP(3);
-                if (threadIdx.x == 0 && gk == nkb - 1) TC_STAMP(4);
             }
             // epilogue of this tile
             if (ok) ok = mbar_wait_bounded(d_full, tl & 1, p.status);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
             tc_fence_after();
-            if (threadIdx.x == 0 && tl == 0) TC_STAMP(5);
             const uint32_t row = row0 + r;
 #pragma unroll 1
             for (int c0 = 32 * static_cast<int>(grp); c0 < NT; c0 += 32 * DEQ_GROUPS) {   // the groups share the columns
@@ -289,12 +270,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(d_empty);
-            if (threadIdx.x == 0 && tl == 0) TC_STAMP(6);
         }
     }
     tc_fence_before();
     __syncthreads();
-    if (threadIdx.x == 0) TC_STAMP(7);
     if (warp == DEQ_WARPS + 1) { tc_fence_after(); tmem_dealloc(tmem_base, TMEM_COLS); }
 }
 
@@ -336,16 +315,8 @@ template <uint32_t TYPE, int NT, bool GROUPED>
 cudaError_t launch_gemm_t(const CUtensorMap& tw, const CUtensorMap& tx, const GParams& p, uint32_t grid_y, cudaStream_t st) {
     auto kern = gemm_tc_kernel<TYPE, NT, GROUPED>;
     const size_t smem = 1024 + static_cast<size_t>(x_stages_of(TYPE, NT)) * NT * 128 + static_cast<size_t>(raw_stages_of(TYPE, NT)) * TILE_N * p.boxw + 512;
-    static std::mutex mu;
-    static bool attr_set = false;
-    {
-        std::lock_guard<std::mutex> lock(mu);
-        if (!attr_set) {
-            cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
-            if (e != cudaSuccess) return e;
-            attr_set = true;
-        }
-    }
+    static PerDeviceFlag attr;
+    if (const cudaError_t e = ensure_max_dynamic_smem(kern, 227 * 1024, attr); e != cudaSuccess) return e;
     const uint32_t row_tiles = (p.n + TILE_N - 1) / TILE_N;
     const dim3 grid((row_tiles + p.tiles_per_cta - 1) / p.tiles_per_cta, grid_y);
     kern<<<grid, GEMM_THREADS, smem, st>>>(tw, tx, p);
@@ -365,11 +336,6 @@ cudaError_t launch_gemm_nt(const CUtensorMap& tw, const CUtensorMap& tx, const G
 
 }  // namespace
 
-#ifdef HF2Q_TC_PROBE
-extern "C" __attribute__((visibility("default"))) int hf2q_tc_probe_read(unsigned long long* host) {
-    return static_cast<int>(cudaMemcpyFromSymbol(host, g_tc_ts, sizeof(g_tc_ts)));
-}
-#endif
 
 bool gemm_tc_supported(uint32_t type, const void* w, uint32_t n, uint32_t k) {
     (void)n;

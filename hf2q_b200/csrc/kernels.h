@@ -3,7 +3,31 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <mutex>
+
 namespace hf2q {
+
+// cudaFuncSetAttribute(MaxDynamicSharedMemorySize) applies to the CURRENT device only, and one
+// process may hold contexts on several GPUs: the opt-in is remembered per device, not per process.
+constexpr int MAX_DEVICES = 64;
+struct PerDeviceFlag {
+    std::mutex mu;
+    bool set[MAX_DEVICES] = {};
+};
+template <typename Kernel>
+inline cudaError_t ensure_max_dynamic_smem(Kernel kern, int bytes, PerDeviceFlag& flag) {
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    if (dev < 0 || dev >= MAX_DEVICES) return cudaErrorInvalidDevice;
+    std::lock_guard<std::mutex> lock(flag.mu);
+    if (!flag.set[dev]) {
+        e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+        if (e != cudaSuccess) return e;
+        flag.set[dev] = true;
+    }
+    return cudaSuccess;
+}
 
 // K0 (k0_dequant.cu)
 cudaError_t launch_dequant(uint32_t type, const void* w, void* out, uint32_t out_dtype,
@@ -20,6 +44,8 @@ struct GatherArgs {
     uint32_t* flags[8];
     uint32_t n_ranks, rank, n_total, col0;   // this rank's rows are columns [col0, col0 + n) of the full output
     uint32_t wait_expected;                  // != 0: wait for the previous products' columns from all ranks before reading x
+    uint32_t peer_ctas[8];                   // CTAs rank r launches for this product (gemv_mma_grid_x of its shard)
+    long long wait_limit;                    // clock ticks a wait for other ranks may take
 };
 struct GemvArgs {
     const void* w;
@@ -55,14 +81,11 @@ uint32_t gemv_mma_max_rows(uint32_t type, uint32_t k, uint32_t x_dtype, const De
 cudaError_t launch_gemv_mma(const GemvArgs& a, const DeviceInfo& dev, cudaStream_t st);
 // whether one launch can take m activation rows with the SwiGLU epilogue (all of k resident, k > 1024)
 bool gemv_mma_swiglu_ok(uint32_t type, uint32_t k, uint32_t m, uint32_t x_dtype, const DeviceInfo& dev);
-// bounded wait (one warp) until the arrival counter flag[0] has caught up with the expected count flag[1]; a
-// timeout sets STATUS_WAIT_TIMEOUT
-cudaError_t launch_gather_wait(const uint32_t* flag, uint32_t* status, cudaStream_t st);
-
-// Tensor-memory variant of the mat-vec (k1_gemv_tc.cu): tcgen05 with thread-per-row dequant and a
-// cluster split of k.  Dense calls only, m <= 8.
-bool gemv_tc_supported(const GemvArgs& a);
-cudaError_t launch_gemv_tc(const GemvArgs& a, const DeviceInfo& dev, cudaStream_t st);
+// CTAs along x that launch_gemv_mma uses for a dense product of n rows (one per SM, at most one per row group)
+uint32_t gemv_mma_grid_x(uint32_t n, uint32_t k, const DeviceInfo& dev);
+// bounded wait (one warp) until every other rank's arrival counter flag[r] has caught up with the expected
+// count flag[8 + r]; a timeout (after `limit` clock ticks) sets STATUS_WAIT_TIMEOUT
+cudaError_t launch_gather_wait(const uint32_t* flag, uint32_t n_ranks, uint32_t rank, long long limit, uint32_t* status, cudaStream_t st);
 
 // K2 (k2_gemm_tc.cu): tcgen05 GEMM for many activation rows.  Needs k % 256 == 0, 16-byte aligned
 // rows and a workspace of gemm_tc_workspace_bytes(m, k) for the f16 copy of the activations.

@@ -40,25 +40,38 @@ __global__ void __launch_bounds__(WARPS * 32) softmax_topk_kernel(const float* _
     for (uint32_t e = lane; e < n_experts; e += 32) probs[e] *= inv_d;
     __syncwarp();
 
+    // Selection is total: a NaN probability (a NaN logit, or a row whose logits are all -inf) ranks
+    // below every number and among NaNs the lower index wins, so every round finds a candidate
+    // (top_k <= n_experts) and no index is ever out of range.  Taken entries are marked -2 in
+    // shared memory; the ranking key of a NaN is -1, so the two cannot be confused.  The reported
+    // weight is the probability itself (a NaN stays a NaN, as IEEE arithmetic gives the reference).
     float sum_sel = 0.f;
     float my_w = 0.f;          // lane s keeps the s-th selected probability (top_k <= 32 per pass)
     uint32_t my_id = 0;
     for (uint32_t s = 0; s < top_k; ++s) {
-        float best = -1.0f;    // probabilities are >= 0; taken entries are marked -2
+        float best = -1.5f;    // keys are >= -1; taken entries (-2) never qualify
         uint32_t bi = 0xffffffffu;
         for (uint32_t e = lane; e < n_experts; e += 32) {
             const float v = probs[e];
-            if (v > best) { best = v; bi = e; }      // strided scan keeps the lowest index on ties
+            const float key = v != v ? -1.0f : v;
+            if (key > best) { best = key; bi = e; }  // strided scan keeps the lowest index on ties
         }
         for (int o = 16; o > 0; o >>= 1) {
             const float ov = __shfl_xor_sync(0xffffffffu, best, o);
             const uint32_t oi = __shfl_xor_sync(0xffffffffu, bi, o);
             if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
         }
-        if (lane == 0) probs[bi] = -2.0f;
+        float val = 0.f;
+        if (bi < n_experts) {                        // always true for top_k <= n_experts; guards the store
+            val = probs[bi];
+            __syncwarp();
+            if (lane == 0) probs[bi] = -2.0f;
+        } else {
+            bi = 0;
+        }
         __syncwarp();
-        sum_sel += best;
-        if ((s & 31u) == static_cast<uint32_t>(lane)) { my_w = best; my_id = bi; }
+        sum_sel += val;
+        if ((s & 31u) == static_cast<uint32_t>(lane)) { my_w = val; my_id = bi; }
         if ((s & 31u) == 31u || s + 1 == top_k) {
             // flush this pass of up to 32 selections; weights are scaled after the loop
             const uint32_t base = s & ~31u;

@@ -1,4 +1,4 @@
-// Device helpers shared by the tcgen05 kernels (k2_gemm_tc.cu, k1_gemv_tc.cu): PTX wrappers for
+// Device helpers of the tcgen05 kernels (k2_gemm_tc.cu): PTX wrappers for
 // TMA tensor copies, tensor-memory allocation / load / store, tcgen05.mma issue and commit, and the
 // per-row block dequantisers that produce f16x2 registers in natural element order.
 #pragma once

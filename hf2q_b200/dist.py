@@ -100,7 +100,7 @@ def ep_mul_mat_id(x_rows: torch.Tensor, ids: torch.Tensor, n_experts: int, n_out
 
 class _Gather(C.Structure):                        # hf2q_gather in include/hf2q_cuda.h
     _fields_ = [("y_all", C.c_void_p * 8), ("flags", C.c_void_p * 8), ("n_ranks", C.c_uint32), ("rank", C.c_uint32),
-                ("n_total", C.c_uint32), ("col0", C.c_uint32), ("wait_previous", C.c_uint32)]
+                ("n_total", C.c_uint32), ("col0", C.c_uint32), ("wait_previous", C.c_uint32), ("n_rows", C.c_uint32 * 8)]
 
 
 class _DevView:
@@ -113,10 +113,19 @@ class _DevView:
 class GatherGroup:
     """Output buffers [max_m][n_total] and arrival counters of all ranks, mapped into this process.
 
+    Every rank owns TWO output buffers and products alternate between them, so that a decode chain
+    (x of a product = the previous product's gathered output) never stores into a buffer that a
+    rank still reads: product i+1 overwrites the buffer of product i-1, and a rank only starts
+    storing product i+1 after every rank has signalled product i complete, i.e. after every rank
+    has finished reading product i-1's output.  That holds when every product after the first is
+    issued with ``wait_previous=True``; a product issued without it is ordered by the caller.  A
+    captured graph whose first product reads the last product's output must hold an even number of
+    products of this group.
+
     Every rank must issue the same sequence of ``matmul`` calls.  ``matmul(..., wait_previous=True)``
-    makes the kernel wait, after it has started prefetching weights, until the previous product's
-    columns from all ranks have arrived here -- what a decode chain needs when x is that output.
-    ``wait()`` queues a tiny kernel that waits for everything issued so far."""
+    makes the kernel wait, after it has started prefetching weights, until the previous products'
+    columns from all ranks have arrived here.  ``wait()`` queues a tiny kernel that waits for
+    everything issued so far."""
 
     def __init__(self, ctx, max_m: int, n_total: int, group=None):
         self.ctx, self.group = ctx, group
@@ -124,6 +133,8 @@ class GatherGroup:
         if self.world > 8:
             raise ValueError("at most 8 ranks")
         self.max_m, self.n_total = max_m, n_total
+        self._buf_bytes = (max_m * n_total * 4 + 255) & ~255
+        self._next = 0                 # buffer the next product writes
         lib, h = ctx._lib, ctx._h
         own_y, own_f = C.c_void_p(), C.c_void_p()
         hy, hf = (C.c_uint8 * 64)(), (C.c_uint8 * 64)()
@@ -132,7 +143,7 @@ class GatherGroup:
         # (no peer access, IPC not permitted) raises on all ranks instead of leaving some of them waiting.
         err = None
         try:
-            ctx._check(lib.hf2q_cuda_ipc_alloc(h, max_m * n_total * 4, C.byref(own_y), hy))
+            ctx._check(lib.hf2q_cuda_ipc_alloc(h, 2 * self._buf_bytes, C.byref(own_y), hy))
             ctx._check(lib.hf2q_cuda_ipc_alloc(h, 256, C.byref(own_f), hf))
         except Exception as exc:                      # noqa: BLE001
             err = exc
@@ -164,31 +175,44 @@ class GatherGroup:
                     lib.hf2q_cuda_free(h, own.value)
             raise RuntimeError(f"GatherGroup: peer buffers could not be set up on every rank (this rank: {err})")
 
-    def _struct(self, col0: int, wait_previous: bool) -> _Gather:
+    def _struct(self, col0: int, wait_previous: bool, buf: int, n_rows: Sequence[int]) -> _Gather:
         g = _Gather()
         for r in range(self.world):
-            g.y_all[r] = self.y_ptrs[r]
+            g.y_all[r] = self.y_ptrs[r] + buf * self._buf_bytes
             g.flags[r] = self.flag_ptrs[r]
+            g.n_rows[r] = n_rows[r]
         g.n_ranks, g.rank, g.n_total, g.col0, g.wait_previous = self.world, self.rank, self.n_total, col0, int(wait_previous)
         return g
 
-    def matmul(self, x: torch.Tensor, weight, m: int, col0: int, wait_previous: bool = False) -> None:
-        """Columns [col0, col0 + weight.rows) of y[m, n_total] = x . dequant(weight)^T on every rank."""
+    def matmul(self, x: torch.Tensor, weight, m: int, col0: int | None = None, wait_previous: bool = False,
+               n_rows: Sequence[int] | None = None) -> None:
+        """Columns [col0, col0 + weight.rows) of y[m, n_total] = x . dequant(weight)^T on every rank.
+
+        ``n_rows[r]`` = rows of rank r's shard of this product (default: every rank holds as many rows
+        as this one); ``col0`` defaults to the sum of the earlier ranks' rows."""
         from . import ops
         if m > self.max_m:
             raise ValueError(f"m={m} exceeds the group's {self.max_m} rows")
-        g = self._struct(col0, wait_previous and self.world > 1)
+        if n_rows is None:
+            n_rows = [weight.rows] * self.world
+        if col0 is None:
+            col0 = sum(n_rows[: self.rank])
+        g = self._struct(col0, wait_previous and self.world > 1, self._next, n_rows)
         self.ctx._check(self.ctx._lib.hf2q_cuda_qmatmul_gather(
             self.ctx._h, self.ctx._stream(), x.data_ptr(), ops._act(x, "x"), weight.ptr, C.byref(g), m, weight.rows,
             weight.cols, weight.ggml_type))
+        self._next ^= 1
 
     def wait(self) -> None:
         if self.world > 1:
-            self.ctx._check(self.ctx._lib.hf2q_cuda_gather_wait(self.ctx._h, self.ctx._stream(), self.flag_ptrs[self.rank]))
+            g = self._struct(0, False, 0, [1] * self.world)
+            self.ctx._check(self.ctx._lib.hf2q_cuda_gather_wait(self.ctx._h, self.ctx._stream(), C.byref(g)))
 
     def output(self, m: int) -> torch.Tensor:
-        """This rank's full-width output buffer as a float32 [m, n_total] tensor (no copy)."""
-        return torch.as_tensor(_DevView(self.y_ptrs[self.rank], (m, self.n_total), "<f4"), device=f"cuda:{self.ctx.device}")
+        """The most recent product's full-width output on this rank as a float32 [m, n_total] tensor (no copy)."""
+        buf = self._next ^ 1
+        ptr = self.y_ptrs[self.rank] + buf * self._buf_bytes
+        return torch.as_tensor(_DevView(ptr, (m, self.n_total), "<f4"), device=f"cuda:{self.ctx.device}")
 
     def close(self) -> None:
         torch.cuda.synchronize()

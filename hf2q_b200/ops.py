@@ -108,6 +108,10 @@ class GpuContext:
         """Synchronises the current stream and raises if a kernel flagged a problem."""
         self._check(self._lib.hf2q_cuda_check_status(self._h, self._stream()))
 
+    def set_wait_limit(self, clock_ticks: int) -> None:
+        """Upper bound (GPU clock ticks) of the device-side waits for other GPUs; a context setting."""
+        self._check(self._lib.hf2q_cuda_set_wait_limit(self._h, int(clock_ticks)))
+
     @property
     def launch_count(self) -> int:
         return int(self._lib.hf2q_cuda_launch_count(self._h))

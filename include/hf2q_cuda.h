@@ -243,26 +243,38 @@ HF2Q_API int32_t hf2q_cuda_moe_softmax_topk(hf2q_ctx* ctx, void* stream, const f
 /* ---- e: row-sharded mat-vec with the all-gather in its epilogue ------------------------------- *
  * The reference runs on one device and has no collective; this is the multi-GPU form of
  * quantized_matmul_ggml for weights sharded by output rows (one process per GPU).  Every rank owns
- * a full-width output buffer [m][n_total] and an arrival counter, allocated with hf2q_cuda_ipc_alloc
- * and opened by the other ranks with hf2q_cuda_ipc_open (CUDA IPC; needs peer access, i.e. NVLink
- * or PCIe P2P between the GPUs).  hf2q_cuda_qmatmul_gather computes this rank's n rows of the
- * product and stores them into columns [col0, col0 + n) of EVERY rank's buffer (plain stores to
- * peer memory from the kernel's epilogue); every CTA then adds 1 to every other rank's arrival
- * counter (word 0 of that rank's 256-byte counter block), and the launch adds the number of arrivals
- * it stands for to the own expected count (word 1 of the own block).  All ranks issue the same
- * sequence of calls, so a rank has received everything once its word 0 has caught up with its
- * word 1.  A consumer waits for that either inside the next product
- * (wait_previous != 0: the kernel prefetches weights, then waits before it reads x) or with
- * hf2q_cuda_gather_wait.  Both waits are bounded (about a second; a timeout is reported by
- * hf2q_cuda_check_status) and depend on device-side counters only, so a captured CUDA graph of such
- * calls can be replayed.  m <= 8 and the shapes of the tensor-core mat-vec only (16-byte aligned
- * weight rows, k % 256 == 0); one launch per call. */
+ * full-width output buffers [m][n_total] and a 256-byte counter block, allocated with
+ * hf2q_cuda_ipc_alloc (zero-filled) and opened by the other ranks with hf2q_cuda_ipc_open (CUDA IPC;
+ * needs peer access, i.e. NVLink or PCIe P2P between the GPUs).  hf2q_cuda_qmatmul_gather computes
+ * this rank's n rows of the product and stores them into columns [col0, col0 + n) of EVERY rank's
+ * buffer (plain stores to peer memory from the kernel's epilogue).  Every CTA then adds 1 to word
+ * `rank` of every other rank's counter block (one arrival counter per SOURCE rank, words 0..7), and
+ * the launch adds, for every source r, the number of CTAs rank r's shard takes (derived from
+ * n_rows[r]) to word 8 + r of the own block (the expected counts).  All ranks issue the same sequence
+ * of calls, so a rank holds source r's columns of every product launched so far once word r has
+ * caught up with word 8 + r -- independently of what the other sources have delivered and of
+ * uneven shards.  A consumer waits for that either inside the next product (wait_previous != 0:
+ * the kernel prefetches weights, then waits before it reads x) or with hf2q_cuda_gather_wait.
+ * Both waits are bounded (hf2q_cuda_set_wait_limit; about a second by default; a timeout is
+ * reported by hf2q_cuda_check_status and leaves the context usable) and depend on device-side
+ * counters only, so a captured CUDA graph of such calls can be replayed.
+ *
+ * Buffers and ordering.  A product must not store into a buffer that some rank may still be
+ * reading.  A decode chain (x of product i+1 = gathered output of product i) therefore alternates
+ * between TWO output buffers and passes wait_previous != 0 on every product after the first: rank q
+ * starts storing product i+1 only after it has seen product i complete on every rank, and a rank
+ * signals completion only after all its CTAs have read their activations, so nobody still reads
+ * the buffer of product i-1 that product i+1 overwrites.  A product launched with
+ * wait_previous == 0 is only ordered by the caller (e.g. a host barrier before it).
+ * m <= 8 and the shapes of the tensor-core mat-vec only (16-byte aligned weight rows,
+ * k % 256 == 0); one launch per call. */
 typedef struct hf2q_gather {
     void* y_all[8];          /* float [m][n_total] of rank 0..n_ranks-1 as mapped in this process */
     void* flags[8];          /* 256-byte counter block of rank 0..n_ranks-1 */
     uint32_t n_ranks, rank;
     uint32_t n_total, col0;
     uint32_t wait_previous;  /* != 0: wait for all ranks' earlier products before reading x */
+    uint32_t n_rows[8];      /* rows of rank r's shard of this product (n_rows[rank] == n, col0 == sum of the earlier ranks') */
 } hf2q_gather;
 HF2Q_API int32_t hf2q_cuda_ipc_alloc(hf2q_ctx* ctx, uint64_t bytes, void** dev, uint8_t* handle64);
 HF2Q_API int32_t hf2q_cuda_ipc_open(hf2q_ctx* ctx, const uint8_t* handle64, void** dev);
@@ -270,7 +282,14 @@ HF2Q_API int32_t hf2q_cuda_ipc_close(hf2q_ctx* ctx, void* dev);
 HF2Q_API int32_t hf2q_cuda_qmatmul_gather(hf2q_ctx* ctx, void* stream, const void* x, uint32_t x_dtype,
                                           const void* w, const hf2q_gather* g, uint32_t m, uint32_t n,
                                           uint32_t k, uint32_t ggml_type);
-HF2Q_API int32_t hf2q_cuda_gather_wait(hf2q_ctx* ctx, void* stream, const void* flag);
+/* Queues a one-warp kernel that waits (bounded) until every other rank's arrivals at this rank have
+ * caught up with the products launched here so far; only flags[], n_ranks and rank of g are read. */
+HF2Q_API int32_t hf2q_cuda_gather_wait(hf2q_ctx* ctx, void* stream, const hf2q_gather* g);
+/* Upper bound, in GPU clock ticks, of the device-side waits for other GPUs (the fused gather's
+ * arrival counters).  A context setting: set once after creation, never on the launch path.  The
+ * default 2^31 ticks is about a second.  After a timeout the waiting kernel records it (reported as
+ * HF2Q_ERR_TIMEOUT by hf2q_cuda_check_status), carries on with whatever data is there and returns. */
+HF2Q_API int32_t hf2q_cuda_set_wait_limit(hf2q_ctx* ctx, uint64_t clock_ticks);
 
 /* ---- a8: element-wise glue of the FFN builders ---------------------------------------------- */
 

@@ -799,7 +799,11 @@ void oracle_softmax_topk_renorm(const float* logits, int64_t seq_len, int64_t nu
         float inv_d = denom > 1e-20f ? 1.0f / denom : 1.0f;
         for (int64_t e = 0; e < num_experts; ++e) ev[e] *= inv_d;
         std::iota(order.begin(), order.end(), 0);
-        std::stable_sort(order.begin(), order.end(), [&](int64_t a, int64_t b) { return ev[b] < ev[a]; });
+        // The reference sorts stably with partial_cmp().unwrap_or(Equal) (gpu_ffn.rs:1903-1908), which is
+        // not a total order once a NaN is present.  The order is made total here the way the CUDA kernel
+        // does it: a NaN ranks below every number, equal keys keep the lower index first.
+        auto key = [&](int64_t i) { return ev[i] != ev[i] ? -1.0f : ev[i]; };
+        std::stable_sort(order.begin(), order.end(), [&](int64_t a, int64_t b) { return key(b) < key(a); });
         float sum_sel = 0.0f;
         for (int64_t s = 0; s < topk; ++s) sum_sel += ev[order[s]];
         float inv_sum = sum_sel > 1e-20f ? 1.0f / sum_sel : 1.0f / (float)topk;

@@ -26,20 +26,3 @@ def gpu_ctx():
     ctx = hf2q_b200.GpuContext(0)
     yield ctx
     ctx.close()
-
-
-@pytest.fixture(scope="session")
-def gpu_ctx_tc():
-    """A context whose dense mat-vecs take the tcgen05 (tensor-memory) kernel instead of the warp-MMA one."""
-    import os
-    import torch
-    if not torch.cuda.is_available():
-        pytest.skip("no CUDA device")
-    import hf2q_b200
-    os.environ["HF2Q_CUDA_TC_MATVEC"] = "1"
-    try:
-        ctx = hf2q_b200.GpuContext(0)
-    finally:
-        del os.environ["HF2Q_CUDA_TC_MATVEC"]
-    yield ctx
-    ctx.close()

@@ -48,30 +48,83 @@ def _rank_main(rank, world, port, ret):
         y = hd.rowshard_matmul(xd, local, n).cpu().numpy()
         want = oracle.matmul_f64(x, oracle.dequantize(t, raw).reshape(n, k))
         ok &= rel_l2(y, want) < 1e-3
-        # --- dense again, all-gather inside the kernel (peer stores + arrival counters), a chain of
-        # products where each waits for the previous one's columns from every rank
+        # --- dense again, all-gather inside the kernel (peer stores + per-source arrival counters)
         gg = hd.GatherGroup(ctx, 8, n)
         xb = make_x(8, k, seed=5)
+        wfull = oracle.dequantize(t, raw).reshape(n, k)
         for step, mm in enumerate((1, 4, 8, 3)):
             xs = torch.from_numpy(xb[:mm] * (step + 1)).cuda().bfloat16()          # bf16: up to 8 rows per launch
             gg.matmul(xs, w, mm, r0, wait_previous=step > 0)
             gg.wait()
             torch.cuda.synchronize()
             got = gg.output(mm).cpu().numpy()
-            ok &= rel_l2(got, oracle.matmul_f64(xs.float().cpu().numpy(), oracle.dequantize(t, raw).reshape(n, k))) < 1e-3
-            dist.barrier()                      # nobody overwrites the buffers while a peer still reads them
-        # the same chain from a CUDA graph (no collective call inside): replay twice
-        xs = torch.from_numpy(xb[:2]).cuda().bfloat16()
+            ok &= rel_l2(got, oracle.matmul_f64(xs.float().cpu().numpy(), wfull)) < 1e-3
+        dist.barrier()
+        gg.close()
+        # --- a real chain: the gathered output of every product is the next product's activations, no host
+        # synchronisation in between, uneven shards (different CTA counts per rank), two alternating buffers
+        nt = 768
+        sizes = [400, 368] if world == 2 else [200, 184, 192, 192][:world]
+        assert sum(sizes) == nt
+        c0 = sum(sizes[:rank])
+        raws = [make_quant_weight(oracle.Q6_K, nt, 2048, seed=11), make_quant_weight(oracle.Q4_K, nt, nt, seed=12),
+                make_quant_weight(oracle.Q5_K, nt, nt, seed=13), make_quant_weight(oracle.Q6_K, nt, nt, seed=14)]
+        types = [oracle.Q6_K, oracle.Q4_K, oracle.Q5_K, oracle.Q6_K]
+        ks = [2048, nt, nt, nt]
+        shards = []
+        for tt, rw, kk in zip(types, raws, ks):
+            rbk = oracle.row_bytes(tt, kk)
+            shards.append(hq.load_quant_weight(ctx, rw[c0 * rbk:(c0 + sizes[rank]) * rbk], tt, sizes[rank], kk))
+        gg = hd.GatherGroup(ctx, 4, nt)
+        mm = 3
+        x0 = make_x(mm, 2048, seed=21)
+        x0d = torch.from_numpy(x0).cuda()
+        want = [x0.astype(np.float64)]
+        for tt, rw, kk in zip(types, raws, ks):
+            want.append(want[-1] @ oracle.dequantize(tt, rw).reshape(nt, kk).astype(np.float64).T * 8.0)
+
+        def chain(snapshots):
+            xin = x0d
+            for i, wsh in enumerate(shards):
+                gg.matmul(xin, wsh, mm, None, wait_previous=i > 0, n_rows=sizes)
+                xin = gg.output(mm)
+                # (a model would normalise here; a scale keeps the values away from zero)
+                # the scale runs as a torch kernel on the same stream AFTER a wait, so it reads complete data
+                gg.wait()
+                xin.mul_(8.0)
+                if snapshots is not None:
+                    snapshots.append(xin.clone())
+            gg.wait()
+
+        snaps = []
+        chain(snaps)
         torch.cuda.synchronize()
+        for i, sn in enumerate(snaps):
+            ok &= rel_l2(sn.cpu().numpy(), want[i + 1]) < 1e-3
+        dist.barrier()
+        # the products alone, back to back (each waits inside the kernel for the previous one's columns),
+        # captured in a graph and replayed: 4 products = an even number, so buffers alternate consistently
+        def bare_chain():
+            xin = x0d
+            for i, wsh in enumerate(shards):
+                gg.matmul(xin, wsh, mm, None, wait_previous=True, n_rows=sizes)
+                xin = gg.output(mm)
+            gg.wait()
+
+        want_b = [x0.astype(np.float64)]
+        for tt, rw, kk in zip(types, raws, ks):
+            want_b.append(want_b[-1] @ oracle.dequantize(tt, rw).reshape(nt, kk).astype(np.float64).T)
+        bare_chain()
+        torch.cuda.synchronize()
+        dist.barrier()
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph):
-            gg.matmul(xs, w, 2, r0)
-            gg.matmul(xs, w, 2, r0, wait_previous=True)
-            gg.wait()
-        for _ in range(3):
+            bare_chain()
+        for _ in range(5):
             graph.replay()
         torch.cuda.synchronize()
-        ok &= rel_l2(gg.output(2).cpu().numpy(), oracle.matmul_f64(xs.float().cpu().numpy(), oracle.dequantize(t, raw).reshape(n, k))) < 1e-3
+        ok &= rel_l2(gg.output(mm).cpu().numpy(), want_b[-1]) < 1e-3
+        ctx.check_status()
         dist.barrier()
         gg.close()
         # --- MoE: experts sharded, routed rows exchanged
@@ -114,7 +167,60 @@ def test_two_gpu_rowshard_and_expert_parallel():
         procs = [ctx.Process(target=_rank_main, args=(r, world, port, ret)) for r in range(world)]
         for p in procs:
             p.start()
-        for p in procs:
-            p.join(240)
-            assert p.exitcode == 0
+        try:
+            for p in procs:
+                p.join(300)
+        finally:
+            # a rank stuck in a collective must not keep its GPU after the test
+            for p in procs:
+                if p.is_alive():
+                    p.terminate()
+                    p.join(10)
+                    if p.is_alive():
+                        p.kill()
+        assert all(p.exitcode == 0 for p in procs), [p.exitcode for p in procs]
         assert all(ret.get(r) for r in range(world))
+
+
+def _two_device_main(ret):
+    import oracle
+    import hf2q_b200 as hq
+    from tests.util import make_quant_weight, make_x, rel_l2
+
+    ok = True
+    ctxs = [hq.GpuContext(0), hq.GpuContext(1)]
+    for t, n, k in ((oracle.Q6_K, 300, 4096), (oracle.Q4_K, 256, 2048)):
+        raw = make_quant_weight(t, n, k, seed=n)
+        wref = oracle.dequantize(t, raw).reshape(n, k)
+        for d, ctx in enumerate(ctxs):
+            with torch.cuda.device(d):
+                w = hq.load_quant_weight(ctx, raw, t, n, k)
+                for m in (2, 72):                               # mat-vec and tensor-core GEMM: both need > 48 KB of shared memory
+                    x = make_x(m, k, seed=m + d)
+                    xd = torch.from_numpy(x).to(f"cuda:{d}")
+                    y = torch.empty((m, n), device=f"cuda:{d}")
+                    hq.quantized_matmul_ggml(ctx, xd, w, y, w.matmul_params(m))
+                    ctx.check_status()
+                    ok &= rel_l2(y.cpu().numpy(), oracle.matmul_f64(x, wref)) < 1e-3
+    ret["ok"] = bool(ok)
+
+
+def test_one_process_two_devices():
+    """Contexts on two GPUs in one process: the shared-memory opt-in of every kernel is per device."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    with ctx.Manager() as mgr:
+        ret = mgr.dict()
+        p = ctx.Process(target=_two_device_main, args=(ret,))
+        p.start()
+        try:
+            p.join(240)
+        finally:
+            if p.is_alive():
+                p.terminate()
+                p.join(10)
+                if p.is_alive():
+                    p.kill()
+        assert p.exitcode == 0 and ret.get("ok")

@@ -109,13 +109,6 @@ def _gemv_sweep(ctx, t, bf16, bound):
 
 @pytest.mark.parametrize("t", TYPES)
 @pytest.mark.parametrize("bf16", [False, True])
-def test_gemv_tcgen05_variant_matches_f64_reference(gpu_ctx_tc, t, bf16):
-    """Opt-in tcgen05 mat-vec (weights rounded to f16 after scaling, cluster split of k)."""
-    _gemv_sweep(gpu_ctx_tc, t, bf16, 5e-4)        # gate is 1e-3; f16 weight rounding measures ~2e-4
-
-
-@pytest.mark.parametrize("t", TYPES)
-@pytest.mark.parametrize("bf16", [False, True])
 def test_gemv_matches_f64_reference(gpu_ctx, t, bf16):
     """Default routing: warp-MMA kernel (integer codes as f16 subnormals) or the fp32 kernel: far inside the gate."""
     _gemv_sweep(gpu_ctx, t, bf16, 2e-5)
