@@ -1,23 +1,31 @@
 #!/usr/bin/env python
-"""Benchmark of the quantized-weight mat-vec path (the decode hot path) on B200.
+"""Benchmark of the quantized-weight matmul path on B200.
 
-Workload (one GPU): the Q6_K decode GEMV sweep -- weight shapes (out x in) 6144x4096, 4096x4096,
-28672x4096 and 4096x14336, N(0, 0.02) weights quantized to Q6_K (210 B per 256 elements) by the
-CPU oracle's port of hf2q's quantizer, bf16 N(0,1) activations, batches of 1, 4 and 8 tokens,
-fp32 accumulation.  Every matrix is smaller than the 126 MB L2, so the sweep rotates over
-`--copies` distinct device copies of the four matrices (>= 1 GiB in total): no launch finds its
-weights in L2.  One "step" is one pass over all copies x shapes x token counts.
+Headline workload (one GPU): the Q6_K decode GEMV sweep -- weight shapes (out x in) 6144x4096,
+4096x4096, 28672x4096 and 4096x14336, N(0, 0.02) weights quantized to Q6_K (210 B per 256 elements)
+by the CPU oracle's port of hf2q's quantizer, bf16 N(0,1) activations, batches of 1, 4 and 8 tokens,
+fp32 accumulation.  Every matrix is smaller than the 126 MB L2, so the sweep rotates over `--copies`
+distinct device copies of the four matrices (>= 1 GiB in total): no launch finds its weights in L2.
+One "step" is `--passes` passes over all copies x shapes x token counts (16 by default, so that the
+default 20..200 steps time a region of 0.5 s and more).
 
   metric  = dequant-GEMV HBM GB/s = algorithmic bytes (W + 2*m*K + 4*m*N per launch) / device time
   value   = inputs resident in HBM, launches back to back on one stream, CUDA-event timed
   e2e     = the same sweep through the host-buffer C-ABI call (hf2q_cuda_qmatmul_host_async): every
             call queues the copy of its activations from pinned host memory, the kernel and the copy
-            of y back to pinned host memory; one hf2q_cuda_host_sync per step waits for all of them
+            of y back to pinned host memory; one hf2q_cuda_host_sync per pass waits for all of them
+  secondary (one GPU) = the other kernels of the path, measured in the same run with the same
+            timing rules: Q4_K 4096x4096 f32 mat-vec, the Q4_K_M prefill GEMM sweep (TFLOP/s against
+            the measured bf16 peaks), and the Q5_K expert layer at 1 and 2048 tokens.
 
-Multi-GPU (torchrun, one rank per GPU): weak scaling.  Each rank holds the shapes above as ITS row
-shard of a matrix G times taller and runs the same sweep; the mat-vec kernel stores its columns into
-every rank's full-width output buffer itself (peer memory over NVLink, arrival counters), so a step
-contains no collective call and is replayed from a CUDA graph like the single-GPU step.
+Multi-GPU (torchrun, one rank per GPU).  `value` is WEAK scaling: each rank holds the shapes above
+as ITS row shard of a matrix G times taller.  The mat-vec kernel stores its columns into every
+rank's full-width output buffer itself (peer memory over NVLink, per-source arrival counters), so
+a step contains no collective call and is replayed from a CUDA graph like the single-GPU step.  The
+line also carries `strong`: the listed shapes themselves split G ways by rows, same kernels.  Before
+timing, every rank checks one gathered full-width product against the oracle and the run stops on
+a mismatch.  The e2e leg goes through the same sharded call: pinned x -> device on every rank,
+hf2q_cuda_qmatmul_gather, and the full-width y -> pinned host on rank 0.
 
 `--impl reference` times the reference's CPU path for the same products (the oracle's port of
 "dequantise to f32, then matmul_a_by_bt") on the host cores, one bounded sample per step.
@@ -43,6 +51,8 @@ TOKENS = [1, 4, 8]
 Q6_K = 14
 METRIC = "dequant-GEMV HBM GB/s"
 UNIT = "GB/s"
+WORKLOAD = ("Q6_K decode GEMV sweep: shapes 6144x4096, 4096x4096, 28672x4096, 4096x14336; "
+            "m in {1,4,8}; bf16 activations; fp32 accumulate")
 
 
 def algo_bytes(n: int, k: int, m: int, row_bytes: int) -> int:
@@ -155,12 +165,22 @@ def host_inputs():
     return bits, vals
 
 
+def host_threads() -> int:
+    """Host threads this process may use.  torchrun exports OMP_NUM_THREADS=1 for its workers, which
+    would turn the reference arm into a single-core run: take the count from the CPU affinity mask."""
+    try:
+        return max(1, len(os.sched_getaffinity(0)))
+    except AttributeError:
+        return max(1, os.cpu_count() or 1)
+
+
 def run_reference(args) -> None:
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
     import oracle
-    threads = oracle.max_threads()
+    threads = host_threads()
+    oracle.set_threads(threads)
     raws = make_weights()
     _, xvals = host_inputs()
     # size the per-step sample so that warmup + steps end within ~2.5 minutes
@@ -180,7 +200,7 @@ def run_reference(args) -> None:
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * t / args.steps,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
         "data": "synthetic",
-        "config": {"workload": "Q6_K decode GEMV sweep, 4 shapes x m in {1,4,8}, bf16 activations"},
+        "config": {"workload": WORKLOAD},
         "cpu_baseline": {"value": val, "unit": UNIT, "cores": threads, "kind": "port",
                          "sample": f"per step: the first {row_frac:.4f} of the rows of each of the four Q6_K matrices x "
                                    "m in {1,4,8} (dequantise to f32 + sequential-k f32 matmul, OpenMP over rows)"},
@@ -189,25 +209,240 @@ def run_reference(args) -> None:
     print(json.dumps(line))
 
 
-def measured_tensor_peak() -> tuple[float, str]:
+def measured_tensor_peaks() -> tuple[float, float, str]:
+    """(sustained, burst) measured bf16 TFLOP/s of this pool's B200s, else the stated fall-back."""
     p = ROOT / "MEASURED_PEAKS.json"
     if p.exists():
         try:
-            return float(json.loads(p.read_text())["bf16_tflops_sustained"]), "measured (sustained)"
+            j = json.loads(p.read_text())
+            return float(j["bf16_tflops_sustained"]), float(j["bf16_tflops"]), "measured"
         except Exception:
             pass
-    return 1400.0, "fallback"
+    return 1400.0, 1590.0, "fallback"
+
+
+def _random_weight(torch, oracle, dev, t, rows, k):
+    """Random block bytes with finite, small scales: throughput does not depend on the values
+    (parity is what the tests check on real quantizer output)."""
+    rb = oracle.row_bytes(t, k)
+    raw = torch.randint(0, 256, (rows * rb,), dtype=torch.uint8, device=dev)
+    _, bb = oracle.block_geometry(t)
+    v = raw.view(-1, bb)
+    for o in {2: [1], 8: [1], 12: [1, 3], 13: [1, 3], 14: [209]}[t]:       # high byte of each f16 scale
+        v[:, o] &= 0x3B                                                     # finite, |d| < 1
+    return raw
+
+
+def _timed(torch, fn, reps, warm=3):
+    for _ in range(warm):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(reps):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) * 1e-3 / reps
+
+
+def _graph_of(torch, fn):
+    for _ in range(3):
+        fn()
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        fn()
+    return graph
+
+
+def bench_gemm(hq, oracle, torch, ctx, dev, args, toks=None) -> dict:
+    """BASELINE config 3: Q4_K for 6144x4096 (rows 0-5119; the V rows 5120-6143 are Q6_K: a row-range
+    type map), 4096x4096, 28672x4096 and Q6_K for the 4096x14336 down projection, bf16 activations,
+    M in {512, 2048, 4096}; TFLOP/s = 2*M*N*K / CUDA-event time (activation conversion included)."""
+    toks = toks or [512, 2048, 4096]
+    sampler = ClockSampler(ctx.device)
+    sampler.start()
+    l0 = ctx.launch_count
+    per, flops, secs = {}, 0.0, 0.0
+    reps = max(3, min(args.steps, 10))
+    for name, segs, k in (("qkv_6144x4096[Q4_K 0-5119|Q6_K 5120-6143]", [(12, 5120), (14, 1024)], 4096),
+                          ("o_4096x4096[Q4_K]", [(12, 4096)], 4096),
+                          ("gate_up_28672x4096[Q4_K]", [(12, 28672)], 4096),
+                          ("down_4096x14336[Q6_K]", [(14, 4096)], 14336)):
+        ws = [hq.load_quant_weight(ctx, _random_weight(torch, oracle, dev, t, rows, k), t, rows, k) for t, rows in segs]
+        n = sum(rows for _, rows in segs)
+        for m in toks:
+            x = torch.randn(m, k, device=dev).bfloat16()
+            y = torch.empty(m, n, device=dev)
+
+            def run():
+                hq.ops.quantized_matmul_segments(ctx, x, ws, y, m)
+
+            dt = _timed(torch, run, reps)
+            per[f"{name}_M{m}"] = round(2.0 * m * n * k / dt / 1e12, 1)
+            flops += 2.0 * m * n * k
+            secs += dt
+        del ws
+    sus, burst, kind = measured_tensor_peaks()
+    val = flops / secs / 1e12
+    ctx.check_status()
+    return {"metric": "prefill dequant-GEMM TFLOP/s", "value": round(val, 1), "unit": "TFLOP/s",
+            "higher_is_better": True, "dtype": "f16 operands, f32 accumulate",
+            "config": {"workload": "Q4_K_M prefill GEMM sweep (fused QKV with Q6_K V rows, Q4_K o and gate/up, Q6_K down), bf16 activations",
+                       "tokens": toks, "timing": f"CUDA events over {reps} calls per case, activation conversion kernel included"},
+            "roofline": {"bound": "tensor", "achieved": round(val, 1), "peak": sus, "unit": "TFLOP/s",
+                         "frac": round(val / sus, 4), "peak_source": f"of {kind} (sustained)", "peak_burst": burst,
+                         "frac_of_burst": round(val / burst, 4), "kernel": "gemm_tc_kernel", "traffic": None},
+            "per_case_TFLOPs": per, "gpu_launches": int(ctx.launch_count - l0), "clocks": sampler.stop()}
+
+
+def bench_config1(hq, oracle, torch, ctx, dev, args) -> dict:
+    """BASELINE config 1: one Q4_K 4096x4096 matrix, x f32 [1, 4096]; graph over 8 distinct copies."""
+    t, n, k, m = 12, 4096, 4096, 1
+    sampler = ClockSampler(ctx.device)
+    sampler.start()
+    ws = [hq.load_quant_weight(ctx, _random_weight(torch, oracle, dev, t, n, k), t, n, k) for _ in range(16)]
+    x = torch.randn(m, k, device=dev)
+    y = torch.empty(m, n, device=dev)
+    pr = hq.GgmlQuantizedMatmulParams(m, n, k, t)
+
+    def walk():
+        for w in ws:
+            hq.quantized_matmul_ggml(ctx, x, w, y, pr)
+
+    graph = _graph_of(torch, walk)
+    dt = _timed(torch, graph.replay, max(20, min(args.steps * 4, 200))) / len(ws)
+    b = n * oracle.row_bytes(t, k) + 4 * k + 4 * n
+    peak, kind = measured_hbm_peak()
+    ctx.check_status()
+    return {"metric": "Q4_K 4096x4096 f32 mat-vec", "value": round(b / dt / 1e9, 1), "unit": "GB/s", "us_per_launch": round(dt * 1e6, 2),
+            "config": {"workload": "Q4_K 4096x4096, x f32 [1,4096]; CUDA graph over 16 distinct copies (151 MB, larger than L2)"},
+            "roofline": {"bound": "hbm", "achieved": round(b / dt / 1e9, 1), "peak": peak, "unit": "GB/s",
+                         "frac": round(b / dt / 1e9 / peak, 4), "peak_source": f"of {kind}", "kernel": "gemv_mma_kernel<Q4_K>", "traffic": None},
+            "clocks": sampler.stop()}
+
+
+def bench_matvec(hq, oracle, torch, ctx, dev, args) -> dict:
+    """Every block format on the decode shapes: per-launch time from a CUDA graph that walks 8
+    distinct copies of the matrix (so weights come from HBM), bf16 activations."""
+    peak_h, kind_h = measured_hbm_peak()
+    per, tot_b, tot_s = {}, 0.0, 0.0
+    l0 = ctx.launch_count
+    sampler = ClockSampler(ctx.device)
+    sampler.start()
+    for t in ([int(args.qtype)] if args.qtype else [2, 8, 12, 13, 14]):
+        for n, k in SHAPES:
+            ws = [hq.load_quant_weight(ctx, _random_weight(torch, oracle, dev, t, n, k), t, n, k) for _ in range(8)]
+            rb = oracle.row_bytes(t, k)
+            for m in (1, 4, 8):
+                x = torch.randn(m, k, device=dev).bfloat16()
+                y = torch.empty(m, n, device=dev)
+                pr = hq.GgmlQuantizedMatmulParams(m, n, k, t)
+
+                def walk():
+                    for w in ws:
+                        hq.quantized_matmul_ggml(ctx, x, w, y, pr)
+
+                graph = _graph_of(torch, walk)
+                dt = _timed(torch, graph.replay, max(3, min(args.steps, 20))) / len(ws)
+                b = n * rb + 2 * m * k + 4 * m * n
+                per[f"{oracle.TYPE_NAMES[t]}_{n}x{k}_m{m}"] = {"us": round(dt * 1e6, 2), "GBps": round(b / dt / 1e9, 1)}
+                tot_b += b
+                tot_s += dt
+            del ws
+    val = tot_b / tot_s / 1e9
+    ctx.check_status()
+    return {"metric": "dequant-GEMV HBM GB/s (all block formats)", "value": round(val, 1), "unit": "GB/s",
+            "higher_is_better": True, "dtype": "f32",
+            "config": {"workload": "decode mat-vec, 4 shapes x m in {1,4,8} x block formats, bf16 activations; "
+                                   "CUDA graph over 8 copies of each matrix (inputs larger than L2)"},
+            "roofline": {"bound": "hbm", "achieved": round(val, 1), "peak": peak_h, "unit": "GB/s", "frac": round(val / peak_h, 4),
+                         "peak_source": f"of {kind_h}", "kernel": "gemv_mma_kernel", "traffic": None},
+            "per_launch": per, "gpu_launches": int(ctx.launch_count - l0), "clocks": sampler.stop()}
+
+
+def bench_moe(hq, oracle, torch, ctx, dev, args, toks=None) -> dict:
+    """BASELINE config 4: 256 experts, hidden 2048, intermediate 512, top-8, Q5_K; the whole expert
+    layer (router softmax/top-k outputs -> gate, up, SwiGLU, down, weighted combine) at T in {1, 2048}."""
+    t, E, H, I, topk = 13, 256, 2048, 512, 8
+    sg, sd = hq.expert_stride(t, I, H), hq.expert_stride(t, H, I)
+    wg, wu, wd = (_random_weight(torch, oracle, dev, t, E * I, H), _random_weight(torch, oracle, dev, t, E * I, H),
+                  _random_weight(torch, oracle, dev, t, E * H, I))
+    res = {}
+    l0 = ctx.launch_count
+    sampler = ClockSampler(ctx.device)
+    sampler.start()
+    sus, burst, kind_t = measured_tensor_peaks()
+    peak_h, kind_h = measured_hbm_peak()
+    for T in (toks or [1, 2048]):
+        # decode (few tokens) touches 8 experts = 17 MB per layer, far less than L2: rotate over
+        # routings that pick different experts so that weights come from HBM; one CUDA graph
+        # holds all of them (launch overhead of the Python calls stays out of the timing)
+        nsets = 16 if T <= 8 else 1
+        x = torch.randn(T, H, device=dev).bfloat16()
+        R = T * topk
+        g, u = torch.empty(R, I, device=dev), torch.empty(R, I, device=dev)
+        d = torch.empty(R, H, device=dev)
+        out = torch.empty(T, H, device=dev)
+        act = torch.randn(R, I, device=dev).bfloat16()
+        sc = hq.IdMmScratch.alloc(ctx, E, R, H)
+        pg = hq.GgmlQuantizedMatmulIdParams(T, topk, I, H, E, sg, t)
+        pd = hq.GgmlQuantizedMatmulIdParams(R, 1, H, I, E, sd, t)
+        id_sets, wt_sets = [], []
+        for i in range(nsets):
+            if T <= 8:          # disjoint expert groups per set
+                logits = torch.full((T, E), -30.0, device=dev)
+                logits[:, (i * topk * T) % E:(i * topk * T) % E + topk * T] = torch.randn(T, topk * T, device=dev)
+            else:
+                logits = torch.randn(T, E, device=dev)
+            ids, wts = hq.moe_softmax_topk(ctx, logits, topk)
+            id_sets.append(ids)
+            wt_sets.append(wts)
+
+        fused = hq.ops.quantized_matmul_id_swiglu_supported(ctx, pg, x.dtype)
+
+        def layer(ids, wts):
+            if fused:     # few routed rows: gate, up and the SwiGLU in one launch
+                hq.ops.quantized_matmul_id_swiglu_ggml(ctx, x, wg.data_ptr(), wu.data_ptr(), ids, g, pg)
+            else:
+                hq.quantized_matmul_id_pair_ggml(ctx, x, wg.data_ptr(), wu.data_ptr(), ids, g, u, sc, pg)   # gate + up
+                ctx._check(ctx._lib.hf2q_cuda_silu_mul(ctx._h, ctx._stream(), g.data_ptr(), u.data_ptr(), g.data_ptr(), g.numel()))
+            # (down reads synthetic activations: products of random block bytes leave the f16 range)
+            hq.quantized_matmul_id_ggml(ctx, act, wd.data_ptr(), ids, d, sc, pd)
+            ctx._check(ctx._lib.hf2q_cuda_moe_combine(ctx._h, ctx._stream(), d.data_ptr(), wts.data_ptr(), None, None, None,
+                                                      out.data_ptr(), T, topk, H))
+
+        def all_sets():
+            for ids, wts in zip(id_sets, wt_sets):
+                layer(ids, wts)
+
+        graph = _graph_of(torch, all_sets)
+        dt = _timed(torch, graph.replay, max(3, min(args.steps, 20))) / nsets
+        nexp = int(torch.unique(id_sets[0]).numel())
+        wbytes = nexp * (2 * sg + sd)
+        fl = 2.0 * R * 3 * I * H
+        t_hbm, t_tc = wbytes / (peak_h * 1e9), fl / (sus * 1e12)
+        res[f"T{T}"] = {"us_per_layer": round(dt * 1e6, 1), "TFLOPs": round(fl / dt / 1e12, 2),
+                        "weight_GBps": round(wbytes / dt / 1e9, 1), "experts_touched": nexp,
+                        "roofline_hbm_us": round(t_hbm * 1e6, 1), "roofline_tensor_us": round(t_tc * 1e6, 1),
+                        "frac_of_binding_roofline": round(max(t_hbm, t_tc) / dt, 4),
+                        "swiglu_in_gate_up_launch": bool(fused),
+                        "timing": f"CUDA graph of {nsets} layer(s) with different routings; gate+up, SwiGLU, down and the weighted combine"}
+    ctx.check_status()
+    last = res[sorted(res)[-1]]
+    return {"metric": "MoE mul_mat_id layer time", "value": last["us_per_layer"], "unit": "us",
+            "higher_is_better": False, "dtype": "f16 operands, f32 accumulate",
+            "config": {"workload": "Qwen3-style A3B expert layer: 256 experts, hidden 2048, intermediate 512, top-8, Q5_K; "
+                                   "gate + up + SwiGLU + down mul_mat_id + weighted combine (router outputs from the softmax/top-k kernel)"},
+            "roofline": {"bound": "hbm", "achieved": last["weight_GBps"], "peak": peak_h, "unit": "GB/s",
+                         "frac": round(last["weight_GBps"] / peak_h, 4), "peak_source": f"of {kind_h}; tensor: {kind_t} sustained",
+                         "kernel": "gemm_tc_kernel<grouped> + moe_sort/gather (T=2048), gemv_mma_kernel (T=1)", "traffic": None},
+            "per_case": res, "gpu_launches": int(ctx.launch_count - l0), "clocks": sampler.stop()}
 
 
 def run_secondary(args) -> None:
-    """The other two kernels of the path on one GPU, same timing rules, one JSON line each run.
-
-    gemm: BASELINE config 3 -- Q4_K for 6144x4096, 4096x4096, 28672x4096 and Q6_K for the 4096x14336
-          down projection, bf16 activations, M in {512, 2048, 4096}; metric = TFLOP/s (2*M*N*K).
-    moe:  BASELINE config 4 -- 256 experts, hidden 2048, intermediate 512, top-8, Q5_K; gate, up and
-          down mul_mat_id at T in {1, 2048}; metric = layer time and the two rooflines.
-    Weights here are random block bytes with finite scales (throughput does not depend on the values;
-    parity is what the tests check)."""
+    """One of the other workloads alone on one GPU: one JSON line."""
     import torch
 
     import hf2q_b200 as hq
@@ -216,179 +451,38 @@ def run_secondary(args) -> None:
     torch.cuda.set_device(0)
     dev = torch.device("cuda", 0)
     ctx = hq.GpuContext(0)
-
-    def random_weight(t, rows, k):
-        rb = oracle.row_bytes(t, k)
-        raw = torch.randint(0, 256, (rows * rb,), dtype=torch.uint8, device=dev)
-        be, bb = oracle.block_geometry(t)
-        v = raw.view(-1, bb)
-        for o in {2: [1], 8: [1], 12: [1, 3], 13: [1, 3], 14: [209]}[t]:       # high byte of each f16 scale
-            v[:, o] &= 0x3B                                                     # finite, |d| < 1
-        return raw
-
-    def timed(fn, reps):
-        for _ in range(max(3, args.warmup)):
-            fn()
-        torch.cuda.synchronize()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for _ in range(reps):
-            fn()
-        e1.record()
-        torch.cuda.synchronize()
-        return e0.elapsed_time(e1) * 1e-3 / reps
-
-    sampler = ClockSampler(0)
-    sampler.start()
-    l0 = ctx.launch_count
+    toks = [args.tokens] if args.tokens else None
     if args.workload == "gemm":
-        cases = [(12, 6144, 4096), (12, 4096, 4096), (12, 28672, 4096), (14, 4096, 14336)]
-        toks = [args.tokens] if args.tokens else [512, 2048, 4096]
-        rows, flops, secs = {}, 0.0, 0.0
-        for (t, n, k) in cases:
-            w = hq.load_quant_weight(ctx, random_weight(t, n, k), t, n, k)
-            for m in toks:
-                x = torch.randn(m, k, device=dev).bfloat16()
-                y = torch.empty(m, n, device=dev)
-                prm = hq.GgmlQuantizedMatmulParams(m, n, k, t)
-                dt = timed(lambda: hq.quantized_matmul_ggml(ctx, x, w, y, prm), max(3, min(args.steps, 20)))
-                rows[f"{oracle.TYPE_NAMES[t]}_{n}x{k}_M{m}"] = round(2.0 * m * n * k / dt / 1e12, 1)
-                flops += 2.0 * m * n * k
-                secs += dt
-        peak, kind = measured_tensor_peak()
-        val = flops / secs / 1e12
-        line = {"metric": "prefill dequant-GEMM TFLOP/s", "value": round(val, 1), "unit": "TFLOP/s", "n_gpus": 1,
-                "higher_is_better": True, "dtype": "f16 operands, f32 accumulate", "data": "synthetic",
-                "config": {"workload": "Q4_K_M prefill GEMM sweep (Q4_K x3 shapes, Q6_K 4096x14336), bf16 activations",
-                           "tokens": toks, "timing": "CUDA events, activation conversion kernel included"},
-                "roofline": {"bound": "tensor", "achieved": round(val, 1), "peak": peak, "unit": "TFLOP/s",
-                             "frac": round(val / peak, 4), "peak_source": f"of {kind}", "kernel": "gemm_tc_kernel", "traffic": None},
-                "per_case_TFLOPs": rows}
+        line = bench_gemm(hq, oracle, torch, ctx, dev, args, toks)
     elif args.workload == "matvec":
-        # every block format on the decode shapes: per-launch time from a CUDA graph that walks 8
-        # distinct copies of the matrix (so weights come from HBM), bf16 activations
-        peak_h, kind_h = measured_hbm_peak()
-        shapes = [(6144, 4096), (4096, 4096), (28672, 4096), (4096, 14336)]
-        per, tot_b, tot_s = {}, 0.0, 0.0
-        for t in ([int(args.qtype)] if args.qtype else [2, 8, 12, 13, 14]):
-            for n, k in shapes:
-                ws = [hq.load_quant_weight(ctx, random_weight(t, n, k), t, n, k) for _ in range(8)]
-                rb = oracle.row_bytes(t, k)
-                for m in (1, 4, 8):
-                    x = torch.randn(m, k, device=dev).bfloat16()
-                    y = torch.empty(m, n, device=dev)
-                    pr = hq.GgmlQuantizedMatmulParams(m, n, k, t)
-
-                    def walk():
-                        for w in ws:
-                            hq.quantized_matmul_ggml(ctx, x, w, y, pr)
-
-                    for _ in range(3):
-                        walk()
-                    torch.cuda.synchronize()
-                    graph = torch.cuda.CUDAGraph()
-                    with torch.cuda.graph(graph):
-                        walk()
-                    dt = timed(graph.replay, max(3, min(args.steps, 20))) / len(ws)
-                    b = n * rb + 2 * m * k + 4 * m * n
-                    per[f"{oracle.TYPE_NAMES[t]}_{n}x{k}_m{m}"] = {"us": round(dt * 1e6, 2), "GBps": round(b / dt / 1e9, 1)}
-                    tot_b += b
-                    tot_s += dt
-                del ws
-        val = tot_b / tot_s / 1e9
-        line = {"metric": "dequant-GEMV HBM GB/s (all block formats)", "value": round(val, 1), "unit": "GB/s", "n_gpus": 1,
-                "higher_is_better": True, "dtype": "f32", "data": "synthetic",
-                "config": {"workload": "decode mat-vec, 4 shapes x m in {1,4,8} x block formats, bf16 activations; "
-                                       "CUDA graph over 8 copies of each matrix (inputs larger than L2)"},
-                "roofline": {"bound": "hbm", "achieved": round(val, 1), "peak": peak_h, "unit": "GB/s", "frac": round(val / peak_h, 4),
-                             "peak_source": f"of {kind_h}", "kernel": "gemv_mma_kernel", "traffic": None},
-                "per_launch": per}
+        line = bench_matvec(hq, oracle, torch, ctx, dev, args)
+    elif args.workload == "config1":
+        line = bench_config1(hq, oracle, torch, ctx, dev, args)
     else:
-        t, E, H, I, topk = 13, 256, 2048, 512, 8
-        sg, sd = hq.expert_stride(t, I, H), hq.expert_stride(t, H, I)
-        wg, wu, wd = random_weight(t, E * I, H), random_weight(t, E * I, H), random_weight(t, E * H, I)
-        res = {}
-        for T in ([args.tokens] if args.tokens else [1, 2048]):
-            # decode (few tokens) touches 8 experts = 17 MB per layer, far less than L2: rotate over
-            # routings that pick different experts so that weights come from HBM; one CUDA graph
-            # holds all of them (launch overhead of the Python calls stays out of the timing)
-            nsets = 16 if T <= 8 else 1
-            x = torch.randn(T, H, device=dev).bfloat16()
-            R = T * topk
-            g, u = torch.empty(R, I, device=dev), torch.empty(R, I, device=dev)
-            d = torch.empty(R, H, device=dev)
-            act = torch.randn(R, I, device=dev).bfloat16()
-            sc = hq.IdMmScratch.alloc(ctx, E, R, H)
-            pg = hq.GgmlQuantizedMatmulIdParams(T, topk, I, H, E, sg, t)
-            pd = hq.GgmlQuantizedMatmulIdParams(R, 1, H, I, E, sd, t)
-            id_sets = []
-            for i in range(nsets):
-                if T <= 8:          # disjoint expert groups per set
-                    logits = torch.full((T, E), -30.0, device=dev)
-                    logits[:, (i * topk * T) % E:(i * topk * T) % E + topk * T] = torch.randn(T, topk * T, device=dev)
-                else:
-                    logits = torch.randn(T, E, device=dev)
-                id_sets.append(hq.moe_softmax_topk(ctx, logits, topk)[0])
-
-            fused = hq.ops.quantized_matmul_id_swiglu_supported(ctx, pg, x.dtype)
-
-            def layer(ids):
-                if fused:     # few routed rows: gate, up and the SwiGLU in one launch
-                    hq.ops.quantized_matmul_id_swiglu_ggml(ctx, x, wg.data_ptr(), wu.data_ptr(), ids, g, pg)
-                else:
-                    hq.quantized_matmul_id_pair_ggml(ctx, x, wg.data_ptr(), wu.data_ptr(), ids, g, u, sc, pg)   # gate + up
-                # (down reads synthetic activations: products of random block bytes leave the f16 range)
-                hq.quantized_matmul_id_ggml(ctx, act, wd.data_ptr(), ids, d, sc, pd)
-
-            def all_sets():
-                for ids in id_sets:
-                    layer(ids)
-
-            for _ in range(3):
-                all_sets()
-            torch.cuda.synchronize()
-            graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(graph):
-                all_sets()
-            dt = timed(graph.replay, max(3, min(args.steps, 20))) / nsets
-            nexp = int(torch.unique(id_sets[0]).numel())
-            wbytes = nexp * (2 * sg + sd)
-            res[f"T{T}"] = {"us_per_layer": round(dt * 1e6, 1), "TFLOPs": round(2.0 * R * 3 * I * H / dt / 1e12, 2),
-                            "weight_GBps": round(wbytes / dt / 1e9, 1), "experts_touched": nexp,
-                            "swiglu_in_gate_up_launch": bool(fused),
-                            "timing": f"CUDA graph of {nsets} layer(s) with different routings"}
-        peak_h, kind_h = measured_hbm_peak()
-        last = res[sorted(res)[-1]]
-        line = {"metric": "MoE mul_mat_id layer time", "value": last["us_per_layer"], "unit": "us", "n_gpus": 1,
-                "higher_is_better": False, "dtype": "f16 operands, f32 accumulate", "data": "synthetic",
-                "config": {"workload": "Qwen3-style A3B expert layer: 256 experts, hidden 2048, intermediate 512, top-8, Q5_K; "
-                                       "gate + up + down mul_mat_id (router outputs from the softmax/top-k kernel)"},
-                "roofline": {"bound": "hbm", "achieved": last["weight_GBps"], "peak": peak_h, "unit": "GB/s",
-                             "frac": round(last["weight_GBps"] / peak_h, 4), "peak_source": f"of {kind_h}",
-                             "kernel": "gemm_tc_kernel<grouped> + moe_sort/gather (T=2048), gemv_mma_kernel (T=1)", "traffic": None},
-                "per_case": res}
-    line["gpu_launches"] = int(ctx.launch_count - l0)
-    line["clocks"] = sampler.stop()
-    ctx.check_status()
+        line = bench_moe(hq, oracle, torch, ctx, dev, args, toks)
+    line.update({"n_gpus": 1, "data": "synthetic"})
     print(json.dumps(line))
 
 
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=200)
-    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--steps", type=int, default=40)
+    ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--copies", type=int, default=8, help="distinct device copies of the four matrices")
-    ap.add_argument("--e2e-steps", type=int, default=0, help="steps of the host-buffer leg (0 = auto)")
+    ap.add_argument("--passes", type=int, default=16, help="passes over all copies x shapes x token counts per step")
+    ap.add_argument("--e2e-steps", type=int, default=0, help="passes of the host-buffer leg (0 = auto)")
     ap.add_argument("--no-chain-wait", action="store_true",
                     help="several GPUs: products do not wait for the previous product's columns (analysis aid)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-secondary", action="store_true", help="one GPU: skip the config 1 / GEMM / MoE measurements")
+    ap.add_argument("--no-strong", action="store_true", help="several GPUs: skip the strong-scaling leg")
     ap.add_argument("--no-graph", action="store_true", help="issue launches eagerly instead of replaying a CUDA graph")
     ap.add_argument("--qtype", default="", help="matvec: one ggml type number (2, 8, 12, 13, 14) instead of all five")
-    ap.add_argument("--workload", default="gemv", choices=["gemv", "gemm", "moe", "matvec"],
-                    help="gemv: the headline Q6_K decode sweep (default); gemm: Q4_K_M prefill GEMM sweep; "
-                         "moe: Qwen3-style A3B expert layer (Q5_K mul_mat_id)")
+    ap.add_argument("--workload", default="gemv", choices=["gemv", "gemm", "moe", "matvec", "config1"],
+                    help="gemv: the headline Q6_K decode sweep (default, carries the others as `secondary`); gemm: Q4_K_M prefill "
+                         "GEMM sweep; moe: Qwen3-style A3B expert layer (Q5_K mul_mat_id); matvec: all block formats; config1: Q4_K 4096^2 f32")
     ap.add_argument("--tokens", type=int, default=0, help="gemm/moe: one token count instead of the sweep")
     args = ap.parse_args()
     if args.warmup < 3:
@@ -405,6 +499,7 @@ def main() -> None:
 
     import hf2q_b200 as hq
     import oracle
+    from tests.util import rel_l2
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -415,6 +510,7 @@ def main() -> None:
     dev = torch.device("cuda", local_rank)
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
+    oracle.set_threads(max(1, host_threads() // max(1, world)))      # torchrun exports OMP_NUM_THREADS=1
     ctx = hq.GpuContext(local_rank)
 
     # ---- inputs: every rank builds its own shard set (distinct seeds per rank) ----
@@ -430,8 +526,8 @@ def main() -> None:
     ydev = {(n, m): torch.empty((m, n), dtype=torch.float32, device=dev) for n, _ in SHAPES for m in TOKENS}
     # Several GPUs: each rank's shard is rows [rank*n, (rank+1)*n) of a matrix world*n rows tall, and the
     # kernel itself stores its columns into every rank's full-width output (peer stores + arrival
-    # counters, hf2q_b200.dist.GatherGroup); each product waits for the previous one's columns from
-    # all ranks before it reads its activations, as a decode chain would.
+    # counters, hf2q_b200.dist.GatherGroup; two alternating output buffers); each product waits for the
+    # previous one's columns from all ranks before it reads its activations, as a decode chain would.
     gather = None
     if world > 1:
         from hf2q_b200.dist import GatherGroup
@@ -445,69 +541,97 @@ def main() -> None:
         ygath = {(n, m): torch.empty((world, m, n), dtype=torch.float32, device=dev) for n, _ in SHAPES for m in TOKENS}
     params = {(n, k, m): hq.GgmlQuantizedMatmulParams(m, n, k, Q6_K) for n, k in SHAPES for m in TOKENS}
 
-    launches_per_step = args.copies * len(SHAPES) * len(TOKENS)
-    bytes_per_step = args.copies * sum(algo_bytes(n, k, m, row_b[k]) for n, k in SHAPES for m in TOKENS)
+    launches_per_pass = args.copies * len(SHAPES) * len(TOKENS)
+    bytes_per_pass = args.copies * sum(algo_bytes(n, k, m, row_b[k]) for n, k in SHAPES for m in TOKENS)
     working_set = args.copies * sum(len(r) for r in raws)
 
-    def step():
+    def one_pass(grp):
         for m in TOKENS:
             for c in range(args.copies):
                 for (n, k), w in zip(SHAPES, weights[c]):
-                    if gather is None:
+                    if grp is None:
                         hq.quantized_matmul_ggml(ctx, xdev[(k, m)], w, ydev[(n, m)], params[(n, k, m)])
                         if world > 1:
                             dist.all_gather_into_tensor(ygath[(n, m)], ydev[(n, m)])
                     else:
-                        gather.matmul(xdev[(k, m)], w, m, rank * n, wait_previous=not args.no_chain_wait)
-        if gather is not None:
-            gather.wait()           # the step ends when every rank's columns of the last product are here
+                        grp.matmul(xdev[(k, m)], w, m, rank * n, wait_previous=not args.no_chain_wait)
+        if grp is not None:
+            grp.wait()           # the pass ends when every rank's columns of the last product are here
+
+    def step():
+        for _ in range(args.passes):
+            one_pass(gather)
 
     def barrier():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
 
-    # ---- parity spot check before timing (oracle is the checker, never the timed path) ----
-    if rank == 0:
-        from tests.util import rel_l2
-        n, k = SHAPES[1]
-        y = ydev[(n, 4)]
-        hq.quantized_matmul_ggml(ctx, xdev[(k, 4)], weights[0][1], y, params[(n, k, 4)])
+    # ---- parity before timing (the oracle is the checker, never the timed path) ----
+    # One GPU: one product against the f64 product on the oracle's weights.  Several GPUs: EVERY rank
+    # checks one gathered full-width product -- all ranks' columns as they arrived in its own buffer
+    # -- against the oracle; any mismatch ends the run with a non-zero exit code.
+    wref = {}
+
+    def ref_weight(r, i):
+        # rank r's copy of shape i (its seed), dequantised by the oracle
+        if (r, i) not in wref:
+            n, k = SHAPES[i]
+            raw = raws[i] if r == rank else make_weights_one(i, seed0=10 * r)
+            wref[(r, i)] = oracle.dequantize(Q6_K, raw).reshape(n, k)
+        return wref[(r, i)]
+
+    def make_weights_one(i, seed0):
+        from tests.util import make_quant_weight
+        n, k = SHAPES[i]
+        return make_quant_weight(Q6_K, n, k, seed=seed0 + i)
+
+    verify = {"checked": None}
+    n1, k1 = SHAPES[1]
+    if gather is None:
+        y = ydev[(n1, 4)]
+        hq.quantized_matmul_ggml(ctx, xdev[(k1, 4)], weights[0][1], y, params[(n1, k1, 4)])
         ctx.check_status()
-        wref = oracle.dequantize(Q6_K, raws[1]).reshape(n, k)
-        err = rel_l2(y.cpu().numpy(), oracle.matmul_f64(xvals[(k, 4)], wref))
+        err = rel_l2(y.cpu().numpy(), oracle.matmul_f64(xvals[(k1, 4)], ref_weight(rank, 1)))
         if not err < 1e-3:
             raise SystemExit(f"parity check failed before timing: rel L2 {err}")
-
-    # Several GPUs: one trial step of the fused form.  A rank whose bounded waits ran out (a peer's
-    # columns never arrived) or whose step took implausibly long votes to drop it, and then every rank
-    # uses NCCL all-gathers instead: the bench must end either way.
-    if gather is not None:
+        verify = {"checked": "4096x4096 m=4 on this GPU", "rel_l2": err}
+    else:
         barrier()
-        t_trial = time.perf_counter()
-        step()
-        torch.cuda.synchronize()
-        bad = time.perf_counter() - t_trial > 0.5
+        ok = 1.0
+        errs = []
+        for i, m in ((1, 4), (3, 8)):                   # a single-phase shape and the k-phase shape
+            n, k = SHAPES[i]
+            gather.matmul(xdev[(k, m)], weights[0][i], m, rank * n, wait_previous=True)
+            gather.wait()
+            torch.cuda.synchronize()
+            got = gather.output(m)[:, : world * n].cpu().numpy()
+            want = np.concatenate([oracle.matmul_f64(xvals[(k, m)], ref_weight(r, i)) for r in range(world)], axis=1)
+            err = rel_l2(got, want)
+            errs.append(err)
+            if not err < 1e-3:
+                ok = 0.0
+            dist.barrier()
         try:
             ctx.check_status()
         except hq.Hf2qError:
-            bad = True
-        vote = torch.tensor([1.0 if bad else 0.0], device=dev)
-        dist.all_reduce(vote, op=dist.ReduceOp.MAX)
-        if float(vote.item()) > 0:
-            if rank == 0:
-                print("[bench] the fused gather did not complete its trial step; using NCCL all-gathers after each product (eager launches)",
-                      file=sys.stderr)
-            gather.close()
-            gather = None
-            ygath = {(n, m): torch.empty((world, m, n), dtype=torch.float32, device=dev) for n, _ in SHAPES for m in TOKENS}
+            ok = 0.0
+        vote = torch.tensor([ok], device=dev)
+        dist.all_reduce(vote, op=dist.ReduceOp.MIN)
+        if float(vote.item()) < 1.0:
+            print(f"[bench] rank {rank}: gathered product differs from the oracle (rel L2 {errs}) or a wait ran out", file=sys.stderr)
+            dist.destroy_process_group()
+            raise SystemExit(3)
+        verify = {"checked": f"gathered full-width products (4096x4096 m=4, 4096x14336 m=8) on all {world} ranks", "rel_l2_rank0": max(errs)}
+        wref.clear()
 
     for _ in range(args.warmup):
-        step()
+        one_pass(gather)
     barrier()
     # One step's launches are captured into a CUDA graph and replayed (what a decode loop does); the
     # multi-GPU step contains no collective call (the all-gather is in the kernels), so it is captured
-    # the same way.
+    # the same way.  (One pass holds an even number of products, so the two output buffers alternate
+    # consistently across replays.)
     graph = None
     if not args.no_graph and (world == 1 or gather is not None):     # NCCL calls are not captured
         try:
@@ -515,11 +639,11 @@ def main() -> None:
             with torch.cuda.graph(g):
                 step()
             graph = g
-            l_per = launches_per_step
         except Exception as exc:      # capture unsupported: fall back to eager launches, say so
             print(f"[bench] graph capture failed ({exc}); timing eager launches", file=sys.stderr)
             graph = None
     run_step = graph.replay if graph is not None else step
+    graph_used = graph is not None
     for _ in range(3):
         run_step()
     barrier()
@@ -534,75 +658,148 @@ def main() -> None:
     barrier()
     clocks = sampler.stop()
     ms = ev0.elapsed_time(ev1)
-    gpu_launches = (ctx.launch_count - l0) if graph is None else (launches_per_step + (1 if gather is not None else 0)) * args.steps
+    per_step_launches = args.passes * (launches_per_pass + (1 if gather is not None else 0))
+    gpu_launches = (ctx.launch_count - l0) if graph is None else per_step_launches * args.steps
     ctx.check_status()
     if world > 1:
         tms = torch.tensor([ms], device=dev)
         dist.all_reduce(tms, op=dist.ReduceOp.MAX)
         ms = float(tms.item())
     ms_per_step = ms / args.steps
+    bytes_per_step = args.passes * bytes_per_pass
     value = world * bytes_per_step / (ms_per_step * 1e-3) / 1e9
     per_gpu = bytes_per_step / (ms_per_step * 1e-3) / 1e9
 
     # ---- per-(m) breakdown, kernel only, rank-local (explains the aggregate) ----
     breakdown = {}
     for m in TOKENS:
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        reps = max(3, min(20, args.steps))
-        torch.cuda.synchronize()
-        e0.record()
-        for _ in range(reps):
+        def walk_m():
             for c in range(args.copies):
                 for (n, k), w in zip(SHAPES, weights[c]):
                     hq.quantized_matmul_ggml(ctx, xdev[(k, m)], w, ydev[(n, m)], params[(n, k, m)])
-        e1.record()
-        torch.cuda.synchronize()
+        gm = _graph_of(torch, walk_m)
+        dt = _timed(torch, gm.replay, max(5, min(20, args.steps)))
         b = args.copies * sum(algo_bytes(n, k, m, row_b[k]) for n, k in SHAPES)
-        breakdown[f"m{m}_GBps"] = round(b * reps / (e0.elapsed_time(e1) * 1e-3) / 1e9, 1)
+        breakdown[f"m{m}_GBps"] = round(b / dt / 1e9, 1)
+        del gm
 
-    # ---- e2e leg: host buffers through hf2q_cuda_qmatmul_host ----
+    # ---- strong scaling (several GPUs): the listed shapes themselves, rows split over the ranks ----
+    strong = None
+    if gather is not None and not args.no_strong:
+        sw = []
+        for c in range(args.copies):
+            row = []
+            for (n, k), w in zip(SHAPES, weights[c]):
+                row.append(w.row_slice(0, n // world))          # any n/world rows of the rank's bytes: same work
+            sw.append(row)
+        sg = GatherGroup(ctx, max(TOKENS), max(n for n, _ in SHAPES))
+
+        def strong_pass():
+            for m in TOKENS:
+                for c in range(args.copies):
+                    for (n, k), w in zip(SHAPES, sw[c]):
+                        sg.matmul(xdev[(k, m)], w, m, rank * (n // world), wait_previous=True)
+            sg.wait()
+
+        def strong_step():
+            for _ in range(args.passes):
+                strong_pass()
+
+        for _ in range(3):
+            strong_pass()
+        barrier()
+        gs = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(gs):
+            strong_step()
+        for _ in range(2):
+            gs.replay()
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        reps = max(3, min(args.steps, 10))
+        e0.record()
+        for _ in range(reps):
+            gs.replay()
+        e1.record()
+        barrier()
+        sms = torch.tensor([e0.elapsed_time(e1) / reps], device=dev)
+        dist.all_reduce(sms, op=dist.ReduceOp.MAX)
+        ctx.check_status()
+        strong = {"ms_per_step": round(float(sms.item()), 4), "GBps": round(bytes_per_step / (float(sms.item()) * 1e-3) / 1e9, 1),
+                  "what": f"the listed shapes split {world} ways by rows (total bytes = the one-GPU sweep's); same kernels, same chain waits; "
+                          "divide by the one-GPU value of this bench for the speed-up"}
+        del gs
+        sg.close()
+
+    # ---- e2e leg: host buffers through the public call ----
     pin_x = {key: torch.from_numpy(b.view(np.int16).copy()).pin_memory() for key, b in xbits.items()}
-    pin_y = {(n, m): torch.empty((m, n), dtype=torch.float32).pin_memory() for n, _ in SHAPES for m in TOKENS}
     np_x = {key: t.numpy() for key, t in pin_x.items()}
-    np_y = {key: t.numpy() for key, t in pin_y.items()}
+    if gather is None:
+        pin_y = {(n, m): torch.empty((m, n), dtype=torch.float32).pin_memory() for n, _ in SHAPES for m in TOKENS}
+        np_y = {key: t.numpy() for key, t in pin_y.items()}
 
-    def e2e_step():
-        for m in TOKENS:
-            for c in range(args.copies):
-                for (n, k), w in zip(SHAPES, weights[c]):
-                    hq.ops.quantized_matmul_host(ctx, np_x[(k, m)], w, np_y[(n, m)], m, hq.ops.DT_BF16, wait=False)
-        hq.ops.host_sync(ctx)                    # the step's results are in pinned host memory from here on
+        def e2e_pass():
+            for m in TOKENS:
+                for c in range(args.copies):
+                    for (n, k), w in zip(SHAPES, weights[c]):
+                        hq.ops.quantized_matmul_host(ctx, np_x[(k, m)], w, np_y[(n, m)], m, hq.ops.DT_BF16, wait=False)
+            hq.ops.host_sync(ctx)                    # the pass's results are in pinned host memory from here on
+        e2e_api = "hf2q_cuda_qmatmul_host_async per product (pinned host x -> device, kernel, y -> pinned host), hf2q_cuda_host_sync once per pass"
+        d2h = args.copies * sum(4 * m * n for n, _ in SHAPES for m in TOKENS)
+    else:
+        # the sharded call: every rank copies its activations in, the product gathers, rank 0 (the
+        # rank that would hand the result on) copies the full-width output to pinned host memory
+        xin = {key: torch.empty_like(t) for key, t in xdev.items()}
+        pin_xv = {key: t.view(torch.bfloat16).reshape(key[1], key[0]) for key, t in pin_x.items()}
+        pin_y = {(n, m): torch.empty((m, world * n), dtype=torch.float32).pin_memory() for n, _ in SHAPES for m in TOKENS} if rank == 0 else {}
 
-    e2e_steps = args.e2e_steps or max(3, min(args.steps, 30))
+        def e2e_pass():
+            for m in TOKENS:
+                for c in range(args.copies):
+                    for (n, k), w in zip(SHAPES, weights[c]):
+                        xin[(k, m)].copy_(pin_xv[(k, m)], non_blocking=True)
+                        gather.matmul(xin[(k, m)], w, m, rank * n, wait_previous=True)
+                        if rank == 0:
+                            gather.wait()
+                            pin_y[(n, m)].copy_(gather.output(m)[:, : world * n], non_blocking=True)
+            gather.wait()
+            torch.cuda.synchronize()
+        e2e_api = ("per product: pinned host x -> device on every rank, hf2q_cuda_qmatmul_gather (all-gather in the kernel), "
+                   "full-width y -> pinned host on rank 0; one synchronize per pass")
+        d2h = args.copies * sum(4 * m * n * world for n, _ in SHAPES for m in TOKENS)
+
+    e2e_passes = args.e2e_steps or max(3, min(args.steps, 20))
     for _ in range(3):
-        e2e_step()
+        e2e_pass()
     barrier()
     t0 = time.perf_counter()
-    for _ in range(e2e_steps):
-        e2e_step()
+    for _ in range(e2e_passes):
+        e2e_pass()
     barrier()
     e2e_s = time.perf_counter() - t0
     if world > 1:
         ts = torch.tensor([e2e_s], device=dev)
         dist.all_reduce(ts, op=dist.ReduceOp.MAX)
         e2e_s = float(ts.item())
-    e2e_val = world * bytes_per_step * e2e_steps / e2e_s / 1e9
+    ctx.check_status()
+    e2e_val = world * bytes_per_pass * e2e_passes / e2e_s / 1e9
     h2d = args.copies * sum(2 * m * k for _, k in SHAPES for m in TOKENS)
-    d2h = args.copies * sum(4 * m * n for n, _ in SHAPES for m in TOKENS)
 
     if rank != 0:
+        if gather is not None:
+            gather.close()
         if world > 1:
             dist.destroy_process_group()
         return
 
     peak, peak_kind = measured_hbm_peak()
     ratio = ncu_traffic_per_launch()
-    mean_launch_bytes = bytes_per_step / launches_per_step
+    mean_launch_bytes = bytes_per_pass / launches_per_pass
     roofline = {
         "bound": "hbm", "achieved": round(per_gpu, 1), "peak": peak, "unit": "GB/s",
         "frac": round(per_gpu / peak, 4), "peak_source": f"of {peak_kind}",
         "kernel": "gemv_mma_kernel<Q6_K>, m in {1,4,8}",
         "traffic": None if ratio is None else round(ratio * mean_launch_bytes),
+        "traffic_source": "dram bytes / algorithmic bytes of the committed ncu capture (profiles/gemv_q6k_traffic.json) x this run's mean launch",
         "algorithmic_bytes_per_launch_mean": round(mean_launch_bytes),
         "frac_of_nominal_8TBps": round(per_gpu / 8000.0, 4),
         "breakdown": breakdown,
@@ -610,10 +807,9 @@ def main() -> None:
 
     cpu_baseline = None
     if world == 1 and not args.no_cpu_baseline:
-        threads = oracle.max_threads()
+        threads = host_threads()
         cpu_reference_pass(raws, xvals, threads)           # warm
         t, b = cpu_reference_pass(raws, xvals, threads)
-        t1, b1 = 0.0, 0
         n, k = SHAPES[1]
         _, td, tm = oracle.qmatmul(Q6_K, raws[1], xvals[(k, 1)], n, k, threads=1)
         cpu_baseline = {
@@ -623,33 +819,48 @@ def main() -> None:
             "single_thread_4096x4096_m1_GBps": round(algo_bytes(n, k, 1, row_b[k]) / (td + tm) / 1e9, 3),
         }
 
+    secondary = None
+    if world == 1 and not args.no_secondary:
+        del weights, graph
+        torch.cuda.empty_cache()
+        secondary = {"config1_q4k_f32": bench_config1(hq, oracle, torch, ctx, dev, args),
+                     "config3_prefill_gemm": bench_gemm(hq, oracle, torch, ctx, dev, args),
+                     "config4_moe_layer": bench_moe(hq, oracle, torch, ctx, dev, args)}
+
     line = {
         "metric": METRIC, "value": round(value, 1), "unit": UNIT, "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": round(ms_per_step, 4), "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {
-            "workload": "Q6_K decode GEMV sweep: shapes 6144x4096, 4096x4096, 28672x4096, 4096x14336; "
-                        "m in {1,4,8}; bf16 activations; fp32 accumulate",
+            "workload": WORKLOAD,
             "weights": "N(0, sigma=0.02), f16 round trip, Q6_K via the oracle's port of hf2q's quantizer",
             "l2_policy": f"inputs larger than L2: {args.copies} distinct copies of the 4 matrices "
                          f"({working_set / 2**30:.2f} GiB) rotated so no launch re-reads cached weights",
-            "launches_per_step": launches_per_step, "bytes_per_step": bytes_per_step,
-            "launch_mode": "CUDA graph replay of one captured step" if graph is not None else "eager launches",
+            "step": f"{args.passes} passes over {args.copies} copies x 4 shapes x 3 token counts",
+            "launches_per_step": per_step_launches, "bytes_per_step": bytes_per_step,
+            "launch_mode": "CUDA graph replay of one captured step" if graph_used else "eager launches",
             "parallelism": "single GPU" if world == 1 else
                            (f"row-sharded x{world}, each rank's shard = the listed shapes; the all-gather of every output is "
-                            "in the kernel's epilogue (stores to the peers' buffers over NVLink + arrival counters), each "
-                            "product waits for the previous one's columns from all ranks") if gather is not None else
+                            "in the kernel's epilogue (stores to the peers' buffers over NVLink + per-source arrival counters, two "
+                            "alternating output buffers), each product waits for the previous one's columns from all ranks") if gather is not None else
                            f"row-sharded x{world}, each rank's shard = the listed shapes; NCCL all-gather after every product",
+            "parity_before_timing": verify,
         },
         "gpu_launches": int(gpu_launches),
-        "e2e": {"value": round(e2e_val, 1), "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                "steps": e2e_steps, "api": "hf2q_cuda_qmatmul_host_async per product (pinned host x -> device, kernel, y -> pinned host), hf2q_cuda_host_sync once per step"},
+        "e2e": {"value": round(e2e_val, 1), "unit": UNIT, "h2d_bytes_per_step": h2d * args.passes, "d2h_bytes_per_step": d2h * args.passes,
+                "passes_timed": e2e_passes, "api": e2e_api},
         "roofline": roofline,
         "clocks": clocks,
     }
+    if strong is not None:
+        line["strong"] = strong
     if cpu_baseline is not None:
         line["cpu_baseline"] = cpu_baseline
+    if secondary is not None:
+        line["secondary"] = secondary
     print(json.dumps(line))
+    if gather is not None:
+        gather.close()
     if world > 1:
         dist.destroy_process_group()
 

@@ -34,6 +34,7 @@ SIGNATURES = {
     "hf2q_cuda_dequantize": (i32, [vp, vp, vp, u32, u64, u64, vp, u32]),
     "hf2q_cuda_qmatmul": (i32, [vp, vp, vp, u32, vp, vp, u32, u32, u32, u32, vp, u64]),
     "hf2q_cuda_qmatmul_workspace_bytes": (i32, [u32, u32, u32, u32, u32, C.POINTER(u64)]),
+    "hf2q_cuda_qmatmul_segments": (i32, [vp, vp, vp, u32, vp, u32, vp, u32, u32, vp, u64]),
     "hf2q_cuda_qmatmul_static": (i32, [vp, vp, vp, u32, vp, vp, u32, u32, u32, u32]),
     "hf2q_cuda_qmatmul_static_max_elements": (u64, []),
     "hf2q_cuda_qmatmul_id_swiglu_supported": (i32, [vp, u32, u32, u32, u32, u32, u32]),

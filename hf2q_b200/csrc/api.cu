@@ -317,6 +317,72 @@ HF2Q_API int32_t hf2q_cuda_qmatmul(hf2q_ctx* ctx, void* stream, const void* x, u
     return run_matvec(ctx, st, a, m, "qmatmul launch");
 }
 
+// A matrix whose row ranges use different block formats (the fused QKV tensor of a Q4_K_M model:
+// Q and K rows Q4_K, V rows Q6_K): one call, one conversion of the activations, one launch per range,
+// every range writing its own columns of the one output.
+HF2Q_API int32_t hf2q_cuda_qmatmul_segments(hf2q_ctx* ctx, void* stream, const void* x, uint32_t x_dtype,
+                                            const hf2q_row_segment* segs, uint32_t n_segs, float* y, uint32_t m, uint32_t k,
+                                            void* workspace, uint64_t workspace_bytes) {
+    if (!ctx) return HF2Q_ERR_INVALID_ARGUMENT;
+    if (!x || !segs || !y || n_segs == 0 || n_segs > 16) return fail(ctx, HF2Q_ERR_INVALID_ARGUMENT, "qmatmul_segments: null pointer or n_segs=%u not in 1..16", n_segs);
+    if (x_dtype != HF2Q_DT_F32 && x_dtype != HF2Q_DT_BF16) return fail(ctx, HF2Q_ERR_INVALID_ARGUMENT, "qmatmul_segments: x_dtype %u (want F32 or BF16)", x_dtype);
+    uint64_t n = 0;
+    for (uint32_t i = 0; i < n_segs; ++i) {
+        if (!segs[i].w) return fail(ctx, HF2Q_ERR_INVALID_ARGUMENT, "qmatmul_segments: segment %u has no weights", i);
+        const int32_t rc = check_matmul_shape(ctx, segs[i].ggml_type, segs[i].rows, k, "qmatmul_segments");
+        if (rc) return rc;
+        n += segs[i].rows;
+    }
+    if (n > 0xffffffffull) return fail(ctx, HF2Q_ERR_INVALID_ARGUMENT, "qmatmul_segments: %llu rows", (unsigned long long)n);
+    if (m == 0) return HF2Q_OK;
+    if (reinterpret_cast<uintptr_t>(x) % dtype_size(x_dtype) || reinterpret_cast<uintptr_t>(y) % 4)
+        return fail(ctx, HF2Q_ERR_INVALID_ARGUMENT, "qmatmul_segments: misaligned buffer");
+    DeviceGuard dg(ctx->device);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const bool gemm = m > 8 && !ctx->fp32_matvec;
+    if (gemm) {
+        const uint64_t need = gemm_tc_workspace_bytes(m, k);
+        if (!workspace || workspace_bytes < need)
+            return fail(ctx, HF2Q_ERR_WORKSPACE, "qmatmul_segments: m=%u needs a workspace of %llu bytes (got %llu)", m,
+                        (unsigned long long)need, (unsigned long long)workspace_bytes);
+        if (reinterpret_cast<uintptr_t>(workspace) % 256) return fail(ctx, HF2Q_ERR_INVALID_ARGUMENT, "qmatmul_segments: workspace must be 256-byte aligned");
+    }
+    // every range must fit the kernel the row count selects: a detour for one range would need a second output layout
+    for (uint32_t i = 0; i < n_segs; ++i) {
+        GemvArgs a{};
+        a.w = segs[i].w; a.x = x; a.x_dtype = x_dtype; a.type = segs[i].ggml_type; a.n = segs[i].rows; a.k = k;
+        const bool ok = gemm ? gemm_tc_supported(segs[i].ggml_type, segs[i].w, segs[i].rows, k)
+                             : (!ctx->fp32_matvec && gemv_mma_supported(a) && gemv_mma_max_rows(segs[i].ggml_type, k, x_dtype, ctx->dev) >= m);
+        if (!ok) return fail(ctx, HF2Q_ERR_INVALID_ARGUMENT, "qmatmul_segments: segment %u (type %u, k=%u, m=%u) needs 16-byte aligned weight rows and k %% 256 == 0", i,
+                             segs[i].ggml_type, k, m);
+    }
+    uint32_t col0 = 0;
+    for (uint32_t i = 0; i < n_segs; ++i) {
+        cudaError_t e;
+        int nl = 1;
+        if (gemm) {
+            e = launch_gemm_tc(segs[i].ggml_type, segs[i].w, x, x_dtype, y + col0, m, segs[i].rows, k, workspace, ctx->status, ctx->dev.sm_count, st, &nl,
+                               static_cast<uint32_t>(n), i != 0);
+        } else {
+            GemvArgs a{};
+            a.w = segs[i].w; a.x = x; a.y = y;
+            a.x_dtype = x_dtype; a.type = segs[i].ggml_type;
+            a.m = m; a.n = segs[i].rows; a.k = k;
+            a.slots = 1; a.top_k = 1; a.n_experts = 0;
+            a.status = ctx->status;
+            GatherArgs ga{};             // the one-rank form of the gathering store: columns [col0, col0 + rows) of a wider y
+            ga.y_all[0] = y; ga.n_ranks = 1; ga.rank = 0; ga.n_total = static_cast<uint32_t>(n); ga.col0 = col0;
+            ga.wait_limit = ctx->wait_limit;
+            a.gather = &ga;
+            e = launch_gemv_mma(a, ctx->dev, st);
+        }
+        if (e != cudaSuccess) return cuda_fail(ctx, e, "qmatmul_segments launch");
+        ctx->launches += nl;
+        col0 += segs[i].rows;
+    }
+    return HF2Q_OK;
+}
+
 // ---- dense FFN fusions: SwiGLU in the gate/up launch, residual add in the down launch ----
 // (the reference's dense builder issues gate, up, dispatch_silu_mul, down and an optional
 // elementwise_add of the residual: src/inference/models/qwen35/gpu_ffn.rs:896-960)
@@ -435,16 +501,15 @@ HF2Q_API int32_t hf2q_cuda_qmatmul_gather(hf2q_ctx* ctx, void* stream, const voi
         if (!g->y_all[r] || !g->flags[r] || reinterpret_cast<uintptr_t>(g->y_all[r]) % 4 || reinterpret_cast<uintptr_t>(g->flags[r]) % 4)
             return fail(ctx, HF2Q_ERR_INVALID_ARGUMENT, "qmatmul_gather: buffer of rank %u missing or misaligned", r);
     {
-        // the shards must tile the output: every rank derives the others' arrival counts from n_rows[]
-        uint64_t sum = 0, before = 0;
+        // every rank derives the others' arrival counts from n_rows[]: they must describe real shards
+        uint64_t sum = 0;
         for (uint32_t r = 0; r < g->n_ranks; ++r) {
             if (g->n_rows[r] == 0) return fail(ctx, HF2Q_ERR_INVALID_ARGUMENT, "qmatmul_gather: n_rows[%u] is zero", r);
-            if (r < g->rank) before += g->n_rows[r];
             sum += g->n_rows[r];
         }
-        if (g->n_rows[g->rank] != n || sum > g->n_total || before != g->col0)
-            return fail(ctx, HF2Q_ERR_INVALID_ARGUMENT, "qmatmul_gather: n_rows[] (sum %llu, %llu before rank %u) does not match n=%u, col0=%u, n_total=%u",
-                        (unsigned long long)sum, (unsigned long long)before, g->rank, n, g->col0, g->n_total);
+        if (g->n_rows[g->rank] != n || sum > g->n_total)
+            return fail(ctx, HF2Q_ERR_INVALID_ARGUMENT, "qmatmul_gather: n_rows[] (sum %llu, own %u) does not match n=%u, n_total=%u",
+                        (unsigned long long)sum, g->n_rows[g->rank], n, g->n_total);
     }
     if (m == 0) return HF2Q_OK;
     DeviceGuard dg(ctx->device);

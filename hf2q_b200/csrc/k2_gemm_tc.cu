@@ -68,6 +68,7 @@ struct GroupTile { uint32_t expert, start, count, pad; };
 struct GParams {
     float* y;
     uint32_t m, n, k;
+    uint32_t ldy;           // floats between consecutive activation rows of y (n, or the full width when y is a column block)
     // grouped mode (mul_mat_id): tile table, its length, and the routed-row index of every sorted row
     const GroupTile* tiles;
     const uint32_t* n_tiles;
@@ -261,7 +262,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
                         const uint32_t tok = tok0 + c0 + j;
                         if (tok < tok_end) {
                             const uint32_t dst = GROUPED ? p.perm[tok] : tok;      // scatter back to routed-row order
-                            p.y[static_cast<size_t>(dst) * p.n + row] = __uint_as_float(v[j]);
+                            p.y[static_cast<size_t>(dst) * p.ldy + row] = __uint_as_float(v[j]);
                         }
                     }
                 }
@@ -367,7 +368,8 @@ uint32_t gemm_tc_token_tile(uint32_t m, uint32_t tiles_n, int sms) {
 }
 
 cudaError_t launch_gemm_tc(uint32_t type, const void* w, const void* x, uint32_t x_dtype, float* y, uint32_t m, uint32_t n,
-                           uint32_t k, void* workspace, uint32_t* status, int sm_count, cudaStream_t st, int* launches) {
+                           uint32_t k, void* workspace, uint32_t* status, int sm_count, cudaStream_t st, int* launches,
+                           uint32_t ldy, bool x_ready) {
     const BlockGeom g = block_geom(type);
     const uint64_t row_bytes = static_cast<uint64_t>(k) / g.elems * g.bytes;
     EncodeTiledFn enc = encode_fn();
@@ -376,7 +378,7 @@ cudaError_t launch_gemm_tc(uint32_t type, const void* w, const void* x, uint32_t
     // 1. activations -> f16 [m][k] in the workspace
     __half* xh = static_cast<__half*>(workspace);
     const uint64_t nx = static_cast<uint64_t>(m) * k;
-    {
+    if (!x_ready) {       // (a caller that runs several products on the same activations converts them once)
         uint64_t want = (nx + 255) / 256;
         const uint64_t cap = static_cast<uint64_t>(sm_count) * 16;
         x_to_f16_kernel<<<static_cast<unsigned>(want < cap ? want : cap), 256, 0, st>>>(x, x_dtype == HF2Q_DT_BF16, xh, nx, status);
@@ -386,6 +388,7 @@ cudaError_t launch_gemm_tc(uint32_t type, const void* w, const void* x, uint32_t
     // 2. tensor maps
     GParams p{};
     p.y = y; p.m = m; p.n = n; p.k = k;
+    p.ldy = ldy ? ldy : n;
     p.tiles_per_cta = 1;
     p.boxw = boxw_of(type);
     p.blk_bytes = KB / g.elems * g.bytes;
@@ -413,7 +416,7 @@ cudaError_t launch_gemm_tc(uint32_t type, const void* w, const void* x, uint32_t
                          CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
         if (r != CUDA_SUCCESS) return cudaErrorInvalidValue;
     }
-    if (launches) *launches = 2;
+    if (launches) *launches = x_ready ? 1 : 2;
     switch (type) {
         case HF2Q_TYPE_Q4_0: return launch_gemm_nt<HF2Q_TYPE_Q4_0>(tw, tx, p, nt, st);
         case HF2Q_TYPE_Q8_0: return launch_gemm_nt<HF2Q_TYPE_Q8_0>(tw, tx, p, nt, st);
@@ -451,6 +454,7 @@ cudaError_t launch_gemm_tc_grouped(uint32_t type, const void* w_stacked, uint64_
     uint8_t* base = static_cast<uint8_t*>(scratch);
     GParams p{};
     p.y = y; p.m = rows; p.n = n; p.k = k;
+    p.ldy = n;
     {
         // One CTA walks several weight-row tiles of its (expert, token tile): barriers, tensor memory and the
         // first copies' latency are paid once.  Keep about two CTAs per resident slot (2 per SM) in the grid.

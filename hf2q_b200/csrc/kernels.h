@@ -91,8 +91,10 @@ cudaError_t launch_gather_wait(const uint32_t* flag, uint32_t n_ranks, uint32_t 
 // rows and a workspace of gemm_tc_workspace_bytes(m, k) for the f16 copy of the activations.
 bool gemm_tc_supported(uint32_t type, const void* w, uint32_t n, uint32_t k);
 uint64_t gemm_tc_workspace_bytes(uint32_t m, uint32_t k);
+// ldy: floats between activation rows of y (0 = n); x_ready: the workspace already holds the f16 copy of x
 cudaError_t launch_gemm_tc(uint32_t type, const void* w, const void* x, uint32_t x_dtype, float* y, uint32_t m, uint32_t n,
-                           uint32_t k, void* workspace, uint32_t* status, int sm_count, cudaStream_t st, int* launches);
+                           uint32_t k, void* workspace, uint32_t* status, int sm_count, cudaStream_t st, int* launches,
+                           uint32_t ldy = 0, bool x_ready = false);
 
 // K4: grouped expert-routed product.  moe_scratch_layout() carves the caller's scratch into header
 // (tile count, sorted-row count), tile table, permutation and the f16 activation panel;

@@ -228,6 +228,37 @@ def quantized_matmul_ggml(ctx: GpuContext, input: torch.Tensor, weight: QuantWei
                                           int(params.ggml_type), ws_ptr, ws_bytes))
 
 
+class _RowSegment(C.Structure):                  # hf2q_row_segment in include/hf2q_cuda.h
+    _fields_ = [("w", C.c_void_p), ("rows", C.c_uint32), ("ggml_type", C.c_uint32)]
+
+
+def quantized_matmul_segments(ctx: GpuContext, input: torch.Tensor, weights, out: torch.Tensor, m: int,
+                              workspace: torch.Tensor | None = None) -> None:
+    """out[m, n] = input[m, k] . W^T for a matrix W whose row ranges are separate QuantWeights of possibly
+    different block formats (fused QKV of a Q4_K_M model: Q/K rows Q4_K, V rows Q6_K,
+    standard_policy.rs:563-567); n = sum of the ranges' rows, ranges in row order."""
+    xdt = _act(input, "input")
+    k = weights[0].cols
+    n = sum(w.rows for w in weights)
+    if any(w.cols != k for w in weights):
+        raise Hf2qError(_lib.ERR_INVALID_ARGUMENT, "all row ranges must share k")
+    if out.dtype != torch.float32 or not out.is_cuda or not out.is_contiguous() or out.numel() < m * n or input.numel() < m * k:
+        raise Hf2qError(_lib.ERR_INVALID_ARGUMENT, "out must be a contiguous float32 CUDA tensor of [m, n]; input [m, k]")
+    segs = (_RowSegment * len(weights))()
+    for s, w in zip(segs, weights):
+        s.w, s.rows, s.ggml_type = w.ptr, w.rows, w.ggml_type
+    if workspace is None and m > 8:
+        need = quantized_matmul_workspace_bytes(GgmlQuantizedMatmulParams(m, n, k, weights[0].ggml_type), input.dtype)
+        ws = getattr(ctx, "_ws", None)
+        if ws is None or ws.numel() < need:
+            ws = torch.empty(need, dtype=torch.uint8, device=input.device)
+            ctx._ws = ws
+        workspace = ws
+    ws_ptr, ws_bytes = (workspace.data_ptr(), workspace.numel() * workspace.element_size()) if workspace is not None else (None, 0)
+    ctx._check(ctx._lib.hf2q_cuda_qmatmul_segments(ctx._h, ctx._stream(), input.data_ptr(), xdt, segs, len(weights), out.data_ptr(),
+                                                  m, k, ws_ptr, ws_bytes))
+
+
 def quantized_matmul_swiglu_supported(ctx: GpuContext, m: int, weight: QuantWeight, x_dtype=torch.bfloat16) -> bool:
     """Whether gate and up products of shape `weight` with m activation rows fit the one fused launch."""
     xdt = DT_BF16 if x_dtype == torch.bfloat16 else DT_F32

@@ -240,6 +240,23 @@ HF2Q_API int32_t hf2q_cuda_moe_softmax_topk(hf2q_ctx* ctx, void* stream, const f
                                             uint32_t* ids, float* weights, uint32_t n_tokens,
                                             uint32_t n_experts, uint32_t top_k);
 
+/* One weight matrix whose ROW RANGES use different block formats -- the Q4_K_M mix keeps the V rows
+ * of a fused QKV tensor in Q6_K while the Q and K rows are Q4_K (use_more_bits / attn_v rule,
+ * src/quantize/ggml_quants/standard_policy.rs:563-567; per-tensor types in the unfused layout,
+ * :646-658).  The reference issues one quantized_matmul_ggml per tensor (gpu_full_attn.rs:848-855,
+ * 941-950); here the ranges are given as segments in row order, each with its own raw-block buffer,
+ * and the call computes y[m][n] with n = sum of the segments' rows: the activations are converted
+ * once and every range writes its own columns of y.  Every segment must fit the kernel that m
+ * selects (16-byte aligned weight rows, k % 256 == 0); workspace as for hf2q_cuda_qmatmul. */
+typedef struct hf2q_row_segment {
+    const void* w;           /* raw blocks of this range's rows, [rows][k / block * block_bytes] */
+    uint32_t rows;
+    uint32_t ggml_type;
+} hf2q_row_segment;
+HF2Q_API int32_t hf2q_cuda_qmatmul_segments(hf2q_ctx* ctx, void* stream, const void* x, uint32_t x_dtype,
+                                            const hf2q_row_segment* segs, uint32_t n_segs, float* y,
+                                            uint32_t m, uint32_t k, void* workspace, uint64_t workspace_bytes);
+
 /* ---- e: row-sharded mat-vec with the all-gather in its epilogue ------------------------------- *
  * The reference runs on one device and has no collective; this is the multi-GPU form of
  * quantized_matmul_ggml for weights sharded by output rows (one process per GPU).  Every rank owns
@@ -274,7 +291,7 @@ typedef struct hf2q_gather {
     uint32_t n_ranks, rank;
     uint32_t n_total, col0;
     uint32_t wait_previous;  /* != 0: wait for all ranks' earlier products before reading x */
-    uint32_t n_rows[8];      /* rows of rank r's shard of this product (n_rows[rank] == n, col0 == sum of the earlier ranks') */
+    uint32_t n_rows[8];      /* rows of rank r's shard of this product (n_rows[rank] == n; the sum must fit n_total) */
 } hf2q_gather;
 HF2Q_API int32_t hf2q_cuda_ipc_alloc(hf2q_ctx* ctx, uint64_t bytes, void** dev, uint8_t* handle64);
 HF2Q_API int32_t hf2q_cuda_ipc_open(hf2q_ctx* ctx, const uint8_t* handle64, void** dev);

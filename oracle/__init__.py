@@ -77,6 +77,8 @@ def lib() -> C.CDLL:
         L.oracle_mulberry32_imatrix.argtypes = [vp, i64, u32]
         L.oracle_mulberry32_imatrix.restype = None
         L.oracle_max_threads.restype = ci
+        L.oracle_set_threads.argtypes = [ci]
+        L.oracle_set_threads.restype = None
         _lib = L
     return _lib
 
@@ -91,6 +93,11 @@ def _f32(a) -> np.ndarray:
 
 def max_threads() -> int:
     return int(lib().oracle_max_threads())
+
+
+def set_threads(n: int) -> None:
+    """Default thread count of the OpenMP loops from here on (overrides an inherited OMP_NUM_THREADS)."""
+    lib().oracle_set_threads(int(n))
 
 
 def block_geometry(t: int) -> tuple[int, int]:

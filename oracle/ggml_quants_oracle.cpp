@@ -912,6 +912,15 @@ void oracle_mulberry32_imatrix(float* out, int64_t n, uint32_t seed) {
     }
 }
 
+// Overrides an inherited OMP_NUM_THREADS (launchers such as torchrun export OMP_NUM_THREADS=1).
+void oracle_set_threads(int n) {
+#ifdef _OPENMP
+    if (n > 0) omp_set_num_threads(n);
+#else
+    (void)n;
+#endif
+}
+
 int oracle_max_threads(void) {
 #ifdef _OPENMP
     return omp_get_max_threads();

@@ -410,11 +410,12 @@ def test_gather_entry_single_rank(gpu_ctx):
         g = _Gather()
         g.y_all[0], g.flags[0] = ybuf.value, fbuf.value
         g.n_ranks, g.rank, g.n_total, g.col0, g.wait_previous = 1, 0, n_total, col0, 1
+        g.n_rows[0] = n
         xd, xs = _dev_x(make_x(m, k, seed=3), True)
         for _ in range(2):        # the second call waits (trivially) for the first
             gpu_ctx._check(lib.hf2q_cuda_qmatmul_gather(h, gpu_ctx._stream(), xd.data_ptr(), hq.ops.DT_BF16, w.ptr, C.byref(g),
                                                         m, n, k, t))
-        gpu_ctx._check(lib.hf2q_cuda_gather_wait(h, gpu_ctx._stream(), fbuf.value))
+        gpu_ctx._check(lib.hf2q_cuda_gather_wait(h, gpu_ctx._stream(), C.byref(g)))
         gpu_ctx.check_status()
         from hf2q_b200.dist import _DevView
         y = torch.as_tensor(_DevView(ybuf.value, (m, n_total), "<f4"), device="cuda").cpu().numpy()
@@ -425,3 +426,46 @@ def test_gather_entry_single_rank(gpu_ctx):
     # argument checks
     g = _Gather()
     assert lib.hf2q_cuda_qmatmul_gather(h, None, xd.data_ptr(), hq.ops.DT_BF16, w.ptr, C.byref(g), 1, n, k, t) == _lib.ERR_INVALID_ARGUMENT
+
+
+@pytest.mark.parametrize("t", TYPES)
+def test_device_dequant_of_golden_blocks_reencodes_to_the_stored_codes(gpu_ctx, golden_dir, t):
+    """The reference's quantizers recompute the codes from (x + dmin*m) / (d*sc) with the stored
+    scales; the DEVICE dequantiser's values of the reference's golden blocks must give every
+    stored code back through that step."""
+    from tests.util import reencode_codes, stored_codes
+    name, n = FIXTURES[t]
+    for variant in ("noim", "im"):
+        raw = np.fromfile(golden_dir / f"{name}_{n}_{variant}_expected.bin", dtype=np.uint8)
+        w = hq.load_quant_weight(gpu_ctx, raw, t, 2, n)
+        y = hq.dequantize(gpu_ctx, w).cpu().numpy().reshape(-1)
+        codes, valid = reencode_codes(t, raw, y)
+        assert np.array_equal(codes[valid], stored_codes(t, raw)[valid])
+
+
+@pytest.mark.parametrize("m", [1, 6, 72, 300])
+def test_row_range_type_map(gpu_ctx, m):
+    """hf2q_cuda_qmatmul_segments: a fused-QKV-like matrix whose last rows are Q6_K and the rest Q4_K
+    (plus a Q5_K middle range), one call, against the f64 product on the oracle's weights."""
+    k = 2048
+    segs = [(oracle.Q4_K, 320), (oracle.Q5_K, 48), (oracle.Q6_K, 136)]
+    raws = [make_quant_weight(t, rows, k, seed=900 + i) for i, (t, rows) in enumerate(segs)]
+    ws = [hq.load_quant_weight(gpu_ctx, raw, t, rows, k) for raw, (t, rows) in zip(raws, segs)]
+    n = sum(rows for _, rows in segs)
+    xd, xs = _dev_x(make_x(m, k, seed=m), True)
+    y = torch.full((m, n), float("nan"), device="cuda")
+    hq.ops.quantized_matmul_segments(gpu_ctx, xd, ws, y, m)
+    gpu_ctx.check_status()
+    want = np.concatenate([_ref(t, raw, xs, rows, k) for raw, (t, rows) in zip(raws, segs)], axis=1)
+    assert rel_l2(y.cpu().numpy(), want) < GATE
+    # the same ranges through separate calls give the same bits
+    c0 = 0
+    for w, (t, rows) in zip(ws, segs):
+        yi = torch.empty((m, rows), device="cuda")
+        hq.quantized_matmul_ggml(gpu_ctx, xd, w, yi, w.matmul_params(m))
+        assert torch.equal(yi, y[:, c0:c0 + rows])
+        c0 += rows
+    # a range the selected kernel cannot take is an error, not a detour
+    bad = hq.load_quant_weight(gpu_ctx, make_quant_weight(oracle.Q4_0, 16, 96, seed=1), oracle.Q4_0, 16, 96)
+    with pytest.raises(hq.Hf2qError):
+        hq.ops.quantized_matmul_segments(gpu_ctx, torch.zeros((2, 96), device="cuda"), [bad], torch.empty((2, 16), device="cuda"), 2)

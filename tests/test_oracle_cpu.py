@@ -8,7 +8,7 @@ import pytest
 
 import oracle
 from oracle import np_dequant
-from tests.util import FIXTURES, make_weight_f32, random_finite_blocks
+from tests.util import FIXTURES, make_weight_f32, random_finite_blocks, reencode_codes, stored_codes
 
 GOLDEN = Path(__file__).resolve().parent / "golden"
 # per-format reconstruction bounds of dequant(expected) vs input on the fixtures (abs, rel-L2)
@@ -69,6 +69,51 @@ def test_two_dequant_restatements_agree_bitwise(t):
     w = oracle.quantize(t, make_weight_f32(16, 1024, seed=3), 1024)
     a, b = oracle.dequantize(t, w), np_dequant.dequantize(t, w)
     assert np.array_equal(a.view(np.uint32), b.view(np.uint32))
+
+
+@pytest.mark.parametrize("t", oracle.ALL_TYPES)
+@pytest.mark.parametrize("variant", ["noim", "im"])
+def test_reencoding_dequantized_golden_blocks_returns_the_stored_codes_exactly(t, variant):
+    """The pin the reference's algebra gives for dequantised VALUES: its quantizers recompute the
+    codes as nearest_int((x + dmin*m) / (d*sc)) (and the per-format equivalents) from the stored
+    scales, so feeding the oracle's dequantised values of the reference's own golden blocks back
+    through that step must reproduce every stored code, bit for bit."""
+    _, expected, _ = _load(t, variant)
+    for deq in (oracle.dequantize, np_dequant.dequantize):
+        codes, valid = reencode_codes(t, expected, deq(t, expected))
+        want = stored_codes(t, expected)
+        assert valid.any()
+        assert np.array_equal(codes[valid], want[valid])
+
+
+@pytest.mark.parametrize("t", oracle.ALL_TYPES)
+def test_reencode_identity_on_synthetic_weights(t):
+    raw = oracle.quantize(t, make_weight_f32(32, 2048, seed=17), 2048)
+    codes, valid = reencode_codes(t, raw, oracle.dequantize(t, raw))
+    assert np.array_equal(codes[valid], stored_codes(t, raw)[valid])
+    # and a wrong dequantiser would be caught: shifting every value by one step moves every code
+    y = oracle.dequantize(t, raw)
+    step = np.abs(y).max() / 31
+    bad, _ = reencode_codes(t, raw, y + np.float32(step))
+    assert not np.array_equal(bad[valid], stored_codes(t, raw)[valid])
+
+
+def test_topk_order_is_total_with_nan_and_ties():
+    """Ties keep the lower index first; a NaN probability ranks below every number (the
+    reference's partial_cmp().unwrap_or(Equal) leaves that case open, gpu_ffn.rs:1903-1908)."""
+    logits = np.array([[0.5, np.nan, 0.5, 2.0, np.nan, -1.0]], np.float32)
+    ids, w = oracle.softmax_topk_renorm(logits, 5)
+    assert ids.tolist() == [3, 0, 2, 5, 1]
+    # the softmax denominator and the selected sum are NaN, so both guards take their fall-back
+    # (1.0 and 1/topk, gpu_ffn.rs:1896, 1913-1917): weights = exp(x - max) / topk, NaN stays NaN
+    ev = np.exp(logits[0, [3, 0, 2, 5]] - np.float32(2.0)).astype(np.float32)
+    assert np.allclose(w[:4], ev / 5, rtol=1e-6) and np.isnan(w[4])
+    masked = np.array([[-np.inf, 1.0, -np.inf, 1.0]], np.float32)
+    ids, w = oracle.softmax_topk_renorm(masked, 3)
+    assert ids.tolist() == [1, 3, 0] and w[2] == 0.0 and abs(w[0] - 0.5) < 1e-6
+    allmasked = np.full((1, 4), -np.inf, np.float32)
+    ids, _ = oracle.softmax_topk_renorm(allmasked, 2)
+    assert ids.tolist() == [0, 1]                # all probabilities NaN: index order
 
 
 @pytest.mark.parametrize("t", oracle.ALL_TYPES)

@@ -70,3 +70,49 @@ def test_static_scratch_entry_refuses_what_does_not_fit(gpu_ctx):
     y2 = torch.empty((4, 16), device="cuda")
     rc = lib.hf2q_cuda_qmatmul_static(gpu_ctx._h, None, x2.data_ptr(), hq.ops.DT_BF16, w2.ptr, y2.data_ptr(), 4, 16, k2, oracle.Q4_0)
     assert rc == _lib.ERR_INVALID_ARGUMENT
+
+
+def _static_call_leaves_free_memory_alone(ctx, device):
+    """What the entry point is for: between two calls the device's free memory must not move (no
+    cudaMalloc / cudaFree behind the caller's back, torch's caching allocator not involved either)."""
+    lib = _lib.load()
+    t, n, k, m = oracle.Q6_K, 256, 2048, 64
+    raw = make_quant_weight(t, n, k, seed=31)
+    with torch.cuda.device(device):
+        w = hq.load_quant_weight(ctx, raw, t, n, k)
+        bits = to_bf16_bits(make_x(m, k, seed=32))
+        x = torch.from_numpy(bits.view(np.int16).copy()).to(f"cuda:{device}").view(torch.bfloat16)
+        y = torch.empty((m, n), device=f"cuda:{device}")
+        stream = torch.cuda.current_stream(device).cuda_stream
+
+        def call():
+            rc = lib.hf2q_cuda_qmatmul_static(ctx._h, stream, x.data_ptr(), hq.ops.DT_BF16, w.ptr, y.data_ptr(), m, n, k, t)
+            assert rc == 0, lib.hf2q_cuda_last_error(ctx._h)
+
+        call()                                        # first call on this device: resolves the array's address
+        torch.cuda.synchronize(device)
+        free0, _ = torch.cuda.mem_get_info(device)
+        reserved0 = torch.cuda.memory_reserved(device)
+        for _ in range(3):
+            call()
+        torch.cuda.synchronize(device)
+        free1, _ = torch.cuda.mem_get_info(device)
+        assert free1 == free0 and torch.cuda.memory_reserved(device) == reserved0
+        ctx.check_status()
+        want = oracle.matmul_f64(x.float().cpu().numpy(), oracle.dequantize(t, raw).reshape(n, k))
+        assert rel_l2(y.cpu().numpy(), want) < 1e-3
+
+
+def test_static_scratch_entry_allocates_nothing(gpu_ctx):
+    _static_call_leaves_free_memory_alone(gpu_ctx, 0)
+
+
+def test_static_scratch_entry_on_a_second_device():
+    """The array's address is resolved per device: a context on GPU 1 must get GPU 1's copy."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    ctx = hq.GpuContext(1)
+    try:
+        _static_call_leaves_free_memory_alone(ctx, 1)
+    finally:
+        ctx.close()

@@ -58,3 +58,87 @@ def random_finite_blocks(t: int, nblocks: int, seed: int) -> np.ndarray:
         bad = (hi & 0x7C) == 0x7C
         raw[bad, o + 1] = hi[bad] & 0xBF       # clear one exponent bit -> finite
     return raw.reshape(-1)
+
+
+def _f16_field(raw2: np.ndarray) -> np.ndarray:
+    return np.ascontiguousarray(raw2).view("<f2").astype(np.float32).reshape(-1)
+
+
+def stored_codes(t: int, raw: np.ndarray) -> np.ndarray:
+    """The integer codes L a block stores, per element in natural order, straight from the packing
+    loops of hf2q's quantizers (q4_0.rs:60-64, q8_0.rs:66, q4_k.rs:204-215, q5_k.rs:137-158,
+    q6_k.rs:120-143).  Shape [blocks, block elements], int32."""
+    be, bb = oracle.block_geometry(t)
+    b = np.ascontiguousarray(raw, dtype=np.uint8).reshape(-1, bb)
+    nb = b.shape[0]
+    if t == oracle.Q4_0:
+        qs = b[:, 2:18]
+        return np.concatenate([qs & 15, qs >> 4], axis=1).astype(np.int32)
+    if t == oracle.Q8_0:
+        return b[:, 2:34].view(np.int8).astype(np.int32)
+    if t in (oracle.Q4_K, oracle.Q5_K):
+        qs = (b[:, 16:144] if t == oracle.Q4_K else b[:, 48:176]).reshape(nb, 4, 32)
+        lo, hi = (qs & 15).astype(np.int32), (qs >> 4).astype(np.int32)
+        if t == oracle.Q5_K:
+            qh = b[:, 16:48].astype(np.int32)
+            for c in range(4):
+                lo[:, c, :] += 16 * ((qh >> (2 * c)) & 1)
+                hi[:, c, :] += 16 * ((qh >> (2 * c + 1)) & 1)
+        return np.stack([lo, hi], axis=2).reshape(nb, 256)
+    ql, qh = b[:, 0:128].astype(np.int32), b[:, 128:192].astype(np.int32)
+    out = np.empty((nb, 256), np.int32)
+    for n in range(2):
+        for l in range(32):
+            h = qh[:, 32 * n + l]
+            out[:, 128 * n + l] = (ql[:, 64 * n + l] & 15) | ((h & 3) << 4)
+            out[:, 128 * n + l + 32] = (ql[:, 64 * n + l + 32] & 15) | (((h >> 2) & 3) << 4)
+            out[:, 128 * n + l + 64] = (ql[:, 64 * n + l] >> 4) | (((h >> 4) & 3) << 4)
+            out[:, 128 * n + l + 96] = (ql[:, 64 * n + l + 32] >> 4) | (((h >> 6) & 3) << 4)
+    return out
+
+
+def reencode_codes(t: int, raw: np.ndarray, y: np.ndarray):
+    """Recomputes the integer codes from dequantised values ``y`` with the STORED f16 scales and
+    packed sub-block scales, by the formulas of the quantizers' second pass (q4_k.rs:183-197,
+    q5_k.rs:100-123, q6_k.rs:96-110, q4_0.rs:47-64, q8_0.rs:59-67).  Returns (codes, valid): codes
+    [blocks, block elements] int32 comparable with ``stored_codes``; valid marks the elements
+    whose (sub-)block scale is non-zero (the quantizers skip the others and keep earlier codes).
+    float32 arithmetic, one operation per numpy call."""
+    be, bb = oracle.block_geometry(t)
+    b = np.ascontiguousarray(raw, dtype=np.uint8).reshape(-1, bb)
+    nb = b.shape[0]
+    y = np.ascontiguousarray(y, dtype=np.float32).reshape(nb, be)
+    one = np.float32(1.0)
+    if t in (oracle.Q4_0, oracle.Q8_0):
+        d = _f16_field(b[:, 0:2])[:, None]
+        with np.errstate(divide="ignore"):
+            inv = np.where(d != 0, one / d, np.float32(0.0)).astype(np.float32)
+        v = (y * inv).astype(np.float32)
+        if t == oracle.Q4_0:
+            codes = np.minimum(15, np.trunc((v + np.float32(8.5)).astype(np.float32))).astype(np.int32)
+        else:
+            codes = (np.sign(v) * np.floor(np.abs(v) + np.float32(0.5))).astype(np.int32)    # f32::round: half away from zero
+        return codes, np.broadcast_to(d != 0, codes.shape)
+    if t in (oracle.Q4_K, oracle.Q5_K):
+        d = _f16_field(b[:, 0:2])[:, None]
+        dmin = _f16_field(b[:, 2:4])[:, None]
+        s = b[:, 4:16]
+        sc = np.empty((nb, 8), np.float32)
+        mn = np.empty((nb, 8), np.float32)
+        sc[:, :4], mn[:, :4] = s[:, 0:4] & 63, s[:, 4:8] & 63
+        sc[:, 4:] = (s[:, 8:12] & 15) | ((s[:, 0:4] >> 6) << 4)
+        mn[:, 4:] = (s[:, 8:12] >> 4) | ((s[:, 4:8] >> 6) << 4)
+        dd = np.repeat((d * sc).astype(np.float32), 32, axis=1)
+        dm = np.repeat((dmin * mn).astype(np.float32), 32, axis=1)
+        with np.errstate(divide="ignore", invalid="ignore"):
+            q = np.rint(((y + dm).astype(np.float32) / dd).astype(np.float32))
+        hi = 15 if t == oracle.Q4_K else 31
+        valid = dd != 0
+        return np.clip(np.where(valid, q, 0), 0, hi).astype(np.int32), valid
+    sc = b[:, 192:208].view(np.int8).astype(np.float32)
+    d = _f16_field(b[:, 208:210])[:, None]
+    dd = np.repeat((d * sc).astype(np.float32), 16, axis=1)
+    with np.errstate(divide="ignore", invalid="ignore"):
+        q = np.rint((y / dd).astype(np.float32))
+    valid = dd != 0
+    return (np.clip(np.where(valid, q, 0), -32, 31) + 32).astype(np.int32), valid
