@@ -74,7 +74,7 @@ struct DeviceGuard {
 size_t dtype_size(uint32_t dt) { return dt == HF2Q_DT_F32 ? 4 : 2; }
 
 int32_t check_matmul_shape(hf2q_ctx* ctx, uint32_t type, uint32_t n, uint32_t k, const char* who) {
-    if (!type_supported(type)) return fail(ctx, HF2Q_ERR_UNSUPPORTED_TYPE, "%s: ggml type %u is not one of Q4_0/Q8_0/Q4_K/Q5_K/Q6_K", who, type);
+    if (!type_supported(type)) return fail(ctx, HF2Q_ERR_UNSUPPORTED_TYPE, "%s: ggml type %u is not one of Q4_0/Q4_1/Q5_0/Q5_1/Q8_0/Q4_K/Q5_K/Q6_K/IQ4_NL", who, type);
     const BlockGeom g = block_geom(type);
     if (n == 0 || k == 0) return fail(ctx, HF2Q_ERR_INVALID_ARGUMENT, "%s: n=%u k=%u must be non-zero", who, n, k);
     if (k % g.elems) return fail(ctx, HF2Q_ERR_INVALID_ARGUMENT, "%s: k=%u is not a multiple of the %u-element block", who, k, g.elems);

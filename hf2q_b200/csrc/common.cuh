@@ -2,7 +2,9 @@
 //
 // Block layouts and the dequantisation formulas are the inverse of hf2q's quantizers' re-encode
 // step (src/quantize/ggml_quants/q4_0.rs:47-64, q8_0.rs:59-67, q4_k.rs:183-215 + 329-337,
-// q5_k.rs:100-158, q6_k.rs:96-143); sizes follow ggml_type.rs:60-133.
+// q5_k.rs:100-158, q6_k.rs:96-143); sizes follow ggml_type.rs:60-133.  The four 32-element fall-back
+// formats (q4_1.rs, q5_0.rs, q5_1.rs, iq4_nl.rs) dequantise to the value their quantizers' error
+// terms assign to a code: d*q + m, (q - 16)*d and d*kvalues[q].
 #pragma once
 #include <cuda_fp16.h>
 #include <cuda_bf16.h>
@@ -26,7 +28,12 @@ struct BlockGeom { uint32_t elems, bytes; };
 
 __host__ __device__ constexpr bool type_supported(uint32_t t) {
     return t == HF2Q_TYPE_Q4_0 || t == HF2Q_TYPE_Q8_0 || t == HF2Q_TYPE_Q4_K ||
-           t == HF2Q_TYPE_Q5_K || t == HF2Q_TYPE_Q6_K;
+           t == HF2Q_TYPE_Q5_K || t == HF2Q_TYPE_Q6_K || t == HF2Q_TYPE_Q4_1 || t == HF2Q_TYPE_Q5_0 ||
+           t == HF2Q_TYPE_Q5_1 || t == HF2Q_TYPE_IQ4_NL;
+}
+// the 32-element formats hf2q's quantizer falls back to (standard_policy.rs:128-192)
+__host__ __device__ constexpr bool type_is_fallback32(uint32_t t) {
+    return t == HF2Q_TYPE_Q4_1 || t == HF2Q_TYPE_Q5_0 || t == HF2Q_TYPE_Q5_1 || t == HF2Q_TYPE_IQ4_NL;
 }
 __host__ __device__ constexpr BlockGeom block_geom(uint32_t t) {
     return t == HF2Q_TYPE_Q4_0 ? BlockGeom{32, 18}
@@ -34,6 +41,10 @@ __host__ __device__ constexpr BlockGeom block_geom(uint32_t t) {
          : t == HF2Q_TYPE_Q4_K ? BlockGeom{256, 144}
          : t == HF2Q_TYPE_Q5_K ? BlockGeom{256, 176}
          : t == HF2Q_TYPE_Q6_K ? BlockGeom{256, 210}
+         : t == HF2Q_TYPE_Q4_1 ? BlockGeom{32, 20}
+         : t == HF2Q_TYPE_Q5_0 ? BlockGeom{32, 22}
+         : t == HF2Q_TYPE_Q5_1 ? BlockGeom{32, 24}
+         : t == HF2Q_TYPE_IQ4_NL ? BlockGeom{32, 18}
                                : BlockGeom{0, 0};
 }
 
@@ -63,6 +74,13 @@ __device__ __forceinline__ void scale_min_k4(int j, uint32_t s0, uint32_t s1, ui
     }
 }
 
+// The IQ4_NL codebook (iq4_nl.rs KVALUES_IQ4NL) as four packed words of signed bytes.
+__device__ __forceinline__ int iq4nl_value(uint32_t code) {
+    // -127 -104 -83 -65 | -49 -35 -22 -10 | 1 13 25 38 | 53 69 89 113   (little-endian bytes)
+    const uint32_t w = code < 8 ? (code < 4 ? 0xBFAD9881u : 0xF6EADDCFu) : (code < 12 ? 0x26190D01u : 0x71594535u);
+    return static_cast<int>(static_cast<int8_t>((w >> (8 * (code & 3u))) & 0xffu));
+}
+
 // Value of element e (0 <= e < block elems) of one block, in f32, bit-exact with the oracle:
 // every product below is exact in f32 (11-bit f16 significand x 6..8-bit scale x <= 6-bit code),
 // and the single subtraction of Q4_K/Q5_K rounds the same exact value with or without FMA
@@ -77,6 +95,22 @@ __device__ __forceinline__ float dequant_elem(const uint8_t* __restrict__ b, int
     } else if constexpr (TYPE == HF2Q_TYPE_Q8_0) {
         const float d = f16_bits_to_f32(ld_u16(b));
         return static_cast<float>(static_cast<int8_t>(b[2 + e])) * d;
+    } else if constexpr (TYPE == HF2Q_TYPE_Q4_1) {
+        const float d = f16_bits_to_f32(ld_u16(b)), m = f16_bits_to_f32(ld_u16(b + 2));
+        const uint32_t q = b[4 + (e & 15)];
+        return __fadd_rn(__fmul_rn(d, static_cast<float>(e < 16 ? (q & 15u) : (q >> 4))), m);
+    } else if constexpr (TYPE == HF2Q_TYPE_Q5_0 || TYPE == HF2Q_TYPE_Q5_1) {
+        constexpr int O = TYPE == HF2Q_TYPE_Q5_0 ? 2 : 4;            // qh follows d (and m)
+        const float d = f16_bits_to_f32(ld_u16(b));
+        const uint32_t qh = ld_u32_a2(b + O);
+        const uint32_t v = b[O + 4 + (e & 15)];
+        const uint32_t q = (e < 16 ? (v & 15u) : (v >> 4)) | (((qh >> e) & 1u) << 4);
+        if constexpr (TYPE == HF2Q_TYPE_Q5_0) return static_cast<float>(static_cast<int>(q) - 16) * d;
+        else return __fadd_rn(__fmul_rn(d, static_cast<float>(q)), f16_bits_to_f32(ld_u16(b + 2)));
+    } else if constexpr (TYPE == HF2Q_TYPE_IQ4_NL) {
+        const float d = f16_bits_to_f32(ld_u16(b));
+        const uint32_t v = b[2 + (e & 15)];
+        return d * static_cast<float>(iq4nl_value(e < 16 ? (v & 15u) : (v >> 4)));
     } else if constexpr (TYPE == HF2Q_TYPE_Q4_K || TYPE == HF2Q_TYPE_Q5_K) {
         const float d = f16_bits_to_f32(ld_u16(b));
         const float dmin = f16_bits_to_f32(ld_u16(b + 2));

@@ -60,6 +60,10 @@ cudaError_t launch_dequant(uint32_t type, const void* w, void* out, uint32_t out
         case HF2Q_TYPE_Q4_K: return launch_dequant_t<HF2Q_TYPE_Q4_K>(w, out, out_dtype, n_elems, sm_count, st);
         case HF2Q_TYPE_Q5_K: return launch_dequant_t<HF2Q_TYPE_Q5_K>(w, out, out_dtype, n_elems, sm_count, st);
         case HF2Q_TYPE_Q6_K: return launch_dequant_t<HF2Q_TYPE_Q6_K>(w, out, out_dtype, n_elems, sm_count, st);
+        case HF2Q_TYPE_Q4_1: return launch_dequant_t<HF2Q_TYPE_Q4_1>(w, out, out_dtype, n_elems, sm_count, st);
+        case HF2Q_TYPE_Q5_0: return launch_dequant_t<HF2Q_TYPE_Q5_0>(w, out, out_dtype, n_elems, sm_count, st);
+        case HF2Q_TYPE_Q5_1: return launch_dequant_t<HF2Q_TYPE_Q5_1>(w, out, out_dtype, n_elems, sm_count, st);
+        case HF2Q_TYPE_IQ4_NL: return launch_dequant_t<HF2Q_TYPE_IQ4_NL>(w, out, out_dtype, n_elems, sm_count, st);
         default: return cudaErrorInvalidValue;
     }
 }

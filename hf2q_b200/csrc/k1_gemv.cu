@@ -205,6 +205,30 @@ __device__ __forceinline__ void consume_q8_0(const uint8_t* sb, int nblk, uint32
     }
 }
 
+// Q4_1 / Q5_0 / Q5_1 / IQ4_NL (the quantizer's fall-back formats for rows that are not a multiple
+// of 256 long): one 32-element block per lane and turn, every element decoded by the shared
+// dequant_elem, so this path and the stand-alone dequantiser cannot drift apart.  These tensors are
+// rare and small; the path is correct and streams, it is not tuned.
+template <uint32_t TYPE, int M, bool XSMEM>
+__device__ __forceinline__ void consume_block32(const uint8_t* sb, int nblk, uint32_t kbase,
+                                                const XAcc<XSMEM>& xa, float (&acc)[M], int lane) {
+    constexpr BlockGeom G = block_geom(TYPE);
+    for (int u = lane; u < nblk; u += 32) {
+        const uint8_t* blk = sb + u * G.bytes;
+        const uint32_t e0 = kbase + u * 32;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const float w0 = dequant_elem<TYPE>(blk, 4 * j), w1 = dequant_elem<TYPE>(blk, 4 * j + 1);
+            const float w2 = dequant_elem<TYPE>(blk, 4 * j + 2), w3 = dequant_elem<TYPE>(blk, 4 * j + 3);
+#pragma unroll
+            for (int t = 0; t < M; ++t) {
+                const float4 x = xa.ld4(t, e0 + 4 * j);
+                acc[t] += (w0 * x.x + w1 * x.y) + (w2 * x.z + w3 * x.w);
+            }
+        }
+    }
+}
+
 // ---- the streaming kernel ---------------------------------------------------------------------
 template <uint32_t TYPE, int M, bool XSMEM>
 __global__ void __launch_bounds__(THREADS) gemv_stream_kernel(const KParams p) {
@@ -327,8 +351,10 @@ __global__ void __launch_bounds__(THREADS) gemv_stream_kernel(const KParams p) {
                     consume_q6k<M, XSMEM>(sb, nblk, kbase, xa, acc, lane);
                 else if constexpr (TYPE == HF2Q_TYPE_Q4_0)
                     consume_q4_0<M, XSMEM>(sb, nblk, kbase, xa, acc, lane);
-                else
+                else if constexpr (TYPE == HF2Q_TYPE_Q8_0)
                     consume_q8_0<M, XSMEM>(sb, nblk, kbase, xa, acc, lane);
+                else
+                    consume_block32<TYPE, M, XSMEM>(sb, nblk, kbase, xa, acc, lane);
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(&empty[st]);
@@ -483,6 +509,10 @@ cudaError_t launch_gemv(const GemvArgs& a, const DeviceInfo& dev, cudaStream_t s
         case HF2Q_TYPE_Q4_K: return launch_type<HF2Q_TYPE_Q4_K>(p, a.slots, can_stream, dev, st);
         case HF2Q_TYPE_Q5_K: return launch_type<HF2Q_TYPE_Q5_K>(p, a.slots, can_stream, dev, st);
         case HF2Q_TYPE_Q6_K: return launch_type<HF2Q_TYPE_Q6_K>(p, a.slots, can_stream, dev, st);
+        case HF2Q_TYPE_Q4_1: return launch_type<HF2Q_TYPE_Q4_1>(p, a.slots, can_stream, dev, st);
+        case HF2Q_TYPE_Q5_0: return launch_type<HF2Q_TYPE_Q5_0>(p, a.slots, can_stream, dev, st);
+        case HF2Q_TYPE_Q5_1: return launch_type<HF2Q_TYPE_Q5_1>(p, a.slots, can_stream, dev, st);
+        case HF2Q_TYPE_IQ4_NL: return launch_type<HF2Q_TYPE_IQ4_NL>(p, a.slots, can_stream, dev, st);
         default: return cudaErrorInvalidValue;
     }
 }

@@ -1125,7 +1125,8 @@ uint32_t gemv_mma_grid_x(uint32_t n, uint32_t k, const DeviceInfo& dev) {
 bool gemv_mma_supported(const GemvArgs& a) {
     const BlockGeom g = block_geom(a.type);
     const uint64_t row_bytes = static_cast<uint64_t>(a.k) / g.elems * g.bytes;
-    return a.k % 256 == 0 && row_bytes % 16 == 0 && a.expert_stride % 16 == 0 &&
+    // (the four 32-element fall-back formats take the CUDA-core kernel: no warp-MMA unpack routine exists for them)
+    return !type_is_fallback32(a.type) && a.k % 256 == 0 && row_bytes % 16 == 0 && a.expert_stride % 16 == 0 &&
            reinterpret_cast<uintptr_t>(a.w) % 16 == 0 && reinterpret_cast<uintptr_t>(a.x) % 16 == 0;
 }
 
@@ -1134,13 +1135,14 @@ bool gemv_mma_supported(const GemvArgs& a) {
 uint32_t gemv_mma_max_rows(uint32_t type, uint32_t k, uint32_t x_dtype, const DeviceInfo& dev) {
     const uint32_t per_row = x_dtype == HF2Q_DT_BF16 ? 1 : 2;
     uint32_t rows = 8 / per_row;
+    if (type_is_fallback32(type)) return 0;
     while (rows > 0 && !make_plan(type, k, rows * per_row, 2, static_cast<size_t>(dev.max_smem_optin)).stages) --rows;
     return rows;
 }
 
 bool gemv_mma_swiglu_ok(uint32_t type, uint32_t k, uint32_t m, uint32_t x_dtype, const DeviceInfo& dev) {
     const uint32_t nslots = x_dtype == HF2Q_DT_BF16 ? m : 2 * m;
-    if (m == 0 || nslots > 8 || k % 256 || sub_groups_of(k) > 1) return false;
+    if (m == 0 || nslots > 8 || k % 256 || sub_groups_of(k) > 1 || type_is_fallback32(type)) return false;
     const Plan pl = make_plan(type, k, nslots, 2, static_cast<size_t>(dev.max_smem_optin));
     return pl.stages && pl.phase_base == (k + SLICE_ELEMS - 1) / SLICE_ELEMS;
 }

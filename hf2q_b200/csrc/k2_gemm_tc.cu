@@ -423,6 +423,10 @@ cudaError_t launch_gemm_tc(uint32_t type, const void* w, const void* x, uint32_t
         case HF2Q_TYPE_Q4_K: return launch_gemm_nt<HF2Q_TYPE_Q4_K>(tw, tx, p, nt, st);
         case HF2Q_TYPE_Q5_K: return launch_gemm_nt<HF2Q_TYPE_Q5_K>(tw, tx, p, nt, st);
         case HF2Q_TYPE_Q6_K: return launch_gemm_nt<HF2Q_TYPE_Q6_K>(tw, tx, p, nt, st);
+        case HF2Q_TYPE_Q4_1: return launch_gemm_nt<HF2Q_TYPE_Q4_1>(tw, tx, p, nt, st);
+        case HF2Q_TYPE_Q5_0: return launch_gemm_nt<HF2Q_TYPE_Q5_0>(tw, tx, p, nt, st);
+        case HF2Q_TYPE_Q5_1: return launch_gemm_nt<HF2Q_TYPE_Q5_1>(tw, tx, p, nt, st);
+        case HF2Q_TYPE_IQ4_NL: return launch_gemm_nt<HF2Q_TYPE_IQ4_NL>(tw, tx, p, nt, st);
         default: return cudaErrorInvalidValue;
     }
 }
@@ -499,6 +503,10 @@ cudaError_t launch_gemm_tc_grouped(uint32_t type, const void* w_stacked, uint64_
         case HF2Q_TYPE_Q4_K: return launch_grouped_nt<HF2Q_TYPE_Q4_K>(tw, tx, p, nt, gy, st);
         case HF2Q_TYPE_Q5_K: return launch_grouped_nt<HF2Q_TYPE_Q5_K>(tw, tx, p, nt, gy, st);
         case HF2Q_TYPE_Q6_K: return launch_grouped_nt<HF2Q_TYPE_Q6_K>(tw, tx, p, nt, gy, st);
+        case HF2Q_TYPE_Q4_1: return launch_grouped_nt<HF2Q_TYPE_Q4_1>(tw, tx, p, nt, gy, st);
+        case HF2Q_TYPE_Q5_0: return launch_grouped_nt<HF2Q_TYPE_Q5_0>(tw, tx, p, nt, gy, st);
+        case HF2Q_TYPE_Q5_1: return launch_grouped_nt<HF2Q_TYPE_Q5_1>(tw, tx, p, nt, gy, st);
+        case HF2Q_TYPE_IQ4_NL: return launch_grouped_nt<HF2Q_TYPE_IQ4_NL>(tw, tx, p, nt, gy, st);
         default: return cudaErrorInvalidValue;
     }
 }

@@ -176,7 +176,7 @@ __device__ __forceinline__ void dq_q6k(WordFn W, int qd, uint32_t (&out)[32]) {
     }
 }
 
-// Q4_0 / Q8_0: eight 32-element blocks per K-block; element-wise decode (correct, not tuned).
+// Q4_0 / Q8_0 / Q4_1 / Q5_0 / Q5_1 / IQ4_NL: eight 32-element blocks per K-block; element-wise decode (correct, not tuned).
 template <uint32_t TYPE>
 __device__ __forceinline__ void dq_legacy(const uint8_t* row, int qd, uint32_t (&out)[32]) {
     constexpr BlockGeom G = block_geom(TYPE);
@@ -256,7 +256,9 @@ __device__ __forceinline__ void with_row_block(uint32_t off, F&& f) {
 __host__ __device__ constexpr uint32_t tc_boxw(uint32_t type) {
     return type == HF2Q_TYPE_Q4_K ? 144u : type == HF2Q_TYPE_Q5_K ? 176u
          : type == HF2Q_TYPE_Q6_K ? 240u   // 210 bytes at an offset of 0..14; pitch of 15 x 16 bytes
-         : type == HF2Q_TYPE_Q4_0 ? 144u : type == HF2Q_TYPE_Q8_0 ? 272u : 0u;
+         : type == HF2Q_TYPE_Q4_0 ? 144u : type == HF2Q_TYPE_Q8_0 ? 272u
+         : type == HF2Q_TYPE_Q4_1 ? 160u : type == HF2Q_TYPE_Q5_0 ? 176u : type == HF2Q_TYPE_Q5_1 ? 192u
+         : type == HF2Q_TYPE_IQ4_NL ? 144u : 0u;
 }
 
 }  // namespace tc

@@ -33,10 +33,14 @@ from . import _lib
 
 class GgmlType(enum.IntEnum):
     Q4_0 = 2
+    Q4_1 = 3
+    Q5_0 = 6
+    Q5_1 = 7
     Q8_0 = 8
     Q4_K = 12
     Q5_K = 13
     Q6_K = 14
+    IQ4_NL = 20
 
 
 DT_F32, DT_F16, DT_BF16 = 0, 1, 2

@@ -42,7 +42,7 @@ typedef struct hf2q_ctx hf2q_ctx;
 enum {
     HF2Q_OK = 0,
     HF2Q_ERR_INVALID_ARGUMENT = 1, /* null pointer, zero or mismatched shape, misaligned buffer   */
-    HF2Q_ERR_UNSUPPORTED_TYPE = 2, /* ggml type outside {Q4_0,Q8_0,Q4_K,Q5_K,Q6_K}                */
+    HF2Q_ERR_UNSUPPORTED_TYPE = 2, /* ggml type outside the nine block formats listed below       */
     HF2Q_ERR_CUDA = 3,             /* a CUDA runtime call failed; see hf2q_cuda_last_error        */
     HF2Q_ERR_WORKSPACE = 4,        /* workspace / scratch missing or too small                    */
     HF2Q_ERR_TIMEOUT = 5,          /* a bounded device-side wait gave up (status word non-zero)   */
@@ -50,13 +50,22 @@ enum {
     HF2Q_ERR_NO_DEVICE = 7
 };
 
-/* GGUF numeric type ids (src/quantize/ggml_quants/ggml_type.rs:18-33). */
+/* GGUF numeric type ids (src/quantize/ggml_quants/ggml_type.rs:18-45).  Q4_0 .. Q6_K are the formats
+ * of the quantized-weight matmul path proper; Q4_1, Q5_0, Q5_1 and IQ4_NL are what hf2q's quantizer
+ * falls back to for tensors whose row length is not a multiple of 256
+ * (tensor_type_fallback, src/quantize/ggml_quants/standard_policy.rs:128-192).  Every entry point
+ * takes all nine; the four fall-back formats run on the CUDA-core mat-vec (m <= 8) and on the
+ * tensor-core GEMM, but not on the fused epilogue variants, which answer "not supported". */
 enum {
     HF2Q_TYPE_Q4_0 = 2,
+    HF2Q_TYPE_Q4_1 = 3,
+    HF2Q_TYPE_Q5_0 = 6,
+    HF2Q_TYPE_Q5_1 = 7,
     HF2Q_TYPE_Q8_0 = 8,
     HF2Q_TYPE_Q4_K = 12,
     HF2Q_TYPE_Q5_K = 13,
-    HF2Q_TYPE_Q6_K = 14
+    HF2Q_TYPE_Q6_K = 14,
+    HF2Q_TYPE_IQ4_NL = 20
 };
 
 /* Element types of activations and of dequantised output. */

@@ -23,9 +23,13 @@ _SO = _HERE / "_build" / "liboracle.so"
 _SRC = _HERE / "ggml_quants_oracle.cpp"
 
 # GGUF numeric type ids (src/quantize/ggml_quants/ggml_type.rs:18-33)
-Q4_0, Q8_0, Q4_K, Q5_K, Q6_K = 2, 8, 12, 13, 14
-TYPE_NAMES = {Q4_0: "q4_0", Q8_0: "q8_0", Q4_K: "q4_k", Q5_K: "q5_k", Q6_K: "q6_k"}
+Q4_0, Q4_1, Q5_0, Q5_1, Q8_0, Q4_K, Q5_K, Q6_K, IQ4_NL = 2, 3, 6, 7, 8, 12, 13, 14, 20
+TYPE_NAMES = {Q4_0: "q4_0", Q8_0: "q8_0", Q4_K: "q4_k", Q5_K: "q5_k", Q6_K: "q6_k",
+              Q4_1: "q4_1", Q5_0: "q5_0", Q5_1: "q5_1", IQ4_NL: "iq4_nl"}
 ALL_TYPES = tuple(TYPE_NAMES)
+# the five formats the benchmark workloads name; the other four are the quantizer's fall-back targets
+# for tensors whose row length is not a multiple of 256 (standard_policy.rs:128-192)
+MAIN_TYPES = (Q4_0, Q8_0, Q4_K, Q5_K, Q6_K)
 
 
 def build(force: bool = False) -> Path:

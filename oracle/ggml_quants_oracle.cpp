@@ -369,6 +369,185 @@ void q4_0_row_impl(const float* x, const float* imatrix, int64_t n_per_row, uint
     }
 }
 
+// ---- the 32-element formats the reference's tensor_type_fallback targets (standard_policy.rs:128-192)
+// Rust `f32 as u8`: truncate toward zero, saturate, NaN -> 0.
+inline uint8_t sat_u8(float v) {
+    if (std::isnan(v)) return 0;
+    if (v <= 0.0f) return 0;
+    if (v >= 255.0f) return 255;
+    return (uint8_t)(int)v;
+}
+inline void put_u32(uint8_t* p, uint32_t v) { p[0] = (uint8_t)v; p[1] = (uint8_t)(v >> 8); p[2] = (uint8_t)(v >> 16); p[3] = (uint8_t)(v >> 24); }
+inline uint32_t get_u32(const uint8_t* p) { return (uint32_t)p[0] | ((uint32_t)p[1] << 8) | ((uint32_t)p[2] << 16) | ((uint32_t)p[3] << 24); }
+
+// weight[j] = qw[j] * sqrt(sigma2 + x[j]^2) with sigma2 = mean(x^2) over the row (q4_1.rs:119-137 and siblings)
+inline float row_sigma2(const float* x, int64_t n) {
+    float sum_x2 = 0.0f;
+    for (int64_t j = 0; j < n; ++j) sum_x2 += x[j] * x[j];
+    return sum_x2 / (float)n;
+}
+
+// q4_1.rs:79-113 (no imatrix) and :116-160 (imatrix, make_qkx3_quants)
+void q4_1_row(const float* x, const float* imatrix, int64_t n, uint8_t* out) {
+    const float sigma2 = imatrix ? row_sigma2(x, n) : 0.0f;
+    for (int64_t i = 0; i < n / 32; ++i) {
+        const float* b = x + 32 * i;
+        uint8_t* o = out + 20 * i;
+        if (!imatrix) {
+            float mn = 3.40282347e+38f, mx = -3.40282347e+38f;
+            for (int j = 0; j < 32; ++j) { if (b[j] < mn) mn = b[j]; if (b[j] > mx) mx = b[j]; }
+            float d = (mx - mn) / 15.0f;
+            float id = d != 0.0f ? 1.0f / d : 0.0f;
+            put_f16(o, f32_to_f16(d));
+            put_f16(o + 2, f32_to_f16(mn));
+            for (int j = 0; j < 16; ++j) {
+                float x0 = (b[j] - mn) * id, x1 = (b[16 + j] - mn) * id;
+                uint8_t xi0 = (uint8_t)std::min<int8_t>(sat_i8(x0 + 0.5f), 15);
+                uint8_t xi1 = (uint8_t)std::min<int8_t>(sat_i8(x1 + 0.5f), 15);
+                o[4 + j] = (uint8_t)(xi0 | (xi1 << 4));
+            }
+        } else {
+            float weight[32]; uint8_t L[32], Laux[32];
+            const float* qw = imatrix + 32 * i;
+            for (int j = 0; j < 32; ++j) weight[j] = qw[j] * std::sqrt(sigma2 + b[j] * b[j]);
+            float min_neg = 0.0f;
+            float d = make_qkx_quants(true, 32, 15, b, weight, L, &min_neg, Laux, -0.9f, 0.05f, 36, false);
+            put_f16(o, f32_to_f16(d));
+            put_f16(o + 2, f32_to_f16(-min_neg));
+            for (int j = 0; j < 16; ++j) o[4 + j] = (uint8_t)(L[j] | (L[j + 16] << 4));
+        }
+    }
+}
+
+// q5_0.rs:67-112 (no imatrix) and :114-193 (imatrix, make_qx_quants with nmax 16)
+void q5_0_row(const float* x, const float* imatrix, int64_t n, uint8_t* out) {
+    const float sigma2 = imatrix ? row_sigma2(x, n) : 0.0f;
+    for (int64_t i = 0; i < n / 32; ++i) {
+        const float* b = x + 32 * i;
+        uint8_t* o = out + 22 * i;
+        uint8_t q[32];
+        float d;
+        if (!imatrix) {
+            float amax = 0.0f, mx = 0.0f;
+            for (int j = 0; j < 32; ++j) { float av = std::fabs(b[j]); if (amax < av) { amax = av; mx = b[j]; } }
+            d = mx / -16.0f;
+            float id = d != 0.0f ? 1.0f / d : 0.0f;
+            for (int j = 0; j < 32; ++j) {
+                float v = b[j] * id + 16.5f;
+                int xi = std::isnan(v) ? 0 : (int)v;                 // `as i32`: truncation toward zero
+                q[j] = (uint8_t)std::min(xi, 31);
+            }
+        } else {
+            float weight[32]; int8_t L[32];
+            const float* qw = imatrix + 32 * i;
+            for (int j = 0; j < 32; ++j) weight[j] = qw[j] * std::sqrt(sigma2 + b[j] * b[j]);
+            d = make_qx_quants(32, 16, b, L, 1, weight);
+            for (int j = 0; j < 32; ++j) q[j] = (uint8_t)L[j];
+        }
+        put_f16(o, f32_to_f16(d));
+        uint32_t qh = 0;
+        for (int j = 0; j < 16; ++j) {
+            o[6 + j] = (uint8_t)((q[j] & 0x0F) | ((q[j + 16] & 0x0F) << 4));
+            qh |= (uint32_t)((q[j] & 0x10) >> 4) << j;
+            qh |= (uint32_t)((q[j + 16] & 0x10) >> 4) << (j + 16);
+        }
+        put_u32(o + 2, qh);
+    }
+}
+
+// q5_1.rs:40-88 (no imatrix) and :90-150 (imatrix, make_qkx3_quants with nmax 31)
+void q5_1_row(const float* x, const float* imatrix, int64_t n, uint8_t* out) {
+    const float sigma2 = imatrix ? row_sigma2(x, n) : 0.0f;
+    for (int64_t i = 0; i < n / 32; ++i) {
+        const float* b = x + 32 * i;
+        uint8_t* o = out + 24 * i;
+        uint8_t q[32];
+        if (!imatrix) {
+            float mn = 3.40282347e+38f, mx = -3.40282347e+38f;
+            for (int j = 0; j < 32; ++j) { if (b[j] < mn) mn = b[j]; if (b[j] > mx) mx = b[j]; }
+            float d = (mx - mn) / 31.0f;
+            float id = d != 0.0f ? 1.0f / d : 0.0f;
+            put_f16(o, f32_to_f16(d));
+            put_f16(o + 2, f32_to_f16(mn));
+            for (int j = 0; j < 32; ++j) q[j] = sat_u8((b[j] - mn) * id + 0.5f);
+        } else {
+            float weight[32]; uint8_t Laux[32];
+            const float* qw = imatrix + 32 * i;
+            for (int j = 0; j < 32; ++j) weight[j] = qw[j] * std::sqrt(sigma2 + b[j] * b[j]);
+            float the_min = 0.0f;
+            float d = make_qkx_quants(true, 32, 31, b, weight, q, &the_min, Laux, -0.9f, 0.05f, 36, false);
+            put_f16(o, f32_to_f16(d));
+            put_f16(o + 2, f32_to_f16(-the_min));
+        }
+        uint32_t qh = 0;
+        for (int j = 0; j < 16; ++j) {
+            o[8 + j] = (uint8_t)((q[j] & 0x0F) | ((q[j + 16] & 0x0F) << 4));
+            qh |= (uint32_t)((q[j] & 0x10) >> 4) << j;
+            qh |= (uint32_t)((q[j + 16] & 0x10) >> 4) << (j + 16);
+        }
+        put_u32(o + 4, qh);
+    }
+}
+
+// iq4_nl.rs: the 16-entry non-linear codebook and the single-block search with ntry = 7
+const int8_t KVALUES_IQ4NL[16] = {-127, -104, -83, -65, -49, -35, -22, -10, 1, 13, 25, 38, 53, 69, 89, 113};
+
+// common.rs:33-55
+inline int best_index_int8(const int8_t* val, int n, float x) {
+    if (x <= (float)val[0]) return 0;
+    if (x >= (float)val[n - 1]) return n - 1;
+    int ml = 0, mu = n - 1;
+    while (mu - ml > 1) {
+        int mav = (ml + mu) / 2;
+        if (x < (float)val[mav]) mu = mav; else ml = mav;
+    }
+    return x - (float)val[mu - 1] < (float)val[mu] - x ? mu - 1 : mu;
+}
+
+void iq4_nl_block(const float* x, const float* qw, uint8_t* out) {
+    const int ntry = 7;
+    const int8_t* values = KVALUES_IQ4NL;
+    float sigma2 = 0.0f;
+    for (int j = 0; j < 32; ++j) sigma2 += x[j] * x[j];
+    sigma2 *= 2.0f / 32.0f;
+    float weight[32]; uint8_t L[32] = {0};
+    for (int j = 0; j < 32; ++j) weight[j] = qw ? qw[j] * std::sqrt(sigma2 + x[j] * x[j]) : x[j] * x[j];
+    float amax = 0.0f, mx = 0.0f;
+    for (int j = 0; j < 32; ++j) { float ax = std::fabs(x[j]); if (ax > amax) { amax = ax; mx = x[j]; } }
+    float scale0 = 0.0f;
+    const bool all_zero = amax < GROUP_MAX_EPS;
+    if (!all_zero) {
+        float d = -mx / (float)values[0];          // ntry > 0
+        float id = 1.0f / d;
+        float sumqx = 0.0f, sumq2 = 0.0f;
+        for (int j = 0; j < 32; ++j) {
+            int l = best_index_int8(values, 16, id * x[j]);
+            L[j] = (uint8_t)l;
+            float q = (float)values[l], w = weight[j];
+            sumqx += w * q * x[j];
+            sumq2 += w * q * q;
+        }
+        d = sumq2 > 0.0f ? sumqx / sumq2 : 0.0f;
+        float best = d * sumqx;
+        for (int itry = -ntry; itry <= ntry; ++itry) {
+            id = ((float)itry + (float)values[0]) / mx;
+            float sqx = 0.0f, sq2 = 0.0f;
+            for (int j = 0; j < 32; ++j) {
+                int l = best_index_int8(values, 16, id * x[j]);
+                float q = (float)values[l], w = weight[j];
+                sqx += w * q * x[j];
+                sq2 += w * q * q;
+            }
+            if (sq2 > 0.0f && sqx * sqx > best * sq2) { d = sqx / sq2; best = d * sqx; }
+        }
+        scale0 = d;
+        id = scale0 != 0.0f ? 1.0f / scale0 : 0.0f;
+        for (int j = 0; j < 32; ++j) L[j] = (uint8_t)best_index_int8(values, 16, id * x[j]);
+    }
+    put_f16(out, f32_to_f16(scale0));
+    for (int j = 0; j < 16; ++j) out[2 + j] = (uint8_t)(L[j] | (L[16 + j] << 4));
+}
+
 // ---- Q8_0 ------------------------------------------------------------------------------------
 // q8_0.rs:31-72.  Rust f32::round is half-away-from-zero == roundf.
 void q8_0_blocks(const float* src, int64_t n, uint8_t* out) {
@@ -550,7 +729,7 @@ void q6_k_block(const float* xb, const float* qw, uint8_t* o) {
 }
 
 // ---- geometry (ggml_type.rs:60-133) ----------------------------------------------------------
-enum : uint32_t { T_Q4_0 = 2, T_Q8_0 = 8, T_Q4_K = 12, T_Q5_K = 13, T_Q6_K = 14 };
+enum : uint32_t { T_Q4_0 = 2, T_Q4_1 = 3, T_Q5_0 = 6, T_Q5_1 = 7, T_Q8_0 = 8, T_Q4_K = 12, T_Q5_K = 13, T_Q6_K = 14, T_IQ4_NL = 20 };
 
 bool geometry(uint32_t t, int* block_elems, int* block_bytes) {
     switch (t) {
@@ -559,6 +738,10 @@ bool geometry(uint32_t t, int* block_elems, int* block_bytes) {
         case T_Q4_K: *block_elems = 256; *block_bytes = 144; return true;
         case T_Q5_K: *block_elems = 256; *block_bytes = 176; return true;
         case T_Q6_K: *block_elems = 256; *block_bytes = 210; return true;
+        case T_Q4_1: *block_elems = 32; *block_bytes = 20; return true;     // ggml_type.rs:100-105
+        case T_Q5_0: *block_elems = 32; *block_bytes = 22; return true;
+        case T_Q5_1: *block_elems = 32; *block_bytes = 24; return true;
+        case T_IQ4_NL: *block_elems = 32; *block_bytes = 18; return true;
         default: return false;
     }
 }
@@ -622,6 +805,44 @@ void dequant_block(uint32_t t, const uint8_t* b, float* y) {
                     y[e] = (d * (float)sc[e / 16]) * (float)q;
                 }
     } break;
+    // The 32-element fallback formats: the value each code stands for is the one the quantizers'
+    // own error terms use -- scale*L + min in make_qkx3_quants (common.rs:339-343, Q4_1 / Q5_1), the
+    // symmetric grid of make_qx_quants shifted by nmax (Q5_0, q5_0.rs:80-100) and d * values[L] for
+    // IQ4_NL (iq4_nl.rs first pass).  d*q is exact in f32, so fused or not the one addition rounds alike.
+    case T_Q4_1: {
+        float d = f16_to_f32(get_u16(b)), m = f16_to_f32(get_u16(b + 2));
+        for (int j = 0; j < 16; ++j) {
+            y[j] = d * (float)(b[4 + j] & 15) + m;
+            y[j + 16] = d * (float)(b[4 + j] >> 4) + m;
+        }
+    } break;
+    case T_Q5_0: {
+        float d = f16_to_f32(get_u16(b));
+        uint32_t qh = get_u32(b + 2);
+        for (int j = 0; j < 16; ++j) {
+            int q0 = (b[6 + j] & 15) | (int)(((qh >> j) & 1u) << 4);
+            int q1 = (b[6 + j] >> 4) | (int)(((qh >> (j + 16)) & 1u) << 4);
+            y[j] = (float)(q0 - 16) * d;
+            y[j + 16] = (float)(q1 - 16) * d;
+        }
+    } break;
+    case T_Q5_1: {
+        float d = f16_to_f32(get_u16(b)), m = f16_to_f32(get_u16(b + 2));
+        uint32_t qh = get_u32(b + 4);
+        for (int j = 0; j < 16; ++j) {
+            int q0 = (b[8 + j] & 15) | (int)(((qh >> j) & 1u) << 4);
+            int q1 = (b[8 + j] >> 4) | (int)(((qh >> (j + 16)) & 1u) << 4);
+            y[j] = d * (float)q0 + m;
+            y[j + 16] = d * (float)q1 + m;
+        }
+    } break;
+    case T_IQ4_NL: {
+        float d = f16_to_f32(get_u16(b));
+        for (int j = 0; j < 16; ++j) {
+            y[j] = d * (float)KVALUES_IQ4NL[b[2 + j] & 15];
+            y[j + 16] = d * (float)KVALUES_IQ4NL[b[2 + j] >> 4];
+        }
+    } break;
     default: break;
     }
 }
@@ -669,6 +890,13 @@ int oracle_quantize(uint32_t ggml_type, const float* src, int64_t n_rows, int64_
         case T_Q6_K:
             for (int64_t i = 0; i < n_per_row / QK_K; ++i)
                 q6_k_block(x + i * QK_K, imatrix ? imatrix + i * QK_K : nullptr, o + i * 210);
+            break;
+        case T_Q4_1: q4_1_row(x, imatrix, n_per_row, o); break;
+        case T_Q5_0: q5_0_row(x, imatrix, n_per_row, o); break;
+        case T_Q5_1: q5_1_row(x, imatrix, n_per_row, o); break;
+        case T_IQ4_NL:
+            for (int64_t i = 0; i < n_per_row / 32; ++i)
+                iq4_nl_block(x + 32 * i, imatrix ? imatrix + 32 * i : nullptr, o + 18 * i);
             break;
         }
     }

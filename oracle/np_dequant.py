@@ -9,8 +9,10 @@ from __future__ import annotations
 
 import numpy as np
 
-Q4_0, Q8_0, Q4_K, Q5_K, Q6_K = 2, 8, 12, 13, 14
-_GEOM = {Q4_0: (32, 18), Q8_0: (32, 34), Q4_K: (256, 144), Q5_K: (256, 176), Q6_K: (256, 210)}
+Q4_0, Q4_1, Q5_0, Q5_1, Q8_0, Q4_K, Q5_K, Q6_K, IQ4_NL = 2, 3, 6, 7, 8, 12, 13, 14, 20
+_GEOM = {Q4_0: (32, 18), Q8_0: (32, 34), Q4_K: (256, 144), Q5_K: (256, 176), Q6_K: (256, 210),
+         Q4_1: (32, 20), Q5_0: (32, 22), Q5_1: (32, 24), IQ4_NL: (32, 18)}
+_KVALUES_IQ4NL = np.array([-127, -104, -83, -65, -49, -35, -22, -10, 1, 13, 25, 38, 53, 69, 89, 113], np.float32)
 
 
 def _f16(b: np.ndarray) -> np.ndarray:
@@ -45,6 +47,31 @@ def dequantize(t: int, raw) -> np.ndarray:
         d = _f16(raw[:, 0:2])[:, None]
         q = raw[:, 2:34].view(np.int8).astype(np.float32)
         return (q * d).reshape(-1)
+    if t in (Q4_1, Q5_0, Q5_1, IQ4_NL):
+        # 32-element blocks: [d][m (Q4_1, Q5_1)][qh u32 (Q5_0, Q5_1)][16 nibble bytes]; the low nibbles are
+        # elements 0..15, the high nibbles 16..31; bit j / j+16 of qh is the fifth bit of element j / j+16
+        # (q4_1.rs:104-110, q5_0.rs:95-110, q5_1.rs:70-85, iq4_nl.rs nibble pack)
+        d = _f16(raw[:, 0:2])[:, None]
+        o = 2
+        m = None
+        if t in (Q4_1, Q5_1):
+            m = _f16(raw[:, 2:4])[:, None]
+            o = 4
+        hi5 = None
+        if t in (Q5_0, Q5_1):
+            qh = np.ascontiguousarray(raw[:, o:o + 4]).view("<u4").astype(np.uint32).reshape(-1, 1)
+            hi5 = ((qh >> np.arange(32, dtype=np.uint32)[None, :]) & 1).astype(np.int32)
+            o += 4
+        qs = raw[:, o:o + 16]
+        q = np.concatenate([qs & 15, qs >> 4], axis=1).astype(np.int32)
+        if hi5 is not None:
+            q = q | (hi5 << 4)
+        if t == IQ4_NL:
+            return (d * _KVALUES_IQ4NL[q]).astype(np.float32).reshape(-1)
+        if t == Q5_0:
+            return ((q - 16).astype(np.float32) * d).reshape(-1)
+        prod = d * q.astype(np.float32)
+        return (prod + m).astype(np.float32).reshape(-1)
     if t in (Q4_K, Q5_K):
         d = _f16(raw[:, 0:2])[:, None]
         dmin = _f16(raw[:, 2:4])[:, None]

@@ -3,7 +3,7 @@
 Two kinds of files are written:
 
 * ``ggml_quants/<type>_<n>_{noim,im}_{input,expected}.bin`` -- the reference's own golden vectors
-  for the five in-scope block formats, copied byte-for-byte from its
+  for the nine block formats the library takes, copied byte-for-byte from its
   ``tests/fixtures/ggml_quants/`` (they were produced by llama.cpp's ``ggml_quantize_chunk`` and
   are what hf2q's ``byte_cmp_noim`` / ``byte_cmp_im`` unit tests compare against).
 * ``MANIFEST.json`` -- sha256 of every copied file, so a silent edit is detected by the tests.
@@ -16,11 +16,13 @@ import shutil
 import sys
 from pathlib import Path
 
-TYPES = {"q4_0": 64, "q8_0": 64, "q4_k": 512, "q5_k": 512, "q6_k": 512}
+TYPES = {"q4_0": 64, "q8_0": 64, "q4_k": 512, "q5_k": 512, "q6_k": 512, "q4_1": 64, "q5_0": 64, "q5_1": 64, "iq4_nl": 64}
 
 
 def main() -> None:
-    ref = Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) != 2:
+        raise SystemExit("usage: python tests/golden/make_golden.py /path/to/hf2q")
+    ref = Path(sys.argv[1])
     src = ref / "tests" / "fixtures" / "ggml_quants"
     dst = Path(__file__).resolve().parent / "ggml_quants"
     dst.mkdir(exist_ok=True)

@@ -23,7 +23,8 @@ def test_every_declared_symbol_is_exported_and_bound(lib):
 
 def test_geometry_matches_ggml_type_rs(lib):
     # ggml_type.rs:60-127
-    for t, (be, bb) in {2: (32, 18), 8: (32, 34), 12: (256, 144), 13: (256, 176), 14: (256, 210)}.items():
+    for t, (be, bb) in {2: (32, 18), 8: (32, 34), 12: (256, 144), 13: (256, 176), 14: (256, 210),
+                        3: (32, 20), 6: (32, 22), 7: (32, 24), 20: (32, 18)}.items():
         e, b = C.c_uint32(), C.c_uint32()
         assert lib.hf2q_cuda_block_geometry(t, C.byref(e), C.byref(b)) == 0
         assert (e.value, b.value) == (be, bb)
@@ -32,7 +33,7 @@ def test_geometry_matches_ggml_type_rs(lib):
         assert out.value == 4096 // be * bb
     out = C.c_uint64()
     assert lib.hf2q_cuda_row_bytes(12, 4096 + 32, C.byref(out)) == _lib.ERR_INVALID_ARGUMENT
-    assert lib.hf2q_cuda_row_bytes(3, 4096, C.byref(out)) == _lib.ERR_UNSUPPORTED_TYPE   # Q4_1: out of scope
+    assert lib.hf2q_cuda_row_bytes(10, 4096, C.byref(out)) == _lib.ERR_UNSUPPORTED_TYPE   # Q2_K: not on this path
     assert lib.hf2q_cuda_expert_stride(13, 512, 2048, C.byref(out)) == 0 and out.value == 720896
 
 

@@ -36,7 +36,7 @@ def test_dense_ffn_builder(gpu_ctx, t, m):
     assert rel_l2(got - res, want - res) < 3e-3
 
 
-@pytest.mark.parametrize("t", list(oracle.ALL_TYPES))
+@pytest.mark.parametrize("t", list(oracle.MAIN_TYPES))
 @pytest.mark.parametrize("bf16", [False, True])
 def test_dense_ffn_fused_launches_equal_the_separate_ops(gpu_ctx, t, bf16):
     """gate/up with the SwiGLU epilogue and down with the residual epilogue: the same arithmetic in the
@@ -79,6 +79,11 @@ def test_dense_ffn_fused_launches_equal_the_separate_ops(gpu_ctx, t, bf16):
 
 def test_swiglu_fusion_declines_what_does_not_fit_one_launch(gpu_ctx):
     from hf2q_b200 import ops
+    # the 32-element fall-back formats have no fused form; the builder then issues the separate ops
+    for tf in (oracle.Q4_1, oracle.Q5_0, oracle.Q5_1, oracle.IQ4_NL):
+        wf = hq.load_quant_weight(gpu_ctx, make_quant_weight(tf, 32, 2048, seed=tf), tf, 32, 2048)
+        assert not ops.quantized_matmul_swiglu_supported(gpu_ctx, 1, wf, torch.bfloat16)
+        assert not ops.quantized_matmul_add_supported(gpu_ctx, wf, torch.float32)
     t = oracle.Q6_K
     long_rows = hq.load_quant_weight(gpu_ctx, make_quant_weight(t, 32, 14336, seed=1), t, 32, 14336)
     assert ops.quantized_matmul_swiglu_supported(gpu_ctx, 1, long_rows, torch.bfloat16)

@@ -66,7 +66,7 @@ def test_dequant_bit_exact_all_f16_scales(gpu_ctx, t):
     off = 208 if t == oracle.Q6_K else 0
     raw[:, off] = h & 0xFF
     raw[:, off + 1] = h >> 8
-    if t in (oracle.Q4_K, oracle.Q5_K):
+    if t in (oracle.Q4_K, oracle.Q5_K, oracle.Q4_1, oracle.Q5_1):       # the second f16 field (dmin / m)
         raw[:, 2] = h[::-1] & 0xFF
         raw[:, 3] = h[::-1] >> 8
     w = hq.load_quant_weight(gpu_ctx, raw.reshape(-1), t, h.size // 8, 8 * be)
@@ -361,8 +361,8 @@ def test_invalid_arguments_are_errors_not_fallbacks(gpu_ctx):
     with pytest.raises(hq.Hf2qError):      # f16 activations are not part of the op surface
         hq.quantized_matmul_ggml(gpu_ctx, x.half(), w, y, w.matmul_params(1))
     lib = _lib.load()
-    rc = lib.hf2q_cuda_qmatmul(gpu_ctx._h, None, x.data_ptr(), 0, w.ptr, y.data_ptr(), 1, n, k, 3, None, 0)
-    assert rc == _lib.ERR_UNSUPPORTED_TYPE     # Q4_1
+    rc = lib.hf2q_cuda_qmatmul(gpu_ctx._h, None, x.data_ptr(), 0, w.ptr, y.data_ptr(), 1, n, k, 10, None, 0)
+    assert rc == _lib.ERR_UNSUPPORTED_TYPE     # Q2_K: not on this path
     rc = lib.hf2q_cuda_qmatmul(gpu_ctx._h, None, x.data_ptr(), 0, w.ptr, y.data_ptr(), 1, n, k + 32, t, None, 0)
     assert rc == _lib.ERR_INVALID_ARGUMENT
     with pytest.raises(hq.Hf2qError):

@@ -13,7 +13,8 @@ from tests.util import FIXTURES, make_weight_f32, random_finite_blocks, reencode
 GOLDEN = Path(__file__).resolve().parent / "golden"
 # per-format reconstruction bounds of dequant(expected) vs input on the fixtures (abs, rel-L2)
 BOUNDS = {oracle.Q4_0: (0.12, 0.068), oracle.Q8_0: (0.0043, 0.0038), oracle.Q4_K: (0.107, 0.057),
-          oracle.Q5_K: (0.045, 0.028), oracle.Q6_K: (0.036, 0.014)}
+          oracle.Q5_K: (0.045, 0.028), oracle.Q6_K: (0.036, 0.014), oracle.Q4_1: (0.065, 0.058),
+          oracle.Q5_0: (0.058, 0.031), oracle.Q5_1: (0.033, 0.029), oracle.IQ4_NL: (0.079, 0.061)}
 
 
 def _load(t, variant):
@@ -25,7 +26,7 @@ def _load(t, variant):
 
 def test_manifest_matches():
     man = json.loads((GOLDEN / "MANIFEST.json").read_text())
-    assert len(man) == 20
+    assert len(man) == 36
     for fn, sha in man.items():
         assert hashlib.sha256((GOLDEN / "ggml_quants" / fn).read_bytes()).hexdigest() == sha, fn
 
@@ -125,7 +126,8 @@ def test_requantizing_dequantized_values_returns_the_same_bytes_for_symmetric_fo
     y2 = oracle.dequantize(t, oracle.quantize(t, y, 1024))
     # the quantizer's scale search may pick another scale for already-quantised data, so compare
     # values: the round trip must not move any element by more than half a quantisation step
-    step = np.abs(y).max() / {oracle.Q4_0: 7, oracle.Q8_0: 127, oracle.Q4_K: 15, oracle.Q5_K: 31, oracle.Q6_K: 31}[t]
+    step = np.abs(y).max() / {oracle.Q4_0: 7, oracle.Q8_0: 127, oracle.Q4_K: 15, oracle.Q5_K: 31, oracle.Q6_K: 31,
+                              oracle.Q4_1: 7, oracle.Q5_0: 15, oracle.Q5_1: 15, oracle.IQ4_NL: 4}[t]
     assert np.abs(y2 - y).max() <= step
 
 

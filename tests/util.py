@@ -12,7 +12,8 @@ import numpy as np
 import oracle
 
 FIXTURES = {oracle.Q4_0: ("q4_0", 64), oracle.Q8_0: ("q8_0", 64), oracle.Q4_K: ("q4_k", 512),
-            oracle.Q5_K: ("q5_k", 512), oracle.Q6_K: ("q6_k", 512)}
+            oracle.Q5_K: ("q5_k", 512), oracle.Q6_K: ("q6_k", 512), oracle.Q4_1: ("q4_1", 64),
+            oracle.Q5_0: ("q5_0", 64), oracle.Q5_1: ("q5_1", 64), oracle.IQ4_NL: ("iq4_nl", 64)}
 
 
 def make_weight_f32(n: int, k: int, seed: int, sigma: float = 0.02) -> np.ndarray:
@@ -52,7 +53,8 @@ def random_finite_blocks(t: int, nblocks: int, seed: int) -> np.ndarray:
     be, bb = oracle.block_geometry(t)
     rng = np.random.default_rng(seed)
     raw = rng.integers(0, 256, size=(nblocks, bb), dtype=np.uint8)
-    offs = {oracle.Q4_0: [0], oracle.Q8_0: [0], oracle.Q4_K: [0, 2], oracle.Q5_K: [0, 2], oracle.Q6_K: [208]}[t]
+    offs = {oracle.Q4_0: [0], oracle.Q8_0: [0], oracle.Q4_K: [0, 2], oracle.Q5_K: [0, 2], oracle.Q6_K: [208],
+            oracle.Q4_1: [0, 2], oracle.Q5_0: [0], oracle.Q5_1: [0, 2], oracle.IQ4_NL: [0]}[t]
     for o in offs:
         hi = raw[:, o + 1]
         bad = (hi & 0x7C) == 0x7C
@@ -76,6 +78,17 @@ def stored_codes(t: int, raw: np.ndarray) -> np.ndarray:
         return np.concatenate([qs & 15, qs >> 4], axis=1).astype(np.int32)
     if t == oracle.Q8_0:
         return b[:, 2:34].view(np.int8).astype(np.int32)
+    if t in (oracle.Q4_1, oracle.IQ4_NL):
+        qs = b[:, 4:20] if t == oracle.Q4_1 else b[:, 2:18]
+        return np.concatenate([qs & 15, qs >> 4], axis=1).astype(np.int32)
+    if t in (oracle.Q5_0, oracle.Q5_1):
+        o = 2 if t == oracle.Q5_0 else 4
+        qh = np.ascontiguousarray(b[:, o:o + 4]).view("<u4").astype(np.int64).reshape(-1, 1)
+        qs = b[:, o + 4:o + 20].astype(np.int32)
+        j = np.arange(16)
+        lo = (qs & 15) | ((((qh >> j) & 1) << 4).astype(np.int32))
+        hi = (qs >> 4) | ((((qh >> (j + 16)) & 1) << 4).astype(np.int32))
+        return np.concatenate([lo, hi], axis=1).astype(np.int32)
     if t in (oracle.Q4_K, oracle.Q5_K):
         qs = (b[:, 16:144] if t == oracle.Q4_K else b[:, 48:176]).reshape(nb, 4, 32)
         lo, hi = (qs & 15).astype(np.int32), (qs >> 4).astype(np.int32)
@@ -135,6 +148,30 @@ def reencode_codes(t: int, raw: np.ndarray, y: np.ndarray):
         hi = 15 if t == oracle.Q4_K else 31
         valid = dd != 0
         return np.clip(np.where(valid, q, 0), 0, hi).astype(np.int32), valid
+    if t in (oracle.Q4_1, oracle.Q5_1):
+        # make_qkx3_quants (common.rs:339-343): L = clamp(nearest_int((x - min) / scale), 0, nmax) with the stored f16 d and m
+        d = _f16_field(b[:, 0:2])[:, None]
+        m = _f16_field(b[:, 2:4])[:, None]
+        with np.errstate(divide="ignore", invalid="ignore"):
+            q = np.rint(((y - m).astype(np.float32) / d).astype(np.float32))
+        valid = np.broadcast_to(d != 0, q.shape)
+        return np.clip(np.where(valid, q, 0), 0, 15 if t == oracle.Q4_1 else 31).astype(np.int32), valid
+    if t == oracle.Q5_0:
+        # q5_0.rs:80-100: q = min(31, trunc(x / d + 16.5)) with the stored f16 d
+        d = _f16_field(b[:, 0:2])[:, None]
+        with np.errstate(divide="ignore"):
+            inv = np.where(d != 0, one / d, np.float32(0.0)).astype(np.float32)
+        v = ((y * inv).astype(np.float32) + np.float32(16.5)).astype(np.float32)
+        return np.minimum(31, np.trunc(v)).astype(np.int32), np.broadcast_to(d != 0, v.shape)
+    if t == oracle.IQ4_NL:
+        # iq4_nl.rs final pass: L = best_index_int8(values, x / d): the nearest codebook entry
+        kv = np.array([-127, -104, -83, -65, -49, -35, -22, -10, 1, 13, 25, 38, 53, 69, 89, 113], np.float32)
+        d = _f16_field(b[:, 0:2])[:, None]
+        with np.errstate(divide="ignore"):
+            inv = np.where(d != 0, one / d, np.float32(0.0)).astype(np.float32)
+        v = (y * inv).astype(np.float32)
+        codes = np.abs(v[:, :, None] - kv[None, None, :]).argmin(axis=2).astype(np.int32)
+        return codes, np.broadcast_to(d != 0, codes.shape)
     sc = b[:, 192:208].view(np.int8).astype(np.float32)
     d = _f16_field(b[:, 208:210])[:, None]
     dd = np.repeat((d * sc).astype(np.float32), 16, axis=1)
