@@ -59,6 +59,15 @@ SIGNATURES = {
     "hf2q_cuda_silu_mul": (i32, [vp, vp, vp, vp, vp, u64]),
     "hf2q_cuda_moe_combine": (i32, [vp, vp, vp, vp, vp, vp, vp, vp, u32, u32, u32]),
     "hf2q_cuda_rowdot": (i32, [vp, vp, vp, vp, vp, u32, u32]),
+    "hf2q_cuda_kv_cache_bytes": (i32, [u32, u32, u32, C.POINTER(u64), C.POINTER(u64)]),
+    "hf2q_cuda_get_rows": (i32, [vp, vp, vp, u32, u32, u32, vp, u32, vp]),
+    "hf2q_cuda_rms_norm": (i32, [vp, vp, vp, vp, vp, C.c_float, vp, u32, u32, u32]),
+    "hf2q_cuda_rope_kv_append": (i32, [vp, vp, vp, u32, u32, C.c_float, vp, vp]),
+    "hf2q_cuda_attn_decode_scratch_bytes": (i32, [vp, u32, u32, C.POINTER(u64)]),
+    "hf2q_cuda_attn_decode": (i32, [vp, vp, vp, u32, vp, vp, vp, u32, vp, u64]),
+    "hf2q_cuda_attn_prefill": (i32, [vp, vp, vp, u32, u32, vp, u32, vp, u32]),
+    "hf2q_cuda_argmax": (i32, [vp, vp, vp, u32, vp, vp]),
+    "hf2q_cuda_add": (i32, [vp, vp, vp, vp, u64]),
     "hf2q_cuda_launch_count": (u64, [vp]),
     "hf2q_cuda_sm_count": (i32, [vp]),
     "hf2q_cuda_version": (C.c_char_p, []),

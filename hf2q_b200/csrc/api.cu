@@ -864,6 +864,140 @@ HF2Q_API int32_t hf2q_cuda_rowdot(hf2q_ctx* ctx, void* stream, const float* x, c
     return HF2Q_OK;
 }
 
+// ---- the glue of a full decoder forward: embedding rows, RMSNorm, rotary + 8-bit KV append, attention, arg-max ----
+
+namespace {
+uint32_t attn_splits(const hf2q_ctx* ctx, uint32_t n_kv) {
+    uint32_t s = n_kv ? static_cast<uint32_t>(2 * ctx->dev.sm_count) / n_kv : 1;
+    return s < 1 ? 1 : s > 64 ? 64 : s;
+}
+int32_t check_kv(hf2q_ctx* ctx, const hf2q_kv_cache* kv, uint32_t n_q, const char* who) {
+    if (!kv || !kv->k_codes || !kv->k_scale || !kv->v_codes || !kv->v_scale) return fail(ctx, HF2Q_ERR_INVALID_ARGUMENT, "%s: null KV cache pointer", who);
+    if (kv->head_dim != 128) return fail(ctx, HF2Q_ERR_INVALID_ARGUMENT, "%s: head_dim %u (the attention kernels take 128)", who, kv->head_dim);
+    const uint32_t g = kv->n_kv_heads ? n_q / kv->n_kv_heads : 0;
+    if (kv->n_kv_heads == 0 || n_q % kv->n_kv_heads || !(g == 1 || g == 2 || g == 4 || g == 8))
+        return fail(ctx, HF2Q_ERR_INVALID_ARGUMENT, "%s: %u query heads over %u KV heads (group size must be 1, 2, 4 or 8)", who, n_q, kv->n_kv_heads);
+    if (kv->max_seq == 0) return fail(ctx, HF2Q_ERR_INVALID_ARGUMENT, "%s: max_seq is zero", who);
+    return HF2Q_OK;
+}
+KvCacheView view_of(const hf2q_kv_cache* kv) {
+    return KvCacheView{static_cast<int8_t*>(kv->k_codes), static_cast<float*>(kv->k_scale), static_cast<int8_t*>(kv->v_codes),
+                       static_cast<float*>(kv->v_scale), kv->max_seq};
+}
+}  // namespace
+
+HF2Q_API int32_t hf2q_cuda_get_rows(hf2q_ctx* ctx, void* stream, const void* w, uint32_t type, uint32_t n_rows, uint32_t k,
+                                    const uint32_t* ids, uint32_t m, float* out) {
+    if (!ctx) return HF2Q_ERR_INVALID_ARGUMENT;
+    if (!w || !ids || !out) return fail(ctx, HF2Q_ERR_INVALID_ARGUMENT, "get_rows: null pointer");
+    const int32_t rc = check_matmul_shape(ctx, type, n_rows, k, "get_rows");
+    if (rc) return rc;
+    if (m == 0) return HF2Q_OK;
+    const BlockGeom g = block_geom(type);
+    DeviceGuard dg(ctx->device);
+    const cudaError_t e = launch_get_rows(type, w, static_cast<uint64_t>(k) / g.elems * g.bytes, n_rows, k, ids, m, out, ctx->status,
+                                          static_cast<cudaStream_t>(stream));
+    if (e != cudaSuccess) return cuda_fail(ctx, e, "get_rows launch");
+    ctx->launches += 1;
+    return HF2Q_OK;
+}
+
+HF2Q_API int32_t hf2q_cuda_rms_norm(hf2q_ctx* ctx, void* stream, float* x, const float* delta, const float* weight, float eps,
+                                    void* out, uint32_t out_dtype, uint32_t m, uint32_t h) {
+    if (!ctx) return HF2Q_ERR_INVALID_ARGUMENT;
+    if (!x || !weight || !out || h == 0) return fail(ctx, HF2Q_ERR_INVALID_ARGUMENT, "rms_norm: null pointer or h == 0");
+    if (out_dtype != HF2Q_DT_F32 && out_dtype != HF2Q_DT_BF16) return fail(ctx, HF2Q_ERR_INVALID_ARGUMENT, "rms_norm: out_dtype %u (want F32 or BF16)", out_dtype);
+    if (m == 0) return HF2Q_OK;
+    DeviceGuard dg(ctx->device);
+    const cudaError_t e = launch_rms_norm(x, delta, weight, eps, out, out_dtype, m, h, static_cast<cudaStream_t>(stream));
+    if (e != cudaSuccess) return cuda_fail(ctx, e, "rms_norm launch");
+    ctx->launches += 1;
+    return HF2Q_OK;
+}
+
+HF2Q_API int32_t hf2q_cuda_kv_cache_bytes(uint32_t n_kv_heads, uint32_t head_dim, uint32_t max_seq, uint64_t* codes_bytes, uint64_t* scale_bytes) {
+    if (!codes_bytes || !scale_bytes) return HF2Q_ERR_INVALID_ARGUMENT;
+    *codes_bytes = static_cast<uint64_t>(n_kv_heads) * max_seq * head_dim;
+    *scale_bytes = static_cast<uint64_t>(n_kv_heads) * max_seq * 4;
+    return HF2Q_OK;
+}
+
+HF2Q_API int32_t hf2q_cuda_rope_kv_append(hf2q_ctx* ctx, void* stream, float* qkv, uint32_t m, uint32_t n_q_heads, float theta,
+                                          const uint32_t* pos, const hf2q_kv_cache* kv) {
+    if (!ctx) return HF2Q_ERR_INVALID_ARGUMENT;
+    if (!qkv || !pos) return fail(ctx, HF2Q_ERR_INVALID_ARGUMENT, "rope_kv_append: null pointer");
+    const int32_t rc = check_kv(ctx, kv, n_q_heads, "rope_kv_append");
+    if (rc) return rc;
+    if (m == 0) return HF2Q_OK;
+    DeviceGuard dg(ctx->device);
+    const cudaError_t e = launch_rope_kv_append(qkv, m, n_q_heads, kv->n_kv_heads, kv->head_dim, pos, theta, view_of(kv), ctx->status,
+                                                static_cast<cudaStream_t>(stream));
+    if (e != cudaSuccess) return cuda_fail(ctx, e, "rope_kv_append launch");
+    ctx->launches += 1;
+    return HF2Q_OK;
+}
+
+HF2Q_API int32_t hf2q_cuda_attn_decode_scratch_bytes(hf2q_ctx* ctx, uint32_t n_q_heads, uint32_t n_kv_heads, uint64_t* out) {
+    if (!ctx || !out || n_kv_heads == 0) return HF2Q_ERR_INVALID_ARGUMENT;
+    *out = attn_decode_scratch_bytes(n_kv_heads, n_q_heads / n_kv_heads, attn_splits(ctx, n_kv_heads));
+    return HF2Q_OK;
+}
+
+HF2Q_API int32_t hf2q_cuda_attn_decode(hf2q_ctx* ctx, void* stream, const float* q, uint32_t n_q_heads, const hf2q_kv_cache* kv,
+                                       const uint32_t* pos, void* out, uint32_t out_dtype, void* scratch, uint64_t scratch_bytes) {
+    if (!ctx) return HF2Q_ERR_INVALID_ARGUMENT;
+    if (!q || !pos || !out || !scratch) return fail(ctx, HF2Q_ERR_INVALID_ARGUMENT, "attn_decode: null pointer");
+    const int32_t rc = check_kv(ctx, kv, n_q_heads, "attn_decode");
+    if (rc) return rc;
+    const uint32_t splits = attn_splits(ctx, kv->n_kv_heads);
+    if (scratch_bytes < attn_decode_scratch_bytes(kv->n_kv_heads, n_q_heads / kv->n_kv_heads, splits))
+        return fail(ctx, HF2Q_ERR_WORKSPACE, "attn_decode: scratch of %llu bytes is too small (ask hf2q_cuda_attn_decode_scratch_bytes)", (unsigned long long)scratch_bytes);
+    DeviceGuard dg(ctx->device);
+    const cudaError_t e = launch_attn_decode(q, n_q_heads, kv->n_kv_heads, kv->head_dim, view_of(kv), pos, out, out_dtype,
+                                             static_cast<float*>(scratch), splits, static_cast<cudaStream_t>(stream));
+    if (e != cudaSuccess) return cuda_fail(ctx, e, "attn_decode launch");
+    ctx->launches += 2;
+    return HF2Q_OK;
+}
+
+HF2Q_API int32_t hf2q_cuda_attn_prefill(hf2q_ctx* ctx, void* stream, const float* qkv, uint32_t m, uint32_t n_q_heads,
+                                        const hf2q_kv_cache* kv, uint32_t pos0, void* out, uint32_t out_dtype) {
+    if (!ctx) return HF2Q_ERR_INVALID_ARGUMENT;
+    if (!qkv || !out) return fail(ctx, HF2Q_ERR_INVALID_ARGUMENT, "attn_prefill: null pointer");
+    const int32_t rc = check_kv(ctx, kv, n_q_heads, "attn_prefill");
+    if (rc) return rc;
+    if (static_cast<uint64_t>(pos0) + m > kv->max_seq) return fail(ctx, HF2Q_ERR_INVALID_ARGUMENT, "attn_prefill: positions %u..%u exceed max_seq %u", pos0, pos0 + m, kv->max_seq);
+    if (m == 0) return HF2Q_OK;
+    DeviceGuard dg(ctx->device);
+    const uint32_t stride = (n_q_heads + 2 * kv->n_kv_heads) * kv->head_dim;
+    const cudaError_t e = launch_attn_prefill(qkv, stride, m, n_q_heads, kv->n_kv_heads, kv->head_dim, view_of(kv), pos0, out, out_dtype,
+                                              n_q_heads * kv->head_dim, static_cast<cudaStream_t>(stream));
+    if (e != cudaSuccess) return cuda_fail(ctx, e, "attn_prefill launch");
+    ctx->launches += 1;
+    return HF2Q_OK;
+}
+
+HF2Q_API int32_t hf2q_cuda_argmax(hf2q_ctx* ctx, void* stream, const float* logits, uint32_t n, uint32_t* out_id, uint32_t* pos) {
+    if (!ctx) return HF2Q_ERR_INVALID_ARGUMENT;
+    if (!logits || !out_id || n == 0) return fail(ctx, HF2Q_ERR_INVALID_ARGUMENT, "argmax: null pointer or n == 0");
+    DeviceGuard dg(ctx->device);
+    const cudaError_t e = launch_argmax(logits, n, out_id, pos, static_cast<cudaStream_t>(stream));
+    if (e != cudaSuccess) return cuda_fail(ctx, e, "argmax launch");
+    ctx->launches += 1;
+    return HF2Q_OK;
+}
+
+HF2Q_API int32_t hf2q_cuda_add(hf2q_ctx* ctx, void* stream, float* x, const float* delta, uint64_t n) {
+    if (!ctx) return HF2Q_ERR_INVALID_ARGUMENT;
+    if (!x || !delta) return fail(ctx, HF2Q_ERR_INVALID_ARGUMENT, "add: null pointer");
+    if (n == 0) return HF2Q_OK;
+    DeviceGuard dg(ctx->device);
+    const cudaError_t e = launch_add(x, delta, n, ctx->dev.sm_count, static_cast<cudaStream_t>(stream));
+    if (e != cudaSuccess) return cuda_fail(ctx, e, "add launch");
+    ctx->launches += 1;
+    return HF2Q_OK;
+}
+
 HF2Q_API uint64_t hf2q_cuda_launch_count(const hf2q_ctx* ctx) { return ctx ? ctx->launches : 0; }
 HF2Q_API int32_t hf2q_cuda_sm_count(const hf2q_ctx* ctx) { return ctx ? ctx->dev.sm_count : 0; }
 

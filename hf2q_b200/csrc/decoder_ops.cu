@@ -1,0 +1,531 @@
+// The kernels that sit between the quantized products in a decoder forward pass: embedding row
+// look-up, RMSNorm (with the residual add), rotary position embedding fused with the append to an
+// 8-bit KV cache, attention over that cache (decode: split over the context; prefill: tiled), and
+// the greedy arg-max.  Together with the products they make the forward of
+// Qwen35Model::forward_gpu_greedy (src/inference/models/qwen35/forward_gpu.rs:4140) on Llama-shaped
+// layers; the arithmetic follows the reference's scalar specs: rms_norm_rows
+// (src/inference/models/qwen35/forward_cpu.rs:36-48), residual_add (:51-56), the causal softmax
+// attention of gated_full_attention_cpu_ref (full_attn.rs:219-360, without its output gate and with
+// the plain rotary embedding of the Llama architecture), embed_tokens / apply_output_head
+// (io_heads.rs).
+//
+// KV cache.  The reference keeps K and V as one byte per element plus one f32 norm per (head,
+// position) (TqFullAttnKvBuffers, kv_cache.rs:1982-2012); its byte is an index into a 256-entry
+// Lloyd-Max codebook that lives in the external mlx-native crate.  That codebook is not available,
+// so the byte here is a signed 8-bit integer and the f32 per (head, position) is the scale
+// amax / 127: same layout, same bytes per position, a linear code instead of the codebook.
+//   k_codes, v_codes : int8  [n_kv_heads][max_seq][head_dim]
+//   k_scale, v_scale : float [n_kv_heads][max_seq]
+#include <math_constants.h>
+
+#include "common.cuh"
+#include "kernels.h"
+
+namespace hf2q {
+namespace {
+
+// ------------------------------------------------------------------ embedding rows
+template <uint32_t TYPE>
+__global__ void __launch_bounds__(256) get_rows_kernel(const uint8_t* __restrict__ w, uint64_t row_bytes, uint32_t n_rows,
+                                                       uint32_t k, const uint32_t* __restrict__ ids, float* __restrict__ out,
+                                                       uint32_t* status) {
+    constexpr BlockGeom G = block_geom(TYPE);
+    const uint32_t t = blockIdx.x;
+    uint32_t id = ids[t];
+    if (id >= n_rows) {                                   // out of range: zero row, flagged
+        if (threadIdx.x == 0) atomicOr(status, STATUS_BAD_EXPERT_ID);
+        for (uint32_t e = threadIdx.x; e < k; e += 256) out[static_cast<size_t>(t) * k + e] = 0.f;
+        return;
+    }
+    const uint8_t* row = w + static_cast<uint64_t>(id) * row_bytes;
+    for (uint32_t e = threadIdx.x; e < k; e += 256)
+        out[static_cast<size_t>(t) * k + e] = dequant_elem<TYPE>(row + (e / G.elems) * G.bytes, static_cast<int>(e % G.elems));
+}
+
+// ------------------------------------------------------------------ RMSNorm (+ residual add)
+// x[t,:] += delta[t,:] (if delta), then out[t,:] = x[t,:] * rsqrt(mean(x^2) + eps) * weight[:]
+// (forward_cpu.rs:36-48: sum of squares in f32, sequential per row there, tree-reduced here).
+template <typename OUT>
+__global__ void __launch_bounds__(1024) rms_norm_kernel(float* __restrict__ x, const float* __restrict__ delta,
+                                                        const float* __restrict__ weight, float eps, OUT* __restrict__ out,
+                                                        uint32_t h) {
+    __shared__ float part[32];
+    float* row = x + static_cast<size_t>(blockIdx.x) * h;
+    const float* drow = delta ? delta + static_cast<size_t>(blockIdx.x) * h : nullptr;
+    OUT* orow = out + static_cast<size_t>(blockIdx.x) * h;
+    float ss = 0.f;
+    for (uint32_t i = threadIdx.x; i < h; i += blockDim.x) {
+        float v = row[i];
+        if (drow) { v += drow[i]; row[i] = v; }
+        ss += v * v;
+    }
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    if (threadIdx.x < 32) {
+        float v = threadIdx.x < (blockDim.x >> 5) ? part[threadIdx.x] : 0.f;
+        for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+        if (threadIdx.x == 0) part[0] = 1.0f / sqrtf(v / static_cast<float>(h) + eps);
+    }
+    __syncthreads();
+    const float inv = part[0];
+    for (uint32_t i = threadIdx.x; i < h; i += blockDim.x) {
+        const float v = row[i] * inv * weight[i];
+        if constexpr (sizeof(OUT) == 4) orow[i] = v;
+        else orow[i] = __float2bfloat16_rn(v);
+    }
+}
+
+// ------------------------------------------------------------------ rotary embedding + KV append
+// qkv: [m][(n_q + 2 n_kv) * hd] f32 (fused QKV product).  Token t sits at position *pos + t.
+// One warp per (token, head).  q heads are rotated in place and scaled by `q_scale` (1/sqrt(hd), so
+// the attention kernels need no multiply); k heads are rotated, then k and v heads are quantized
+// to int8 with one scale per (head, position) and stored in the cache.  Pairs are (2i, 2i+1) with
+// angle pos * theta^(-2i/hd) -- the rotary form of the Llama architecture.
+__global__ void __launch_bounds__(256) rope_kv_append_kernel(float* __restrict__ qkv, uint32_t m, uint32_t n_q, uint32_t n_kv,
+                                                             uint32_t hd, const uint32_t* __restrict__ pos_dev, float theta,
+                                                             float q_scale, int8_t* __restrict__ k_codes, float* __restrict__ k_scale,
+                                                             int8_t* __restrict__ v_codes, float* __restrict__ v_scale,
+                                                             uint32_t max_seq, uint32_t* status) {
+    const uint32_t heads = n_q + 2 * n_kv;
+    const uint32_t wid = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (wid >= m * heads) return;
+    const uint32_t t = wid / heads, hidx = wid % heads;
+    const uint32_t pos = *pos_dev + t;
+    float* v = qkv + static_cast<size_t>(t) * heads * hd + static_cast<size_t>(hidx) * hd;
+    const bool is_q = hidx < n_q, is_k = !is_q && hidx < n_q + n_kv;
+    // hd <= 256: each lane owns up to 4 consecutive pairs
+    float vals[8];
+    const uint32_t per = hd / 32;                        // elements per lane (hd = 64, 128 or 256)
+    float amax = 0.f;
+    for (uint32_t j = 0; j < per; j += 2) {
+        const uint32_t e = lane * per + j;
+        float a = v[e], b = v[e + 1];
+        if (is_q || is_k) {
+            const float freq = powf(theta, -static_cast<float>(e) / static_cast<float>(hd));
+            float sn, cs;
+            sincosf(static_cast<float>(pos) * freq, &sn, &cs);
+            const float ra = a * cs - b * sn, rb = a * sn + b * cs;
+            a = ra; b = rb;
+        }
+        if (is_q) { a *= q_scale; b *= q_scale; v[e] = a; v[e + 1] = b; }
+        vals[j] = a; vals[j + 1] = b;
+        amax = fmaxf(amax, fmaxf(fabsf(a), fabsf(b)));
+    }
+    if (is_q) return;
+    if (pos >= max_seq) { if (lane == 0) atomicOr(status, STATUS_BAD_EXPERT_ID); return; }
+    for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    const float scale = amax / 127.0f, inv = amax > 0.f ? 127.0f / amax : 0.f;
+    const uint32_t kvh = is_k ? hidx - n_q : hidx - n_q - n_kv;
+    int8_t* codes = (is_k ? k_codes : v_codes) + (static_cast<size_t>(kvh) * max_seq + pos) * hd;
+    for (uint32_t j = 0; j < per; ++j) codes[lane * per + j] = static_cast<int8_t>(__float2int_rn(vals[j] * inv));
+    if (lane == 0) (is_k ? k_scale : v_scale)[static_cast<size_t>(kvh) * max_seq + pos] = scale;
+}
+
+// ------------------------------------------------------------------ decode attention, split over the context
+// grid (n_kv_heads, n_splits); one CTA handles the G = n_q / n_kv query heads of its KV head over
+// positions [lo, hi) of the n_ctx = *pos + 1 cached positions.  hd == 128, G <= 8.
+// Scores: a warp takes 32 positions at a time, lane = position: the lane walks its K row (128 int8)
+// against the G query vectors in shared memory.  Values: lane = 4 dims; the warp walks the 32
+// positions with their probabilities from shared memory.  Each CTA leaves (max, sum, acc[G][128]) of
+// its range in scratch; attn_combine_kernel merges the splits.
+constexpr int ATT_WARPS = 8;
+constexpr int ATT_HD = 128;
+constexpr int ATT_MAXG = 8;
+
+__device__ __forceinline__ float4 s8x4_to_float4(uint32_t w) {
+    return make_float4(byte_to_float<128>(w ^ 0x80808080u, 0), byte_to_float<128>(w ^ 0x80808080u, 1),
+                       byte_to_float<128>(w ^ 0x80808080u, 2), byte_to_float<128>(w ^ 0x80808080u, 3));
+}
+
+template <int G>
+__global__ void __launch_bounds__(ATT_WARPS * 32) attn_decode_kernel(const float* __restrict__ q, uint32_t q_stride_heads,
+                                                                     const int8_t* __restrict__ k_codes, const float* __restrict__ k_scale,
+                                                                     const int8_t* __restrict__ v_codes, const float* __restrict__ v_scale,
+                                                                     uint32_t max_seq, const uint32_t* __restrict__ pos_dev,
+                                                                     float* __restrict__ part /* [n_kv][splits][G][2 + 128] */) {
+    __shared__ __align__(16) float qs[G][ATT_HD];
+    __shared__ float ps[ATT_WARPS][G][32];
+    __shared__ float red_m[ATT_WARPS][G], red_l[ATT_WARPS][G];
+    __shared__ __align__(16) float red_acc[ATT_WARPS][G][ATT_HD];
+    (void)q_stride_heads;
+    const uint32_t kvh = blockIdx.x, split = blockIdx.y, nsplit = gridDim.y;
+    const uint32_t n_ctx = *pos_dev + 1;
+    const uint32_t chunk = (n_ctx + nsplit - 1) / nsplit;
+    const uint32_t lo = min(split * chunk, n_ctx), hi = min(lo + chunk, n_ctx);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    for (uint32_t i = threadIdx.x; i < G * ATT_HD; i += ATT_WARPS * 32)
+        qs[i / ATT_HD][i % ATT_HD] = q[(static_cast<size_t>(kvh) * G + i / ATT_HD) * ATT_HD + i % ATT_HD];
+    __syncthreads();
+    const int8_t* kc = k_codes + static_cast<size_t>(kvh) * max_seq * ATT_HD;
+    const int8_t* vc = v_codes + static_cast<size_t>(kvh) * max_seq * ATT_HD;
+    const float* ksc = k_scale + static_cast<size_t>(kvh) * max_seq;
+    const float* vsc = v_scale + static_cast<size_t>(kvh) * max_seq;
+
+    float mx[G], l[G], acc[G][4];
+#pragma unroll
+    for (int g = 0; g < G; ++g) { mx[g] = -CUDART_INF_F; l[g] = 0.f; acc[g][0] = acc[g][1] = acc[g][2] = acc[g][3] = 0.f; }
+
+    for (uint32_t p0 = lo + warp * 32; p0 < hi; p0 += ATT_WARPS * 32) {
+        const uint32_t p = p0 + lane;
+        const bool live = p < hi;
+        float s[G];
+#pragma unroll
+        for (int g = 0; g < G; ++g) s[g] = 0.f;
+        if (live) {
+            const uint4* kr = reinterpret_cast<const uint4*>(kc + static_cast<size_t>(p) * ATT_HD);
+#pragma unroll
+            for (int c = 0; c < ATT_HD / 16; ++c) {
+                const uint4 kv = __ldcs(kr + c);
+                const uint32_t kw[4] = {kv.x, kv.y, kv.z, kv.w};
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const float4 kf = s8x4_to_float4(kw[j]);
+#pragma unroll
+                    for (int g = 0; g < G; ++g) {
+                        const float4 qv = *reinterpret_cast<const float4*>(&qs[g][16 * c + 4 * j]);
+                        s[g] += kf.x * qv.x + kf.y * qv.y + kf.z * qv.z + kf.w * qv.w;
+                    }
+                }
+            }
+            const float sc = ksc[p];
+#pragma unroll
+            for (int g = 0; g < G; ++g) s[g] *= sc;
+        }
+        // online softmax over this batch of 32 positions; the V scale is folded into the probability
+        const float vs = live ? vsc[p] : 0.f;
+#pragma unroll
+        for (int g = 0; g < G; ++g) {
+            float bm = live ? s[g] : -CUDART_INF_F;
+            for (int o = 16; o > 0; o >>= 1) bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, o));
+            const float nm = fmaxf(mx[g], bm);
+            const float corr = __expf(mx[g] - nm);             // exp(-inf) = 0 on the first batch
+            const float pr = live ? __expf(s[g] - nm) : 0.f;
+            float bs = pr;
+            for (int o = 16; o > 0; o >>= 1) bs += __shfl_xor_sync(0xffffffffu, bs, o);
+            l[g] = l[g] * corr + bs;
+            mx[g] = nm;
+            acc[g][0] *= corr; acc[g][1] *= corr; acc[g][2] *= corr; acc[g][3] *= corr;
+            ps[warp][g][lane] = pr * vs;
+        }
+        __syncwarp();
+        const uint32_t cnt = min(32u, hi - p0);
+        for (uint32_t i = 0; i < cnt; ++i) {
+            const uint32_t vw = __ldcs(reinterpret_cast<const uint32_t*>(vc + static_cast<size_t>(p0 + i) * ATT_HD) + lane);
+            const float4 vf = s8x4_to_float4(vw);
+#pragma unroll
+            for (int g = 0; g < G; ++g) {
+                const float pw = ps[warp][g][i];
+                acc[g][0] += pw * vf.x; acc[g][1] += pw * vf.y; acc[g][2] += pw * vf.z; acc[g][3] += pw * vf.w;
+            }
+        }
+        __syncwarp();
+    }
+    // merge the warps of this CTA
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+        if (lane == 0) { red_m[warp][g] = mx[g]; red_l[warp][g] = l[g]; }
+        *reinterpret_cast<float4*>(&red_acc[warp][g][4 * lane]) = make_float4(acc[g][0], acc[g][1], acc[g][2], acc[g][3]);
+    }
+    __syncthreads();
+    for (uint32_t i = threadIdx.x; i < G * ATT_HD; i += ATT_WARPS * 32) {
+        const int g = i / ATT_HD, d = i % ATT_HD;
+        float m_all = -CUDART_INF_F;
+        for (int w = 0; w < ATT_WARPS; ++w) m_all = fmaxf(m_all, red_m[w][g]);
+        float l_all = 0.f, a = 0.f;
+        for (int w = 0; w < ATT_WARPS; ++w) {
+            const float c = red_m[w][g] == -CUDART_INF_F ? 0.f : __expf(red_m[w][g] - m_all);
+            l_all += red_l[w][g] * c;
+            a += red_acc[w][g][d] * c;
+        }
+        float* dst = part + ((static_cast<size_t>(kvh) * nsplit + split) * G + g) * (2 + ATT_HD);
+        if (d == 0) { dst[0] = m_all; dst[1] = l_all; }
+        dst[2 + d] = a;
+    }
+}
+
+// out[head][d] = sum over splits, renormalised.  grid = n_q heads, block = 128.
+template <typename OUT>
+__global__ void __launch_bounds__(ATT_HD) attn_combine_kernel(const float* __restrict__ part, uint32_t nsplit, uint32_t G,
+                                                              OUT* __restrict__ out) {
+    const uint32_t head = blockIdx.x, kvh = head / G, g = head % G, d = threadIdx.x;
+    float m_all = -CUDART_INF_F;
+    for (uint32_t s = 0; s < nsplit; ++s) m_all = fmaxf(m_all, part[((static_cast<size_t>(kvh) * nsplit + s) * G + g) * (2 + ATT_HD)]);
+    float l_all = 0.f, a = 0.f;
+    for (uint32_t s = 0; s < nsplit; ++s) {
+        const float* src = part + ((static_cast<size_t>(kvh) * nsplit + s) * G + g) * (2 + ATT_HD);
+        const float c = src[0] == -CUDART_INF_F ? 0.f : __expf(src[0] - m_all);
+        l_all += src[1] * c;
+        a += src[2 + d] * c;
+    }
+    const float v = l_all > 0.f ? a / l_all : 0.f;
+    if constexpr (sizeof(OUT) == 4) out[static_cast<size_t>(head) * ATT_HD + d] = v;
+    else out[static_cast<size_t>(head) * ATT_HD + d] = __float2bfloat16_rn(v);
+}
+
+// ------------------------------------------------------------------ prefill attention (causal, tiled)
+// grid (ceil(m / QT), n_kv_heads); one CTA handles QT = 16 query tokens x the G heads of its KV head
+// (rows r = tok * G + g, up to 128 rows), walking the cached positions [0, pos0 + tok] in tiles of
+// 32: the K / V tile is dequantised into shared memory once and used by all rows.  Thread = one
+// row for the scores (q in registers would need 128 floats; q stays in shared memory and is read as
+// broadcast-free float4s since every thread reads its own row), then thread = (row, 32 dims) for the
+// values.  CUDA cores only: the prefill of the decode benchmark is not the timed part.
+constexpr int PF_QT = 16;
+constexpr int PF_KT = 32;
+
+template <int G, typename OUT>
+__global__ void __launch_bounds__(PF_QT * G * 4) attn_prefill_kernel(const float* __restrict__ qkv, uint32_t row_stride, uint32_t m,
+                                                                     const int8_t* __restrict__ k_codes, const float* __restrict__ k_scale,
+                                                                     const int8_t* __restrict__ v_codes, const float* __restrict__ v_scale,
+                                                                     uint32_t max_seq, uint32_t pos0, OUT* __restrict__ out,
+                                                                     uint32_t out_stride) {
+    constexpr int ROWS = PF_QT * G;                         // (token, head) rows of this CTA
+    constexpr int THREADS = ROWS * 4;
+    extern __shared__ __align__(16) float sm[];
+    float* qs = sm;                                         // [ROWS][128 + 4]
+    float* kt = qs + ROWS * (ATT_HD + 4);                   // [PF_KT][128 + 4]   K tile, later V tile
+    float* pt = kt + PF_KT * (ATT_HD + 4);                  // [ROWS][PF_KT + 1]  probabilities of the tile
+    const uint32_t kvh = blockIdx.y, tok0 = blockIdx.x * PF_QT;
+    const int tid = threadIdx.x;
+    for (int i = tid; i < ROWS * ATT_HD; i += THREADS) {
+        const int r = i / ATT_HD, d = i % ATT_HD;
+        const uint32_t tok = tok0 + r / G;
+        qs[r * (ATT_HD + 4) + d] = tok < m ? qkv[static_cast<size_t>(tok) * row_stride + (static_cast<size_t>(kvh) * G + r % G) * ATT_HD + d] : 0.f;
+    }
+    const int8_t* kc = k_codes + static_cast<size_t>(kvh) * max_seq * ATT_HD;
+    const int8_t* vc = v_codes + static_cast<size_t>(kvh) * max_seq * ATT_HD;
+    const float* ksc = k_scale + static_cast<size_t>(kvh) * max_seq;
+    const float* vsc = v_scale + static_cast<size_t>(kvh) * max_seq;
+    // scores: thread (row = tid / 4, quarter qt = tid % 4) takes the tile's positions 4j + qt, j = 0..7;
+    // values: the same thread takes dims 16i + 4qt .. +3, i = 0..7, of its row (both interleaved so that
+    // the four threads of a row read different shared-memory banks)
+    const int row = tid >> 2, qt = tid & 3;
+    const uint32_t my_tok = tok0 + row / G;
+    const uint32_t my_last = pos0 + my_tok;                 // last visible position of this row (causal)
+    const uint32_t last_tok = min(tok0 + PF_QT, m) - 1;
+    const uint32_t n_pos = pos0 + last_tok + 1;
+    float mx = -CUDART_INF_F, l = 0.f, acc[32];
+#pragma unroll
+    for (int i = 0; i < 32; ++i) acc[i] = 0.f;
+    __syncthreads();
+    for (uint32_t p0 = 0; p0 < n_pos; p0 += PF_KT) {
+        // K tile -> f32 (scaled)
+        for (int i = tid; i < PF_KT * ATT_HD / 4; i += THREADS) {
+            const int pr = i / (ATT_HD / 4), c = i % (ATT_HD / 4);
+            const uint32_t p = p0 + pr;
+            float4 f = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (p < n_pos) {
+                f = s8x4_to_float4(reinterpret_cast<const uint32_t*>(kc + static_cast<size_t>(p) * ATT_HD)[c]);
+                const float sc = ksc[p];
+                f.x *= sc; f.y *= sc; f.z *= sc; f.w *= sc;
+            }
+            *reinterpret_cast<float4*>(&kt[pr * (ATT_HD + 4) + 4 * c]) = f;
+        }
+        __syncthreads();
+        float s[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) s[j] = 0.f;
+        for (int d = 0; d < ATT_HD; d += 4) {
+            const float4 qv = *reinterpret_cast<const float4*>(&qs[row * (ATT_HD + 4) + d]);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const float4 kv = *reinterpret_cast<const float4*>(&kt[(4 * j + qt) * (ATT_HD + 4) + d]);
+                s[j] += qv.x * kv.x + qv.y * kv.y + qv.z * kv.z + qv.w * kv.w;
+            }
+        }
+        float bm = -CUDART_INF_F;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const uint32_t p = p0 + 4 * j + qt;
+            if (p > my_last || my_tok >= m) s[j] = -CUDART_INF_F;
+            bm = fmaxf(bm, s[j]);
+        }
+        bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, 1));
+        bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, 2));
+        const float nm = fmaxf(mx, bm);
+        const float corr = nm == -CUDART_INF_F ? 1.f : __expf(mx - nm);
+        float bs = 0.f;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const float pr = s[j] == -CUDART_INF_F ? 0.f : __expf(s[j] - nm);
+            bs += pr;
+            pt[row * (PF_KT + 1) + 4 * j + qt] = pr;
+        }
+        bs += __shfl_xor_sync(0xffffffffu, bs, 1);
+        bs += __shfl_xor_sync(0xffffffffu, bs, 2);
+        l = l * corr + bs;
+        mx = nm;
+#pragma unroll
+        for (int i = 0; i < 32; ++i) acc[i] *= corr;
+        __syncthreads();                                    // scores done with the K tile; probabilities visible
+        // V tile -> f32 (scaled) into the same buffer
+        for (int i = tid; i < PF_KT * ATT_HD / 4; i += THREADS) {
+            const int pr = i / (ATT_HD / 4), c = i % (ATT_HD / 4);
+            const uint32_t p = p0 + pr;
+            float4 f = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (p < n_pos) {
+                f = s8x4_to_float4(reinterpret_cast<const uint32_t*>(vc + static_cast<size_t>(p) * ATT_HD)[c]);
+                const float sc = vsc[p];
+                f.x *= sc; f.y *= sc; f.z *= sc; f.w *= sc;
+            }
+            *reinterpret_cast<float4*>(&kt[pr * (ATT_HD + 4) + 4 * c]) = f;
+        }
+        __syncthreads();
+        for (int pr = 0; pr < PF_KT; ++pr) {
+            const float pw = pt[row * (PF_KT + 1) + pr];
+#pragma unroll
+            for (int i = 0; i < 32; i += 4) {
+                const float4 vv = *reinterpret_cast<const float4*>(&kt[pr * (ATT_HD + 4) + 4 * i + 4 * qt]);
+                acc[i] += pw * vv.x; acc[i + 1] += pw * vv.y; acc[i + 2] += pw * vv.z; acc[i + 3] += pw * vv.w;
+            }
+        }
+        __syncthreads();
+    }
+    if (my_tok < m) {
+        const float inv = l > 0.f ? 1.0f / l : 0.f;
+        OUT* dst = out + static_cast<size_t>(my_tok) * out_stride + (static_cast<size_t>(kvh) * G + row % G) * ATT_HD;
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+            const int d = 4 * (i & ~3) + 4 * qt + (i & 3);          // acc[i] holds dim 16 * (i / 4) + 4 qt + i % 4
+            if constexpr (sizeof(OUT) == 4) dst[d] = acc[i] * inv;
+            else dst[d] = __float2bfloat16_rn(acc[i] * inv);
+        }
+    }
+}
+
+// ------------------------------------------------------------------ greedy arg-max (+ position advance)
+// One CTA: the index of the largest logit (the lowest index on ties, NaN never wins) goes to
+// *out_id; if pos != nullptr the position counter is advanced by one -- the decode loop's hand-over
+// to the next step, so that a captured step can be replayed without the host.
+__global__ void __launch_bounds__(1024) argmax_kernel(const float* __restrict__ logits, uint32_t n, uint32_t* __restrict__ out_id,
+                                                      uint32_t* __restrict__ pos) {
+    __shared__ float bv[32];
+    __shared__ uint32_t bi[32];
+    float best = -CUDART_INF_F;
+    uint32_t idx = 0xffffffffu;
+    for (uint32_t i = threadIdx.x; i < n; i += blockDim.x) {
+        const float v = logits[i];
+        if (v > best || (idx == 0xffffffffu && v == v)) { best = v; idx = i; }
+    }
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+        const uint32_t oi = __shfl_xor_sync(0xffffffffu, idx, o);
+        if (oi != 0xffffffffu && (idx == 0xffffffffu || ov > best || (ov == best && oi < idx))) { best = ov; idx = oi; }
+    }
+    if ((threadIdx.x & 31) == 0) { bv[threadIdx.x >> 5] = best; bi[threadIdx.x >> 5] = idx; }
+    __syncthreads();
+    if (threadIdx.x < 32) {
+        best = threadIdx.x < (blockDim.x >> 5) ? bv[threadIdx.x] : -CUDART_INF_F;
+        idx = threadIdx.x < (blockDim.x >> 5) ? bi[threadIdx.x] : 0xffffffffu;
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+            const uint32_t oi = __shfl_xor_sync(0xffffffffu, idx, o);
+            if (oi != 0xffffffffu && (idx == 0xffffffffu || ov > best || (ov == best && oi < idx))) { best = ov; idx = oi; }
+        }
+        if (threadIdx.x == 0) {
+            *out_id = idx == 0xffffffffu ? 0u : idx;
+            if (pos) *pos += 1;
+        }
+    }
+}
+
+__global__ void __launch_bounds__(256) add_kernel(float* __restrict__ x, const float* __restrict__ d, uint64_t n) {
+    const uint64_t stride = static_cast<uint64_t>(gridDim.x) * blockDim.x;
+    for (uint64_t i = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride) x[i] += d[i];
+}
+
+}  // namespace
+
+cudaError_t launch_get_rows(uint32_t type, const void* w, uint64_t row_bytes, uint32_t n_rows, uint32_t k, const uint32_t* ids,
+                            uint32_t m, float* out, uint32_t* status, cudaStream_t st) {
+    const uint8_t* wb = static_cast<const uint8_t*>(w);
+    switch (type) {
+#define HF2Q_CASE(T) case T: get_rows_kernel<T><<<m, 256, 0, st>>>(wb, row_bytes, n_rows, k, ids, out, status); break;
+        HF2Q_CASE(HF2Q_TYPE_Q4_0) HF2Q_CASE(HF2Q_TYPE_Q8_0) HF2Q_CASE(HF2Q_TYPE_Q4_K) HF2Q_CASE(HF2Q_TYPE_Q5_K) HF2Q_CASE(HF2Q_TYPE_Q6_K)
+        HF2Q_CASE(HF2Q_TYPE_Q4_1) HF2Q_CASE(HF2Q_TYPE_Q5_0) HF2Q_CASE(HF2Q_TYPE_Q5_1) HF2Q_CASE(HF2Q_TYPE_IQ4_NL)
+#undef HF2Q_CASE
+        default: return cudaErrorInvalidValue;
+    }
+    return cudaGetLastError();
+}
+
+cudaError_t launch_rms_norm(float* x, const float* delta, const float* weight, float eps, void* out, uint32_t out_dtype, uint32_t m,
+                            uint32_t h, cudaStream_t st) {
+    const unsigned threads = h >= 4096 ? 1024 : h >= 1024 ? 512 : 256;
+    if (out_dtype == HF2Q_DT_F32) rms_norm_kernel<float><<<m, threads, 0, st>>>(x, delta, weight, eps, static_cast<float*>(out), h);
+    else if (out_dtype == HF2Q_DT_BF16) rms_norm_kernel<__nv_bfloat16><<<m, threads, 0, st>>>(x, delta, weight, eps, static_cast<__nv_bfloat16*>(out), h);
+    else return cudaErrorInvalidValue;
+    return cudaGetLastError();
+}
+
+cudaError_t launch_rope_kv_append(float* qkv, uint32_t m, uint32_t n_q, uint32_t n_kv, uint32_t hd, const uint32_t* pos, float theta,
+                                  const KvCacheView& kv, uint32_t* status, cudaStream_t st) {
+    const uint32_t warps = m * (n_q + 2 * n_kv);
+    rope_kv_append_kernel<<<(warps + 7) / 8, 256, 0, st>>>(qkv, m, n_q, n_kv, hd, pos, theta, 1.0f / sqrtf(static_cast<float>(hd)),
+                                                            kv.k_codes, kv.k_scale, kv.v_codes, kv.v_scale, kv.max_seq, status);
+    return cudaGetLastError();
+}
+
+size_t attn_decode_scratch_bytes(uint32_t n_kv, uint32_t group, uint32_t n_splits) {
+    return static_cast<size_t>(n_kv) * n_splits * group * (2 + ATT_HD) * sizeof(float);
+}
+
+cudaError_t launch_attn_decode(const float* q, uint32_t n_q, uint32_t n_kv, uint32_t hd, const KvCacheView& kv, const uint32_t* pos,
+                               void* out, uint32_t out_dtype, float* scratch, uint32_t n_splits, cudaStream_t st) {
+    if (hd != ATT_HD || n_kv == 0 || n_q % n_kv || n_q / n_kv > ATT_MAXG) return cudaErrorInvalidValue;
+    const uint32_t G = n_q / n_kv;
+    const dim3 grid(n_kv, n_splits);
+    switch (G) {
+#define HF2Q_CASE(GG) case GG: attn_decode_kernel<GG><<<grid, ATT_WARPS * 32, 0, st>>>(q, n_q, kv.k_codes, kv.k_scale, kv.v_codes, kv.v_scale, kv.max_seq, pos, scratch); break;
+        HF2Q_CASE(1) HF2Q_CASE(2) HF2Q_CASE(4) HF2Q_CASE(8)
+#undef HF2Q_CASE
+        default: return cudaErrorInvalidValue;
+    }
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return e;
+    if (out_dtype == HF2Q_DT_F32) attn_combine_kernel<float><<<n_q, ATT_HD, 0, st>>>(scratch, n_splits, G, static_cast<float*>(out));
+    else if (out_dtype == HF2Q_DT_BF16) attn_combine_kernel<__nv_bfloat16><<<n_q, ATT_HD, 0, st>>>(scratch, n_splits, G, static_cast<__nv_bfloat16*>(out));
+    else return cudaErrorInvalidValue;
+    return cudaGetLastError();
+}
+
+template <int G, typename OUT>
+static cudaError_t launch_prefill_g(const float* qkv, uint32_t row_stride, uint32_t m, const KvCacheView& kv, uint32_t n_kv, uint32_t pos0,
+                                    OUT* out, uint32_t out_stride, cudaStream_t st) {
+    constexpr int ROWS = PF_QT * G;
+    const size_t smem = (static_cast<size_t>(ROWS) * (ATT_HD + 4) + PF_KT * (ATT_HD + 4) + ROWS * (PF_KT + 1)) * sizeof(float);
+    auto kern = attn_prefill_kernel<G, OUT>;
+    static PerDeviceFlag attr;
+    if (const cudaError_t e = ensure_max_dynamic_smem(kern, 160 * 1024, attr); e != cudaSuccess) return e;
+    const dim3 grid((m + PF_QT - 1) / PF_QT, n_kv);
+    kern<<<grid, ROWS * 4, smem, st>>>(qkv, row_stride, m, kv.k_codes, kv.k_scale, kv.v_codes, kv.v_scale, kv.max_seq, pos0, out, out_stride);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_attn_prefill(const float* qkv, uint32_t row_stride, uint32_t m, uint32_t n_q, uint32_t n_kv, uint32_t hd,
+                                const KvCacheView& kv, uint32_t pos0, void* out, uint32_t out_dtype, uint32_t out_stride, cudaStream_t st) {
+    if (hd != ATT_HD || n_kv == 0 || n_q % n_kv) return cudaErrorInvalidValue;
+    const uint32_t G = n_q / n_kv;
+    const bool f32 = out_dtype == HF2Q_DT_F32;
+    if (!f32 && out_dtype != HF2Q_DT_BF16) return cudaErrorInvalidValue;
+    switch (G) {
+#define HF2Q_CASE(GG) case GG: return f32 ? launch_prefill_g<GG, float>(qkv, row_stride, m, kv, n_kv, pos0, static_cast<float*>(out), out_stride, st) \
+                                          : launch_prefill_g<GG, __nv_bfloat16>(qkv, row_stride, m, kv, n_kv, pos0, static_cast<__nv_bfloat16*>(out), out_stride, st);
+        HF2Q_CASE(1) HF2Q_CASE(2) HF2Q_CASE(4) HF2Q_CASE(8)
+#undef HF2Q_CASE
+        default: return cudaErrorInvalidValue;
+    }
+}
+
+cudaError_t launch_argmax(const float* logits, uint32_t n, uint32_t* out_id, uint32_t* pos, cudaStream_t st) {
+    argmax_kernel<<<1, 1024, 0, st>>>(logits, n, out_id, pos);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_add(float* x, const float* d, uint64_t n, int sm_count, cudaStream_t st) {
+    const uint64_t want = (n + 255) / 256, cap = static_cast<uint64_t>(sm_count) * 16;
+    add_kernel<<<static_cast<unsigned>(want < cap ? (want ? want : 1) : cap), 256, 0, st>>>(x, d, n);
+    return cudaGetLastError();
+}
+
+}  // namespace hf2q

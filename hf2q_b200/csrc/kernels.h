@@ -124,6 +124,30 @@ cudaError_t launch_softmax_topk(const float* logits, uint32_t* ids, float* weigh
                                 cudaStream_t st);
 
 
+// ---- the glue of a full decoder forward (decoder_ops.cu) ----
+// 8-bit KV cache of one layer: int8 codes [n_kv_heads][max_seq][head_dim] and one f32 scale per
+// (head, position), for K and for V.
+struct KvCacheView {
+    int8_t* k_codes;
+    float* k_scale;
+    int8_t* v_codes;
+    float* v_scale;
+    uint32_t max_seq;
+};
+cudaError_t launch_get_rows(uint32_t type, const void* w, uint64_t row_bytes, uint32_t n_rows, uint32_t k, const uint32_t* ids,
+                            uint32_t m, float* out, uint32_t* status, cudaStream_t st);
+cudaError_t launch_rms_norm(float* x, const float* delta, const float* weight, float eps, void* out, uint32_t out_dtype, uint32_t m,
+                            uint32_t h, cudaStream_t st);
+cudaError_t launch_rope_kv_append(float* qkv, uint32_t m, uint32_t n_q, uint32_t n_kv, uint32_t hd, const uint32_t* pos, float theta,
+                                  const KvCacheView& kv, uint32_t* status, cudaStream_t st);
+size_t attn_decode_scratch_bytes(uint32_t n_kv, uint32_t group, uint32_t n_splits);
+cudaError_t launch_attn_decode(const float* q, uint32_t n_q, uint32_t n_kv, uint32_t hd, const KvCacheView& kv, const uint32_t* pos,
+                               void* out, uint32_t out_dtype, float* scratch, uint32_t n_splits, cudaStream_t st);
+cudaError_t launch_attn_prefill(const float* qkv, uint32_t row_stride, uint32_t m, uint32_t n_q, uint32_t n_kv, uint32_t hd,
+                                const KvCacheView& kv, uint32_t pos0, void* out, uint32_t out_dtype, uint32_t out_stride, cudaStream_t st);
+cudaError_t launch_argmax(const float* logits, uint32_t n, uint32_t* out_id, uint32_t* pos, cudaStream_t st);
+cudaError_t launch_add(float* x, const float* d, uint64_t n, int sm_count, cudaStream_t st);
+
 // element-wise glue of the FFN builders (ffn_elementwise.cu)
 cudaError_t launch_silu_mul(const float* gate, const float* up, float* out, uint64_t n, int sm_count, cudaStream_t st);
 cudaError_t launch_moe_combine(const float* y, const float* w, const float* shared, const float* gate_logit, const float* residual,

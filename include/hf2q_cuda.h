@@ -338,6 +338,60 @@ HF2Q_API int32_t hf2q_cuda_moe_combine(hf2q_ctx* ctx, void* stream, const float*
 HF2Q_API int32_t hf2q_cuda_rowdot(hf2q_ctx* ctx, void* stream, const float* x, const float* v, float* out,
                                   uint32_t n_tokens, uint32_t hidden);
 
+/* ---- f-3: the glue of a full decoder forward ---------------------------------------------------- *
+ * What sits between the quantized products in forward_gpu_greedy
+ * (src/inference/models/qwen35/forward_gpu.rs:4140) on Llama-shaped layers.  Arithmetic after the
+ * reference's scalar specs: rms_norm_rows and residual_add (forward_cpu.rs:36-56), causal softmax
+ * attention (full_attn.rs:219-360, without the output gate, with the plain rotary embedding of the
+ * Llama architecture: pairs (2i, 2i+1), angle pos * theta^(-2i/head_dim)), embed_tokens /
+ * apply_output_head (io_heads.rs).
+ *
+ * KV cache of one layer, laid out like TqFullAttnKvBuffers (kv_cache.rs:1982-2012): one byte per
+ * element, [n_kv_heads][max_seq][head_dim], plus one f32 per (head, position).  The reference's
+ * byte indexes a 256-entry codebook that lives in the external mlx-native crate; here it is a
+ * signed 8-bit integer and the f32 is the scale amax / 127 (a stand-in with the same footprint). */
+typedef struct hf2q_kv_cache {
+    void* k_codes;           /* int8 [n_kv_heads][max_seq][head_dim] */
+    void* k_scale;           /* f32  [n_kv_heads][max_seq] */
+    void* v_codes;
+    void* v_scale;
+    uint32_t n_kv_heads, head_dim, max_seq;
+} hf2q_kv_cache;
+HF2Q_API int32_t hf2q_cuda_kv_cache_bytes(uint32_t n_kv_heads, uint32_t head_dim, uint32_t max_seq,
+                                          uint64_t* codes_bytes, uint64_t* scale_bytes);
+/* embed_tokens: out[t,:] = dequant(W[ids[t],:]), W any of the block formats, [n_rows][k]. */
+HF2Q_API int32_t hf2q_cuda_get_rows(hf2q_ctx* ctx, void* stream, const void* w, uint32_t ggml_type,
+                                    uint32_t n_rows, uint32_t k, const uint32_t* ids, uint32_t m, float* out);
+/* x[t,:] += delta[t,:] (delta may be NULL), then out[t,:] = x[t,:] / sqrt(mean(x^2) + eps) * weight. */
+HF2Q_API int32_t hf2q_cuda_rms_norm(hf2q_ctx* ctx, void* stream, float* x, const float* delta,
+                                    const float* weight, float eps, void* out, uint32_t out_dtype,
+                                    uint32_t m, uint32_t h);
+/* qkv: the fused QKV product, f32 [m][(n_q_heads + 2 n_kv_heads) * head_dim].  Token t is at
+ * position *pos + t (pos: device memory, so a captured decode step can be replayed).  Query heads
+ * are rotated in place and scaled by 1/sqrt(head_dim); key heads are rotated; key and value heads
+ * are quantized and stored at their positions of the cache. */
+HF2Q_API int32_t hf2q_cuda_rope_kv_append(hf2q_ctx* ctx, void* stream, float* qkv, uint32_t m,
+                                          uint32_t n_q_heads, float theta, const uint32_t* pos,
+                                          const hf2q_kv_cache* kv);
+/* One query token at position *pos against cache positions 0..*pos: out[n_q_heads][head_dim].
+ * q: the rotated, scaled query heads (the first n_q_heads * head_dim floats of a qkv row). */
+HF2Q_API int32_t hf2q_cuda_attn_decode_scratch_bytes(hf2q_ctx* ctx, uint32_t n_q_heads,
+                                                     uint32_t n_kv_heads, uint64_t* out);
+HF2Q_API int32_t hf2q_cuda_attn_decode(hf2q_ctx* ctx, void* stream, const float* q, uint32_t n_q_heads,
+                                       const hf2q_kv_cache* kv, const uint32_t* pos, void* out,
+                                       uint32_t out_dtype, void* scratch, uint64_t scratch_bytes);
+/* m query tokens at positions pos0 .. pos0 + m - 1 (already appended), causal:
+ * out[m][n_q_heads * head_dim].  qkv as for hf2q_cuda_rope_kv_append (after it). */
+HF2Q_API int32_t hf2q_cuda_attn_prefill(hf2q_ctx* ctx, void* stream, const float* qkv, uint32_t m,
+                                        uint32_t n_q_heads, const hf2q_kv_cache* kv, uint32_t pos0,
+                                        void* out, uint32_t out_dtype);
+/* Greedy sampling: *out_id = index of the largest logit (lowest index on ties); if pos != NULL,
+ * *pos += 1 afterwards, which hands a captured decode step over to its next replay. */
+HF2Q_API int32_t hf2q_cuda_argmax(hf2q_ctx* ctx, void* stream, const float* logits, uint32_t n,
+                                  uint32_t* out_id, uint32_t* pos);
+/* residual_add: x[i] += delta[i]. */
+HF2Q_API int32_t hf2q_cuda_add(hf2q_ctx* ctx, void* stream, float* x, const float* delta, uint64_t n);
+
 /* ---- introspection ------------------------------------------------------------------------ */
 
 /* Number of kernels this library has launched through `ctx` since creation (the reference keeps
