@@ -441,6 +441,108 @@ def bench_moe(hq, oracle, torch, ctx, dev, args, toks=None) -> dict:
             "per_case": res, "gpu_launches": int(ctx.launch_count - l0), "clocks": sampler.stop()}
 
 
+def build_llama_weights(hq, oracle, torch, ctx, dev, cfg, distinct_rows: int = 16384):
+    """Random-init Llama-shaped weights under the Q4_K_M type map, quantized by the oracle's port of
+    hf2q's quantizers.  To keep the host work to seconds, ONE tensor is quantized per distinct (role,
+    block format) and every layer gets its own device copy of those bytes (so a decode step streams
+    every layer from HBM); the two vocabulary-sized tensors repeat a block of `distinct_rows` rows."""
+    from hf2q_b200 import decoder as D
+    from tests.util import make_quant_weight
+    types = D.q4_k_m_types(cfg)
+    cache = {}
+
+    def raw(role, t, n, k, seed):
+        key = (role, t)
+        if key not in cache:
+            cache[key] = torch.from_numpy(make_quant_weight(t, n, k, seed=seed)).to(dev)
+        return cache[key]
+
+    def weight(role, t, n, k, seed):
+        return hq.load_quant_weight(ctx, raw(role, t, n, k, seed).clone(), t, n, k)
+
+    def vocab_weight(role, t, seed):
+        rows = min(distinct_rows, cfg.vocab)
+        block = raw(role, t, rows, cfg.hidden, seed)
+        reps = (cfg.vocab + rows - 1) // rows
+        rb = oracle.row_bytes(t, cfg.hidden)
+        full = block.repeat(reps)[: cfg.vocab * rb].contiguous()
+        return hq.load_quant_weight(ctx, full, t, cfg.vocab, cfg.hidden)
+
+    ones = lambda: torch.ones(cfg.hidden, dtype=torch.float32, device=dev)
+    layers = []
+    for i in range(cfg.n_layers):
+        p = f"blk.{i}."
+        same = types[p + "attn_v"] == types[p + "attn_q"]        # V shares the block format of Q and K: one tensor, one launch
+        layers.append(D.LayerWeights(
+            ones(),
+            weight("qkv", types[p + "attn_q"], cfg.q_rows + 2 * cfg.kv_rows, cfg.hidden, 9) if same
+            else weight("qk", types[p + "attn_q"], cfg.q_rows + cfg.kv_rows, cfg.hidden, 1),
+            None if same else weight("v", types[p + "attn_v"], cfg.kv_rows, cfg.hidden, 2),
+            weight("o", types[p + "attn_output"], cfg.hidden, cfg.q_rows, 3), ones(),
+            weight("gate", types[p + "ffn_gate"], cfg.ffn, cfg.hidden, 4), weight("up", types[p + "ffn_up"], cfg.ffn, cfg.hidden, 5),
+            weight("down", types[p + "ffn_down"], cfg.hidden, cfg.ffn, 6)))
+    return D.ModelWeights(vocab_weight("embd", types["token_embd"], 7), layers, ones(), vocab_weight("out", types["output"], 8))
+
+
+def bench_decode(hq, oracle, torch, ctx, dev, args) -> dict:
+    """BASELINE config 5: random-init decoder forward on Llama-3-8B shapes, Q4_K_M weights, 8-bit KV cache
+    with room for 32K positions; greedy decode of 200 tokens after an 8192-token prefill of uniform-random
+    ids.  One GPU; the decode loop is one captured CUDA graph replayed per token."""
+    from hf2q_b200 import decoder as D
+    cfg = D.LlamaConfig()
+    n_prompt, n_new = (args.tokens or 8192), 200
+    sampler = ClockSampler(ctx.device)
+    t0 = time.perf_counter()
+    w = build_llama_weights(hq, oracle, torch, ctx, dev, cfg)
+    dec = D.LlamaDecoder(ctx, cfg, w)
+    t_build = time.perf_counter() - t0
+    ids = torch.randint(0, cfg.vocab, (n_prompt,), dtype=torch.int32, device=dev, generator=torch.Generator(device=dev).manual_seed(0))
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    dec.prefill(ids)
+    e1.record()
+    torch.cuda.synchronize()
+    ctx.check_status()
+    prefill_s = e0.elapsed_time(e1) * 1e-3
+    state = (dec.pos.clone(), dec.tok.clone())
+    dec.generate(8, use_graph=True, collect=False)              # captures the step and warms the replay
+    dec.pos.copy_(state[0]); dec.tok.copy_(state[1])
+    torch.cuda.synchronize()
+    l0 = ctx.launch_count
+    sampler.start()
+    e0.record()
+    dec.generate(n_new, use_graph=True, collect=False)
+    e1.record()
+    torch.cuda.synchronize()
+    clocks = sampler.stop()
+    ctx.check_status()
+    dt = e0.elapsed_time(e1) * 1e-3
+    assert int(dec.pos.item()) == n_prompt + n_new
+    logits_finite = bool(torch.isfinite(dec.logits).all().item())
+    tok_s = n_new / dt
+    wbytes = dec.weight_bytes_per_token()
+    ctx_mid = n_prompt + n_new // 2
+    kvbytes = dec.kv_bytes_per_position() * ctx_mid
+    peak, kind = measured_hbm_peak()
+    roof_tok_s = peak * 1e9 / (wbytes + kvbytes)
+    return {"metric": "decode tok/s", "value": round(tok_s, 1), "unit": "tok/s", "higher_is_better": True,
+            "ms_per_token": round(1e3 * dt / n_new, 4), "dtype": "f32 activations, f32 accumulate, int8 KV",
+            "config": {"workload": f"Llama-3-8B shapes (32 layers, hidden 4096, 32/8 heads, head dim 128, FFN 14336, vocab 128256, RMSNorm, RoPE theta 500000), "
+                                   f"Q4_K_M type map (Q6_K attn_v / ffn_down on 16 layers, Q6_K output), 8-bit per-(head, position)-scaled KV cache sized for 32K positions; "
+                                   f"greedy decode of {n_new} tokens after a {n_prompt}-token prefill of uniform-random ids",
+                       "weights": "N(0, sigma=0.02) quantized by the oracle's port of hf2q's quantizers: one tensor per (role, format), a device copy per layer",
+                       "launch_mode": "one CUDA graph of the whole decode step, replayed per token; token id and position stay on the device"},
+            "roofline": {"bound": "hbm", "achieved": round((wbytes + kvbytes) / (dt / n_new) / 1e9, 1), "peak": peak, "unit": "GB/s",
+                         "frac": round(tok_s / roof_tok_s, 4), "peak_source": f"of {kind}", "roofline_tok_s": round(roof_tok_s, 1),
+                         "weight_bytes_per_token": wbytes, "kv_bytes_per_token_at_mid_context": kvbytes,
+                         "kernel": "gemv_mma_kernel (7 products per layer in 4 launches) + attn_decode_kernel + glue", "traffic": None},
+            "prefill": {"tokens": n_prompt, "seconds": round(prefill_s, 3), "tok_s": round(n_prompt / prefill_s, 1),
+                        "note": "tensor-core GEMMs + CUDA-core tiled attention over the 8-bit cache; not the timed metric"},
+            "launches_per_token": dec.launches_per_token, "gpu_launches": int(dec.launches_per_token * n_new), "logits_finite": logits_finite,
+            "host_seconds_building_weights": round(t_build, 1), "eager_launches_seen": int(ctx.launch_count - l0), "clocks": clocks}
+
+
 def run_secondary(args) -> None:
     """One of the other workloads alone on one GPU: one JSON line."""
     import torch
@@ -458,6 +560,8 @@ def run_secondary(args) -> None:
         line = bench_matvec(hq, oracle, torch, ctx, dev, args)
     elif args.workload == "config1":
         line = bench_config1(hq, oracle, torch, ctx, dev, args)
+    elif args.workload == "decode":
+        line = bench_decode(hq, oracle, torch, ctx, dev, args)
     else:
         line = bench_moe(hq, oracle, torch, ctx, dev, args, toks)
     line.update({"n_gpus": 1, "data": "synthetic"})
@@ -477,10 +581,11 @@ def main() -> None:
                     help="several GPUs: products do not wait for the previous product's columns (analysis aid)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-secondary", action="store_true", help="one GPU: skip the config 1 / GEMM / MoE measurements")
+    ap.add_argument("--no-decode", action="store_true", help="one GPU: skip the full-decoder decode tok/s measurement")
     ap.add_argument("--no-strong", action="store_true", help="several GPUs: skip the strong-scaling leg")
     ap.add_argument("--no-graph", action="store_true", help="issue launches eagerly instead of replaying a CUDA graph")
     ap.add_argument("--qtype", default="", help="matvec: one ggml type number (2, 8, 12, 13, 14) instead of all five")
-    ap.add_argument("--workload", default="gemv", choices=["gemv", "gemm", "moe", "matvec", "config1"],
+    ap.add_argument("--workload", default="gemv", choices=["gemv", "gemm", "moe", "matvec", "config1", "decode"],
                     help="gemv: the headline Q6_K decode sweep (default, carries the others as `secondary`); gemm: Q4_K_M prefill "
                          "GEMM sweep; moe: Qwen3-style A3B expert layer (Q5_K mul_mat_id); matvec: all block formats; config1: Q4_K 4096^2 f32")
     ap.add_argument("--tokens", type=int, default=0, help="gemm/moe: one token count instead of the sweep")
@@ -826,6 +931,9 @@ def main() -> None:
         secondary = {"config1_q4k_f32": bench_config1(hq, oracle, torch, ctx, dev, args),
                      "config3_prefill_gemm": bench_gemm(hq, oracle, torch, ctx, dev, args),
                      "config4_moe_layer": bench_moe(hq, oracle, torch, ctx, dev, args)}
+        if not args.no_decode:
+            torch.cuda.empty_cache()
+            secondary["config5_decode"] = bench_decode(hq, oracle, torch, ctx, dev, args)
 
     line = {
         "metric": METRIC, "value": round(value, 1), "unit": UNIT, "n_gpus": world, "steps": args.steps,

@@ -10,4 +10,4 @@ from .ops import (  # noqa: F401
     QuantWeight, IdMmScratch, load_quant_weight, quantized_matmul_ggml, quantized_matmul_id_ggml, quantized_matmul_id_pair_ggml,
     dequantize, moe_softmax_topk, row_bytes, expert_stride,
 )
-from . import ffn, dist, gguf  # noqa: F401,E402
+from . import ffn, dist, gguf, decoder  # noqa: F401,E402

@@ -58,6 +58,7 @@ SIGNATURES = {
     "hf2q_cuda_moe_softmax_topk": (i32, [vp, vp, vp, vp, vp, u32, u32, u32]),
     "hf2q_cuda_silu_mul": (i32, [vp, vp, vp, vp, vp, u64]),
     "hf2q_cuda_moe_combine": (i32, [vp, vp, vp, vp, vp, vp, vp, vp, u32, u32, u32]),
+    "hf2q_cuda_router_logits": (i32, [vp, vp, vp, u32, vp, vp, u32, u32, u32]),
     "hf2q_cuda_rowdot": (i32, [vp, vp, vp, vp, vp, u32, u32]),
     "hf2q_cuda_kv_cache_bytes": (i32, [u32, u32, u32, C.POINTER(u64), C.POINTER(u64)]),
     "hf2q_cuda_get_rows": (i32, [vp, vp, vp, u32, u32, u32, vp, u32, vp]),
@@ -65,6 +66,10 @@ SIGNATURES = {
     "hf2q_cuda_rope_kv_append": (i32, [vp, vp, vp, u32, u32, C.c_float, vp, vp]),
     "hf2q_cuda_attn_decode_scratch_bytes": (i32, [vp, u32, u32, C.POINTER(u64)]),
     "hf2q_cuda_attn_decode": (i32, [vp, vp, vp, u32, vp, vp, vp, u32, vp, u64]),
+    "hf2q_cuda_norm_supported": (i32, [vp, u32, u32, u32]),
+    "hf2q_cuda_norm_qmatmul_segments": (i32, [vp, vp, vp, vp, C.c_float, vp, u32, vp, u32, u32]),
+    "hf2q_cuda_norm_qmatmul_swiglu": (i32, [vp, vp, vp, vp, C.c_float, vp, vp, vp, u32, u32, u32, u32]),
+    "hf2q_cuda_attn_decode_fused": (i32, [vp, vp, vp, u32, C.c_float, vp, vp, vp, u32, vp, u64]),
     "hf2q_cuda_attn_prefill": (i32, [vp, vp, vp, u32, u32, vp, u32, vp, u32]),
     "hf2q_cuda_argmax": (i32, [vp, vp, vp, u32, vp, vp]),
     "hf2q_cuda_add": (i32, [vp, vp, vp, vp, u64]),

@@ -20,6 +20,11 @@ struct hf2q_ctx {
     uint64_t launches = 0;
     bool fp32_matvec = false;          // HF2Q_CUDA_F32_MATVEC=1: CUDA-core fp32 mat-vec only
     long long wait_limit = 1ll << 31;  // clock ticks a device-side wait for another GPU may take (about a second)
+    // partial sums of the mat-vec's split-k form (rows too long for the activation panel); one buffer per
+    // context, used by one launch at a time in stream order (a context serves one thread and stream at a time)
+    float* splitk = nullptr;
+    static constexpr uint64_t SPLITK_BYTES = 8ull << 20;
+    uint32_t* misc = nullptr;          // 1 KiB of zero-initialised words: arrival counter and candidates of the arg-max
     // staging for the *_host convenience calls
     // A ring of device staging buffers and three streams: copy-in on in_stream, kernels on
     // host_stream, copy-out on out_stream, so that the copy-in of later calls, the kernel of call i
@@ -111,6 +116,9 @@ int32_t run_matvec(hf2q_ctx* ctx, cudaStream_t st, GemvArgs a, uint32_t m_total,
         if (r0) a.residual = r0 + static_cast<size_t>(m0) * a.n;
         cudaError_t e;
         int nl = 1;
+        a.splitk_scratch = ctx->splitk;
+        a.splitk_bytes = hf2q_ctx::SPLITK_BYTES;
+        a.n_launches = &nl;
         if (use_mma) e = launch_gemv_mma(a, ctx->dev, st);
         else e = launch_gemv(a, ctx->dev, st, &nl);
         if (e != cudaSuccess) return cuda_fail(ctx, e, who);
@@ -157,10 +165,14 @@ HF2Q_API int32_t hf2q_cuda_ctx_create(int32_t device, hf2q_ctx** out) {
     c->dev.sm_count = prop.multiProcessorCount;
     c->dev.max_smem_optin = static_cast<int>(prop.sharedMemPerBlockOptin);
     if (cudaMalloc(&c->status, 256) != cudaSuccess || cudaMemset(c->status, 0, 256) != cudaSuccess ||
+        cudaMalloc(&c->splitk, hf2q_ctx::SPLITK_BYTES) != cudaSuccess ||
+        cudaMalloc(&c->misc, 1024) != cudaSuccess || cudaMemset(c->misc, 0, 1024) != cudaSuccess ||
         cudaStreamCreateWithFlags(&c->host_stream, cudaStreamNonBlocking) != cudaSuccess ||
         cudaStreamCreateWithFlags(&c->out_stream, cudaStreamNonBlocking) != cudaSuccess ||
         cudaStreamCreateWithFlags(&c->in_stream, cudaStreamNonBlocking) != cudaSuccess) {
         if (c->status) cudaFree(c->status);
+        if (c->splitk) cudaFree(c->splitk);
+        if (c->misc) cudaFree(c->misc);
         delete c;
         return HF2Q_ERR_CUDA;
     }
@@ -177,6 +189,8 @@ HF2Q_API int32_t hf2q_cuda_ctx_destroy(hf2q_ctx* ctx) {
     DeviceGuard g(ctx->device);
     cudaDeviceSynchronize();
     if (ctx->status) cudaFree(ctx->status);
+    if (ctx->splitk) cudaFree(ctx->splitk);
+    if (ctx->misc) cudaFree(ctx->misc);
     for (auto& hs : ctx->hslot) {
         if (hs.x) cudaFree(hs.x);
         if (hs.y) cudaFree(hs.y);
@@ -320,9 +334,8 @@ HF2Q_API int32_t hf2q_cuda_qmatmul(hf2q_ctx* ctx, void* stream, const void* x, u
 // A matrix whose row ranges use different block formats (the fused QKV tensor of a Q4_K_M model:
 // Q and K rows Q4_K, V rows Q6_K): one call, one conversion of the activations, one launch per range,
 // every range writing its own columns of the one output.
-HF2Q_API int32_t hf2q_cuda_qmatmul_segments(hf2q_ctx* ctx, void* stream, const void* x, uint32_t x_dtype,
-                                            const hf2q_row_segment* segs, uint32_t n_segs, float* y, uint32_t m, uint32_t k,
-                                            void* workspace, uint64_t workspace_bytes) {
+static int32_t segments_impl(hf2q_ctx* ctx, void* stream, const void* x, uint32_t x_dtype, const hf2q_row_segment* segs, uint32_t n_segs,
+                             float* y, uint32_t m, uint32_t k, void* workspace, uint64_t workspace_bytes, const float* norm_w, float norm_eps) {
     if (!ctx) return HF2Q_ERR_INVALID_ARGUMENT;
     if (!x || !segs || !y || n_segs == 0 || n_segs > 16) return fail(ctx, HF2Q_ERR_INVALID_ARGUMENT, "qmatmul_segments: null pointer or n_segs=%u not in 1..16", n_segs);
     if (x_dtype != HF2Q_DT_F32 && x_dtype != HF2Q_DT_BF16) return fail(ctx, HF2Q_ERR_INVALID_ARGUMENT, "qmatmul_segments: x_dtype %u (want F32 or BF16)", x_dtype);
@@ -340,6 +353,13 @@ HF2Q_API int32_t hf2q_cuda_qmatmul_segments(hf2q_ctx* ctx, void* stream, const v
     DeviceGuard dg(ctx->device);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const bool gemm = m > 8 && !ctx->fp32_matvec;
+    if (norm_w) {
+        if (gemm || x_dtype != HF2Q_DT_F32 || m > 4)
+            return fail(ctx, HF2Q_ERR_INVALID_ARGUMENT, "norm_qmatmul_segments: the fused RMSNorm takes 1..4 f32 activation rows (m=%u, x_dtype=%u)", m, x_dtype);
+        for (uint32_t i = 0; i < n_segs; ++i)
+            if (!gemv_mma_norm_ok(segs[i].ggml_type, k, m, ctx->dev))
+                return fail(ctx, HF2Q_ERR_INVALID_ARGUMENT, "norm_qmatmul_segments: k=%u / type %u does not fit the fused RMSNorm (k <= 4096, k %% 256 == 0)", k, segs[i].ggml_type);
+    }
     if (gemm) {
         const uint64_t need = gemm_tc_workspace_bytes(m, k);
         if (!workspace || workspace_bytes < need)
@@ -348,39 +368,73 @@ HF2Q_API int32_t hf2q_cuda_qmatmul_segments(hf2q_ctx* ctx, void* stream, const v
         if (reinterpret_cast<uintptr_t>(workspace) % 256) return fail(ctx, HF2Q_ERR_INVALID_ARGUMENT, "qmatmul_segments: workspace must be 256-byte aligned");
     }
     // every range must fit the kernel the row count selects: a detour for one range would need a second output layout
+    uint32_t step = m;                  // activation rows per mat-vec launch (f32 rows take two MMA columns each)
     for (uint32_t i = 0; i < n_segs; ++i) {
         GemvArgs a{};
         a.w = segs[i].w; a.x = x; a.x_dtype = x_dtype; a.type = segs[i].ggml_type; a.n = segs[i].rows; a.k = k;
-        const bool ok = gemm ? gemm_tc_supported(segs[i].ggml_type, segs[i].w, segs[i].rows, k)
-                             : (!ctx->fp32_matvec && gemv_mma_supported(a) && gemv_mma_max_rows(segs[i].ggml_type, k, x_dtype, ctx->dev) >= m);
+        bool ok;
+        if (gemm) {
+            ok = gemm_tc_supported(segs[i].ggml_type, segs[i].w, segs[i].rows, k);
+        } else {
+            const uint32_t rows = (!ctx->fp32_matvec && gemv_mma_supported(a)) ? gemv_mma_max_rows(segs[i].ggml_type, k, x_dtype, ctx->dev) : 0;
+            ok = rows > 0;
+            if (ok && rows < step) step = rows;
+        }
         if (!ok) return fail(ctx, HF2Q_ERR_INVALID_ARGUMENT, "qmatmul_segments: segment %u (type %u, k=%u, m=%u) needs 16-byte aligned weight rows and k %% 256 == 0", i,
                              segs[i].ggml_type, k, m);
     }
     uint32_t col0 = 0;
     for (uint32_t i = 0; i < n_segs; ++i) {
-        cudaError_t e;
-        int nl = 1;
         if (gemm) {
-            e = launch_gemm_tc(segs[i].ggml_type, segs[i].w, x, x_dtype, y + col0, m, segs[i].rows, k, workspace, ctx->status, ctx->dev.sm_count, st, &nl,
-                               static_cast<uint32_t>(n), i != 0);
+            int nl = 1;
+            const cudaError_t e = launch_gemm_tc(segs[i].ggml_type, segs[i].w, x, x_dtype, y + col0, m, segs[i].rows, k, workspace, ctx->status,
+                                                 ctx->dev.sm_count, st, &nl, static_cast<uint32_t>(n), i != 0);
+            if (e != cudaSuccess) return cuda_fail(ctx, e, "qmatmul_segments launch");
+            ctx->launches += nl;
         } else {
-            GemvArgs a{};
-            a.w = segs[i].w; a.x = x; a.y = y;
-            a.x_dtype = x_dtype; a.type = segs[i].ggml_type;
-            a.m = m; a.n = segs[i].rows; a.k = k;
-            a.slots = 1; a.top_k = 1; a.n_experts = 0;
-            a.status = ctx->status;
-            GatherArgs ga{};             // the one-rank form of the gathering store: columns [col0, col0 + rows) of a wider y
-            ga.y_all[0] = y; ga.n_ranks = 1; ga.rank = 0; ga.n_total = static_cast<uint32_t>(n); ga.col0 = col0;
-            ga.wait_limit = ctx->wait_limit;
-            a.gather = &ga;
-            e = launch_gemv_mma(a, ctx->dev, st);
+            for (uint32_t m0 = 0; m0 < m; m0 += step) {
+                GemvArgs a{};
+                a.w = segs[i].w;
+                a.x = static_cast<const uint8_t*>(x) + static_cast<size_t>(m0) * k * dtype_size(x_dtype);
+                a.y = y + static_cast<size_t>(m0) * n;
+                a.x_dtype = x_dtype; a.type = segs[i].ggml_type;
+                a.m = (m - m0) < step ? (m - m0) : step; a.n = segs[i].rows; a.k = k;
+                a.slots = 1; a.top_k = 1; a.n_experts = 0;
+                a.status = ctx->status;
+                GatherArgs ga{};             // the one-rank form of the gathering store: columns [col0, col0 + rows) of a wider y
+                ga.y_all[0] = a.y; ga.n_ranks = 1; ga.rank = 0; ga.n_total = static_cast<uint32_t>(n); ga.col0 = col0;
+                ga.wait_limit = ctx->wait_limit;
+                a.gather = &ga;
+                a.norm_weight = norm_w;
+                a.norm_eps = norm_eps;
+                const cudaError_t e = launch_gemv_mma(a, ctx->dev, st);
+                if (e != cudaSuccess) return cuda_fail(ctx, e, "qmatmul_segments launch");
+                ctx->launches += 1;
+            }
         }
-        if (e != cudaSuccess) return cuda_fail(ctx, e, "qmatmul_segments launch");
-        ctx->launches += nl;
         col0 += segs[i].rows;
     }
     return HF2Q_OK;
+}
+
+HF2Q_API int32_t hf2q_cuda_qmatmul_segments(hf2q_ctx* ctx, void* stream, const void* x, uint32_t x_dtype,
+                                            const hf2q_row_segment* segs, uint32_t n_segs, float* y, uint32_t m, uint32_t k,
+                                            void* workspace, uint64_t workspace_bytes) {
+    return segments_impl(ctx, stream, x, x_dtype, segs, n_segs, y, m, k, workspace, workspace_bytes, nullptr, 0.f);
+}
+
+HF2Q_API int32_t hf2q_cuda_norm_qmatmul_segments(hf2q_ctx* ctx, void* stream, const float* x, const float* norm_weight, float eps,
+                                                 const hf2q_row_segment* segs, uint32_t n_segs, float* y, uint32_t m, uint32_t k) {
+    if (!ctx) return HF2Q_ERR_INVALID_ARGUMENT;
+    if (!norm_weight) return fail(ctx, HF2Q_ERR_INVALID_ARGUMENT, "norm_qmatmul_segments: null norm weight");
+    return segments_impl(ctx, stream, x, HF2Q_DT_F32, segs, n_segs, y, m, k, nullptr, 0, norm_weight, eps);
+}
+
+HF2Q_API int32_t hf2q_cuda_norm_supported(hf2q_ctx* ctx, uint32_t m, uint32_t k, uint32_t type) {
+    if (!ctx || !type_supported(type) || ctx->fp32_matvec) return 0;
+    const BlockGeom g = block_geom(type);
+    if (k % g.elems || (static_cast<uint64_t>(k) / g.elems * g.bytes) % 16) return 0;
+    return gemv_mma_norm_ok(type, k, m, ctx->dev) ? 1 : 0;
 }
 
 // ---- dense FFN fusions: SwiGLU in the gate/up launch, residual add in the down launch ----
@@ -394,8 +448,8 @@ HF2Q_API int32_t hf2q_cuda_qmatmul_swiglu_supported(hf2q_ctx* ctx, uint32_t m, u
     return gemv_mma_swiglu_ok(type, k, m, x_dtype, ctx->dev) ? 1 : 0;
 }
 
-HF2Q_API int32_t hf2q_cuda_qmatmul_swiglu(hf2q_ctx* ctx, void* stream, const void* x, uint32_t x_dtype, const void* w_gate,
-                                          const void* w_up, float* y, uint32_t m, uint32_t n, uint32_t k, uint32_t type) {
+static int32_t swiglu_impl(hf2q_ctx* ctx, void* stream, const void* x, uint32_t x_dtype, const void* w_gate, const void* w_up, float* y,
+                           uint32_t m, uint32_t n, uint32_t k, uint32_t type, const float* norm_w, float norm_eps) {
     if (!ctx) return HF2Q_ERR_INVALID_ARGUMENT;
     if (!x || !w_gate || !w_up || !y) return fail(ctx, HF2Q_ERR_INVALID_ARGUMENT, "qmatmul_swiglu: null pointer");
     if (x_dtype != HF2Q_DT_F32 && x_dtype != HF2Q_DT_BF16) return fail(ctx, HF2Q_ERR_INVALID_ARGUMENT, "qmatmul_swiglu: x_dtype %u (want F32 or BF16)", x_dtype);
@@ -409,8 +463,12 @@ HF2Q_API int32_t hf2q_cuda_qmatmul_swiglu(hf2q_ctx* ctx, void* stream, const voi
     a.slots = 1; a.top_k = 1; a.n_experts = 0;
     a.swiglu = true;
     a.status = ctx->status;
+    a.norm_weight = norm_w;
+    a.norm_eps = norm_eps;
     GemvArgs up = a;
     up.w = w_up;
+    if (norm_w && (x_dtype != HF2Q_DT_F32 || !gemv_mma_norm_ok(type, k, m, ctx->dev)))
+        return fail(ctx, HF2Q_ERR_INVALID_ARGUMENT, "norm_qmatmul_swiglu: the fused RMSNorm takes 1..4 f32 rows of k <= 4096 (m=%u, k=%u)", m, k);
     if (!hf2q_cuda_qmatmul_swiglu_supported(ctx, m, n, k, type, x_dtype) || !gemv_mma_supported(a) || !gemv_mma_supported(up))
         return fail(ctx, HF2Q_ERR_INVALID_ARGUMENT,
                     "qmatmul_swiglu: m=%u k=%u does not fit one fused launch (ask hf2q_cuda_qmatmul_swiglu_supported; needs 16-byte aligned rows, "
@@ -420,6 +478,19 @@ HF2Q_API int32_t hf2q_cuda_qmatmul_swiglu(hf2q_ctx* ctx, void* stream, const voi
     if (e != cudaSuccess) return cuda_fail(ctx, e, "qmatmul_swiglu launch");
     ctx->launches += 1;
     return HF2Q_OK;
+}
+
+HF2Q_API int32_t hf2q_cuda_qmatmul_swiglu(hf2q_ctx* ctx, void* stream, const void* x, uint32_t x_dtype, const void* w_gate,
+                                          const void* w_up, float* y, uint32_t m, uint32_t n, uint32_t k, uint32_t type) {
+    return swiglu_impl(ctx, stream, x, x_dtype, w_gate, w_up, y, m, n, k, type, nullptr, 0.f);
+}
+
+HF2Q_API int32_t hf2q_cuda_norm_qmatmul_swiglu(hf2q_ctx* ctx, void* stream, const float* x, const float* norm_weight, float eps,
+                                               const void* w_gate, const void* w_up, float* y, uint32_t m, uint32_t n, uint32_t k,
+                                               uint32_t type) {
+    if (!ctx) return HF2Q_ERR_INVALID_ARGUMENT;
+    if (!norm_weight) return fail(ctx, HF2Q_ERR_INVALID_ARGUMENT, "norm_qmatmul_swiglu: null norm weight");
+    return swiglu_impl(ctx, stream, x, HF2Q_DT_F32, w_gate, w_up, y, m, n, k, type, norm_weight, eps);
 }
 
 HF2Q_API int32_t hf2q_cuda_qmatmul_add_supported(hf2q_ctx* ctx, uint32_t n, uint32_t k, uint32_t type, uint32_t x_dtype) {
@@ -852,6 +923,19 @@ HF2Q_API int32_t hf2q_cuda_moe_combine(hf2q_ctx* ctx, void* stream, const float*
     return HF2Q_OK;
 }
 
+HF2Q_API int32_t hf2q_cuda_router_logits(hf2q_ctx* ctx, void* stream, const void* x, uint32_t x_dtype, const float* router,
+                                         float* logits, uint32_t n_tokens, uint32_t n_experts, uint32_t hidden) {
+    if (!ctx) return HF2Q_ERR_INVALID_ARGUMENT;
+    if (!x || !router || !logits || n_experts == 0 || hidden == 0) return fail(ctx, HF2Q_ERR_INVALID_ARGUMENT, "router_logits: null pointer or empty shape");
+    if (x_dtype != HF2Q_DT_F32 && x_dtype != HF2Q_DT_BF16) return fail(ctx, HF2Q_ERR_INVALID_ARGUMENT, "router_logits: x_dtype %u (want F32 or BF16)", x_dtype);
+    if (n_tokens == 0) return HF2Q_OK;
+    DeviceGuard dg(ctx->device);
+    const cudaError_t e = launch_router_logits(x, x_dtype == HF2Q_DT_BF16, router, logits, n_tokens, n_experts, hidden, static_cast<cudaStream_t>(stream));
+    if (e != cudaSuccess) return cuda_fail(ctx, e, "router_logits launch");
+    ctx->launches += 1;
+    return HF2Q_OK;
+}
+
 HF2Q_API int32_t hf2q_cuda_rowdot(hf2q_ctx* ctx, void* stream, const float* x, const float* v, float* out, uint32_t n_tokens,
                                   uint32_t hidden) {
     if (!ctx) return HF2Q_ERR_INVALID_ARGUMENT;
@@ -960,6 +1044,25 @@ HF2Q_API int32_t hf2q_cuda_attn_decode(hf2q_ctx* ctx, void* stream, const float*
     return HF2Q_OK;
 }
 
+HF2Q_API int32_t hf2q_cuda_attn_decode_fused(hf2q_ctx* ctx, void* stream, const float* qkv, uint32_t n_q_heads, float theta,
+                                             const hf2q_kv_cache* kv, const uint32_t* pos, void* out, uint32_t out_dtype, void* scratch,
+                                             uint64_t scratch_bytes) {
+    if (!ctx) return HF2Q_ERR_INVALID_ARGUMENT;
+    if (!qkv || !pos || !out || !scratch) return fail(ctx, HF2Q_ERR_INVALID_ARGUMENT, "attn_decode_fused: null pointer");
+    const int32_t rc = check_kv(ctx, kv, n_q_heads, "attn_decode_fused");
+    if (rc) return rc;
+    const uint32_t splits = attn_splits(ctx, kv->n_kv_heads);
+    if (scratch_bytes < attn_decode_scratch_bytes(kv->n_kv_heads, n_q_heads / kv->n_kv_heads, splits))
+        return fail(ctx, HF2Q_ERR_WORKSPACE, "attn_decode_fused: scratch of %llu bytes is too small (ask hf2q_cuda_attn_decode_scratch_bytes)", (unsigned long long)scratch_bytes);
+    if (reinterpret_cast<uintptr_t>(scratch) % 16) return fail(ctx, HF2Q_ERR_INVALID_ARGUMENT, "attn_decode_fused: scratch must be 16-byte aligned");
+    DeviceGuard dg(ctx->device);
+    const cudaError_t e = launch_attn_decode_fused(qkv, n_q_heads, kv->n_kv_heads, kv->head_dim, theta, view_of(kv), pos, out, out_dtype,
+                                                   static_cast<float*>(scratch), splits, ctx->status, static_cast<cudaStream_t>(stream));
+    if (e != cudaSuccess) return cuda_fail(ctx, e, "attn_decode_fused launch");
+    ctx->launches += 1;
+    return HF2Q_OK;
+}
+
 HF2Q_API int32_t hf2q_cuda_attn_prefill(hf2q_ctx* ctx, void* stream, const float* qkv, uint32_t m, uint32_t n_q_heads,
                                         const hf2q_kv_cache* kv, uint32_t pos0, void* out, uint32_t out_dtype) {
     if (!ctx) return HF2Q_ERR_INVALID_ARGUMENT;
@@ -981,7 +1084,7 @@ HF2Q_API int32_t hf2q_cuda_argmax(hf2q_ctx* ctx, void* stream, const float* logi
     if (!ctx) return HF2Q_ERR_INVALID_ARGUMENT;
     if (!logits || !out_id || n == 0) return fail(ctx, HF2Q_ERR_INVALID_ARGUMENT, "argmax: null pointer or n == 0");
     DeviceGuard dg(ctx->device);
-    const cudaError_t e = launch_argmax(logits, n, out_id, pos, static_cast<cudaStream_t>(stream));
+    const cudaError_t e = launch_argmax(logits, n, out_id, pos, ctx->misc, static_cast<cudaStream_t>(stream));
     if (e != cudaSuccess) return cuda_fail(ctx, e, "argmax launch");
     ctx->launches += 1;
     return HF2Q_OK;

@@ -244,6 +244,197 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) attn_decode_kernel(const float
     }
 }
 
+// ---- the same, as ONE launch per layer: rotary embedding of the query, append of the new position's K
+// and V, the split attention, and the merge of the splits.
+//   * every CTA rotates and scales the G query heads of its KV head itself (512 values);
+//   * the CTA whose range holds the new position (*pos) rotates and quantizes that position's K and V
+//     from the fused QKV row, writes them to the cache and then reads them like any other position;
+//   * every CTA leaves its (max, sum, acc) in scratch, bumps a per-KV-head counter, and the CTA that
+//     arrives last merges all splits of that head and resets the counter (no atomics on data, fixed
+//     merge order: bit-reproducible).
+// qkv: one fused QKV row, f32 [(n_q + 2 n_kv) * 128]; the query part is NOT modified.
+template <int G, typename OUT>
+__global__ void __launch_bounds__(ATT_WARPS * 32) attn_decode_fused_kernel(const float* __restrict__ qkv, uint32_t n_q, uint32_t n_kv,
+                                                                           float theta, float q_scale,
+                                                                           int8_t* __restrict__ k_codes, float* __restrict__ k_scale,
+                                                                           int8_t* __restrict__ v_codes, float* __restrict__ v_scale,
+                                                                           uint32_t max_seq, const uint32_t* __restrict__ pos_dev,
+                                                                           float* __restrict__ part, uint32_t* __restrict__ counters,
+                                                                           OUT* __restrict__ out, uint32_t* status) {
+    __shared__ __align__(16) float qs[G][ATT_HD];
+    __shared__ float ps[ATT_WARPS][G][32];
+    __shared__ float red_m[ATT_WARPS][G], red_l[ATT_WARPS][G];
+    __shared__ __align__(16) float red_acc[ATT_WARPS][G][ATT_HD];
+    __shared__ uint32_t is_last;
+    const uint32_t kvh = blockIdx.x, split = blockIdx.y, nsplit = gridDim.y;
+    const uint32_t pos = *pos_dev;
+    if (pos >= max_seq) { if (threadIdx.x == 0 && split == 0) atomicOr(status, STATUS_BAD_EXPERT_ID); return; }
+    const uint32_t n_ctx = pos + 1;
+    const uint32_t chunk = (n_ctx + nsplit - 1) / nsplit;
+    const uint32_t lo = min(split * chunk, n_ctx), hi = min(lo + chunk, n_ctx);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    // rotated, scaled query heads: thread -> (head g, pair i)
+    for (uint32_t i = threadIdx.x; i < G * ATT_HD / 2; i += ATT_WARPS * 32) {
+        const uint32_t g = i / (ATT_HD / 2), pr = i % (ATT_HD / 2);
+        const float* src = qkv + (static_cast<size_t>(kvh) * G + g) * ATT_HD + 2 * pr;
+        const float freq = powf(theta, -static_cast<float>(2 * pr) / static_cast<float>(ATT_HD));
+        float sn, cs;
+        sincosf(static_cast<float>(pos) * freq, &sn, &cs);
+        const float a = src[0], b = src[1];
+        qs[g][2 * pr] = (a * cs - b * sn) * q_scale;
+        qs[g][2 * pr + 1] = (a * sn + b * cs) * q_scale;
+    }
+    int8_t* kc = k_codes + static_cast<size_t>(kvh) * max_seq * ATT_HD;
+    int8_t* vc = v_codes + static_cast<size_t>(kvh) * max_seq * ATT_HD;
+    float* ksc = k_scale + static_cast<size_t>(kvh) * max_seq;
+    float* vsc = v_scale + static_cast<size_t>(kvh) * max_seq;
+    if (pos >= lo && pos < hi && warp < 2) {
+        // the new position: warp 0 -> K (rotated), warp 1 -> V; lane owns 4 consecutive elements
+        const bool is_k = warp == 0;
+        const float* src = qkv + (static_cast<size_t>(n_q) + (is_k ? 0u : n_kv) + kvh) * ATT_HD + 4 * lane;
+        float v4[4] = {src[0], src[1], src[2], src[3]};
+        if (is_k) {
+#pragma unroll
+            for (int j = 0; j < 4; j += 2) {
+                const float freq = powf(theta, -static_cast<float>(4 * lane + j) / static_cast<float>(ATT_HD));
+                float sn, cs;
+                sincosf(static_cast<float>(pos) * freq, &sn, &cs);
+                const float a = v4[j], b = v4[j + 1];
+                v4[j] = a * cs - b * sn;
+                v4[j + 1] = a * sn + b * cs;
+            }
+        }
+        float amax = fmaxf(fmaxf(fabsf(v4[0]), fabsf(v4[1])), fmaxf(fabsf(v4[2]), fabsf(v4[3])));
+        for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+        const float inv = amax > 0.f ? 127.0f / amax : 0.f;
+        uint32_t w = 0;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) w |= (static_cast<uint32_t>(__float2int_rn(v4[j] * inv)) & 0xffu) << (8 * j);
+        reinterpret_cast<uint32_t*>((is_k ? kc : vc) + static_cast<size_t>(pos) * ATT_HD)[lane] = w;
+        if (lane == 0) (is_k ? ksc : vsc)[pos] = amax / 127.0f;
+    }
+    __syncthreads();            // qs ready; the new position's codes are visible to this CTA
+
+    float mx[G], l[G], acc[G][4];
+#pragma unroll
+    for (int g = 0; g < G; ++g) { mx[g] = -CUDART_INF_F; l[g] = 0.f; acc[g][0] = acc[g][1] = acc[g][2] = acc[g][3] = 0.f; }
+    for (uint32_t p0 = lo + warp * 32; p0 < hi; p0 += ATT_WARPS * 32) {
+        const uint32_t p = p0 + lane;
+        const bool live = p < hi;
+        float s[G];
+#pragma unroll
+        for (int g = 0; g < G; ++g) s[g] = 0.f;
+        float vs = 0.f;
+        if (live) {
+            const uint4* kr = reinterpret_cast<const uint4*>(kc + static_cast<size_t>(p) * ATT_HD);
+            uint4 kv[ATT_HD / 16];
+#pragma unroll
+            for (int c = 0; c < ATT_HD / 16; ++c) kv[c] = kr[c];              // all of the row in flight at once
+            const float sc = ksc[p];
+            vs = vsc[p];
+#pragma unroll
+            for (int c = 0; c < ATT_HD / 16; ++c) {
+                const uint32_t kw[4] = {kv[c].x, kv[c].y, kv[c].z, kv[c].w};
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const float4 kf = s8x4_to_float4(kw[j]);
+#pragma unroll
+                    for (int g = 0; g < G; ++g) {
+                        const float4 qv = *reinterpret_cast<const float4*>(&qs[g][16 * c + 4 * j]);
+                        s[g] += kf.x * qv.x + kf.y * qv.y + kf.z * qv.z + kf.w * qv.w;
+                    }
+                }
+            }
+#pragma unroll
+            for (int g = 0; g < G; ++g) s[g] *= sc;
+        }
+        const uint32_t cnt = min(32u, hi - p0);
+        // this batch's V words (lane = 4 dims), requested before the softmax arithmetic
+        uint32_t vw[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i)
+            vw[i] = static_cast<uint32_t>(i) < cnt ? reinterpret_cast<const uint32_t*>(vc + static_cast<size_t>(p0 + i) * ATT_HD)[lane] : 0u;
+#pragma unroll
+        for (int g = 0; g < G; ++g) {
+            float bm = live ? s[g] : -CUDART_INF_F;
+            for (int o = 16; o > 0; o >>= 1) bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, o));
+            const float nm = fmaxf(mx[g], bm);
+            const float corr = __expf(mx[g] - nm);
+            const float pr = live ? __expf(s[g] - nm) : 0.f;
+            float bs = pr;
+            for (int o = 16; o > 0; o >>= 1) bs += __shfl_xor_sync(0xffffffffu, bs, o);
+            l[g] = l[g] * corr + bs;
+            mx[g] = nm;
+            acc[g][0] *= corr; acc[g][1] *= corr; acc[g][2] *= corr; acc[g][3] *= corr;
+            ps[warp][g][lane] = pr * vs;
+        }
+        __syncwarp();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+            const float4 vf = s8x4_to_float4(vw[i]);
+#pragma unroll
+            for (int g = 0; g < G; ++g) {
+                const float pw = ps[warp][g][i];                              // zero beyond the batch's end
+                acc[g][0] += pw * vf.x; acc[g][1] += pw * vf.y; acc[g][2] += pw * vf.z; acc[g][3] += pw * vf.w;
+            }
+        }
+        __syncwarp();
+    }
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+        if (lane == 0) { red_m[warp][g] = mx[g]; red_l[warp][g] = l[g]; }
+        *reinterpret_cast<float4*>(&red_acc[warp][g][4 * lane]) = make_float4(acc[g][0], acc[g][1], acc[g][2], acc[g][3]);
+    }
+    __syncthreads();
+    for (uint32_t i = threadIdx.x; i < G * ATT_HD; i += ATT_WARPS * 32) {
+        const int g = i / ATT_HD, d = i % ATT_HD;
+        float m_all = -CUDART_INF_F;
+#pragma unroll
+        for (int w = 0; w < ATT_WARPS; ++w) m_all = fmaxf(m_all, red_m[w][g]);
+        float l_all = 0.f, a = 0.f;
+#pragma unroll
+        for (int w = 0; w < ATT_WARPS; ++w) {
+            const float c = red_m[w][g] == -CUDART_INF_F ? 0.f : __expf(red_m[w][g] - m_all);
+            l_all += red_l[w][g] * c;
+            a += red_acc[w][g][d] * c;
+        }
+        float* dst = part + ((static_cast<size_t>(kvh) * nsplit + split) * G + g) * (2 + ATT_HD);
+        if (d == 0) { dst[0] = m_all; dst[1] = l_all; }
+        dst[2 + d] = a;
+    }
+    // the CTA that completes this KV head merges its splits
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const uint32_t old = atomicAdd(&counters[kvh], 1u);
+        is_last = old == nsplit - 1 ? 1u : 0u;
+        if (is_last) counters[kvh] = 0;
+    }
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
+    for (uint32_t i = threadIdx.x; i < G * ATT_HD; i += ATT_WARPS * 32) {
+        const uint32_t g = i / ATT_HD, d = i % ATT_HD;
+        const float* base = part + (static_cast<size_t>(kvh) * nsplit * G + g) * (2 + ATT_HD);
+        const size_t stride = static_cast<size_t>(G) * (2 + ATT_HD);
+        float m_all = -CUDART_INF_F;
+        for (uint32_t sp = 0; sp < nsplit; ++sp) m_all = fmaxf(m_all, __ldcg(base + sp * stride));
+        float l_all = 0.f, a = 0.f;
+#pragma unroll 4
+        for (uint32_t sp = 0; sp < nsplit; ++sp) {
+            const float* src = base + sp * stride;
+            const float ms = __ldcg(src);
+            const float c = ms == -CUDART_INF_F ? 0.f : __expf(ms - m_all);
+            l_all += __ldcg(src + 1) * c;
+            a += __ldcg(src + 2 + d) * c;
+        }
+        const float v = l_all > 0.f ? a / l_all : 0.f;
+        const size_t o = (static_cast<size_t>(kvh) * G + g) * ATT_HD + d;
+        if constexpr (sizeof(OUT) == 4) out[o] = v;
+        else out[o] = __float2bfloat16_rn(v);
+    }
+}
+
 // out[head][d] = sum over splits, renormalised.  grid = n_q heads, block = 128.
 template <typename OUT>
 __global__ void __launch_bounds__(ATT_HD) attn_combine_kernel(const float* __restrict__ part, uint32_t nsplit, uint32_t G,
@@ -394,38 +585,61 @@ __global__ void __launch_bounds__(PF_QT * G * 4) attn_prefill_kernel(const float
 }
 
 // ------------------------------------------------------------------ greedy arg-max (+ position advance)
-// One CTA: the index of the largest logit (the lowest index on ties, NaN never wins) goes to
-// *out_id; if pos != nullptr the position counter is advanced by one -- the decode loop's hand-over
-// to the next step, so that a captured step can be replayed without the host.
-__global__ void __launch_bounds__(1024) argmax_kernel(const float* __restrict__ logits, uint32_t n, uint32_t* __restrict__ out_id,
-                                                      uint32_t* __restrict__ pos) {
-    __shared__ float bv[32];
-    __shared__ uint32_t bi[32];
-    float best = -CUDART_INF_F;
-    uint32_t idx = 0xffffffffu;
-    for (uint32_t i = threadIdx.x; i < n; i += blockDim.x) {
-        const float v = logits[i];
-        if (v > best || (idx == 0xffffffffu && v == v)) { best = v; idx = i; }
-    }
-    for (int o = 16; o > 0; o >>= 1) {
-        const float ov = __shfl_xor_sync(0xffffffffu, best, o);
-        const uint32_t oi = __shfl_xor_sync(0xffffffffu, idx, o);
-        if (oi != 0xffffffffu && (idx == 0xffffffffu || ov > best || (ov == best && oi < idx))) { best = ov; idx = oi; }
-    }
+// The index of the largest logit (the lowest index on ties, NaN never wins) goes to *out_id; if
+// pos != nullptr the position counter is advanced by one -- the decode loop's hand-over to the next
+// step, so that a captured step can be replayed without the host.  ARGMAX_CTAS CTAs scan a slice
+// each and leave (value, index) in scratch; the CTA that arrives last picks the winner.
+constexpr int ARGMAX_CTAS = 64;
+
+__device__ __forceinline__ void argmax_take(float& best, uint32_t& idx, float ov, uint32_t oi) {
+    if (oi != 0xffffffffu && (idx == 0xffffffffu || ov > best || (ov == best && oi < idx))) { best = ov; idx = oi; }
+}
+__device__ __forceinline__ void argmax_block(float& best, uint32_t& idx, float* bv, uint32_t* bi) {
+    for (int o = 16; o > 0; o >>= 1) argmax_take(best, idx, __shfl_xor_sync(0xffffffffu, best, o), __shfl_xor_sync(0xffffffffu, idx, o));
     if ((threadIdx.x & 31) == 0) { bv[threadIdx.x >> 5] = best; bi[threadIdx.x >> 5] = idx; }
     __syncthreads();
     if (threadIdx.x < 32) {
         best = threadIdx.x < (blockDim.x >> 5) ? bv[threadIdx.x] : -CUDART_INF_F;
         idx = threadIdx.x < (blockDim.x >> 5) ? bi[threadIdx.x] : 0xffffffffu;
-        for (int o = 16; o > 0; o >>= 1) {
-            const float ov = __shfl_xor_sync(0xffffffffu, best, o);
-            const uint32_t oi = __shfl_xor_sync(0xffffffffu, idx, o);
-            if (oi != 0xffffffffu && (idx == 0xffffffffu || ov > best || (ov == best && oi < idx))) { best = ov; idx = oi; }
-        }
-        if (threadIdx.x == 0) {
-            *out_id = idx == 0xffffffffu ? 0u : idx;
-            if (pos) *pos += 1;
-        }
+        for (int o = 16; o > 0; o >>= 1) argmax_take(best, idx, __shfl_xor_sync(0xffffffffu, best, o), __shfl_xor_sync(0xffffffffu, idx, o));
+    }
+}
+
+// scratch: [0] arrival counter, then ARGMAX_CTAS (value, index) pairs
+__global__ void __launch_bounds__(256) argmax_kernel(const float* __restrict__ logits, uint32_t n, uint32_t* __restrict__ out_id,
+                                                     uint32_t* __restrict__ pos, uint32_t* __restrict__ scratch) {
+    __shared__ float bv[8];
+    __shared__ uint32_t bi[8];
+    __shared__ uint32_t is_last;
+    float best = -CUDART_INF_F;
+    uint32_t idx = 0xffffffffu;
+    for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
+        const float v = logits[i];
+        if (v > best || (idx == 0xffffffffu && v == v)) { best = v; idx = i; }
+    }
+    argmax_block(best, idx, bv, bi);
+    if (threadIdx.x == 0) {
+        scratch[2 + 2 * blockIdx.x] = __float_as_uint(best);
+        scratch[3 + 2 * blockIdx.x] = idx;
+        __threadfence();
+        const uint32_t old = atomicAdd(&scratch[0], 1u);
+        is_last = old == gridDim.x - 1 ? 1u : 0u;
+        if (is_last) scratch[0] = 0;
+    }
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
+    best = -CUDART_INF_F;
+    idx = 0xffffffffu;
+    if (threadIdx.x < gridDim.x) {
+        best = __uint_as_float(__ldcg(&scratch[2 + 2 * threadIdx.x]));
+        idx = __ldcg(&scratch[3 + 2 * threadIdx.x]);
+    }
+    __syncthreads();
+    argmax_block(best, idx, bv, bi);
+    if (threadIdx.x == 0) {
+        *out_id = idx == 0xffffffffu ? 0u : idx;
+        if (pos) *pos += 1;
     }
 }
 
@@ -467,7 +681,8 @@ cudaError_t launch_rope_kv_append(float* qkv, uint32_t m, uint32_t n_q, uint32_t
 }
 
 size_t attn_decode_scratch_bytes(uint32_t n_kv, uint32_t group, uint32_t n_splits) {
-    return static_cast<size_t>(n_kv) * n_splits * group * (2 + ATT_HD) * sizeof(float);
+    // 256 bytes of per-KV-head completion counters (the fused form), then the splits' partial results
+    return 256 + static_cast<size_t>(n_kv) * n_splits * group * (2 + ATT_HD) * sizeof(float);
 }
 
 cudaError_t launch_attn_decode(const float* q, uint32_t n_q, uint32_t n_kv, uint32_t hd, const KvCacheView& kv, const uint32_t* pos,
@@ -476,16 +691,40 @@ cudaError_t launch_attn_decode(const float* q, uint32_t n_q, uint32_t n_kv, uint
     const uint32_t G = n_q / n_kv;
     const dim3 grid(n_kv, n_splits);
     switch (G) {
-#define HF2Q_CASE(GG) case GG: attn_decode_kernel<GG><<<grid, ATT_WARPS * 32, 0, st>>>(q, n_q, kv.k_codes, kv.k_scale, kv.v_codes, kv.v_scale, kv.max_seq, pos, scratch); break;
+#define HF2Q_CASE(GG) case GG: attn_decode_kernel<GG><<<grid, ATT_WARPS * 32, 0, st>>>(q, n_q, kv.k_codes, kv.k_scale, kv.v_codes, kv.v_scale, kv.max_seq, pos, scratch + 64); break;
         HF2Q_CASE(1) HF2Q_CASE(2) HF2Q_CASE(4) HF2Q_CASE(8)
 #undef HF2Q_CASE
         default: return cudaErrorInvalidValue;
     }
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return e;
-    if (out_dtype == HF2Q_DT_F32) attn_combine_kernel<float><<<n_q, ATT_HD, 0, st>>>(scratch, n_splits, G, static_cast<float*>(out));
-    else if (out_dtype == HF2Q_DT_BF16) attn_combine_kernel<__nv_bfloat16><<<n_q, ATT_HD, 0, st>>>(scratch, n_splits, G, static_cast<__nv_bfloat16*>(out));
+    if (out_dtype == HF2Q_DT_F32) attn_combine_kernel<float><<<n_q, ATT_HD, 0, st>>>(scratch + 64, n_splits, G, static_cast<float*>(out));
+    else if (out_dtype == HF2Q_DT_BF16) attn_combine_kernel<__nv_bfloat16><<<n_q, ATT_HD, 0, st>>>(scratch + 64, n_splits, G, static_cast<__nv_bfloat16*>(out));
     else return cudaErrorInvalidValue;
+    return cudaGetLastError();
+}
+
+cudaError_t launch_attn_decode_fused(const float* qkv, uint32_t n_q, uint32_t n_kv, uint32_t hd, float theta, const KvCacheView& kv,
+                                     const uint32_t* pos, void* out, uint32_t out_dtype, float* scratch, uint32_t n_splits, uint32_t* status,
+                                     cudaStream_t st) {
+    if (hd != ATT_HD || n_kv == 0 || n_q % n_kv || n_q / n_kv > ATT_MAXG) return cudaErrorInvalidValue;
+    const uint32_t G = n_q / n_kv;
+    const dim3 grid(n_kv, n_splits);
+    // scratch: [n_kv] counters (256 bytes reserved), then the partial results
+    uint32_t* counters = reinterpret_cast<uint32_t*>(scratch);
+    float* part = scratch + 64;
+    const float qs = 1.0f / sqrtf(static_cast<float>(hd));
+    const bool f32 = out_dtype == HF2Q_DT_F32;
+    if (!f32 && out_dtype != HF2Q_DT_BF16) return cudaErrorInvalidValue;
+    switch (G) {
+#define HF2Q_CASE(GG) case GG: \
+        if (f32) attn_decode_fused_kernel<GG, float><<<grid, ATT_WARPS * 32, 0, st>>>(qkv, n_q, n_kv, theta, qs, kv.k_codes, kv.k_scale, kv.v_codes, kv.v_scale, kv.max_seq, pos, part, counters, static_cast<float*>(out), status); \
+        else attn_decode_fused_kernel<GG, __nv_bfloat16><<<grid, ATT_WARPS * 32, 0, st>>>(qkv, n_q, n_kv, theta, qs, kv.k_codes, kv.k_scale, kv.v_codes, kv.v_scale, kv.max_seq, pos, part, counters, static_cast<__nv_bfloat16*>(out), status); \
+        break;
+        HF2Q_CASE(1) HF2Q_CASE(2) HF2Q_CASE(4) HF2Q_CASE(8)
+#undef HF2Q_CASE
+        default: return cudaErrorInvalidValue;
+    }
     return cudaGetLastError();
 }
 
@@ -517,8 +756,8 @@ cudaError_t launch_attn_prefill(const float* qkv, uint32_t row_stride, uint32_t 
     }
 }
 
-cudaError_t launch_argmax(const float* logits, uint32_t n, uint32_t* out_id, uint32_t* pos, cudaStream_t st) {
-    argmax_kernel<<<1, 1024, 0, st>>>(logits, n, out_id, pos);
+cudaError_t launch_argmax(const float* logits, uint32_t n, uint32_t* out_id, uint32_t* pos, uint32_t* scratch, cudaStream_t st) {
+    argmax_kernel<<<ARGMAX_CTAS, 256, 0, st>>>(logits, n, out_id, pos, scratch);
     return cudaGetLastError();
 }
 

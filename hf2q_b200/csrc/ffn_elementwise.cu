@@ -62,7 +62,57 @@ __global__ void __launch_bounds__(256) rowdot_kernel(const float* __restrict__ x
     (void)n_tokens;
 }
 
+// Router logits of an MoE layer: out[t, e] = sum_h x[t, h] * w[e, h], all f32 (the router is a small
+// dense f32 matrix in the reference as well: phase 1 of the six-phase graph at gpu_ffn.rs:2347-2359).
+// Classic shared-memory tiling: a CTA computes 64 tokens x 64 experts, 4 x 4 outputs per thread.
+constexpr int RT = 64, RKT = 16;
+__global__ void __launch_bounds__(256) router_logits_kernel(const void* __restrict__ x, uint32_t x_bf16, const float* __restrict__ w,
+                                                            float* __restrict__ out, uint32_t n_tokens, uint32_t n_experts, uint32_t h) {
+    __shared__ float xs[RKT][RT + 4], ws[RKT][RT + 4];
+    const uint32_t t0 = blockIdx.y * RT, e0 = blockIdx.x * RT;
+    const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;          // outputs: tokens 4ty..4ty+3, experts 4tx..4tx+3
+    float acc[4][4] = {};
+    for (uint32_t k0 = 0; k0 < h; k0 += RKT) {
+        for (int i = threadIdx.x; i < RT * RKT; i += 256) {
+            const int r = i / RKT, c = i % RKT;
+            const uint32_t t = t0 + r, e = e0 + r, kk = k0 + c;
+            float xv = 0.f;
+            if (t < n_tokens && kk < h)
+                xv = x_bf16 ? __bfloat162float(static_cast<const __nv_bfloat16*>(x)[static_cast<size_t>(t) * h + kk])
+                            : static_cast<const float*>(x)[static_cast<size_t>(t) * h + kk];
+            xs[c][r] = xv;
+            ws[c][r] = (e < n_experts && kk < h) ? w[static_cast<size_t>(e) * h + kk] : 0.f;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int c = 0; c < RKT; ++c) {
+            const float4 a = *reinterpret_cast<const float4*>(&xs[c][4 * ty]);
+            const float4 b = *reinterpret_cast<const float4*>(&ws[c][4 * tx]);
+            const float av[4] = {a.x, a.y, a.z, a.w}, bv[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) acc[i][j] += av[i] * bv[j];
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const uint32_t t = t0 + 4 * ty + i, e = e0 + 4 * tx + j;
+            if (t < n_tokens && e < n_experts) out[static_cast<size_t>(t) * n_experts + e] = acc[i][j];
+        }
+}
+
 }  // namespace
+
+cudaError_t launch_router_logits(const void* x, uint32_t x_bf16, const float* w, float* out, uint32_t n_tokens, uint32_t n_experts,
+                                 uint32_t h, cudaStream_t st) {
+    const dim3 grid((n_experts + RT - 1) / RT, (n_tokens + RT - 1) / RT);
+    router_logits_kernel<<<grid, 256, 0, st>>>(x, x_bf16, w, out, n_tokens, n_experts, h);
+    return cudaGetLastError();
+}
 
 cudaError_t launch_silu_mul(const float* gate, const float* up, float* out, uint64_t n, int sm_count, cudaStream_t st) {
     const bool vec = (reinterpret_cast<uintptr_t>(gate) | reinterpret_cast<uintptr_t>(up) | reinterpret_cast<uintptr_t>(out)) % 16 == 0;

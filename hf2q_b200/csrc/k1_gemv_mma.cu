@@ -93,6 +93,12 @@ struct MParams {
     uint32_t g_peer_ctas[8];   // CTAs of the same product on every rank (their arrivals at this rank)
     uint32_t g_nranks, g_rank, g_ntotal, g_col0, g_wait;
     long long wait_limit;      // clock ticks a wait for other ranks may take before it gives up
+    // split-k (EXT): k is cut into `split` parts of one 2048-element slice each, part = blockIdx.y; every
+    // part writes its partial sums to y + part * m * n (a scratch buffer) and a second kernel adds the parts
+    const float* norm_w;       // != nullptr: x is RMS-normalised with this weight (and norm_eps) while the panel is built
+    float norm_eps;
+    uint32_t split, k_last;    // parts (0 = off); elements of the last part
+    uint32_t kx;               // elements between activation rows of x in global memory (k of the whole product)
     uint32_t* status;
 };
 
@@ -365,7 +371,8 @@ __device__ __forceinline__ void half_legacy(const uint8_t* p0, const uint8_t* p1
 template <uint32_t TYPE, int CTH, int U, bool INPLACE>
 __device__ __forceinline__ void build_panel(const void* x, bool x_bf16, uint32_t nslots, uint32_t k, uint32_t xpitch,
                                          uint32_t* status, uint8_t* xh, uint8_t* sxp, uint32_t sx_slot_bytes,
-                                         uint32_t xrow_idx, uint32_t k0, uint32_t klen, uint64_t* xbar, uint32_t xparity) {
+                                         uint32_t xrow_idx, uint32_t k0, uint32_t klen, uint64_t* xbar, uint32_t xparity,
+                                         const float* norm_w, float norm_eps, float* nscratch) {
     constexpr bool K45 = TYPE == HF2Q_TYPE_Q4_K || TYPE == HF2Q_TYPE_Q5_K;
     constexpr bool LEG = TYPE == HF2Q_TYPE_Q4_0 || TYPE == HF2Q_TYPE_Q8_0;
     constexpr uint32_t SXB = K45 ? 32 : 64;
@@ -468,6 +475,59 @@ __device__ __forceinline__ void build_panel(const void* x, bool x_bf16, uint32_t
         } else {
             bf16_rounds(std::integral_constant<int, U>{}, std::integral_constant<int, 1>{});
         }
+    } else if (norm_w) {
+        // f32 input with the RMSNorm in front of the product fused in (rms_norm_rows, forward_cpu.rs:36-48:
+        // x * rsqrt(mean(x^2) + eps) * weight).  The whole row is resident (k <= 8 * CTH, one chunk of eight
+        // elements per thread and activation row, at most four rows): sums of squares per row across the
+        // consumer threads, then scale, split into hi + lo halves and store as below.
+        asm volatile("griddepcontrol.wait;" ::: "memory");               // x may be an earlier kernel's output
+        const uint32_t ntok = nslots >> 1, pos = ctid;
+        const bool have = pos < k8;
+        float v[4][8], ss[4] = {0.f, 0.f, 0.f, 0.f};
+        const float* src = static_cast<const float*>(x) + static_cast<size_t>(xrow_idx) * k + 8 * pos;
+#pragma unroll
+        for (int t = 0; t < 4; ++t) {
+            if (static_cast<uint32_t>(t) < ntok && have) {
+                const float4* q = reinterpret_cast<const float4*>(src + static_cast<size_t>(t) * k);
+                const float4 a = __ldcg(q), b = __ldcg(q + 1);
+                v[t][0] = a.x; v[t][1] = a.y; v[t][2] = a.z; v[t][3] = a.w; v[t][4] = b.x; v[t][5] = b.y; v[t][6] = b.z; v[t][7] = b.w;
+#pragma unroll
+                for (int j = 0; j < 8; ++j) ss[t] += v[t][j] * v[t][j];
+            }
+        }
+#pragma unroll
+        for (int t = 0; t < 4; ++t)
+            for (int o = 16; o > 0; o >>= 1) ss[t] += __shfl_xor_sync(0xffffffffu, ss[t], o);
+        if (lane == 0)
+#pragma unroll
+            for (int t = 0; t < 4; ++t) nscratch[(ctid >> 5) * 4 + t] = ss[t];
+        asm volatile("bar.sync 1, %0;" ::"n"(CTH));
+        float inv[4];
+#pragma unroll
+        for (int t = 0; t < 4; ++t) {
+            float tot = 0.f;
+            for (int w = 0; w < CTH / 32; ++w) tot += nscratch[w * 4 + t];
+            inv[t] = 1.0f / sqrtf(tot / static_cast<float>(klen) + norm_eps);
+        }
+        if (have) {                                                      // (k8 is a multiple of 32: whole warps)
+            const float4 wa = __ldg(reinterpret_cast<const float4*>(norm_w + 8 * pos)), wb = __ldg(reinterpret_cast<const float4*>(norm_w + 8 * pos) + 1);
+            const float w8[8] = {wa.x, wa.y, wa.z, wa.w, wb.x, wb.y, wb.z, wb.w};
+            for (uint32_t t = 0; t < ntok; ++t) {
+                __half2 hi[4], lo[4];
+                float acc_hi = 0.f, acc_lo = 0.f;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const float ra = v[t][2 * j] * inv[t] * w8[2 * j], rb = v[t][2 * j + 1] * inv[t] * w8[2 * j + 1];
+                    const float a = fminf(fmaxf(ra, -65504.0f), 65504.0f), b = fminf(fmaxf(rb, -65504.0f), 65504.0f);
+                    clipped |= static_cast<uint32_t>(!(a == ra)) | static_cast<uint32_t>(!(b == rb));
+                    hi[j] = pack(a, b, acc_hi);
+                    const float2 f = __half22float2(hi[j]);
+                    lo[j] = pack(a - f.x, b - f.y, acc_lo);
+                }
+                store(2 * t, pos, hi, acc_hi);
+                store(2 * t + 1, pos, lo, acc_lo);
+            }
+        }
     } else {
     asm volatile("griddepcontrol.wait;" ::: "memory");                   // x may be an earlier kernel's output
     for (uint32_t pos = ctid; pos < k8; pos += CTH) {
@@ -555,11 +615,18 @@ __global__ void __launch_bounds__((NTEAMS * TEAM + 2) * 32, 1) gemv_mma_kernel(c
     float* scr = red + 2 * CW * 128;                                            // [CW][16][8]
     uint8_t* xh = reinterpret_cast<uint8_t*>(scr + CW * 16 * 8);                 // [nslots][xpitch]
     uint8_t* sxp = xh + p.nslots * p.xpitch;
-    const uint32_t kphase = min(spp * SLICE_ELEMS, p.k);                        // elements of k resident at a time
+    const uint32_t kphase = min(spp * SLICE_ELEMS, (EXT && p.split) ? static_cast<uint32_t>(SLICE_ELEMS) : p.k);   // elements of k resident at a time
     const uint32_t sx_slot_bytes = (kphase >> 8) * SXB + 16;                    // K45 / Q6 panels; +16: columns 4 banks apart
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     uint32_t slot = blockIdx.y;
+    // split-k: this CTA works on slice `part` of every row of its groups; to the loops below that is a
+    // product with one-slice rows whose copies start `part` slices into the row
+    const uint32_t part = (EXT && p.split) ? blockIdx.y : 0u;
+    if (EXT && p.split) slot = 0;
+    const uint32_t kloc = (EXT && p.split) ? (part + 1 == p.split ? p.k_last : static_cast<uint32_t>(SLICE_ELEMS)) : p.k;
+    const void* xbase = (EXT && p.split) ? static_cast<const void*>(static_cast<const uint8_t*>(p.x) + static_cast<size_t>(part) * SLICE_ELEMS * (p.x_bf16 ? 2u : 4u))
+                                         : p.x;
     const uint8_t* wbase = p.w;
     float* ybase = p.y;
     const uint8_t* wbase2 = EXT ? p.w2 : nullptr;     // fused SwiGLU: the up tensor (of the same expert)
@@ -575,7 +642,7 @@ __global__ void __launch_bounds__((NTEAMS * TEAM + 2) * 32, 1) gemv_mma_kernel(c
         if (EXT && p.w2) wbase2 += static_cast<uint64_t>(slot_ok ? e : 0) * p.expert_stride;
         xrow_idx = slot / p.top_k;
     }
-    float* yout = ybase + static_cast<size_t>(slot) * p.n;
+    float* yout = ybase + ((EXT && p.split) ? static_cast<size_t>(part) * p.m * p.n : static_cast<size_t>(slot) * p.n);
     // row groups of this CTA: blockIdx.x, blockIdx.x + gridDim.x, ...
     const uint32_t own = blockIdx.x < p.ngroups ? (p.ngroups - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
     // fused SwiGLU: every row group is walked twice in a row, first in the gate matrix, then in the up matrix
@@ -629,7 +696,7 @@ __global__ void __launch_bounds__((NTEAMS * TEAM + 2) * 32, 1) gemv_mma_kernel(c
                             alive = __all_sync(0xffffffffu, alive);
                             if (!alive) return;
                         }
-                        const uint32_t off = s * p.slice_bytes;
+                        const uint32_t off = (s + part) * p.slice_bytes;
                         const uint32_t bytes = min(p.slice_bytes, p.row_bytes - off);
                         if (p.use_tmap) {
                             // one tensor copy for the whole stage: the copy engine spends ~15 cycles per copy
@@ -640,7 +707,7 @@ __global__ void __launch_bounds__((NTEAMS * TEAM + 2) * 32, 1) gemv_mma_kernel(c
                                 asm volatile(
                                     "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%2, %3}], [%4], %5;"
                                     ::"r"(smem_u32(ring + st * stage_bytes)), "l"(reinterpret_cast<uint64_t>(tmap)),
-                                      "r"(static_cast<int>(s * (p.slice_bytes >> 3))), "r"(static_cast<int>(row0)), "r"(smem_u32(&full[st])),
+                                      "r"(static_cast<int>((s + part) * (p.slice_bytes >> 3))), "r"(static_cast<int>(row0)), "r"(smem_u32(&full[st])),
                                       "l"(wpolicy)
                                     : "memory");
                             }
@@ -770,7 +837,7 @@ __global__ void __launch_bounds__((NTEAMS * TEAM + 2) * 32, 1) gemv_mma_kernel(c
     const int ctid = threadIdx.x;
     // Ahead of the dependency wait: ask for the activations' lines (and their address translation).
     // A prefetch returns no data, so it may run while the previous kernel is still writing them.
-    if (!p.ids) {
+    if (!p.ids && !(EXT && p.split)) {
         const uint32_t xbytes = p.k * (p.x_bf16 ? 2u : 4u), m_rows = p.x_bf16 ? p.nslots : p.nslots >> 1;
         for (uint32_t off = static_cast<uint32_t>(ctid) * 128u; off < m_rows * xbytes; off += CTH * 128u)
             asm volatile("prefetch.global.L2 [%0];" ::"l"(static_cast<const uint8_t*>(p.x) + off));
@@ -800,7 +867,7 @@ __global__ void __launch_bounds__((NTEAMS * TEAM + 2) * 32, 1) gemv_mma_kernel(c
     const uint32_t team = static_cast<uint32_t>(warp) / TEAM;
     const uint8_t* ring_g = ring + g * pitch;                            // this lane's first row in slot 0
     float* red_t = red + team * (TEAM * 128) + g * 8 + 2 * t;              // + block * 128: this team's partial sums
-    const uint32_t last_slice = nslices - 1, last_nblk = p.last_nblk;
+    const uint32_t last_slice = nslices - 1, last_nblk = (EXT && p.split) ? kloc >> 8 : p.last_nblk;
     uint32_t blk = static_cast<uint32_t>(warp) % TEAM;                   // block of the stage this warp takes; rotates
     uint32_t fl_base = 0;                                                // flushes of earlier phases
 
@@ -816,8 +883,8 @@ __global__ void __launch_bounds__((NTEAMS * TEAM + 2) * 32, 1) gemv_mma_kernel(c
                 gather_wait_source(p.g_flag[p.g_rank], ctid, p.wait_limit, p.status);
             asm volatile("bar.sync 1, %0;" ::"n"(CTH));
         }
-        build_panel<TYPE, CTH, (PHASED ? 2 : 8), PHASED>(p.x, p.x_bf16 != 0, p.nslots, p.k, p.xpitch, p.status, xh, sxp, sx_slot_bytes, xrow_idx, k0,
-                               min(nsp * SLICE_ELEMS, p.k - k0), xbar, pi & 1u);
+        build_panel<TYPE, CTH, (PHASED ? 2 : 8), PHASED>(xbase, p.x_bf16 != 0, p.nslots, p.kx, p.xpitch, p.status, xh, sxp, sx_slot_bytes, xrow_idx, k0,
+                               min(nsp * SLICE_ELEMS, kloc - k0), xbar, pi & 1u, p.norm_w, p.norm_eps, scr);
         if (s0 == 0) cta_sync_n<(NTEAMS * TEAM + 2) * 32>();             // panel + all barrier initialisations
         else asm volatile("bar.sync 1, %0;" ::"n"(CTH));
 
@@ -1062,6 +1129,7 @@ cudaError_t launch_mma_tt(MParams p, uint32_t slots, const Plan& pl, const Devic
     const uint32_t kphase = longest * SLICE_ELEMS < p.k ? longest * SLICE_ELEMS : p.k;
     p.xpitch = 2 * kphase + 32;                   // activation rows land 8 banks apart
     uint32_t gx = (static_cast<uint32_t>(dev.sm_count) + slots - 1) / slots;      // one CTA per SM
+    if (p.split) gx = static_cast<uint32_t>(dev.sm_count) / slots;                // split-k: all parts of a group run at the same time
     if (gx > p.ngroups) gx = p.ngroups;
     if (gx < 1) gx = 1;
     static const int pdl = env_int("HF2Q_CUDA_PDL", 1);
@@ -1084,19 +1152,78 @@ cudaError_t launch_mma_tt(MParams p, uint32_t slots, const Plan& pl, const Devic
     return cudaLaunchKernelEx(&cfg, kern, tmap, tmap2, p);
 }
 
+// Adds the split-k parts: y[i] = sum over parts of scratch[part][i] (+ residual[i]), parts in index order.
+__global__ void __launch_bounds__(256) splitk_reduce_kernel(const float* __restrict__ scratch, uint32_t parts, uint64_t count,
+                                                            const float* __restrict__ residual, float* __restrict__ y) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");                    // the parts are the previous kernel's output
+    const uint64_t stride = static_cast<uint64_t>(gridDim.x) * blockDim.x;
+    for (uint64_t i = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < count; i += stride) {
+        float v = __ldcg(scratch + i);
+        for (uint32_t pt = 1; pt < parts; ++pt) v += __ldcg(scratch + pt * count + i);
+        if (residual) v += residual[i];
+        y[i] = v;
+    }
+}
+
+cudaError_t launch_splitk_reduce(const float* scratch, uint32_t parts, uint64_t count, const float* residual, float* y, const DeviceInfo& dev,
+                                 cudaStream_t st) {
+    static const int pdl = env_int("HF2Q_CUDA_PDL", 1);
+    cudaLaunchConfig_t cfg{};
+    const uint64_t want = (count + 255) / 256, cap = static_cast<uint64_t>(dev.sm_count) * 4;
+    cfg.gridDim = dim3(static_cast<unsigned>(want < cap ? want : cap));
+    cfg.blockDim = dim3(256);
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, splitk_reduce_kernel, scratch, parts, count, residual, y);
+}
+
 template <uint32_t TYPE>
-cudaError_t launch_mma_t(MParams p, uint32_t slots, const DeviceInfo& dev, cudaStream_t st) {
+cudaError_t launch_mma_t(MParams p, uint32_t slots, const DeviceInfo& dev, cudaStream_t st, const GemvArgs& a) {
     const size_t limit = static_cast<size_t>(dev.max_smem_optin);
     // two teams: a third (26 warps, 72 registers) measured no faster
     const Plan pl = make_plan(TYPE, p.k, p.nslots, 2, limit);
     if (!pl.stages) return cudaErrorInvalidConfiguration;
     const bool phased = pl.phase_base != p.nslices;
     if (phased && p.swiglu) return cudaErrorInvalidConfiguration;       // the gate sums cannot wait across phases
+    // the fused RMSNorm needs the whole f32 row in one panel, one chunk of eight elements per consumer thread
+    if (p.norm_w && (phased || p.x_bf16 || p.ids || p.k > 8u * 2 * TEAM * 32 || p.nslots > 8)) return cudaErrorInvalidConfiguration;
     const bool ext = p.g_nranks != 0 || p.w2 != nullptr;
     if (p.sub_groups > 1)                                                                          // one short slice per row
         return ext ? launch_mma_tt<TYPE, 2, false, true, true>(p, slots, pl, dev, st) : launch_mma_tt<TYPE, 2, false, true, false>(p, slots, pl, dev, st);
-    if (phased)
+    if (phased) {
+        // Rows too long for the activation panel.  Preferred: split k over the CTAs -- every CTA keeps ONE
+        // slice of the activations and streams that slice of all its row groups, the parts meet in a
+        // scratch buffer and a small second kernel adds them in part order (deterministic).  Needs the
+        // context's scratch, a dense plain product and at least as many SMs as parts; otherwise the CTA
+        // walks its groups once per k-phase (below).
+        static const bool split_on = env_int("HF2Q_CUDA_MMA_SPLITK", 1) != 0;                      // tuning aid
+        const uint32_t parts = p.nslices;
+        const uint64_t count = static_cast<uint64_t>(p.m) * p.n;
+        if (split_on && !ext && !p.ids && slots == 1 && a.splitk_scratch && parts * count * 4 <= a.splitk_bytes &&
+            parts <= static_cast<uint32_t>(dev.sm_count)) {
+            MParams q = p;
+            q.split = parts;
+            q.k_last = p.k - (parts - 1) * SLICE_ELEMS;
+            q.k = SLICE_ELEMS;
+            q.nslices = 1;
+            q.last_nblk = SLICE_ELEMS >> 8;
+            q.y = a.splitk_scratch;
+            q.residual = nullptr;
+            const Plan pl1 = make_plan(TYPE, SLICE_ELEMS, p.nslots, 2, limit);
+            if (pl1.stages && pl1.phase_base == 1) {
+                cudaError_t e = launch_mma_tt<TYPE, 2, false, false, true>(q, parts, pl1, dev, st);
+                if (e != cudaSuccess) return e;
+                if (a.n_launches) *a.n_launches = 2;
+                return launch_splitk_reduce(a.splitk_scratch, parts, count, p.residual, p.y, dev, st);
+            }
+        }
         return ext ? launch_mma_tt<TYPE, 2, true, false, true>(p, slots, pl, dev, st) : launch_mma_tt<TYPE, 2, true, false, false>(p, slots, pl, dev, st);
+    }
     return ext ? launch_mma_tt<TYPE, 2, false, false, true>(p, slots, pl, dev, st) : launch_mma_tt<TYPE, 2, false, false, false>(p, slots, pl, dev, st);
 }
 
@@ -1140,6 +1267,13 @@ uint32_t gemv_mma_max_rows(uint32_t type, uint32_t k, uint32_t x_dtype, const De
     return rows;
 }
 
+// whether a launch can take m f32 activation rows with the RMSNorm fused into its panel build
+bool gemv_mma_norm_ok(uint32_t type, uint32_t k, uint32_t m, const DeviceInfo& dev) {
+    if (m == 0 || m > 4 || k % 256 || k > 8u * 2 * TEAM * 32 || type_is_fallback32(type)) return false;
+    const Plan pl = make_plan(type, k, 2 * m, 2, static_cast<size_t>(dev.max_smem_optin));
+    return pl.stages && pl.phase_base == (k + SLICE_ELEMS - 1) / SLICE_ELEMS;
+}
+
 bool gemv_mma_swiglu_ok(uint32_t type, uint32_t k, uint32_t m, uint32_t x_dtype, const DeviceInfo& dev) {
     const uint32_t nslots = x_dtype == HF2Q_DT_BF16 ? m : 2 * m;
     if (m == 0 || nslots > 8 || k % 256 || sub_groups_of(k) > 1 || type_is_fallback32(type)) return false;
@@ -1157,6 +1291,8 @@ cudaError_t launch_gemv_mma(const GemvArgs& a, const DeviceInfo& dev, cudaStream
     p.pair_slots = a.swiglu ? 0xffffffffu : a.slots;
     p.swiglu = a.swiglu ? 1u : 0u;
     p.residual = a.residual;
+    p.norm_w = a.norm_weight;
+    p.norm_eps = a.norm_eps;
     p.x = a.x;
     p.y = a.y;
     p.ids = a.ids;
@@ -1167,6 +1303,7 @@ cudaError_t launch_gemv_mma(const GemvArgs& a, const DeviceInfo& dev, cudaStream
     if (p.nslots > 8) return cudaErrorInvalidValue;
     p.n = a.n;
     p.k = a.k;
+    p.kx = a.k;
     p.top_k = a.top_k ? a.top_k : 1;
     p.n_experts = a.n_experts;
     p.row_bytes = a.k / g.elems * g.bytes;
@@ -1190,11 +1327,11 @@ cudaError_t launch_gemv_mma(const GemvArgs& a, const DeviceInfo& dev, cudaStream
     if (a.swiglu && (!a.w2 || a.gather || a.residual || p.sub_groups > 1)) return cudaErrorInvalidValue;
     const uint32_t slots = a.w2 && !a.swiglu ? 2 * a.slots : a.slots;
     switch (a.type) {
-        case HF2Q_TYPE_Q4_0: return launch_mma_t<HF2Q_TYPE_Q4_0>(p, slots, dev, st);
-        case HF2Q_TYPE_Q8_0: return launch_mma_t<HF2Q_TYPE_Q8_0>(p, slots, dev, st);
-        case HF2Q_TYPE_Q4_K: return launch_mma_t<HF2Q_TYPE_Q4_K>(p, slots, dev, st);
-        case HF2Q_TYPE_Q5_K: return launch_mma_t<HF2Q_TYPE_Q5_K>(p, slots, dev, st);
-        case HF2Q_TYPE_Q6_K: return launch_mma_t<HF2Q_TYPE_Q6_K>(p, slots, dev, st);
+        case HF2Q_TYPE_Q4_0: return launch_mma_t<HF2Q_TYPE_Q4_0>(p, slots, dev, st, a);
+        case HF2Q_TYPE_Q8_0: return launch_mma_t<HF2Q_TYPE_Q8_0>(p, slots, dev, st, a);
+        case HF2Q_TYPE_Q4_K: return launch_mma_t<HF2Q_TYPE_Q4_K>(p, slots, dev, st, a);
+        case HF2Q_TYPE_Q5_K: return launch_mma_t<HF2Q_TYPE_Q5_K>(p, slots, dev, st, a);
+        case HF2Q_TYPE_Q6_K: return launch_mma_t<HF2Q_TYPE_Q6_K>(p, slots, dev, st, a);
         default: return cudaErrorInvalidValue;
     }
 }

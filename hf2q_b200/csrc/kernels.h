@@ -67,6 +67,15 @@ struct GemvArgs {
     bool swiglu = false;
     // y = residual + product (dense and routed mat-vec; may alias y); nullptr = plain product
     const float* residual = nullptr;
+    // RMSNorm fused in front of the product: x is normalised with this f32 [k] weight while the
+    // activation panel is built (f32 x, m <= 4, the whole row resident); nullptr = none
+    const float* norm_weight = nullptr;
+    float norm_eps = 0.f;
+    // scratch for the split-k form of long rows (the context's; nullptr = k-phases instead), and where to
+    // report that a call took two launches
+    float* splitk_scratch = nullptr;
+    uint64_t splitk_bytes = 0;
+    int* n_launches = nullptr;
 };
 struct DeviceInfo {
     int sm_count;
@@ -79,6 +88,7 @@ cudaError_t launch_gemv(const GemvArgs& a, const DeviceInfo& dev, cudaStream_t s
 bool gemv_mma_supported(const GemvArgs& a);
 uint32_t gemv_mma_max_rows(uint32_t type, uint32_t k, uint32_t x_dtype, const DeviceInfo& dev);
 cudaError_t launch_gemv_mma(const GemvArgs& a, const DeviceInfo& dev, cudaStream_t st);
+bool gemv_mma_norm_ok(uint32_t type, uint32_t k, uint32_t m, const DeviceInfo& dev);
 // whether one launch can take m activation rows with the SwiGLU epilogue (all of k resident, k > 1024)
 bool gemv_mma_swiglu_ok(uint32_t type, uint32_t k, uint32_t m, uint32_t x_dtype, const DeviceInfo& dev);
 // CTAs along x that launch_gemv_mma uses for a dense product of n rows (one per SM, at most one per row group)
@@ -145,13 +155,21 @@ cudaError_t launch_attn_decode(const float* q, uint32_t n_q, uint32_t n_kv, uint
                                void* out, uint32_t out_dtype, float* scratch, uint32_t n_splits, cudaStream_t st);
 cudaError_t launch_attn_prefill(const float* qkv, uint32_t row_stride, uint32_t m, uint32_t n_q, uint32_t n_kv, uint32_t hd,
                                 const KvCacheView& kv, uint32_t pos0, void* out, uint32_t out_dtype, uint32_t out_stride, cudaStream_t st);
-cudaError_t launch_argmax(const float* logits, uint32_t n, uint32_t* out_id, uint32_t* pos, cudaStream_t st);
+// scratch: 1 + 2 * 64 + 1 zero-initialised words owned by the caller (the context), one arg-max at a time
+cudaError_t launch_argmax(const float* logits, uint32_t n, uint32_t* out_id, uint32_t* pos, uint32_t* scratch, cudaStream_t st);
+// rotary embedding of the query, append of the new position, split attention and merge in one launch;
+// scratch as for launch_attn_decode (its first 256 bytes are completion counters and must start zeroed)
+cudaError_t launch_attn_decode_fused(const float* qkv, uint32_t n_q, uint32_t n_kv, uint32_t hd, float theta, const KvCacheView& kv,
+                                     const uint32_t* pos, void* out, uint32_t out_dtype, float* scratch, uint32_t n_splits, uint32_t* status,
+                                     cudaStream_t st);
 cudaError_t launch_add(float* x, const float* d, uint64_t n, int sm_count, cudaStream_t st);
 
 // element-wise glue of the FFN builders (ffn_elementwise.cu)
 cudaError_t launch_silu_mul(const float* gate, const float* up, float* out, uint64_t n, int sm_count, cudaStream_t st);
 cudaError_t launch_moe_combine(const float* y, const float* w, const float* shared, const float* gate_logit, const float* residual,
                                float* out, uint32_t n_tokens, uint32_t top_k, uint32_t h, cudaStream_t st);
+cudaError_t launch_router_logits(const void* x, uint32_t x_bf16, const float* w, float* out, uint32_t n_tokens, uint32_t n_experts,
+                                 uint32_t h, cudaStream_t st);
 cudaError_t launch_rowdot(const float* x, const float* v, float* out, uint32_t n_tokens, uint32_t h, cudaStream_t st);
 
 }  // namespace hf2q

@@ -70,7 +70,8 @@ def build_dense_ffn_layer_gpu_q(ctx: ops.GpuContext, x: torch.Tensor, w: DenseFf
         return y
     ops.quantized_matmul_ggml(ctx, c, w.down_q, y, w.down_q.matmul_params(m))
     if residual is not None:
-        y += residual
+        r = residual.contiguous().float()
+        ctx._check(ctx._lib.hf2q_cuda_add(ctx._h, ctx._stream(), y.data_ptr(), r.data_ptr(), y.numel()))
     return y
 
 
@@ -83,7 +84,9 @@ def build_moe_ffn_layer_gpu_q(ctx: ops.GpuContext, x: torch.Tensor, w: MoeFfnWei
     E, k, inter = w.num_experts, w.num_experts_per_tok, w.moe_intermediate_size
     x = x.contiguous()
     # the router is a small dense f32 matrix in the reference as well (gpu_ffn.rs:2347-2359 phase 1)
-    logits = torch.matmul(x.float(), w.router.t()).contiguous()
+    logits = torch.empty((T, E), dtype=torch.float32, device=x.device)
+    ctx._check(ctx._lib.hf2q_cuda_router_logits(ctx._h, ctx._stream(), x.data_ptr(), ops._act(x, "x"), w.router.data_ptr(),
+                                                logits.data_ptr(), T, E, hidden))
     ids, wts = ops.moe_softmax_topk(ctx, logits, k)
     rows = T * k
     sg = ops.expert_stride(w.ggml_type_gate_up, inter, hidden)

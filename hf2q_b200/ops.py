@@ -236,8 +236,14 @@ class _RowSegment(C.Structure):                  # hf2q_row_segment in include/h
     _fields_ = [("w", C.c_void_p), ("rows", C.c_uint32), ("ggml_type", C.c_uint32)]
 
 
+def norm_supported(ctx: GpuContext, m: int, weight: "QuantWeight") -> bool:
+    """Whether a product of m f32 rows against `weight` can take the RMSNorm fused into its launch."""
+    return bool(ctx._lib.hf2q_cuda_norm_supported(ctx._h, m, weight.cols, weight.ggml_type))
+
+
 def quantized_matmul_segments(ctx: GpuContext, input: torch.Tensor, weights, out: torch.Tensor, m: int,
-                              workspace: torch.Tensor | None = None) -> None:
+                              workspace: torch.Tensor | None = None, norm_weight: torch.Tensor | None = None,
+                              norm_eps: float = 0.0) -> None:
     """out[m, n] = input[m, k] . W^T for a matrix W whose row ranges are separate QuantWeights of possibly
     different block formats (fused QKV of a Q4_K_M model: Q/K rows Q4_K, V rows Q6_K,
     standard_policy.rs:563-567); n = sum of the ranges' rows, ranges in row order."""
@@ -251,6 +257,10 @@ def quantized_matmul_segments(ctx: GpuContext, input: torch.Tensor, weights, out
     segs = (_RowSegment * len(weights))()
     for s, w in zip(segs, weights):
         s.w, s.rows, s.ggml_type = w.ptr, w.rows, w.ggml_type
+    if norm_weight is not None:      # RMSNorm(input) fused into the launches (rms_norm_rows, forward_cpu.rs:36-48)
+        ctx._check(ctx._lib.hf2q_cuda_norm_qmatmul_segments(ctx._h, ctx._stream(), input.data_ptr(), norm_weight.data_ptr(), norm_eps,
+                                                           segs, len(weights), out.data_ptr(), m, k))
+        return
     if workspace is None and m > 8:
         need = quantized_matmul_workspace_bytes(GgmlQuantizedMatmulParams(m, n, k, weights[0].ggml_type), input.dtype)
         ws = getattr(ctx, "_ws", None)
@@ -269,13 +279,19 @@ def quantized_matmul_swiglu_supported(ctx: GpuContext, m: int, weight: QuantWeig
     return bool(ctx._lib.hf2q_cuda_qmatmul_swiglu_supported(ctx._h, m, weight.rows, weight.cols, weight.ggml_type, xdt))
 
 
-def quantized_matmul_swiglu(ctx: GpuContext, input: torch.Tensor, gate: QuantWeight, up: QuantWeight, out: torch.Tensor, m: int) -> None:
-    """out[m,n] = silu(input . gate^T) * (input . up^T) in one launch (gpu_ffn.rs:896-935: gate, up, dispatch_silu_mul)."""
+def quantized_matmul_swiglu(ctx: GpuContext, input: torch.Tensor, gate: QuantWeight, up: QuantWeight, out: torch.Tensor, m: int,
+                            norm_weight: torch.Tensor | None = None, norm_eps: float = 0.0) -> None:
+    """out[m,n] = silu(input . gate^T) * (input . up^T) in one launch (gpu_ffn.rs:896-935: gate, up, dispatch_silu_mul);
+    with ``norm_weight`` the input is RMS-normalised inside the same launch."""
     xdt = _act(input, "input")
     if out.dtype != torch.float32 or not out.is_cuda or not out.is_contiguous() or out.numel() < m * gate.rows:
         raise Hf2qError(_lib.ERR_INVALID_ARGUMENT, "out must be a contiguous float32 CUDA tensor of [m, n]")
     if (gate.rows, gate.cols, gate.ggml_type) != (up.rows, up.cols, up.ggml_type) or input.numel() < m * gate.cols:
         raise Hf2qError(_lib.ERR_INVALID_ARGUMENT, "gate and up must share (rows, cols, type); input must hold [m, k]")
+    if norm_weight is not None:
+        ctx._check(ctx._lib.hf2q_cuda_norm_qmatmul_swiglu(ctx._h, ctx._stream(), input.data_ptr(), norm_weight.data_ptr(), norm_eps, gate.ptr,
+                                                          up.ptr, out.data_ptr(), m, gate.rows, gate.cols, gate.ggml_type))
+        return
     ctx._check(ctx._lib.hf2q_cuda_qmatmul_swiglu(ctx._h, ctx._stream(), input.data_ptr(), xdt, gate.ptr, up.ptr, out.data_ptr(),
                                                  m, gate.rows, gate.cols, gate.ggml_type))
 

@@ -333,6 +333,12 @@ HF2Q_API int32_t hf2q_cuda_moe_combine(hf2q_ctx* ctx, void* stream, const float*
                                        const float* shared, const float* shared_gate_logit,
                                        const float* residual, float* out, uint32_t n_tokens,
                                        uint32_t top_k, uint32_t hidden);
+/* Router logits of build_moe_ffn_layer_gpu_q_into (phase 1 of the graph at gpu_ffn.rs:2347-2359;
+ * moe_ffn_cpu_ref ffn.rs:203-214): logits[t, e] = sum_h x[t, h] * router[e, h], router f32
+ * [n_experts, hidden], x f32 or bf16. */
+HF2Q_API int32_t hf2q_cuda_router_logits(hf2q_ctx* ctx, void* stream, const void* x, uint32_t x_dtype,
+                                         const float* router, float* logits, uint32_t n_tokens,
+                                         uint32_t n_experts, uint32_t hidden);
 /* The shared expert's gate logit, a [1, hidden] f32 matrix applied per token (ffn.rs:298-304):
  * out[t] = sum_i v[i] * x[t,i]. */
 HF2Q_API int32_t hf2q_cuda_rowdot(hf2q_ctx* ctx, void* stream, const float* x, const float* v, float* out,
@@ -380,6 +386,27 @@ HF2Q_API int32_t hf2q_cuda_attn_decode_scratch_bytes(hf2q_ctx* ctx, uint32_t n_q
 HF2Q_API int32_t hf2q_cuda_attn_decode(hf2q_ctx* ctx, void* stream, const float* q, uint32_t n_q_heads,
                                        const hf2q_kv_cache* kv, const uint32_t* pos, void* out,
                                        uint32_t out_dtype, void* scratch, uint64_t scratch_bytes);
+/* RMSNorm fused in front of a product (decode: 1..4 f32 activation rows, k <= 4096): the kernel
+ * normalises x -- x / sqrt(mean(x^2) + eps) * norm_weight, rms_norm_rows of forward_cpu.rs:36-48 --
+ * while it converts the activations for its tensor-core operand, so the norm costs no launch and
+ * no round trip through memory.  x itself is not modified.  hf2q_cuda_norm_supported tells whether
+ * a (m, k, type) fits; otherwise call hf2q_cuda_rms_norm and the plain product. */
+HF2Q_API int32_t hf2q_cuda_norm_supported(hf2q_ctx* ctx, uint32_t m, uint32_t k, uint32_t ggml_type);
+HF2Q_API int32_t hf2q_cuda_norm_qmatmul_segments(hf2q_ctx* ctx, void* stream, const float* x,
+                                                 const float* norm_weight, float eps,
+                                                 const hf2q_row_segment* segs, uint32_t n_segs, float* y,
+                                                 uint32_t m, uint32_t k);
+HF2Q_API int32_t hf2q_cuda_norm_qmatmul_swiglu(hf2q_ctx* ctx, void* stream, const float* x,
+                                               const float* norm_weight, float eps, const void* w_gate,
+                                               const void* w_up, float* y, uint32_t m, uint32_t n,
+                                               uint32_t k, uint32_t ggml_type);
+/* The decode step's attention as ONE launch: hf2q_cuda_rope_kv_append (m = 1) and
+ * hf2q_cuda_attn_decode together.  qkv is one fused QKV row and is not modified; the new position's
+ * K and V go to the cache.  The first 256 bytes of scratch are completion counters: zero them once
+ * when the buffer is allocated (every call leaves them zero). */
+HF2Q_API int32_t hf2q_cuda_attn_decode_fused(hf2q_ctx* ctx, void* stream, const float* qkv, uint32_t n_q_heads,
+                                             float theta, const hf2q_kv_cache* kv, const uint32_t* pos,
+                                             void* out, uint32_t out_dtype, void* scratch, uint64_t scratch_bytes);
 /* m query tokens at positions pos0 .. pos0 + m - 1 (already appended), causal:
  * out[m][n_q_heads * head_dim].  qkv as for hf2q_cuda_rope_kv_append (after it). */
 HF2Q_API int32_t hf2q_cuda_attn_prefill(hf2q_ctx* ctx, void* stream, const float* qkv, uint32_t m,

@@ -68,8 +68,8 @@ def _rank_main(rank, world, port, ret):
         assert sum(sizes) == nt
         c0 = sum(sizes[:rank])
         raws = [make_quant_weight(oracle.Q6_K, nt, 2048, seed=11), make_quant_weight(oracle.Q4_K, nt, nt, seed=12),
-                make_quant_weight(oracle.Q5_K, nt, nt, seed=13), make_quant_weight(oracle.Q6_K, nt, nt, seed=14)]
-        types = [oracle.Q6_K, oracle.Q4_K, oracle.Q5_K, oracle.Q6_K]
+                make_quant_weight(oracle.Q5_K, nt, nt, seed=13), make_quant_weight(oracle.Q8_0, nt, nt, seed=14)]
+        types = [oracle.Q6_K, oracle.Q4_K, oracle.Q5_K, oracle.Q8_0]      # (Q6_K rows of 768 elements are not 16-byte aligned)
         ks = [2048, nt, nt, nt]
         shards = []
         for tt, rw, kk in zip(types, raws, ks):
