@@ -33,6 +33,7 @@ hf2q_cuda_qmatmul_gather, and the full-width y -> pinned host on rank 0.
 from __future__ import annotations
 
 import argparse
+import ctypes
 import json
 import os
 import statistics
@@ -835,6 +836,56 @@ def main() -> None:
         del gs
         sg.close()
 
+    # ---- expert-parallel MoE layer (several GPUs): BASELINE config 4 with the experts split 256 / G per GPU ----
+    moe_ep = None
+    if world > 1 and not args.no_strong:
+        from hf2q_b200.dist import Comm
+        t5, E, H, I, topk, T = 13, 256, 2048, 512, 8, 2048
+        comm = Comm(ctx)
+        e_local = E // world
+        sg, sdn = hq.expert_stride(t5, I, H), hq.expert_stride(t5, H, I)
+        wg, wu, wd = (_random_weight(torch, oracle, dev, t5, e_local * I, H), _random_weight(torch, oracle, dev, t5, e_local * I, H),
+                      _random_weight(torch, oracle, dev, t5, e_local * H, I))
+        t_local = T // world                                   # tokens are sharded over the ranks as well
+        R = t_local * topk
+        gen = torch.Generator(device=dev).manual_seed(100 + rank)
+        logits = torch.randn(t_local, E, device=dev, generator=gen)
+        ids5, wts5 = hq.moe_softmax_topk(ctx, logits, topk)
+        xrows = (torch.randn(t_local, H, device=dev, generator=gen) * 0.1).bfloat16().repeat_interleave(topk, dim=0).contiguous()
+        cap = T * topk                                          # every routed row of the job could land on one rank
+        need = ctypes.c_uint64()
+        comm._check(comm.lib.hf2q_cuda_moe_experts_ep_scratch_bytes(R, cap, world, H, I, E, hq.ops.DT_BF16, ctypes.byref(need)))
+        scr = torch.empty(need.value, dtype=torch.uint8, device=dev)
+        yrows = torch.empty((R, H), dtype=torch.float32, device=dev)
+        outl = torch.empty((t_local, H), dtype=torch.float32, device=dev)
+
+        def ep_layer():
+            comm.moe_experts_ep(xrows, ids5, wg.data_ptr(), wu.data_ptr(), wd.data_ptr(), H, I, E, sg, sdn, t5, t5, cap, scratch=scr, out=yrows)
+            ctx._check(ctx._lib.hf2q_cuda_moe_combine(ctx._h, ctx._stream(), yrows.data_ptr(), wts5.data_ptr(), None, None, None, outl.data_ptr(),
+                                                      t_local, topk, H))
+
+        for _ in range(3):
+            ep_layer()
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        reps = 10
+        e0.record()
+        for _ in range(reps):
+            ep_layer()
+        e1.record()
+        barrier()
+        tt = torch.tensor([e0.elapsed_time(e1) / reps], device=dev)
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        ctx.check_status()
+        us = float(tt.item()) * 1e3
+        moe_ep = {"metric": "expert-parallel MoE layer time", "value": round(us, 1), "unit": "us", "higher_is_better": False,
+                  "tokens_per_s": round(T / (us * 1e-6), 1),
+                  "config": {"workload": f"256 experts (Q5_K, hidden 2048, intermediate 512, top-8) split {e_local} per GPU over {world} GPUs; "
+                                         f"{T} tokens sharded {t_local} per GPU; hf2q_cuda_moe_experts_ep (device pack, ncclSend/Recv all-to-all, gate+up, "
+                                         "SwiGLU, down at the owner, all-to-all back, device unpack) + weighted combine; one host read-back of the row counts per call",
+                             "timing": f"CUDA events over {reps} eager calls, max over ranks"}}
+        comm.close()
+
     # ---- e2e leg: host buffers through the public call ----
     pin_x = {key: torch.from_numpy(b.view(np.int16).copy()).pin_memory() for key, b in xbits.items()}
     np_x = {key: t.numpy() for key, t in pin_x.items()}
@@ -962,6 +1013,8 @@ def main() -> None:
     }
     if strong is not None:
         line["strong"] = strong
+    if moe_ep is not None:
+        line.setdefault("secondary", {})["config4_moe_expert_parallel"] = moe_ep
     if cpu_baseline is not None:
         line["cpu_baseline"] = cpu_baseline
     if secondary is not None:

@@ -52,6 +52,16 @@ SIGNATURES = {
     "hf2q_cuda_qmatmul_gather": (i32, [vp, vp, vp, u32, vp, vp, u32, u32, u32, u32]),
     "hf2q_cuda_gather_wait": (i32, [vp, vp, vp]),
     "hf2q_cuda_set_wait_limit": (i32, [vp, u64]),
+    "hf2q_cuda_comm_unique_id": (i32, [vp]),
+    "hf2q_cuda_comm_create": (i32, [i32, vp, i32, i32, pp]),
+    "hf2q_cuda_comm_destroy": (i32, [vp]),
+    "hf2q_cuda_comm_last_error": (C.c_char_p, [vp]),
+    "hf2q_cuda_qmatmul_rowshard_workspace_bytes": (i32, [u32, u32, u32, u32, u32, u32, C.POINTER(u64)]),
+    "hf2q_cuda_qmatmul_rowshard": (i32, [vp, vp, vp, vp, u32, vp, vp, u32, u32, u32, u32, vp, u64]),
+    "hf2q_cuda_qmatmul_id_ep_scratch_bytes": (i32, [u32, u32, u32, u32, u32, u32, u32, C.POINTER(u64)]),
+    "hf2q_cuda_qmatmul_id_ep": (i32, [vp, vp, vp, vp, u32, vp, vp, vp, u32, u32, u32, u32, u32, u64, u32, vp, u64]),
+    "hf2q_cuda_moe_experts_ep_scratch_bytes": (i32, [u32, u32, u32, u32, u32, u32, u32, C.POINTER(u64)]),
+    "hf2q_cuda_moe_experts_ep": (i32, [vp, vp, vp, vp, u32, vp, vp, vp, vp, vp, u32, u32, u32, u32, u32, u64, u64, u32, u32, vp, u64]),
     "hf2q_cuda_qmatmul_id": (i32, [vp, vp, vp, u32, vp, vp, vp, u32, u32, u32, u32, u32, u64, u32, vp, u64]),
     "hf2q_cuda_qmatmul_id_pair": (i32, [vp, vp, vp, u32, vp, vp, vp, vp, vp, u32, u32, u32, u32, u32, u64, u32, vp, u64]),
     "hf2q_cuda_qmatmul_id_scratch_bytes": (i32, [u32, u32, u32, u32, C.POINTER(u64)]),

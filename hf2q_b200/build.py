@@ -14,7 +14,7 @@ from pathlib import Path
 PKG = Path(__file__).resolve().parent
 CSRC = PKG / "csrc"
 OUT = PKG / "libhf2q_cuda.so"
-SOURCES = ["api.cu", "k0_dequant.cu", "k1_gemv.cu", "k1_gemv_mma.cu", "k2_gemm_tc.cu", "k4_moe_prep.cu", "moe_router.cu", "ffn_elementwise.cu", "decoder_ops.cu"]
+SOURCES = ["api.cu", "k0_dequant.cu", "k1_gemv.cu", "k1_gemv_mma.cu", "k2_gemm_tc.cu", "k4_moe_prep.cu", "moe_router.cu", "ffn_elementwise.cu", "decoder_ops.cu", "comm_nccl.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC,-fvisibility=hidden",
@@ -59,7 +59,7 @@ def build(force: bool = False, verbose: bool = False) -> Path:
         if p.returncode:
             raise RuntimeError(f"nvcc failed on {src}:\n{out}")
     (objdir / "ptxas.log").write_text("\n".join(log))
-    cmd = [_nvcc(), "-shared", "-ccbin", "g++", "-o", str(OUT), *objs]
+    cmd = [_nvcc(), "-shared", "-ccbin", "g++", "-o", str(OUT), *objs, "-ldl"]
     r = subprocess.run(cmd, env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
     if r.returncode:
         raise RuntimeError(f"link failed:\n{r.stdout}")

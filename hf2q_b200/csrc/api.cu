@@ -48,6 +48,10 @@ struct hf2q_ctx {
     char err[512] = {0};
 };
 
+namespace hf2q {
+uint32_t* ctx_status_word(hf2q_ctx* ctx) { return ctx ? ctx->status : nullptr; }
+}  // namespace hf2q
+
 namespace {
 
 int32_t fail(hf2q_ctx* ctx, int32_t code, const char* fmt, ...) {

@@ -267,6 +267,10 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) attn_decode_fused_kernel(const
     __shared__ __align__(16) float red_acc[ATT_WARPS][G][ATT_HD];
     __shared__ uint32_t is_last;
     const uint32_t kvh = blockIdx.x, split = blockIdx.y, nsplit = gridDim.y;
+    // programmatic dependent launch: the next kernel of the stream (the O product) may start its own
+    // prologue now; this kernel touches nothing an earlier kernel writes before that kernel has completed
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     const uint32_t pos = *pos_dev;
     if (pos >= max_seq) { if (threadIdx.x == 0 && split == 0) atomicOr(status, STATUS_BAD_EXPERT_ID); return; }
     const uint32_t n_ctx = pos + 1;
@@ -716,16 +720,23 @@ cudaError_t launch_attn_decode_fused(const float* qkv, uint32_t n_q, uint32_t n_
     const float qs = 1.0f / sqrtf(static_cast<float>(hd));
     const bool f32 = out_dtype == HF2Q_DT_F32;
     if (!f32 && out_dtype != HF2Q_DT_BF16) return cudaErrorInvalidValue;
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(ATT_WARPS * 32);
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
     switch (G) {
 #define HF2Q_CASE(GG) case GG: \
-        if (f32) attn_decode_fused_kernel<GG, float><<<grid, ATT_WARPS * 32, 0, st>>>(qkv, n_q, n_kv, theta, qs, kv.k_codes, kv.k_scale, kv.v_codes, kv.v_scale, kv.max_seq, pos, part, counters, static_cast<float*>(out), status); \
-        else attn_decode_fused_kernel<GG, __nv_bfloat16><<<grid, ATT_WARPS * 32, 0, st>>>(qkv, n_q, n_kv, theta, qs, kv.k_codes, kv.k_scale, kv.v_codes, kv.v_scale, kv.max_seq, pos, part, counters, static_cast<__nv_bfloat16*>(out), status); \
-        break;
+        if (f32) return cudaLaunchKernelEx(&cfg, attn_decode_fused_kernel<GG, float>, qkv, n_q, n_kv, theta, qs, kv.k_codes, kv.k_scale, kv.v_codes, kv.v_scale, kv.max_seq, pos, part, counters, static_cast<float*>(out), status); \
+        return cudaLaunchKernelEx(&cfg, attn_decode_fused_kernel<GG, __nv_bfloat16>, qkv, n_q, n_kv, theta, qs, kv.k_codes, kv.k_scale, kv.v_codes, kv.v_scale, kv.max_seq, pos, part, counters, static_cast<__nv_bfloat16*>(out), status);
         HF2Q_CASE(1) HF2Q_CASE(2) HF2Q_CASE(4) HF2Q_CASE(8)
 #undef HF2Q_CASE
         default: return cudaErrorInvalidValue;
     }
-    return cudaGetLastError();
 }
 
 template <int G, typename OUT>

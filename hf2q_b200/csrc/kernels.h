@@ -5,7 +5,12 @@
 
 #include <mutex>
 
+struct hf2q_ctx;
+
 namespace hf2q {
+
+// the context's device status word (api.cu), for the translation units that launch kernels outside api.cu
+uint32_t* ctx_status_word(hf2q_ctx* ctx);
 
 // cudaFuncSetAttribute(MaxDynamicSharedMemorySize) applies to the CURRENT device only, and one
 // process may hold contexts on several GPUs: the opt-in is remembered per device, not per process.

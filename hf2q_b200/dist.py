@@ -98,6 +98,86 @@ def ep_mul_mat_id(x_rows: torch.Tensor, ids: torch.Tensor, n_experts: int, n_out
     return out
 
 
+class Comm:
+    """The library's own NCCL communicator (hf2q_cuda_comm_*): the 128-byte id is made on rank 0 and
+    handed round with torch.distributed, then every rank joins.  Used by the C-ABI forms
+    ``qmatmul_rowshard`` / ``qmatmul_id_ep`` / ``moe_experts_ep`` below, which run the pack and unpack
+    kernels and the NCCL calls inside the library."""
+
+    def __init__(self, ctx, group=None):
+        self.ctx, self.lib = ctx, ctx._lib
+        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        ident = (C.c_uint8 * 128)()
+        if self.rank == 0:
+            rc = self.lib.hf2q_cuda_comm_unique_id(ident)
+            if rc:
+                raise RuntimeError(f"hf2q_cuda_comm_unique_id failed ({rc}): NCCL not found")
+        box = [bytes(ident)]
+        dist.broadcast_object_list(box, src=0, group=group)
+        h = C.c_void_p()
+        rc = self.lib.hf2q_cuda_comm_create(ctx.device, (C.c_uint8 * 128).from_buffer_copy(box[0]), self.rank, self.world, C.byref(h))
+        if rc:
+            raise RuntimeError(f"hf2q_cuda_comm_create failed ({rc})")
+        self._h = h
+
+    def _check(self, rc: int) -> None:
+        if rc:
+            from . import ops
+            detail = self.lib.hf2q_cuda_comm_last_error(self._h).decode() or self.lib.hf2q_cuda_last_error(self.ctx._h).decode()
+            raise ops.Hf2qError(rc, detail)
+
+    def close(self) -> None:
+        if getattr(self, "_h", None):
+            self.lib.hf2q_cuda_comm_destroy(self._h)
+            self._h = None
+
+    def qmatmul_rowshard(self, x: torch.Tensor, w_shard, m: int) -> torch.Tensor:
+        """y[m, world * n_local] = x . W^T, W sharded by rows (hf2q_cuda_qmatmul_rowshard)."""
+        from . import ops
+        xdt = ops._act(x, "x")
+        need = C.c_uint64()
+        self._check(self.lib.hf2q_cuda_qmatmul_rowshard_workspace_bytes(m, w_shard.rows, w_shard.cols, w_shard.ggml_type, xdt, self.world, C.byref(need)))
+        ws = torch.empty(max(need.value, 256), dtype=torch.uint8, device=x.device)
+        y = torch.empty((m, self.world * w_shard.rows), dtype=torch.float32, device=x.device)
+        self._check(self.lib.hf2q_cuda_qmatmul_rowshard(self.ctx._h, self._h, self.ctx._stream(), x.data_ptr(), xdt, w_shard.ptr, y.data_ptr(), m,
+                                                        w_shard.rows, w_shard.cols, w_shard.ggml_type, ws.data_ptr(), ws.numel()))
+        self._keep = ws
+        return y
+
+    def qmatmul_id_ep(self, x_rows: torch.Tensor, ids: torch.Tensor, w_local_ptr: int, n: int, k: int, n_experts: int, stride: int,
+                      ggml_type: int, cap_recv: int) -> torch.Tensor:
+        """Expert-parallel mul_mat_id through the C ABI (hf2q_cuda_qmatmul_id_ep)."""
+        from . import ops
+        xdt = ops._act(x_rows, "x_rows")
+        rows = x_rows.shape[0]
+        need = C.c_uint64()
+        self._check(self.lib.hf2q_cuda_qmatmul_id_ep_scratch_bytes(rows, cap_recv, self.world, n, k, n_experts, xdt, C.byref(need)))
+        sc = torch.empty(max(need.value, 256), dtype=torch.uint8, device=x_rows.device)
+        y = torch.empty((rows, n), dtype=torch.float32, device=x_rows.device)
+        self._check(self.lib.hf2q_cuda_qmatmul_id_ep(self.ctx._h, self._h, self.ctx._stream(), x_rows.data_ptr(), xdt, ids.data_ptr(), w_local_ptr,
+                                                     y.data_ptr(), rows, cap_recv, n, k, n_experts, stride, ggml_type, sc.data_ptr(), sc.numel()))
+        self._keep = sc
+        return y
+
+    def moe_experts_ep(self, x_rows: torch.Tensor, ids: torch.Tensor, gate_ptr: int, up_ptr: int, down_ptr: int, hidden: int, inter: int,
+                       n_experts: int, stride_gu: int, stride_d: int, type_gu: int, type_d: int, cap_recv: int,
+                       scratch: torch.Tensor | None = None, out: torch.Tensor | None = None) -> torch.Tensor:
+        """y[rows, hidden] = down_e(silu(gate_e x) * (up_e x)) with the experts spread over the ranks (hf2q_cuda_moe_experts_ep)."""
+        from . import ops
+        xdt = ops._act(x_rows, "x_rows")
+        rows = x_rows.shape[0]
+        if scratch is None:
+            need = C.c_uint64()
+            self._check(self.lib.hf2q_cuda_moe_experts_ep_scratch_bytes(rows, cap_recv, self.world, hidden, inter, n_experts, xdt, C.byref(need)))
+            scratch = torch.empty(max(need.value, 256), dtype=torch.uint8, device=x_rows.device)
+        y = out if out is not None else torch.empty((rows, hidden), dtype=torch.float32, device=x_rows.device)
+        self._check(self.lib.hf2q_cuda_moe_experts_ep(self.ctx._h, self._h, self.ctx._stream(), x_rows.data_ptr(), xdt, ids.data_ptr(), gate_ptr, up_ptr,
+                                                      down_ptr, y.data_ptr(), rows, cap_recv, hidden, inter, n_experts, stride_gu, stride_d, type_gu,
+                                                      type_d, scratch.data_ptr(), scratch.numel()))
+        self._keep = scratch
+        return y
+
+
 class _Gather(C.Structure):                        # hf2q_gather in include/hf2q_cuda.h
     _fields_ = [("y_all", C.c_void_p * 8), ("flags", C.c_void_p * 8), ("n_ranks", C.c_uint32), ("rank", C.c_uint32),
                 ("n_total", C.c_uint32), ("col0", C.c_uint32), ("wait_previous", C.c_uint32), ("n_rows", C.c_uint32 * 8)]

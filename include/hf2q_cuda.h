@@ -317,6 +317,51 @@ HF2Q_API int32_t hf2q_cuda_gather_wait(hf2q_ctx* ctx, void* stream, const hf2q_g
  * HF2Q_ERR_TIMEOUT by hf2q_cuda_check_status), carries on with whatever data is there and returns. */
 HF2Q_API int32_t hf2q_cuda_set_wait_limit(hf2q_ctx* ctx, uint64_t clock_ticks);
 
+/* ---- e: the general multi-GPU forms over NCCL ---------------------------------------------------- *
+ * One process per GPU.  NCCL is looked up at run time (libnccl.so.2, the copy the host framework has
+ * loaded if there is one).  hf2q_cuda_comm_unique_id is called on one rank, its 128 bytes reach the
+ * others by the application's own means (a file, MPI, torch.distributed), and every rank then calls
+ * hf2q_cuda_comm_create.  No counterpart in the reference, which is single-device. */
+typedef struct hf2q_comm hf2q_comm;
+HF2Q_API int32_t hf2q_cuda_comm_unique_id(uint8_t* id128);
+HF2Q_API int32_t hf2q_cuda_comm_create(int32_t device, const uint8_t* id128, int32_t rank, int32_t world, hf2q_comm** out);
+HF2Q_API int32_t hf2q_cuda_comm_destroy(hf2q_comm* comm);
+HF2Q_API const char* hf2q_cuda_comm_last_error(const hf2q_comm* comm);
+/* quantized_matmul_ggml for weights sharded by output rows, any m: this rank's n_local rows (the same
+ * count on every rank), ncclAllGather of the column blocks, unpacked on the device into
+ * y_full[m][world * n_local] with rank r's columns at [r * n_local, (r + 1) * n_local). */
+HF2Q_API int32_t hf2q_cuda_qmatmul_rowshard_workspace_bytes(uint32_t m, uint32_t n_local, uint32_t k, uint32_t ggml_type,
+                                                            uint32_t x_dtype, uint32_t world, uint64_t* out);
+HF2Q_API int32_t hf2q_cuda_qmatmul_rowshard(hf2q_ctx* ctx, hf2q_comm* comm, void* stream, const void* x, uint32_t x_dtype,
+                                            const void* w_shard, float* y_full, uint32_t m, uint32_t n_local, uint32_t k,
+                                            uint32_t ggml_type, void* workspace, uint64_t workspace_bytes);
+/* quantized_matmul_id_ggml_pooled with the experts split in contiguous ranges of n_experts / world over
+ * the ranks: x_rows[rows][k] holds one activation row per routed row of THIS rank, ids[rows] their
+ * global expert indices, w_local this rank's stacked experts; y[rows][n] comes back in the caller's row
+ * order.  Routed rows travel to the owner of their expert and the results travel back (two all-to-alls
+ * made of ncclSend / ncclRecv groups, packed and unpacked by device kernels).  cap_recv bounds the rows
+ * that may ARRIVE at this rank (at most the sum of all ranks' rows); the scratch is sized from it.  The
+ * call reads the per-rank row counts back to the host: it synchronises the stream once. */
+HF2Q_API int32_t hf2q_cuda_qmatmul_id_ep_scratch_bytes(uint32_t rows, uint32_t cap_recv, uint32_t world, uint32_t n, uint32_t k,
+                                                       uint32_t n_experts, uint32_t x_dtype, uint64_t* out);
+HF2Q_API int32_t hf2q_cuda_qmatmul_id_ep(hf2q_ctx* ctx, hf2q_comm* comm, void* stream, const void* x_rows, uint32_t x_dtype,
+                                         const uint32_t* ids, const void* w_local, float* y, uint32_t rows, uint32_t cap_recv,
+                                         uint32_t n, uint32_t k, uint32_t n_experts, uint64_t expert_stride, uint32_t ggml_type,
+                                         void* scratch, uint64_t scratch_bytes);
+
+/* The expert part of build_moe_ffn_layer_gpu_q_into (gpu_ffn.rs:2313-2802, phases B-E) expert-parallel:
+ * every routed row travels ONCE to the owner of its expert, which runs gate, up, SwiGLU and down on it,
+ * and the [hidden] result travels back: y[rows][hidden] = down_e(silu(gate_e x) * (up_e x)), e = ids[row].
+ * The weighted sum over the top-k slots stays with the caller (hf2q_cuda_moe_combine). */
+HF2Q_API int32_t hf2q_cuda_moe_experts_ep_scratch_bytes(uint32_t rows, uint32_t cap_recv, uint32_t world, uint32_t hidden,
+                                                        uint32_t inter, uint32_t n_experts, uint32_t x_dtype, uint64_t* out);
+HF2Q_API int32_t hf2q_cuda_moe_experts_ep(hf2q_ctx* ctx, hf2q_comm* comm, void* stream, const void* x_rows, uint32_t x_dtype,
+                                          const uint32_t* ids, const void* w_gate_local, const void* w_up_local,
+                                          const void* w_down_local, float* y, uint32_t rows, uint32_t cap_recv,
+                                          uint32_t hidden, uint32_t inter, uint32_t n_experts, uint64_t stride_gate_up,
+                                          uint64_t stride_down, uint32_t type_gate_up, uint32_t type_down, void* scratch,
+                                          uint64_t scratch_bytes);
+
 /* ---- a8: element-wise glue of the FFN builders ---------------------------------------------- */
 
 /* dispatch_silu_mul as used by build_dense_ffn_layer_gpu_q_into (gpu_ffn.rs:1086-1351), semantics

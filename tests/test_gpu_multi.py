@@ -149,6 +149,45 @@ def _rank_main(rank, world, port, ret):
         got = hd.ep_mul_mat_id(torch.from_numpy(xr).cuda(), torch.from_numpy(ids).cuda(), E, n, local_id).cpu().numpy()
         want = oracle.qmatmul_id(t, raw, stride, xr, ids.astype(np.uint32), rows, 1, n, k, E)
         ok &= rel_l2(got, want) < 1e-3
+        # --- the same two schemes through the library's own C entries (NCCL inside the library)
+        comm = hd.Comm(ctx)
+        got_c = comm.qmatmul_id_ep(torch.from_numpy(xr).cuda(), torch.from_numpy(ids).cuda(), mine.data_ptr(), n, k, E, stride, t,
+                                   cap_recv=world * 130).cpu().numpy()
+        ok &= rel_l2(got_c, want) < 1e-3
+        # dense, rows sharded, mat-vec (m = 4) and tensor-core (m = 40) sizes
+        td, nd, kd = oracle.Q6_K, 512, 2048
+        rawd = make_quant_weight(td, nd, kd, seed=3)
+        rbd = oracle.row_bytes(td, kd)
+        nl = nd // world
+        wsh = hq.load_quant_weight(ctx, rawd[rank * nl * rbd:(rank + 1) * nl * rbd], td, nl, kd)
+        wd_full = oracle.dequantize(td, rawd).reshape(nd, kd)
+        for mm in (4, 40):
+            xm = make_x(mm, kd, seed=90 + mm)
+            yc = comm.qmatmul_rowshard(torch.from_numpy(xm).cuda(), wsh, mm).cpu().numpy()
+            ok &= rel_l2(yc, oracle.matmul_f64(xm, wd_full)) < 1e-3
+        # the whole expert FFN expert-parallel: gate, up, SwiGLU and down at the owner, one exchange each way
+        H, I = 512, 256
+        sg, sdn = hq.expert_stride(t, I, H), hq.expert_stride(t, H, I)
+        rg = np.concatenate([make_quant_weight(t, I, H, seed=100 + e) for e in range(E)])
+        ru = np.concatenate([make_quant_weight(t, I, H, seed=200 + e) for e in range(E)])
+        rdn = np.concatenate([make_quant_weight(t, H, I, seed=300 + e) for e in range(E)])
+        lg = torch.from_numpy(rg[rank * e_local * sg:(rank + 1) * e_local * sg]).cuda()
+        lu = torch.from_numpy(ru[rank * e_local * sg:(rank + 1) * e_local * sg]).cuda()
+        ldn = torch.from_numpy(rdn[rank * e_local * sdn:(rank + 1) * e_local * sdn]).cuda()
+        xe = make_x(rows, H, seed=80 + rank)
+        ye = comm.moe_experts_ep(torch.from_numpy(xe).cuda(), torch.from_numpy(ids).cuda(), lg.data_ptr(), lu.data_ptr(), ldn.data_ptr(),
+                                 H, I, E, sg, sdn, t, t, cap_recv=world * 130).cpu().numpy()
+        want_e = np.empty((rows, H))
+        for r in range(rows):
+            e = int(ids[r])
+            gf = oracle.dequantize(t, rg[e * sg:(e + 1) * sg]).reshape(I, H).astype(np.float64)
+            uf = oracle.dequantize(t, ru[e * sg:(e + 1) * sg]).reshape(I, H).astype(np.float64)
+            df = oracle.dequantize(t, rdn[e * sdn:(e + 1) * sdn]).reshape(H, I).astype(np.float64)
+            a, b = gf @ xe[r].astype(np.float64), uf @ xe[r].astype(np.float64)
+            want_e[r] = df @ ((a / (1.0 + np.exp(-a))) * b)
+        ok &= rel_l2(ye, want_e) < 2e-3
+        torch.cuda.synchronize()
+        comm.close()
         ctx.check_status()
         ret[rank] = bool(ok)
     finally:
