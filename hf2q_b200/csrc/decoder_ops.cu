@@ -417,21 +417,40 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) attn_decode_fused_kernel(const
     __syncthreads();
     if (!is_last) return;
     __threadfence();
+    // Merge of the splits, all loads in flight at once: (1) every split's (max, sum) into shared memory,
+    // (2) one thread per head turns them into weights exp(max_s - max) and the normaliser, (3) every
+    // thread (head, dim) adds its column of the partial results in split order.
+    float* sm_m = &ps[0][0][0];                          // [nsplit][G] (nsplit <= 64: fits the probability scratch)
+    float* sm_c = &red_acc[0][0][0];                     // [nsplit][G] weights, then the normaliser per head at [64 * G + g]
+    for (uint32_t i = threadIdx.x; i < nsplit * G; i += ATT_WARPS * 32) {
+        const uint32_t sp = i / G, g = i % G;
+        const float* src = part + ((static_cast<size_t>(kvh) * nsplit + sp) * G + g) * (2 + ATT_HD);
+        sm_m[i] = __ldcg(src);
+        sm_c[i] = __ldcg(src + 1);                       // the sums for now
+    }
+    __syncthreads();
+    if (threadIdx.x < G) {
+        const uint32_t g = threadIdx.x;
+        float m_all = -CUDART_INF_F;
+        for (uint32_t sp = 0; sp < nsplit; ++sp) m_all = fmaxf(m_all, sm_m[sp * G + g]);
+        float l_all = 0.f;
+        for (uint32_t sp = 0; sp < nsplit; ++sp) {
+            const float ms = sm_m[sp * G + g];
+            const float c = ms == -CUDART_INF_F ? 0.f : __expf(ms - m_all);
+            l_all += sm_c[sp * G + g] * c;
+            sm_c[sp * G + g] = c;
+        }
+        sm_c[64 * G + g] = l_all;
+    }
+    __syncthreads();
     for (uint32_t i = threadIdx.x; i < G * ATT_HD; i += ATT_WARPS * 32) {
         const uint32_t g = i / ATT_HD, d = i % ATT_HD;
-        const float* base = part + (static_cast<size_t>(kvh) * nsplit * G + g) * (2 + ATT_HD);
+        const float* base = part + (static_cast<size_t>(kvh) * nsplit * G + g) * (2 + ATT_HD) + 2 + d;
         const size_t stride = static_cast<size_t>(G) * (2 + ATT_HD);
-        float m_all = -CUDART_INF_F;
-        for (uint32_t sp = 0; sp < nsplit; ++sp) m_all = fmaxf(m_all, __ldcg(base + sp * stride));
-        float l_all = 0.f, a = 0.f;
-#pragma unroll 4
-        for (uint32_t sp = 0; sp < nsplit; ++sp) {
-            const float* src = base + sp * stride;
-            const float ms = __ldcg(src);
-            const float c = ms == -CUDART_INF_F ? 0.f : __expf(ms - m_all);
-            l_all += __ldcg(src + 1) * c;
-            a += __ldcg(src + 2 + d) * c;
-        }
+        float a = 0.f;
+#pragma unroll 8
+        for (uint32_t sp = 0; sp < nsplit; ++sp) a += __ldcg(base + sp * stride) * sm_c[sp * G + g];
+        const float l_all = sm_c[64 * G + g];
         const float v = l_all > 0.f ? a / l_all : 0.f;
         const size_t o = (static_cast<size_t>(kvh) * G + g) * ATT_HD + d;
         if constexpr (sizeof(OUT) == 4) out[o] = v;
