@@ -43,6 +43,10 @@ SIGNATURES = {
     "hf2q_cuda_qmatmul_swiglu": (i32, [vp, vp, vp, u32, vp, vp, vp, u32, u32, u32, u32]),
     "hf2q_cuda_qmatmul_add_supported": (i32, [vp, u32, u32, u32, u32]),
     "hf2q_cuda_qmatmul_add": (i32, [vp, vp, vp, u32, vp, vp, vp, u32, u32, u32, u32]),
+    "hf2q_cuda_qmatmul_swiglu_ws_supported": (i32, [vp, u32, u32, u32, u32, u32]),
+    "hf2q_cuda_qmatmul_swiglu_ws": (i32, [vp, vp, vp, u32, vp, vp, vp, u32, u32, u32, u32, vp, u64]),
+    "hf2q_cuda_qmatmul_add_ws_supported": (i32, [vp, u32, u32, u32, u32, u32]),
+    "hf2q_cuda_qmatmul_add_ws": (i32, [vp, vp, vp, u32, vp, vp, vp, u32, u32, u32, u32, vp, u64]),
     "hf2q_cuda_qmatmul_host": (i32, [vp, vp, u32, vp, vp, u32, u32, u32, u32]),
     "hf2q_cuda_qmatmul_host_async": (i32, [vp, vp, u32, vp, vp, u32, u32, u32, u32]),
     "hf2q_cuda_host_sync": (i32, [vp]),
@@ -65,6 +69,9 @@ SIGNATURES = {
     "hf2q_cuda_qmatmul_id": (i32, [vp, vp, vp, u32, vp, vp, vp, u32, u32, u32, u32, u32, u64, u32, vp, u64]),
     "hf2q_cuda_qmatmul_id_pair": (i32, [vp, vp, vp, u32, vp, vp, vp, vp, vp, u32, u32, u32, u32, u32, u64, u32, vp, u64]),
     "hf2q_cuda_qmatmul_id_scratch_bytes": (i32, [u32, u32, u32, u32, C.POINTER(u64)]),
+    "hf2q_cuda_moe_experts_scratch_bytes": (i32, [u32, u32, u32, u32, C.POINTER(u64)]),
+    "hf2q_cuda_moe_experts_supported": (i32, [vp, u32, u32, u32, u32, u32, u32, u32]),
+    "hf2q_cuda_moe_experts": (i32, [vp, vp, vp, u32, vp, vp, vp, vp, vp, u32, u32, u32, u32, u32, u64, u32, u64, u32, vp, u64]),
     "hf2q_cuda_moe_softmax_topk": (i32, [vp, vp, vp, vp, vp, u32, u32, u32]),
     "hf2q_cuda_silu_mul": (i32, [vp, vp, vp, vp, vp, u64]),
     "hf2q_cuda_moe_combine": (i32, [vp, vp, vp, vp, vp, vp, vp, vp, u32, u32, u32]),

@@ -527,6 +527,82 @@ HF2Q_API int32_t hf2q_cuda_qmatmul_add(hf2q_ctx* ctx, void* stream, const void* 
     return run_matvec(ctx, static_cast<cudaStream_t>(stream), a, m, "qmatmul_add launch");
 }
 
+// ---- the same two fusions for any number of activation rows: mat-vec kernels up to 8 rows, above that the
+// tensor-core GEMM with the SwiGLU pair in one tile / the residual in the epilogue (workspace as for hf2q_cuda_qmatmul)
+
+HF2Q_API int32_t hf2q_cuda_qmatmul_swiglu_ws_supported(hf2q_ctx* ctx, uint32_t m, uint32_t n, uint32_t k, uint32_t type, uint32_t x_dtype) {
+    if (!ctx || !type_supported(type) || n == 0 || k == 0 || m == 0 || ctx->fp32_matvec) return 0;
+    if (m <= 8) return hf2q_cuda_qmatmul_swiglu_supported(ctx, m, n, k, type, x_dtype);
+    const BlockGeom g = block_geom(type);
+    if (k % 256 || (static_cast<uint64_t>(k) / g.elems * g.bytes) % 16) return 0;
+    return gemm_tc_swiglu_supported(type) ? 1 : 0;
+}
+
+HF2Q_API int32_t hf2q_cuda_qmatmul_swiglu_ws(hf2q_ctx* ctx, void* stream, const void* x, uint32_t x_dtype, const void* w_gate,
+                                             const void* w_up, float* y, uint32_t m, uint32_t n, uint32_t k, uint32_t type,
+                                             void* workspace, uint64_t workspace_bytes) {
+    if (!ctx) return HF2Q_ERR_INVALID_ARGUMENT;
+    if (m <= 8) return swiglu_impl(ctx, stream, x, x_dtype, w_gate, w_up, y, m, n, k, type, nullptr, 0.f);
+    const char* who = "qmatmul_swiglu_ws";
+    if (!x || !w_gate || !w_up || !y) return fail(ctx, HF2Q_ERR_INVALID_ARGUMENT, "%s: null pointer", who);
+    if (x_dtype != HF2Q_DT_F32 && x_dtype != HF2Q_DT_BF16) return fail(ctx, HF2Q_ERR_INVALID_ARGUMENT, "%s: x_dtype %u (want F32 or BF16)", who, x_dtype);
+    int32_t rc = check_matmul_shape(ctx, type, n, k, who);
+    if (rc) return rc;
+    if (reinterpret_cast<uintptr_t>(x) % dtype_size(x_dtype) || reinterpret_cast<uintptr_t>(y) % 4)
+        return fail(ctx, HF2Q_ERR_INVALID_ARGUMENT, "%s: misaligned buffer", who);
+    if (ctx->fp32_matvec || !gemm_tc_swiglu_supported(type) || !gemm_tc_supported(type, w_gate, n, k) || !gemm_tc_supported(type, w_up, n, k))
+        return fail(ctx, HF2Q_ERR_INVALID_ARGUMENT, "%s: needs one of the five main formats, 16-byte aligned rows and k %% 256 == 0 "
+                    "(ask hf2q_cuda_qmatmul_swiglu_ws_supported)", who);
+    const uint64_t need = gemm_tc_workspace_bytes(m, k);
+    if (!workspace || workspace_bytes < need)
+        return fail(ctx, HF2Q_ERR_WORKSPACE, "%s: m=%u needs a workspace of %llu bytes (got %llu)", who, m, (unsigned long long)need,
+                    (unsigned long long)workspace_bytes);
+    if (reinterpret_cast<uintptr_t>(workspace) % 256) return fail(ctx, HF2Q_ERR_INVALID_ARGUMENT, "%s: workspace must be 256-byte aligned", who);
+    DeviceGuard dg(ctx->device);
+    int nl = 0;
+    const cudaError_t e = launch_gemm_tc_swiglu(type, w_gate, w_up, x, x_dtype, y, m, n, k, workspace, ctx->status, ctx->dev.sm_count,
+                                                static_cast<cudaStream_t>(stream), &nl);
+    if (e != cudaSuccess) return cuda_fail(ctx, e, "qmatmul_swiglu_ws launch");
+    ctx->launches += nl;
+    return HF2Q_OK;
+}
+
+HF2Q_API int32_t hf2q_cuda_qmatmul_add_ws_supported(hf2q_ctx* ctx, uint32_t m, uint32_t n, uint32_t k, uint32_t type, uint32_t x_dtype) {
+    if (!ctx || m == 0) return 0;
+    if (m <= 8) return hf2q_cuda_qmatmul_add_supported(ctx, n, k, type, x_dtype);
+    if (!type_supported(type) || n == 0 || k == 0 || ctx->fp32_matvec) return 0;
+    const BlockGeom g = block_geom(type);
+    return (k % 256 == 0 && (static_cast<uint64_t>(k) / g.elems * g.bytes) % 16 == 0) ? 1 : 0;
+}
+
+HF2Q_API int32_t hf2q_cuda_qmatmul_add_ws(hf2q_ctx* ctx, void* stream, const void* x, uint32_t x_dtype, const void* w,
+                                          const float* residual, float* y, uint32_t m, uint32_t n, uint32_t k, uint32_t type,
+                                          void* workspace, uint64_t workspace_bytes) {
+    if (!ctx) return HF2Q_ERR_INVALID_ARGUMENT;
+    if (m <= 8) return hf2q_cuda_qmatmul_add(ctx, stream, x, x_dtype, w, residual, y, m, n, k, type);
+    const char* who = "qmatmul_add_ws";
+    if (!x || !w || !y || !residual) return fail(ctx, HF2Q_ERR_INVALID_ARGUMENT, "%s: null pointer", who);
+    if (x_dtype != HF2Q_DT_F32 && x_dtype != HF2Q_DT_BF16) return fail(ctx, HF2Q_ERR_INVALID_ARGUMENT, "%s: x_dtype %u (want F32 or BF16)", who, x_dtype);
+    int32_t rc = check_matmul_shape(ctx, type, n, k, who);
+    if (rc) return rc;
+    if (reinterpret_cast<uintptr_t>(x) % dtype_size(x_dtype) || reinterpret_cast<uintptr_t>(y) % 4 || reinterpret_cast<uintptr_t>(residual) % 4)
+        return fail(ctx, HF2Q_ERR_INVALID_ARGUMENT, "%s: misaligned buffer", who);
+    if (ctx->fp32_matvec || !gemm_tc_supported(type, w, n, k))
+        return fail(ctx, HF2Q_ERR_INVALID_ARGUMENT, "%s: needs 16-byte aligned rows and k %% 256 == 0 (ask hf2q_cuda_qmatmul_add_ws_supported)", who);
+    const uint64_t need = gemm_tc_workspace_bytes(m, k);
+    if (!workspace || workspace_bytes < need)
+        return fail(ctx, HF2Q_ERR_WORKSPACE, "%s: m=%u needs a workspace of %llu bytes (got %llu)", who, m, (unsigned long long)need,
+                    (unsigned long long)workspace_bytes);
+    if (reinterpret_cast<uintptr_t>(workspace) % 256) return fail(ctx, HF2Q_ERR_INVALID_ARGUMENT, "%s: workspace must be 256-byte aligned", who);
+    DeviceGuard dg(ctx->device);
+    int nl = 0;
+    const cudaError_t e = launch_gemm_tc(type, w, x, x_dtype, y, m, n, k, workspace, ctx->status, ctx->dev.sm_count,
+                                         static_cast<cudaStream_t>(stream), &nl, 0, false, residual);
+    if (e != cudaSuccess) return cuda_fail(ctx, e, "qmatmul_add_ws launch");
+    ctx->launches += nl;
+    return HF2Q_OK;
+}
+
 // ---- row-sharded mat-vec with the all-gather in its epilogue (several GPUs, one process each) ----
 
 HF2Q_API int32_t hf2q_cuda_ipc_alloc(hf2q_ctx* ctx, uint64_t bytes, void** dev, uint8_t* handle64) {
@@ -883,6 +959,83 @@ HF2Q_API int32_t hf2q_cuda_qmatmul_id_swiglu(hf2q_ctx* ctx, void* stream, const 
     const cudaError_t e = launch_gemv_mma(a, ctx->dev, static_cast<cudaStream_t>(stream));
     if (e != cudaSuccess) return cuda_fail(ctx, e, "qmatmul_id_swiglu launch");
     ctx->launches += 1;
+    return HF2Q_OK;
+}
+
+// ---- the routed experts of an MoE layer in four launches: sort + gather, gate/up pair with the SwiGLU in the
+// epilogue writing the f16 activation panel in expert-sorted order, the down product reading that panel and
+// scattering its rows back to routed-row order.  (The reference runs mul_mat_id, mul_mat_id, silu_mul,
+// mul_mat_id: gpu_ffn.rs:2606-2760.)
+
+HF2Q_API int32_t hf2q_cuda_moe_experts_scratch_bytes(uint32_t n_experts, uint32_t max_rows, uint32_t hidden, uint32_t ffn, uint64_t* out) {
+    if (!out) return HF2Q_ERR_INVALID_ARGUMENT;
+    const uint64_t act = (static_cast<uint64_t>(max_rows) * ffn * 2 + 255) & ~255ull;
+    *out = moe_scratch_layout(n_experts, max_rows, hidden).total + act;
+    return HF2Q_OK;
+}
+
+HF2Q_API int32_t hf2q_cuda_moe_experts_supported(hf2q_ctx* ctx, uint32_t n_tokens, uint32_t top_k, uint32_t hidden, uint32_t ffn,
+                                                 uint32_t n_experts, uint32_t type_gate_up, uint32_t type_down) {
+    if (!ctx || ctx->fp32_matvec || !gemm_tc_swiglu_supported(type_gate_up) || !type_supported(type_down)) return 0;
+    const uint64_t rows = static_cast<uint64_t>(n_tokens) * top_k;
+    if (rows <= MM_ID_ROUTING_THRESHOLD || rows / 32 + n_experts > 65535 || n_experts == 0 || n_experts > 2048) return 0;
+    const BlockGeom gg = block_geom(type_gate_up), gd = block_geom(type_down);
+    if (hidden % 256 || ffn % 256) return 0;
+    if ((static_cast<uint64_t>(hidden) / gg.elems * gg.bytes) % 16 || (static_cast<uint64_t>(ffn) / gd.elems * gd.bytes) % 16) return 0;
+    return 1;
+}
+
+HF2Q_API int32_t hf2q_cuda_moe_experts(hf2q_ctx* ctx, void* stream, const void* x, uint32_t x_dtype, const void* w_gate,
+                                       const void* w_up, const void* w_down, const uint32_t* ids, float* y, uint32_t n_tokens,
+                                       uint32_t top_k, uint32_t hidden, uint32_t ffn, uint32_t n_experts, uint64_t stride_gate_up,
+                                       uint32_t type_gate_up, uint64_t stride_down, uint32_t type_down, void* scratch,
+                                       uint64_t scratch_bytes) {
+    if (!ctx) return HF2Q_ERR_INVALID_ARGUMENT;
+    const char* who = "moe_experts";
+    if (!x || !w_gate || !w_up || !w_down || !ids || !y) return fail(ctx, HF2Q_ERR_INVALID_ARGUMENT, "%s: null pointer", who);
+    if (x_dtype != HF2Q_DT_F32 && x_dtype != HF2Q_DT_BF16) return fail(ctx, HF2Q_ERR_INVALID_ARGUMENT, "%s: x_dtype %u", who, x_dtype);
+    int32_t rc = check_matmul_shape(ctx, type_gate_up, ffn, hidden, who);
+    if (!rc) rc = check_matmul_shape(ctx, type_down, hidden, ffn, who);
+    if (rc) return rc;
+    if (top_k == 0 || n_experts == 0) return fail(ctx, HF2Q_ERR_INVALID_ARGUMENT, "%s: top_k=%u n_experts=%u must be non-zero", who, top_k, n_experts);
+    uint64_t min_gu = 0, min_d = 0;
+    hf2q_cuda_expert_stride(type_gate_up, ffn, hidden, &min_gu);
+    hf2q_cuda_expert_stride(type_down, hidden, ffn, &min_d);
+    if (stride_gate_up < min_gu || stride_down < min_d)
+        return fail(ctx, HF2Q_ERR_INVALID_ARGUMENT, "%s: expert strides %llu / %llu are smaller than one matrix (%llu / %llu bytes)", who,
+                    (unsigned long long)stride_gate_up, (unsigned long long)stride_down, (unsigned long long)min_gu, (unsigned long long)min_d);
+    if (n_tokens == 0) return HF2Q_OK;
+    if (!hf2q_cuda_moe_experts_supported(ctx, n_tokens, top_k, hidden, ffn, n_experts, type_gate_up, type_down) ||
+        !gemm_tc_grouped_supported(type_gate_up, w_gate, stride_gate_up, n_experts, hidden) ||
+        !gemm_tc_grouped_supported(type_gate_up, w_up, stride_gate_up, n_experts, hidden) ||
+        !gemm_tc_grouped_supported(type_down, w_down, stride_down, n_experts, ffn) || reinterpret_cast<uintptr_t>(x) % 16)
+        return fail(ctx, HF2Q_ERR_INVALID_ARGUMENT, "%s: %u x %u routed rows, hidden=%u, ffn=%u do not fit the grouped launches "
+                    "(ask hf2q_cuda_moe_experts_supported; few rows take hf2q_cuda_qmatmul_id_swiglu + hf2q_cuda_qmatmul_id)", who,
+                    n_tokens, top_k, hidden, ffn);
+    const uint32_t rows = n_tokens * top_k;
+    const MoeScratch lay = moe_scratch_layout(n_experts, rows, hidden);
+    uint64_t need = 0;
+    hf2q_cuda_moe_experts_scratch_bytes(n_experts, rows, hidden, ffn, &need);
+    if (!scratch || scratch_bytes < need)
+        return fail(ctx, HF2Q_ERR_WORKSPACE, "%s: %u routed rows need %llu bytes of scratch (got %llu)", who, rows, (unsigned long long)need,
+                    (unsigned long long)scratch_bytes);
+    if (reinterpret_cast<uintptr_t>(scratch) % 256) return fail(ctx, HF2Q_ERR_INVALID_ARGUMENT, "%s: scratch must be 256-byte aligned", who);
+    DeviceGuard dg(ctx->device);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    void* act16 = static_cast<uint8_t*>(scratch) + lay.total;
+    uint32_t nt = moe_token_tile(rows, n_experts);
+    if (nt > 128) nt = 128;                                    // the pair launch takes token tiles of at most 128
+    // the sort also zero-fills y: rows whose expert id is out of range stay zero, as in hf2q_cuda_qmatmul_id
+    cudaError_t e = launch_moe_prep(ids, rows, n_experts, top_k, nt, x, x_dtype, hidden, y, nullptr, hidden, scratch, lay, ctx->status,
+                                    ctx->dev.sm_count, st);
+    if (e == cudaSuccess)
+        e = launch_gemm_tc_grouped(type_gate_up, w_gate, stride_gate_up, n_experts, rows, nullptr, ffn, hidden, nt, scratch, lay, ctx->status,
+                                   st, w_up, nullptr, act16);
+    if (e == cudaSuccess)
+        e = launch_gemm_tc_grouped(type_down, w_down, stride_down, n_experts, rows, y, hidden, ffn, nt, scratch, lay, ctx->status, st, nullptr,
+                                   act16, nullptr);
+    if (e != cudaSuccess) return cuda_fail(ctx, e, who);
+    ctx->launches += 4;
     return HF2Q_OK;
 }
 

@@ -73,6 +73,10 @@ struct GParams {
     const GroupTile* tiles;
     const uint32_t* n_tiles;
     const uint32_t* perm;
+    // epilogue options: y += residual (same layout as y); DUAL kernels store silu(gate) * up, either as f32 into y
+    // or, for the expert-routed form, as f16 into act16[sorted row][n] (the down product's activation panel)
+    const float* residual;
+    __half* act16;
     uint32_t tiles_per_cta; // weight-row tiles (of 128 rows) one CTA walks, re-using its barriers, TMEM and token tile
     uint32_t boxw;          // bytes per weight row in one raw stage
     uint32_t blk_bytes;     // bytes of one 256-element K-block of a row
@@ -111,15 +115,23 @@ __device__ __forceinline__ void dequant_dispatch(uint32_t grp, const uint8_t* ro
 
 
 // ---------------------------------------------------------------- the kernel
-template <uint32_t TYPE, int NT, bool GROUPED>
+// DUAL: a tile is 64 output rows of a GATE matrix and the same 64 rows of an UP matrix -- two 64-row boxes per
+// raw stage from two tensor maps.  The dequantiser thread of tensor-memory lane 32q + l reads gate row 16q + l
+// (l < 16) or up row 16q + l - 16, so each warp holds both halves of 16 outputs; the MMA loop does not know.
+// The epilogue pairs lane l with lane l + 16 by one shuffle per value and stores silu(gate) * up: the
+// SwiGLU of build_dense_ffn_layer_gpu_q / build_moe_ffn_layer_gpu_q (gpu_ffn.rs:896-935, 2606-2760) without
+// the two f32 round trips and the dispatch_silu_mul in between.
+template <uint32_t TYPE, int NT, bool GROUPED, bool DUAL>
 __global__ void __launch_bounds__(GEMM_THREADS, (NT <= 64 ? 2 : 1))
-gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x, const GParams p) {
+gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_w2,
+               const __grid_constant__ CUtensorMap tmap_x, const GParams p) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
     constexpr uint32_t X_STAGE = NT * 128;                       // NT rows x 64 f16, 128B-swizzled
     constexpr int X_STAGES = x_stages_of(TYPE, NT);
     uint8_t* xs = smem;                                          // X_STAGES x X_STAGE (1024-aligned)
-    constexpr int RAW_STAGES = raw_stages_of(TYPE, NT);
+    constexpr int RAW_STAGES = DUAL ? 2 : raw_stages_of(TYPE, NT);
+    constexpr uint32_t TILE_ROWS = DUAL ? 64 : TILE_N;           // output rows of one tile
     uint8_t* raw = xs + X_STAGES * X_STAGE;                      // RAW_STAGES x 128 x boxw
     const uint32_t raw_stage = TILE_N * p.boxw;
     uint64_t* bars = reinterpret_cast<uint64_t*>(raw + RAW_STAGES * raw_stage);
@@ -137,7 +149,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     // this CTA's weight-row tiles: [tile0, tile0 + ntile)
-    const uint32_t n_row_tiles = (p.n + TILE_N - 1) / TILE_N;
+    const uint32_t n_row_tiles = (p.n + TILE_ROWS - 1) / TILE_ROWS;
     const uint32_t tile0 = blockIdx.x * p.tiles_per_cta;
     const uint32_t ntile = min(p.tiles_per_cta, n_row_tiles - tile0);
     uint32_t tok0 = blockIdx.y * NT, tok_end = p.m, expert = 0;
@@ -169,7 +181,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
         if (lane == 0) {
             bool ok = true;
             for (uint32_t tl = 0, gk = 0; tl < ntile && ok; ++tl) {           // gk: K-block count over all tiles
-                const uint32_t row0 = (tile0 + tl) * TILE_N;
+                const uint32_t row0 = (tile0 + tl) * TILE_ROWS;
                 for (uint32_t kb = 0; kb < nkb && ok; ++kb, ++gk) {
                     const uint32_t rs = gk % RAW_STAGES;
                     if (gk >= RAW_STAGES) ok = mbar_wait_bounded(&raw_empty[rs], ((gk / RAW_STAGES) - 1) & 1, p.status);
@@ -180,6 +192,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
                         tma_3d(raw + rs * raw_stage, &tmap_w, static_cast<int>(byte0 >> 1), static_cast<int>(row0), static_cast<int>(expert), &raw_full[rs]);
                     else
                         tma_2d(raw + rs * raw_stage, &tmap_w, static_cast<int>(byte0 >> 1), static_cast<int>(row0), &raw_full[rs]);
+                    if constexpr (DUAL) {                                   // the up rows: second half of the stage (both boxes hold 64 rows)
+                        uint8_t* dst2 = raw + rs * raw_stage + 64 * p.boxw;
+                        if constexpr (GROUPED)
+                            tma_3d(dst2, &tmap_w2, static_cast<int>(byte0 >> 1), static_cast<int>(row0), static_cast<int>(expert), &raw_full[rs]);
+                        else
+                            tma_2d(dst2, &tmap_w2, static_cast<int>(byte0 >> 1), static_cast<int>(row0), &raw_full[rs]);
+                    }
                     for (uint32_t j = 0; j < KB / XK && ok; ++j) {
                         const uint32_t xi = gk * (KB / XK) + j, st = xi % X_STAGES;
                         if (xi >= X_STAGES) ok = mbar_wait_bounded(&x_empty[st], ((xi / X_STAGES) - 1) & 1, p.status);
@@ -228,9 +247,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
         const uint32_t quad = warp & 3, grp = static_cast<uint32_t>(warp) >> 2;
         const uint32_t r = quad * 32 + lane;               // weight row of the tile == TMEM lane
         const uint32_t lane_addr = (quad * 32u) << 16;
+        // row of the raw stage this thread dequantises (DUAL: gate box rows 0..63, up box rows 64..127)
+        const uint32_t src_row = DUAL ? ((lane < 16 ? 0u : 64u) + 16 * quad + (lane & 15)) : r;
         bool ok = true;
         for (uint32_t tl = 0, gk = 0; tl < ntile && ok; ++tl) {
-            const uint32_t row0 = (tile0 + tl) * TILE_N;
+            const uint32_t row0 = (tile0 + tl) * TILE_ROWS;
             for (uint32_t kb = 0; kb < nkb; ++kb, ++gk) {
                 const uint32_t rs = gk % RAW_STAGES, ab = gk % A_BUFS;
                 if (ok) ok = mbar_wait_bounded(&raw_full[rs], (gk / RAW_STAGES) & 1, p.status);
@@ -239,7 +260,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
                 if (!ok) break;
                 tc_fence_after();
                 const uint32_t off = (kb * p.blk_bytes) & 15u;
-                dequant_dispatch<TYPE>(grp, raw + rs * raw_stage + r * p.boxw, off, tmem_a + ab * 128 + lane_addr);
+                dequant_dispatch<TYPE>(grp, raw + rs * raw_stage + src_row * p.boxw, off, tmem_a + ab * 128 + lane_addr);
                 tmem_wait_st();
                 tc_fence_before();
                 __syncwarp();
@@ -250,6 +271,33 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
             tc_fence_after();
+            if constexpr (DUAL) {
+                // lanes 0..15 of this warp hold gate rows, lanes 16..31 the up rows of the same 16 outputs
+                const uint32_t row = row0 + 16 * quad + (lane & 15);
+                bool clipped = false;
+#pragma unroll 1
+                for (int c0 = 32 * static_cast<int>(grp); c0 < NT; c0 += 32 * DEQ_GROUPS) {
+                    uint32_t v[32];
+                    tmem_ld32(tmem_d + lane_addr + c0, v);
+                    tmem_wait_ld();
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        const float u = __shfl_down_sync(0xffffffffu, __uint_as_float(v[j]), 16);
+                        const uint32_t tok = tok0 + c0 + j;
+                        if (lane < 16 && row < p.n && tok < tok_end) {
+                            const float g = __uint_as_float(v[j]);
+                            const float act = g / (1.0f + expf(-g)) * u;
+                            if (GROUPED && p.act16) {          // same clipping rule as the f32 -> f16 conversion of any activation panel
+                                clipped |= fabsf(act) > 65504.0f;
+                                p.act16[static_cast<size_t>(tok) * p.n + row] = __float2half_rn(fminf(fmaxf(act, -65504.0f), 65504.0f));
+                            } else {
+                                p.y[static_cast<size_t>(GROUPED ? p.perm[tok] : tok) * p.ldy + row] = act;
+                            }
+                        }
+                    }
+                }
+                if (clipped) atomicOr(p.status, STATUS_X_CLIPPED);
+            } else {
             const uint32_t row = row0 + r;
 #pragma unroll 1
             for (int c0 = 32 * static_cast<int>(grp); c0 < NT; c0 += 32 * DEQ_GROUPS) {   // the groups share the columns
@@ -262,10 +310,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
                         const uint32_t tok = tok0 + c0 + j;
                         if (tok < tok_end) {
                             const uint32_t dst = GROUPED ? p.perm[tok] : tok;      // scatter back to routed-row order
-                            p.y[static_cast<size_t>(dst) * p.ldy + row] = __uint_as_float(v[j]);
+                            const size_t o = static_cast<size_t>(dst) * p.ldy + row;
+                            float out = __uint_as_float(v[j]);
+                            if (p.residual) out += p.residual[o];
+                            p.y[o] = out;
                         }
                     }
                 }
+            }
             }
             // this warp is done reading the accumulators: the next tile's MMAs may overwrite them
             tc_fence_before();
@@ -312,15 +364,17 @@ EncodeTiledFn encode_fn() {
 
 uint32_t boxw_of(uint32_t type) { return tc_boxw(type); }
 
-template <uint32_t TYPE, int NT, bool GROUPED>
-cudaError_t launch_gemm_t(const CUtensorMap& tw, const CUtensorMap& tx, const GParams& p, uint32_t grid_y, cudaStream_t st) {
-    auto kern = gemm_tc_kernel<TYPE, NT, GROUPED>;
-    const size_t smem = 1024 + static_cast<size_t>(x_stages_of(TYPE, NT)) * NT * 128 + static_cast<size_t>(raw_stages_of(TYPE, NT)) * TILE_N * p.boxw + 512;
+template <uint32_t TYPE, int NT, bool GROUPED, bool DUAL = false>
+cudaError_t launch_gemm_t(const CUtensorMap& tw, const CUtensorMap& tw2, const CUtensorMap& tx, const GParams& p, uint32_t grid_y, cudaStream_t st) {
+    auto kern = gemm_tc_kernel<TYPE, NT, GROUPED, DUAL>;
+    const size_t raw_stages = DUAL ? 2 : raw_stages_of(TYPE, NT);
+    const size_t smem = 1024 + static_cast<size_t>(x_stages_of(TYPE, NT)) * NT * 128 + raw_stages * TILE_N * p.boxw + 512;
     static PerDeviceFlag attr;
     if (const cudaError_t e = ensure_max_dynamic_smem(kern, 227 * 1024, attr); e != cudaSuccess) return e;
-    const uint32_t row_tiles = (p.n + TILE_N - 1) / TILE_N;
+    const uint32_t tile_rows = DUAL ? 64 : TILE_N;
+    const uint32_t row_tiles = (p.n + tile_rows - 1) / tile_rows;
     const dim3 grid((row_tiles + p.tiles_per_cta - 1) / p.tiles_per_cta, grid_y);
-    kern<<<grid, GEMM_THREADS, smem, st>>>(tw, tx, p);
+    kern<<<grid, GEMM_THREADS, smem, st>>>(tw, tw2, tx, p);
     return cudaGetLastError();
 }
 
@@ -328,10 +382,21 @@ template <uint32_t TYPE>
 cudaError_t launch_gemm_nt(const CUtensorMap& tw, const CUtensorMap& tx, const GParams& p, uint32_t nt, cudaStream_t st) {
     const uint32_t gy = (p.m + nt - 1) / nt;
     switch (nt) {
-        case 32: return launch_gemm_t<TYPE, 32, false>(tw, tx, p, gy, st);
-        case 64: return launch_gemm_t<TYPE, 64, false>(tw, tx, p, gy, st);
-        case 128: return launch_gemm_t<TYPE, 128, false>(tw, tx, p, gy, st);
-        default: return launch_gemm_t<TYPE, 256, false>(tw, tx, p, gy, st);
+        case 32: return launch_gemm_t<TYPE, 32, false>(tw, tw, tx, p, gy, st);
+        case 64: return launch_gemm_t<TYPE, 64, false>(tw, tw, tx, p, gy, st);
+        case 128: return launch_gemm_t<TYPE, 128, false>(tw, tw, tx, p, gy, st);
+        default: return launch_gemm_t<TYPE, 256, false>(tw, tw, tx, p, gy, st);
+    }
+}
+
+// the SwiGLU pair: token tiles of at most 128
+template <uint32_t TYPE, bool GROUPED>
+cudaError_t launch_gemm_dual_nt(const CUtensorMap& tg, const CUtensorMap& tu, const CUtensorMap& tx, const GParams& p, uint32_t nt, uint32_t gy,
+                                cudaStream_t st) {
+    switch (nt) {
+        case 32: return launch_gemm_t<TYPE, 32, GROUPED, true>(tg, tu, tx, p, gy, st);
+        case 64: return launch_gemm_t<TYPE, 64, GROUPED, true>(tg, tu, tx, p, gy, st);
+        default: return launch_gemm_t<TYPE, 128, GROUPED, true>(tg, tu, tx, p, gy, st);
     }
 }
 
@@ -367,9 +432,12 @@ uint32_t gemm_tc_token_tile(uint32_t m, uint32_t tiles_n, int sms) {
     return best;
 }
 
-cudaError_t launch_gemm_tc(uint32_t type, const void* w, const void* x, uint32_t x_dtype, float* y, uint32_t m, uint32_t n,
-                           uint32_t k, void* workspace, uint32_t* status, int sm_count, cudaStream_t st, int* launches,
-                           uint32_t ldy, bool x_ready) {
+namespace {
+// w_up != nullptr: the SwiGLU pair (w = gate); residual != nullptr: y = product + residual
+cudaError_t gemm_tc_dense(uint32_t type, const void* w, const void* w_up, const void* x, uint32_t x_dtype, float* y, uint32_t m, uint32_t n,
+                          uint32_t k, void* workspace, uint32_t* status, int sm_count, cudaStream_t st, int* launches,
+                          uint32_t ldy, bool x_ready, const float* residual) {
+    const bool dual = w_up != nullptr;
     const BlockGeom g = block_geom(type);
     const uint64_t row_bytes = static_cast<uint64_t>(k) / g.elems * g.bytes;
     EncodeTiledFn enc = encode_fn();
@@ -389,19 +457,22 @@ cudaError_t launch_gemm_tc(uint32_t type, const void* w, const void* x, uint32_t
     GParams p{};
     p.y = y; p.m = m; p.n = n; p.k = k;
     p.ldy = ldy ? ldy : n;
+    p.residual = residual;
     p.tiles_per_cta = 1;
     p.boxw = boxw_of(type);
     p.blk_bytes = KB / g.elems * g.bytes;
     p.status = status;
-    const uint32_t nt = gemm_tc_token_tile(m, (n + TILE_N - 1) / TILE_N, sm_count);
-    alignas(64) CUtensorMap tw, tx;
-    {
-        // weights: [n rows][row_bytes] viewed as u16, box = boxw bytes x 128 rows, no swizzle
+    const uint32_t tile_rows = dual ? 64 : TILE_N;
+    uint32_t nt = gemm_tc_token_tile(m, (n + tile_rows - 1) / tile_rows, sm_count);
+    if (dual && nt > 128) nt = 128;
+    alignas(64) CUtensorMap tw, tw2, tx;
+    for (int which = 0; which < (dual ? 2 : 1); ++which) {
+        // weights: [n rows][row_bytes] viewed as u16, box = boxw bytes x 128 (pair: 64) rows, no swizzle
         cuuint64_t dims[2] = {row_bytes / 2, n};
         cuuint64_t strides[1] = {row_bytes};
-        cuuint32_t box[2] = {p.boxw / 2, TILE_N};
+        cuuint32_t box[2] = {p.boxw / 2, tile_rows};
         cuuint32_t es[2] = {1, 1};
-        CUresult r = enc(&tw, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, const_cast<void*>(w), dims, strides, box, es,
+        CUresult r = enc(which ? &tw2 : &tw, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, const_cast<void*>(which ? w_up : w), dims, strides, box, es,
                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
         if (r != CUDA_SUCCESS) return cudaErrorInvalidValue;
@@ -417,6 +488,17 @@ cudaError_t launch_gemm_tc(uint32_t type, const void* w, const void* x, uint32_t
         if (r != CUDA_SUCCESS) return cudaErrorInvalidValue;
     }
     if (launches) *launches = x_ready ? 1 : 2;
+    if (dual) {
+        const uint32_t gy = (m + nt - 1) / nt;
+        switch (type) {
+            case HF2Q_TYPE_Q4_0: return launch_gemm_dual_nt<HF2Q_TYPE_Q4_0, false>(tw, tw2, tx, p, nt, gy, st);
+            case HF2Q_TYPE_Q8_0: return launch_gemm_dual_nt<HF2Q_TYPE_Q8_0, false>(tw, tw2, tx, p, nt, gy, st);
+            case HF2Q_TYPE_Q4_K: return launch_gemm_dual_nt<HF2Q_TYPE_Q4_K, false>(tw, tw2, tx, p, nt, gy, st);
+            case HF2Q_TYPE_Q5_K: return launch_gemm_dual_nt<HF2Q_TYPE_Q5_K, false>(tw, tw2, tx, p, nt, gy, st);
+            case HF2Q_TYPE_Q6_K: return launch_gemm_dual_nt<HF2Q_TYPE_Q6_K, false>(tw, tw2, tx, p, nt, gy, st);
+            default: return cudaErrorNotSupported;
+        }
+    }
     switch (type) {
         case HF2Q_TYPE_Q4_0: return launch_gemm_nt<HF2Q_TYPE_Q4_0>(tw, tx, p, nt, st);
         case HF2Q_TYPE_Q8_0: return launch_gemm_nt<HF2Q_TYPE_Q8_0>(tw, tx, p, nt, st);
@@ -430,6 +512,24 @@ cudaError_t launch_gemm_tc(uint32_t type, const void* w, const void* x, uint32_t
         default: return cudaErrorInvalidValue;
     }
 }
+}  // namespace
+
+cudaError_t launch_gemm_tc(uint32_t type, const void* w, const void* x, uint32_t x_dtype, float* y, uint32_t m, uint32_t n,
+                           uint32_t k, void* workspace, uint32_t* status, int sm_count, cudaStream_t st, int* launches,
+                           uint32_t ldy, bool x_ready, const float* residual) {
+    return gemm_tc_dense(type, w, nullptr, x, x_dtype, y, m, n, k, workspace, status, sm_count, st, launches, ldy, x_ready, residual);
+}
+
+// the five formats hf2q's quantizer writes for FFN tensors; the 32-element fallback formats keep the unfused sequence
+bool gemm_tc_swiglu_supported(uint32_t type) {
+    return type == HF2Q_TYPE_Q4_0 || type == HF2Q_TYPE_Q8_0 || type == HF2Q_TYPE_Q4_K || type == HF2Q_TYPE_Q5_K || type == HF2Q_TYPE_Q6_K;
+}
+
+cudaError_t launch_gemm_tc_swiglu(uint32_t type, const void* w_gate, const void* w_up, const void* x, uint32_t x_dtype, float* y,
+                                  uint32_t m, uint32_t n, uint32_t k, void* workspace, uint32_t* status, int sm_count,
+                                  cudaStream_t st, int* launches, bool x_ready) {
+    return gemm_tc_dense(type, w_gate, w_up, x, x_dtype, y, m, n, k, workspace, status, sm_count, st, launches, n, x_ready, nullptr);
+}
 
 
 bool gemm_tc_grouped_supported(uint32_t type, const void* w, uint64_t expert_stride, uint32_t n_experts, uint32_t k) {
@@ -439,18 +539,24 @@ bool gemm_tc_grouped_supported(uint32_t type, const void* w, uint64_t expert_str
 template <uint32_t TYPE>
 cudaError_t launch_grouped_nt(const CUtensorMap& tw, const CUtensorMap& tx, const GParams& p, uint32_t nt, uint32_t gy, cudaStream_t st) {
     switch (nt) {
-        case 32: return launch_gemm_t<TYPE, 32, true>(tw, tx, p, gy, st);
-        case 64: return launch_gemm_t<TYPE, 64, true>(tw, tx, p, gy, st);
-        case 128: return launch_gemm_t<TYPE, 128, true>(tw, tx, p, gy, st);
-        default: return launch_gemm_t<TYPE, 256, true>(tw, tx, p, gy, st);
+        case 32: return launch_gemm_t<TYPE, 32, true>(tw, tw, tx, p, gy, st);
+        case 64: return launch_gemm_t<TYPE, 64, true>(tw, tw, tx, p, gy, st);
+        case 128: return launch_gemm_t<TYPE, 128, true>(tw, tw, tx, p, gy, st);
+        default: return launch_gemm_t<TYPE, 256, true>(tw, tw, tx, p, gy, st);
     }
 }
 
 // One launch over (weight-row tile, token tile of one expert).  The grid is sized for the largest
 // possible number of token tiles; CTAs past the actual count (read from the scratch header) exit.
+// w_up != nullptr: the SwiGLU pair (w_stacked = gate, token tiles of at most 128); act16 != nullptr: its result
+// goes to act16[sorted row][n] as f16 instead of y.  x_panel overrides the gathered activation panel of the
+// scratch (the down product reads the act16 panel of the pair launch).
 cudaError_t launch_gemm_tc_grouped(uint32_t type, const void* w_stacked, uint64_t expert_stride, uint32_t n_experts, uint32_t rows,
                                    float* y, uint32_t n, uint32_t k, uint32_t nt, void* scratch, const MoeScratch& lay,
-                                   uint32_t* status, cudaStream_t st) {
+                                   uint32_t* status, cudaStream_t st, const void* w_up, const void* x_panel, void* act16) {
+    const bool dual = w_up != nullptr;
+    if (dual && nt > 128) return cudaErrorInvalidValue;
+    const uint32_t tile_rows = dual ? 64 : TILE_N;
     const BlockGeom g = block_geom(type);
     const uint64_t row_bytes = static_cast<uint64_t>(k) / g.elems * g.bytes;
     EncodeTiledFn enc = encode_fn();
@@ -463,7 +569,7 @@ cudaError_t launch_gemm_tc_grouped(uint32_t type, const void* w_stacked, uint64_
         // One CTA walks several weight-row tiles of its (expert, token tile): barriers, tensor memory and the
         // first copies' latency are paid once.  Keep about two CTAs per resident slot (2 per SM) in the grid.
         static const int forced = [] { const char* v = getenv("HF2Q_CUDA_MOE_TPC"); return v && *v ? atoi(v) : 0; }();   // tuning aid
-        const uint32_t row_tiles = (n + TILE_N - 1) / TILE_N, token_tiles = rows / nt + n_experts / 2;
+        const uint32_t row_tiles = (n + tile_rows - 1) / tile_rows, token_tiles = rows / nt + n_experts / 2;
         uint32_t tpc = static_cast<uint32_t>(static_cast<uint64_t>(row_tiles) * token_tiles / (4 * 148 * 2));
         if (forced > 0) tpc = static_cast<uint32_t>(forced);
         p.tiles_per_cta = tpc < 1 ? 1 : tpc > 8 ? 8 : tpc;
@@ -472,17 +578,18 @@ cudaError_t launch_gemm_tc_grouped(uint32_t type, const void* w_stacked, uint64_
     p.tiles = reinterpret_cast<const GroupTile*>(base + lay.tiles_off);
     p.n_tiles = reinterpret_cast<const uint32_t*>(base);
     p.perm = reinterpret_cast<const uint32_t*>(base + lay.perm_off);
+    p.act16 = static_cast<__half*>(act16);
     p.boxw = boxw_of(type);
     p.blk_bytes = KB / g.elems * g.bytes;
     p.status = status;
-    alignas(64) CUtensorMap tw, tx;
-    {
-        // stacked experts: [E][n rows][row_bytes] viewed as u16; box = boxw bytes x 128 rows x 1 expert
+    alignas(64) CUtensorMap tw, tw2, tx;
+    for (int which = 0; which < (dual ? 2 : 1); ++which) {
+        // stacked experts: [E][n rows][row_bytes] viewed as u16; box = boxw bytes x 128 (pair: 64) rows x 1 expert
         cuuint64_t dims[3] = {row_bytes / 2, n, n_experts};
         cuuint64_t strides[2] = {row_bytes, expert_stride};
-        cuuint32_t box[3] = {p.boxw / 2, TILE_N, 1};
+        cuuint32_t box[3] = {p.boxw / 2, tile_rows, 1};
         cuuint32_t es[3] = {1, 1, 1};
-        CUresult r = enc(&tw, CU_TENSOR_MAP_DATA_TYPE_UINT16, 3, const_cast<void*>(w_stacked), dims, strides, box, es,
+        CUresult r = enc(which ? &tw2 : &tw, CU_TENSOR_MAP_DATA_TYPE_UINT16, 3, const_cast<void*>(which ? w_up : w_stacked), dims, strides, box, es,
                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
         if (r != CUDA_SUCCESS) return cudaErrorInvalidValue;
@@ -492,11 +599,22 @@ cudaError_t launch_gemm_tc_grouped(uint32_t type, const void* w_stacked, uint64_
         cuuint64_t strides[1] = {static_cast<cuuint64_t>(k) * 2};
         cuuint32_t box[2] = {XK, nt};
         cuuint32_t es[2] = {1, 1};
-        CUresult r = enc(&tx, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, base + lay.xg_off, dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
+        void* xp = x_panel ? const_cast<void*>(x_panel) : static_cast<void*>(base + lay.xg_off);
+        CUresult r = enc(&tx, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, xp, dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
                          CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
         if (r != CUDA_SUCCESS) return cudaErrorInvalidValue;
     }
     const uint32_t gy = rows / nt + n_experts;           // >= sum over experts of ceil(count / nt)
+    if (dual) {
+        switch (type) {
+            case HF2Q_TYPE_Q4_0: return launch_gemm_dual_nt<HF2Q_TYPE_Q4_0, true>(tw, tw2, tx, p, nt, gy, st);
+            case HF2Q_TYPE_Q8_0: return launch_gemm_dual_nt<HF2Q_TYPE_Q8_0, true>(tw, tw2, tx, p, nt, gy, st);
+            case HF2Q_TYPE_Q4_K: return launch_gemm_dual_nt<HF2Q_TYPE_Q4_K, true>(tw, tw2, tx, p, nt, gy, st);
+            case HF2Q_TYPE_Q5_K: return launch_gemm_dual_nt<HF2Q_TYPE_Q5_K, true>(tw, tw2, tx, p, nt, gy, st);
+            case HF2Q_TYPE_Q6_K: return launch_gemm_dual_nt<HF2Q_TYPE_Q6_K, true>(tw, tw2, tx, p, nt, gy, st);
+            default: return cudaErrorNotSupported;
+        }
+    }
     switch (type) {
         case HF2Q_TYPE_Q4_0: return launch_grouped_nt<HF2Q_TYPE_Q4_0>(tw, tx, p, nt, gy, st);
         case HF2Q_TYPE_Q8_0: return launch_grouped_nt<HF2Q_TYPE_Q8_0>(tw, tx, p, nt, gy, st);

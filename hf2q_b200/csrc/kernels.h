@@ -109,7 +109,12 @@ uint64_t gemm_tc_workspace_bytes(uint32_t m, uint32_t k);
 // ldy: floats between activation rows of y (0 = n); x_ready: the workspace already holds the f16 copy of x
 cudaError_t launch_gemm_tc(uint32_t type, const void* w, const void* x, uint32_t x_dtype, float* y, uint32_t m, uint32_t n,
                            uint32_t k, void* workspace, uint32_t* status, int sm_count, cudaStream_t st, int* launches,
-                           uint32_t ldy = 0, bool x_ready = false);
+                           uint32_t ldy = 0, bool x_ready = false, const float* residual = nullptr);
+// y[m][n] = silu(x . gate^T) * (x . up^T) in one launch (the five main formats)
+bool gemm_tc_swiglu_supported(uint32_t type);
+cudaError_t launch_gemm_tc_swiglu(uint32_t type, const void* w_gate, const void* w_up, const void* x, uint32_t x_dtype, float* y,
+                                  uint32_t m, uint32_t n, uint32_t k, void* workspace, uint32_t* status, int sm_count,
+                                  cudaStream_t st, int* launches, bool x_ready = false);
 
 // K4: grouped expert-routed product.  moe_scratch_layout() carves the caller's scratch into header
 // (tile count, sorted-row count), tile table, permutation and the f16 activation panel;
@@ -127,7 +132,8 @@ cudaError_t launch_moe_prep(const uint32_t* ids, uint32_t rows, uint32_t n_exper
 bool gemm_tc_grouped_supported(uint32_t type, const void* w, uint64_t expert_stride, uint32_t n_experts, uint32_t k);
 cudaError_t launch_gemm_tc_grouped(uint32_t type, const void* w_stacked, uint64_t expert_stride, uint32_t n_experts, uint32_t rows,
                                    float* y, uint32_t n, uint32_t k, uint32_t nt, void* scratch, const MoeScratch& lay,
-                                   uint32_t* status, cudaStream_t st);
+                                   uint32_t* status, cudaStream_t st, const void* w_up = nullptr, const void* x_panel = nullptr,
+                                   void* act16 = nullptr);
 
 // Fixed scratch of the allocation-free GEMM entry (lives in k2_gemm_tc.cu).
 uint64_t gemm_tc_static_scratch_bytes();

@@ -50,8 +50,9 @@ def build_dense_ffn_layer_gpu_q(ctx: ops.GpuContext, x: torch.Tensor, w: DenseFf
                                 residual: torch.Tensor | None = None, fused: bool = True) -> torch.Tensor:
     """y = down @ (silu(gate @ x) * (up @ x)) (+ residual); x [m, hidden] f32/bf16, y f32 [m, hidden].
 
-    With ``fused`` (default) and a shape the fused kernels take, this is two launches: gate/up with
-    the SwiGLU in the epilogue, down with the residual add in the epilogue.  Otherwise the
+    With ``fused`` (default) and a shape the fused kernels take, this is two products: gate/up with
+    the SwiGLU in the epilogue, down with the residual add in the epilogue (mat-vec kernels up to 8
+    rows, the tensor-core GEMM beyond).  Otherwise the
     reference's sequence: gate, up, silu_mul, down, add (gpu_ffn.rs:896-960)."""
     m = x.shape[0]
     inter, hidden = w.gate_q.rows, w.gate_q.cols
@@ -65,7 +66,7 @@ def build_dense_ffn_layer_gpu_q(ctx: ops.GpuContext, x: torch.Tensor, w: DenseFf
         ops.quantized_matmul_ggml(ctx, x, w.up_q, b, w.up_q.matmul_params(m))
         c = _silu_mul(ctx, a, b)
     y = torch.empty((m, hidden), dtype=torch.float32, device=x.device)
-    if residual is not None and fused and m <= 8 and ops.quantized_matmul_add_supported(ctx, w.down_q, c.dtype):
+    if residual is not None and fused and ops.quantized_matmul_add_supported(ctx, w.down_q, c.dtype, m):
         ops.quantized_matmul_add(ctx, c, w.down_q, residual.contiguous().float(), y, m)
         return y
     ops.quantized_matmul_ggml(ctx, c, w.down_q, y, w.down_q.matmul_params(m))
@@ -91,8 +92,14 @@ def build_moe_ffn_layer_gpu_q(ctx: ops.GpuContext, x: torch.Tensor, w: MoeFfnWei
     rows = T * k
     sg = ops.expert_stride(w.ggml_type_gate_up, inter, hidden)
     sd = ops.expert_stride(w.ggml_type_down, hidden, inter)
-    scratch = ops.IdMmScratch.alloc(ctx, E, rows, max(hidden, inter))
     pg = ops.GgmlQuantizedMatmulIdParams(T, k, inter, hidden, E, sg, w.ggml_type_gate_up)
+    d = torch.empty((rows, hidden), dtype=torch.float32, device=x.device)
+    if fused and ops.moe_experts_supported(ctx, T, k, hidden, inter, E, w.ggml_type_gate_up, w.ggml_type_down):
+        # many routed rows: sort + gather, gate/up pair with the SwiGLU in its epilogue, down -- four launches
+        ops.moe_experts(ctx, x, w.expert_gate.data_ptr(), w.expert_up.data_ptr(), w.expert_down.data_ptr(), ids, d,
+                        T, k, hidden, inter, E, w.ggml_type_gate_up, w.ggml_type_down, sg, sd)
+        return _moe_finish(ctx, x, w, d, wts, residual, T, k, hidden)
+    scratch = ops.IdMmScratch.alloc(ctx, E, rows, max(hidden, inter))
     if fused and ops.quantized_matmul_id_swiglu_supported(ctx, pg, x.dtype):
         # few routed rows: gate, up and the SwiGLU in one launch
         act = torch.empty((rows, inter), dtype=torch.float32, device=x.device)
@@ -102,9 +109,13 @@ def build_moe_ffn_layer_gpu_q(ctx: ops.GpuContext, x: torch.Tensor, w: MoeFfnWei
         u = torch.empty_like(g)
         ops.quantized_matmul_id_pair_ggml(ctx, x, w.expert_gate.data_ptr(), w.expert_up.data_ptr(), ids, g, u, scratch, pg)
         act = _silu_mul(ctx, g, u)
-    d = torch.empty((rows, hidden), dtype=torch.float32, device=x.device)
     pd = ops.GgmlQuantizedMatmulIdParams(rows, 1, hidden, inter, E, sd, w.ggml_type_down)
     ops.quantized_matmul_id_ggml(ctx, act, w.expert_down.data_ptr(), ids, d, scratch, pd)
+    return _moe_finish(ctx, x, w, d, wts, residual, T, k, hidden)
+
+
+def _moe_finish(ctx, x, w, d, wts, residual, T, k, hidden):
+    """Shared expert, its sigmoid gate, the weighted sum over the slots and the residual (gpu_ffn.rs:2762-2802)."""
     shared_y = gate_logit = None
     if w.shared is not None:
         shared_y = build_dense_ffn_layer_gpu_q(ctx, x, w.shared)

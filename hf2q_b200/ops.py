@@ -276,13 +276,26 @@ def quantized_matmul_segments(ctx: GpuContext, input: torch.Tensor, weights, out
 def quantized_matmul_swiglu_supported(ctx: GpuContext, m: int, weight: QuantWeight, x_dtype=torch.bfloat16) -> bool:
     """Whether gate and up products of shape `weight` with m activation rows fit the one fused launch."""
     xdt = DT_BF16 if x_dtype == torch.bfloat16 else DT_F32
-    return bool(ctx._lib.hf2q_cuda_qmatmul_swiglu_supported(ctx._h, m, weight.rows, weight.cols, weight.ggml_type, xdt))
+    return bool(ctx._lib.hf2q_cuda_qmatmul_swiglu_ws_supported(ctx._h, m, weight.rows, weight.cols, weight.ggml_type, xdt))
+
+
+def _pooled_workspace(ctx: GpuContext, m: int, weight: QuantWeight, x_dtype, device):
+    """(pointer, bytes) of the context's pooled GEMM workspace grown for m rows of `weight` (decode_pool.rs:51-76)."""
+    need = quantized_matmul_workspace_bytes(GgmlQuantizedMatmulParams(m, weight.rows, weight.cols, weight.ggml_type), x_dtype)
+    if not need:
+        return None, 0
+    ws = getattr(ctx, "_ws", None)
+    if ws is None or ws.numel() < need:
+        ws = torch.empty(need, dtype=torch.uint8, device=device)
+        ctx._ws = ws
+    return ws.data_ptr(), ws.numel()
 
 
 def quantized_matmul_swiglu(ctx: GpuContext, input: torch.Tensor, gate: QuantWeight, up: QuantWeight, out: torch.Tensor, m: int,
                             norm_weight: torch.Tensor | None = None, norm_eps: float = 0.0) -> None:
     """out[m,n] = silu(input . gate^T) * (input . up^T) in one launch (gpu_ffn.rs:896-935: gate, up, dispatch_silu_mul);
-    with ``norm_weight`` the input is RMS-normalised inside the same launch."""
+    with ``norm_weight`` the input is RMS-normalised inside the same launch (few rows only).  More than 8 rows take
+    the tensor-core form, which computes the two tiles side by side."""
     xdt = _act(input, "input")
     if out.dtype != torch.float32 or not out.is_cuda or not out.is_contiguous() or out.numel() < m * gate.rows:
         raise Hf2qError(_lib.ERR_INVALID_ARGUMENT, "out must be a contiguous float32 CUDA tensor of [m, n]")
@@ -292,13 +305,14 @@ def quantized_matmul_swiglu(ctx: GpuContext, input: torch.Tensor, gate: QuantWei
         ctx._check(ctx._lib.hf2q_cuda_norm_qmatmul_swiglu(ctx._h, ctx._stream(), input.data_ptr(), norm_weight.data_ptr(), norm_eps, gate.ptr,
                                                           up.ptr, out.data_ptr(), m, gate.rows, gate.cols, gate.ggml_type))
         return
-    ctx._check(ctx._lib.hf2q_cuda_qmatmul_swiglu(ctx._h, ctx._stream(), input.data_ptr(), xdt, gate.ptr, up.ptr, out.data_ptr(),
-                                                 m, gate.rows, gate.cols, gate.ggml_type))
+    ws_ptr, ws_bytes = _pooled_workspace(ctx, m, gate, input.dtype, input.device)
+    ctx._check(ctx._lib.hf2q_cuda_qmatmul_swiglu_ws(ctx._h, ctx._stream(), input.data_ptr(), xdt, gate.ptr, up.ptr, out.data_ptr(),
+                                                    m, gate.rows, gate.cols, gate.ggml_type, ws_ptr, ws_bytes))
 
 
-def quantized_matmul_add_supported(ctx: GpuContext, weight: QuantWeight, x_dtype=torch.float32) -> bool:
+def quantized_matmul_add_supported(ctx: GpuContext, weight: QuantWeight, x_dtype=torch.float32, m: int = 1) -> bool:
     xdt = DT_BF16 if x_dtype == torch.bfloat16 else DT_F32
-    return bool(ctx._lib.hf2q_cuda_qmatmul_add_supported(ctx._h, weight.rows, weight.cols, weight.ggml_type, xdt))
+    return bool(ctx._lib.hf2q_cuda_qmatmul_add_ws_supported(ctx._h, m, weight.rows, weight.cols, weight.ggml_type, xdt))
 
 
 def quantized_matmul_add(ctx: GpuContext, input: torch.Tensor, weight: QuantWeight, residual: torch.Tensor, out: torch.Tensor, m: int) -> None:
@@ -309,8 +323,9 @@ def quantized_matmul_add(ctx: GpuContext, input: torch.Tensor, weight: QuantWeig
             raise Hf2qError(_lib.ERR_INVALID_ARGUMENT, f"{name} must be a contiguous float32 CUDA tensor of [m, n]")
     if input.numel() < m * weight.cols:
         raise Hf2qError(_lib.ERR_INVALID_ARGUMENT, "input smaller than [m, k]")
-    ctx._check(ctx._lib.hf2q_cuda_qmatmul_add(ctx._h, ctx._stream(), input.data_ptr(), xdt, weight.ptr, residual.data_ptr(),
-                                              out.data_ptr(), m, weight.rows, weight.cols, weight.ggml_type))
+    ws_ptr, ws_bytes = _pooled_workspace(ctx, m, weight, input.dtype, input.device)
+    ctx._check(ctx._lib.hf2q_cuda_qmatmul_add_ws(ctx._h, ctx._stream(), input.data_ptr(), xdt, weight.ptr, residual.data_ptr(),
+                                                 out.data_ptr(), m, weight.rows, weight.cols, weight.ggml_type, ws_ptr, ws_bytes))
 
 
 def quantized_matmul_host(ctx: GpuContext, x_host: np.ndarray, weight: QuantWeight, y_host: np.ndarray,
@@ -406,6 +421,37 @@ def quantized_matmul_id_swiglu_ggml(ctx: GpuContext, input: torch.Tensor, weight
     ctx._check(ctx._lib.hf2q_cuda_qmatmul_id_swiglu(ctx._h, ctx._stream(), input.data_ptr(), xdt, wg, wu, ids.data_ptr(),
                                                     out.data_ptr(), params.n_tokens, params.top_k, params.n, params.k,
                                                     params.n_experts, params.expert_stride, int(params.ggml_type)))
+
+
+def moe_experts_supported(ctx: GpuContext, n_tokens: int, top_k: int, hidden: int, ffn: int, n_experts: int,
+                          type_gate_up: int, type_down: int) -> bool:
+    return bool(ctx._lib.hf2q_cuda_moe_experts_supported(ctx._h, n_tokens, top_k, hidden, ffn, n_experts, int(type_gate_up), int(type_down)))
+
+
+def moe_experts(ctx: GpuContext, input: torch.Tensor, gate_ptr: int, up_ptr: int, down_ptr: int, ids: torch.Tensor, out: torch.Tensor,
+                n_tokens: int, top_k: int, hidden: int, ffn: int, n_experts: int, type_gate_up: int, type_down: int,
+                stride_gate_up: int | None = None, stride_down: int | None = None) -> None:
+    """out[t*top_k+s, :] = down_e . (silu(gate_e . x_t) * (up_e . x_t)), e = ids[t*top_k+s]: the routed experts of an MoE
+    layer for many routed rows in four launches (gpu_ffn.rs:2606-2760 runs mul_mat_id x2, silu_mul, mul_mat_id)."""
+    xdt = _act(input, "input")
+    rows = n_tokens * top_k
+    if ids.dtype not in (torch.int32, torch.uint32) or not ids.is_cuda or not ids.is_contiguous() or ids.numel() < rows:
+        raise Hf2qError(_lib.ERR_INVALID_ARGUMENT, "ids must be a contiguous 32-bit integer CUDA tensor of n_tokens * top_k")
+    if out.dtype != torch.float32 or not out.is_cuda or not out.is_contiguous() or out.numel() < rows * hidden:
+        raise Hf2qError(_lib.ERR_INVALID_ARGUMENT, "out must be a contiguous float32 CUDA tensor of [n_tokens * top_k, hidden]")
+    if input.numel() < n_tokens * hidden:
+        raise Hf2qError(_lib.ERR_INVALID_ARGUMENT, "input smaller than [n_tokens, hidden]")
+    sg = stride_gate_up if stride_gate_up is not None else expert_stride(type_gate_up, ffn, hidden)
+    sd = stride_down if stride_down is not None else expert_stride(type_down, hidden, ffn)
+    need = C.c_uint64()
+    ctx._check(ctx._lib.hf2q_cuda_moe_experts_scratch_bytes(n_experts, rows, hidden, ffn, C.byref(need)))
+    sc = getattr(ctx, "_moe_scratch", None)
+    if sc is None or sc.numel() < need.value:
+        sc = torch.empty(need.value, dtype=torch.uint8, device=input.device)
+        ctx._moe_scratch = sc
+    ctx._check(ctx._lib.hf2q_cuda_moe_experts(ctx._h, ctx._stream(), input.data_ptr(), xdt, int(gate_ptr), int(up_ptr), int(down_ptr),
+                                              ids.data_ptr(), out.data_ptr(), n_tokens, top_k, hidden, ffn, n_experts, sg,
+                                              int(type_gate_up), sd, int(type_down), sc.data_ptr(), sc.numel()))
 
 
 def dequantize(ctx: GpuContext, weight: QuantWeight, out_dtype=torch.float32) -> torch.Tensor:

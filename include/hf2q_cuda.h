@@ -180,6 +180,26 @@ HF2Q_API int32_t hf2q_cuda_qmatmul_add(hf2q_ctx* ctx, void* stream, const void* 
                                        const void* w, const float* residual, float* y, uint32_t m,
                                        uint32_t n, uint32_t k, uint32_t ggml_type);
 
+/* The two fusions above for ANY number of activation rows (prefill): up to 8 rows they are the calls above;
+ * beyond that the tensor-core GEMM computes the gate and the up tile side by side in tensor memory and
+ * stores silu(gate) * up (five main formats), or adds the residual in its epilogue (any format; residual
+ * may be y itself).  Workspace as for hf2q_cuda_qmatmul (hf2q_cuda_qmatmul_workspace_bytes(m, n, k, ...)).
+ * Replace the reference's gate, up, silu_mul / down, add sequences of build_dense_ffn_layer_gpu_q_into
+ * (src/inference/models/qwen35/gpu_ffn.rs:1150-1330) when m > 8.  *_supported() returns 1 when the
+ * shape takes the fused form; otherwise the calls fail with HF2Q_ERR_INVALID_ARGUMENT. */
+HF2Q_API int32_t hf2q_cuda_qmatmul_swiglu_ws_supported(hf2q_ctx* ctx, uint32_t m, uint32_t n, uint32_t k,
+                                                       uint32_t ggml_type, uint32_t x_dtype);
+HF2Q_API int32_t hf2q_cuda_qmatmul_swiglu_ws(hf2q_ctx* ctx, void* stream, const void* x, uint32_t x_dtype,
+                                             const void* w_gate, const void* w_up, float* y, uint32_t m,
+                                             uint32_t n, uint32_t k, uint32_t ggml_type, void* workspace,
+                                             uint64_t workspace_bytes);
+HF2Q_API int32_t hf2q_cuda_qmatmul_add_ws_supported(hf2q_ctx* ctx, uint32_t m, uint32_t n, uint32_t k,
+                                                    uint32_t ggml_type, uint32_t x_dtype);
+HF2Q_API int32_t hf2q_cuda_qmatmul_add_ws(hf2q_ctx* ctx, void* stream, const void* x, uint32_t x_dtype,
+                                          const void* w, const float* residual, float* y, uint32_t m,
+                                          uint32_t n, uint32_t k, uint32_t ggml_type, void* workspace,
+                                          uint64_t workspace_bytes);
+
 /* Same product for callers that hold HOST buffers: copies x in, runs, copies y out, waits.
  * Uses staging buffers the context grows on first use.  Stands for the reference's
  * `apply_linear_projection_f32` + download pattern in its tests (gpu_ffn.rs:3209-3275). */
@@ -241,6 +261,31 @@ HF2Q_API int32_t hf2q_cuda_qmatmul_id_swiglu(hf2q_ctx* ctx, void* stream, const 
                                              uint32_t ggml_type);
 HF2Q_API int32_t hf2q_cuda_qmatmul_id_scratch_bytes(uint32_t n_experts, uint32_t max_rows,
                                                     uint32_t k, uint32_t x_dtype, uint64_t* out);
+
+/* The routed experts of one MoE layer for MANY routed rows (n_tokens * top_k > 32), four launches:
+ *   sort by expert + gather of x as f16;  gate and up tiles side by side with silu(gate) * up stored as
+ *   the f16 activation panel in expert-sorted order;  the down product reading that panel, rows
+ *   scattered back:  y[n_tokens * top_k][hidden] f32, row r = routed slot r (feed hf2q_cuda_moe_combine).
+ * Replaces quantized_matmul_id (gate), (up), dispatch_silu_mul, quantized_matmul_id (down) of
+ * build_moe_ffn_layer_gpu_q_into (src/inference/models/qwen35/gpu_ffn.rs:2606-2760).  The activation
+ * between the two products is f16, as it is for every tensor-core product of this library.
+ * Rows whose expert id is >= n_experts give zero rows and set the bad-expert status bit.
+ * w_gate / w_up: n_experts stacked [ffn][hidden] matrices `stride_gate_up` bytes apart (one of the five main
+ * formats); w_down: stacked [hidden][ffn], `stride_down` apart.  hidden % 256 == 0, ffn % 256 == 0 and
+ * 16-byte aligned rows; hf2q_cuda_moe_experts_supported() returns 1 when the call will run, otherwise use
+ * hf2q_cuda_qmatmul_id_swiglu / _pair + hf2q_cuda_qmatmul_id.  scratch: 256-byte aligned,
+ * hf2q_cuda_moe_experts_scratch_bytes(). */
+HF2Q_API int32_t hf2q_cuda_moe_experts_scratch_bytes(uint32_t n_experts, uint32_t max_rows, uint32_t hidden,
+                                                     uint32_t ffn, uint64_t* out);
+HF2Q_API int32_t hf2q_cuda_moe_experts_supported(hf2q_ctx* ctx, uint32_t n_tokens, uint32_t top_k, uint32_t hidden,
+                                                 uint32_t ffn, uint32_t n_experts, uint32_t type_gate_up,
+                                                 uint32_t type_down);
+HF2Q_API int32_t hf2q_cuda_moe_experts(hf2q_ctx* ctx, void* stream, const void* x, uint32_t x_dtype,
+                                       const void* w_gate, const void* w_up, const void* w_down,
+                                       const uint32_t* ids, float* y, uint32_t n_tokens, uint32_t top_k,
+                                       uint32_t hidden, uint32_t ffn, uint32_t n_experts,
+                                       uint64_t stride_gate_up, uint32_t type_gate_up, uint64_t stride_down,
+                                       uint32_t type_down, void* scratch, uint64_t scratch_bytes);
 
 /* dispatch_moe_softmax_topk (gpu_ffn.rs:2551), semantics of softmax_topk_renorm_cpu
  * (gpu_ffn.rs:1879-1924): logits f32 [n_tokens, n_experts] -> ids u32 [n_tokens*top_k] (descending

@@ -159,3 +159,95 @@ def test_moe_ffn_builder(gpu_ctx, T):
     got = y.cpu().numpy()
     assert np.abs(got - want).max() < 2e-2
     assert rel_l2(got, want) < 3e-3
+
+
+@pytest.mark.parametrize("t", list(oracle.MAIN_TYPES))
+def test_dense_ffn_gemm_forms_equal_the_separate_ops(gpu_ctx, t):
+    """More than 8 rows: gate and up tiles side by side in tensor memory with the SwiGLU in the epilogue, and the
+    residual added in the GEMM's epilogue -- the same tensor-core accumulation as the separate products, so the
+    outputs are bit-identical to gate, up, silu_mul / down, add."""
+    from hf2q_b200 import ops
+    hidden, inter = 2048, 1536 + 48                   # inter: a partial last 64-row tile
+    gq, gf = _qw(gpu_ctx, t, inter, hidden, 21)
+    uq, uf = _qw(gpu_ctx, t, inter, hidden, 22)
+    dq, _ = _qw(gpu_ctx, t, hidden, 2048, 23)
+    for m, bf16 in ((9, False), (70, True), (200, False), (333, True)):
+        x = make_x(m, hidden, seed=30 + m)
+        xd = torch.from_numpy(x).cuda()
+        if bf16:
+            xd = xd.bfloat16()
+            x = xd.float().cpu().numpy()
+        assert ops.quantized_matmul_swiglu_supported(gpu_ctx, m, gq, xd.dtype)
+        a = torch.empty((m, inter), device="cuda")
+        b = torch.empty_like(a)
+        ops.quantized_matmul_ggml(gpu_ctx, xd, gq, a, gq.matmul_params(m))
+        ops.quantized_matmul_ggml(gpu_ctx, xd, uq, b, uq.matmul_params(m))
+        sep = ffn._silu_mul(gpu_ctx, a, b)
+        fused = torch.full((m, inter), float("nan"), device="cuda")
+        n0 = gpu_ctx.launch_count
+        ops.quantized_matmul_swiglu(gpu_ctx, xd, gq, uq, fused, m)
+        assert gpu_ctx.launch_count - n0 == 2              # activation conversion + the one GEMM
+        gpu_ctx.check_status()
+        assert torch.equal(fused, sep), (t, m)
+        g64, u64 = x.astype(np.float64) @ gf.T.astype(np.float64), x.astype(np.float64) @ uf.T.astype(np.float64)
+        assert rel_l2(fused.cpu().numpy(), g64 / (1.0 + np.exp(-g64)) * u64) < 2e-3
+        c = torch.from_numpy(make_x(m, 2048, seed=40 + m)).cuda()
+        res = torch.from_numpy(make_x(m, hidden, seed=50 + m)).cuda()
+        assert ops.quantized_matmul_add_supported(gpu_ctx, dq, c.dtype, m)
+        y = torch.empty((m, hidden), device="cuda")
+        ops.quantized_matmul_ggml(gpu_ctx, c, dq, y, dq.matmul_params(m))
+        want_y = y + res
+        got = res.clone()
+        ops.quantized_matmul_add(gpu_ctx, c, dq, got, got, m)         # in place on the residual stream
+        gpu_ctx.check_status()
+        assert torch.equal(got, want_y), (t, m)
+    # the 32-element fall-back formats have the residual form but not the pair
+    wf = hq.load_quant_weight(gpu_ctx, make_quant_weight(oracle.Q5_0, 64, 2048, seed=3), oracle.Q5_0, 64, 2048)
+    assert not ops.quantized_matmul_swiglu_supported(gpu_ctx, 40, wf, torch.float32)
+    assert ops.quantized_matmul_add_supported(gpu_ctx, wf, torch.float32, 40)
+    with pytest.raises(hq.Hf2qError):
+        ops.quantized_matmul_swiglu(gpu_ctx, torch.zeros((40, 2048), device="cuda"), wf, wf, torch.empty((40, 64), device="cuda"), 40)
+
+
+@pytest.mark.parametrize("tg,td", [(oracle.Q4_K, oracle.Q6_K), (oracle.Q4_0, oracle.Q8_0), (oracle.Q5_K, oracle.Q5_1)])
+def test_moe_experts_equals_the_separate_ops(gpu_ctx, tg, td):
+    """Sort + gather, gate/up pair with the SwiGLU epilogue writing the sorted f16 panel, down reading it:
+    bit-identical to mul_mat_id (gate), (up), silu_mul, mul_mat_id (down)."""
+    from hf2q_b200 import ops
+    hidden, inter, E, top_k = 2048, 2048, 7, 3            # Q6_K rows are 16-byte aligned from 2048 elements on
+    sg, sd = hq.expert_stride(tg, inter, hidden), hq.expert_stride(td, hidden, inter)
+    gate = torch.from_numpy(np.concatenate([make_quant_weight(tg, inter, hidden, seed=60 + e) for e in range(E)])).cuda()
+    up = torch.from_numpy(np.concatenate([make_quant_weight(tg, inter, hidden, seed=70 + e) for e in range(E)])).cuda()
+    down = torch.from_numpy(np.concatenate([make_quant_weight(td, hidden, inter, seed=80 + e) for e in range(E)])).cuda()
+    for T in (12, 150, 700):
+        rows = T * top_k
+        x = torch.from_numpy(make_x(T, hidden, seed=90 + T)).cuda()
+        rng = np.random.default_rng(T)
+        # skewed routing: expert 0 is hot, expert E-1 gets nothing
+        pick = np.stack([rng.choice(E - 1, size=top_k, replace=False, p=np.r_[0.4, np.full(E - 2, 0.6 / (E - 2))]) for _ in range(T)])
+        ids = torch.from_numpy(pick.astype(np.int32).reshape(-1)).cuda()
+        assert ops.moe_experts_supported(gpu_ctx, T, top_k, hidden, inter, E, tg, td)
+        pg = hq.GgmlQuantizedMatmulIdParams(T, top_k, inter, hidden, E, sg, tg)
+        pd = hq.GgmlQuantizedMatmulIdParams(rows, 1, hidden, inter, E, sd, td)
+        scratch = ops.IdMmScratch.alloc(gpu_ctx, E, rows, max(hidden, inter))
+        g = torch.empty((rows, inter), device="cuda")
+        u = torch.empty_like(g)
+        hq.quantized_matmul_id_pair_ggml(gpu_ctx, x, gate.data_ptr(), up.data_ptr(), ids, g, u, scratch, pg)
+        act = ffn._silu_mul(gpu_ctx, g, u)
+        want = torch.empty((rows, hidden), device="cuda")
+        hq.quantized_matmul_id_ggml(gpu_ctx, act, down.data_ptr(), ids, want, scratch, pd)
+        got = torch.full((rows, hidden), float("nan"), device="cuda")
+        n0 = gpu_ctx.launch_count
+        ops.moe_experts(gpu_ctx, x, gate.data_ptr(), up.data_ptr(), down.data_ptr(), ids, got, T, top_k, hidden, inter, E, tg, td)
+        assert gpu_ctx.launch_count - n0 == 4
+        gpu_ctx.check_status()
+        assert torch.equal(got, want), (tg, td, T)
+    # an expert index out of range: zero row, status bit
+    bad = ids.clone()
+    bad[5] = E + 3
+    ops.moe_experts(gpu_ctx, x, gate.data_ptr(), up.data_ptr(), down.data_ptr(), bad, got, T, top_k, hidden, inter, E, tg, td)
+    with pytest.raises(hq.Hf2qError):
+        gpu_ctx.check_status()
+    assert torch.count_nonzero(got[5]) == 0 and torch.equal(got[4], want[4]) and torch.equal(got[6], want[6])
+    assert not ops.moe_experts_supported(gpu_ctx, 4, top_k, hidden, inter, E, tg, td)          # few rows: the mat-vec forms
+    assert not ops.moe_experts_supported(gpu_ctx, T, top_k, hidden, inter, E, oracle.IQ4_NL, td)
