@@ -287,6 +287,23 @@ def bench_gemm(hq, oracle, torch, ctx, dev, args, toks=None) -> dict:
             flops += 2.0 * m * n * k
             secs += dt
         del ws
+    # the same gate/up product with the two tiles side by side and the SwiGLU in the epilogue, and the down product
+    # with the residual in its epilogue (reported beside the sweep, not part of its sum)
+    fused = {}
+    # (scales of order 2^-11 keep gate and up of order one, as real activations are: the SiLU's division then stays on
+    # its fast path; with |gate| in the thousands half of the divisions take the slow path for an infinite divisor)
+    gq, uq = (hq.load_quant_weight(ctx, _random_weight(torch, oracle, dev, 12, 14336, 4096, exp_mask=0x0F), 12, 14336, 4096) for _ in range(2))
+    dq = hq.load_quant_weight(ctx, _random_weight(torch, oracle, dev, 14, 4096, 14336), 14, 4096, 14336)
+    for m in toks:
+        x = torch.randn(m, 4096, device=dev).bfloat16()
+        act = torch.empty(m, 14336, device=dev)
+        dt = _timed(torch, lambda: hq.ops.quantized_matmul_swiglu(ctx, x, gq, uq, act, m), reps)
+        fused[f"gate_up_swiglu_2x14336x4096[Q4_K]_M{m}"] = round(2.0 * m * 28672 * 4096 / dt / 1e12, 1)
+        a16 = torch.randn(m, 14336, device=dev).bfloat16()
+        res = torch.zeros(m, 4096, device=dev)
+        dt = _timed(torch, lambda: hq.ops.quantized_matmul_add(ctx, a16, dq, res, res, m), reps)
+        fused[f"down_add_4096x14336[Q6_K]_M{m}"] = round(2.0 * m * 4096 * 14336 / dt / 1e12, 1)
+    del gq, uq, dq
     sus, burst, kind = measured_tensor_peaks()
     val = flops / secs / 1e12
     ctx.check_status()
@@ -297,7 +314,7 @@ def bench_gemm(hq, oracle, torch, ctx, dev, args, toks=None) -> dict:
             "roofline": {"bound": "tensor", "achieved": round(val, 1), "peak": sus, "unit": "TFLOP/s",
                          "frac": round(val / sus, 4), "peak_source": f"of {kind} (sustained)", "peak_burst": burst,
                          "frac_of_burst": round(val / burst, 4), "kernel": "gemm_tc_kernel", "traffic": None},
-            "per_case_TFLOPs": per, "gpu_launches": int(ctx.launch_count - l0), "clocks": sampler.stop()}
+            "per_case_TFLOPs": per, "fused_epilogue_TFLOPs": fused, "gpu_launches": int(ctx.launch_count - l0), "clocks": sampler.stop()}
 
 
 def bench_config1(hq, oracle, torch, ctx, dev, args) -> dict:
@@ -370,8 +387,9 @@ def bench_moe(hq, oracle, torch, ctx, dev, args, toks=None) -> dict:
     layer (router softmax/top-k outputs -> gate, up, SwiGLU, down, weighted combine) at T in {1, 2048}."""
     t, E, H, I, topk = 13, 256, 2048, 512, 8
     sg, sd = hq.expert_stride(t, I, H), hq.expert_stride(t, H, I)
-    wg, wu, wd = (_random_weight(torch, oracle, dev, t, E * I, H), _random_weight(torch, oracle, dev, t, E * I, H),
-                  _random_weight(torch, oracle, dev, t, E * H, I))
+    # scales of order 2^-11: the SwiGLU output feeds the down product as f16 and must stay inside its range
+    wg, wu, wd = (_random_weight(torch, oracle, dev, t, E * I, H, exp_mask=0x0F), _random_weight(torch, oracle, dev, t, E * I, H, exp_mask=0x0F),
+                  _random_weight(torch, oracle, dev, t, E * H, I, exp_mask=0x0F))
     res = {}
     l0 = ctx.launch_count
     sampler = ClockSampler(ctx.device)
@@ -383,12 +401,11 @@ def bench_moe(hq, oracle, torch, ctx, dev, args, toks=None) -> dict:
         # routings that pick different experts so that weights come from HBM; one CUDA graph
         # holds all of them (launch overhead of the Python calls stays out of the timing)
         nsets = 16 if T <= 8 else 1
-        x = torch.randn(T, H, device=dev).bfloat16()
+        x = (torch.randn(T, H, device=dev) * 0.02).bfloat16()
         R = T * topk
         g, u = torch.empty(R, I, device=dev), torch.empty(R, I, device=dev)
         d = torch.empty(R, H, device=dev)
         out = torch.empty(T, H, device=dev)
-        act = torch.randn(R, I, device=dev).bfloat16()
         sc = hq.IdMmScratch.alloc(ctx, E, R, H)
         pg = hq.GgmlQuantizedMatmulIdParams(T, topk, I, H, E, sg, t)
         pd = hq.GgmlQuantizedMatmulIdParams(R, 1, H, I, E, sd, t)
@@ -404,15 +421,18 @@ def bench_moe(hq, oracle, torch, ctx, dev, args, toks=None) -> dict:
             wt_sets.append(wts)
 
         fused = hq.ops.quantized_matmul_id_swiglu_supported(ctx, pg, x.dtype)
+        experts = hq.ops.moe_experts_supported(ctx, T, topk, H, I, E, t, t)
 
         def layer(ids, wts):
-            if fused:     # few routed rows: gate, up and the SwiGLU in one launch
-                hq.ops.quantized_matmul_id_swiglu_ggml(ctx, x, wg.data_ptr(), wu.data_ptr(), ids, g, pg)
+            if experts:   # many routed rows: sort + gather, gate/up pair with the SwiGLU epilogue, down
+                hq.ops.moe_experts(ctx, x, wg.data_ptr(), wu.data_ptr(), wd.data_ptr(), ids, d, T, topk, H, I, E, t, t, sg, sd)
             else:
-                hq.quantized_matmul_id_pair_ggml(ctx, x, wg.data_ptr(), wu.data_ptr(), ids, g, u, sc, pg)   # gate + up
-                ctx._check(ctx._lib.hf2q_cuda_silu_mul(ctx._h, ctx._stream(), g.data_ptr(), u.data_ptr(), g.data_ptr(), g.numel()))
-            # (down reads synthetic activations: products of random block bytes leave the f16 range)
-            hq.quantized_matmul_id_ggml(ctx, act, wd.data_ptr(), ids, d, sc, pd)
+                if fused:     # few routed rows: gate, up and the SwiGLU in one launch
+                    hq.ops.quantized_matmul_id_swiglu_ggml(ctx, x, wg.data_ptr(), wu.data_ptr(), ids, g, pg)
+                else:
+                    hq.quantized_matmul_id_pair_ggml(ctx, x, wg.data_ptr(), wu.data_ptr(), ids, g, u, sc, pg)   # gate + up
+                    ctx._check(ctx._lib.hf2q_cuda_silu_mul(ctx._h, ctx._stream(), g.data_ptr(), u.data_ptr(), g.data_ptr(), g.numel()))
+                hq.quantized_matmul_id_ggml(ctx, g, wd.data_ptr(), ids, d, sc, pd)
             ctx._check(ctx._lib.hf2q_cuda_moe_combine(ctx._h, ctx._stream(), d.data_ptr(), wts.data_ptr(), None, None, None,
                                                       out.data_ptr(), T, topk, H))
 
@@ -430,7 +450,7 @@ def bench_moe(hq, oracle, torch, ctx, dev, args, toks=None) -> dict:
                         "weight_GBps": round(wbytes / dt / 1e9, 1), "experts_touched": nexp,
                         "roofline_hbm_us": round(t_hbm * 1e6, 1), "roofline_tensor_us": round(t_tc * 1e6, 1),
                         "frac_of_binding_roofline": round(max(t_hbm, t_tc) / dt, 4),
-                        "swiglu_in_gate_up_launch": bool(fused),
+                        "swiglu_in_gate_up_launch": bool(fused or experts), "launches_per_layer": 5 if experts else (3 if fused else None),
                         "timing": f"CUDA graph of {nsets} layer(s) with different routings; gate+up, SwiGLU, down and the weighted combine"}
     ctx.check_status()
     last = res[sorted(res)[-1]]

@@ -335,6 +335,37 @@ HF2Q_API int32_t hf2q_cuda_qmatmul(hf2q_ctx* ctx, void* stream, const void* x, u
     return run_matvec(ctx, st, a, m, "qmatmul launch");
 }
 
+// The O projection of a prefill chunk reading the attention output where flash attention wrote it:
+// x is [k / head_dim heads][m][head_dim] (bf16 in the reference, f32 accepted as well).
+HF2Q_API int32_t hf2q_cuda_qmatmul_perm021(hf2q_ctx* ctx, void* stream, const void* x, uint32_t x_dtype, const void* w, float* y,
+                                           uint32_t m, uint32_t n, uint32_t k, uint32_t head_dim, uint32_t type, void* workspace,
+                                           uint64_t workspace_bytes) {
+    if (!ctx) return HF2Q_ERR_INVALID_ARGUMENT;
+    const char* who = "qmatmul_perm021";
+    if (!x || !w || !y) return fail(ctx, HF2Q_ERR_INVALID_ARGUMENT, "%s: null pointer", who);
+    if (x_dtype != HF2Q_DT_F32 && x_dtype != HF2Q_DT_BF16) return fail(ctx, HF2Q_ERR_INVALID_ARGUMENT, "%s: x_dtype %u (want F32 or BF16)", who, x_dtype);
+    int32_t rc = check_matmul_shape(ctx, type, n, k, who);
+    if (rc) return rc;
+    if (head_dim == 0 || head_dim % 8 || k % head_dim)
+        return fail(ctx, HF2Q_ERR_INVALID_ARGUMENT, "%s: head_dim=%u must be a multiple of 8 that divides k=%u", who, head_dim, k);
+    if (m == 0) return HF2Q_OK;
+    if (reinterpret_cast<uintptr_t>(x) % 16 || reinterpret_cast<uintptr_t>(y) % 4) return fail(ctx, HF2Q_ERR_INVALID_ARGUMENT, "%s: misaligned buffer", who);
+    if (ctx->fp32_matvec || !gemm_tc_supported(type, w, n, k))
+        return fail(ctx, HF2Q_ERR_INVALID_ARGUMENT, "%s: needs the tensor-core GEMM (16-byte aligned weight rows, k %% 256 == 0)", who);
+    const uint64_t need = gemm_tc_workspace_bytes(m, k);
+    if (!workspace || workspace_bytes < need)
+        return fail(ctx, HF2Q_ERR_WORKSPACE, "%s: m=%u needs a workspace of %llu bytes (got %llu)", who, m, (unsigned long long)need,
+                    (unsigned long long)workspace_bytes);
+    if (reinterpret_cast<uintptr_t>(workspace) % 256) return fail(ctx, HF2Q_ERR_INVALID_ARGUMENT, "%s: workspace must be 256-byte aligned", who);
+    DeviceGuard dg(ctx->device);
+    int nl = 0;
+    const cudaError_t e = launch_gemm_tc(type, w, x, x_dtype, y, m, n, k, workspace, ctx->status, ctx->dev.sm_count,
+                                         static_cast<cudaStream_t>(stream), &nl, 0, false, nullptr, head_dim);
+    if (e != cudaSuccess) return cuda_fail(ctx, e, "qmatmul_perm021 launch");
+    ctx->launches += nl;
+    return HF2Q_OK;
+}
+
 // A matrix whose row ranges use different block formats (the fused QKV tensor of a Q4_K_M model:
 // Q and K rows Q4_K, V rows Q6_K): one call, one conversion of the activations, one launch per range,
 // every range writing its own columns of the one output.
@@ -1023,8 +1054,7 @@ HF2Q_API int32_t hf2q_cuda_moe_experts(hf2q_ctx* ctx, void* stream, const void* 
     DeviceGuard dg(ctx->device);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     void* act16 = static_cast<uint8_t*>(scratch) + lay.total;
-    uint32_t nt = moe_token_tile(rows, n_experts);
-    if (nt > 128) nt = 128;                                    // the pair launch takes token tiles of at most 128
+    const uint32_t nt = moe_token_tile(rows, n_experts);
     // the sort also zero-fills y: rows whose expert id is out of range stay zero, as in hf2q_cuda_qmatmul_id
     cudaError_t e = launch_moe_prep(ids, rows, n_experts, top_k, nt, x, x_dtype, hidden, y, nullptr, hidden, scratch, lay, ctx->status,
                                     ctx->dev.sm_count, st);

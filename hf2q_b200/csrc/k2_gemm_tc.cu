@@ -48,14 +48,20 @@ namespace {
 constexpr int TILE_N = 128;      // weight rows per CTA (MMA M)
 constexpr int KB = 256;          // K elements per block step
 constexpr int XK = 64;           // K elements per activation stage (128 bytes of f16)
-constexpr int raw_stages_of(uint32_t type, int nt) { return (type == HF2Q_TYPE_Q8_0 || nt >= 256 || nt <= 64) ? 2 : 3; }
-// Tiles of <= 64 tokens run two CTAs per SM (one CTA's fixed latencies hide behind the other's work):
-// one A buffer instead of two and 256 TMEM columns instead of 512.
-constexpr int a_bufs_of(int nt) { return nt <= 64 ? 1 : 2; }
-constexpr uint32_t tmem_cols_of(int nt) { return nt <= 64 ? 256u : 512u; }
+// Tiles of <= 64 tokens, and the 128-token tiles of the expert-routed product (short K, many tiles), run two CTAs
+// per SM (one CTA's fixed latencies and its epilogue hide behind the other's work): one A buffer instead of two,
+// 256 TMEM columns instead of 512, and buffers sized so that two CTAs fit the SM's shared memory.
+constexpr bool two_ctas_of(int nt, bool grouped) { return nt <= 64 || (grouped && nt == 128); }
+constexpr int raw_stages_of(uint32_t type, int nt, bool grouped) {
+    return (type == HF2Q_TYPE_Q8_0 || nt >= 256 || two_ctas_of(nt, grouped)) ? 2 : 3;
+}
+constexpr int a_bufs_of(int nt, bool grouped) { return two_ctas_of(nt, grouped) ? 1 : 2; }
+constexpr uint32_t tmem_cols_of(int nt, bool grouped) { return two_ctas_of(nt, grouped) ? 256u : 512u; }
 // activation stages: one stage is NT rows x 64 elements; keep ~128 KB of them in flight so that the
 // copies for the next K-blocks are issued long before the MMA warp needs them
-constexpr int x_stages_of(uint32_t type, int nt) { return nt >= 256 ? (type == HF2Q_TYPE_Q8_0 ? 4 : 5) : 8; }
+constexpr int x_stages_of(uint32_t type, int nt, bool grouped) {
+    return nt >= 256 ? (type == HF2Q_TYPE_Q8_0 ? 4 : 5) : (grouped && nt == 128) ? 3 : 8;
+}
 constexpr int DEQ_GROUPS = 2;                        // groups of 4 dequantiser warps; group g takes quarters g*2, g*2+1
 constexpr int QPG = 4 / DEQ_GROUPS;                  // quarters (64 elements) of a K-block per group
 constexpr int DEQ_WARPS = 4 * DEQ_GROUPS;
@@ -122,15 +128,15 @@ __device__ __forceinline__ void dequant_dispatch(uint32_t grp, const uint8_t* ro
 // SwiGLU of build_dense_ffn_layer_gpu_q / build_moe_ffn_layer_gpu_q (gpu_ffn.rs:896-935, 2606-2760) without
 // the two f32 round trips and the dispatch_silu_mul in between.
 template <uint32_t TYPE, int NT, bool GROUPED, bool DUAL>
-__global__ void __launch_bounds__(GEMM_THREADS, (NT <= 64 ? 2 : 1))
+__global__ void __launch_bounds__(GEMM_THREADS, (two_ctas_of(NT, GROUPED) ? 2 : 1))
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_w2,
                const __grid_constant__ CUtensorMap tmap_x, const GParams p) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
     constexpr uint32_t X_STAGE = NT * 128;                       // NT rows x 64 f16, 128B-swizzled
-    constexpr int X_STAGES = x_stages_of(TYPE, NT);
+    constexpr int X_STAGES = x_stages_of(TYPE, NT, GROUPED);
     uint8_t* xs = smem;                                          // X_STAGES x X_STAGE (1024-aligned)
-    constexpr int RAW_STAGES = DUAL ? 2 : raw_stages_of(TYPE, NT);
+    constexpr int RAW_STAGES = raw_stages_of(TYPE, NT, GROUPED);
     constexpr uint32_t TILE_ROWS = DUAL ? 64 : TILE_N;           // output rows of one tile
     uint8_t* raw = xs + X_STAGES * X_STAGE;                      // RAW_STAGES x 128 x boxw
     const uint32_t raw_stage = TILE_N * p.boxw;
@@ -139,8 +145,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
     uint64_t* raw_empty = raw_full + RAW_STAGES;
     uint64_t* x_full = raw_empty + RAW_STAGES;  // [X_STAGES]
     uint64_t* x_empty = x_full + X_STAGES;
-    constexpr int A_BUFS = a_bufs_of(NT);
-    constexpr uint32_t TMEM_COLS = tmem_cols_of(NT);
+    constexpr int A_BUFS = a_bufs_of(NT, GROUPED);
+    constexpr uint32_t TMEM_COLS = tmem_cols_of(NT, GROUPED);
     uint64_t* a_full = x_empty + X_STAGES;      // [2]
     uint64_t* a_empty = a_full + 2;
     uint64_t* d_full = a_empty + 2;             // [1]
@@ -177,7 +183,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
     const uint32_t tmem_a = tmem_base + (A_BUFS == 1 ? 128 : 256);     // A_BUFS buffers of 128 columns
 
     if (warp == DEQ_WARPS) {
-        // ------------------------------ TMA producer
+        // ------------------------------ TMA producer: lane 0 streams the weight stages, lane 1 the activation stages
+        // (two independent rings: a full activation ring must not hold back the next weight stage)
         if (lane == 0) {
             bool ok = true;
             for (uint32_t tl = 0, gk = 0; tl < ntile && ok; ++tl) {           // gk: K-block count over all tiles
@@ -199,14 +206,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
                         else
                             tma_2d(dst2, &tmap_w2, static_cast<int>(byte0 >> 1), static_cast<int>(row0), &raw_full[rs]);
                     }
-                    for (uint32_t j = 0; j < KB / XK && ok; ++j) {
-                        const uint32_t xi = gk * (KB / XK) + j, st = xi % X_STAGES;
-                        if (xi >= X_STAGES) ok = mbar_wait_bounded(&x_empty[st], ((xi / X_STAGES) - 1) & 1, p.status);
-                        if (!ok) break;
-                        mbar_arrive_expect_tx(&x_full[st], X_STAGE);
-                        tma_2d(xs + st * X_STAGE, &tmap_x, static_cast<int>(kb * KB + j * XK), static_cast<int>(tok0), &x_full[st]);
-                    }
                 }
+            }
+        } else if (lane == 1) {
+            bool ok = true;
+            const uint32_t nx = ntile * nkb * (KB / XK);
+            for (uint32_t xi = 0; xi < nx && ok; ++xi) {
+                const uint32_t st = xi % X_STAGES, kx = xi % (nkb * (KB / XK));      // K position inside the current tile
+                if (xi >= X_STAGES) ok = mbar_wait_bounded(&x_empty[st], ((xi / X_STAGES) - 1) & 1, p.status);
+                if (!ok) break;
+                mbar_arrive_expect_tx(&x_full[st], X_STAGE);
+                tma_2d(xs + st * X_STAGE, &tmap_x, static_cast<int>(kx * XK), static_cast<int>(tok0), &x_full[st]);
             }
         }
     } else if (warp == DEQ_WARPS + 1) {
@@ -272,8 +282,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
             if (!ok) break;
             tc_fence_after();
             if constexpr (DUAL) {
-                // lanes 0..15 of this warp hold gate rows, lanes 16..31 the up rows of the same 16 outputs
+                // lanes 0..15 of this warp hold gate rows, lanes 16..31 the up rows of the same 16 outputs.  Of each
+                // pair of tokens the lower lane finishes the even one and the upper lane the odd one: one exchange
+                // per pair, every lane busy.
                 const uint32_t row = row0 + 16 * quad + (lane & 15);
+                const bool upper = lane >= 16;
                 bool clipped = false;
 #pragma unroll 1
                 for (int c0 = 32 * static_cast<int>(grp); c0 < NT; c0 += 32 * DEQ_GROUPS) {
@@ -281,11 +294,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
                     tmem_ld32(tmem_d + lane_addr + c0, v);
                     tmem_wait_ld();
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) {
-                        const float u = __shfl_down_sync(0xffffffffu, __uint_as_float(v[j]), 16);
-                        const uint32_t tok = tok0 + c0 + j;
-                        if (lane < 16 && row < p.n && tok < tok_end) {
-                            const float g = __uint_as_float(v[j]);
+                    for (int j = 0; j < 32; j += 2) {
+                        const float other = __shfl_xor_sync(0xffffffffu, __uint_as_float(upper ? v[j] : v[j + 1]), 16);
+                        const float g = upper ? other : __uint_as_float(v[j]);
+                        const float u = upper ? __uint_as_float(v[j + 1]) : other;
+                        const uint32_t tok = tok0 + c0 + j + (upper ? 1 : 0);
+                        if (row < p.n && tok < tok_end) {
                             const float act = g / (1.0f + expf(-g)) * u;
                             if (GROUPED && p.act16) {          // same clipping rule as the f32 -> f16 conversion of any activation panel
                                 clipped |= fabsf(act) > 65504.0f;
@@ -305,15 +319,23 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
                 tmem_ld32(tmem_d + lane_addr + c0, v);
                 tmem_wait_ld();
                 if (row < p.n) {
+                    if (p.residual) {
+                        // y may be the residual itself: issue all loads before the first store
+                        float res[32];
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) {
+                            const uint32_t tok = tok0 + c0 + j;
+                            res[j] = tok < tok_end ? __ldcg(p.residual + static_cast<size_t>(GROUPED ? p.perm[tok] : tok) * p.ldy + row) : 0.f;
+                        }
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) v[j] = __float_as_uint(__uint_as_float(v[j]) + res[j]);
+                    }
 #pragma unroll
                     for (int j = 0; j < 32; ++j) {
                         const uint32_t tok = tok0 + c0 + j;
                         if (tok < tok_end) {
                             const uint32_t dst = GROUPED ? p.perm[tok] : tok;      // scatter back to routed-row order
-                            const size_t o = static_cast<size_t>(dst) * p.ldy + row;
-                            float out = __uint_as_float(v[j]);
-                            if (p.residual) out += p.residual[o];
-                            p.y[o] = out;
+                            p.y[static_cast<size_t>(dst) * p.ldy + row] = __uint_as_float(v[j]);
                         }
                     }
                 }
@@ -344,6 +366,40 @@ __global__ void __launch_bounds__(256) x_to_f16_kernel(const void* __restrict__ 
     if (clipped) atomicOr(status, STATUS_X_CLIPPED);
 }
 
+// The same conversion for activations stored [n_heads][m][head_dim] (the layout flash attention writes; the
+// reference's O projection reads it through quantized_matmul_mm_tensor_perm021, forward_prefill_batched.rs:2218-2258):
+// logical (t, c) is physical (h = c / head_dim, t, f = c % head_dim).  8 elements per thread.
+__global__ void __launch_bounds__(256) x_perm021_to_f16_kernel(const void* __restrict__ x, uint32_t x_bf16, __half* __restrict__ out,
+                                                               uint32_t m, uint32_t k, uint32_t head_dim, uint32_t* status) {
+    const uint64_t n8 = static_cast<uint64_t>(m) * k / 8, stride = static_cast<uint64_t>(gridDim.x) * blockDim.x;
+    bool clipped = false;
+    for (uint64_t i = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n8; i += stride) {
+        const uint64_t e = i * 8;
+        const uint32_t t = static_cast<uint32_t>(e / k), c = static_cast<uint32_t>(e % k), h = c / head_dim, f = c % head_dim;
+        const uint64_t src = (static_cast<uint64_t>(h) * m + t) * head_dim + f;
+        float v[8];
+        if (x_bf16) {
+            const uint4 r = __ldg(reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(x) + src));
+            const uint32_t rr[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+            for (int j = 0; j < 4; ++j) { v[2 * j] = __uint_as_float(rr[j] << 16); v[2 * j + 1] = __uint_as_float(rr[j] & 0xffff0000u); }
+        } else {
+            const float4 a = __ldg(reinterpret_cast<const float4*>(static_cast<const float*>(x) + src));
+            const float4 b = __ldg(reinterpret_cast<const float4*>(static_cast<const float*>(x) + src + 4));
+            v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+        }
+        uint32_t o[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            clipped |= (fabsf(v[2 * j]) > 65504.0f) | (fabsf(v[2 * j + 1]) > 65504.0f);
+            const __half2 hh = __floats2half2_rn(fminf(fmaxf(v[2 * j], -65504.0f), 65504.0f), fminf(fmaxf(v[2 * j + 1], -65504.0f), 65504.0f));
+            o[j] = *reinterpret_cast<const uint32_t*>(&hh);
+        }
+        *reinterpret_cast<uint4*>(out + e) = make_uint4(o[0], o[1], o[2], o[3]);
+    }
+    if (clipped) atomicOr(status, STATUS_X_CLIPPED);
+}
+
 // ---------------------------------------------------------------- host side
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
@@ -367,8 +423,8 @@ uint32_t boxw_of(uint32_t type) { return tc_boxw(type); }
 template <uint32_t TYPE, int NT, bool GROUPED, bool DUAL = false>
 cudaError_t launch_gemm_t(const CUtensorMap& tw, const CUtensorMap& tw2, const CUtensorMap& tx, const GParams& p, uint32_t grid_y, cudaStream_t st) {
     auto kern = gemm_tc_kernel<TYPE, NT, GROUPED, DUAL>;
-    const size_t raw_stages = DUAL ? 2 : raw_stages_of(TYPE, NT);
-    const size_t smem = 1024 + static_cast<size_t>(x_stages_of(TYPE, NT)) * NT * 128 + raw_stages * TILE_N * p.boxw + 512;
+    const size_t raw_stages = raw_stages_of(TYPE, NT, GROUPED);
+    const size_t smem = 1024 + static_cast<size_t>(x_stages_of(TYPE, NT, GROUPED)) * NT * 128 + raw_stages * TILE_N * p.boxw + 512;
     static PerDeviceFlag attr;
     if (const cudaError_t e = ensure_max_dynamic_smem(kern, 227 * 1024, attr); e != cudaSuccess) return e;
     const uint32_t tile_rows = DUAL ? 64 : TILE_N;
@@ -389,14 +445,15 @@ cudaError_t launch_gemm_nt(const CUtensorMap& tw, const CUtensorMap& tx, const G
     }
 }
 
-// the SwiGLU pair: token tiles of at most 128
+// the SwiGLU pair
 template <uint32_t TYPE, bool GROUPED>
 cudaError_t launch_gemm_dual_nt(const CUtensorMap& tg, const CUtensorMap& tu, const CUtensorMap& tx, const GParams& p, uint32_t nt, uint32_t gy,
                                 cudaStream_t st) {
     switch (nt) {
         case 32: return launch_gemm_t<TYPE, 32, GROUPED, true>(tg, tu, tx, p, gy, st);
         case 64: return launch_gemm_t<TYPE, 64, GROUPED, true>(tg, tu, tx, p, gy, st);
-        default: return launch_gemm_t<TYPE, 128, GROUPED, true>(tg, tu, tx, p, gy, st);
+        case 128: return launch_gemm_t<TYPE, 128, GROUPED, true>(tg, tu, tx, p, gy, st);
+        default: return launch_gemm_t<TYPE, 256, GROUPED, true>(tg, tu, tx, p, gy, st);
     }
 }
 
@@ -436,7 +493,7 @@ namespace {
 // w_up != nullptr: the SwiGLU pair (w = gate); residual != nullptr: y = product + residual
 cudaError_t gemm_tc_dense(uint32_t type, const void* w, const void* w_up, const void* x, uint32_t x_dtype, float* y, uint32_t m, uint32_t n,
                           uint32_t k, void* workspace, uint32_t* status, int sm_count, cudaStream_t st, int* launches,
-                          uint32_t ldy, bool x_ready, const float* residual) {
+                          uint32_t ldy, bool x_ready, const float* residual, uint32_t perm_head_dim = 0) {
     const bool dual = w_up != nullptr;
     const BlockGeom g = block_geom(type);
     const uint64_t row_bytes = static_cast<uint64_t>(k) / g.elems * g.bytes;
@@ -449,7 +506,12 @@ cudaError_t gemm_tc_dense(uint32_t type, const void* w, const void* w_up, const 
     if (!x_ready) {       // (a caller that runs several products on the same activations converts them once)
         uint64_t want = (nx + 255) / 256;
         const uint64_t cap = static_cast<uint64_t>(sm_count) * 16;
-        x_to_f16_kernel<<<static_cast<unsigned>(want < cap ? want : cap), 256, 0, st>>>(x, x_dtype == HF2Q_DT_BF16, xh, nx, status);
+        if (perm_head_dim) {
+            want = (nx / 8 + 255) / 256;
+            x_perm021_to_f16_kernel<<<static_cast<unsigned>(want < cap ? want : cap), 256, 0, st>>>(x, x_dtype == HF2Q_DT_BF16, xh, m, k, perm_head_dim, status);
+        } else {
+            x_to_f16_kernel<<<static_cast<unsigned>(want < cap ? want : cap), 256, 0, st>>>(x, x_dtype == HF2Q_DT_BF16, xh, nx, status);
+        }
         cudaError_t e = cudaGetLastError();
         if (e != cudaSuccess) return e;
     }
@@ -463,8 +525,7 @@ cudaError_t gemm_tc_dense(uint32_t type, const void* w, const void* w_up, const 
     p.blk_bytes = KB / g.elems * g.bytes;
     p.status = status;
     const uint32_t tile_rows = dual ? 64 : TILE_N;
-    uint32_t nt = gemm_tc_token_tile(m, (n + tile_rows - 1) / tile_rows, sm_count);
-    if (dual && nt > 128) nt = 128;
+    const uint32_t nt = gemm_tc_token_tile(m, (n + tile_rows - 1) / tile_rows, sm_count);
     alignas(64) CUtensorMap tw, tw2, tx;
     for (int which = 0; which < (dual ? 2 : 1); ++which) {
         // weights: [n rows][row_bytes] viewed as u16, box = boxw bytes x 128 (pair: 64) rows, no swizzle
@@ -516,8 +577,8 @@ cudaError_t gemm_tc_dense(uint32_t type, const void* w, const void* w_up, const 
 
 cudaError_t launch_gemm_tc(uint32_t type, const void* w, const void* x, uint32_t x_dtype, float* y, uint32_t m, uint32_t n,
                            uint32_t k, void* workspace, uint32_t* status, int sm_count, cudaStream_t st, int* launches,
-                           uint32_t ldy, bool x_ready, const float* residual) {
-    return gemm_tc_dense(type, w, nullptr, x, x_dtype, y, m, n, k, workspace, status, sm_count, st, launches, ldy, x_ready, residual);
+                           uint32_t ldy, bool x_ready, const float* residual, uint32_t perm_head_dim) {
+    return gemm_tc_dense(type, w, nullptr, x, x_dtype, y, m, n, k, workspace, status, sm_count, st, launches, ldy, x_ready, residual, perm_head_dim);
 }
 
 // the five formats hf2q's quantizer writes for FFN tensors; the 32-element fallback formats keep the unfused sequence
@@ -548,14 +609,13 @@ cudaError_t launch_grouped_nt(const CUtensorMap& tw, const CUtensorMap& tx, cons
 
 // One launch over (weight-row tile, token tile of one expert).  The grid is sized for the largest
 // possible number of token tiles; CTAs past the actual count (read from the scratch header) exit.
-// w_up != nullptr: the SwiGLU pair (w_stacked = gate, token tiles of at most 128); act16 != nullptr: its result
+// w_up != nullptr: the SwiGLU pair (w_stacked = gate); act16 != nullptr: its result
 // goes to act16[sorted row][n] as f16 instead of y.  x_panel overrides the gathered activation panel of the
 // scratch (the down product reads the act16 panel of the pair launch).
 cudaError_t launch_gemm_tc_grouped(uint32_t type, const void* w_stacked, uint64_t expert_stride, uint32_t n_experts, uint32_t rows,
                                    float* y, uint32_t n, uint32_t k, uint32_t nt, void* scratch, const MoeScratch& lay,
                                    uint32_t* status, cudaStream_t st, const void* w_up, const void* x_panel, void* act16) {
     const bool dual = w_up != nullptr;
-    if (dual && nt > 128) return cudaErrorInvalidValue;
     const uint32_t tile_rows = dual ? 64 : TILE_N;
     const BlockGeom g = block_geom(type);
     const uint64_t row_bytes = static_cast<uint64_t>(k) / g.elems * g.bytes;

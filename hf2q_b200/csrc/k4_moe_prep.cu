@@ -17,7 +17,21 @@ namespace {
 
 constexpr int SORT_THREADS = 1024;
 
-// Single CTA: histogram, exclusive scans, scatter.  Shared memory: 4 arrays of (E+1) u32.
+// Single CTA: histogram, exclusive scans, scatter.  Shared memory: 4 arrays of (E+1) u32 + 66 words of scan scratch.
+// The ids are read 16 per thread and step with all loads in flight (the kernel is one CTA deep in load latency
+// otherwise), the two scans over the experts are block-wide shuffle scans.
+__device__ __forceinline__ void load_ids16(const uint32_t* __restrict__ ids, uint32_t r0, uint32_t rows, bool vec, uint32_t (&e)[16]) {
+    if (vec && r0 + 16 <= rows) {
+        const uint4* p = reinterpret_cast<const uint4*>(ids + r0);
+        const uint4 a = __ldg(p), b = __ldg(p + 1), c = __ldg(p + 2), d = __ldg(p + 3);
+        e[0] = a.x; e[1] = a.y; e[2] = a.z; e[3] = a.w; e[4] = b.x; e[5] = b.y; e[6] = b.z; e[7] = b.w;
+        e[8] = c.x; e[9] = c.y; e[10] = c.z; e[11] = c.w; e[12] = d.x; e[13] = d.y; e[14] = d.z; e[15] = d.w;
+    } else {
+#pragma unroll
+        for (int j = 0; j < 16; ++j) e[j] = r0 + j < rows ? __ldg(ids + r0 + j) : 0xffffffffu;
+    }
+}
+
 __global__ void __launch_bounds__(SORT_THREADS) moe_sort_kernel(const uint32_t* __restrict__ ids, uint32_t rows, uint32_t n_experts,
                                                                 uint32_t nt, uint32_t* __restrict__ header, uint4* __restrict__ tiles,
                                                                 uint32_t* __restrict__ perm, float* __restrict__ y, float* __restrict__ y2,
@@ -27,29 +41,62 @@ __global__ void __launch_bounds__(SORT_THREADS) moe_sort_kernel(const uint32_t* 
     uint32_t* off = cnt + n_experts;          // [E+1] first sorted row of each expert
     uint32_t* toff = off + n_experts + 1;     // [E+1] first tile of each expert
     uint32_t* cur = toff + n_experts + 1;     // [E]
-    const uint32_t tid = threadIdx.x;
+    uint32_t* wsum = cur + n_experts;         // [32] + [32] warp totals of the two scans, [2] running totals
+    const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const bool vec = reinterpret_cast<uintptr_t>(ids) % 16 == 0;
     for (uint32_t e = tid; e < n_experts; e += SORT_THREADS) cnt[e] = 0;
+    if (tid < 2) wsum[64 + tid] = 0;
     __syncthreads();
     bool bad = false;
-    for (uint32_t r = tid; r < rows; r += SORT_THREADS) {
-        const uint32_t e = ids[r];
-        if (e < n_experts) atomicAdd(&cnt[e], 1u);
-        else bad = true;
+    for (uint32_t r0 = tid * 16; r0 < rows; r0 += SORT_THREADS * 16) {
+        uint32_t e[16];
+        load_ids16(ids, r0, rows, vec, e);
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+            if (e[j] < n_experts) atomicAdd(&cnt[e[j]], 1u);
+            else bad |= r0 + j < rows;
+        }
     }
     if (bad) atomicOr(status, STATUS_BAD_EXPERT_ID);
     __syncthreads();
-    if (tid == 0) {
-        uint32_t a = 0, t = 0;
-        for (uint32_t e = 0; e < n_experts; ++e) {
-            off[e] = a; toff[e] = t;
-            a += cnt[e];
-            t += (cnt[e] + nt - 1) / nt;
+    // exclusive scans of the row counts and of the tile counts over the experts
+    for (uint32_t base = 0; base < n_experts; base += SORT_THREADS) {
+        const uint32_t e = base + tid;
+        const uint32_t c = e < n_experts ? cnt[e] : 0u, t = (c + nt - 1) / nt;
+        uint32_t ic = c, it = t;
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+            const uint32_t uc = __shfl_up_sync(0xffffffffu, ic, d), ut = __shfl_up_sync(0xffffffffu, it, d);
+            if (lane >= static_cast<uint32_t>(d)) { ic += uc; it += ut; }
         }
-        off[n_experts] = a; toff[n_experts] = t;
-        header[0] = t;       // number of token tiles
-        header[1] = a;       // number of sorted (valid) rows
+        if (lane == 31) { wsum[warp] = ic; wsum[32 + warp] = it; }
+        __syncthreads();
+        if (warp == 0) {
+            uint32_t wc = wsum[lane], wt = wsum[32 + lane];
+            const uint32_t tc = wc, tt = wt;
+#pragma unroll
+            for (int d = 1; d < 32; d <<= 1) {
+                const uint32_t uc = __shfl_up_sync(0xffffffffu, wc, d), ut = __shfl_up_sync(0xffffffffu, wt, d);
+                if (lane >= static_cast<uint32_t>(d)) { wc += uc; wt += ut; }
+            }
+            wsum[lane] = wc - tc;             // exclusive prefix of the warp totals
+            wsum[32 + lane] = wt - tt;
+            if (lane == 31) { wsum[66] = wc; wsum[67] = wt; }          // totals of this pass
+        }
+        __syncthreads();
+        if (e < n_experts) {
+            off[e] = wsum[64] + wsum[warp] + ic - c;
+            toff[e] = wsum[65] + wsum[32 + warp] + it - t;
+        }
+        __syncthreads();
+        if (tid == 0) { wsum[64] += wsum[66]; wsum[65] += wsum[67]; }
+        __syncthreads();
     }
-    __syncthreads();
+    if (tid == 0) {
+        off[n_experts] = wsum[64]; toff[n_experts] = wsum[65];
+        header[0] = wsum[65];       // number of token tiles
+        header[1] = wsum[64];       // number of sorted (valid) rows
+    }
     for (uint32_t e = tid; e < n_experts; e += SORT_THREADS) {
         cur[e] = off[e];
         const uint32_t c = cnt[e];
@@ -57,14 +104,19 @@ __global__ void __launch_bounds__(SORT_THREADS) moe_sort_kernel(const uint32_t* 
             tiles[t] = make_uint4(e, off[e] + j * nt, min(nt, c - j * nt), 0u);
     }
     __syncthreads();
-    for (uint32_t r = tid; r < rows; r += SORT_THREADS) {
-        const uint32_t e = ids[r];
-        if (e < n_experts) {
-            perm[atomicAdd(&cur[e], 1u)] = r;
-        } else {
-            for (uint32_t c = 0; c < n; ++c) {                                           // rejected row: defined output
-                y[static_cast<size_t>(r) * n + c] = 0.f;
-                if (y2) y2[static_cast<size_t>(r) * n + c] = 0.f;
+    for (uint32_t r0 = tid * 16; r0 < rows; r0 += SORT_THREADS * 16) {
+        uint32_t e[16];
+        load_ids16(ids, r0, rows, vec, e);
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+            const uint32_t r = r0 + j;
+            if (e[j] < n_experts) {
+                perm[atomicAdd(&cur[e[j]], 1u)] = r;
+            } else if (r < rows) {
+                for (uint32_t c = 0; c < n; ++c) {                                       // rejected row: defined output
+                    y[static_cast<size_t>(r) * n + c] = 0.f;
+                    if (y2) y2[static_cast<size_t>(r) * n + c] = 0.f;
+                }
             }
         }
     }
@@ -117,7 +169,9 @@ uint32_t moe_token_tile(uint32_t rows, uint32_t n_experts) {
     static const int forced = [] { const char* v = getenv("HF2Q_CUDA_MOE_NT"); return v && *v ? atoi(v) : 0; }();   // tuning aid
     if (forced == 32 || forced == 64 || forced == 128 || forced == 256) return static_cast<uint32_t>(forced);
     const uint32_t avg = rows / (n_experts ? n_experts : 1);
-    return avg <= 40 ? 32 : avg <= 96 ? 64 : avg <= 192 ? 128 : 256;
+    // (128-token tiles run two CTAs per SM like the smaller ones, and a tile that holds all rows of its expert
+    // dequantises that expert's weights once)
+    return avg <= 20 ? 32 : avg <= 40 ? 64 : avg <= 192 ? 128 : 256;
 }
 
 MoeScratch moe_scratch_layout(uint32_t n_experts, uint32_t rows, uint32_t k) {
@@ -139,7 +193,7 @@ cudaError_t launch_moe_prep(const uint32_t* ids, uint32_t rows, uint32_t n_exper
     uint4* tiles = reinterpret_cast<uint4*>(base + lay.tiles_off);
     uint32_t* perm = reinterpret_cast<uint32_t*>(base + lay.perm_off);
     __half* xg = reinterpret_cast<__half*>(base + lay.xg_off);
-    const size_t smem = (4 * static_cast<size_t>(n_experts) + 2) * 4;
+    const size_t smem = (4 * static_cast<size_t>(n_experts) + 2 + 68) * 4;
     moe_sort_kernel<<<1, SORT_THREADS, smem, st>>>(ids, rows, n_experts, nt, header, tiles, perm, y, y2, n, status);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return e;

@@ -106,10 +106,11 @@ cudaError_t launch_gather_wait(const uint32_t* flag, uint32_t n_ranks, uint32_t 
 // rows and a workspace of gemm_tc_workspace_bytes(m, k) for the f16 copy of the activations.
 bool gemm_tc_supported(uint32_t type, const void* w, uint32_t n, uint32_t k);
 uint64_t gemm_tc_workspace_bytes(uint32_t m, uint32_t k);
-// ldy: floats between activation rows of y (0 = n); x_ready: the workspace already holds the f16 copy of x
+// ldy: floats between activation rows of y (0 = n); x_ready: the workspace already holds the f16 copy of x;
+// perm_head_dim != 0: x is stored [k / head_dim][m][head_dim] (attention output, heads outermost)
 cudaError_t launch_gemm_tc(uint32_t type, const void* w, const void* x, uint32_t x_dtype, float* y, uint32_t m, uint32_t n,
                            uint32_t k, void* workspace, uint32_t* status, int sm_count, cudaStream_t st, int* launches,
-                           uint32_t ldy = 0, bool x_ready = false, const float* residual = nullptr);
+                           uint32_t ldy = 0, bool x_ready = false, const float* residual = nullptr, uint32_t perm_head_dim = 0);
 // y[m][n] = silu(x . gate^T) * (x . up^T) in one launch (the five main formats)
 bool gemm_tc_swiglu_supported(uint32_t type);
 cudaError_t launch_gemm_tc_swiglu(uint32_t type, const void* w_gate, const void* w_up, const void* x, uint32_t x_dtype, float* y,

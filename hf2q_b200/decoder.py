@@ -119,6 +119,8 @@ class LlamaDecoder:
         self.act = torch.zeros((1, c.ffn), **f32)
         self.tmp = torch.zeros((1, c.hidden), **f32)
         self.fused_attention = True
+        self.fused_prefill = True          # prompt chunks: SwiGLU pair and residual adds inside the tensor-core products
+        self._pf_delta = None
         # RMSNorm inside the product that consumes it, where every tensor of the model allows it
         self.fused_norm = all(ops.norm_supported(ctx, 1, w) for lw in weights.layers for w in (lw.wqk, lw.wv, lw.gate) if w is not None) and \
             ops.norm_supported(ctx, 1, weights.output)
@@ -254,22 +256,36 @@ class LlamaDecoder:
             self._get_rows(ids[p0:p0 + m], m, x)
             delta = None
             for i, lw in enumerate(self.w.layers):
-                self._rms(x, delta, lw.attn_norm, xn, m)                                   # x += previous layer's FFN output
+                self._rms(x, delta, lw.attn_norm, xn, m)                                   # x += previous layer's FFN output (unfused form)
                 ops.quantized_matmul_segments(ctx, xn, self._qkv_segments(lw), qkv, m)
                 self._rope_append(qkv, m, i)
                 ctx._check(lib.hf2q_cuda_attn_prefill(ctx._h, self._s(), qkv.data_ptr(), m, c.n_heads, C.byref(self.kv[i]), p0,
                                                       att.data_ptr(), ops.DT_F32))
-                ops.quantized_matmul_ggml(ctx, att, lw.wo, o, lw.wo.matmul_params(m))
-                self._rms(x, o, lw.ffn_norm, xn, m)                                        # x += O(att)
-                ops.quantized_matmul_ggml(ctx, xn, lw.gate, g, lw.gate.matmul_params(m))
-                ops.quantized_matmul_ggml(ctx, xn, lw.up, u, lw.up.matmul_params(m))
-                ctx._check(lib.hf2q_cuda_silu_mul(ctx._h, self._s(), g.data_ptr(), u.data_ptr(), g.data_ptr(), g.numel()))
-                ops.quantized_matmul_ggml(ctx, g, lw.down, o, lw.down.matmul_params(m))
-                delta = o
+                # the residual stream is updated in the epilogue of the O and down products where the shape allows
+                if self.fused_prefill and ops.quantized_matmul_add_supported(ctx, lw.wo, att.dtype, m):
+                    ops.quantized_matmul_add(ctx, att, lw.wo, x, x, m)
+                    self._rms(x, None, lw.ffn_norm, xn, m)
+                else:
+                    ops.quantized_matmul_ggml(ctx, att, lw.wo, o, lw.wo.matmul_params(m))
+                    self._rms(x, o, lw.ffn_norm, xn, m)                                    # x += O(att)
+                if (self.fused_prefill and lw.gate.ggml_type == lw.up.ggml_type and
+                        ops.quantized_matmul_swiglu_supported(ctx, m, lw.gate, xn.dtype)):
+                    ops.quantized_matmul_swiglu(ctx, xn, lw.gate, lw.up, g, m)             # gate, up and the SwiGLU in one product
+                else:
+                    ops.quantized_matmul_ggml(ctx, xn, lw.gate, g, lw.gate.matmul_params(m))
+                    ops.quantized_matmul_ggml(ctx, xn, lw.up, u, lw.up.matmul_params(m))
+                    ctx._check(lib.hf2q_cuda_silu_mul(ctx._h, self._s(), g.data_ptr(), u.data_ptr(), g.data_ptr(), g.numel()))
+                if self.fused_prefill and ops.quantized_matmul_add_supported(ctx, lw.down, g.dtype, m):
+                    ops.quantized_matmul_add(ctx, g, lw.down, x, x, m)
+                    delta = None
+                else:
+                    ops.quantized_matmul_ggml(ctx, g, lw.down, o, lw.down.matmul_params(m))
+                    delta = o
+            self._pf_delta = delta
             if p0 + m == T:
                 # only the last token's logits are needed: x_last += delta_last, final norm, output head
                 self.x.copy_(x[m - 1:m])
-                self._rms(self.x, delta[m - 1:m], self.w.out_norm, self.xn, 1)
+                self._rms(self.x, None if delta is None else delta[m - 1:m], self.w.out_norm, self.xn, 1)
                 ops.quantized_matmul_ggml(ctx, self.xn, self.w.output, self.logits, self.w.output.matmul_params(1))
                 self.pos.fill_(T - 1)
                 ctx._check(lib.hf2q_cuda_argmax(ctx._h, self._s(), self.logits.data_ptr(), c.vocab, self.tok.data_ptr(), self.pos.data_ptr()))
@@ -286,10 +302,10 @@ class LlamaDecoder:
         finally:
             self.prefill_chunk = saved
         b = self._pf
-        x, o = b["x"][:T], b["o"][:T]
+        x = b["x"][:T]
         xn = torch.empty((T, c.hidden), dtype=torch.float32, device=self.dev)
         xs = x.clone()
-        self._rms(xs, o, self.w.out_norm, xn, T)
+        self._rms(xs, None if self._pf_delta is None else self._pf_delta[:T], self.w.out_norm, xn, T)
         logits = torch.empty((T, c.vocab), dtype=torch.float32, device=self.dev)
         ops.quantized_matmul_ggml(ctx, xn, self.w.output, logits, self.w.output.matmul_params(T))
         return logits

@@ -232,6 +232,25 @@ def quantized_matmul_ggml(ctx: GpuContext, input: torch.Tensor, weight: QuantWei
                                           int(params.ggml_type), ws_ptr, ws_bytes))
 
 
+def quantized_matmul_mm_tensor_perm021(ctx: GpuContext, input: torch.Tensor, weight: QuantWeight, out: torch.Tensor,
+                                       m: int, head_dim: int) -> None:
+    """out[m,n] = X . dequant(weight)^T where X[t, h*head_dim + f] = input[h, t, f]: the O projection reading the
+    attention output heads-outermost (GgmlQuantizedMatmulPerm021Params {m,n,k,head_dim,ggml_type},
+    forward_prefill_batched.rs:2218-2258)."""
+    xdt = _act(input, "input")
+    if out.dtype != torch.float32 or not out.is_cuda or not out.is_contiguous() or out.numel() < m * weight.rows:
+        raise Hf2qError(_lib.ERR_INVALID_ARGUMENT, "out must be a contiguous float32 CUDA tensor of [m, n]")
+    if input.numel() < m * weight.cols:
+        raise Hf2qError(_lib.ERR_INVALID_ARGUMENT, "input smaller than [k / head_dim, m, head_dim]")
+    need = (m * weight.cols * 2 + 255) // 256 * 256
+    ws = getattr(ctx, "_ws", None)
+    if ws is None or ws.numel() < need:
+        ws = torch.empty(need, dtype=torch.uint8, device=input.device)
+        ctx._ws = ws
+    ctx._check(ctx._lib.hf2q_cuda_qmatmul_perm021(ctx._h, ctx._stream(), input.data_ptr(), xdt, weight.ptr, out.data_ptr(), m,
+                                                  weight.rows, weight.cols, head_dim, weight.ggml_type, ws.data_ptr(), ws.numel()))
+
+
 class _RowSegment(C.Structure):                  # hf2q_row_segment in include/hf2q_cuda.h
     _fields_ = [("w", C.c_void_p), ("rows", C.c_uint32), ("ggml_type", C.c_uint32)]
 

@@ -180,6 +180,18 @@ HF2Q_API int32_t hf2q_cuda_qmatmul_add(hf2q_ctx* ctx, void* stream, const void* 
                                        const void* w, const float* residual, float* y, uint32_t m,
                                        uint32_t n, uint32_t k, uint32_t ggml_type);
 
+/* hf2q_cuda_qmatmul for activations stored heads-outermost: x is [k / head_dim][m][head_dim] (what flash
+ * attention writes), logical element (t, c) at ((c / head_dim) * m + t) * head_dim + c % head_dim.  Replaces
+ * mlx_native::quantized_matmul_mm_tensor_perm021 (params {m, n, k, head_dim, ggml_type}; call site
+ * src/serve/forward_prefill_batched.rs:2218-2258, the O projection of the batched prefill).  The permute is
+ * folded into the f16 staging of the activations, as the reference folds it into its B-stage; any m runs on
+ * the tensor-core GEMM.  head_dim % 8 == 0, x 16-byte aligned, workspace as for hf2q_cuda_qmatmul with m > 8
+ * (gemm: m * k * 2 bytes, rounded up to 256). */
+HF2Q_API int32_t hf2q_cuda_qmatmul_perm021(hf2q_ctx* ctx, void* stream, const void* x, uint32_t x_dtype,
+                                           const void* w, float* y, uint32_t m, uint32_t n, uint32_t k,
+                                           uint32_t head_dim, uint32_t ggml_type, void* workspace,
+                                           uint64_t workspace_bytes);
+
 /* The two fusions above for ANY number of activation rows (prefill): up to 8 rows they are the calls above;
  * beyond that the tensor-core GEMM computes the gate and the up tile side by side in tensor memory and
  * stores silu(gate) * up (five main formats), or adds the residual in its epilogue (any format; residual

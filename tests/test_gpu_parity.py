@@ -159,6 +159,31 @@ def test_gemm_matches_f64_reference(gpu_ctx, t):
         assert err < GATE, (t, n, k, m, err)
 
 
+@pytest.mark.parametrize("t", [oracle.Q4_0, oracle.Q6_K, oracle.Q8_0])
+def test_gemm_perm021_reads_heads_outermost_activations(gpu_ctx, t):
+    """The O projection reading attention output stored [n_heads, seq, head_dim]: bit-identical to the plain
+    product on the token-major copy (the permute only changes where the f16 staging reads), any m."""
+    from hf2q_b200 import ops
+    n, k, hd = 192, 2048, 128
+    raw = make_quant_weight(t, n, k, seed=77)
+    w = hq.load_quant_weight(gpu_ctx, raw, t, n, k)
+    for m, bf16 in ((1, True), (7, False), (40, True), (300, True)):
+        xd, xs = _dev_x(make_x(m, k, seed=100 + m), bf16)
+        perm = xd.view(m, k // hd, hd).permute(1, 0, 2).contiguous()           # [heads, m, head_dim]
+        got = torch.full((m, n), float("nan"), device="cuda")
+        ops.quantized_matmul_mm_tensor_perm021(gpu_ctx, perm, w, got, m, hd)
+        gpu_ctx.check_status()
+        assert rel_l2(got.cpu().numpy(), _ref(t, raw, xs, n, k)) < GATE
+        if m > 8:
+            want = torch.empty((m, n), device="cuda")
+            hq.quantized_matmul_ggml(gpu_ctx, xd, w, want, w.matmul_params(m))
+            assert torch.equal(got, want)
+    lib = _lib.load()
+    ws = torch.empty(1 << 20, dtype=torch.uint8, device="cuda")
+    rc = lib.hf2q_cuda_qmatmul_perm021(gpu_ctx._h, None, perm.data_ptr(), 1, w.ptr, got.data_ptr(), 4, n, k, 100, t, ws.data_ptr(), ws.numel())
+    assert rc == _lib.ERR_INVALID_ARGUMENT                                     # head_dim must divide k
+
+
 def test_gemm_needs_its_workspace(gpu_ctx):
     t, n, k, m = oracle.Q4_K, 128, 512, 64
     w = hq.load_quant_weight(gpu_ctx, make_quant_weight(t, n, k, seed=1), t, n, k)
