@@ -11,9 +11,10 @@ default 20..200 steps time a region of 0.5 s and more).
 
   metric  = dequant-GEMV HBM GB/s = algorithmic bytes (W + 2*m*K + 4*m*N per launch) / device time
   value   = inputs resident in HBM, launches back to back on one stream, CUDA-event timed
-  e2e     = the same sweep through the host-buffer C-ABI call (hf2q_cuda_qmatmul_host_async): every
-            call queues the copy of its activations from pinned host memory, the kernel and the copy
-            of y back to pinned host memory; one hf2q_cuda_host_sync per pass waits for all of them
+  e2e     = the same sweep through the host-buffer C-ABI call (hf2q_cuda_qmatmul_host_batch): one call
+            per pass queues, for every product, the copy of its activations from pinned host memory,
+            the kernel and the copy of y back to pinned host memory; one hf2q_cuda_host_sync per pass
+            waits for all of them
   secondary (one GPU) = the other kernels of the path, measured in the same run with the same
             timing rules: Q4_K 4096x4096 f32 mat-vec, the Q4_K_M prefill GEMM sweep (TFLOP/s against
             the measured bf16 peaks), and the Q5_K expert layer at 1 and 2048 tokens.
@@ -915,13 +916,14 @@ def main() -> None:
         pin_y = {(n, m): torch.empty((m, n), dtype=torch.float32).pin_memory() for n, _ in SHAPES for m in TOKENS}
         np_y = {key: t.numpy() for key, t in pin_y.items()}
 
+        batch = hq.ops.HostBatch([(np_x[(k, m)], w, np_y[(n, m)], m, hq.ops.DT_BF16)
+                                  for m in TOKENS for c in range(args.copies) for (n, k), w in zip(SHAPES, weights[c])])
+
         def e2e_pass():
-            for m in TOKENS:
-                for c in range(args.copies):
-                    for (n, k), w in zip(SHAPES, weights[c]):
-                        hq.ops.quantized_matmul_host(ctx, np_x[(k, m)], w, np_y[(n, m)], m, hq.ops.DT_BF16, wait=False)
+            hq.ops.quantized_matmul_host_batch(ctx, batch)
             hq.ops.host_sync(ctx)                    # the pass's results are in pinned host memory from here on
-        e2e_api = "hf2q_cuda_qmatmul_host_async per product (pinned host x -> device, kernel, y -> pinned host), hf2q_cuda_host_sync once per pass"
+        e2e_api = ("hf2q_cuda_qmatmul_host_batch: one call queues the pass's products (each: pinned host x -> device, kernel, y -> pinned host), "
+                   "hf2q_cuda_host_sync once per pass")
         d2h = args.copies * sum(4 * m * n for n, _ in SHAPES for m in TOKENS)
     else:
         # the sharded call: every rank copies its activations in, the product gathers, rank 0 (the

@@ -51,6 +51,7 @@ SIGNATURES = {
     "hf2q_cuda_qmatmul_host": (i32, [vp, vp, u32, vp, vp, u32, u32, u32, u32]),
     "hf2q_cuda_qmatmul_host_async": (i32, [vp, vp, u32, vp, vp, u32, u32, u32, u32]),
     "hf2q_cuda_host_sync": (i32, [vp]),
+    "hf2q_cuda_qmatmul_host_batch": (i32, [vp, vp, u32]),
     "hf2q_cuda_ipc_alloc": (i32, [vp, u64, pp, vp]),
     "hf2q_cuda_ipc_open": (i32, [vp, vp, pp]),
     "hf2q_cuda_ipc_close": (i32, [vp, vp]),

@@ -6,6 +6,7 @@
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
+#include <vector>
 #include <new>
 
 #include "common.cuh"
@@ -45,6 +46,12 @@ struct hf2q_ctx {
     float* pin_y = nullptr;   size_t pin_y_bytes = 0;
     void* ws = nullptr;       size_t ws_bytes = 0;
     cudaStream_t host_stream = nullptr;
+    // staging of hf2q_cuda_qmatmul_host_batch: one x and one y buffer for the whole batch, one event pair per group
+    void* bx = nullptr;       size_t bx_bytes = 0;
+    void* by = nullptr;       size_t by_bytes = 0;
+    std::vector<cudaEvent_t> b_loaded, b_computed;
+    cudaEvent_t b_all_computed = nullptr, b_all_drained = nullptr;
+    bool b_used = false;
     char err[512] = {0};
 };
 
@@ -205,6 +212,12 @@ HF2Q_API int32_t hf2q_cuda_ctx_destroy(hf2q_ctx* ctx) {
     if (ctx->out_stream) cudaStreamDestroy(ctx->out_stream);
     if (ctx->in_stream) cudaStreamDestroy(ctx->in_stream);
     if (ctx->ws) cudaFree(ctx->ws);
+    if (ctx->bx) cudaFree(ctx->bx);
+    if (ctx->by) cudaFree(ctx->by);
+    for (cudaEvent_t ev : ctx->b_loaded) cudaEventDestroy(ev);
+    for (cudaEvent_t ev : ctx->b_computed) cudaEventDestroy(ev);
+    if (ctx->b_all_computed) cudaEventDestroy(ctx->b_all_computed);
+    if (ctx->b_all_drained) cudaEventDestroy(ctx->b_all_drained);
     if (ctx->pin_x) cudaFreeHost(ctx->pin_x);
     if (ctx->pin_y) cudaFreeHost(ctx->pin_y);
     if (ctx->host_stream) cudaStreamDestroy(ctx->host_stream);
@@ -813,6 +826,93 @@ HF2Q_API int32_t hf2q_cuda_qmatmul_host_async(hf2q_ctx* ctx, const void* x_host,
     if (e == cudaSuccess) e = cudaEventRecord(hs.drained, ctx->out_stream);
     if (e != cudaSuccess) return cuda_fail(ctx, e, "qmatmul_host: copy-out");
     hs.used = true;
+    return HF2Q_OK;
+}
+
+// Many host-buffer products in one call: the copies-in run ahead on their own stream, the kernels run back to back
+// on one stream (so consecutive mat-vecs keep their programmatic-dependent-launch overlap), the copies-out follow
+// group by group on a third stream.  One event pair per group of 8 products instead of three event edges per product.
+HF2Q_API int32_t hf2q_cuda_qmatmul_host_batch(hf2q_ctx* ctx, const hf2q_host_product* items, uint32_t n_items) {
+    if (!ctx) return HF2Q_ERR_INVALID_ARGUMENT;
+    const char* who = "qmatmul_host_batch";
+    if (!items && n_items) return fail(ctx, HF2Q_ERR_INVALID_ARGUMENT, "%s: null item array", who);
+    if (n_items == 0) return HF2Q_OK;
+    constexpr uint32_t GROUP = 8;
+    std::vector<size_t> xo(n_items), yo(n_items);
+    size_t xt = 0, yt = 0;
+    uint64_t wsb = 0;
+    for (uint32_t i = 0; i < n_items; ++i) {
+        const hf2q_host_product& it = items[i];
+        if (!it.x_host || !it.w_dev || !it.y_host) return fail(ctx, HF2Q_ERR_INVALID_ARGUMENT, "%s: item %u has a null pointer", who, i);
+        if (it.x_dtype != HF2Q_DT_F32 && it.x_dtype != HF2Q_DT_BF16) return fail(ctx, HF2Q_ERR_INVALID_ARGUMENT, "%s: item %u x_dtype %u", who, i, it.x_dtype);
+        const int32_t rc = check_matmul_shape(ctx, it.ggml_type, it.n, it.k, who);
+        if (rc) return rc;
+        xo[i] = xt; yo[i] = yt;
+        xt += (static_cast<size_t>(it.m) * it.k * dtype_size(it.x_dtype) + 255) & ~static_cast<size_t>(255);
+        yt += (static_cast<size_t>(it.m) * it.n * 4 + 255) & ~static_cast<size_t>(255);
+        uint64_t w1 = 0;
+        hf2q_cuda_qmatmul_workspace_bytes(it.m, it.n, it.k, it.ggml_type, it.x_dtype, &w1);
+        if (w1 > wsb) wsb = w1;
+    }
+    DeviceGuard dg(ctx->device);
+    cudaError_t e = cudaSuccess;
+    const uint32_t n_groups = (n_items + GROUP - 1) / GROUP;
+    if (ctx->bx_bytes < xt || ctx->by_bytes < yt || ctx->ws_bytes < wsb) {
+        e = cudaStreamSynchronize(ctx->in_stream);            // growing frees the old buffers: nothing may still use them
+        if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->host_stream);
+        if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->out_stream);
+        if (e != cudaSuccess) return cuda_fail(ctx, e, "qmatmul_host_batch: sync before growing staging buffers");
+        int32_t rc;
+        if ((rc = grow(ctx, &ctx->bx, &ctx->bx_bytes, xt, false))) return rc;
+        if ((rc = grow(ctx, &ctx->by, &ctx->by_bytes, yt, false))) return rc;
+        if (wsb && (rc = grow(ctx, &ctx->ws, &ctx->ws_bytes, wsb, false))) return rc;
+    }
+    while (ctx->b_loaded.size() < n_groups) {
+        cudaEvent_t a = nullptr, b = nullptr;
+        if (cudaEventCreateWithFlags(&a, cudaEventDisableTiming) != cudaSuccess || cudaEventCreateWithFlags(&b, cudaEventDisableTiming) != cudaSuccess)
+            return cuda_fail(ctx, cudaGetLastError(), "qmatmul_host_batch: event");
+        ctx->b_loaded.push_back(a);
+        ctx->b_computed.push_back(b);
+    }
+    if (!ctx->b_all_computed) {
+        e = cudaEventCreateWithFlags(&ctx->b_all_computed, cudaEventDisableTiming);
+        if (e == cudaSuccess) e = cudaEventCreateWithFlags(&ctx->b_all_drained, cudaEventDisableTiming);
+        if (e != cudaSuccess) return cuda_fail(ctx, e, "qmatmul_host_batch: event");
+    }
+    if (ctx->b_used) {
+        // the previous batch: its kernels have read the x staging, its copies-out the y staging
+        e = cudaStreamWaitEvent(ctx->in_stream, ctx->b_all_computed, 0);
+        if (e == cudaSuccess) e = cudaStreamWaitEvent(ctx->host_stream, ctx->b_all_drained, 0);
+        if (e != cudaSuccess) return cuda_fail(ctx, e, "qmatmul_host_batch: ordering after the previous batch");
+    }
+    uint8_t* bx = static_cast<uint8_t*>(ctx->bx);
+    uint8_t* by = static_cast<uint8_t*>(ctx->by);
+    for (uint32_t g = 0; g < n_groups; ++g) {
+        const uint32_t i0 = g * GROUP, i1 = i0 + GROUP < n_items ? i0 + GROUP : n_items;
+        for (uint32_t i = i0; i < i1 && e == cudaSuccess; ++i)
+            e = cudaMemcpyAsync(bx + xo[i], items[i].x_host, static_cast<size_t>(items[i].m) * items[i].k * dtype_size(items[i].x_dtype),
+                                cudaMemcpyHostToDevice, ctx->in_stream);
+        if (e == cudaSuccess) e = cudaEventRecord(ctx->b_loaded[g], ctx->in_stream);
+        if (e == cudaSuccess) e = cudaStreamWaitEvent(ctx->host_stream, ctx->b_loaded[g], 0);
+        if (e != cudaSuccess) return cuda_fail(ctx, e, "qmatmul_host_batch: copy-in");
+        for (uint32_t i = i0; i < i1; ++i) {
+            const hf2q_host_product& it = items[i];
+            if (it.m == 0) continue;
+            const int32_t rc = hf2q_cuda_qmatmul(ctx, ctx->host_stream, bx + xo[i], it.x_dtype, it.w_dev, reinterpret_cast<float*>(by + yo[i]), it.m,
+                                                 it.n, it.k, it.ggml_type, ctx->ws, ctx->ws_bytes);
+            if (rc) return rc;
+        }
+        e = cudaEventRecord(ctx->b_computed[g], ctx->host_stream);
+        if (e == cudaSuccess) e = cudaStreamWaitEvent(ctx->out_stream, ctx->b_computed[g], 0);
+        for (uint32_t i = i0; i < i1 && e == cudaSuccess; ++i)
+            if (items[i].m)
+                e = cudaMemcpyAsync(items[i].y_host, by + yo[i], static_cast<size_t>(items[i].m) * items[i].n * 4, cudaMemcpyDeviceToHost, ctx->out_stream);
+        if (e != cudaSuccess) return cuda_fail(ctx, e, "qmatmul_host_batch: copy-out");
+    }
+    e = cudaEventRecord(ctx->b_all_computed, ctx->host_stream);
+    if (e == cudaSuccess) e = cudaEventRecord(ctx->b_all_drained, ctx->out_stream);
+    if (e != cudaSuccess) return cuda_fail(ctx, e, "qmatmul_host_batch: events");
+    ctx->b_used = true;
     return HF2Q_OK;
 }
 

@@ -357,6 +357,31 @@ def quantized_matmul_host(ctx: GpuContext, x_host: np.ndarray, weight: QuantWeig
                   weight.ggml_type))
 
 
+class _HostProduct(C.Structure):                 # hf2q_host_product in include/hf2q_cuda.h
+    _fields_ = [("x_host", C.c_void_p), ("w_dev", C.c_void_p), ("y_host", C.c_void_p), ("m", C.c_uint32), ("n", C.c_uint32),
+                ("k", C.c_uint32), ("ggml_type", C.c_uint32), ("x_dtype", C.c_uint32), ("reserved", C.c_uint32)]
+
+
+class HostBatch:
+    """A list of independent host-buffer products (x_host, weight, y_host, m, x_dtype) for ``quantized_matmul_host_batch``;
+    the arrays are kept alive by the object."""
+
+    def __init__(self, items):
+        self._keep = list(items)
+        self.array = (_HostProduct * len(self._keep))()
+        for slot, (x, w, y, m, xdt) in zip(self.array, self._keep):
+            slot.x_host, slot.w_dev, slot.y_host = x.ctypes.data, w.ptr, y.ctypes.data
+            slot.m, slot.n, slot.k, slot.ggml_type, slot.x_dtype = m, w.rows, w.cols, w.ggml_type, xdt
+
+    def __len__(self):
+        return len(self._keep)
+
+
+def quantized_matmul_host_batch(ctx: GpuContext, batch: HostBatch) -> None:
+    """Queues every product of the batch with one call (hf2q_cuda_qmatmul_host_batch); results are valid after ``host_sync``."""
+    ctx._check(ctx._lib.hf2q_cuda_qmatmul_host_batch(ctx._h, C.cast(batch.array, C.c_void_p), len(batch)))
+
+
 def host_sync(ctx: GpuContext) -> None:
     """Waits for everything queued by ``quantized_matmul_host(..., wait=False)``."""
     ctx._check(ctx._lib.hf2q_cuda_host_sync(ctx._h))

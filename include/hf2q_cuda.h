@@ -226,6 +226,19 @@ HF2Q_API int32_t hf2q_cuda_qmatmul_host(hf2q_ctx* ctx, const void* x_host, uint3
 HF2Q_API int32_t hf2q_cuda_qmatmul_host_async(hf2q_ctx* ctx, const void* x_host, uint32_t x_dtype,
                                         const void* w_dev, float* y_host, uint32_t m, uint32_t n,
                                         uint32_t k, uint32_t ggml_type);
+/* Many host-buffer products queued by ONE call (a decode step's products, a benchmark pass): copies-in on one
+ * stream, the kernels back to back on a second (consecutive mat-vecs overlap as they do for device callers),
+ * copies-out on a third; results are valid after hf2q_cuda_host_sync.  Buffers as for
+ * hf2q_cuda_qmatmul_host_async (pinned memory for real overlap; alive until the sync).  The products are
+ * independent: no item may read another item's output. */
+typedef struct hf2q_host_product {
+    const void* x_host;   /* [m][k], x_dtype */
+    const void* w_dev;    /* device blocks, as for hf2q_cuda_qmatmul */
+    float* y_host;        /* [m][n] */
+    uint32_t m, n, k, ggml_type, x_dtype, reserved;
+} hf2q_host_product;
+HF2Q_API int32_t hf2q_cuda_qmatmul_host_batch(hf2q_ctx* ctx, const hf2q_host_product* items, uint32_t n_items);
+
 HF2Q_API int32_t hf2q_cuda_host_sync(hf2q_ctx* ctx);
 
 /* ---- a6: expert-routed quantized matmul --------------------------------------------------- */

@@ -228,6 +228,36 @@ def test_host_buffer_call(gpu_ctx):
         assert rel_l2(yi, _ref(t, raw, xi, n, k)) < GATE
 
 
+def test_host_buffer_batch_call(gpu_ctx):
+    """One call queues many independent host-buffer products (mat-vec and GEMM sized, several formats); a second
+    batch issued before the first one was waited for reuses the staging buffers in order."""
+    specs = [(oracle.Q4_K, 256, 2048, 4), (oracle.Q6_K, 96, 2048, 1), (oracle.Q8_0, 64, 512, 8), (oracle.Q5_K, 128, 1024, 40),
+             (oracle.Q4_0, 80, 256, 3)] * 4                                   # 20 products: three groups of 8
+    ws, raws = [], []
+    for i, (t, n, k, m) in enumerate(specs):
+        raw = make_quant_weight(t, n, k, seed=300 + i)
+        raws.append(raw)
+        ws.append(hq.load_quant_weight(gpu_ctx, raw, t, n, k))
+
+    def make(seed):
+        xs = [make_x(m, k, seed=seed + i) for i, (t, n, k, m) in enumerate(specs)]
+        ys = [np.full((m, n), np.nan, np.float32) for (t, n, k, m) in specs]
+        return xs, ys, hq.ops.HostBatch([(x, w, y, m, hq.ops.DT_F32) for x, w, y, (t, n, k, m) in zip(xs, ws, ys, specs)])
+
+    xa, ya, ba = make(1000)
+    xb, yb, bb = make(2000)
+    hq.ops.quantized_matmul_host_batch(gpu_ctx, ba)
+    hq.ops.quantized_matmul_host_batch(gpu_ctx, bb)
+    hq.ops.host_sync(gpu_ctx)
+    gpu_ctx.check_status()
+    for xs, ys in ((xa, ya), (xb, yb)):
+        for x, y, raw, (t, n, k, m) in zip(xs, ys, raws, specs):
+            assert rel_l2(y, _ref(t, raw, x, n, k)) < GATE, (t, n, k, m)
+    lib = _lib.load()
+    assert lib.hf2q_cuda_qmatmul_host_batch(gpu_ctx._h, None, 3) == _lib.ERR_INVALID_ARGUMENT
+    assert lib.hf2q_cuda_qmatmul_host_batch(gpu_ctx._h, None, 0) == 0
+
+
 # ---------------------------------------------------------------- K3 routed mat-vec
 @pytest.mark.parametrize("t", TYPES)
 def test_mul_mat_id_small(gpu_ctx, t):
