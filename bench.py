@@ -465,6 +465,54 @@ def bench_moe(hq, oracle, torch, ctx, dev, args, toks=None) -> dict:
             "per_case": res, "gpu_launches": int(ctx.launch_count - l0), "clocks": sampler.stop()}
 
 
+def bench_attention(hq, oracle, torch, ctx, dev, args) -> dict:
+    """The decode step's attention launch alone (config 5 shapes: 32 query / 8 KV heads of 128, 8-bit KV): rotary
+    embedding of the query, append of the new position, split attention over `--tokens` cached positions and the
+    merge, one launch per layer; 8 layers with their own caches rotate so that the cache comes from HBM."""
+    import ctypes as C
+    from hf2q_b200 import decoder as D
+    n_ctx, layers, n_q, n_kv, hd = (args.tokens or 8192), 8, 32, 8, 128
+    max_seq = n_ctx + 64
+    bufs, kvs = [], []
+    g = torch.Generator(device=dev).manual_seed(0)
+    for _ in range(layers):
+        kc = torch.randint(-127, 128, (n_kv, max_seq, hd), dtype=torch.int8, device=dev, generator=g)
+        vc = torch.randint(-127, 128, (n_kv, max_seq, hd), dtype=torch.int8, device=dev, generator=g)
+        ks = torch.rand((n_kv, max_seq), device=dev, generator=g) * 0.02
+        vs = torch.rand((n_kv, max_seq), device=dev, generator=g) * 0.02
+        bufs.append((kc, ks, vc, vs))
+        kvs.append(D._KvCache(kc.data_ptr(), ks.data_ptr(), vc.data_ptr(), vs.data_ptr(), n_kv, hd, max_seq))
+    qkv = torch.randn((1, (n_q + 2 * n_kv) * hd), device=dev, generator=g)
+    out = torch.empty((1, n_q * hd), device=dev)
+    pos = torch.full((1,), n_ctx, dtype=torch.int32, device=dev)
+    need = C.c_uint64()
+    ctx._check(ctx._lib.hf2q_cuda_attn_decode_scratch_bytes(ctx._h, n_q, n_kv, C.byref(need)))
+    scratch = torch.zeros(max(need.value, 16), dtype=torch.uint8, device=dev)
+
+    def all_layers():
+        for kv in kvs:
+            ctx._check(ctx._lib.hf2q_cuda_attn_decode_fused(ctx._h, ctx._stream(), qkv.data_ptr(), n_q, 500000.0, C.byref(kv), pos.data_ptr(),
+                                                            out.data_ptr(), hq.ops.DT_F32, scratch.data_ptr(), scratch.numel()))
+
+    sampler = ClockSampler(ctx.device)
+    sampler.start()
+    l0 = ctx.launch_count
+    graph = _graph_of(torch, all_layers)
+    dt = _timed(torch, graph.replay, max(3, min(args.steps, 20))) / layers
+    ctx.check_status()
+    kv_bytes = 2 * n_kv * (n_ctx + 1) * (hd + 4)
+    peak, kind = measured_hbm_peak()
+    return {"metric": "decode attention time per layer", "value": round(dt * 1e6, 2), "unit": "us", "higher_is_better": False,
+            "dtype": "int8 KV codes, f32 scores and accumulation",
+            "config": {"workload": f"decode attention, 32 query / 8 KV heads of 128, 8-bit KV cache, {n_ctx} cached positions; "
+                                   f"one launch per layer (rotary, append, split attention, merge), {layers} layers rotating",
+                       "timing": "CUDA events around replays of one CUDA graph of the layers"},
+            "roofline": {"bound": "hbm", "achieved": round(kv_bytes / dt / 1e9, 1), "peak": peak, "unit": "GB/s",
+                         "frac": round(kv_bytes / dt / 1e9 / peak, 4), "peak_source": f"of {kind}", "kernel": "attn_decode_fused_kernel",
+                         "traffic": None},
+            "gpu_launches": int(ctx.launch_count - l0), "clocks": sampler.stop()}
+
+
 def build_llama_weights(hq, oracle, torch, ctx, dev, cfg, distinct_rows: int = 16384):
     """Random-init Llama-shaped weights under the Q4_K_M type map, quantized by the oracle's port of
     hf2q's quantizers.  To keep the host work to seconds, ONE tensor is quantized per distinct (role,
@@ -586,6 +634,8 @@ def run_secondary(args) -> None:
         line = bench_config1(hq, oracle, torch, ctx, dev, args)
     elif args.workload == "decode":
         line = bench_decode(hq, oracle, torch, ctx, dev, args)
+    elif args.workload == "attention":
+        line = bench_attention(hq, oracle, torch, ctx, dev, args)
     else:
         line = bench_moe(hq, oracle, torch, ctx, dev, args, toks)
     line.update({"n_gpus": 1, "data": "synthetic"})
@@ -609,7 +659,7 @@ def main() -> None:
     ap.add_argument("--no-strong", action="store_true", help="several GPUs: skip the strong-scaling leg")
     ap.add_argument("--no-graph", action="store_true", help="issue launches eagerly instead of replaying a CUDA graph")
     ap.add_argument("--qtype", default="", help="matvec: one ggml type number (2, 8, 12, 13, 14) instead of all five")
-    ap.add_argument("--workload", default="gemv", choices=["gemv", "gemm", "moe", "matvec", "config1", "decode"],
+    ap.add_argument("--workload", default="gemv", choices=["gemv", "gemm", "moe", "matvec", "config1", "decode", "attention"],
                     help="gemv: the headline Q6_K decode sweep (default, carries the others as `secondary`); gemm: Q4_K_M prefill "
                          "GEMM sweep; moe: Qwen3-style A3B expert layer (Q5_K mul_mat_id); matvec: all block formats; config1: Q4_K 4096^2 f32")
     ap.add_argument("--tokens", type=int, default=0, help="gemm/moe: one token count instead of the sweep")

@@ -132,6 +132,14 @@ __global__ void __launch_bounds__(256) rope_kv_append_kernel(float* __restrict__
 constexpr int ATT_WARPS = 8;
 constexpr int ATT_HD = 128;
 constexpr int ATT_MAXG = 8;
+constexpr int ATT_PART = 4 + ATT_HD;     // floats of one partial result: max, sum, two pad words, 128 accumulators (16-byte aligned)
+
+// D (16x8, f32) += A (16x16, f16, row-major) * B (16x8, f16, column-major); c[0..1] = row lane/4, columns 2 (lane%4) + {0,1}
+__device__ __forceinline__ void mma_m16n8k16_f16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
 
 __device__ __forceinline__ float4 s8x4_to_float4(uint32_t w) {
     return make_float4(byte_to_float<128>(w ^ 0x80808080u, 0), byte_to_float<128>(w ^ 0x80808080u, 1),
@@ -238,9 +246,9 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) attn_decode_kernel(const float
             l_all += red_l[w][g] * c;
             a += red_acc[w][g][d] * c;
         }
-        float* dst = part + ((static_cast<size_t>(kvh) * nsplit + split) * G + g) * (2 + ATT_HD);
+        float* dst = part + ((static_cast<size_t>(kvh) * nsplit + split) * G + g) * ATT_PART;
         if (d == 0) { dst[0] = m_all; dst[1] = l_all; }
-        dst[2 + d] = a;
+        dst[4 + d] = a;
     }
 }
 
@@ -254,7 +262,7 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) attn_decode_kernel(const float
 //     merge order: bit-reproducible).
 // qkv: one fused QKV row, f32 [(n_q + 2 n_kv) * 128]; the query part is NOT modified.
 template <int G, typename OUT>
-__global__ void __launch_bounds__(ATT_WARPS * 32) attn_decode_fused_kernel(const float* __restrict__ qkv, uint32_t n_q, uint32_t n_kv,
+__global__ void __launch_bounds__(ATT_WARPS * 32, 2) attn_decode_fused_kernel(const float* __restrict__ qkv, uint32_t n_q, uint32_t n_kv,
                                                                            float theta, float q_scale,
                                                                            int8_t* __restrict__ k_codes, float* __restrict__ k_scale,
                                                                            int8_t* __restrict__ v_codes, float* __restrict__ v_scale,
@@ -277,6 +285,10 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) attn_decode_fused_kernel(const
     const uint32_t chunk = (n_ctx + nsplit - 1) / nsplit;
     const uint32_t lo = min(split * chunk, n_ctx), hi = min(lo + chunk, n_ctx);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    int8_t* kc = k_codes + static_cast<size_t>(kvh) * max_seq * ATT_HD;
+    int8_t* vc = v_codes + static_cast<size_t>(kvh) * max_seq * ATT_HD;
+    float* ksc = k_scale + static_cast<size_t>(kvh) * max_seq;
+    float* vsc = v_scale + static_cast<size_t>(kvh) * max_seq;
     // rotated, scaled query heads: thread -> (head g, pair i)
     for (uint32_t i = threadIdx.x; i < G * ATT_HD / 2; i += ATT_WARPS * 32) {
         const uint32_t g = i / (ATT_HD / 2), pr = i % (ATT_HD / 2);
@@ -288,10 +300,6 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) attn_decode_fused_kernel(const
         qs[g][2 * pr] = (a * cs - b * sn) * q_scale;
         qs[g][2 * pr + 1] = (a * sn + b * cs) * q_scale;
     }
-    int8_t* kc = k_codes + static_cast<size_t>(kvh) * max_seq * ATT_HD;
-    int8_t* vc = v_codes + static_cast<size_t>(kvh) * max_seq * ATT_HD;
-    float* ksc = k_scale + static_cast<size_t>(kvh) * max_seq;
-    float* vsc = v_scale + static_cast<size_t>(kvh) * max_seq;
     if (pos >= lo && pos < hi && warp < 2) {
         // the new position: warp 0 -> K (rotated), warp 1 -> V; lane owns 4 consecutive elements
         const bool is_k = warp == 0;
@@ -319,75 +327,125 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) attn_decode_fused_kernel(const
     }
     __syncthreads();            // qs ready; the new position's codes are visible to this CTA
 
-    float mx[G], l[G], acc[G][4];
+    // ---- scores and weighted values on the tensor cores (mma.sync m16n8k16, f16 operands, f32 accumulators).
+    // M = query heads of this KV head (rows gid < G; the rest of the 16 rows are zero), a warp step = 16 positions.
+    //   scores:  A = Q (f16), B = K^T with the 8-bit codes as the integers 1024 + (code + 128) in f16 (exact);
+    //            the offset 1152 * sum(q) is taken off afterwards.  The contraction order over the 128 dims is
+    //            free, so lane (gid, t) takes bytes [32t, 32t + 32) of row gid: two 16-byte loads, no shuffles.
+    //   values:  A = P * vscale (f16, straight from the score accumulators: same fragment layout), B = V with the
+    //            codes as f16 SUBNORMALS (code + 128) * 2^-24 (exact); pairs of positions are gathered byte-wise
+    //            from two rows; the offset 128 * sum(P * vscale) is taken off at the end.
+    const uint32_t gid = lane >> 2, t = lane & 3;
+    uint32_t qa0[8], qa2[8];
+    float qsum = 0.f;
 #pragma unroll
-    for (int g = 0; g < G; ++g) { mx[g] = -CUDART_INF_F; l[g] = 0.f; acc[g][0] = acc[g][1] = acc[g][2] = acc[g][3] = 0.f; }
-    for (uint32_t p0 = lo + warp * 32; p0 < hi; p0 += ATT_WARPS * 32) {
-        const uint32_t p = p0 + lane;
-        const bool live = p < hi;
-        float s[G];
-#pragma unroll
-        for (int g = 0; g < G; ++g) s[g] = 0.f;
-        float vs = 0.f;
-        if (live) {
-            const uint4* kr = reinterpret_cast<const uint4*>(kc + static_cast<size_t>(p) * ATT_HD);
-            uint4 kv[ATT_HD / 16];
-#pragma unroll
-            for (int c = 0; c < ATT_HD / 16; ++c) kv[c] = kr[c];              // all of the row in flight at once
-            const float sc = ksc[p];
-            vs = vsc[p];
-#pragma unroll
-            for (int c = 0; c < ATT_HD / 16; ++c) {
-                const uint32_t kw[4] = {kv[c].x, kv[c].y, kv[c].z, kv[c].w};
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    const float4 kf = s8x4_to_float4(kw[j]);
-#pragma unroll
-                    for (int g = 0; g < G; ++g) {
-                        const float4 qv = *reinterpret_cast<const float4*>(&qs[g][16 * c + 4 * j]);
-                        s[g] += kf.x * qv.x + kf.y * qv.y + kf.z * qv.z + kf.w * qv.w;
-                    }
-                }
-            }
-#pragma unroll
-            for (int g = 0; g < G; ++g) s[g] *= sc;
+    for (int j = 0; j < 8; ++j) {
+        qa0[j] = qa2[j] = 0u;
+        if (gid < static_cast<uint32_t>(G)) {
+            const float4 q4 = *reinterpret_cast<const float4*>(&qs[gid][32 * t + 4 * j]);
+            const __half2 lo2 = __floats2half2_rn(q4.x, q4.y), hi2 = __floats2half2_rn(q4.z, q4.w);
+            qa0[j] = *reinterpret_cast<const uint32_t*>(&lo2);
+            qa2[j] = *reinterpret_cast<const uint32_t*>(&hi2);
+            qsum += (__low2float(lo2) + __high2float(lo2)) + (__low2float(hi2) + __high2float(hi2));
         }
-        const uint32_t cnt = min(32u, hi - p0);
-        // this batch's V words (lane = 4 dims), requested before the softmax arithmetic
-        uint32_t vw[32];
-#pragma unroll
-        for (int i = 0; i < 32; ++i)
-            vw[i] = static_cast<uint32_t>(i) < cnt ? reinterpret_cast<const uint32_t*>(vc + static_cast<size_t>(p0 + i) * ATT_HD)[lane] : 0u;
-#pragma unroll
-        for (int g = 0; g < G; ++g) {
-            float bm = live ? s[g] : -CUDART_INF_F;
-            for (int o = 16; o > 0; o >>= 1) bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, o));
-            const float nm = fmaxf(mx[g], bm);
-            const float corr = __expf(mx[g] - nm);
-            const float pr = live ? __expf(s[g] - nm) : 0.f;
-            float bs = pr;
-            for (int o = 16; o > 0; o >>= 1) bs += __shfl_xor_sync(0xffffffffu, bs, o);
-            l[g] = l[g] * corr + bs;
-            mx[g] = nm;
-            acc[g][0] *= corr; acc[g][1] *= corr; acc[g][2] *= corr; acc[g][3] *= corr;
-            ps[warp][g][lane] = pr * vs;
-        }
-        __syncwarp();
-#pragma unroll
-        for (int i = 0; i < 32; ++i) {
-            const float4 vf = s8x4_to_float4(vw[i]);
-#pragma unroll
-            for (int g = 0; g < G; ++g) {
-                const float pw = ps[warp][g][i];                              // zero beyond the batch's end
-                acc[g][0] += pw * vf.x; acc[g][1] += pw * vf.y; acc[g][2] += pw * vf.z; acc[g][3] += pw * vf.w;
-            }
-        }
-        __syncwarp();
     }
+    qsum += __shfl_xor_sync(0xffffffffu, qsum, 1);
+    qsum += __shfl_xor_sync(0xffffffffu, qsum, 2);
+    const float qfix = 1152.0f * qsum;
+
+    float mx = -CUDART_INF_F, l = 0.f, lfix = 0.f;       // of head gid (the four lanes of a row group agree)
+    float o0[16], o1[16];                                 // out[gid][32t + j], out[gid][32t + 16 + j]
 #pragma unroll
-    for (int g = 0; g < G; ++g) {
-        if (lane == 0) { red_m[warp][g] = mx[g]; red_l[warp][g] = l[g]; }
-        *reinterpret_cast<float4*>(&red_acc[warp][g][4 * lane]) = make_float4(acc[g][0], acc[g][1], acc[g][2], acc[g][3]);
+    for (int j = 0; j < 16; ++j) o0[j] = o1[j] = 0.f;
+    for (uint32_t p0 = lo + warp * 16; p0 < hi; p0 += ATT_WARPS * 16) {
+        // K: rows p0 + gid and p0 + 8 + gid, bytes [32t, 32t + 32); V: rows p0 + 2t, +1, +8, +9, bytes [16 gid, 16 gid + 16).
+        // Rows past the end are clamped to the last one; their probabilities are forced to zero.
+        const uint32_t last = hi - 1;
+        uint4 kq[2][2], vq[4];
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt) {
+            const uint4* kr = reinterpret_cast<const uint4*>(kc + static_cast<size_t>(min(p0 + 8 * nt + gid, last)) * ATT_HD + 32 * t);
+            kq[nt][0] = kr[0];
+            kq[nt][1] = kr[1];
+        }
+        const uint32_t pc[4] = {p0 + 2 * t, p0 + 2 * t + 1, p0 + 2 * t + 8, p0 + 2 * t + 9};   // this lane's score / probability columns
+        float kscl[4], vscl[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            vq[i] = *reinterpret_cast<const uint4*>(vc + static_cast<size_t>(min(pc[i], last)) * ATT_HD + 16 * gid);
+            kscl[i] = ksc[min(pc[i], last)];
+            vscl[i] = vsc[min(pc[i], last)];
+        }
+        float sc[4];
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt) {
+            float c[4] = {0.f, 0.f, 0.f, 0.f};
+            const uint32_t kw[8] = {kq[nt][0].x, kq[nt][0].y, kq[nt][0].z, kq[nt][0].w, kq[nt][1].x, kq[nt][1].y, kq[nt][1].z, kq[nt][1].w};
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const uint32_t x = kw[j] ^ 0x80808080u;
+                const uint32_t b0 = __byte_perm(x, 0x64646464u, 0x4140u), b1 = __byte_perm(x, 0x64646464u, 0x4342u);
+                mma_m16n8k16_f16(c, qa0[j], 0u, qa2[j], 0u, b0, b1);
+            }
+            sc[2 * nt] = pc[2 * nt] < hi ? (c[0] - qfix) * kscl[2 * nt] : -CUDART_INF_F;
+            sc[2 * nt + 1] = pc[2 * nt + 1] < hi ? (c[1] - qfix) * kscl[2 * nt + 1] : -CUDART_INF_F;
+        }
+        float bm = fmaxf(fmaxf(sc[0], sc[1]), fmaxf(sc[2], sc[3]));
+        bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, 1));
+        bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, 2));          // finite: position p0 < hi is one of the sixteen
+        const float nm = fmaxf(mx, bm);
+        const float corr = __expf(mx - nm);
+        float pr[4], wf[4];
+        uint32_t pa[2];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) pr[i] = __expf(sc[i] - nm);       // exp(-inf) = 0 for the clamped columns
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const __half2 w2 = __floats2half2_rn(pr[2 * h] * vscl[2 * h] * 256.0f, pr[2 * h + 1] * vscl[2 * h + 1] * 256.0f);
+            pa[h] = *reinterpret_cast<const uint32_t*>(&w2);
+            wf[2 * h] = __low2float(w2);
+            wf[2 * h + 1] = __high2float(w2);
+        }
+        float bs = (pr[0] + pr[1]) + (pr[2] + pr[3]), bw = (wf[0] + wf[1]) + (wf[2] + wf[3]);
+        bs += __shfl_xor_sync(0xffffffffu, bs, 1);
+        bw += __shfl_xor_sync(0xffffffffu, bw, 1);
+        bs += __shfl_xor_sync(0xffffffffu, bs, 2);
+        bw += __shfl_xor_sync(0xffffffffu, bw, 2);
+        l = l * corr + bs;
+        lfix = lfix * corr + bw;
+        mx = nm;
+#pragma unroll
+        for (int j = 0; j < 16; ++j) { o0[j] *= corr; o1[j] *= corr; }
+        // V operand: word c of the lane's 16 bytes = dims 16 gid + 4c .. + 3 = column gid of the tiles 4c .. 4c + 3
+        const uint32_t va[4] = {vq[0].x ^ 0x80808080u, vq[0].y ^ 0x80808080u, vq[0].z ^ 0x80808080u, vq[0].w ^ 0x80808080u};
+        const uint32_t vb[4] = {vq[1].x ^ 0x80808080u, vq[1].y ^ 0x80808080u, vq[1].z ^ 0x80808080u, vq[1].w ^ 0x80808080u};
+        const uint32_t vc8[4] = {vq[2].x ^ 0x80808080u, vq[2].y ^ 0x80808080u, vq[2].z ^ 0x80808080u, vq[2].w ^ 0x80808080u};
+        const uint32_t vd[4] = {vq[3].x ^ 0x80808080u, vq[3].y ^ 0x80808080u, vq[3].z ^ 0x80808080u, vq[3].w ^ 0x80808080u};
+#pragma unroll
+        for (int c4 = 0; c4 < 4; ++c4) {
+            // [A.b0 A.b1 B.b0 B.b1] and [A.b2 A.b3 B.b2 B.b3] of the row pairs (2t, 2t+1) and (2t+8, 2t+9)
+            const uint32_t lo01 = __byte_perm(va[c4], vb[c4], 0x5410u), hi01 = __byte_perm(va[c4], vb[c4], 0x7632u);
+            const uint32_t lo89 = __byte_perm(vc8[c4], vd[c4], 0x5410u), hi89 = __byte_perm(vc8[c4], vd[c4], 0x7632u);
+            const uint32_t b0[4] = {lo01 & 0x00FF00FFu, __byte_perm(lo01, 0u, 0x4341u), hi01 & 0x00FF00FFu, __byte_perm(hi01, 0u, 0x4341u)};
+            const uint32_t b1[4] = {lo89 & 0x00FF00FFu, __byte_perm(lo89, 0u, 0x4341u), hi89 & 0x00FF00FFu, __byte_perm(hi89, 0u, 0x4341u)};
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                float d[4] = {o0[4 * c4 + i], o1[4 * c4 + i], 0.f, 0.f};
+                mma_m16n8k16_f16(d, pa[0], 0u, pa[1], 0u, b0[i], b1[i]);
+                o0[4 * c4 + i] = d[0];
+                o1[4 * c4 + i] = d[1];
+            }
+        }
+    }
+    // accumulators hold sum(P vscale 2^8 * (code + 128) 2^-24): back to sum(P vscale code)
+    if (gid < static_cast<uint32_t>(G)) {
+        const float off = 128.0f * lfix * (1.0f / 256.0f);
+        if (t == 0) { red_m[warp][gid] = mx; red_l[warp][gid] = l; }
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+            red_acc[warp][gid][32 * t + j] = o0[j] * 65536.0f - off;
+            red_acc[warp][gid][32 * t + 16 + j] = o1[j] * 65536.0f - off;
+        }
     }
     __syncthreads();
     for (uint32_t i = threadIdx.x; i < G * ATT_HD; i += ATT_WARPS * 32) {
@@ -402,9 +460,9 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) attn_decode_fused_kernel(const
             l_all += red_l[w][g] * c;
             a += red_acc[w][g][d] * c;
         }
-        float* dst = part + ((static_cast<size_t>(kvh) * nsplit + split) * G + g) * (2 + ATT_HD);
+        float* dst = part + ((static_cast<size_t>(kvh) * nsplit + split) * G + g) * ATT_PART;
         if (d == 0) { dst[0] = m_all; dst[1] = l_all; }
-        dst[2 + d] = a;
+        dst[4 + d] = a;
     }
     // the CTA that completes this KV head merges its splits
     __threadfence();
@@ -417,40 +475,56 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) attn_decode_fused_kernel(const
     __syncthreads();
     if (!is_last) return;
     __threadfence();
-    // Merge of the splits, all loads in flight at once: (1) every split's (max, sum) into shared memory,
-    // (2) one thread per head turns them into weights exp(max_s - max) and the normaliser, (3) every
-    // thread (head, dim) adds its column of the partial results in split order.
+    // Merge of the splits: (1) every split's (max, sum) into shared memory; (2) warp g turns those of head g into
+    // the weights exp(max_s - max) and the normaliser; (3) warp w adds the partial results of splits w, w + 8, ...
+    // (16-byte loads, all in flight), the eight sums are added in warp order: a fixed order, bit-reproducible.
     float* sm_m = &ps[0][0][0];                          // [nsplit][G] (nsplit <= 64: fits the probability scratch)
-    float* sm_c = &red_acc[0][0][0];                     // [nsplit][G] weights, then the normaliser per head at [64 * G + g]
+    float* sm_c = &qs[0][0];                             // [nsplit][G] weights (G * 128 floats), normaliser per head in red_m[0][g]
+    const float* pbase = part + static_cast<size_t>(kvh) * nsplit * G * ATT_PART;
     for (uint32_t i = threadIdx.x; i < nsplit * G; i += ATT_WARPS * 32) {
-        const uint32_t sp = i / G, g = i % G;
-        const float* src = part + ((static_cast<size_t>(kvh) * nsplit + sp) * G + g) * (2 + ATT_HD);
-        sm_m[i] = __ldcg(src);
-        sm_c[i] = __ldcg(src + 1);                       // the sums for now
+        const float2 ml = __ldcg(reinterpret_cast<const float2*>(pbase + static_cast<size_t>(i) * ATT_PART));
+        sm_m[i] = ml.x;
+        sm_c[i] = ml.y;                                  // the sums for now
     }
     __syncthreads();
-    if (threadIdx.x < G) {
-        const uint32_t g = threadIdx.x;
-        float m_all = -CUDART_INF_F;
-        for (uint32_t sp = 0; sp < nsplit; ++sp) m_all = fmaxf(m_all, sm_m[sp * G + g]);
-        float l_all = 0.f;
-        for (uint32_t sp = 0; sp < nsplit; ++sp) {
-            const float ms = sm_m[sp * G + g];
-            const float c = ms == -CUDART_INF_F ? 0.f : __expf(ms - m_all);
-            l_all += sm_c[sp * G + g] * c;
-            sm_c[sp * G + g] = c;
+    if (warp < G) {
+        const uint32_t g = warp;
+        const uint32_t s0 = lane, s1 = lane + 32;
+        const float m0 = s0 < nsplit ? sm_m[s0 * G + g] : -CUDART_INF_F, m1 = s1 < nsplit ? sm_m[s1 * G + g] : -CUDART_INF_F;
+        float m_all = fmaxf(m0, m1);
+        for (int o = 16; o > 0; o >>= 1) m_all = fmaxf(m_all, __shfl_xor_sync(0xffffffffu, m_all, o));
+        const float c0 = m0 == -CUDART_INF_F ? 0.f : __expf(m0 - m_all), c1 = m1 == -CUDART_INF_F ? 0.f : __expf(m1 - m_all);
+        float l_all = (s0 < nsplit ? sm_c[s0 * G + g] * c0 : 0.f) + (s1 < nsplit ? sm_c[s1 * G + g] * c1 : 0.f);
+        for (int o = 16; o > 0; o >>= 1) l_all += __shfl_xor_sync(0xffffffffu, l_all, o);
+        if (s0 < nsplit) sm_c[s0 * G + g] = c0;
+        if (s1 < nsplit) sm_c[s1 * G + g] = c1;
+        if (lane == 0) red_m[0][g] = l_all;
+    }
+    __syncthreads();
+    {
+        // lane: float4 column `lane` of each of the G heads
+        float4 a4[G];
+#pragma unroll
+        for (int g = 0; g < G; ++g) a4[g] = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 4
+        for (uint32_t sp = warp; sp < nsplit; sp += ATT_WARPS) {
+#pragma unroll
+            for (int g = 0; g < G; ++g) {
+                const float4 v = __ldcg(reinterpret_cast<const float4*>(pbase + (static_cast<size_t>(sp) * G + g) * ATT_PART + 4) + lane);
+                const float c = sm_c[sp * G + g];
+                a4[g].x += v.x * c; a4[g].y += v.y * c; a4[g].z += v.z * c; a4[g].w += v.w * c;
+            }
         }
-        sm_c[64 * G + g] = l_all;
+#pragma unroll
+        for (int g = 0; g < G; ++g) *reinterpret_cast<float4*>(&red_acc[warp][g][4 * lane]) = a4[g];
     }
     __syncthreads();
     for (uint32_t i = threadIdx.x; i < G * ATT_HD; i += ATT_WARPS * 32) {
         const uint32_t g = i / ATT_HD, d = i % ATT_HD;
-        const float* base = part + (static_cast<size_t>(kvh) * nsplit * G + g) * (2 + ATT_HD) + 2 + d;
-        const size_t stride = static_cast<size_t>(G) * (2 + ATT_HD);
         float a = 0.f;
-#pragma unroll 8
-        for (uint32_t sp = 0; sp < nsplit; ++sp) a += __ldcg(base + sp * stride) * sm_c[sp * G + g];
-        const float l_all = sm_c[64 * G + g];
+#pragma unroll
+        for (int w = 0; w < ATT_WARPS; ++w) a += red_acc[w][g][d];
+        const float l_all = red_m[0][g];
         const float v = l_all > 0.f ? a / l_all : 0.f;
         const size_t o = (static_cast<size_t>(kvh) * G + g) * ATT_HD + d;
         if constexpr (sizeof(OUT) == 4) out[o] = v;
@@ -464,13 +538,13 @@ __global__ void __launch_bounds__(ATT_HD) attn_combine_kernel(const float* __res
                                                               OUT* __restrict__ out) {
     const uint32_t head = blockIdx.x, kvh = head / G, g = head % G, d = threadIdx.x;
     float m_all = -CUDART_INF_F;
-    for (uint32_t s = 0; s < nsplit; ++s) m_all = fmaxf(m_all, part[((static_cast<size_t>(kvh) * nsplit + s) * G + g) * (2 + ATT_HD)]);
+    for (uint32_t s = 0; s < nsplit; ++s) m_all = fmaxf(m_all, part[((static_cast<size_t>(kvh) * nsplit + s) * G + g) * ATT_PART]);
     float l_all = 0.f, a = 0.f;
     for (uint32_t s = 0; s < nsplit; ++s) {
-        const float* src = part + ((static_cast<size_t>(kvh) * nsplit + s) * G + g) * (2 + ATT_HD);
+        const float* src = part + ((static_cast<size_t>(kvh) * nsplit + s) * G + g) * ATT_PART;
         const float c = src[0] == -CUDART_INF_F ? 0.f : __expf(src[0] - m_all);
         l_all += src[1] * c;
-        a += src[2 + d] * c;
+        a += src[4 + d] * c;
     }
     const float v = l_all > 0.f ? a / l_all : 0.f;
     if constexpr (sizeof(OUT) == 4) out[static_cast<size_t>(head) * ATT_HD + d] = v;
@@ -705,7 +779,7 @@ cudaError_t launch_rope_kv_append(float* qkv, uint32_t m, uint32_t n_q, uint32_t
 
 size_t attn_decode_scratch_bytes(uint32_t n_kv, uint32_t group, uint32_t n_splits) {
     // 256 bytes of per-KV-head completion counters (the fused form), then the splits' partial results
-    return 256 + static_cast<size_t>(n_kv) * n_splits * group * (2 + ATT_HD) * sizeof(float);
+    return 256 + static_cast<size_t>(n_kv) * n_splits * group * ATT_PART * sizeof(float);
 }
 
 cudaError_t launch_attn_decode(const float* q, uint32_t n_q, uint32_t n_kv, uint32_t hd, const KvCacheView& kv, const uint32_t* pos,
