@@ -279,32 +279,46 @@ __global__ void __launch_bounds__(ATT_WARPS * 32, 2) attn_decode_fused_kernel(co
     // prologue now; this kernel touches nothing an earlier kernel writes before that kernel has completed
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    // everything that does not depend on the position is requested before the position itself is read:
+    // the query pairs of this thread and (warps 0 and 1) the new row's K / V values
+    constexpr int QPAIRS = (G * ATT_HD / 2 + ATT_WARPS * 32 - 1) / (ATT_WARPS * 32);
+    float2 qraw[QPAIRS];
+#pragma unroll
+    for (int u = 0; u < QPAIRS; ++u) {
+        const uint32_t i = threadIdx.x + u * ATT_WARPS * 32;
+        qraw[u] = i < G * ATT_HD / 2
+                      ? *reinterpret_cast<const float2*>(qkv + (static_cast<size_t>(kvh) * G + i / (ATT_HD / 2)) * ATT_HD + 2 * (i % (ATT_HD / 2)))
+                      : make_float2(0.f, 0.f);
+    }
+    float4 newrow = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (warp < 2) newrow = *reinterpret_cast<const float4*>(qkv + (static_cast<size_t>(n_q) + (warp == 0 ? 0u : n_kv) + kvh) * ATT_HD + 4 * lane);
     const uint32_t pos = *pos_dev;
     if (pos >= max_seq) { if (threadIdx.x == 0 && split == 0) atomicOr(status, STATUS_BAD_EXPERT_ID); return; }
     const uint32_t n_ctx = pos + 1;
     const uint32_t chunk = (n_ctx + nsplit - 1) / nsplit;
     const uint32_t lo = min(split * chunk, n_ctx), hi = min(lo + chunk, n_ctx);
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     int8_t* kc = k_codes + static_cast<size_t>(kvh) * max_seq * ATT_HD;
     int8_t* vc = v_codes + static_cast<size_t>(kvh) * max_seq * ATT_HD;
     float* ksc = k_scale + static_cast<size_t>(kvh) * max_seq;
     float* vsc = v_scale + static_cast<size_t>(kvh) * max_seq;
     // rotated, scaled query heads: thread -> (head g, pair i)
-    for (uint32_t i = threadIdx.x; i < G * ATT_HD / 2; i += ATT_WARPS * 32) {
-        const uint32_t g = i / (ATT_HD / 2), pr = i % (ATT_HD / 2);
-        const float* src = qkv + (static_cast<size_t>(kvh) * G + g) * ATT_HD + 2 * pr;
-        const float freq = powf(theta, -static_cast<float>(2 * pr) / static_cast<float>(ATT_HD));
-        float sn, cs;
-        sincosf(static_cast<float>(pos) * freq, &sn, &cs);
-        const float a = src[0], b = src[1];
-        qs[g][2 * pr] = (a * cs - b * sn) * q_scale;
-        qs[g][2 * pr + 1] = (a * sn + b * cs) * q_scale;
+#pragma unroll
+    for (int u = 0; u < QPAIRS; ++u) {
+        const uint32_t i = threadIdx.x + u * ATT_WARPS * 32;
+        if (i < G * ATT_HD / 2) {
+            const uint32_t g = i / (ATT_HD / 2), pr = i % (ATT_HD / 2);
+            const float freq = powf(theta, -static_cast<float>(2 * pr) / static_cast<float>(ATT_HD));      // as in rope_kv_append_kernel
+            float sn, cs;
+            sincosf(static_cast<float>(pos) * freq, &sn, &cs);
+            qs[g][2 * pr] = (qraw[u].x * cs - qraw[u].y * sn) * q_scale;
+            qs[g][2 * pr + 1] = (qraw[u].x * sn + qraw[u].y * cs) * q_scale;
+        }
     }
     if (pos >= lo && pos < hi && warp < 2) {
         // the new position: warp 0 -> K (rotated), warp 1 -> V; lane owns 4 consecutive elements
         const bool is_k = warp == 0;
-        const float* src = qkv + (static_cast<size_t>(n_q) + (is_k ? 0u : n_kv) + kvh) * ATT_HD + 4 * lane;
-        float v4[4] = {src[0], src[1], src[2], src[3]};
+        float v4[4] = {newrow.x, newrow.y, newrow.z, newrow.w};
         if (is_k) {
 #pragma unroll
             for (int j = 0; j < 4; j += 2) {
