@@ -272,7 +272,7 @@ __global__ void __launch_bounds__(ATT_WARPS * 32, 2) attn_decode_fused_kernel(co
     __shared__ __align__(16) float qs[G][ATT_HD];
     __shared__ float ps[ATT_WARPS][G][32];
     __shared__ float red_m[ATT_WARPS][G], red_l[ATT_WARPS][G];
-    __shared__ __align__(16) float red_acc[ATT_WARPS][G][ATT_HD];
+    __shared__ __align__(16) float red_acc[ATT_WARPS][G][ATT_HD + 4];     // rows padded by 16 bytes: the accumulator fragments of the eight row groups land in different banks
     __shared__ uint32_t is_last;
     const uint32_t kvh = blockIdx.x, split = blockIdx.y, nsplit = gridDim.y;
     // programmatic dependent launch: the next kernel of the stream (the O product) may start its own
