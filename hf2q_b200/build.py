@@ -14,7 +14,7 @@ from pathlib import Path
 PKG = Path(__file__).resolve().parent
 CSRC = PKG / "csrc"
 OUT = PKG / "libhf2q_cuda.so"
-SOURCES = ["api.cu", "k0_dequant.cu", "k1_gemv.cu", "k1_gemv_mma.cu", "k2_gemm_tc.cu", "k4_moe_prep.cu", "moe_router.cu", "ffn_elementwise.cu", "decoder_ops.cu", "comm_nccl.cu"]
+SOURCES = ["api.cu", "k0_dequant.cu", "k1_gemv.cu", "k1_gemv_mma.cu", "k2_gemm_tc.cu", "k4_moe_prep.cu", "moe_router.cu", "ffn_elementwise.cu", "decoder_ops.cu", "comm_nccl.cu", "ffn_builders.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC,-fvisibility=hidden",

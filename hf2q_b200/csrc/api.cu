@@ -57,6 +57,11 @@ struct hf2q_ctx {
 
 namespace hf2q {
 uint32_t* ctx_status_word(hf2q_ctx* ctx) { return ctx ? ctx->status : nullptr; }
+// records `msg` as the context's last error and returns `code` (for the library's other translation units)
+int32_t ctx_fail(hf2q_ctx* ctx, int32_t code, const char* msg) {
+    if (ctx) snprintf(ctx->err, sizeof ctx->err, "%s", msg);
+    return code;
+}
 }  // namespace hf2q
 
 namespace {

@@ -268,6 +268,11 @@ EpLayout ep_layout(uint32_t rows, uint32_t cap_recv, uint32_t world, uint32_t n,
     uint64_t inner = 0, inner2 = 0;
     hf2q_cuda_qmatmul_id_scratch_bytes(e_local, cap_recv, k, x_dtype, &inner);
     if (inter) hf2q_cuda_qmatmul_id_scratch_bytes(e_local, cap_recv, inter, HF2Q_DT_F32, &inner2);
+    if (inter) {                                      // the four-launch form of the expert FFN (sort + gather, SwiGLU pair, down)
+        uint64_t inner3 = 0;
+        hf2q_cuda_moe_experts_scratch_bytes(e_local, cap_recv, k, inter, &inner3);
+        if (inner3 > inner2) inner2 = inner3;
+    }
     o += align256(inner > inner2 ? inner : inner2);
     L.total = o;
     (void)world;
@@ -373,6 +378,11 @@ int32_t ep_impl(hf2q_ctx* ctx, hf2q_comm* comm, void* stream, const void* x_rows
         if (!w_up) {
             rc = hf2q_cuda_qmatmul_id(ctx, stream, x_recv, x_dtype, w_local, lids_recv, y_recv, total_recv, 1, n, k, e_local, expert_stride, type,
                                       inner ? sb + L.inner : nullptr, inner);
+        } else if (hf2q_cuda_moe_experts_supported(ctx, total_recv, 1, k, inter, e_local, type, type_down)) {
+            uint64_t need = 0;
+            hf2q_cuda_moe_experts_scratch_bytes(e_local, total_recv, k, inter, &need);
+            rc = hf2q_cuda_moe_experts(ctx, stream, x_recv, x_dtype, w_local, w_up, w_down, lids_recv, y_recv, total_recv, 1, k, inter, e_local,
+                                       expert_stride, type, stride_down, type_down, sb + L.inner, need);
         } else {
             float* g = reinterpret_cast<float*>(sb + L.g);
             float* u = reinterpret_cast<float*>(sb + L.u);

@@ -11,6 +11,7 @@ namespace hf2q {
 
 // the context's device status word (api.cu), for the translation units that launch kernels outside api.cu
 uint32_t* ctx_status_word(hf2q_ctx* ctx);
+int32_t ctx_fail(hf2q_ctx* ctx, int32_t code, const char* msg);      // sets the context's last-error text, returns code
 
 // cudaFuncSetAttribute(MaxDynamicSharedMemorySize) applies to the CURRENT device only, and one
 // process may hold contexts on several GPUs: the opt-in is remembered per device, not per process.

@@ -2,12 +2,14 @@
 ``build_dense_ffn_layer_gpu_q_into`` (src/inference/models/qwen35/gpu_ffn.rs:1086-1351) and
 ``build_moe_ffn_layer_gpu_q_into`` (gpu_ffn.rs:2313-2802).
 
-They only compose calls of the C ABI (quantized products, router, element-wise glue) on torch's
-current stream; nothing here computes on the host.  The math is that of the reference's scalar
+Each builder is ONE call of the C ABI (``hf2q_cuda_dense_ffn`` / ``hf2q_cuda_moe_ffn``, which compose the
+quantized products, the router and the element-wise glue on torch's current stream); nothing here
+computes on the host.  The math is that of the reference's scalar
 specs ``dense_swiglu_cpu_ref`` (ffn.rs:91-112) and ``moe_ffn_cpu_ref`` (ffn.rs:179-336).
 """
 from __future__ import annotations
 
+import ctypes as C
 from dataclasses import dataclass
 
 import torch
@@ -46,33 +48,44 @@ def _silu_mul(ctx, gate, up):
     return out
 
 
+class _MoeFfnWeights(C.Structure):            # hf2q_moe_ffn_weights in include/hf2q_cuda.h
+    _fields_ = [("router", C.c_void_p), ("expert_gate", C.c_void_p), ("expert_up", C.c_void_p), ("expert_down", C.c_void_p),
+                ("stride_gate_up", C.c_uint64), ("stride_down", C.c_uint64), ("type_gate_up", C.c_uint32), ("type_down", C.c_uint32),
+                ("n_experts", C.c_uint32), ("top_k", C.c_uint32), ("ffn", C.c_uint32), ("shared_ffn", C.c_uint32),
+                ("shared_gate", C.c_void_p), ("shared_up", C.c_void_p), ("shared_down", C.c_void_p),
+                ("shared_type_gate", C.c_uint32), ("shared_type_up", C.c_uint32), ("shared_type_down", C.c_uint32), ("reserved", C.c_uint32),
+                ("shared_gate_logit", C.c_void_p)]
+
+
+def _pooled_scratch(ctx, nbytes: int, device) -> torch.Tensor:
+    """The builders' scratch, grown on demand and kept on the context (decode_pool.rs:181-228 pools it per thread)."""
+    sc = getattr(ctx, "_ffn_scratch", None)
+    if sc is None or sc.numel() < nbytes:
+        sc = torch.empty(max(nbytes, 256), dtype=torch.uint8, device=device)
+        ctx._ffn_scratch = sc
+    return sc
+
+
 def build_dense_ffn_layer_gpu_q(ctx: ops.GpuContext, x: torch.Tensor, w: DenseFfnWeightsGpuQ,
                                 residual: torch.Tensor | None = None, fused: bool = True) -> torch.Tensor:
     """y = down @ (silu(gate @ x) * (up @ x)) (+ residual); x [m, hidden] f32/bf16, y f32 [m, hidden].
 
-    With ``fused`` (default) and a shape the fused kernels take, this is two products: gate/up with
-    the SwiGLU in the epilogue, down with the residual add in the epilogue (mat-vec kernels up to 8
-    rows, the tensor-core GEMM beyond).  Otherwise the
-    reference's sequence: gate, up, silu_mul, down, add (gpu_ffn.rs:896-960)."""
+    One call of ``hf2q_cuda_dense_ffn``: with ``fused`` (default) and a shape the fused kernels take, two
+    products -- gate/up with the SwiGLU in the epilogue, down with the residual add in the epilogue (mat-vec
+    kernels up to 8 rows, the tensor-core GEMM beyond); otherwise the reference's sequence gate, up,
+    silu_mul, down, add (gpu_ffn.rs:896-960)."""
     m = x.shape[0]
     inter, hidden = w.gate_q.rows, w.gate_q.cols
-    if fused and ops.quantized_matmul_swiglu_supported(ctx, m, w.gate_q, x.dtype):
-        c = torch.empty((m, inter), dtype=torch.float32, device=x.device)
-        ops.quantized_matmul_swiglu(ctx, x, w.gate_q, w.up_q, c, m)
-    else:
-        a = torch.empty((m, inter), dtype=torch.float32, device=x.device)
-        b = torch.empty_like(a)
-        ops.quantized_matmul_ggml(ctx, x, w.gate_q, a, w.gate_q.matmul_params(m))
-        ops.quantized_matmul_ggml(ctx, x, w.up_q, b, w.up_q.matmul_params(m))
-        c = _silu_mul(ctx, a, b)
+    x = x.contiguous()
     y = torch.empty((m, hidden), dtype=torch.float32, device=x.device)
-    if residual is not None and fused and ops.quantized_matmul_add_supported(ctx, w.down_q, c.dtype, m):
-        ops.quantized_matmul_add(ctx, c, w.down_q, residual.contiguous().float(), y, m)
-        return y
-    ops.quantized_matmul_ggml(ctx, c, w.down_q, y, w.down_q.matmul_params(m))
-    if residual is not None:
-        r = residual.contiguous().float()
-        ctx._check(ctx._lib.hf2q_cuda_add(ctx._h, ctx._stream(), y.data_ptr(), r.data_ptr(), y.numel()))
+    r = residual.contiguous().float() if residual is not None else None
+    need = C.c_uint64()
+    ctx._check(ctx._lib.hf2q_cuda_dense_ffn_scratch_bytes(m, hidden, inter, C.byref(need)))
+    sc = _pooled_scratch(ctx, need.value, x.device)
+    ctx._check(ctx._lib.hf2q_cuda_dense_ffn(ctx._h, ctx._stream(), x.data_ptr(), ops._act(x, "x"), w.gate_q.ptr, w.gate_q.ggml_type,
+                                            w.up_q.ptr, w.up_q.ggml_type, w.down_q.ptr, w.down_q.ggml_type,
+                                            r.data_ptr() if r is not None else None, y.data_ptr(), m, hidden, inter,
+                                            sc.data_ptr(), sc.numel(), 0 if fused else 1))
     return y
 
 
@@ -80,55 +93,32 @@ def build_moe_ffn_layer_gpu_q(ctx: ops.GpuContext, x: torch.Tensor, w: MoeFfnWei
                               residual: torch.Tensor | None = None, fused: bool = True) -> torch.Tensor:
     """Router -> softmax/top-k/renorm -> expert gate, up (mul_mat_id) -> SwiGLU -> expert down
     (mul_mat_id, one activation row per routed slot) -> weighted sum over the slots, plus the
-    sigmoid-gated shared expert and the residual.  x f32 [T, hidden]; returns f32 [T, hidden]."""
+    sigmoid-gated shared expert and the residual.  x [T, hidden]; returns f32 [T, hidden].
+    One call of ``hf2q_cuda_moe_ffn`` (build_moe_ffn_layer_gpu_q_into, gpu_ffn.rs:2313-2802)."""
     T, hidden = x.shape
-    E, k, inter = w.num_experts, w.num_experts_per_tok, w.moe_intermediate_size
     x = x.contiguous()
-    # the router is a small dense f32 matrix in the reference as well (gpu_ffn.rs:2347-2359 phase 1)
-    logits = torch.empty((T, E), dtype=torch.float32, device=x.device)
-    ctx._check(ctx._lib.hf2q_cuda_router_logits(ctx._h, ctx._stream(), x.data_ptr(), ops._act(x, "x"), w.router.data_ptr(),
-                                                logits.data_ptr(), T, E, hidden))
-    ids, wts = ops.moe_softmax_topk(ctx, logits, k)
-    rows = T * k
-    sg = ops.expert_stride(w.ggml_type_gate_up, inter, hidden)
-    sd = ops.expert_stride(w.ggml_type_down, hidden, inter)
-    pg = ops.GgmlQuantizedMatmulIdParams(T, k, inter, hidden, E, sg, w.ggml_type_gate_up)
-    d = torch.empty((rows, hidden), dtype=torch.float32, device=x.device)
-    if fused and ops.moe_experts_supported(ctx, T, k, hidden, inter, E, w.ggml_type_gate_up, w.ggml_type_down):
-        # many routed rows: sort + gather, gate/up pair with the SwiGLU in its epilogue, down -- four launches
-        ops.moe_experts(ctx, x, w.expert_gate.data_ptr(), w.expert_up.data_ptr(), w.expert_down.data_ptr(), ids, d,
-                        T, k, hidden, inter, E, w.ggml_type_gate_up, w.ggml_type_down, sg, sd)
-        return _moe_finish(ctx, x, w, d, wts, residual, T, k, hidden)
-    scratch = ops.IdMmScratch.alloc(ctx, E, rows, max(hidden, inter))
-    if fused and ops.quantized_matmul_id_swiglu_supported(ctx, pg, x.dtype):
-        # few routed rows: gate, up and the SwiGLU in one launch
-        act = torch.empty((rows, inter), dtype=torch.float32, device=x.device)
-        ops.quantized_matmul_id_swiglu_ggml(ctx, x, w.expert_gate.data_ptr(), w.expert_up.data_ptr(), ids, act, pg)
-    else:
-        g = torch.empty((rows, inter), dtype=torch.float32, device=x.device)
-        u = torch.empty_like(g)
-        ops.quantized_matmul_id_pair_ggml(ctx, x, w.expert_gate.data_ptr(), w.expert_up.data_ptr(), ids, g, u, scratch, pg)
-        act = _silu_mul(ctx, g, u)
-    pd = ops.GgmlQuantizedMatmulIdParams(rows, 1, hidden, inter, E, sd, w.ggml_type_down)
-    ops.quantized_matmul_id_ggml(ctx, act, w.expert_down.data_ptr(), ids, d, scratch, pd)
-    return _moe_finish(ctx, x, w, d, wts, residual, T, k, hidden)
-
-
-def _moe_finish(ctx, x, w, d, wts, residual, T, k, hidden):
-    """Shared expert, its sigmoid gate, the weighted sum over the slots and the residual (gpu_ffn.rs:2762-2802)."""
-    shared_y = gate_logit = None
+    if w.shared_gate_logit is not None and x.dtype != torch.float32:
+        x = x.float()                                   # the shared expert's gate logit is an f32 row dot
+    E, k, inter = w.num_experts, w.num_experts_per_tok, w.moe_intermediate_size
+    cw = _MoeFfnWeights()
+    cw.router, cw.expert_gate, cw.expert_up, cw.expert_down = (w.router.data_ptr(), w.expert_gate.data_ptr(), w.expert_up.data_ptr(),
+                                                               w.expert_down.data_ptr())
+    cw.stride_gate_up = ops.expert_stride(w.ggml_type_gate_up, inter, hidden)
+    cw.stride_down = ops.expert_stride(w.ggml_type_down, hidden, inter)
+    cw.type_gate_up, cw.type_down, cw.n_experts, cw.top_k, cw.ffn = int(w.ggml_type_gate_up), int(w.ggml_type_down), E, k, inter
     if w.shared is not None:
-        shared_y = build_dense_ffn_layer_gpu_q(ctx, x, w.shared)
+        s = w.shared
+        cw.shared_gate, cw.shared_up, cw.shared_down = s.gate_q.ptr, s.up_q.ptr, s.down_q.ptr
+        cw.shared_type_gate, cw.shared_type_up, cw.shared_type_down = s.gate_q.ggml_type, s.up_q.ggml_type, s.down_q.ggml_type
+        cw.shared_ffn = s.gate_q.rows
         if w.shared_gate_logit is not None:
-            gate_logit = torch.empty((T,), dtype=torch.float32, device=x.device)
-            xf = x if x.dtype == torch.float32 else x.float()
-            ctx._check(ctx._lib.hf2q_cuda_rowdot(ctx._h, ctx._stream(), xf.data_ptr(), w.shared_gate_logit.data_ptr(),
-                                                 gate_logit.data_ptr(), T, hidden))
+            cw.shared_gate_logit = w.shared_gate_logit.data_ptr()
+    need = C.c_uint64()
+    ctx._check(ctx._lib.hf2q_cuda_moe_ffn_scratch_bytes(C.byref(cw), T, hidden, C.byref(need)))
+    sc = _pooled_scratch(ctx, need.value, x.device)
     out = torch.empty((T, hidden), dtype=torch.float32, device=x.device)
-    ctx._check(ctx._lib.hf2q_cuda_moe_combine(
-        ctx._h, ctx._stream(), d.data_ptr(), wts.data_ptr(),
-        shared_y.data_ptr() if shared_y is not None else None,
-        gate_logit.data_ptr() if gate_logit is not None else None,
-        residual.data_ptr() if residual is not None else None,
-        out.data_ptr(), T, k, hidden))
+    r = residual.contiguous().float() if residual is not None else None
+    ctx._check(ctx._lib.hf2q_cuda_moe_ffn(ctx._h, ctx._stream(), x.data_ptr(), ops._act(x, "x"), C.byref(cw),
+                                          r.data_ptr() if r is not None else None, out.data_ptr(), T, hidden, sc.data_ptr(), sc.numel(),
+                                          0 if fused else 1))
     return out

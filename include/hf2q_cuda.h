@@ -459,6 +459,46 @@ HF2Q_API int32_t hf2q_cuda_router_logits(hf2q_ctx* ctx, void* stream, const void
 HF2Q_API int32_t hf2q_cuda_rowdot(hf2q_ctx* ctx, void* stream, const float* x, const float* v, float* out,
                                   uint32_t n_tokens, uint32_t hidden);
 
+/* ---- the two FFN builders as single calls ------------------------------------------------------ *
+ * build_dense_ffn_layer_gpu_q_into (src/inference/models/qwen35/gpu_ffn.rs:1086-1351) and
+ * build_moe_ffn_layer_gpu_q_into (gpu_ffn.rs:2313-2802) composed from the entries above on the caller's
+ * stream; every intermediate lives in the ONE scratch buffer the caller passes (the reference pools them
+ * per thread, decode_pool.rs:181-228).  Fused kernels are used where the shape takes them; otherwise, or
+ * with HF2Q_FFN_NO_FUSION in `flags`, the reference's own op sequence runs -- same values either way.
+ *   dense:  y[m][hidden] = down . (silu(gate . x) * (up . x)) (+ residual, which may be y itself)
+ *   moe:    router logits -> softmax/top-k/renorm -> routed experts -> weighted sum over the slots
+ *           + sigmoid(shared_gate_logit . x) * shared expert + residual   (moe_ffn_cpu_ref, ffn.rs:179-336)
+ * scratch: 256-byte aligned, hf2q_cuda_dense_ffn_scratch_bytes / hf2q_cuda_moe_ffn_scratch_bytes. */
+#define HF2Q_FFN_NO_FUSION 1u
+HF2Q_API int32_t hf2q_cuda_dense_ffn_scratch_bytes(uint32_t m, uint32_t hidden, uint32_t ffn, uint64_t* out);
+HF2Q_API int32_t hf2q_cuda_dense_ffn(hf2q_ctx* ctx, void* stream, const void* x, uint32_t x_dtype,
+                                     const void* w_gate, uint32_t type_gate, const void* w_up, uint32_t type_up,
+                                     const void* w_down, uint32_t type_down, const float* residual, float* y,
+                                     uint32_t m, uint32_t hidden, uint32_t ffn, void* scratch,
+                                     uint64_t scratch_bytes, uint32_t flags);
+/* MoeFfnWeightsGpuQ (gpu_ffn.rs:362-398) as plain pointers. */
+typedef struct hf2q_moe_ffn_weights {
+    const float* router;            /* f32 [n_experts][hidden] */
+    const void* expert_gate;        /* n_experts stacked [ffn][hidden], stride_gate_up bytes apart */
+    const void* expert_up;
+    const void* expert_down;        /* n_experts stacked [hidden][ffn], stride_down bytes apart */
+    uint64_t stride_gate_up, stride_down;
+    uint32_t type_gate_up, type_down;
+    uint32_t n_experts, top_k, ffn; /* ffn = moe_intermediate_size */
+    uint32_t shared_ffn;            /* intermediate size of the shared expert (ignored without one) */
+    const void* shared_gate;        /* shared expert (all three or none) */
+    const void* shared_up;
+    const void* shared_down;
+    uint32_t shared_type_gate, shared_type_up, shared_type_down, reserved;
+    const float* shared_gate_logit; /* f32 [hidden] or NULL (gate = 1); needs f32 activations */
+} hf2q_moe_ffn_weights;
+HF2Q_API int32_t hf2q_cuda_moe_ffn_scratch_bytes(const hf2q_moe_ffn_weights* w, uint32_t n_tokens, uint32_t hidden,
+                                                 uint64_t* out);
+HF2Q_API int32_t hf2q_cuda_moe_ffn(hf2q_ctx* ctx, void* stream, const void* x, uint32_t x_dtype,
+                                   const hf2q_moe_ffn_weights* w, const float* residual, float* y,
+                                   uint32_t n_tokens, uint32_t hidden, void* scratch, uint64_t scratch_bytes,
+                                   uint32_t flags);
+
 /* ---- f-3: the glue of a full decoder forward ---------------------------------------------------- *
  * What sits between the quantized products in forward_gpu_greedy
  * (src/inference/models/qwen35/forward_gpu.rs:4140) on Llama-shaped layers.  Arithmetic after the

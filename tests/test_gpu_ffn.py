@@ -251,3 +251,57 @@ def test_moe_experts_equals_the_separate_ops(gpu_ctx, tg, td):
     assert torch.count_nonzero(got[5]) == 0 and torch.equal(got[4], want[4]) and torch.equal(got[6], want[6])
     assert not ops.moe_experts_supported(gpu_ctx, 4, top_k, hidden, inter, E, tg, td)          # few rows: the mat-vec forms
     assert not ops.moe_experts_supported(gpu_ctx, T, top_k, hidden, inter, E, oracle.IQ4_NL, td)
+
+
+def test_builder_entries_fused_equals_reference_sequence(gpu_ctx):
+    """hf2q_cuda_dense_ffn / hf2q_cuda_moe_ffn: the fused forms and the reference's own op sequence
+    (HF2Q_FFN_NO_FUSION) give the same bits; the dense entry works in place on the residual stream in both."""
+    import ctypes as C
+    lib = _lib_load()
+    t, hidden, inter = oracle.Q4_K, 2048, 2048
+    gq, _ = _qw(gpu_ctx, t, inter, hidden, 1)
+    uq, _ = _qw(gpu_ctx, t, inter, hidden, 2)
+    dq, _ = _qw(gpu_ctx, oracle.Q6_K, hidden, inter, 3)
+    w = ffn.DenseFfnWeightsGpuQ(gq, uq, dq)
+    for m in (3, 40):
+        x = torch.from_numpy(make_x(m, hidden, seed=4 + m)).cuda()
+        res = torch.from_numpy(make_x(m, hidden, seed=5 + m)).cuda()
+        a = ffn.build_dense_ffn_layer_gpu_q(gpu_ctx, x, w, residual=res, fused=True)
+        b = ffn.build_dense_ffn_layer_gpu_q(gpu_ctx, x, w, residual=res, fused=False)
+        gpu_ctx.check_status()
+        assert torch.equal(a, b), m
+        need = C.c_uint64()
+        assert lib.hf2q_cuda_dense_ffn_scratch_bytes(m, hidden, inter, C.byref(need)) == 0
+        sc = torch.empty(need.value, dtype=torch.uint8, device="cuda")
+        for flags in (0, 1):
+            y = res.clone()                                 # y doubles as the residual
+            rc = lib.hf2q_cuda_dense_ffn(gpu_ctx._h, None, x.data_ptr(), 0, gq.ptr, t, uq.ptr, t, dq.ptr, oracle.Q6_K, y.data_ptr(),
+                                         y.data_ptr(), m, hidden, inter, sc.data_ptr(), sc.numel(), flags)
+            assert rc == 0
+            torch.cuda.synchronize()
+            assert torch.equal(y, a), (m, flags)
+        assert lib.hf2q_cuda_dense_ffn(gpu_ctx._h, None, x.data_ptr(), 0, gq.ptr, t, uq.ptr, t, dq.ptr, oracle.Q6_K, None, y.data_ptr(),
+                                       m, hidden, inter, sc.data_ptr(), 16, 0) == hq._lib.ERR_WORKSPACE
+    # the expert layer, few and many routed rows, with the shared expert
+    E, k, mi = 6, 2, 2048
+    tq = oracle.Q5_K
+    eg = torch.from_numpy(np.concatenate([make_quant_weight(tq, mi, hidden, seed=100 + e) for e in range(E)])).cuda()
+    eu = torch.from_numpy(np.concatenate([make_quant_weight(tq, mi, hidden, seed=200 + e) for e in range(E)])).cuda()
+    ed = torch.from_numpy(np.concatenate([make_quant_weight(tq, hidden, mi, seed=300 + e) for e in range(E)])).cuda()
+    rng = np.random.default_rng(3)
+    router = torch.from_numpy((rng.standard_normal((E, hidden)) * 0.05).astype(np.float32)).cuda()
+    sl = torch.from_numpy((rng.standard_normal(hidden) * 0.05).astype(np.float32)).cuda()
+    mw = ffn.MoeFfnWeightsGpuQ(router=router, expert_gate=eg, expert_up=eu, expert_down=ed, ggml_type_gate_up=tq, ggml_type_down=tq,
+                               num_experts=E, num_experts_per_tok=k, moe_intermediate_size=mi, shared=w, shared_gate_logit=sl)
+    for T in (2, 90):
+        x = torch.from_numpy(make_x(T, hidden, seed=31 + T)).cuda()
+        res = torch.from_numpy(make_x(T, hidden, seed=32 + T)).cuda()
+        a = ffn.build_moe_ffn_layer_gpu_q(gpu_ctx, x, mw, residual=res, fused=True)
+        b = ffn.build_moe_ffn_layer_gpu_q(gpu_ctx, x, mw, residual=res, fused=False)
+        gpu_ctx.check_status()
+        assert torch.equal(a, b), T
+
+
+def _lib_load():
+    from hf2q_b200 import _lib
+    return _lib.load()
