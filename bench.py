@@ -610,7 +610,7 @@ def bench_decode(hq, oracle, torch, ctx, dev, args) -> dict:
                          "weight_bytes_per_token": wbytes, "kv_bytes_per_token_at_mid_context": kvbytes,
                          "kernel": "gemv_mma_kernel (7 products per layer in 4-5 launches) + attn_decode_fused_kernel + glue", "traffic": None},
             "prefill": {"tokens": n_prompt, "seconds": round(prefill_s, 3), "tok_s": round(n_prompt / prefill_s, 1),
-                        "note": "tensor-core GEMMs + CUDA-core tiled attention over the 8-bit cache; not the timed metric"},
+                        "note": "tensor-core GEMMs with fused epilogues + tensor-core causal attention over the 8-bit cache; not the timed metric"},
             "launches_per_token": dec.launches_per_token, "gpu_launches": int(dec.launches_per_token * n_new), "logits_finite": logits_finite,
             "host_seconds_building_weights": round(t_build, 1), "eager_launches_seen": int(ctx.launch_count - l0), "clocks": clocks}
 

@@ -565,132 +565,145 @@ __global__ void __launch_bounds__(ATT_HD) attn_combine_kernel(const float* __res
     else out[static_cast<size_t>(head) * ATT_HD + d] = __float2bfloat16_rn(v);
 }
 
-// ------------------------------------------------------------------ prefill attention (causal, tiled)
-// grid (ceil(m / QT), n_kv_heads); one CTA handles QT = 16 query tokens x the G heads of its KV head
-// (rows r = tok * G + g, up to 128 rows), walking the cached positions [0, pos0 + tok] in tiles of
-// 32: the K / V tile is dequantised into shared memory once and used by all rows.  Thread = one
-// row for the scores (q in registers would need 128 floats; q stays in shared memory and is read as
-// broadcast-free float4s since every thread reads its own row), then thread = (row, 32 dims) for the
-// values.  CUDA cores only: the prefill of the decode benchmark is not the timed part.
-constexpr int PF_QT = 16;
-constexpr int PF_KT = 32;
+// ------------------------------------------------------------------ prefill attention (causal, tensor cores)
+// grid (ceil(m / tokens per CTA), n_kv_heads), 4 warps per CTA.  A warp owns 16 rows = 16 / G query tokens x the
+// G heads of its KV head (row r: token r / G, head r % G) and walks the cached positions [0, pos0 + token] in
+// steps of 16 with the decode kernel's two products (mma.sync m16n8k16: K codes as the exact f16 integers
+// 1024 + (code + 128), V codes as f16 subnormals gathered byte-wise from pairs of rows, P * vscale straight
+// from the score accumulators), here with all 16 rows of the A operand in use.  The K / V rows of a KV head are
+// shared by the warps and CTAs of that head through L2 (1 MB per head at 8192 positions).  Heavy tiles (late
+// tokens) are scheduled first.  q is read rotated and scaled (rope_kv_append_kernel ran before).
+constexpr int PF_WARPS = 4;
 
 template <int G, typename OUT>
-__global__ void __launch_bounds__(PF_QT * G * 4) attn_prefill_kernel(const float* __restrict__ qkv, uint32_t row_stride, uint32_t m,
+__global__ void __launch_bounds__(PF_WARPS * 32) attn_prefill_kernel(const float* __restrict__ qkv, uint32_t row_stride, uint32_t m,
                                                                      const int8_t* __restrict__ k_codes, const float* __restrict__ k_scale,
                                                                      const int8_t* __restrict__ v_codes, const float* __restrict__ v_scale,
                                                                      uint32_t max_seq, uint32_t pos0, OUT* __restrict__ out,
                                                                      uint32_t out_stride) {
-    constexpr int ROWS = PF_QT * G;                         // (token, head) rows of this CTA
-    constexpr int THREADS = ROWS * 4;
-    extern __shared__ __align__(16) float sm[];
-    float* qs = sm;                                         // [ROWS][128 + 4]
-    float* kt = qs + ROWS * (ATT_HD + 4);                   // [PF_KT][128 + 4]   K tile, later V tile
-    float* pt = kt + PF_KT * (ATT_HD + 4);                  // [ROWS][PF_KT + 1]  probabilities of the tile
-    const uint32_t kvh = blockIdx.y, tok0 = blockIdx.x * PF_QT;
-    const int tid = threadIdx.x;
-    for (int i = tid; i < ROWS * ATT_HD; i += THREADS) {
-        const int r = i / ATT_HD, d = i % ATT_HD;
-        const uint32_t tok = tok0 + r / G;
-        qs[r * (ATT_HD + 4) + d] = tok < m ? qkv[static_cast<size_t>(tok) * row_stride + (static_cast<size_t>(kvh) * G + r % G) * ATT_HD + d] : 0.f;
-    }
+    constexpr uint32_t TPW = 16 / G;                        // tokens per warp
+    const uint32_t kvh = blockIdx.y, tile = gridDim.x - 1 - blockIdx.x;
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31, gid = lane >> 2, t = lane & 3;
+    const uint32_t wtok0 = (tile * PF_WARPS + warp) * TPW;
+    if (wtok0 >= m) return;
     const int8_t* kc = k_codes + static_cast<size_t>(kvh) * max_seq * ATT_HD;
     const int8_t* vc = v_codes + static_cast<size_t>(kvh) * max_seq * ATT_HD;
     const float* ksc = k_scale + static_cast<size_t>(kvh) * max_seq;
     const float* vsc = v_scale + static_cast<size_t>(kvh) * max_seq;
-    // scores: thread (row = tid / 4, quarter qt = tid % 4) takes the tile's positions 4j + qt, j = 0..7;
-    // values: the same thread takes dims 16i + 4qt .. +3, i = 0..7, of its row (both interleaved so that
-    // the four threads of a row read different shared-memory banks)
-    const int row = tid >> 2, qt = tid & 3;
-    const uint32_t my_tok = tok0 + row / G;
-    const uint32_t my_last = pos0 + my_tok;                 // last visible position of this row (causal)
-    const uint32_t last_tok = min(tok0 + PF_QT, m) - 1;
-    const uint32_t n_pos = pos0 + last_tok + 1;
-    float mx = -CUDART_INF_F, l = 0.f, acc[32];
+    const uint32_t wlast = pos0 + min(wtok0 + TPW, m) - 1;  // last position any row of this warp sees
+    // this lane's two rows: gid and gid + 8
+    uint32_t rtok[2], rlast[2];
+    uint32_t qa[4][8];                                      // A fragments of the 8 k-steps: [a0 a1 a2 a3][j]
+    float qfix[2];
 #pragma unroll
-    for (int i = 0; i < 32; ++i) acc[i] = 0.f;
-    __syncthreads();
-    for (uint32_t p0 = 0; p0 < n_pos; p0 += PF_KT) {
-        // K tile -> f32 (scaled)
-        for (int i = tid; i < PF_KT * ATT_HD / 4; i += THREADS) {
-            const int pr = i / (ATT_HD / 4), c = i % (ATT_HD / 4);
-            const uint32_t p = p0 + pr;
-            float4 f = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (p < n_pos) {
-                f = s8x4_to_float4(reinterpret_cast<const uint32_t*>(kc + static_cast<size_t>(p) * ATT_HD)[c]);
-                const float sc = ksc[p];
-                f.x *= sc; f.y *= sc; f.z *= sc; f.w *= sc;
-            }
-            *reinterpret_cast<float4*>(&kt[pr * (ATT_HD + 4) + 4 * c]) = f;
+    for (int h = 0; h < 2; ++h) {
+        const uint32_t r = gid + 8 * h;
+        rtok[h] = wtok0 + r / G;
+        const bool live = rtok[h] < m;
+        rlast[h] = live ? pos0 + rtok[h] : wlast;           // (rows past the end compute on zeros and are not stored)
+        const float* q = qkv + static_cast<size_t>(live ? rtok[h] : 0) * row_stride + (static_cast<size_t>(kvh) * G + r % G) * ATT_HD + 32 * t;
+        float qsum = 0.f;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const float4 q4 = live ? __ldg(reinterpret_cast<const float4*>(q) + j) : make_float4(0.f, 0.f, 0.f, 0.f);
+            const __half2 lo2 = __floats2half2_rn(q4.x, q4.y), hi2 = __floats2half2_rn(q4.z, q4.w);
+            qa[h][j] = *reinterpret_cast<const uint32_t*>(&lo2);
+            qa[2 + h][j] = *reinterpret_cast<const uint32_t*>(&hi2);
+            qsum += (__low2float(lo2) + __high2float(lo2)) + (__low2float(hi2) + __high2float(hi2));
         }
-        __syncthreads();
-        float s[8];
+        qsum += __shfl_xor_sync(0xffffffffu, qsum, 1);
+        qsum += __shfl_xor_sync(0xffffffffu, qsum, 2);
+        qfix[h] = 1152.0f * qsum;
+    }
+    float mx[2] = {-CUDART_INF_F, -CUDART_INF_F}, l[2] = {0.f, 0.f}, lfix[2] = {0.f, 0.f};
+    float o[16][4];                                         // [tile j]: rows gid (0,1) and gid + 8 (2,3), dims 32t + j and 32t + 16 + j
 #pragma unroll
-        for (int j = 0; j < 8; ++j) s[j] = 0.f;
-        for (int d = 0; d < ATT_HD; d += 4) {
-            const float4 qv = *reinterpret_cast<const float4*>(&qs[row * (ATT_HD + 4) + d]);
+    for (int j = 0; j < 16; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f;
+    for (uint32_t p0 = 0; p0 <= wlast; p0 += 16) {
+        uint4 kq[2][2], vq[4];
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt) {
+            const uint4* kr = reinterpret_cast<const uint4*>(kc + static_cast<size_t>(min(p0 + 8 * nt + gid, wlast)) * ATT_HD + 32 * t);
+            kq[nt][0] = kr[0];
+            kq[nt][1] = kr[1];
+        }
+        const uint32_t pc[4] = {p0 + 2 * t, p0 + 2 * t + 1, p0 + 2 * t + 8, p0 + 2 * t + 9};
+        float kscl[4], vscl[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            vq[i] = *reinterpret_cast<const uint4*>(vc + static_cast<size_t>(min(pc[i], wlast)) * ATT_HD + 16 * gid);
+            kscl[i] = ksc[min(pc[i], wlast)];
+            vscl[i] = vsc[min(pc[i], wlast)];
+        }
+        float sc[2][4];
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt) {
+            float c[4] = {0.f, 0.f, 0.f, 0.f};
+            const uint32_t kw[8] = {kq[nt][0].x, kq[nt][0].y, kq[nt][0].z, kq[nt][0].w, kq[nt][1].x, kq[nt][1].y, kq[nt][1].z, kq[nt][1].w};
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
-                const float4 kv = *reinterpret_cast<const float4*>(&kt[(4 * j + qt) * (ATT_HD + 4) + d]);
-                s[j] += qv.x * kv.x + qv.y * kv.y + qv.z * kv.z + qv.w * kv.w;
+                const uint32_t x = kw[j] ^ 0x80808080u;
+                mma_m16n8k16_f16(c, qa[0][j], qa[1][j], qa[2][j], qa[3][j], __byte_perm(x, 0x64646464u, 0x4140u), __byte_perm(x, 0x64646464u, 0x4342u));
             }
-        }
-        float bm = -CUDART_INF_F;
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-            const uint32_t p = p0 + 4 * j + qt;
-            if (p > my_last || my_tok >= m) s[j] = -CUDART_INF_F;
-            bm = fmaxf(bm, s[j]);
-        }
-        bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, 1));
-        bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, 2));
-        const float nm = fmaxf(mx, bm);
-        const float corr = nm == -CUDART_INF_F ? 1.f : __expf(mx - nm);
-        float bs = 0.f;
+            for (int h = 0; h < 2; ++h)
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-            const float pr = s[j] == -CUDART_INF_F ? 0.f : __expf(s[j] - nm);
-            bs += pr;
-            pt[row * (PF_KT + 1) + 4 * j + qt] = pr;
+                for (int i = 0; i < 2; ++i)
+                    sc[h][2 * nt + i] = pc[2 * nt + i] <= rlast[h] ? (c[2 * h + i] - qfix[h]) * kscl[2 * nt + i] : -CUDART_INF_F;
         }
-        bs += __shfl_xor_sync(0xffffffffu, bs, 1);
-        bs += __shfl_xor_sync(0xffffffffu, bs, 2);
-        l = l * corr + bs;
-        mx = nm;
+        uint32_t pa[4];                                     // a0 (row gid, tile 0), a1 (row gid + 8, tile 0), a2, a3 (tile 1)
 #pragma unroll
-        for (int i = 0; i < 32; ++i) acc[i] *= corr;
-        __syncthreads();                                    // scores done with the K tile; probabilities visible
-        // V tile -> f32 (scaled) into the same buffer
-        for (int i = tid; i < PF_KT * ATT_HD / 4; i += THREADS) {
-            const int pr = i / (ATT_HD / 4), c = i % (ATT_HD / 4);
-            const uint32_t p = p0 + pr;
-            float4 f = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (p < n_pos) {
-                f = s8x4_to_float4(reinterpret_cast<const uint32_t*>(vc + static_cast<size_t>(p) * ATT_HD)[c]);
-                const float sc = vsc[p];
-                f.x *= sc; f.y *= sc; f.z *= sc; f.w *= sc;
+        for (int h = 0; h < 2; ++h) {
+            float bm = fmaxf(fmaxf(sc[h][0], sc[h][1]), fmaxf(sc[h][2], sc[h][3]));
+            bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, 1));
+            bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, 2));
+            const float nm = fmaxf(mx[h], bm);              // finite from the first step on: position 0 is visible to every row
+            const float corr = __expf(mx[h] - nm);
+            float pr[4], wsum = 0.f, psum = 0.f;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) pr[i] = __expf(sc[h][i] - nm);
+#pragma unroll
+            for (int nt = 0; nt < 2; ++nt) {
+                const __half2 w2 = __floats2half2_rn(pr[2 * nt] * vscl[2 * nt] * 256.0f, pr[2 * nt + 1] * vscl[2 * nt + 1] * 256.0f);
+                pa[2 * nt + h] = *reinterpret_cast<const uint32_t*>(&w2);
+                wsum += __low2float(w2) + __high2float(w2);
+                psum += pr[2 * nt] + pr[2 * nt + 1];
             }
-            *reinterpret_cast<float4*>(&kt[pr * (ATT_HD + 4) + 4 * c]) = f;
-        }
-        __syncthreads();
-        for (int pr = 0; pr < PF_KT; ++pr) {
-            const float pw = pt[row * (PF_KT + 1) + pr];
+            psum += __shfl_xor_sync(0xffffffffu, psum, 1);
+            wsum += __shfl_xor_sync(0xffffffffu, wsum, 1);
+            psum += __shfl_xor_sync(0xffffffffu, psum, 2);
+            wsum += __shfl_xor_sync(0xffffffffu, wsum, 2);
+            l[h] = l[h] * corr + psum;
+            lfix[h] = lfix[h] * corr + wsum;
+            mx[h] = nm;
 #pragma unroll
-            for (int i = 0; i < 32; i += 4) {
-                const float4 vv = *reinterpret_cast<const float4*>(&kt[pr * (ATT_HD + 4) + 4 * i + 4 * qt]);
-                acc[i] += pw * vv.x; acc[i + 1] += pw * vv.y; acc[i + 2] += pw * vv.z; acc[i + 3] += pw * vv.w;
-            }
+            for (int j = 0; j < 16; ++j) { o[j][2 * h] *= corr; o[j][2 * h + 1] *= corr; }
         }
-        __syncthreads();
+        const uint32_t va[4] = {vq[0].x ^ 0x80808080u, vq[0].y ^ 0x80808080u, vq[0].z ^ 0x80808080u, vq[0].w ^ 0x80808080u};
+        const uint32_t vb[4] = {vq[1].x ^ 0x80808080u, vq[1].y ^ 0x80808080u, vq[1].z ^ 0x80808080u, vq[1].w ^ 0x80808080u};
+        const uint32_t vc8[4] = {vq[2].x ^ 0x80808080u, vq[2].y ^ 0x80808080u, vq[2].z ^ 0x80808080u, vq[2].w ^ 0x80808080u};
+        const uint32_t vd[4] = {vq[3].x ^ 0x80808080u, vq[3].y ^ 0x80808080u, vq[3].z ^ 0x80808080u, vq[3].w ^ 0x80808080u};
+#pragma unroll
+        for (int c4 = 0; c4 < 4; ++c4) {
+            const uint32_t lo01 = __byte_perm(va[c4], vb[c4], 0x5410u), hi01 = __byte_perm(va[c4], vb[c4], 0x7632u);
+            const uint32_t lo89 = __byte_perm(vc8[c4], vd[c4], 0x5410u), hi89 = __byte_perm(vc8[c4], vd[c4], 0x7632u);
+            const uint32_t b0[4] = {lo01 & 0x00FF00FFu, __byte_perm(lo01, 0u, 0x4341u), hi01 & 0x00FF00FFu, __byte_perm(hi01, 0u, 0x4341u)};
+            const uint32_t b1[4] = {lo89 & 0x00FF00FFu, __byte_perm(lo89, 0u, 0x4341u), hi89 & 0x00FF00FFu, __byte_perm(hi89, 0u, 0x4341u)};
+#pragma unroll
+            for (int i = 0; i < 4; ++i) mma_m16n8k16_f16(o[4 * c4 + i], pa[0], pa[1], pa[2], pa[3], b0[i], b1[i]);
+        }
     }
-    if (my_tok < m) {
-        const float inv = l > 0.f ? 1.0f / l : 0.f;
-        OUT* dst = out + static_cast<size_t>(my_tok) * out_stride + (static_cast<size_t>(kvh) * G + row % G) * ATT_HD;
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-            const int d = 4 * (i & ~3) + 4 * qt + (i & 3);          // acc[i] holds dim 16 * (i / 4) + 4 qt + i % 4
-            if constexpr (sizeof(OUT) == 4) dst[d] = acc[i] * inv;
-            else dst[d] = __float2bfloat16_rn(acc[i] * inv);
+    for (int h = 0; h < 2; ++h) {
+        if (rtok[h] >= m) continue;
+        const uint32_t r = gid + 8 * h;
+        const float inv = l[h] > 0.f ? 1.0f / l[h] : 0.f, off = 128.0f * lfix[h] * (1.0f / 256.0f);
+        OUT* dst = out + static_cast<size_t>(rtok[h]) * out_stride + (static_cast<size_t>(kvh) * G + r % G) * ATT_HD + 32 * t;
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+            const float v0 = (o[j][2 * h] * 65536.0f - off) * inv, v1 = (o[j][2 * h + 1] * 65536.0f - off) * inv;
+            if constexpr (sizeof(OUT) == 4) { dst[j] = v0; dst[16 + j] = v1; }
+            else { dst[j] = __float2bfloat16_rn(v0); dst[16 + j] = __float2bfloat16_rn(v1); }
         }
     }
 }
@@ -849,13 +862,10 @@ cudaError_t launch_attn_decode_fused(const float* qkv, uint32_t n_q, uint32_t n_
 template <int G, typename OUT>
 static cudaError_t launch_prefill_g(const float* qkv, uint32_t row_stride, uint32_t m, const KvCacheView& kv, uint32_t n_kv, uint32_t pos0,
                                     OUT* out, uint32_t out_stride, cudaStream_t st) {
-    constexpr int ROWS = PF_QT * G;
-    const size_t smem = (static_cast<size_t>(ROWS) * (ATT_HD + 4) + PF_KT * (ATT_HD + 4) + ROWS * (PF_KT + 1)) * sizeof(float);
-    auto kern = attn_prefill_kernel<G, OUT>;
-    static PerDeviceFlag attr;
-    if (const cudaError_t e = ensure_max_dynamic_smem(kern, 160 * 1024, attr); e != cudaSuccess) return e;
-    const dim3 grid((m + PF_QT - 1) / PF_QT, n_kv);
-    kern<<<grid, ROWS * 4, smem, st>>>(qkv, row_stride, m, kv.k_codes, kv.k_scale, kv.v_codes, kv.v_scale, kv.max_seq, pos0, out, out_stride);
+    constexpr uint32_t TOK = PF_WARPS * (16 / G);           // query tokens per CTA
+    const dim3 grid((m + TOK - 1) / TOK, n_kv);
+    attn_prefill_kernel<G, OUT><<<grid, PF_WARPS * 32, 0, st>>>(qkv, row_stride, m, kv.k_codes, kv.k_scale, kv.v_codes, kv.v_scale, kv.max_seq, pos0,
+                                                                out, out_stride);
     return cudaGetLastError();
 }
 
