@@ -18,7 +18,7 @@ graph and replayed once per generated token.
 from __future__ import annotations
 
 import ctypes as C
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 
 import torch
 

@@ -9,7 +9,6 @@ same context must keep working afterwards.  No second process, no peer GPU and n
 import ctypes as C
 import time
 
-import numpy as np
 import pytest
 import torch
 

@@ -9,7 +9,6 @@ finds the previous call's bytes in the array) is still right, and a product larg
 is refused with a clear error.  The file sorts last on purpose: a run that stops at the first
 failure has already gone through every other test.
 """
-import ctypes as C
 
 import numpy as np
 import pytest
