@@ -443,6 +443,13 @@ def bench_moe(hq, oracle, torch, ctx, dev, args, toks=None) -> dict:
 
         graph = _graph_of(torch, all_sets)
         dt = _timed(torch, graph.replay, max(3, min(args.steps, 20))) / nsets
+        dt_atomic = None
+        if experts:
+            # the opt-in form: weighted reduce inside the down product (f32 atomics), no [rows][hidden] round trip
+            def layer_atomic():
+                out.zero_()
+                hq.ops.moe_experts_reduce(ctx, x, wg.data_ptr(), wu.data_ptr(), wd.data_ptr(), id_sets[0], wt_sets[0], out, T, topk, H, I, E, t, t)
+            dt_atomic = _timed(torch, _graph_of(torch, layer_atomic).replay, max(3, min(args.steps, 20)))
         nexp = int(torch.unique(id_sets[0]).numel())
         wbytes = nexp * (2 * sg + sd)
         fl = 2.0 * R * 3 * I * H
@@ -451,6 +458,7 @@ def bench_moe(hq, oracle, torch, ctx, dev, args, toks=None) -> dict:
                         "weight_GBps": round(wbytes / dt / 1e9, 1), "experts_touched": nexp,
                         "roofline_hbm_us": round(t_hbm * 1e6, 1), "roofline_tensor_us": round(t_tc * 1e6, 1),
                         "frac_of_binding_roofline": round(max(t_hbm, t_tc) / dt, 4),
+                        "us_per_layer_reduce_in_down_product": round(dt_atomic * 1e6, 1) if dt_atomic else None,
                         "swiglu_in_gate_up_launch": bool(fused or experts), "launches_per_layer": 5 if experts else (3 if fused else None),
                         "timing": f"CUDA graph of {nsets} layer(s) with different routings; gate+up, SwiGLU, down and the weighted combine"}
     ctx.check_status()

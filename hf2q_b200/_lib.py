@@ -78,6 +78,7 @@ SIGNATURES = {
     "hf2q_cuda_dense_ffn": (i32, [vp, vp, vp, u32, vp, u32, vp, u32, vp, u32, vp, vp, u32, u32, u32, vp, u64, u32]),
     "hf2q_cuda_moe_ffn_scratch_bytes": (i32, [vp, u32, u32, C.POINTER(u64)]),
     "hf2q_cuda_moe_ffn": (i32, [vp, vp, vp, u32, vp, vp, vp, u32, u32, vp, u64, u32]),
+    "hf2q_cuda_moe_experts_reduce": (i32, [vp, vp, vp, u32, vp, vp, vp, vp, vp, vp, u32, u32, u32, u32, u32, u64, u32, u64, u32, vp, u64]),
     "hf2q_cuda_moe_softmax_topk": (i32, [vp, vp, vp, vp, vp, u32, u32, u32]),
     "hf2q_cuda_silu_mul": (i32, [vp, vp, vp, vp, vp, u64]),
     "hf2q_cuda_moe_combine": (i32, [vp, vp, vp, vp, vp, vp, vp, vp, u32, u32, u32]),

@@ -1121,13 +1121,14 @@ HF2Q_API int32_t hf2q_cuda_moe_experts_supported(hf2q_ctx* ctx, uint32_t n_token
     return 1;
 }
 
-HF2Q_API int32_t hf2q_cuda_moe_experts(hf2q_ctx* ctx, void* stream, const void* x, uint32_t x_dtype, const void* w_gate,
-                                       const void* w_up, const void* w_down, const uint32_t* ids, float* y, uint32_t n_tokens,
-                                       uint32_t top_k, uint32_t hidden, uint32_t ffn, uint32_t n_experts, uint64_t stride_gate_up,
-                                       uint32_t type_gate_up, uint64_t stride_down, uint32_t type_down, void* scratch,
-                                       uint64_t scratch_bytes) {
+// route_w == nullptr: y = [n_tokens * top_k][hidden] rows of the routed slots.  Otherwise y = [n_tokens][hidden] and every
+// slot's row is ADDED to its token's row, scaled by route_w[slot] (the caller has initialised y).
+static int32_t moe_experts_impl(hf2q_ctx* ctx, void* stream, const void* x, uint32_t x_dtype, const void* w_gate,
+                                const void* w_up, const void* w_down, const uint32_t* ids, const float* route_w, float* y, uint32_t n_tokens,
+                                uint32_t top_k, uint32_t hidden, uint32_t ffn, uint32_t n_experts, uint64_t stride_gate_up,
+                                uint32_t type_gate_up, uint64_t stride_down, uint32_t type_down, void* scratch,
+                                uint64_t scratch_bytes, const char* who) {
     if (!ctx) return HF2Q_ERR_INVALID_ARGUMENT;
-    const char* who = "moe_experts";
     if (!x || !w_gate || !w_up || !w_down || !ids || !y) return fail(ctx, HF2Q_ERR_INVALID_ARGUMENT, "%s: null pointer", who);
     if (x_dtype != HF2Q_DT_F32 && x_dtype != HF2Q_DT_BF16) return fail(ctx, HF2Q_ERR_INVALID_ARGUMENT, "%s: x_dtype %u", who, x_dtype);
     int32_t rc = check_matmul_shape(ctx, type_gate_up, ffn, hidden, who);
@@ -1161,17 +1162,38 @@ HF2Q_API int32_t hf2q_cuda_moe_experts(hf2q_ctx* ctx, void* stream, const void* 
     void* act16 = static_cast<uint8_t*>(scratch) + lay.total;
     const uint32_t nt = moe_token_tile(rows, n_experts);
     // the sort also zero-fills y: rows whose expert id is out of range stay zero, as in hf2q_cuda_qmatmul_id
-    cudaError_t e = launch_moe_prep(ids, rows, n_experts, top_k, nt, x, x_dtype, hidden, y, nullptr, hidden, scratch, lay, ctx->status,
-                                    ctx->dev.sm_count, st);
+    // (in the reducing form such rows simply add nothing)
+    cudaError_t e = launch_moe_prep(ids, rows, n_experts, top_k, nt, x, x_dtype, hidden, route_w ? nullptr : y, nullptr, hidden, scratch, lay,
+                                    ctx->status, ctx->dev.sm_count, st);
     if (e == cudaSuccess)
         e = launch_gemm_tc_grouped(type_gate_up, w_gate, stride_gate_up, n_experts, rows, nullptr, ffn, hidden, nt, scratch, lay, ctx->status,
                                    st, w_up, nullptr, act16);
     if (e == cudaSuccess)
         e = launch_gemm_tc_grouped(type_down, w_down, stride_down, n_experts, rows, y, hidden, ffn, nt, scratch, lay, ctx->status, st, nullptr,
-                                   act16, nullptr);
+                                   act16, nullptr, route_w, route_w ? y : nullptr, top_k);
     if (e != cudaSuccess) return cuda_fail(ctx, e, who);
     ctx->launches += 4;
     return HF2Q_OK;
+}
+
+HF2Q_API int32_t hf2q_cuda_moe_experts(hf2q_ctx* ctx, void* stream, const void* x, uint32_t x_dtype, const void* w_gate,
+                                       const void* w_up, const void* w_down, const uint32_t* ids, float* y, uint32_t n_tokens,
+                                       uint32_t top_k, uint32_t hidden, uint32_t ffn, uint32_t n_experts, uint64_t stride_gate_up,
+                                       uint32_t type_gate_up, uint64_t stride_down, uint32_t type_down, void* scratch,
+                                       uint64_t scratch_bytes) {
+    return moe_experts_impl(ctx, stream, x, x_dtype, w_gate, w_up, w_down, ids, nullptr, y, n_tokens, top_k, hidden, ffn, n_experts,
+                            stride_gate_up, type_gate_up, stride_down, type_down, scratch, scratch_bytes, "moe_experts");
+}
+
+HF2Q_API int32_t hf2q_cuda_moe_experts_reduce(hf2q_ctx* ctx, void* stream, const void* x, uint32_t x_dtype, const void* w_gate,
+                                              const void* w_up, const void* w_down, const uint32_t* ids, const float* weights, float* out,
+                                              uint32_t n_tokens, uint32_t top_k, uint32_t hidden, uint32_t ffn, uint32_t n_experts,
+                                              uint64_t stride_gate_up, uint32_t type_gate_up, uint64_t stride_down, uint32_t type_down,
+                                              void* scratch, uint64_t scratch_bytes) {
+    if (!ctx) return HF2Q_ERR_INVALID_ARGUMENT;
+    if (!weights) return fail(ctx, HF2Q_ERR_INVALID_ARGUMENT, "moe_experts_reduce: null routing weights");
+    return moe_experts_impl(ctx, stream, x, x_dtype, w_gate, w_up, w_down, ids, weights, out, n_tokens, top_k, hidden, ffn, n_experts,
+                            stride_gate_up, type_gate_up, stride_down, type_down, scratch, scratch_bytes, "moe_experts_reduce");
 }
 
 HF2Q_API int32_t hf2q_cuda_moe_softmax_topk(hf2q_ctx* ctx, void* stream, const float* logits, uint32_t* ids,
@@ -1203,8 +1225,8 @@ HF2Q_API int32_t hf2q_cuda_moe_combine(hf2q_ctx* ctx, void* stream, const float*
                                        const float* shared_gate_logit, const float* residual, float* out, uint32_t n_tokens,
                                        uint32_t top_k, uint32_t hidden) {
     if (!ctx) return HF2Q_ERR_INVALID_ARGUMENT;
-    if (!y || !weights || !out) return fail(ctx, HF2Q_ERR_INVALID_ARGUMENT, "moe_combine: null pointer");
-    if (top_k == 0 || hidden == 0) return fail(ctx, HF2Q_ERR_INVALID_ARGUMENT, "moe_combine: top_k and hidden must be non-zero");
+    if (!out || (top_k && (!y || !weights))) return fail(ctx, HF2Q_ERR_INVALID_ARGUMENT, "moe_combine: null pointer");
+    if (hidden == 0) return fail(ctx, HF2Q_ERR_INVALID_ARGUMENT, "moe_combine: hidden must be non-zero");
     if (n_tokens == 0) return HF2Q_OK;
     if (n_tokens > 65535) return fail(ctx, HF2Q_ERR_INVALID_ARGUMENT, "moe_combine: n_tokens=%u exceeds 65535 per call", n_tokens);
     DeviceGuard dg(ctx->device);

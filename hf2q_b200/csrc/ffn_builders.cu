@@ -156,6 +156,25 @@ HF2Q_API int32_t hf2q_cuda_moe_ffn(hf2q_ctx* ctx, void* stream, const void* x, u
     int32_t rc = hf2q_cuda_router_logits(ctx, stream, x, x_dtype, w->router, logits, T, E, hidden);
     if (!rc) rc = hf2q_cuda_moe_softmax_topk(ctx, stream, logits, ids, wts, T, E, K);
     if (rc) return rc;
+    // phases B-F in the opt-in form: shared expert + residual first, the routed experts add their weighted rows on top
+    if (fuse && (flags & HF2Q_FFN_ATOMIC_COMBINE) && hf2q_cuda_moe_experts_supported(ctx, T, K, hidden, I, E, w->type_gate_up, w->type_down)) {
+        float* shared_y = nullptr;
+        float* gate_logit = nullptr;
+        if (w->shared_gate) {
+            shared_y = reinterpret_cast<float*>(sb + L.shared_y);
+            rc = dense_ffn(ctx, stream, x, x_dtype, w->shared_gate, w->shared_type_gate, w->shared_up, w->shared_type_up, w->shared_down,
+                           w->shared_type_down, nullptr, shared_y, T, hidden, w->shared_ffn, sb + L.dense, flags);
+            if (!rc && w->shared_gate_logit) {
+                gate_logit = reinterpret_cast<float*>(sb + L.gate_logit);
+                rc = hf2q_cuda_rowdot(ctx, stream, static_cast<const float*>(x), w->shared_gate_logit, gate_logit, T, hidden);
+            }
+            if (rc) return rc;
+        }
+        rc = hf2q_cuda_moe_combine(ctx, stream, nullptr, nullptr, shared_y, gate_logit, residual, y, T, 0, hidden);
+        if (rc) return rc;
+        return hf2q_cuda_moe_experts_reduce(ctx, stream, x, x_dtype, w->expert_gate, w->expert_up, w->expert_down, ids, wts, y, T, K, hidden, I,
+                                            E, w->stride_gate_up, w->type_gate_up, w->stride_down, w->type_down, inner, inner_bytes);
+    }
     // phases B-E: the routed experts
     if (fuse && hf2q_cuda_moe_experts_supported(ctx, T, K, hidden, I, E, w->type_gate_up, w->type_down)) {
         rc = hf2q_cuda_moe_experts(ctx, stream, x, x_dtype, w->expert_gate, w->expert_up, w->expert_down, ids, d, T, K, hidden, I, E,

@@ -83,6 +83,12 @@ struct GParams {
     // or, for the expert-routed form, as f16 into act16[sorted row][n] (the down product's activation panel)
     const float* residual;
     __half* act16;
+    // expert-routed product only: instead of storing row perm[tok] of y, add route_w[perm[tok]] * value to row
+    // perm[tok] / top_k of reduce_out (the weighted sum over the top-k slots; floating-point atomics, so the
+    // rounding depends on the arrival order)
+    const float* route_w;
+    float* reduce_out;
+    uint32_t top_k;
     uint32_t tiles_per_cta; // weight-row tiles (of 128 rows) one CTA walks, re-using its barriers, TMEM and token tile
     uint32_t boxw;          // bytes per weight row in one raw stage
     uint32_t blk_bytes;     // bytes of one 256-element K-block of a row
@@ -330,6 +336,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
 #pragma unroll
                         for (int j = 0; j < 32; ++j) v[j] = __float_as_uint(__uint_as_float(v[j]) + res[j]);
                     }
+                    if (GROUPED && p.reduce_out) {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) {
+                            const uint32_t tok = tok0 + c0 + j;
+                            if (tok < tok_end) {
+                                const uint32_t dst = p.perm[tok];
+                                atomicAdd(p.reduce_out + static_cast<size_t>(dst / p.top_k) * p.ldy + row, p.route_w[dst] * __uint_as_float(v[j]));
+                            }
+                        }
+                    } else {
 #pragma unroll
                     for (int j = 0; j < 32; ++j) {
                         const uint32_t tok = tok0 + c0 + j;
@@ -337,6 +353,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
                             const uint32_t dst = GROUPED ? p.perm[tok] : tok;      // scatter back to routed-row order
                             p.y[static_cast<size_t>(dst) * p.ldy + row] = __uint_as_float(v[j]);
                         }
+                    }
                     }
                 }
             }
@@ -614,7 +631,8 @@ cudaError_t launch_grouped_nt(const CUtensorMap& tw, const CUtensorMap& tx, cons
 // scratch (the down product reads the act16 panel of the pair launch).
 cudaError_t launch_gemm_tc_grouped(uint32_t type, const void* w_stacked, uint64_t expert_stride, uint32_t n_experts, uint32_t rows,
                                    float* y, uint32_t n, uint32_t k, uint32_t nt, void* scratch, const MoeScratch& lay,
-                                   uint32_t* status, cudaStream_t st, const void* w_up, const void* x_panel, void* act16) {
+                                   uint32_t* status, cudaStream_t st, const void* w_up, const void* x_panel, void* act16,
+                                   const float* route_w, float* reduce_out, uint32_t top_k) {
     const bool dual = w_up != nullptr;
     const uint32_t tile_rows = dual ? 64 : TILE_N;
     const BlockGeom g = block_geom(type);
@@ -639,6 +657,7 @@ cudaError_t launch_gemm_tc_grouped(uint32_t type, const void* w_stacked, uint64_
     p.n_tiles = reinterpret_cast<const uint32_t*>(base);
     p.perm = reinterpret_cast<const uint32_t*>(base + lay.perm_off);
     p.act16 = static_cast<__half*>(act16);
+    p.route_w = route_w; p.reduce_out = reduce_out; p.top_k = top_k ? top_k : 1;
     p.boxw = boxw_of(type);
     p.blk_bytes = KB / g.elems * g.bytes;
     p.status = status;

@@ -112,7 +112,7 @@ __global__ void __launch_bounds__(SORT_THREADS) moe_sort_kernel(const uint32_t* 
             const uint32_t r = r0 + j;
             if (e[j] < n_experts) {
                 perm[atomicAdd(&cur[e[j]], 1u)] = r;
-            } else if (r < rows) {
+            } else if (r < rows && y) {
                 for (uint32_t c = 0; c < n; ++c) {                                       // rejected row: defined output
                     y[static_cast<size_t>(r) * n + c] = 0.f;
                     if (y2) y2[static_cast<size_t>(r) * n + c] = 0.f;

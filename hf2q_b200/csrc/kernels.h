@@ -135,7 +135,7 @@ bool gemm_tc_grouped_supported(uint32_t type, const void* w, uint64_t expert_str
 cudaError_t launch_gemm_tc_grouped(uint32_t type, const void* w_stacked, uint64_t expert_stride, uint32_t n_experts, uint32_t rows,
                                    float* y, uint32_t n, uint32_t k, uint32_t nt, void* scratch, const MoeScratch& lay,
                                    uint32_t* status, cudaStream_t st, const void* w_up = nullptr, const void* x_panel = nullptr,
-                                   void* act16 = nullptr);
+                                   void* act16 = nullptr, const float* route_w = nullptr, float* reduce_out = nullptr, uint32_t top_k = 0);
 
 // Fixed scratch of the allocation-free GEMM entry (lives in k2_gemm_tc.cu).
 uint64_t gemm_tc_static_scratch_bytes();

@@ -90,11 +90,12 @@ def build_dense_ffn_layer_gpu_q(ctx: ops.GpuContext, x: torch.Tensor, w: DenseFf
 
 
 def build_moe_ffn_layer_gpu_q(ctx: ops.GpuContext, x: torch.Tensor, w: MoeFfnWeightsGpuQ,
-                              residual: torch.Tensor | None = None, fused: bool = True) -> torch.Tensor:
+                              residual: torch.Tensor | None = None, fused: bool = True, atomic_combine: bool = False) -> torch.Tensor:
     """Router -> softmax/top-k/renorm -> expert gate, up (mul_mat_id) -> SwiGLU -> expert down
     (mul_mat_id, one activation row per routed slot) -> weighted sum over the slots, plus the
     sigmoid-gated shared expert and the residual.  x [T, hidden]; returns f32 [T, hidden].
-    One call of ``hf2q_cuda_moe_ffn`` (build_moe_ffn_layer_gpu_q_into, gpu_ffn.rs:2313-2802)."""
+    One call of ``hf2q_cuda_moe_ffn`` (build_moe_ffn_layer_gpu_q_into, gpu_ffn.rs:2313-2802).  ``atomic_combine``:
+    the weighted sum over the slots happens inside the down product (floating-point atomics: last bits may vary)."""
     T, hidden = x.shape
     x = x.contiguous()
     if w.shared_gate_logit is not None and x.dtype != torch.float32:
@@ -120,5 +121,5 @@ def build_moe_ffn_layer_gpu_q(ctx: ops.GpuContext, x: torch.Tensor, w: MoeFfnWei
     r = residual.contiguous().float() if residual is not None else None
     ctx._check(ctx._lib.hf2q_cuda_moe_ffn(ctx._h, ctx._stream(), x.data_ptr(), ops._act(x, "x"), C.byref(cw),
                                           r.data_ptr() if r is not None else None, out.data_ptr(), T, hidden, sc.data_ptr(), sc.numel(),
-                                          0 if fused else 1))
+                                          (0 if fused else 1) | (2 if atomic_combine else 0)))
     return out

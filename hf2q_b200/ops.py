@@ -498,6 +498,29 @@ def moe_experts(ctx: GpuContext, input: torch.Tensor, gate_ptr: int, up_ptr: int
                                               int(type_gate_up), sd, int(type_down), sc.data_ptr(), sc.numel()))
 
 
+def moe_experts_reduce(ctx: GpuContext, input: torch.Tensor, gate_ptr: int, up_ptr: int, down_ptr: int, ids: torch.Tensor,
+                       weights: torch.Tensor, out: torch.Tensor, n_tokens: int, top_k: int, hidden: int, ffn: int, n_experts: int,
+                       type_gate_up: int, type_down: int) -> None:
+    """``moe_experts`` with the weighted sum over the slots folded into the down product: every slot's row times
+    weights[slot] is ADDED to out[token] (f32 [n_tokens, hidden], initialised by the caller) with floating-point atomics."""
+    xdt = _act(input, "input")
+    rows = n_tokens * top_k
+    if out.dtype != torch.float32 or not out.is_cuda or not out.is_contiguous() or out.numel() < n_tokens * hidden:
+        raise Hf2qError(_lib.ERR_INVALID_ARGUMENT, "out must be a contiguous float32 CUDA tensor of [n_tokens, hidden]")
+    if weights.dtype != torch.float32 or weights.numel() < rows or ids.numel() < rows:
+        raise Hf2qError(_lib.ERR_INVALID_ARGUMENT, "ids / weights must hold n_tokens * top_k entries")
+    need = C.c_uint64()
+    ctx._check(ctx._lib.hf2q_cuda_moe_experts_scratch_bytes(n_experts, rows, hidden, ffn, C.byref(need)))
+    sc = getattr(ctx, "_moe_scratch", None)
+    if sc is None or sc.numel() < need.value:
+        sc = torch.empty(need.value, dtype=torch.uint8, device=input.device)
+        ctx._moe_scratch = sc
+    ctx._check(ctx._lib.hf2q_cuda_moe_experts_reduce(ctx._h, ctx._stream(), input.data_ptr(), xdt, int(gate_ptr), int(up_ptr), int(down_ptr),
+                                                     ids.data_ptr(), weights.data_ptr(), out.data_ptr(), n_tokens, top_k, hidden, ffn,
+                                                     n_experts, expert_stride(type_gate_up, ffn, hidden), int(type_gate_up),
+                                                     expert_stride(type_down, hidden, ffn), int(type_down), sc.data_ptr(), sc.numel()))
+
+
 def dequantize(ctx: GpuContext, weight: QuantWeight, out_dtype=torch.float32) -> torch.Tensor:
     out = torch.empty((weight.rows, weight.cols), dtype=out_dtype, device=f"cuda:{ctx.device}")
     ctx._check(ctx._lib.hf2q_cuda_dequantize(ctx._h, ctx._stream(), weight.ptr, weight.ggml_type,

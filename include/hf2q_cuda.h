@@ -311,6 +311,21 @@ HF2Q_API int32_t hf2q_cuda_moe_experts(hf2q_ctx* ctx, void* stream, const void* 
                                        uint32_t hidden, uint32_t ffn, uint32_t n_experts,
                                        uint64_t stride_gate_up, uint32_t type_gate_up, uint64_t stride_down,
                                        uint32_t type_down, void* scratch, uint64_t scratch_bytes);
+/* The same four launches with the weighted sum over the top-k slots (dispatch_moe_weighted_reduce,
+ * gpu_ffn.rs:2347-2359 phase F) folded into the down product's epilogue: every slot's row, scaled by
+ * weights[slot], is ADDED to row slot / top_k of out[n_tokens][hidden] with floating-point atomics.  The caller
+ * initialises `out` first (zeros, or shared expert + residual: hf2q_cuda_moe_combine with top_k = 0 writes
+ * exactly that).  Saves the [n_tokens * top_k][hidden] f32 round trip and the combine pass; the price is that
+ * the rounding of each sum depends on the order in which the experts' tiles finish, so results can differ
+ * in the last bits from run to run -- which is why this is a separate, opt-in entry. */
+HF2Q_API int32_t hf2q_cuda_moe_experts_reduce(hf2q_ctx* ctx, void* stream, const void* x, uint32_t x_dtype,
+                                              const void* w_gate, const void* w_up, const void* w_down,
+                                              const uint32_t* ids, const float* weights, float* out,
+                                              uint32_t n_tokens, uint32_t top_k, uint32_t hidden, uint32_t ffn,
+                                              uint32_t n_experts, uint64_t stride_gate_up, uint32_t type_gate_up,
+                                              uint64_t stride_down, uint32_t type_down, void* scratch,
+                                              uint64_t scratch_bytes);
+
 
 /* dispatch_moe_softmax_topk (gpu_ffn.rs:2551), semantics of softmax_topk_renorm_cpu
  * (gpu_ffn.rs:1879-1924): logits f32 [n_tokens, n_experts] -> ids u32 [n_tokens*top_k] (descending
@@ -443,6 +458,7 @@ HF2Q_API int32_t hf2q_cuda_silu_mul(hf2q_ctx* ctx, void* stream, const float* ga
  * (ffn.rs:179-336): out[t,:] = sum_s weights[t*top_k+s] * y[t*top_k+s,:]
  *                             + sigmoid(shared_gate_logit[t]) * shared[t,:]   (if shared != NULL;
  *                               gate 1 if shared_gate_logit == NULL)
+ * top_k == 0 (y, weights may be NULL): only the shared-expert and residual terms (zeros without them).
  *                             + residual[t,:]                                 (if residual != NULL). */
 HF2Q_API int32_t hf2q_cuda_moe_combine(hf2q_ctx* ctx, void* stream, const float* y, const float* weights,
                                        const float* shared, const float* shared_gate_logit,
@@ -470,6 +486,7 @@ HF2Q_API int32_t hf2q_cuda_rowdot(hf2q_ctx* ctx, void* stream, const float* x, c
  *           + sigmoid(shared_gate_logit . x) * shared expert + residual   (moe_ffn_cpu_ref, ffn.rs:179-336)
  * scratch: 256-byte aligned, hf2q_cuda_dense_ffn_scratch_bytes / hf2q_cuda_moe_ffn_scratch_bytes. */
 #define HF2Q_FFN_NO_FUSION 1u
+#define HF2Q_FFN_ATOMIC_COMBINE 2u   /* moe: weighted reduce inside the down product (hf2q_cuda_moe_experts_reduce) */
 HF2Q_API int32_t hf2q_cuda_dense_ffn_scratch_bytes(uint32_t m, uint32_t hidden, uint32_t ffn, uint64_t* out);
 HF2Q_API int32_t hf2q_cuda_dense_ffn(hf2q_ctx* ctx, void* stream, const void* x, uint32_t x_dtype,
                                      const void* w_gate, uint32_t type_gate, const void* w_up, uint32_t type_up,

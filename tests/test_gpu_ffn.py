@@ -305,3 +305,55 @@ def test_builder_entries_fused_equals_reference_sequence(gpu_ctx):
 def _lib_load():
     from hf2q_b200 import _lib
     return _lib.load()
+
+
+def test_moe_weighted_reduce_inside_the_down_product(gpu_ctx):
+    """HF2Q_FFN_ATOMIC_COMBINE: the slots' rows are added to their token's row by the down product's epilogue
+    (f32 atomics).  Same terms as the separate combine, summed in arrival order: equal to it within a few ulps of
+    the largest term, and a defined result for a row whose expert id is out of range."""
+    from hf2q_b200 import ops
+    t, hidden, inter, E, k = oracle.Q5_K, 2048, 512, 16, 4
+    eg = torch.from_numpy(np.concatenate([make_quant_weight(t, inter, hidden, seed=100 + e) for e in range(E)])).cuda()
+    eu = torch.from_numpy(np.concatenate([make_quant_weight(t, inter, hidden, seed=200 + e) for e in range(E)])).cuda()
+    ed = torch.from_numpy(np.concatenate([make_quant_weight(t, hidden, inter, seed=300 + e) for e in range(E)])).cuda()
+    rng = np.random.default_rng(5)
+    router = torch.from_numpy((rng.standard_normal((E, hidden)) * 0.05).astype(np.float32)).cuda()
+    sgq, _ = _qw(gpu_ctx, t, 512, hidden, 11)
+    suq, _ = _qw(gpu_ctx, t, 512, hidden, 12)
+    sdq, _ = _qw(gpu_ctx, t, hidden, 512, 13)
+    sl = torch.from_numpy((rng.standard_normal(hidden) * 0.05).astype(np.float32)).cuda()
+    w = ffn.MoeFfnWeightsGpuQ(router=router, expert_gate=eg, expert_up=eu, expert_down=ed, ggml_type_gate_up=t, ggml_type_down=t,
+                              num_experts=E, num_experts_per_tok=k, moe_intermediate_size=inter,
+                              shared=ffn.DenseFfnWeightsGpuQ(sgq, suq, sdq), shared_gate_logit=sl)
+    T = 300
+    x = torch.from_numpy(make_x(T, hidden, seed=9)).cuda()
+    res = torch.from_numpy(make_x(T, hidden, seed=10)).cuda()
+    want = ffn.build_moe_ffn_layer_gpu_q(gpu_ctx, x, w, residual=res)
+    got = ffn.build_moe_ffn_layer_gpu_q(gpu_ctx, x, w, residual=res, atomic_combine=True)
+    gpu_ctx.check_status()
+    scale = float(want.abs().max())
+    assert float((got - want).abs().max()) < 1e-5 * scale
+    assert rel_l2(got.cpu().numpy(), want.cpu().numpy()) < 1e-6
+    # the entry itself, with one expert id out of range: that slot adds nothing
+    ids = torch.from_numpy(np.stack([rng.permutation(E)[:k] for _ in range(T)]).astype(np.int32).reshape(-1)).cuda()
+    wts = torch.rand(T * k, device="cuda")
+    rows = torch.empty((T * k, hidden), device="cuda")
+    bad = ids.clone()
+    bad[7] = E + 1
+    ops.moe_experts(gpu_ctx, x, eg.data_ptr(), eu.data_ptr(), ed.data_ptr(), bad, rows, T, k, hidden, inter, E, t, t)
+    with pytest.raises(hq.Hf2qError):
+        gpu_ctx.check_status()
+    ref = (rows.view(T, k, hidden) * wts.view(T, k, 1)).sum(1)
+    out = torch.zeros((T, hidden), device="cuda")
+    lib = _lib_load()
+    import ctypes as C
+    need = C.c_uint64()
+    lib.hf2q_cuda_moe_experts_scratch_bytes(E, T * k, hidden, inter, C.byref(need))
+    sc = torch.empty(need.value, dtype=torch.uint8, device="cuda")
+    rc = lib.hf2q_cuda_moe_experts_reduce(gpu_ctx._h, None, x.data_ptr(), 0, eg.data_ptr(), eu.data_ptr(), ed.data_ptr(), bad.data_ptr(),
+                                          wts.data_ptr(), out.data_ptr(), T, k, hidden, inter, E, hq.expert_stride(t, inter, hidden), t,
+                                          hq.expert_stride(t, hidden, inter), t, sc.data_ptr(), sc.numel())
+    assert rc == 0
+    with pytest.raises(hq.Hf2qError):
+        gpu_ctx.check_status()
+    assert float((out - ref).abs().max()) < 1e-5 * float(ref.abs().max())
