@@ -7,7 +7,7 @@ streams and ``torch.distributed`` only.
 """
 from .ops import (  # noqa: F401
     GgmlType, GgmlQuantizedMatmulParams, GgmlQuantizedMatmulIdParams, Hf2qError, GpuContext,
-    QuantWeight, IdMmScratch, load_quant_weight, quantized_matmul_ggml, quantized_matmul_id_ggml, quantized_matmul_id_pair_ggml,
+    QuantWeight, IdMmScratch, load_quant_weight, load_mlx_affine_weight, quantized_matmul_ggml, quantized_matmul_id_ggml, quantized_matmul_id_pair_ggml,
     dequantize, moe_softmax_topk, row_bytes, expert_stride,
 )
 from . import ffn, dist, gguf, decoder  # noqa: F401,E402

@@ -43,6 +43,7 @@ SIGNATURES = {
     "hf2q_cuda_qmatmul_swiglu": (i32, [vp, vp, vp, u32, vp, vp, vp, u32, u32, u32, u32]),
     "hf2q_cuda_qmatmul_add_supported": (i32, [vp, u32, u32, u32, u32]),
     "hf2q_cuda_qmatmul_add": (i32, [vp, vp, vp, u32, vp, vp, vp, u32, u32, u32, u32]),
+    "hf2q_cuda_affine_pack": (i32, [vp, vp, vp, vp, vp, u32, u32, u32, u32, vp]),
     "hf2q_cuda_qmatmul_perm021": (i32, [vp, vp, vp, u32, vp, vp, u32, u32, u32, u32, u32, vp, u64]),
     "hf2q_cuda_qmatmul_swiglu_ws_supported": (i32, [vp, u32, u32, u32, u32, u32]),
     "hf2q_cuda_qmatmul_swiglu_ws": (i32, [vp, vp, vp, u32, vp, vp, vp, u32, u32, u32, u32, vp, u64]),

@@ -95,7 +95,7 @@ struct DeviceGuard {
 size_t dtype_size(uint32_t dt) { return dt == HF2Q_DT_F32 ? 4 : 2; }
 
 int32_t check_matmul_shape(hf2q_ctx* ctx, uint32_t type, uint32_t n, uint32_t k, const char* who) {
-    if (!type_supported(type)) return fail(ctx, HF2Q_ERR_UNSUPPORTED_TYPE, "%s: ggml type %u is not one of Q4_0/Q4_1/Q5_0/Q5_1/Q8_0/Q4_K/Q5_K/Q6_K/IQ4_NL", who, type);
+    if (!type_supported(type)) return fail(ctx, HF2Q_ERR_UNSUPPORTED_TYPE, "%s: type %u is not one of Q4_0/Q4_1/Q5_0/Q5_1/Q8_0/Q4_K/Q5_K/Q6_K/IQ4_NL/MLX_AFFINE4_GS32", who, type);
     const BlockGeom g = block_geom(type);
     if (n == 0 || k == 0) return fail(ctx, HF2Q_ERR_INVALID_ARGUMENT, "%s: n=%u k=%u must be non-zero", who, n, k);
     if (k % g.elems) return fail(ctx, HF2Q_ERR_INVALID_ARGUMENT, "%s: k=%u is not a multiple of the %u-element block", who, k, g.elems);
@@ -303,6 +303,25 @@ HF2Q_API int32_t hf2q_cuda_dequantize(hf2q_ctx* ctx, void* stream, const void* w
     DeviceGuard dg(ctx->device);
     const cudaError_t e = launch_dequant(type, w, out, out_dtype, n * k, ctx->dev.sm_count, static_cast<cudaStream_t>(stream));
     if (e != cudaSuccess) return cuda_fail(ctx, e, "dequantize launch");
+    ctx->launches += 1;
+    return HF2Q_OK;
+}
+
+HF2Q_API int32_t hf2q_cuda_affine_pack(hf2q_ctx* ctx, void* stream, const uint32_t* codes, const float* scales, const float* biases,
+                                       uint32_t n, uint32_t k, uint32_t bits, uint32_t group_size, void* out_blocks) {
+    if (!ctx) return HF2Q_ERR_INVALID_ARGUMENT;
+    if (!codes || !scales || !biases || !out_blocks) return fail(ctx, HF2Q_ERR_INVALID_ARGUMENT, "affine_pack: null pointer");
+    if (bits != 4 || group_size != 32)
+        return fail(ctx, HF2Q_ERR_UNSUPPORTED_TYPE, "affine_pack: only bits=4, group_size=32 (got bits=%u gs=%u)", bits, group_size);
+    if (k == 0 || k % 32) return fail(ctx, HF2Q_ERR_INVALID_ARGUMENT, "affine_pack: k=%u must be a non-zero multiple of 32", k);
+    if (reinterpret_cast<uintptr_t>(codes) % 16 || reinterpret_cast<uintptr_t>(out_blocks) % 8 || reinterpret_cast<uintptr_t>(scales) % 4 ||
+        reinterpret_cast<uintptr_t>(biases) % 4)
+        return fail(ctx, HF2Q_ERR_INVALID_ARGUMENT, "affine_pack: codes must be 16-byte, the output 8-byte, scales and biases 4-byte aligned");
+    if (n == 0) return HF2Q_OK;
+    DeviceGuard dg(ctx->device);
+    const cudaError_t e = launch_affine_pack(codes, scales, biases, static_cast<uint64_t>(n) * (k / 32), out_blocks, ctx->dev.sm_count,
+                                             static_cast<cudaStream_t>(stream));
+    if (e != cudaSuccess) return cuda_fail(ctx, e, "affine_pack launch");
     ctx->launches += 1;
     return HF2Q_OK;
 }

@@ -29,11 +29,12 @@ struct BlockGeom { uint32_t elems, bytes; };
 __host__ __device__ constexpr bool type_supported(uint32_t t) {
     return t == HF2Q_TYPE_Q4_0 || t == HF2Q_TYPE_Q8_0 || t == HF2Q_TYPE_Q4_K ||
            t == HF2Q_TYPE_Q5_K || t == HF2Q_TYPE_Q6_K || t == HF2Q_TYPE_Q4_1 || t == HF2Q_TYPE_Q5_0 ||
-           t == HF2Q_TYPE_Q5_1 || t == HF2Q_TYPE_IQ4_NL;
+           t == HF2Q_TYPE_Q5_1 || t == HF2Q_TYPE_IQ4_NL || t == HF2Q_TYPE_MLX_AFFINE4_GS32;
 }
-// the 32-element formats hf2q's quantizer falls back to (standard_policy.rs:128-192)
+// the 32-element formats hf2q's quantizer falls back to (standard_policy.rs:128-192), and the mlx-affine container:
+// all of them run on the generic element-wise consumers
 __host__ __device__ constexpr bool type_is_fallback32(uint32_t t) {
-    return t == HF2Q_TYPE_Q4_1 || t == HF2Q_TYPE_Q5_0 || t == HF2Q_TYPE_Q5_1 || t == HF2Q_TYPE_IQ4_NL;
+    return t == HF2Q_TYPE_Q4_1 || t == HF2Q_TYPE_Q5_0 || t == HF2Q_TYPE_Q5_1 || t == HF2Q_TYPE_IQ4_NL || t == HF2Q_TYPE_MLX_AFFINE4_GS32;
 }
 __host__ __device__ constexpr BlockGeom block_geom(uint32_t t) {
     return t == HF2Q_TYPE_Q4_0 ? BlockGeom{32, 18}
@@ -45,6 +46,7 @@ __host__ __device__ constexpr BlockGeom block_geom(uint32_t t) {
          : t == HF2Q_TYPE_Q5_0 ? BlockGeom{32, 22}
          : t == HF2Q_TYPE_Q5_1 ? BlockGeom{32, 24}
          : t == HF2Q_TYPE_IQ4_NL ? BlockGeom{32, 18}
+         : t == HF2Q_TYPE_MLX_AFFINE4_GS32 ? BlockGeom{32, 24}
                                : BlockGeom{0, 0};
 }
 
@@ -111,6 +113,11 @@ __device__ __forceinline__ float dequant_elem(const uint8_t* __restrict__ b, int
         const float d = f16_bits_to_f32(ld_u16(b));
         const uint32_t v = b[2 + (e & 15)];
         return d * static_cast<float>(iq4nl_value(e < 16 ? (v & 15u) : (v >> 4)));
+    } else if constexpr (TYPE == HF2Q_TYPE_MLX_AFFINE4_GS32) {
+        // f32 scale, f32 bias, codes in element order (element e = nibble e): scale * code + bias, two roundings
+        const float sc = __uint_as_float(ld_u32_a2(b)), bias = __uint_as_float(ld_u32_a2(b + 4));
+        const uint32_t q = (b[8 + (e >> 1)] >> (4 * (e & 1))) & 15u;
+        return __fadd_rn(__fmul_rn(sc, static_cast<float>(q)), bias);
     } else if constexpr (TYPE == HF2Q_TYPE_Q4_K || TYPE == HF2Q_TYPE_Q5_K) {
         const float d = f16_bits_to_f32(ld_u16(b));
         const float dmin = f16_bits_to_f32(ld_u16(b + 2));

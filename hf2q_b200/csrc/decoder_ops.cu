@@ -781,6 +781,7 @@ cudaError_t launch_get_rows(uint32_t type, const void* w, uint64_t row_bytes, ui
 #define HF2Q_CASE(T) case T: get_rows_kernel<T><<<m, 256, 0, st>>>(wb, row_bytes, n_rows, k, ids, out, status); break;
         HF2Q_CASE(HF2Q_TYPE_Q4_0) HF2Q_CASE(HF2Q_TYPE_Q8_0) HF2Q_CASE(HF2Q_TYPE_Q4_K) HF2Q_CASE(HF2Q_TYPE_Q5_K) HF2Q_CASE(HF2Q_TYPE_Q6_K)
         HF2Q_CASE(HF2Q_TYPE_Q4_1) HF2Q_CASE(HF2Q_TYPE_Q5_0) HF2Q_CASE(HF2Q_TYPE_Q5_1) HF2Q_CASE(HF2Q_TYPE_IQ4_NL)
+        HF2Q_CASE(HF2Q_TYPE_MLX_AFFINE4_GS32)
 #undef HF2Q_CASE
         default: return cudaErrorInvalidValue;
     }

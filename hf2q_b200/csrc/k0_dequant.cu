@@ -64,8 +64,33 @@ cudaError_t launch_dequant(uint32_t type, const void* w, void* out, uint32_t out
         case HF2Q_TYPE_Q5_0: return launch_dequant_t<HF2Q_TYPE_Q5_0>(w, out, out_dtype, n_elems, sm_count, st);
         case HF2Q_TYPE_Q5_1: return launch_dequant_t<HF2Q_TYPE_Q5_1>(w, out, out_dtype, n_elems, sm_count, st);
         case HF2Q_TYPE_IQ4_NL: return launch_dequant_t<HF2Q_TYPE_IQ4_NL>(w, out, out_dtype, n_elems, sm_count, st);
+        case HF2Q_TYPE_MLX_AFFINE4_GS32: return launch_dequant_t<HF2Q_TYPE_MLX_AFFINE4_GS32>(w, out, out_dtype, n_elems, sm_count, st);
         default: return cudaErrorInvalidValue;
     }
+}
+
+// mlx-affine arrays -> the library's 24-byte blocks (f32 scale, f32 bias, 16 code bytes): one thread per group of
+// 32 elements.  The four u32 words of a group hold its 32 nibbles already in element order (mlx packs element i
+// of a word into bits 4 (i % 8) ..), so the code bytes are copied as they are.
+__global__ void __launch_bounds__(256) affine_pack_kernel(const uint32_t* __restrict__ codes, const float* __restrict__ scales,
+                                                          const float* __restrict__ biases, uint64_t n_groups, uint8_t* __restrict__ out) {
+    const uint64_t stride = static_cast<uint64_t>(gridDim.x) * blockDim.x;
+    for (uint64_t g = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x; g < n_groups; g += stride) {
+        const uint4 c = __ldg(reinterpret_cast<const uint4*>(codes) + g);
+        uint32_t* dst = reinterpret_cast<uint32_t*>(out + g * 24);          // 24 g is a multiple of 8
+        dst[0] = __float_as_uint(__ldg(scales + g));
+        dst[1] = __float_as_uint(__ldg(biases + g));
+        dst[2] = c.x; dst[3] = c.y; dst[4] = c.z; dst[5] = c.w;
+    }
+}
+
+cudaError_t launch_affine_pack(const uint32_t* codes, const float* scales, const float* biases, uint64_t n_groups, void* out, int sm_count,
+                               cudaStream_t st) {
+    uint64_t want = (n_groups + 255) / 256;
+    const uint64_t cap = static_cast<uint64_t>(sm_count) * 16;
+    affine_pack_kernel<<<static_cast<unsigned>(want < cap ? (want ? want : 1) : cap), 256, 0, st>>>(codes, scales, biases, n_groups,
+                                                                                                    static_cast<uint8_t*>(out));
+    return cudaGetLastError();
 }
 
 }  // namespace hf2q

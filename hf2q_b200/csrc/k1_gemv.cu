@@ -513,6 +513,7 @@ cudaError_t launch_gemv(const GemvArgs& a, const DeviceInfo& dev, cudaStream_t s
         case HF2Q_TYPE_Q5_0: return launch_type<HF2Q_TYPE_Q5_0>(p, a.slots, can_stream, dev, st);
         case HF2Q_TYPE_Q5_1: return launch_type<HF2Q_TYPE_Q5_1>(p, a.slots, can_stream, dev, st);
         case HF2Q_TYPE_IQ4_NL: return launch_type<HF2Q_TYPE_IQ4_NL>(p, a.slots, can_stream, dev, st);
+        case HF2Q_TYPE_MLX_AFFINE4_GS32: return launch_type<HF2Q_TYPE_MLX_AFFINE4_GS32>(p, a.slots, can_stream, dev, st);
         default: return cudaErrorInvalidValue;
     }
 }

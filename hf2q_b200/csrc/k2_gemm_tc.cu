@@ -587,6 +587,7 @@ cudaError_t gemm_tc_dense(uint32_t type, const void* w, const void* w_up, const 
         case HF2Q_TYPE_Q5_0: return launch_gemm_nt<HF2Q_TYPE_Q5_0>(tw, tx, p, nt, st);
         case HF2Q_TYPE_Q5_1: return launch_gemm_nt<HF2Q_TYPE_Q5_1>(tw, tx, p, nt, st);
         case HF2Q_TYPE_IQ4_NL: return launch_gemm_nt<HF2Q_TYPE_IQ4_NL>(tw, tx, p, nt, st);
+        case HF2Q_TYPE_MLX_AFFINE4_GS32: return launch_gemm_nt<HF2Q_TYPE_MLX_AFFINE4_GS32>(tw, tx, p, nt, st);
         default: return cudaErrorInvalidValue;
     }
 }
@@ -704,6 +705,7 @@ cudaError_t launch_gemm_tc_grouped(uint32_t type, const void* w_stacked, uint64_
         case HF2Q_TYPE_Q5_0: return launch_grouped_nt<HF2Q_TYPE_Q5_0>(tw, tx, p, nt, gy, st);
         case HF2Q_TYPE_Q5_1: return launch_grouped_nt<HF2Q_TYPE_Q5_1>(tw, tx, p, nt, gy, st);
         case HF2Q_TYPE_IQ4_NL: return launch_grouped_nt<HF2Q_TYPE_IQ4_NL>(tw, tx, p, nt, gy, st);
+        case HF2Q_TYPE_MLX_AFFINE4_GS32: return launch_grouped_nt<HF2Q_TYPE_MLX_AFFINE4_GS32>(tw, tx, p, nt, gy, st);
         default: return cudaErrorInvalidValue;
     }
 }

@@ -103,6 +103,10 @@ uint32_t gemv_mma_grid_x(uint32_t n, uint32_t k, const DeviceInfo& dev);
 // count flag[8 + r]; a timeout (after `limit` clock ticks) sets STATUS_WAIT_TIMEOUT
 cudaError_t launch_gather_wait(const uint32_t* flag, uint32_t n_ranks, uint32_t rank, long long limit, uint32_t* status, cudaStream_t st);
 
+// mlx-affine arrays (u32 codes [groups][4], f32 scales, f32 biases) -> 24-byte blocks (k0_dequant.cu)
+cudaError_t launch_affine_pack(const uint32_t* codes, const float* scales, const float* biases, uint64_t n_groups, void* out, int sm_count,
+                               cudaStream_t st);
+
 // K2 (k2_gemm_tc.cu): tcgen05 GEMM for many activation rows.  Needs k % 256 == 0, 16-byte aligned
 // rows and a workspace of gemm_tc_workspace_bytes(m, k) for the f16 copy of the activations.
 bool gemm_tc_supported(uint32_t type, const void* w, uint32_t n, uint32_t k);

@@ -258,7 +258,7 @@ __host__ __device__ constexpr uint32_t tc_boxw(uint32_t type) {
          : type == HF2Q_TYPE_Q6_K ? 240u   // 210 bytes at an offset of 0..14; pitch of 15 x 16 bytes
          : type == HF2Q_TYPE_Q4_0 ? 144u : type == HF2Q_TYPE_Q8_0 ? 272u
          : type == HF2Q_TYPE_Q4_1 ? 160u : type == HF2Q_TYPE_Q5_0 ? 176u : type == HF2Q_TYPE_Q5_1 ? 192u
-         : type == HF2Q_TYPE_IQ4_NL ? 144u : 0u;
+         : type == HF2Q_TYPE_IQ4_NL ? 144u : type == HF2Q_TYPE_MLX_AFFINE4_GS32 ? 192u : 0u;
 }
 
 }  // namespace tc

@@ -41,6 +41,7 @@ class GgmlType(enum.IntEnum):
     Q5_K = 13
     Q6_K = 14
     IQ4_NL = 20
+    MLX_AFFINE4_GS32 = 1000        # not a GGML id: mlx-affine 4-bit / group 32 in this library's 24-byte block
 
 
 DT_F32, DT_F16, DT_BF16 = 0, 1, 2
@@ -188,6 +189,25 @@ def load_quant_weight(ctx: GpuContext, raw, ggml_type: int, rows: int, cols: int
     dev = C.c_void_p()
     ctx._check(ctx._lib.hf2q_cuda_upload_blocks(ctx._h, raw.ctypes.data, raw.size, C.byref(dev)))
     return QuantWeight(ctx, dev.value, want, ggml_type, rows, cols, abi_owned=True)
+
+
+def load_mlx_affine_weight(ctx: GpuContext, codes: torch.Tensor, scales: torch.Tensor, biases: torch.Tensor,
+                           bits: int = 4, group_size: int = 32) -> QuantWeight:
+    """MlxQWeight::from_mlx_affine_linear (src/serve/forward_mlx.rs:425-520): mlx-affine codes (u32/i32 [n, k/8], eight
+    nibbles per word, low nibble first) with f32 scales and biases [n, k/32] on the device -> one weight of type
+    MLX_AFFINE4_GS32 that every quantized product of this package takes (the interleave runs once, here)."""
+    n, k = codes.shape[0], codes.shape[1] * 8
+    for t, name in ((codes, "codes"), (scales, "scales"), (biases, "biases")):
+        if not t.is_cuda or not t.is_contiguous():
+            raise Hf2qError(_lib.ERR_INVALID_ARGUMENT, f"{name} must be a contiguous CUDA tensor")
+    if codes.dtype not in (torch.int32, torch.uint32) or scales.dtype != torch.float32 or biases.dtype != torch.float32:
+        raise Hf2qError(_lib.ERR_INVALID_ARGUMENT, "codes must be 32-bit integers, scales and biases float32")
+    if tuple(scales.shape) != (n, k // 32) or tuple(biases.shape) != (n, k // 32):
+        raise Hf2qError(_lib.ERR_INVALID_ARGUMENT, "scales / biases must be [n, k / 32]")
+    out = torch.empty(n * (k // 32) * 24, dtype=torch.uint8, device=codes.device)
+    ctx._check(ctx._lib.hf2q_cuda_affine_pack(ctx._h, ctx._stream(), codes.data_ptr(), scales.data_ptr(), biases.data_ptr(), n, k, bits,
+                                              group_size, out.data_ptr()))
+    return QuantWeight(ctx, out.data_ptr(), out.numel(), GgmlType.MLX_AFFINE4_GS32, n, k, owner=out)
 
 
 def _act(t: torch.Tensor, name: str) -> int:

@@ -42,7 +42,7 @@ typedef struct hf2q_ctx hf2q_ctx;
 enum {
     HF2Q_OK = 0,
     HF2Q_ERR_INVALID_ARGUMENT = 1, /* null pointer, zero or mismatched shape, misaligned buffer   */
-    HF2Q_ERR_UNSUPPORTED_TYPE = 2, /* ggml type outside the nine block formats listed below       */
+    HF2Q_ERR_UNSUPPORTED_TYPE = 2, /* type outside the block formats listed below                  */
     HF2Q_ERR_CUDA = 3,             /* a CUDA runtime call failed; see hf2q_cuda_last_error        */
     HF2Q_ERR_WORKSPACE = 4,        /* workspace / scratch missing or too small                    */
     HF2Q_ERR_TIMEOUT = 5,          /* a bounded device-side wait gave up (status word non-zero)   */
@@ -65,7 +65,11 @@ enum {
     HF2Q_TYPE_Q4_K = 12,
     HF2Q_TYPE_Q5_K = 13,
     HF2Q_TYPE_Q6_K = 14,
-    HF2Q_TYPE_IQ4_NL = 20
+    HF2Q_TYPE_IQ4_NL = 20,
+    /* Not a GGML id: mlx-affine 4-bit weights with groups of 32 (MlxAffineExtra, src/serve/forward_mlx.rs:340-360;
+     * w = scale * code + bias), in this library's own 24-byte block: f32 scale, f32 bias, 16 bytes of codes with
+     * element i in nibble i (low nibble first) -- what hf2q_cuda_affine_pack writes from the three mlx arrays. */
+    HF2Q_TYPE_MLX_AFFINE4_GS32 = 1000
 };
 
 /* Element types of activations and of dequantised output. */
@@ -211,6 +215,17 @@ HF2Q_API int32_t hf2q_cuda_qmatmul_add_ws(hf2q_ctx* ctx, void* stream, const voi
                                           const void* w, const float* residual, float* y, uint32_t m,
                                           uint32_t n, uint32_t k, uint32_t ggml_type, void* workspace,
                                           uint64_t workspace_bytes);
+
+/* mlx-affine (DWQ) weights: `codes` u32 [n][k / 8] (element i of a word in bits 4 (i % 8) .., mlx/ops.cpp
+ * packing as MlxQWeight::from_mlx_affine_linear writes it, forward_mlx.rs:425-470), `scales` / `biases` f32
+ * [n][k / 32].  Interleaves them, once, at load time, into HF2Q_TYPE_MLX_AFFINE4_GS32 blocks (k / 32 * 24 bytes
+ * per row, at `out_blocks`); from then on the weight goes through every entry of this header like any block
+ * format -- the replacement for dispatch_qmm_affine_t_packed_simd4_b4 in dispatch_qmatmul's affine branch
+ * (forward_mlx.rs:9749-9790) is hf2q_cuda_qmatmul with that type.  bits = 4 and group_size = 32 only, as in
+ * the reference. */
+HF2Q_API int32_t hf2q_cuda_affine_pack(hf2q_ctx* ctx, void* stream, const uint32_t* codes, const float* scales,
+                                       const float* biases, uint32_t n, uint32_t k, uint32_t bits,
+                                       uint32_t group_size, void* out_blocks);
 
 /* Same product for callers that hold HOST buffers: copies x in, runs, copies y out, waits.
  * Uses staging buffers the context grows on first use.  Stands for the reference's
