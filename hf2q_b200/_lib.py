@@ -58,6 +58,9 @@ SIGNATURES = {
     "hf2q_cuda_ipc_close": (i32, [vp, vp]),
     "hf2q_cuda_qmatmul_gather": (i32, [vp, vp, vp, u32, vp, vp, u32, u32, u32, u32]),
     "hf2q_cuda_gather_wait": (i32, [vp, vp, vp]),
+    "hf2q_cuda_gather_sum": (i32, [vp, vp, vp, vp, u32]),
+    "hf2q_cuda_gather_supported": (i32, [vp, vp, u32, u32, u32, u32, u32]),
+    "hf2q_cuda_gather_copy": (i32, [vp, vp, vp, vp, u32]),
     "hf2q_cuda_set_wait_limit": (i32, [vp, u64]),
     "hf2q_cuda_comm_unique_id": (i32, [vp]),
     "hf2q_cuda_comm_create": (i32, [i32, vp, i32, i32, pp]),

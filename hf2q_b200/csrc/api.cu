@@ -767,6 +767,48 @@ HF2Q_API int32_t hf2q_cuda_gather_wait(hf2q_ctx* ctx, void* stream, const hf2q_g
     return HF2Q_OK;
 }
 
+HF2Q_API int32_t hf2q_cuda_gather_supported(hf2q_ctx* ctx, const void* w, uint32_t m, uint32_t n, uint32_t k, uint32_t type, uint32_t x_dtype) {
+    if (!ctx || !w || !type_supported(type) || m == 0 || m > 8 || n == 0 || k == 0 || ctx->fp32_matvec) return 0;
+    GemvArgs a{};
+    a.w = w; a.x = nullptr; a.x_dtype = x_dtype; a.type = type; a.m = m; a.n = n; a.k = k; a.slots = 1; a.top_k = 1;
+    return gemv_mma_supported(a) && gemv_mma_max_rows(type, k, x_dtype, ctx->dev) >= m ? 1 : 0;
+}
+
+HF2Q_API int32_t hf2q_cuda_gather_copy(hf2q_ctx* ctx, void* stream, const hf2q_gather* g, const float* src, uint32_t n) {
+    if (!ctx || !g) return HF2Q_ERR_INVALID_ARGUMENT;
+    if (!src || n == 0) return fail(ctx, HF2Q_ERR_INVALID_ARGUMENT, "gather_copy: null or empty source");
+    if (g->n_ranks < 1 || g->n_ranks > 8 || g->rank >= g->n_ranks || static_cast<uint64_t>(g->col0) + n > g->n_total || g->n_rows[g->rank] != n)
+        return fail(ctx, HF2Q_ERR_INVALID_ARGUMENT, "gather_copy: rank %u of %u, columns [%u, %u) of %u, n_rows[rank]=%u", g->rank, g->n_ranks,
+                    g->col0, g->col0 + n, g->n_total, g->n_rows[g->rank]);
+    GatherArgs ga{};
+    for (uint32_t r = 0; r < g->n_ranks; ++r) {
+        if (!g->y_all[r] || !g->flags[r] || g->n_rows[r] == 0) return fail(ctx, HF2Q_ERR_INVALID_ARGUMENT, "gather_copy: buffer or n_rows of rank %u missing", r);
+        ga.y_all[r] = static_cast<float*>(g->y_all[r]);
+        ga.flags[r] = static_cast<uint32_t*>(g->flags[r]);
+    }
+    ga.n_ranks = g->n_ranks; ga.rank = g->rank; ga.n_total = g->n_total; ga.col0 = g->col0;
+    DeviceGuard dg(ctx->device);
+    const cudaError_t e = launch_gather_copy(src, ga, n, g->n_rows, static_cast<cudaStream_t>(stream));
+    if (e != cudaSuccess) return cuda_fail(ctx, e, "gather_copy launch");
+    ctx->launches += 1;
+    return HF2Q_OK;
+}
+
+HF2Q_API int32_t hf2q_cuda_gather_sum(hf2q_ctx* ctx, void* stream, const hf2q_gather* g, float* x, uint32_t n) {
+    if (!ctx || !g) return HF2Q_ERR_INVALID_ARGUMENT;
+    if (!x || n == 0) return fail(ctx, HF2Q_ERR_INVALID_ARGUMENT, "gather_sum: null or empty x");
+    if (g->n_ranks < 1 || g->n_ranks > 8 || g->rank >= g->n_ranks || !g->flags[g->rank] || !g->y_all[g->rank])
+        return fail(ctx, HF2Q_ERR_INVALID_ARGUMENT, "gather_sum: rank %u of %u", g->rank, g->n_ranks);
+    if (static_cast<uint64_t>(n) * g->n_ranks > g->n_total)
+        return fail(ctx, HF2Q_ERR_INVALID_ARGUMENT, "gather_sum: %u ranks x %u values exceed the buffer's %u columns", g->n_ranks, n, g->n_total);
+    DeviceGuard dg(ctx->device);
+    const cudaError_t e = launch_gather_sum(static_cast<const uint32_t*>(g->flags[g->rank]), g->n_ranks, g->rank, ctx->wait_limit, ctx->status,
+                                            static_cast<const float*>(g->y_all[g->rank]), n, x, n, static_cast<cudaStream_t>(stream));
+    if (e != cudaSuccess) return cuda_fail(ctx, e, "gather_sum launch");
+    ctx->launches += 1;
+    return HF2Q_OK;
+}
+
 HF2Q_API int32_t hf2q_cuda_set_wait_limit(hf2q_ctx* ctx, uint64_t clock_ticks) {
     if (!ctx || clock_ticks == 0 || clock_ticks > (1ull << 40)) return HF2Q_ERR_INVALID_ARGUMENT;
     ctx->wait_limit = static_cast<long long>(clock_ticks);

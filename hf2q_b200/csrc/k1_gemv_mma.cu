@@ -1242,6 +1242,72 @@ cudaError_t launch_gather_wait(const uint32_t* flag, uint32_t n_ranks, uint32_t 
     return cudaGetLastError();
 }
 
+namespace {
+// x[i] += sum over ranks r (in rank order: the same bits on every rank) of parts[r * stride + i], after the
+// columns of every rank have arrived here.  The gathered buffer holds one full-length PARTIAL product per rank
+// (a product whose contraction dimension is sharded): this is the all-reduce of a column-sharded projection,
+// built from the all-gather in the producing product's epilogue and a local sum.
+__global__ void __launch_bounds__(256) gather_sum_kernel(const uint32_t* flag, uint32_t n_ranks, uint32_t rank, long long limit, uint32_t* status,
+                                                         const float* __restrict__ parts, uint32_t stride, float* __restrict__ x, uint32_t n) {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    if (threadIdx.x < n_ranks && threadIdx.x != rank) gather_wait_source(flag, threadIdx.x, limit, status);
+    __syncthreads();
+    const uint32_t i = blockIdx.x * 256 + threadIdx.x;
+    if (i >= n) return;
+    float acc = x[i];
+    for (uint32_t r = 0; r < n_ranks; ++r) acc += __ldcg(parts + static_cast<size_t>(r) * stride + i);
+    x[i] = acc;
+}
+}  // namespace
+
+namespace {
+// The exchange of the fused all-gather without a product: src[0 .. n) goes to columns [col0, col0 + n) of row 0 of
+// every rank's buffer, and the peers' arrival counters are bumped exactly as the mat-vec's epilogue does it (one
+// fence, then one relaxed add per peer and CTA; CTA 0 books the arrivals this rank expects from every source).
+// For results that the gathering mat-vec cannot produce itself (unaligned rows run on the fp32 kernel).
+constexpr uint32_t GCOPY_PER_CTA = 1024;
+struct GatherCopyParams {
+    float* y[8];
+    uint32_t* flag[8];
+    uint32_t peer_ctas[8];
+    uint32_t n_ranks, rank, col0, n;
+};
+__global__ void __launch_bounds__(256) gather_copy_kernel(const float* __restrict__ src, const GatherCopyParams p) {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    for (uint32_t i = blockIdx.x * GCOPY_PER_CTA + threadIdx.x; i < min((blockIdx.x + 1) * GCOPY_PER_CTA, p.n); i += 256) {
+        const float v = src[i];
+        for (uint32_t r = 0; r < p.n_ranks; ++r) p.y[r][p.col0 + i] = v;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0 && p.n_ranks > 1) {
+        if (blockIdx.x == 0)
+            for (uint32_t r = 0; r < p.n_ranks; ++r)
+                if (r != p.rank) atomicAdd(p.flag[p.rank] + 8 + r, p.peer_ctas[r]);
+        asm volatile("fence.acq_rel.sys;" ::: "memory");
+        for (uint32_t r = 0; r < p.n_ranks; ++r)
+            if (r != p.rank) asm volatile("red.relaxed.sys.global.add.u32 [%0], 1;" ::"l"(p.flag[r] + p.rank) : "memory");
+    }
+}
+}  // namespace
+
+cudaError_t launch_gather_copy(const float* src, const GatherArgs& g, uint32_t n, const uint32_t* n_each, cudaStream_t st) {
+    GatherCopyParams p{};
+    for (uint32_t r = 0; r < g.n_ranks; ++r) {
+        p.y[r] = g.y_all[r];
+        p.flag[r] = g.flags[r];
+        p.peer_ctas[r] = (n_each[r] + GCOPY_PER_CTA - 1) / GCOPY_PER_CTA;
+    }
+    p.n_ranks = g.n_ranks; p.rank = g.rank; p.col0 = g.col0; p.n = n;
+    gather_copy_kernel<<<(n + GCOPY_PER_CTA - 1) / GCOPY_PER_CTA, 256, 0, st>>>(src, p);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_gather_sum(const uint32_t* flag, uint32_t n_ranks, uint32_t rank, long long limit, uint32_t* status, const float* parts,
+                              uint32_t stride, float* x, uint32_t n, cudaStream_t st) {
+    gather_sum_kernel<<<(n + 255) / 256, 256, 0, st>>>(flag, n_ranks, rank, limit, status, parts, stride, x, n);
+    return cudaGetLastError();
+}
+
 uint32_t gemv_mma_grid_x(uint32_t n, uint32_t k, const DeviceInfo& dev) {
     const uint32_t rows = ROWS * sub_groups_of(k);
     const uint32_t ngroups = (n + rows - 1) / rows;

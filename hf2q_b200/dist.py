@@ -283,6 +283,26 @@ class GatherGroup:
             weight.cols, weight.ggml_type))
         self._next ^= 1
 
+    def supports(self, weight, m: int, x_dtype=torch.float32) -> bool:
+        """Whether ``matmul`` takes this product (else: a plain product into a local buffer + ``copy``)."""
+        from . import ops
+        return bool(self.ctx._lib.hf2q_cuda_gather_supported(self.ctx._h, weight.ptr, m, weight.rows, weight.cols, weight.ggml_type,
+                                                             ops._TORCH_DT[x_dtype]))
+
+    def copy(self, src: torch.Tensor, col0: int, n_each: Sequence[int] | None = None) -> None:
+        """The exchange alone: src (f32, n values) -> columns [col0, col0 + n) of row 0 on every rank; counts as one
+        product of the group (buffers alternate, arrival counters advance)."""
+        n = src.numel()
+        g = self._struct(col0, False, self._next, list(n_each) if n_each is not None else [n] * self.world)
+        self.ctx._check(self.ctx._lib.hf2q_cuda_gather_copy(self.ctx._h, self.ctx._stream(), C.byref(g), src.data_ptr(), n))
+        self._next ^= 1
+
+    def sum_into(self, x: torch.Tensor, n: int) -> None:
+        """x[:n] += the sum over the ranks of the most recent product's n-value partials (columns r * n .. of its
+        buffer), after waiting for all of them; rank order, so every rank gets the same bits."""
+        g = self._struct(0, False, self._next ^ 1, [n] * self.world)
+        self.ctx._check(self.ctx._lib.hf2q_cuda_gather_sum(self.ctx._h, self.ctx._stream(), C.byref(g), x.data_ptr(), n))
+
     def wait(self) -> None:
         if self.world > 1:
             g = self._struct(0, False, 0, [1] * self.world)

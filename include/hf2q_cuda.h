@@ -411,6 +411,23 @@ HF2Q_API int32_t hf2q_cuda_qmatmul_gather(hf2q_ctx* ctx, void* stream, const voi
 /* Queues a one-warp kernel that waits (bounded) until every other rank's arrivals at this rank have
  * caught up with the products launched here so far; only flags[], n_ranks and rank of g are read. */
 HF2Q_API int32_t hf2q_cuda_gather_wait(hf2q_ctx* ctx, void* stream, const hf2q_gather* g);
+/* Whether hf2q_cuda_qmatmul_gather takes this product (it runs on the warp-MMA mat-vec only: 16-byte aligned
+ * weight rows, k % 256 == 0, one of the five main formats, m within one launch).  When it does not, run the product
+ * with hf2q_cuda_qmatmul into a local buffer and distribute it with hf2q_cuda_gather_copy: the exchange of
+ * the fused gather without a product -- src[0 .. n) goes to columns [col0, col0 + n) of row 0 of every rank's buffer
+ * and the arrival counters are bumped the same way (n_rows[r] = the length rank r copies in the same step). */
+HF2Q_API int32_t hf2q_cuda_gather_supported(hf2q_ctx* ctx, const void* w, uint32_t m, uint32_t n, uint32_t k,
+                                            uint32_t ggml_type, uint32_t x_dtype);
+HF2Q_API int32_t hf2q_cuda_gather_copy(hf2q_ctx* ctx, void* stream, const hf2q_gather* g, const float* src, uint32_t n);
+
+/* The all-reduce of a projection whose CONTRACTION dimension is sharded (the O and down projections of a
+ * tensor-parallel decoder: every rank multiplies its columns of the weight with its slice of the activations):
+ * each rank runs hf2q_cuda_qmatmul_gather with m = 1, n = the full output length, col0 = rank * n,
+ * n_rows[r] = n and n_total >= n_ranks * n, so that the gathered row holds one partial product per rank; this
+ * call then waits (bounded, like hf2q_cuda_gather_wait) until every rank's partial has arrived in `g`'s buffer
+ * of THIS rank and adds them to x in rank order:  x[i] += sum_r y[r * n + i].  Same bits on every rank. */
+HF2Q_API int32_t hf2q_cuda_gather_sum(hf2q_ctx* ctx, void* stream, const hf2q_gather* g, float* x, uint32_t n);
+
 /* Upper bound, in GPU clock ticks, of the device-side waits for other GPUs (the fused gather's
  * arrival counters).  A context setting: set once after creation, never on the launch path.  The
  * default 2^31 ticks is about a second.  After a timeout the waiting kernel records it (reported as

@@ -263,3 +263,114 @@ def test_one_process_two_devices():
                 if p.is_alive():
                     p.kill()
         assert p.exitcode == 0 and ret.get("ok")
+
+
+def _tp_decoder_main(rank, world, port, ret):
+    """Tensor-parallel decode step against the single-GPU decoder on the same weights (each rank runs both)."""
+    import torch.distributed as dist
+
+    import hf2q_b200 as hq
+    from hf2q_b200 import decoder as D, decoder_tp as TP
+    from tests.util import make_quant_weight, rel_l2
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        ctx = hq.GpuContext(rank)
+        cfg = D.LlamaConfig(n_layers=2, hidden=2048, n_heads=16, n_kv_heads=4, head_dim=128, ffn=6144, vocab=4096, max_seq=256)
+        types = D.q4_k_m_types(cfg)
+        rng = np.random.default_rng(0)                      # the same model on every rank
+        raws, norms = {}, {}
+
+        def tensor(name, n, k):
+            raws[name] = (make_quant_weight(types[name], n, k, seed=int(rng.integers(1 << 30))), types[name], n, k)
+
+        tensor("token_embd", cfg.vocab, cfg.hidden)
+        tensor("output", cfg.vocab, cfg.hidden)
+        for i in range(cfg.n_layers):
+            p = f"blk.{i}."
+            tensor(p + "attn_q", cfg.q_rows, cfg.hidden)
+            tensor(p + "attn_k", cfg.kv_rows, cfg.hidden)
+            tensor(p + "attn_v", cfg.kv_rows, cfg.hidden)
+            tensor(p + "attn_output", cfg.hidden, cfg.q_rows)
+            tensor(p + "ffn_gate", cfg.ffn, cfg.hidden)
+            tensor(p + "ffn_up", cfg.ffn, cfg.hidden)
+            tensor(p + "ffn_down", cfg.hidden, cfg.ffn)
+            for nm in ("attn_norm", "ffn_norm"):
+                norms[p + nm] = torch.from_numpy((1.0 + 0.1 * rng.standard_normal(cfg.hidden)).astype(np.float32)).cuda()
+        norms["out_norm"] = torch.from_numpy((1.0 + 0.1 * rng.standard_normal(cfg.hidden)).astype(np.float32)).cuda()
+
+        def full(*names):
+            parts = [raws[nm] for nm in names]
+            return hq.load_quant_weight(ctx, np.concatenate([p[0] for p in parts]), parts[0][1], sum(p[2] for p in parts), parts[0][3])
+
+        def shard(*names):
+            parts = [TP.shard_raw(nm, *raws[nm], cfg, rank, world) for nm in names]
+            return hq.load_quant_weight(ctx, np.concatenate([p[0] for p in parts]), raws[names[0]][1], sum(p[1] for p in parts), parts[0][2])
+
+        ref_layers, tp_layers = [], []
+        for i in range(cfg.n_layers):
+            p = f"blk.{i}."
+            same = types[p + "attn_v"] == types[p + "attn_q"]
+            qk = (p + "attn_q", p + "attn_k") + ((p + "attn_v",) if same else ())
+            ref_layers.append(D.LayerWeights(norms[p + "attn_norm"], full(*qk), None if same else full(p + "attn_v"), full(p + "attn_output"),
+                                             norms[p + "ffn_norm"], full(p + "ffn_gate"), full(p + "ffn_up"), full(p + "ffn_down")))
+            tp_layers.append(TP.TpLayerWeights(norms[p + "attn_norm"], shard(*qk), None if same else shard(p + "attn_v"), shard(p + "attn_output"),
+                                               norms[p + "ffn_norm"], shard(p + "ffn_gate"), shard(p + "ffn_up"), shard(p + "ffn_down")))
+        ref = D.LlamaDecoder(ctx, cfg, D.ModelWeights(full("token_embd"), ref_layers, norms["out_norm"], full("output")))
+        tp = TP.TensorParallelDecoder(ctx, cfg, TP.TpModelWeights(full("token_embd"), tp_layers, norms["out_norm"], shard("output")))
+        ok = True
+        ids = np.random.default_rng(5).integers(0, cfg.vocab, size=10)
+        for t, tok in enumerate(ids):                       # teacher-forced: both decoders see the same tokens
+            for d in (ref, tp):
+                d.tok.fill_(int(tok))
+                d.pos.fill_(t)
+                d.decode_step()
+            torch.cuda.synchronize()
+            a, b = ref.logits.cpu().numpy().reshape(-1), tp.logits.cpu().numpy().reshape(-1)
+            ok &= bool(rel_l2(b, a) < 2e-2)                 # the 8-bit KV rounding can flip a code between the two summation orders
+            ok &= bool(np.isfinite(b).all())
+        # the residual stream and the logits are replicated bit for bit
+        mine = tp.logits.reshape(-1).clone()
+        allv = [torch.empty_like(mine) for _ in range(world)]
+        dist.all_gather(allv, mine)
+        ok &= all(bool(torch.equal(v, mine)) for v in allv)
+        # greedy continuation from the replayed graph: every rank produces the same tokens
+        toks = tp.generate(5, use_graph=True)
+        torch.cuda.synchronize()
+        allt = [torch.empty_like(toks) for _ in range(world)]
+        dist.all_gather(allt, toks)
+        ok &= all(bool(torch.equal(v, toks)) for v in allt)
+        ok &= int(tp.pos.item()) == len(ids) - 1 + 1 + 5
+        ctx.check_status()
+        tp.close()
+        ret[rank] = bool(ok)
+    finally:
+        dist.destroy_process_group()
+
+
+def test_tensor_parallel_decoder_matches_single_gpu():
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    with ctx.Manager() as mgr:
+        ret = mgr.dict()
+        port = _free_port()
+        world = 4 if torch.cuda.device_count() >= 4 else 2
+        procs = [ctx.Process(target=_tp_decoder_main, args=(r, world, port, ret)) for r in range(world)]
+        for p in procs:
+            p.start()
+        try:
+            for p in procs:
+                p.join(300)
+        finally:
+            for p in procs:
+                if p.is_alive():
+                    p.terminate()
+                    p.join(10)
+                    if p.is_alive():
+                        p.kill()
+        assert all(p.exitcode == 0 for p in procs), [p.exitcode for p in procs]
+        assert all(ret.get(r) for r in range(world))
