@@ -564,6 +564,74 @@ def build_llama_weights(hq, oracle, torch, ctx, dev, cfg, distinct_rows: int = 1
     return D.ModelWeights(vocab_weight("embd", types["token_embd"], 7), layers, ones(), vocab_weight("out", types["output"], 8))
 
 
+def bench_decode_tp(hq, oracle, torch, ctx, dev, args, rank, world, barrier) -> dict | None:
+    """BASELINE config 5 on `world` GPUs: the tensor-parallel decode step (hf2q_b200/decoder_tp.py) on Llama-3-8B
+    shapes.  Every rank holds its shard of every tensor (random block bytes with small scales: throughput does not
+    depend on the values); the 8-bit KV caches of the rank's heads are filled with random codes for 8192
+    positions instead of running a prefill; 100 greedy tokens from one captured CUDA graph per rank."""
+    import torch.distributed as dist
+    from hf2q_b200 import decoder as D, decoder_tp as TP
+    cfg = D.LlamaConfig()
+    if cfg.n_kv_heads % world or cfg.vocab % world or cfg.ffn % world:
+        return None
+    types = D.q4_k_m_types(cfg)
+    n_ctx, n_new = 8192, 100
+    hl, kl, fl, vl = cfg.n_heads // world, cfg.n_kv_heads // world, cfg.ffn // world, cfg.vocab // world
+
+    def weight(t, n, k):
+        return hq.load_quant_weight(ctx, _random_weight(torch, oracle, dev, t, n, k, exp_mask=0x0F), t, n, k)
+
+    ones = lambda: torch.ones(cfg.hidden, dtype=torch.float32, device=dev)
+    layers = []
+    for i in range(cfg.n_layers):
+        p = f"blk.{i}."
+        tq, tv = types[p + "attn_q"], types[p + "attn_v"]
+        same = tq == tv
+        layers.append(TP.TpLayerWeights(
+            ones(), weight(tq, (hl + kl + (kl if same else 0)) * cfg.head_dim, cfg.hidden), None if same else weight(tv, kl * cfg.head_dim, cfg.hidden),
+            weight(types[p + "attn_output"], cfg.hidden, hl * cfg.head_dim), ones(),
+            weight(types[p + "ffn_gate"], fl, cfg.hidden), weight(types[p + "ffn_up"], fl, cfg.hidden),
+            weight(types[p + "ffn_down"], cfg.hidden, fl) if TP.column_shard_ok(types[p + "ffn_down"], cfg.ffn, world)
+            else weight(types[p + "ffn_down"], cfg.hidden // world, cfg.ffn)))
+    embd = hq.load_quant_weight(ctx, _random_weight(torch, oracle, dev, types["token_embd"], 16384, cfg.hidden, exp_mask=0x0F).repeat(8)[
+        : cfg.vocab * oracle.row_bytes(types["token_embd"], cfg.hidden)].contiguous(), types["token_embd"], cfg.vocab, cfg.hidden)
+    w = TP.TpModelWeights(embd, layers, ones(), weight(types["output"], vl, cfg.hidden))
+    dec = TP.TensorParallelDecoder(ctx, cfg, w)
+    g = torch.Generator(device=dev).manual_seed(rank)
+    for kc, ks, vc, vs in dec.kv_bufs:
+        kc[:, :n_ctx].copy_(torch.randint(-127, 128, kc[:, :n_ctx].shape, dtype=torch.int8, device=dev, generator=g))
+        vc[:, :n_ctx].copy_(torch.randint(-127, 128, vc[:, :n_ctx].shape, dtype=torch.int8, device=dev, generator=g))
+        ks[:, :n_ctx].fill_(0.01)
+        vs[:, :n_ctx].fill_(0.01)
+    dec.pos.fill_(n_ctx)
+    dec.tok.fill_(1)
+    dec.generate(6, use_graph=True, collect=False)              # captures the step and warms the replay
+    dec.pos.fill_(n_ctx)
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    dec.generate(n_new, use_graph=True, collect=False)
+    e1.record()
+    barrier()
+    ctx.check_status()
+    tt = torch.tensor([e0.elapsed_time(e1)], device=dev)
+    dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+    dt = float(tt.item()) * 1e-3
+    finite = bool(torch.isfinite(dec.logits).all().item())
+    wbytes = dec.weight_bytes_per_token()
+    line = {"metric": "decode tok/s", "value": round(n_new / dt, 1), "unit": "tok/s", "higher_is_better": True,
+            "ms_per_token": round(1e3 * dt / n_new, 4),
+            "config": {"workload": f"Llama-3-8B shapes, Q4_K_M type map, tensor-parallel over {world} GPUs: QKV / gate / up sharded by rows, O / down by "
+                                   f"their contraction dimension with the partial sums exchanged inside the products' gather epilogue and added in rank order "
+                                   f"(Q6_K down tensors, whose column shards would lose the 16-byte row alignment, by rows with their input gathered first), "
+                                   f"output head sharded by vocabulary; "
+                                   f"{n_new} greedy tokens at {n_ctx} cached positions (caches filled with random codes, no prefill)",
+                       "launch_mode": "one CUDA graph of the decode step per rank; no NCCL call and no host synchronisation inside a step"},
+            "weight_bytes_per_token_per_rank": wbytes, "launches_per_token_per_rank": dec.launches_per_token, "logits_finite": finite}
+    dec.close()
+    return line
+
+
 def bench_decode(hq, oracle, torch, ctx, dev, args) -> dict:
     """BASELINE config 5: random-init decoder forward on Llama-3-8B shapes, Q4_K_M weights, 8-bit KV cache
     with room for 32K positions; greedy decode of 200 tokens after an 8192-token prefill of uniform-random
@@ -967,6 +1035,11 @@ def main() -> None:
                              "timing": f"CUDA events over {reps} eager calls, max over ranks"}}
         comm.close()
 
+    # ---- tensor-parallel decode (several GPUs): BASELINE config 5 with every tensor sharded ----
+    decode_tp = None
+    if world > 1 and not args.no_decode and not args.no_strong:
+        decode_tp = bench_decode_tp(hq, oracle, torch, ctx, dev, args, rank, world, barrier)
+
     # ---- e2e leg: host buffers through the public call ----
     pin_x = {key: torch.from_numpy(b.view(np.int16).copy()).pin_memory() for key, b in xbits.items()}
     np_x = {key: t.numpy() for key, t in pin_x.items()}
@@ -1097,6 +1170,8 @@ def main() -> None:
         line["strong"] = strong
     if moe_ep is not None:
         line.setdefault("secondary", {})["config4_moe_expert_parallel"] = moe_ep
+    if decode_tp is not None:
+        line.setdefault("secondary", {})["config5_decode_tensor_parallel"] = decode_tp
     if cpu_baseline is not None:
         line["cpu_baseline"] = cpu_baseline
     if secondary is not None:

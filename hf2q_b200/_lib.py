@@ -58,7 +58,7 @@ SIGNATURES = {
     "hf2q_cuda_ipc_close": (i32, [vp, vp]),
     "hf2q_cuda_qmatmul_gather": (i32, [vp, vp, vp, u32, vp, vp, u32, u32, u32, u32]),
     "hf2q_cuda_gather_wait": (i32, [vp, vp, vp]),
-    "hf2q_cuda_gather_sum": (i32, [vp, vp, vp, vp, u32]),
+    "hf2q_cuda_gather_sum": (i32, [vp, vp, vp, vp, u32, u32]),
     "hf2q_cuda_gather_supported": (i32, [vp, vp, u32, u32, u32, u32, u32]),
     "hf2q_cuda_gather_copy": (i32, [vp, vp, vp, vp, u32]),
     "hf2q_cuda_set_wait_limit": (i32, [vp, u64]),

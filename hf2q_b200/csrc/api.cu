@@ -794,16 +794,16 @@ HF2Q_API int32_t hf2q_cuda_gather_copy(hf2q_ctx* ctx, void* stream, const hf2q_g
     return HF2Q_OK;
 }
 
-HF2Q_API int32_t hf2q_cuda_gather_sum(hf2q_ctx* ctx, void* stream, const hf2q_gather* g, float* x, uint32_t n) {
+HF2Q_API int32_t hf2q_cuda_gather_sum(hf2q_ctx* ctx, void* stream, const hf2q_gather* g, float* x, uint32_t n, uint32_t n_parts) {
     if (!ctx || !g) return HF2Q_ERR_INVALID_ARGUMENT;
-    if (!x || n == 0) return fail(ctx, HF2Q_ERR_INVALID_ARGUMENT, "gather_sum: null or empty x");
+    if (!x || n == 0 || n_parts == 0) return fail(ctx, HF2Q_ERR_INVALID_ARGUMENT, "gather_sum: null or empty x");
     if (g->n_ranks < 1 || g->n_ranks > 8 || g->rank >= g->n_ranks || !g->flags[g->rank] || !g->y_all[g->rank])
         return fail(ctx, HF2Q_ERR_INVALID_ARGUMENT, "gather_sum: rank %u of %u", g->rank, g->n_ranks);
-    if (static_cast<uint64_t>(n) * g->n_ranks > g->n_total)
-        return fail(ctx, HF2Q_ERR_INVALID_ARGUMENT, "gather_sum: %u ranks x %u values exceed the buffer's %u columns", g->n_ranks, n, g->n_total);
+    if (static_cast<uint64_t>(n) * n_parts > g->n_total)
+        return fail(ctx, HF2Q_ERR_INVALID_ARGUMENT, "gather_sum: %u parts x %u values exceed the buffer's %u columns", n_parts, n, g->n_total);
     DeviceGuard dg(ctx->device);
     const cudaError_t e = launch_gather_sum(static_cast<const uint32_t*>(g->flags[g->rank]), g->n_ranks, g->rank, ctx->wait_limit, ctx->status,
-                                            static_cast<const float*>(g->y_all[g->rank]), n, x, n, static_cast<cudaStream_t>(stream));
+                                            static_cast<const float*>(g->y_all[g->rank]), n, n_parts, x, n, static_cast<cudaStream_t>(stream));
     if (e != cudaSuccess) return cuda_fail(ctx, e, "gather_sum launch");
     ctx->launches += 1;
     return HF2Q_OK;

@@ -1243,19 +1243,20 @@ cudaError_t launch_gather_wait(const uint32_t* flag, uint32_t n_ranks, uint32_t 
 }
 
 namespace {
-// x[i] += sum over ranks r (in rank order: the same bits on every rank) of parts[r * stride + i], after the
+// x[i] += sum over the n_parts parts r (in order: the same bits on every rank) of parts[r * stride + i], after the
 // columns of every rank have arrived here.  The gathered buffer holds one full-length PARTIAL product per rank
 // (a product whose contraction dimension is sharded): this is the all-reduce of a column-sharded projection,
 // built from the all-gather in the producing product's epilogue and a local sum.
 __global__ void __launch_bounds__(256) gather_sum_kernel(const uint32_t* flag, uint32_t n_ranks, uint32_t rank, long long limit, uint32_t* status,
-                                                         const float* __restrict__ parts, uint32_t stride, float* __restrict__ x, uint32_t n) {
+                                                         const float* __restrict__ parts, uint32_t stride, uint32_t n_parts, float* __restrict__ x,
+                                                         uint32_t n) {
     asm volatile("griddepcontrol.wait;" ::: "memory");
     if (threadIdx.x < n_ranks && threadIdx.x != rank) gather_wait_source(flag, threadIdx.x, limit, status);
     __syncthreads();
     const uint32_t i = blockIdx.x * 256 + threadIdx.x;
     if (i >= n) return;
     float acc = x[i];
-    for (uint32_t r = 0; r < n_ranks; ++r) acc += __ldcg(parts + static_cast<size_t>(r) * stride + i);
+    for (uint32_t r = 0; r < n_parts; ++r) acc += __ldcg(parts + static_cast<size_t>(r) * stride + i);
     x[i] = acc;
 }
 }  // namespace
@@ -1303,8 +1304,8 @@ cudaError_t launch_gather_copy(const float* src, const GatherArgs& g, uint32_t n
 }
 
 cudaError_t launch_gather_sum(const uint32_t* flag, uint32_t n_ranks, uint32_t rank, long long limit, uint32_t* status, const float* parts,
-                              uint32_t stride, float* x, uint32_t n, cudaStream_t st) {
-    gather_sum_kernel<<<(n + 255) / 256, 256, 0, st>>>(flag, n_ranks, rank, limit, status, parts, stride, x, n);
+                              uint32_t stride, uint32_t n_parts, float* x, uint32_t n, cudaStream_t st) {
+    gather_sum_kernel<<<(n + 255) / 256, 256, 0, st>>>(flag, n_ranks, rank, limit, status, parts, stride, n_parts, x, n);
     return cudaGetLastError();
 }
 

@@ -104,9 +104,9 @@ uint32_t gemv_mma_grid_x(uint32_t n, uint32_t k, const DeviceInfo& dev);
 cudaError_t launch_gather_wait(const uint32_t* flag, uint32_t n_ranks, uint32_t rank, long long limit, uint32_t* status, cudaStream_t st);
 // src[0 .. n) -> columns [col0, col0 + n) of row 0 of every rank's buffer + the arrival signalling of the fused gather
 cudaError_t launch_gather_copy(const float* src, const GatherArgs& g, uint32_t n, const uint32_t* n_each, cudaStream_t st);
-// waits like launch_gather_wait, then x[i] += sum_r parts[r * stride + i], i < n (rank order)
+// waits like launch_gather_wait, then x[i] += sum_{r < n_parts} parts[r * stride + i], i < n (in order)
 cudaError_t launch_gather_sum(const uint32_t* flag, uint32_t n_ranks, uint32_t rank, long long limit, uint32_t* status, const float* parts,
-                              uint32_t stride, float* x, uint32_t n, cudaStream_t st);
+                              uint32_t stride, uint32_t n_parts, float* x, uint32_t n, cudaStream_t st);
 
 // mlx-affine arrays (u32 codes [groups][4], f32 scales, f32 biases) -> 24-byte blocks (k0_dequant.cu)
 cudaError_t launch_affine_pack(const uint32_t* codes, const float* scales, const float* biases, uint64_t n_groups, void* out, int sm_count,

@@ -38,7 +38,7 @@ class TpLayerWeights:
     ffn_norm: torch.Tensor
     gate: ops.QuantWeight              # [ffn / world, hidden]
     up: ops.QuantWeight
-    down: ops.QuantWeight              # [hidden, ffn / world]
+    down: ops.QuantWeight              # [hidden, ffn / world], or [hidden / world, ffn] where a column shard would be unaligned
 
 
 @dataclass
@@ -49,14 +49,22 @@ class TpModelWeights:
     output: ops.QuantWeight            # [vocab / world, hidden]
 
 
+def column_shard_ok(ggml_type: int, k: int, world: int) -> bool:
+    """Whether a 1 / world column shard of a [n, k] tensor keeps 16-byte aligned rows of whole 256-element blocks
+    (what the gathering mat-vec needs).  Q6_K rows (210 bytes per block) are aligned only in multiples of 8 blocks;
+    a tensor that fails this is sharded by rows instead, with its input gathered first."""
+    kl = k // world
+    return k % world == 0 and kl % 256 == 0 and ops.row_bytes(ggml_type, kl) % 16 == 0
+
+
 def shard_raw(name: str, raw: np.ndarray, ggml_type: int, n: int, k: int, cfg: LlamaConfig, rank: int, world: int):
     """Rank `rank`'s part of one GGUF tensor of the model as (bytes, rows, cols): a row range for attn_q / attn_k /
-    attn_v / ffn_gate / ffn_up / output, a column range (whole blocks of every row) for attn_output / ffn_down,
-    everything for token_embd."""
+    attn_v / ffn_gate / ffn_up / output, a column range (whole blocks of every row) for attn_output / ffn_down where
+    ``column_shard_ok`` (else a row range), everything for token_embd."""
     rb = ops.row_bytes(ggml_type, k)
     rows = np.ascontiguousarray(raw, dtype=np.uint8).reshape(n, rb)
     base = name.split(".")[-1]
-    if base in ("attn_output", "ffn_down"):
+    if base in ("attn_output", "ffn_down") and column_shard_ok(ggml_type, k, world):
         c0, c1 = rank * k // world, (rank + 1) * k // world
         b0, b1 = ops.row_bytes(ggml_type, c0) if c0 else 0, ops.row_bytes(ggml_type, c1)
         return np.ascontiguousarray(rows[:, b0:b1]).reshape(-1), n, c1 - c0
@@ -102,6 +110,7 @@ class TensorParallelDecoder:
         # the partial sums of O and down: world x hidden values per product; the logits: vocab values
         self.partials = GatherGroup(ctx, 1, W * c.hidden, group=group)
         self.logit_group = GatherGroup(ctx, 1, c.vocab, group=group)
+        self.wide = GatherGroup(ctx, 1, max(c.ffn, c.q_rows, c.hidden), group=group)      # gathered inputs / outputs of row-sharded O / down
         self._graph = None
         for lw in weights.layers:
             for w_ in (lw.wqk, lw.wv, lw.gate):
@@ -110,6 +119,20 @@ class TensorParallelDecoder:
 
     def _s(self):
         return self.ctx._stream()
+
+    def _project_sum(self, inp: torch.Tensor, weight: ops.QuantWeight, k_full: int) -> None:
+        """self.x += (full input) . W^T for a projection whose input `inp` is this rank's slice of a length-k_full vector.
+        Column-sharded weight (cols == len(inp)): partial products, exchanged and summed.  Row-sharded weight
+        (cols == k_full; used where a column shard would break the 16-byte row alignment): the input slices are
+        gathered first, the product's own epilogue gathers its rows, and the gathered result is added."""
+        c = self.cfg
+        if weight.cols != k_full:
+            return self._partial_sum(inp, weight)
+        nl = inp.numel()
+        self.wide.copy(inp, self.rank * nl)                                   # everyone's slice -> the full input on every rank
+        xin = self.wide.output(1)[:, :k_full]
+        self.wide.matmul(xin, weight, 1, self.rank * weight.rows, wait_previous=True, n_rows=[weight.rows] * self.world)
+        self.wide.sum_into(self.x, c.hidden, n_parts=1)
 
     def _partial_sum(self, inp: torch.Tensor, weight: ops.QuantWeight) -> None:
         """self.x += all-reduce(inp . weight^T): the ranks' partial products side by side in every rank's buffer
@@ -133,9 +156,9 @@ class TensorParallelDecoder:
             ctx._check(lib.hf2q_cuda_attn_decode_fused(ctx._h, self._s(), self.qkv.data_ptr(), self.heads_l, c.rope_theta, C.byref(self.kv[i]),
                                                        self.pos.data_ptr(), self.att.data_ptr(), ops.DT_F32, self.att_scratch.data_ptr(),
                                                        self.att_scratch.numel()))
-            self._partial_sum(self.att, lw.wo)                                              # x += O(att), summed over the ranks
+            self._project_sum(self.att, lw.wo, c.q_rows)                                    # x += O(att), summed over the ranks
             ops.quantized_matmul_swiglu(ctx, self.x, lw.gate, lw.up, self.act, 1, norm_weight=lw.ffn_norm, norm_eps=c.rms_eps)
-            self._partial_sum(self.act, lw.down)                                            # x += down(act)
+            self._project_sum(self.act, lw.down, c.ffn)                                     # x += down(act)
         ctx._check(lib.hf2q_cuda_rms_norm(ctx._h, self._s(), self.x.data_ptr(), None, self.w.out_norm.data_ptr(), c.rms_eps, self.xn.data_ptr(),
                                           ops.DT_F32, 1, c.hidden))
         self.logit_group.matmul(self.xn, self.w.output, 1, self.rank * self.vocab_l, n_rows=[self.vocab_l] * self.world)
@@ -187,3 +210,4 @@ class TensorParallelDecoder:
     def close(self) -> None:
         self.partials.close()
         self.logit_group.close()
+        self.wide.close()

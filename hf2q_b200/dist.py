@@ -297,11 +297,13 @@ class GatherGroup:
         self.ctx._check(self.ctx._lib.hf2q_cuda_gather_copy(self.ctx._h, self.ctx._stream(), C.byref(g), src.data_ptr(), n))
         self._next ^= 1
 
-    def sum_into(self, x: torch.Tensor, n: int) -> None:
-        """x[:n] += the sum over the ranks of the most recent product's n-value partials (columns r * n .. of its
-        buffer), after waiting for all of them; rank order, so every rank gets the same bits."""
-        g = self._struct(0, False, self._next ^ 1, [n] * self.world)
-        self.ctx._check(self.ctx._lib.hf2q_cuda_gather_sum(self.ctx._h, self.ctx._stream(), C.byref(g), x.data_ptr(), n))
+    def sum_into(self, x: torch.Tensor, n: int, n_parts: int | None = None) -> None:
+        """x[:n] += the sum of the most recent product's n-value parts (columns r * n .. of its buffer, r < n_parts;
+        default one partial per rank), after waiting for every rank's columns; rank order, so every rank gets the
+        same bits.  ``n_parts=1`` adds a gathered full-length result."""
+        g = self._struct(0, False, self._next ^ 1, [1] * self.world)
+        self.ctx._check(self.ctx._lib.hf2q_cuda_gather_sum(self.ctx._h, self.ctx._stream(), C.byref(g), x.data_ptr(), n,
+                                                           self.world if n_parts is None else n_parts))
 
     def wait(self) -> None:
         if self.world > 1:

@@ -424,9 +424,11 @@ HF2Q_API int32_t hf2q_cuda_gather_copy(hf2q_ctx* ctx, void* stream, const hf2q_g
  * tensor-parallel decoder: every rank multiplies its columns of the weight with its slice of the activations):
  * each rank runs hf2q_cuda_qmatmul_gather with m = 1, n = the full output length, col0 = rank * n,
  * n_rows[r] = n and n_total >= n_ranks * n, so that the gathered row holds one partial product per rank; this
- * call then waits (bounded, like hf2q_cuda_gather_wait) until every rank's partial has arrived in `g`'s buffer
- * of THIS rank and adds them to x in rank order:  x[i] += sum_r y[r * n + i].  Same bits on every rank. */
-HF2Q_API int32_t hf2q_cuda_gather_sum(hf2q_ctx* ctx, void* stream, const hf2q_gather* g, float* x, uint32_t n);
+ * call then waits (bounded, like hf2q_cuda_gather_wait) until every rank's columns have arrived in `g`'s buffer
+ * of THIS rank and adds n_parts = n_ranks partials to x in rank order:  x[i] += sum_{r < n_parts} y[r * n + i].
+ * Same bits on every rank.  n_parts = 1 adds a gathered full-length result (a row-sharded projection). */
+HF2Q_API int32_t hf2q_cuda_gather_sum(hf2q_ctx* ctx, void* stream, const hf2q_gather* g, float* x, uint32_t n,
+                                      uint32_t n_parts);
 
 /* Upper bound, in GPU clock ticks, of the device-side waits for other GPUs (the fused gather's
  * arrival counters).  A context setting: set once after creation, never on the launch path.  The

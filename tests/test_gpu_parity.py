@@ -453,8 +453,9 @@ def test_gather_entry_single_rank(gpu_ctx):
     import ctypes as C
     from hf2q_b200.dist import _Gather
     lib, h = gpu_ctx._lib, gpu_ctx._h
-    t = oracle.Q6_K
-    for (n, k, m) in ((48, 2048, 3), (32, 14336, 8)):
+    # (Q4_K with 1, 2 and 4 blocks per row: the stacked row groups of short rows -- the O shard of a tensor-parallel decoder)
+    for (t, n, k, m) in ((oracle.Q6_K, 48, 2048, 3), (oracle.Q6_K, 32, 14336, 8), (oracle.Q4_K, 200, 512, 2), (oracle.Q4_K, 72, 256, 1),
+                         (oracle.Q4_K, 130, 1024, 4)):
         raw = make_quant_weight(t, n, k, seed=n + k)
         w = hq.load_quant_weight(gpu_ctx, raw, t, n, k)
         n_total, col0 = n + 40, 24
@@ -476,11 +477,25 @@ def test_gather_entry_single_rank(gpu_ctx):
         y = torch.as_tensor(_DevView(ybuf.value, (m, n_total), "<f4"), device="cuda").cpu().numpy()
         assert rel_l2(y[:, col0:col0 + n], _ref(t, raw, xs, n, k)) < 2e-5
         assert not y[:, :col0].any() and not y[:, col0 + n:].any()          # nothing outside the rank's columns
+        if m == 1:
+            # the exchange without a product, and the sum of the gathered parts into a vector
+            src = torch.arange(16, dtype=torch.float32, device="cuda")
+            g.col0, g.n_rows[0] = 4, 16
+            gpu_ctx._check(lib.hf2q_cuda_gather_copy(h, gpu_ctx._stream(), C.byref(g), src.data_ptr(), 16))
+            acc = torch.ones(8, device="cuda")
+            gpu_ctx._check(lib.hf2q_cuda_gather_sum(h, gpu_ctx._stream(), C.byref(g), acc.data_ptr(), 8, 2))
+            gpu_ctx.check_status()
+            y2 = torch.as_tensor(_DevView(ybuf.value, (1, n_total), "<f4"), device="cuda").cpu().numpy()[0]
+            assert np.array_equal(y2[4:20], np.arange(16, dtype=np.float32))
+            assert np.array_equal(acc.cpu().numpy(), 1.0 + y2[0:8] + y2[8:16])
+            assert lib.hf2q_cuda_gather_supported(h, w.ptr, 1, n, k, t, 0) == 1
         lib.hf2q_cuda_free(h, ybuf.value)
         lib.hf2q_cuda_free(h, fbuf.value)
     # argument checks
     g = _Gather()
     assert lib.hf2q_cuda_qmatmul_gather(h, None, xd.data_ptr(), hq.ops.DT_BF16, w.ptr, C.byref(g), 1, n, k, t) == _lib.ERR_INVALID_ARGUMENT
+    odd = hq.load_quant_weight(gpu_ctx, make_quant_weight(oracle.Q6_K, 16, 1792, seed=1), oracle.Q6_K, 16, 1792)      # 1470-byte rows
+    assert lib.hf2q_cuda_gather_supported(h, odd.ptr, 1, 16, 1792, oracle.Q6_K, 0) == 0
 
 
 @pytest.mark.parametrize("t", TYPES)
