@@ -1250,6 +1250,7 @@ namespace {
 __global__ void __launch_bounds__(256) gather_sum_kernel(const uint32_t* flag, uint32_t n_ranks, uint32_t rank, long long limit, uint32_t* status,
                                                          const float* __restrict__ parts, uint32_t stride, uint32_t n_parts, float* __restrict__ x,
                                                          uint32_t n) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");      // the next kernel may start its own prologue
     asm volatile("griddepcontrol.wait;" ::: "memory");
     if (threadIdx.x < n_ranks && threadIdx.x != rank) gather_wait_source(flag, threadIdx.x, limit, status);
     __syncthreads();
@@ -1274,6 +1275,7 @@ struct GatherCopyParams {
     uint32_t n_ranks, rank, col0, n;
 };
 __global__ void __launch_bounds__(256) gather_copy_kernel(const float* __restrict__ src, const GatherCopyParams p) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");      // the next kernel may start its own prologue
     asm volatile("griddepcontrol.wait;" ::: "memory");
     for (uint32_t i = blockIdx.x * GCOPY_PER_CTA + threadIdx.x; i < min((blockIdx.x + 1) * GCOPY_PER_CTA, p.n); i += 256) {
         const float v = src[i];
@@ -1299,14 +1301,30 @@ cudaError_t launch_gather_copy(const float* src, const GatherArgs& g, uint32_t n
         p.peer_ctas[r] = (n_each[r] + GCOPY_PER_CTA - 1) / GCOPY_PER_CTA;
     }
     p.n_ranks = g.n_ranks; p.rank = g.rank; p.col0 = g.col0; p.n = n;
-    gather_copy_kernel<<<(n + GCOPY_PER_CTA - 1) / GCOPY_PER_CTA, 256, 0, st>>>(src, p);
-    return cudaGetLastError();
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3((n + GCOPY_PER_CTA - 1) / GCOPY_PER_CTA);
+    cfg.blockDim = dim3(256);
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, gather_copy_kernel, src, p);
 }
 
 cudaError_t launch_gather_sum(const uint32_t* flag, uint32_t n_ranks, uint32_t rank, long long limit, uint32_t* status, const float* parts,
                               uint32_t stride, uint32_t n_parts, float* x, uint32_t n, cudaStream_t st) {
-    gather_sum_kernel<<<(n + 255) / 256, 256, 0, st>>>(flag, n_ranks, rank, limit, status, parts, stride, n_parts, x, n);
-    return cudaGetLastError();
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3((n + 255) / 256);
+    cfg.blockDim = dim3(256);
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, gather_sum_kernel, flag, n_ranks, rank, limit, status, parts, stride, n_parts, x, n);
 }
 
 uint32_t gemv_mma_grid_x(uint32_t n, uint32_t k, const DeviceInfo& dev) {
