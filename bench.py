@@ -71,15 +71,15 @@ def measured_hbm_peak() -> tuple[float, str]:
     return 6650.0, "fallback"
 
 
+# DRAM bytes per algorithmic byte of gemv_mma_kernel<Q6_K>: `dram__bytes_read.sum + dram__bytes_write.sum` of the ncu
+# capture summarised in profiles/gemv_q6k_sweep.md (four m = 1 launches: 182.98 MB over 179.14 MB algorithmic).
+NCU_DRAM_BYTES_PER_ALGORITHMIC_BYTE = 1.0214
+
+
 def ncu_traffic_per_launch() -> float | None:
-    """Mean DRAM bytes per launch scaled to this sweep, from the committed ncu summary."""
-    p = ROOT / "profiles" / "gemv_q6k_traffic.json"
-    if not p.exists():
-        return None
-    try:
-        return float(json.loads(p.read_text())["dram_bytes_per_algorithmic_byte"])
-    except Exception:
-        return None
+    """DRAM bytes per algorithmic byte of the headline kernel, from the ncu capture (a constant of that capture, not
+    a measurement of this run)."""
+    return NCU_DRAM_BYTES_PER_ALGORITHMIC_BYTE
 
 
 class ClockSampler:
@@ -1117,7 +1117,7 @@ def main() -> None:
         "frac": round(per_gpu / peak, 4), "peak_source": f"of {peak_kind}",
         "kernel": "gemv_mma_kernel<Q6_K>, m in {1,4,8}",
         "traffic": None if ratio is None else round(ratio * mean_launch_bytes),
-        "traffic_source": "dram bytes / algorithmic bytes of the committed ncu capture (profiles/gemv_q6k_traffic.json) x this run's mean launch",
+        "traffic_source": "dram bytes / algorithmic bytes of the ncu capture summarised in profiles/gemv_q6k_sweep.md (1.0214) x this run's mean launch",
         "algorithmic_bytes_per_launch_mean": round(mean_launch_bytes),
         "frac_of_nominal_8TBps": round(per_gpu / 8000.0, 4),
         "breakdown": breakdown,
