@@ -368,7 +368,7 @@ __device__ __forceinline__ void half_legacy(const uint8_t* p0, const uint8_t* p1
 // hi = f16(x) and lo = f16(x - hi).  Values beyond the f16 range are clamped and flagged.
 // INPLACE (bf16 input, used by the k-phase variant, whose main loop leaves no registers for loads in
 // flight): the raw rows are bulk-copied into the panel's own place and converted there.
-template <uint32_t TYPE, int CTH, int U, bool INPLACE>
+template <uint32_t TYPE, int CTH, int U, bool INPLACE, bool NORM>
 __device__ __forceinline__ void build_panel(const void* x, bool x_bf16, uint32_t nslots, uint32_t k, uint32_t xpitch,
                                          uint32_t* status, uint8_t* xh, uint8_t* sxp, uint32_t sx_slot_bytes,
                                          uint32_t xrow_idx, uint32_t k0, uint32_t klen, uint64_t* xbar, uint32_t xparity,
@@ -475,7 +475,7 @@ __device__ __forceinline__ void build_panel(const void* x, bool x_bf16, uint32_t
         } else {
             bf16_rounds(std::integral_constant<int, U>{}, std::integral_constant<int, 1>{});
         }
-    } else if (norm_w) {
+    } else if (NORM && norm_w) {
         // f32 input with the RMSNorm in front of the product fused in (rms_norm_rows, forward_cpu.rs:36-48:
         // x * rsqrt(mean(x^2) + eps) * weight).  The whole row is resident (k <= 8 * CTH, one chunk of eight
         // elements per thread and activation row, at most four rows): sums of squares per row across the
@@ -883,7 +883,7 @@ __global__ void __launch_bounds__((NTEAMS * TEAM + 2) * 32, 1) gemv_mma_kernel(c
                 gather_wait_source(p.g_flag[p.g_rank], ctid, p.wait_limit, p.status);
             asm volatile("bar.sync 1, %0;" ::"n"(CTH));
         }
-        build_panel<TYPE, CTH, (PHASED ? 2 : 8), PHASED>(xbase, p.x_bf16 != 0, p.nslots, p.kx, p.xpitch, p.status, xh, sxp, sx_slot_bytes, xrow_idx, k0,
+        build_panel<TYPE, CTH, (PHASED ? 2 : 8), PHASED, EXT>(xbase, p.x_bf16 != 0, p.nslots, p.kx, p.xpitch, p.status, xh, sxp, sx_slot_bytes, xrow_idx, k0,
                                min(nsp * SLICE_ELEMS, kloc - k0), xbar, pi & 1u, p.norm_w, p.norm_eps, scr);
         if (s0 == 0) cta_sync_n<(NTEAMS * TEAM + 2) * 32>();             // panel + all barrier initialisations
         else asm volatile("bar.sync 1, %0;" ::"n"(CTH));
@@ -1192,7 +1192,7 @@ cudaError_t launch_mma_t(MParams p, uint32_t slots, const DeviceInfo& dev, cudaS
     if (phased && p.swiglu) return cudaErrorInvalidConfiguration;       // the gate sums cannot wait across phases
     // the fused RMSNorm needs the whole f32 row in one panel, one chunk of eight elements per consumer thread
     if (p.norm_w && (phased || p.x_bf16 || p.ids || p.k > 8u * 2 * TEAM * 32 || p.nslots > 8)) return cudaErrorInvalidConfiguration;
-    const bool ext = p.g_nranks != 0 || p.w2 != nullptr;
+    const bool ext = p.g_nranks != 0 || p.w2 != nullptr || p.norm_w != nullptr;      // (the fused RMSNorm is compiled into the EXT variants only)
     if (p.sub_groups > 1)                                                                          // one short slice per row
         return ext ? launch_mma_tt<TYPE, 2, false, true, true>(p, slots, pl, dev, st) : launch_mma_tt<TYPE, 2, false, true, false>(p, slots, pl, dev, st);
     if (phased) {
