@@ -72,8 +72,8 @@ def measured_hbm_peak() -> tuple[float, str]:
 
 
 # DRAM bytes per algorithmic byte of gemv_mma_kernel<Q6_K>: `dram__bytes_read.sum + dram__bytes_write.sum` of the ncu
-# capture summarised in profiles/gemv_q6k_sweep.md (four m = 1 launches: 182.98 MB over 179.14 MB algorithmic).
-NCU_DRAM_BYTES_PER_ALGORITHMIC_BYTE = 1.0214
+# capture summarised in profiles/gemv_q6k_sweep.md (four m = 1 launches: 183.27 MB over 179.14 MB algorithmic).
+NCU_DRAM_BYTES_PER_ALGORITHMIC_BYTE = 1.0231
 
 
 def ncu_traffic_per_launch() -> float | None:
@@ -1117,7 +1117,7 @@ def main() -> None:
         "frac": round(per_gpu / peak, 4), "peak_source": f"of {peak_kind}",
         "kernel": "gemv_mma_kernel<Q6_K>, m in {1,4,8}",
         "traffic": None if ratio is None else round(ratio * mean_launch_bytes),
-        "traffic_source": "dram bytes / algorithmic bytes of the ncu capture summarised in profiles/gemv_q6k_sweep.md (1.0214) x this run's mean launch",
+        "traffic_source": "dram bytes / algorithmic bytes of the ncu capture summarised in profiles/gemv_q6k_sweep.md (1.0231) x this run's mean launch",
         "algorithmic_bytes_per_launch_mean": round(mean_launch_bytes),
         "frac_of_nominal_8TBps": round(per_gpu / 8000.0, 4),
         "breakdown": breakdown,

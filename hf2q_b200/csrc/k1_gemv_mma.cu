@@ -470,8 +470,8 @@ __device__ __forceinline__ void build_panel(const void* x, bool x_bf16, uint32_t
     } else if (x_bf16) {
         if constexpr (U >= 8) {
             if (k8 <= CTH) bf16_rounds(std::integral_constant<int, 8>{}, std::integral_constant<int, 1>{});
-            else if (nslots <= 2) bf16_rounds(std::integral_constant<int, 2>{}, std::integral_constant<int, 4>{});
-            else bf16_rounds(std::integral_constant<int, 4>{}, std::integral_constant<int, 2>{});
+            else if (NORM && nslots > 2) bf16_rounds(std::integral_constant<int, 4>{}, std::integral_constant<int, 2>{});
+            else bf16_rounds(std::integral_constant<int, 2>{}, std::integral_constant<int, 4>{});       // (the plain variants carry one long-row form only)
         } else {
             bf16_rounds(std::integral_constant<int, U>{}, std::integral_constant<int, 1>{});
         }
