@@ -153,9 +153,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
     uint64_t* x_empty = x_full + X_STAGES;
     constexpr int A_BUFS = a_bufs_of(NT, GROUPED);
     constexpr uint32_t TMEM_COLS = tmem_cols_of(NT, GROUPED);
-    uint64_t* a_full = x_empty + X_STAGES;      // [2]
-    uint64_t* a_empty = a_full + 2;
-    uint64_t* d_full = a_empty + 2;             // [1]
+    uint64_t* a_full = x_empty + X_STAGES;      // [A_BUFS][DEQ_GROUPS]: each group's half (128 K elements) of an A buffer
+    uint64_t* a_empty = a_full + 4;
+    uint64_t* d_full = a_empty + 4;             // [1]
     uint64_t* d_empty = d_full + 1;             // [1]
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(d_empty + 1);
 
@@ -175,7 +175,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
     if (threadIdx.x == 0) {
         for (int s = 0; s < RAW_STAGES; ++s) { mbar_init(&raw_full[s], 1); mbar_init(&raw_empty[s], DEQ_WARPS); }
         for (int s = 0; s < X_STAGES; ++s) { mbar_init(&x_full[s], 1); mbar_init(&x_empty[s], 1); }
-        for (int s = 0; s < 2; ++s) { mbar_init(&a_full[s], DEQ_WARPS); mbar_init(&a_empty[s], 1); }
+        for (int s = 0; s < 4; ++s) { mbar_init(&a_full[s], DEQ_WARPS / DEQ_GROUPS); mbar_init(&a_empty[s], 1); }
         mbar_init(d_full, 1);
         mbar_init(d_empty, DEQ_WARPS);
         mbar_fence_init();
@@ -228,18 +228,23 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
     } else if (warp == DEQ_WARPS + 1) {
         // ------------------------------ MMA issuer
         if (lane == 0) {
-            // instruction descriptor: D f32, A/B f16, both K-major, N = NT, M = 128
-            constexpr uint32_t IDESC = (1u << 4) | (static_cast<uint32_t>(NT >> 3) << 17) | (static_cast<uint32_t>(128 >> 4) << 24);
+            // instruction descriptor: D f32, A/B f16, both K-major, M = 128, N = the tile's token count rounded up to 16
+            // (an expert's tile is rarely full: the MMAs skip the token columns nobody reads)
+            const uint32_t n_mma = max(16u, (min(static_cast<uint32_t>(NT), tok_end - tok0) + 15u) & ~15u);
+            const uint32_t IDESC = (1u << 4) | ((n_mma >> 3) << 17) | (static_cast<uint32_t>(128 >> 4) << 24);
             bool ok = true;
             for (uint32_t tl = 0, gk = 0; tl < ntile && ok; ++tl) {
                 // the previous tile's accumulators must have been read before they are overwritten
                 if (tl) ok = mbar_wait_bounded(d_empty, (tl - 1) & 1, p.status);
                 for (uint32_t kb = 0; kb < nkb && ok; ++kb, ++gk) {
                     const uint32_t ab = gk % A_BUFS;
-                    ok = mbar_wait_bounded(&a_full[ab], (gk / A_BUFS) & 1, p.status);
-                    if (!ok) break;
-                    tc_fence_after();
                     for (uint32_t j = 0; j < KB / XK && ok; ++j) {
+                        // quarters 0, 1 come from dequantiser group 0, quarters 2, 3 from group 1
+                        if ((j & (QPG - 1)) == 0) {
+                            ok = mbar_wait_bounded(&a_full[ab * DEQ_GROUPS + j / QPG], (gk / A_BUFS) & 1, p.status);
+                            if (!ok) break;
+                            tc_fence_after();
+                        }
                         const uint32_t xi = gk * (KB / XK) + j, st = xi % X_STAGES;
                         ok = mbar_wait_bounded(&x_full[st], (xi / X_STAGES) & 1, p.status);
                         if (!ok) break;
@@ -251,9 +256,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
                             umma_ts(tmem_d, tmem_a + ab * 128 + (j * (XK / 16) + kk) * 8, bdesc + 2 * kk, IDESC,
                                     (kb | j | kk) != 0 ? 1u : 0u);
                         }
-                        tc_commit(&x_empty[st]);       // activation stage free once these MMAs retire
+                        tc_commit(&x_empty[st]);       // activation stage free once these MMAs retire,
+                        if ((j & (QPG - 1)) == QPG - 1) tc_commit(&a_empty[ab * DEQ_GROUPS + j / QPG]);   // and the group's half of A
                     }
-                    if (ok) tc_commit(&a_empty[ab]);
                 }
                 if (ok) tc_commit(d_full);
             }
@@ -265,13 +270,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
         const uint32_t lane_addr = (quad * 32u) << 16;
         // row of the raw stage this thread dequantises (DUAL: gate box rows 0..63, up box rows 64..127)
         const uint32_t src_row = DUAL ? ((lane < 16 ? 0u : 64u) + 16 * quad + (lane & 15)) : r;
+        const int n_cols = static_cast<int>(min(static_cast<uint32_t>(NT), tok_end - tok0));   // token columns in use
         bool ok = true;
         for (uint32_t tl = 0, gk = 0; tl < ntile && ok; ++tl) {
             const uint32_t row0 = (tile0 + tl) * TILE_ROWS;
             for (uint32_t kb = 0; kb < nkb; ++kb, ++gk) {
                 const uint32_t rs = gk % RAW_STAGES, ab = gk % A_BUFS;
                 if (ok) ok = mbar_wait_bounded(&raw_full[rs], (gk / RAW_STAGES) & 1, p.status);
-                if (ok && gk >= A_BUFS) ok = mbar_wait_bounded(&a_empty[ab], ((gk / A_BUFS) - 1) & 1, p.status);
+                if (ok && gk >= A_BUFS) ok = mbar_wait_bounded(&a_empty[ab * DEQ_GROUPS + grp], ((gk / A_BUFS) - 1) & 1, p.status);
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
                 tc_fence_after();
@@ -280,7 +286,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
                 tmem_wait_st();
                 tc_fence_before();
                 __syncwarp();
-                if (lane == 0) { mbar_arrive(&a_full[ab]); mbar_arrive(&raw_empty[rs]); }
+                if (lane == 0) { mbar_arrive(&a_full[ab * DEQ_GROUPS + grp]); mbar_arrive(&raw_empty[rs]); }
             }
             // epilogue of this tile
             if (ok) ok = mbar_wait_bounded(d_full, tl & 1, p.status);
@@ -295,7 +301,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
                 const bool upper = lane >= 16;
                 bool clipped = false;
 #pragma unroll 1
-                for (int c0 = 32 * static_cast<int>(grp); c0 < NT; c0 += 32 * DEQ_GROUPS) {
+                for (int c0 = 32 * static_cast<int>(grp); c0 < n_cols; c0 += 32 * DEQ_GROUPS) {
                     uint32_t v[32];
                     tmem_ld32(tmem_d + lane_addr + c0, v);
                     tmem_wait_ld();
@@ -320,7 +326,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
             } else {
             const uint32_t row = row0 + r;
 #pragma unroll 1
-            for (int c0 = 32 * static_cast<int>(grp); c0 < NT; c0 += 32 * DEQ_GROUPS) {   // the groups share the columns
+            for (int c0 = 32 * static_cast<int>(grp); c0 < n_cols; c0 += 32 * DEQ_GROUPS) {   // the groups share the columns
                 uint32_t v[32];
                 tmem_ld32(tmem_d + lane_addr + c0, v);
                 tmem_wait_ld();
