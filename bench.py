@@ -1060,7 +1060,7 @@ def main() -> None:
         def e2e_pass():
             hq.ops.quantized_matmul_host_batch(ctx, batch)
             hq.ops.host_sync(ctx)                    # the pass's results are in pinned host memory from here on
-        e2e_api = ("hf2q_cuda_qmatmul_host_batch: one call queues the pass's products (each: pinned host x -> device, kernel, y -> pinned host), "
+        e2e_api = ("hf2q_cuda_qmatmul_host_batch: one call queues the pass's products (each: pinned host x -> device, kernel, y -> pinned host; the library replays the unchanged batch as one CUDA graph), "
                    "hf2q_cuda_host_sync once per pass")
         d2h = args.copies * sum(4 * m * n for n, _ in SHAPES for m in TOKENS)
     else:

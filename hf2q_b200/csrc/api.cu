@@ -52,6 +52,11 @@ struct hf2q_ctx {
     std::vector<cudaEvent_t> b_loaded, b_computed;
     cudaEvent_t b_all_computed = nullptr, b_all_drained = nullptr;
     bool b_used = false;
+    // a batch that comes a second time unchanged (same items, same staging) is captured into a CUDA graph and replayed
+    uint64_t b_last_key = 0, b_graph_key = 0, b_nograph_key = 0;
+    cudaGraphExec_t b_graph = nullptr;
+    uint64_t b_graph_launches = 0;
+    cudaEvent_t b_fork = nullptr, b_join_in = nullptr, b_join_out = nullptr;
     char err[512] = {0};
 };
 
@@ -223,6 +228,10 @@ HF2Q_API int32_t hf2q_cuda_ctx_destroy(hf2q_ctx* ctx) {
     for (cudaEvent_t ev : ctx->b_computed) cudaEventDestroy(ev);
     if (ctx->b_all_computed) cudaEventDestroy(ctx->b_all_computed);
     if (ctx->b_all_drained) cudaEventDestroy(ctx->b_all_drained);
+    if (ctx->b_graph) cudaGraphExecDestroy(ctx->b_graph);
+    if (ctx->b_fork) cudaEventDestroy(ctx->b_fork);
+    if (ctx->b_join_in) cudaEventDestroy(ctx->b_join_in);
+    if (ctx->b_join_out) cudaEventDestroy(ctx->b_join_out);
     if (ctx->pin_x) cudaFreeHost(ctx->pin_x);
     if (ctx->pin_y) cudaFreeHost(ctx->pin_y);
     if (ctx->host_stream) cudaStreamDestroy(ctx->host_stream);
@@ -897,13 +906,108 @@ HF2Q_API int32_t hf2q_cuda_qmatmul_host_async(hf2q_ctx* ctx, const void* x_host,
 
 // Many host-buffer products in one call: the copies-in run ahead on their own stream, the kernels run back to back
 // on one stream (so consecutive mat-vecs keep their programmatic-dependent-launch overlap), the copies-out follow
-// group by group on a third stream.  One event pair per group of 8 products instead of three event edges per product.
+// group by group on a third stream.  One event pair per group of 4 products instead of three event edges per product
+// (small groups: the copies-out of the last group are the tail of the call).
+// A decode loop hands in the same batch again and again (same host buffers, same weights): the second time an
+// unchanged batch arrives, the three streams' work is captured into one CUDA graph, and from then on the call is one
+// graph launch.  Anything that changes (an item, a staging buffer that grew) falls back to plain enqueueing.
+namespace {
+constexpr uint32_t BATCH_GROUP = 4;
+
+uint64_t batch_key(const hf2q_ctx* ctx, const hf2q_host_product* items, uint32_t n_items) {
+    uint64_t h = 1469598103934665603ull;
+    auto mix = [&](const void* p, size_t n) {
+        const unsigned char* b = static_cast<const unsigned char*>(p);
+        for (size_t i = 0; i < n; ++i) { h ^= b[i]; h *= 1099511628211ull; }
+    };
+    for (uint32_t i = 0; i < n_items; ++i) {       // field by field: padding bytes of the struct are not data
+        const hf2q_host_product& it = items[i];
+        mix(&it.x_host, sizeof it.x_host); mix(&it.w_dev, sizeof it.w_dev); mix(&it.y_host, sizeof it.y_host);
+        mix(&it.m, sizeof it.m); mix(&it.n, sizeof it.n); mix(&it.k, sizeof it.k);
+        mix(&it.ggml_type, sizeof it.ggml_type); mix(&it.x_dtype, sizeof it.x_dtype);
+    }
+    mix(&ctx->bx, sizeof ctx->bx); mix(&ctx->by, sizeof ctx->by); mix(&ctx->ws, sizeof ctx->ws);
+    return h ? h : 1;
+}
+
+// Queues the batch on the three streams.  Returns HF2Q_OK or the first error (already recorded in the context).
+int32_t batch_enqueue(hf2q_ctx* ctx, const hf2q_host_product* items, uint32_t n_items, const std::vector<size_t>& xo,
+                      const std::vector<size_t>& yo) {
+    cudaError_t e = cudaSuccess;
+    uint8_t* bx = static_cast<uint8_t*>(ctx->bx);
+    uint8_t* by = static_cast<uint8_t*>(ctx->by);
+    const uint32_t n_groups = (n_items + BATCH_GROUP - 1) / BATCH_GROUP;
+    for (uint32_t g = 0; g < n_groups; ++g) {
+        const uint32_t i0 = g * BATCH_GROUP, i1 = i0 + BATCH_GROUP < n_items ? i0 + BATCH_GROUP : n_items;
+        for (uint32_t i = i0; i < i1 && e == cudaSuccess; ++i)
+            e = cudaMemcpyAsync(bx + xo[i], items[i].x_host, static_cast<size_t>(items[i].m) * items[i].k * dtype_size(items[i].x_dtype),
+                                cudaMemcpyHostToDevice, ctx->in_stream);
+        if (e == cudaSuccess) e = cudaEventRecord(ctx->b_loaded[g], ctx->in_stream);
+        if (e == cudaSuccess) e = cudaStreamWaitEvent(ctx->host_stream, ctx->b_loaded[g], 0);
+        if (e != cudaSuccess) return cuda_fail(ctx, e, "qmatmul_host_batch: copy-in");
+        for (uint32_t i = i0; i < i1; ++i) {
+            const hf2q_host_product& it = items[i];
+            if (it.m == 0) continue;
+            const int32_t rc = hf2q_cuda_qmatmul(ctx, ctx->host_stream, bx + xo[i], it.x_dtype, it.w_dev, reinterpret_cast<float*>(by + yo[i]), it.m,
+                                                 it.n, it.k, it.ggml_type, ctx->ws, ctx->ws_bytes);
+            if (rc) return rc;
+        }
+        e = cudaEventRecord(ctx->b_computed[g], ctx->host_stream);
+        if (e == cudaSuccess) e = cudaStreamWaitEvent(ctx->out_stream, ctx->b_computed[g], 0);
+        for (uint32_t i = i0; i < i1 && e == cudaSuccess; ++i)
+            if (items[i].m)
+                e = cudaMemcpyAsync(items[i].y_host, by + yo[i], static_cast<size_t>(items[i].m) * items[i].n * 4, cudaMemcpyDeviceToHost, ctx->out_stream);
+        if (e != cudaSuccess) return cuda_fail(ctx, e, "qmatmul_host_batch: copy-out");
+    }
+    return HF2Q_OK;
+}
+
+// Captures batch_enqueue into ctx->b_graph.  False (and no graph) when anything about the capture fails; the streams
+// are left usable and the caller enqueues the batch the plain way.
+bool batch_capture(hf2q_ctx* ctx, const hf2q_host_product* items, uint32_t n_items, const std::vector<size_t>& xo,
+                   const std::vector<size_t>& yo, uint64_t key) {
+    if (ctx->b_graph) { cudaGraphExecDestroy(ctx->b_graph); ctx->b_graph = nullptr; ctx->b_graph_key = 0; }
+    if (!ctx->b_fork) {
+        if (cudaEventCreateWithFlags(&ctx->b_fork, cudaEventDisableTiming) != cudaSuccess ||
+            cudaEventCreateWithFlags(&ctx->b_join_in, cudaEventDisableTiming) != cudaSuccess ||
+            cudaEventCreateWithFlags(&ctx->b_join_out, cudaEventDisableTiming) != cudaSuccess) {
+            cudaGetLastError();
+            return false;
+        }
+    }
+    if (cudaStreamBeginCapture(ctx->host_stream, cudaStreamCaptureModeThreadLocal) != cudaSuccess) { cudaGetLastError(); return false; }
+    const uint64_t launches0 = ctx->launches;
+    bool ok = cudaEventRecord(ctx->b_fork, ctx->host_stream) == cudaSuccess &&
+              cudaStreamWaitEvent(ctx->in_stream, ctx->b_fork, 0) == cudaSuccess &&
+              cudaStreamWaitEvent(ctx->out_stream, ctx->b_fork, 0) == cudaSuccess;
+    if (ok) ok = batch_enqueue(ctx, items, n_items, xo, yo) == HF2Q_OK;
+    if (ok) ok = cudaEventRecord(ctx->b_join_in, ctx->in_stream) == cudaSuccess &&
+                 cudaEventRecord(ctx->b_join_out, ctx->out_stream) == cudaSuccess &&
+                 cudaStreamWaitEvent(ctx->host_stream, ctx->b_join_in, 0) == cudaSuccess &&
+                 cudaStreamWaitEvent(ctx->host_stream, ctx->b_join_out, 0) == cudaSuccess;
+    cudaGraph_t graph = nullptr;
+    const cudaError_t ec = cudaStreamEndCapture(ctx->host_stream, &graph);      // always: it ends the capture on all three streams
+    const uint64_t launches = ctx->launches - launches0;
+    ctx->launches = launches0;                                                  // nothing ran yet
+    if (ok && ec == cudaSuccess && graph && cudaGraphInstantiate(&ctx->b_graph, graph, 0) == cudaSuccess) {
+        ctx->b_graph_key = key;
+        ctx->b_graph_launches = launches;
+    } else {
+        ctx->b_graph = nullptr;
+        ok = false;
+    }
+    if (graph) cudaGraphDestroy(graph);
+    cudaGetLastError();
+    if (!ok) ctx->err[0] = 0;              // the plain path reports its own errors
+    return ok;
+}
+}  // namespace
+
 HF2Q_API int32_t hf2q_cuda_qmatmul_host_batch(hf2q_ctx* ctx, const hf2q_host_product* items, uint32_t n_items) {
     if (!ctx) return HF2Q_ERR_INVALID_ARGUMENT;
     const char* who = "qmatmul_host_batch";
     if (!items && n_items) return fail(ctx, HF2Q_ERR_INVALID_ARGUMENT, "%s: null item array", who);
     if (n_items == 0) return HF2Q_OK;
-    constexpr uint32_t GROUP = 8;
     std::vector<size_t> xo(n_items), yo(n_items);
     size_t xt = 0, yt = 0;
     uint64_t wsb = 0;
@@ -922,7 +1026,7 @@ HF2Q_API int32_t hf2q_cuda_qmatmul_host_batch(hf2q_ctx* ctx, const hf2q_host_pro
     }
     DeviceGuard dg(ctx->device);
     cudaError_t e = cudaSuccess;
-    const uint32_t n_groups = (n_items + GROUP - 1) / GROUP;
+    const uint32_t n_groups = (n_items + BATCH_GROUP - 1) / BATCH_GROUP;
     if (ctx->bx_bytes < xt || ctx->by_bytes < yt || ctx->ws_bytes < wsb) {
         e = cudaStreamSynchronize(ctx->in_stream);            // growing frees the old buffers: nothing may still use them
         if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->host_stream);
@@ -945,36 +1049,31 @@ HF2Q_API int32_t hf2q_cuda_qmatmul_host_batch(hf2q_ctx* ctx, const hf2q_host_pro
         if (e == cudaSuccess) e = cudaEventCreateWithFlags(&ctx->b_all_drained, cudaEventDisableTiming);
         if (e != cudaSuccess) return cuda_fail(ctx, e, "qmatmul_host_batch: event");
     }
+    const uint64_t key = batch_key(ctx, items, n_items);
+    static const bool graphs_off = [] { const char* v = getenv("HF2Q_HOST_BATCH_GRAPH"); return v && v[0] == '0'; }();
+    if (!graphs_off && key != ctx->b_nograph_key && key == ctx->b_last_key && key != ctx->b_graph_key &&
+        !batch_capture(ctx, items, n_items, xo, yo, key))
+        ctx->b_nograph_key = key;          // do not try again on every call
+    ctx->b_last_key = key;
+    if (ctx->b_graph && key == ctx->b_graph_key) {
+        // the graph starts after everything queued on the kernel stream; the previous batch's copies-out must have read
+        // the y staging (its copies-in were waited for by its kernels)
+        if (ctx->b_used) e = cudaStreamWaitEvent(ctx->host_stream, ctx->b_all_drained, 0);
+        if (e == cudaSuccess) e = cudaGraphLaunch(ctx->b_graph, ctx->host_stream);
+        if (e == cudaSuccess) e = cudaEventRecord(ctx->b_all_computed, ctx->host_stream);
+        if (e == cudaSuccess) e = cudaEventRecord(ctx->b_all_drained, ctx->host_stream);
+        if (e != cudaSuccess) return cuda_fail(ctx, e, "qmatmul_host_batch: graph launch");
+        ctx->launches += ctx->b_graph_launches;
+        ctx->b_used = true;
+        return HF2Q_OK;
+    }
     if (ctx->b_used) {
         // the previous batch: its kernels have read the x staging, its copies-out the y staging
         e = cudaStreamWaitEvent(ctx->in_stream, ctx->b_all_computed, 0);
         if (e == cudaSuccess) e = cudaStreamWaitEvent(ctx->host_stream, ctx->b_all_drained, 0);
         if (e != cudaSuccess) return cuda_fail(ctx, e, "qmatmul_host_batch: ordering after the previous batch");
     }
-    uint8_t* bx = static_cast<uint8_t*>(ctx->bx);
-    uint8_t* by = static_cast<uint8_t*>(ctx->by);
-    for (uint32_t g = 0; g < n_groups; ++g) {
-        const uint32_t i0 = g * GROUP, i1 = i0 + GROUP < n_items ? i0 + GROUP : n_items;
-        for (uint32_t i = i0; i < i1 && e == cudaSuccess; ++i)
-            e = cudaMemcpyAsync(bx + xo[i], items[i].x_host, static_cast<size_t>(items[i].m) * items[i].k * dtype_size(items[i].x_dtype),
-                                cudaMemcpyHostToDevice, ctx->in_stream);
-        if (e == cudaSuccess) e = cudaEventRecord(ctx->b_loaded[g], ctx->in_stream);
-        if (e == cudaSuccess) e = cudaStreamWaitEvent(ctx->host_stream, ctx->b_loaded[g], 0);
-        if (e != cudaSuccess) return cuda_fail(ctx, e, "qmatmul_host_batch: copy-in");
-        for (uint32_t i = i0; i < i1; ++i) {
-            const hf2q_host_product& it = items[i];
-            if (it.m == 0) continue;
-            const int32_t rc = hf2q_cuda_qmatmul(ctx, ctx->host_stream, bx + xo[i], it.x_dtype, it.w_dev, reinterpret_cast<float*>(by + yo[i]), it.m,
-                                                 it.n, it.k, it.ggml_type, ctx->ws, ctx->ws_bytes);
-            if (rc) return rc;
-        }
-        e = cudaEventRecord(ctx->b_computed[g], ctx->host_stream);
-        if (e == cudaSuccess) e = cudaStreamWaitEvent(ctx->out_stream, ctx->b_computed[g], 0);
-        for (uint32_t i = i0; i < i1 && e == cudaSuccess; ++i)
-            if (items[i].m)
-                e = cudaMemcpyAsync(items[i].y_host, by + yo[i], static_cast<size_t>(items[i].m) * items[i].n * 4, cudaMemcpyDeviceToHost, ctx->out_stream);
-        if (e != cudaSuccess) return cuda_fail(ctx, e, "qmatmul_host_batch: copy-out");
-    }
+    if (const int32_t rc = batch_enqueue(ctx, items, n_items, xo, yo)) return rc;
     e = cudaEventRecord(ctx->b_all_computed, ctx->host_stream);
     if (e == cudaSuccess) e = cudaEventRecord(ctx->b_all_drained, ctx->out_stream);
     if (e != cudaSuccess) return cuda_fail(ctx, e, "qmatmul_host_batch: events");

@@ -245,7 +245,10 @@ HF2Q_API int32_t hf2q_cuda_qmatmul_host_async(hf2q_ctx* ctx, const void* x_host,
  * stream, the kernels back to back on a second (consecutive mat-vecs overlap as they do for device callers),
  * copies-out on a third; results are valid after hf2q_cuda_host_sync.  Buffers as for
  * hf2q_cuda_qmatmul_host_async (pinned memory for real overlap; alive until the sync).  The products are
- * independent: no item may read another item's output. */
+ * independent: no item may read another item's output.  A batch that arrives a second time unchanged (same
+ * pointers, shapes and types -- a decode loop) is captured into a CUDA graph and replayed from then on: the
+ * host buffers are read and written at every call as before, the call itself costs one graph launch
+ * (HF2Q_HOST_BATCH_GRAPH=0 in the environment keeps the plain enqueueing). */
 typedef struct hf2q_host_product {
     const void* x_host;   /* [m][k], x_dtype */
     const void* w_dev;    /* device blocks, as for hf2q_cuda_qmatmul */

@@ -232,7 +232,7 @@ def test_host_buffer_batch_call(gpu_ctx):
     """One call queues many independent host-buffer products (mat-vec and GEMM sized, several formats); a second
     batch issued before the first one was waited for reuses the staging buffers in order."""
     specs = [(oracle.Q4_K, 256, 2048, 4), (oracle.Q6_K, 96, 2048, 1), (oracle.Q8_0, 64, 512, 8), (oracle.Q5_K, 128, 1024, 40),
-             (oracle.Q4_0, 80, 256, 3)] * 4                                   # 20 products: three groups of 8
+             (oracle.Q4_0, 80, 256, 3)] * 4                                   # 20 products: five groups of 4
     ws, raws = [], []
     for i, (t, n, k, m) in enumerate(specs):
         raw = make_quant_weight(t, n, k, seed=300 + i)
@@ -253,6 +253,25 @@ def test_host_buffer_batch_call(gpu_ctx):
     for xs, ys in ((xa, ya), (xb, yb)):
         for x, y, raw, (t, n, k, m) in zip(xs, ys, raws, specs):
             assert rel_l2(y, _ref(t, raw, x, n, k)) < GATE, (t, n, k, m)
+    # The same batch again and again (a decode loop): from its second arrival on it is replayed as one CUDA graph.
+    # New contents in the same host buffers must come through, another batch in between must not disturb it, and the
+    # launch counter must advance by the same amount per call.
+    per_call = []
+    for rep in range(4):
+        for i, x in enumerate(xa):
+            x[...] = make_x(x.shape[0], x.shape[1], seed=5000 + 100 * rep + i)
+        for y in ya:
+            y[...] = np.nan
+        n0 = gpu_ctx.launch_count
+        hq.ops.quantized_matmul_host_batch(gpu_ctx, ba)
+        per_call.append(gpu_ctx.launch_count - n0)
+        if rep == 2:
+            hq.ops.quantized_matmul_host_batch(gpu_ctx, bb)
+        hq.ops.host_sync(gpu_ctx)
+        gpu_ctx.check_status()
+        for x, y, raw, (t, n, k, m) in zip(xa, ya, raws, specs):
+            assert rel_l2(y, _ref(t, raw, x, n, k)) < GATE, (rep, t, n, k, m)
+    assert len(set(per_call)) == 1 and per_call[0] >= len(specs)
     lib = _lib.load()
     assert lib.hf2q_cuda_qmatmul_host_batch(gpu_ctx._h, None, 3) == _lib.ERR_INVALID_ARGUMENT
     assert lib.hf2q_cuda_qmatmul_host_batch(gpu_ctx._h, None, 0) == 0
