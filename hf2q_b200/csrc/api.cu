@@ -906,13 +906,27 @@ HF2Q_API int32_t hf2q_cuda_qmatmul_host_async(hf2q_ctx* ctx, const void* x_host,
 
 // Many host-buffer products in one call: the copies-in run ahead on their own stream, the kernels run back to back
 // on one stream (so consecutive mat-vecs keep their programmatic-dependent-launch overlap), the copies-out follow
-// group by group on a third stream.  One event pair per group of 4 products instead of three event edges per product
-// (small groups: the copies-out of the last group are the tail of the call).
+// group by group on a third stream.  One event pair per group of products instead of three event edges per product.
 // A decode loop hands in the same batch again and again (same host buffers, same weights): the second time an
 // unchanged batch arrives, the three streams' work is captured into one CUDA graph, and from then on the call is one
 // graph launch.  Anything that changes (an item, a staging buffer that grew) falls back to plain enqueueing.
 namespace {
-constexpr uint32_t BATCH_GROUP = 4;
+// Group boundaries of a batch of n products: [b[g], b[g+1]) is group g.  Every boundary costs the two kernels around
+// it their start-up overlap (~3 us); every product of the LAST group delays the end of the call by its copy-out
+// (~7 us), and the first group's copies-in delay the start.  So: groups of 8 in the middle, tapering to single
+// products at the end (.., 4, 4, 2, 2, 1, 1) and starting small (2, 4, ..).
+std::vector<uint32_t> batch_groups(uint32_t n) {
+    std::vector<uint32_t> head, mid, tail;
+    uint32_t r = n;
+    for (uint32_t s : {1u, 1u, 2u, 2u, 4u, 4u}) { if (r < s) break; tail.push_back(s); r -= s; }
+    for (uint32_t s : {2u, 4u}) { if (r < s) break; head.push_back(s); r -= s; }
+    while (r) { const uint32_t g = r < 8 ? r : 8; mid.push_back(g); r -= g; }
+    std::vector<uint32_t> b{0};
+    for (uint32_t s : head) b.push_back(b.back() + s);
+    for (uint32_t s : mid) b.push_back(b.back() + s);
+    for (auto it = tail.rbegin(); it != tail.rend(); ++it) b.push_back(b.back() + *it);
+    return b;
+}
 
 uint64_t batch_key(const hf2q_ctx* ctx, const hf2q_host_product* items, uint32_t n_items) {
     uint64_t h = 1469598103934665603ull;
@@ -936,9 +950,9 @@ int32_t batch_enqueue(hf2q_ctx* ctx, const hf2q_host_product* items, uint32_t n_
     cudaError_t e = cudaSuccess;
     uint8_t* bx = static_cast<uint8_t*>(ctx->bx);
     uint8_t* by = static_cast<uint8_t*>(ctx->by);
-    const uint32_t n_groups = (n_items + BATCH_GROUP - 1) / BATCH_GROUP;
-    for (uint32_t g = 0; g < n_groups; ++g) {
-        const uint32_t i0 = g * BATCH_GROUP, i1 = i0 + BATCH_GROUP < n_items ? i0 + BATCH_GROUP : n_items;
+    const std::vector<uint32_t> bounds = batch_groups(n_items);
+    for (uint32_t g = 0; g + 1 < bounds.size(); ++g) {
+        const uint32_t i0 = bounds[g], i1 = bounds[g + 1];
         for (uint32_t i = i0; i < i1 && e == cudaSuccess; ++i)
             e = cudaMemcpyAsync(bx + xo[i], items[i].x_host, static_cast<size_t>(items[i].m) * items[i].k * dtype_size(items[i].x_dtype),
                                 cudaMemcpyHostToDevice, ctx->in_stream);
@@ -1026,7 +1040,7 @@ HF2Q_API int32_t hf2q_cuda_qmatmul_host_batch(hf2q_ctx* ctx, const hf2q_host_pro
     }
     DeviceGuard dg(ctx->device);
     cudaError_t e = cudaSuccess;
-    const uint32_t n_groups = (n_items + BATCH_GROUP - 1) / BATCH_GROUP;
+    const uint32_t n_groups = static_cast<uint32_t>(batch_groups(n_items).size()) - 1;
     if (ctx->bx_bytes < xt || ctx->by_bytes < yt || ctx->ws_bytes < wsb) {
         e = cudaStreamSynchronize(ctx->in_stream);            // growing frees the old buffers: nothing may still use them
         if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->host_stream);

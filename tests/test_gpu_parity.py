@@ -232,7 +232,7 @@ def test_host_buffer_batch_call(gpu_ctx):
     """One call queues many independent host-buffer products (mat-vec and GEMM sized, several formats); a second
     batch issued before the first one was waited for reuses the staging buffers in order."""
     specs = [(oracle.Q4_K, 256, 2048, 4), (oracle.Q6_K, 96, 2048, 1), (oracle.Q8_0, 64, 512, 8), (oracle.Q5_K, 128, 1024, 40),
-             (oracle.Q4_0, 80, 256, 3)] * 4                                   # 20 products: five groups of 4
+             (oracle.Q4_0, 80, 256, 3)] * 4                                   # 20 products: groups of 2, 4 | 1, 1, 2, 2, 4, 4 (from the end)
     ws, raws = [], []
     for i, (t, n, k, m) in enumerate(specs):
         raw = make_quant_weight(t, n, k, seed=300 + i)
