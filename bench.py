@@ -1066,23 +1066,16 @@ def main() -> None:
     else:
         # the sharded call: every rank copies its activations in, the product gathers, rank 0 (the
         # rank that would hand the result on) copies the full-width output to pinned host memory
-        xin = {key: torch.empty_like(t) for key, t in xdev.items()}
-        pin_xv = {key: t.view(torch.bfloat16).reshape(key[1], key[0]) for key, t in pin_x.items()}
         pin_y = {(n, m): torch.empty((m, world * n), dtype=torch.float32).pin_memory() for n, _ in SHAPES for m in TOKENS} if rank == 0 else {}
+        np_y = {key: t.numpy() for key, t in pin_y.items()}
+        batch = hq.ops.HostBatch([(np_x[(k, m)], w, np_y.get((n, m)), m, hq.ops.DT_BF16)
+                                  for m in TOKENS for c in range(args.copies) for (n, k), w in zip(SHAPES, weights[c])])
 
         def e2e_pass():
-            for m in TOKENS:
-                for c in range(args.copies):
-                    for (n, k), w in zip(SHAPES, weights[c]):
-                        xin[(k, m)].copy_(pin_xv[(k, m)], non_blocking=True)
-                        gather.matmul(xin[(k, m)], w, m, rank * n, wait_previous=True)
-                        if rank == 0:
-                            gather.wait()
-                            pin_y[(n, m)].copy_(gather.output(m)[:, : world * n], non_blocking=True)
-            gather.wait()
-            torch.cuda.synchronize()
-        e2e_api = ("per product: pinned host x -> device on every rank, hf2q_cuda_qmatmul_gather (all-gather in the kernel), "
-                   "full-width y -> pinned host on rank 0; one synchronize per pass")
+            gather.host_batch(batch)
+            hq.ops.host_sync(ctx)
+        e2e_api = ("hf2q_cuda_qmatmul_gather_host_batch: one call per rank queues the pass's products (each: pinned host x -> device on every rank, "
+                   "hf2q_cuda_qmatmul_gather with the all-gather in the kernel, full-width y -> pinned host on rank 0), hf2q_cuda_host_sync once per pass")
         d2h = args.copies * sum(4 * m * n * world for n, _ in SHAPES for m in TOKENS)
 
     e2e_passes = args.e2e_steps or max(3, min(args.steps, 20))

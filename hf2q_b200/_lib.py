@@ -59,6 +59,7 @@ SIGNATURES = {
     "hf2q_cuda_qmatmul_gather": (i32, [vp, vp, vp, u32, vp, vp, u32, u32, u32, u32]),
     "hf2q_cuda_gather_wait": (i32, [vp, vp, vp]),
     "hf2q_cuda_gather_sum": (i32, [vp, vp, vp, vp, u32, u32]),
+    "hf2q_cuda_qmatmul_gather_host_batch": (i32, [vp, vp, u64, u32, vp, u32]),
     "hf2q_cuda_gather_supported": (i32, [vp, vp, u32, u32, u32, u32, u32]),
     "hf2q_cuda_gather_copy": (i32, [vp, vp, vp, vp, u32]),
     "hf2q_cuda_set_wait_limit": (i32, [vp, u64]),

@@ -944,9 +944,17 @@ uint64_t batch_key(const hf2q_ctx* ctx, const hf2q_host_product* items, uint32_t
     return h ? h : 1;
 }
 
+// The row-sharded form of a batch: every product goes through the fused all-gather of `g` (buffer 0 of every rank in
+// g->y_all[], buffer 1 buf_stride bytes behind it; product i uses buffer (first_buf + i) & 1), equal shards.
+struct GatherBatch {
+    const hf2q_gather* g;
+    uint64_t buf_stride;
+    uint32_t first_buf;
+};
+
 // Queues the batch on the three streams.  Returns HF2Q_OK or the first error (already recorded in the context).
 int32_t batch_enqueue(hf2q_ctx* ctx, const hf2q_host_product* items, uint32_t n_items, const std::vector<size_t>& xo,
-                      const std::vector<size_t>& yo) {
+                      const std::vector<size_t>& yo, const GatherBatch* gb = nullptr) {
     cudaError_t e = cudaSuccess;
     uint8_t* bx = static_cast<uint8_t*>(ctx->bx);
     uint8_t* by = static_cast<uint8_t*>(ctx->by);
@@ -962,15 +970,39 @@ int32_t batch_enqueue(hf2q_ctx* ctx, const hf2q_host_product* items, uint32_t n_
         for (uint32_t i = i0; i < i1; ++i) {
             const hf2q_host_product& it = items[i];
             if (it.m == 0) continue;
-            const int32_t rc = hf2q_cuda_qmatmul(ctx, ctx->host_stream, bx + xo[i], it.x_dtype, it.w_dev, reinterpret_cast<float*>(by + yo[i]), it.m,
-                                                 it.n, it.k, it.ggml_type, ctx->ws, ctx->ws_bytes);
+            if (!gb) {
+                const int32_t rc = hf2q_cuda_qmatmul(ctx, ctx->host_stream, bx + xo[i], it.x_dtype, it.w_dev, reinterpret_cast<float*>(by + yo[i]), it.m,
+                                                     it.n, it.k, it.ggml_type, ctx->ws, ctx->ws_bytes);
+                if (rc) return rc;
+                continue;
+            }
+            // the sharded product: columns [rank * n, (rank + 1) * n) of this product's buffer on every rank
+            hf2q_gather gi = *gb->g;
+            const uint64_t shift = ((gb->first_buf + i) & 1u) * gb->buf_stride;
+            for (uint32_t r = 0; r < gi.n_ranks; ++r) {
+                gi.y_all[r] = static_cast<uint8_t*>(gi.y_all[r]) + shift;
+                gi.n_rows[r] = it.n;
+            }
+            gi.col0 = gi.rank * it.n;
+            gi.wait_previous = 1;
+            int32_t rc = hf2q_cuda_qmatmul_gather(ctx, ctx->host_stream, bx + xo[i], it.x_dtype, it.w_dev, &gi, it.m, it.n, it.k, it.ggml_type);
             if (rc) return rc;
+            if (it.y_host) {
+                // The full-width rows leave the gather buffer on the kernel stream, BEFORE this rank's next product is
+                // queued: a peer stores product i+2 into this buffer once it has seen product i+1 from every rank.
+                e = launch_gather_take(static_cast<const uint32_t*>(gi.flags[gi.rank]), gi.n_ranks, gi.rank, ctx->wait_limit, ctx->status,
+                                       static_cast<const float*>(gi.y_all[gi.rank]), gi.n_total, gi.n_ranks * it.n, it.m,
+                                       reinterpret_cast<float*>(by + yo[i]), ctx->dev.sm_count, ctx->host_stream);
+                if (e != cudaSuccess) return cuda_fail(ctx, e, "qmatmul_gather_host_batch: copy out of the gather buffer");
+                ctx->launches += 1;
+            }
         }
         e = cudaEventRecord(ctx->b_computed[g], ctx->host_stream);
         if (e == cudaSuccess) e = cudaStreamWaitEvent(ctx->out_stream, ctx->b_computed[g], 0);
         for (uint32_t i = i0; i < i1 && e == cudaSuccess; ++i)
-            if (items[i].m)
-                e = cudaMemcpyAsync(items[i].y_host, by + yo[i], static_cast<size_t>(items[i].m) * items[i].n * 4, cudaMemcpyDeviceToHost, ctx->out_stream);
+            if (items[i].m && items[i].y_host)
+                e = cudaMemcpyAsync(items[i].y_host, by + yo[i], static_cast<size_t>(items[i].m) * items[i].n * 4 * (gb ? gb->g->n_ranks : 1u),
+                                    cudaMemcpyDeviceToHost, ctx->out_stream);
         if (e != cudaSuccess) return cuda_fail(ctx, e, "qmatmul_host_batch: copy-out");
     }
     return HF2Q_OK;
@@ -1017,27 +1049,31 @@ bool batch_capture(hf2q_ctx* ctx, const hf2q_host_product* items, uint32_t n_ite
 }
 }  // namespace
 
-HF2Q_API int32_t hf2q_cuda_qmatmul_host_batch(hf2q_ctx* ctx, const hf2q_host_product* items, uint32_t n_items) {
+static int32_t host_batch_impl(hf2q_ctx* ctx, const hf2q_host_product* items, uint32_t n_items, const GatherBatch* gb) {
     if (!ctx) return HF2Q_ERR_INVALID_ARGUMENT;
-    const char* who = "qmatmul_host_batch";
+    const char* who = gb ? "qmatmul_gather_host_batch" : "qmatmul_host_batch";
     if (!items && n_items) return fail(ctx, HF2Q_ERR_INVALID_ARGUMENT, "%s: null item array", who);
     if (n_items == 0) return HF2Q_OK;
+    const uint32_t wide = gb ? gb->g->n_ranks : 1u;          // a gathered result is n_ranks shards wide
     std::vector<size_t> xo(n_items), yo(n_items);
     size_t xt = 0, yt = 0;
     uint64_t wsb = 0;
     for (uint32_t i = 0; i < n_items; ++i) {
         const hf2q_host_product& it = items[i];
-        if (!it.x_host || !it.w_dev || !it.y_host) return fail(ctx, HF2Q_ERR_INVALID_ARGUMENT, "%s: item %u has a null pointer", who, i);
+        if (!it.x_host || !it.w_dev || (!it.y_host && !gb)) return fail(ctx, HF2Q_ERR_INVALID_ARGUMENT, "%s: item %u has a null pointer", who, i);
         if (it.x_dtype != HF2Q_DT_F32 && it.x_dtype != HF2Q_DT_BF16) return fail(ctx, HF2Q_ERR_INVALID_ARGUMENT, "%s: item %u x_dtype %u", who, i, it.x_dtype);
         const int32_t rc = check_matmul_shape(ctx, it.ggml_type, it.n, it.k, who);
         if (rc) return rc;
+        if (gb && static_cast<uint64_t>(wide) * it.n > gb->g->n_total)
+            return fail(ctx, HF2Q_ERR_INVALID_ARGUMENT, "%s: item %u: %u shards of %u rows exceed the group's %u columns", who, i, wide, it.n, gb->g->n_total);
         xo[i] = xt; yo[i] = yt;
         xt += (static_cast<size_t>(it.m) * it.k * dtype_size(it.x_dtype) + 255) & ~static_cast<size_t>(255);
-        yt += (static_cast<size_t>(it.m) * it.n * 4 + 255) & ~static_cast<size_t>(255);
+        if (it.y_host) yt += (static_cast<size_t>(it.m) * it.n * 4 * wide + 255) & ~static_cast<size_t>(255);
         uint64_t w1 = 0;
-        hf2q_cuda_qmatmul_workspace_bytes(it.m, it.n, it.k, it.ggml_type, it.x_dtype, &w1);
+        if (!gb) hf2q_cuda_qmatmul_workspace_bytes(it.m, it.n, it.k, it.ggml_type, it.x_dtype, &w1);
         if (w1 > wsb) wsb = w1;
     }
+    if (yt == 0) yt = 256;
     DeviceGuard dg(ctx->device);
     cudaError_t e = cudaSuccess;
     const uint32_t n_groups = static_cast<uint32_t>(batch_groups(n_items).size()) - 1;
@@ -1063,13 +1099,14 @@ HF2Q_API int32_t hf2q_cuda_qmatmul_host_batch(hf2q_ctx* ctx, const hf2q_host_pro
         if (e == cudaSuccess) e = cudaEventCreateWithFlags(&ctx->b_all_drained, cudaEventDisableTiming);
         if (e != cudaSuccess) return cuda_fail(ctx, e, "qmatmul_host_batch: event");
     }
-    const uint64_t key = batch_key(ctx, items, n_items);
+    // (the sharded form is always enqueued: its buffer parity and the peers' state are not part of a key)
+    const uint64_t key = gb ? 0 : batch_key(ctx, items, n_items);
     static const bool graphs_off = [] { const char* v = getenv("HF2Q_HOST_BATCH_GRAPH"); return v && v[0] == '0'; }();
-    if (!graphs_off && key != ctx->b_nograph_key && key == ctx->b_last_key && key != ctx->b_graph_key &&
+    if (!gb && !graphs_off && key != ctx->b_nograph_key && key == ctx->b_last_key && key != ctx->b_graph_key &&
         !batch_capture(ctx, items, n_items, xo, yo, key))
         ctx->b_nograph_key = key;          // do not try again on every call
-    ctx->b_last_key = key;
-    if (ctx->b_graph && key == ctx->b_graph_key) {
+    if (!gb) ctx->b_last_key = key;
+    if (!gb && ctx->b_graph && key == ctx->b_graph_key) {
         // the graph starts after everything queued on the kernel stream; the previous batch's copies-out must have read
         // the y staging (its copies-in were waited for by its kernels)
         if (ctx->b_used) e = cudaStreamWaitEvent(ctx->host_stream, ctx->b_all_drained, 0);
@@ -1087,12 +1124,25 @@ HF2Q_API int32_t hf2q_cuda_qmatmul_host_batch(hf2q_ctx* ctx, const hf2q_host_pro
         if (e == cudaSuccess) e = cudaStreamWaitEvent(ctx->host_stream, ctx->b_all_drained, 0);
         if (e != cudaSuccess) return cuda_fail(ctx, e, "qmatmul_host_batch: ordering after the previous batch");
     }
-    if (const int32_t rc = batch_enqueue(ctx, items, n_items, xo, yo)) return rc;
+    if (const int32_t rc = batch_enqueue(ctx, items, n_items, xo, yo, gb)) return rc;
     e = cudaEventRecord(ctx->b_all_computed, ctx->host_stream);
     if (e == cudaSuccess) e = cudaEventRecord(ctx->b_all_drained, ctx->out_stream);
     if (e != cudaSuccess) return cuda_fail(ctx, e, "qmatmul_host_batch: events");
     ctx->b_used = true;
     return HF2Q_OK;
+}
+
+HF2Q_API int32_t hf2q_cuda_qmatmul_host_batch(hf2q_ctx* ctx, const hf2q_host_product* items, uint32_t n_items) {
+    return host_batch_impl(ctx, items, n_items, nullptr);
+}
+
+HF2Q_API int32_t hf2q_cuda_qmatmul_gather_host_batch(hf2q_ctx* ctx, const hf2q_gather* g, uint64_t buf_stride, uint32_t first_buf,
+                                                     const hf2q_host_product* items, uint32_t n_items) {
+    if (!ctx) return HF2Q_ERR_INVALID_ARGUMENT;
+    if (!g || g->n_ranks == 0 || g->n_ranks > 8 || g->rank >= g->n_ranks)
+        return fail(ctx, HF2Q_ERR_INVALID_ARGUMENT, "qmatmul_gather_host_batch: bad group");
+    const GatherBatch gb{g, buf_stride, first_buf & 1u};
+    return host_batch_impl(ctx, items, n_items, &gb);
 }
 
 HF2Q_API int32_t hf2q_cuda_host_sync(hf2q_ctx* ctx) {

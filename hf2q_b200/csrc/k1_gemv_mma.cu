@@ -1260,6 +1260,31 @@ __global__ void __launch_bounds__(256) gather_sum_kernel(const uint32_t* flag, u
     for (uint32_t r = 0; r < n_parts; ++r) acc += __ldcg(parts + static_cast<size_t>(r) * stride + i);
     x[i] = acc;
 }
+// dst[r][0 .. width) = src[r * pitch + 0 .. width) for r < m, after the columns of every rank have arrived here: the
+// gathered rows of the most recent product leave the group's buffer in one launch (the sharded host-buffer batch
+// copies them out behind the kernels).
+__global__ void __launch_bounds__(256) gather_take_kernel(const uint32_t* flag, uint32_t n_ranks, uint32_t rank, long long limit, uint32_t* status,
+                                                          const float* __restrict__ src, uint32_t pitch, uint32_t width, uint32_t m,
+                                                          float* __restrict__ dst, uint32_t vec4) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");      // the next kernel may start its own prologue
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    if (threadIdx.x < n_ranks && threadIdx.x != rank) gather_wait_source(flag, threadIdx.x, limit, status);
+    __syncthreads();
+    const uint32_t stride = gridDim.x * 256;
+    if (vec4) {
+        const uint32_t w4 = width / 4, total = m * w4;
+        for (uint32_t i = blockIdx.x * 256 + threadIdx.x; i < total; i += stride) {
+            const uint32_t r = i / w4, c = i - r * w4;
+            reinterpret_cast<float4*>(dst)[i] = __ldcg(reinterpret_cast<const float4*>(src + static_cast<size_t>(r) * pitch) + c);
+        }
+    } else {
+        const uint32_t total = m * width;
+        for (uint32_t i = blockIdx.x * 256 + threadIdx.x; i < total; i += stride) {
+            const uint32_t r = i / width, c = i - r * width;
+            dst[i] = __ldcg(src + static_cast<size_t>(r) * pitch + c);
+        }
+    }
+}
 }  // namespace
 
 namespace {
@@ -1325,6 +1350,23 @@ cudaError_t launch_gather_sum(const uint32_t* flag, uint32_t n_ranks, uint32_t r
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     return cudaLaunchKernelEx(&cfg, gather_sum_kernel, flag, n_ranks, rank, limit, status, parts, stride, n_parts, x, n);
+}
+
+cudaError_t launch_gather_take(const uint32_t* flag, uint32_t n_ranks, uint32_t rank, long long limit, uint32_t* status, const float* src,
+                               uint32_t pitch, uint32_t width, uint32_t m, float* dst, int sm_count, cudaStream_t st) {
+    const bool vec4 = width % 4 == 0 && pitch % 4 == 0 && reinterpret_cast<uintptr_t>(src) % 16 == 0 && reinterpret_cast<uintptr_t>(dst) % 16 == 0;
+    const uint64_t items = static_cast<uint64_t>(m) * width / (vec4 ? 4 : 1);
+    const uint64_t want = (items + 255) / 256, cap = static_cast<uint64_t>(sm_count) * 4;
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(static_cast<unsigned>(want < 1 ? 1 : want < cap ? want : cap));
+    cfg.blockDim = dim3(256);
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, gather_take_kernel, flag, n_ranks, rank, limit, status, src, pitch, width, m, dst, vec4 ? 1u : 0u);
 }
 
 uint32_t gemv_mma_grid_x(uint32_t n, uint32_t k, const DeviceInfo& dev) {

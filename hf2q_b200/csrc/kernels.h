@@ -105,6 +105,8 @@ cudaError_t launch_gather_wait(const uint32_t* flag, uint32_t n_ranks, uint32_t 
 // src[0 .. n) -> columns [col0, col0 + n) of row 0 of every rank's buffer + the arrival signalling of the fused gather
 cudaError_t launch_gather_copy(const float* src, const GatherArgs& g, uint32_t n, const uint32_t* n_each, cudaStream_t st);
 // waits like launch_gather_wait, then x[i] += sum_{r < n_parts} parts[r * stride + i], i < n (in order)
+cudaError_t launch_gather_take(const uint32_t* flag, uint32_t n_ranks, uint32_t rank, long long limit, uint32_t* status, const float* src,
+                               uint32_t pitch, uint32_t width, uint32_t m, float* dst, int sm_count, cudaStream_t st);
 cudaError_t launch_gather_sum(const uint32_t* flag, uint32_t n_ranks, uint32_t rank, long long limit, uint32_t* status, const float* parts,
                               uint32_t stride, uint32_t n_parts, float* x, uint32_t n, cudaStream_t st);
 

@@ -305,6 +305,15 @@ class GatherGroup:
         self.ctx._check(self.ctx._lib.hf2q_cuda_gather_sum(self.ctx._h, self.ctx._stream(), C.byref(g), x.data_ptr(), n,
                                                            self.world if n_parts is None else n_parts))
 
+    def host_batch(self, batch) -> None:
+        """``ops.HostBatch`` through the sharded product (hf2q_cuda_qmatmul_gather_host_batch): every rank passes the
+        same products with its own shard as the weight; item.y_host (where given) receives the gathered
+        [m, world * rows] result.  Valid after ``ops.host_sync``; counts as len(batch) products of the group."""
+        g = self._struct(0, True, 0, [1] * self.world)
+        self.ctx._check(self.ctx._lib.hf2q_cuda_qmatmul_gather_host_batch(
+            self.ctx._h, C.byref(g), self._buf_bytes, self._next, C.cast(batch.array, C.c_void_p), len(batch)))
+        self._next ^= len(batch) & 1
+
     def wait(self) -> None:
         if self.world > 1:
             g = self._struct(0, False, 0, [1] * self.world)

@@ -384,13 +384,14 @@ class _HostProduct(C.Structure):                 # hf2q_host_product in include/
 
 class HostBatch:
     """A list of independent host-buffer products (x_host, weight, y_host, m, x_dtype) for ``quantized_matmul_host_batch``;
-    the arrays are kept alive by the object."""
+    the arrays are kept alive by the object.  ``y_host`` may be None only for ``GatherGroup.host_batch`` (a rank that
+    does not take the gathered result on the host)."""
 
     def __init__(self, items):
         self._keep = list(items)
         self.array = (_HostProduct * len(self._keep))()
         for slot, (x, w, y, m, xdt) in zip(self.array, self._keep):
-            slot.x_host, slot.w_dev, slot.y_host = x.ctypes.data, w.ptr, y.ctypes.data
+            slot.x_host, slot.w_dev, slot.y_host = x.ctypes.data, w.ptr, (y.ctypes.data if y is not None else None)
             slot.m, slot.n, slot.k, slot.ggml_type, slot.x_dtype = m, w.rows, w.cols, w.ggml_type, xdt
 
     def __len__(self):

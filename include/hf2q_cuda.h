@@ -432,6 +432,19 @@ HF2Q_API int32_t hf2q_cuda_gather_copy(hf2q_ctx* ctx, void* stream, const hf2q_g
  * Same bits on every rank.  n_parts = 1 adds a gathered full-length result (a row-sharded projection). */
 HF2Q_API int32_t hf2q_cuda_gather_sum(hf2q_ctx* ctx, void* stream, const hf2q_gather* g, float* x, uint32_t n,
                                       uint32_t n_parts);
+/* hf2q_cuda_qmatmul_host_batch for row-sharded weights: every rank calls it with the same list of products (its own
+ * shard in w_dev, n = rows of one shard, equal on all ranks; the same activations in x_host).  Product i runs
+ * through hf2q_cuda_qmatmul_gather with wait_previous set, columns [rank * n, (rank + 1) * n), into buffer
+ * (first_buf + i) & 1 of the group: g->y_all[] names every rank's buffer 0, its buffer 1 lies buf_stride bytes behind
+ * it; pass the parity the group's previous product left off at, the next call continues with first_buf + n_items.
+ * A rank whose item has y_host != NULL receives the gathered [m][n_ranks * n] rows there (the rows leave the gather
+ * buffer on the kernel stream before that rank's next product, so the two-buffer rule above holds with the copies
+ * to the host running behind); y_host == NULL on the ranks that do not need the result on the host.  Copies-in,
+ * kernels and copies-out run on the context's three streams as in hf2q_cuda_qmatmul_host_batch; results are valid
+ * after hf2q_cuda_host_sync.  The serving shape of a tensor-parallel decode step: hf2q's single-device
+ * "append ops, commit_and_wait once" (gpu_ffn.rs:1044-1049) with every weight split by rows over the GPUs. */
+HF2Q_API int32_t hf2q_cuda_qmatmul_gather_host_batch(hf2q_ctx* ctx, const hf2q_gather* g, uint64_t buf_stride, uint32_t first_buf,
+                                                     const hf2q_host_product* items, uint32_t n_items);
 
 /* Upper bound, in GPU clock ticks, of the device-side waits for other GPUs (the fused gather's
  * arrival counters).  A context setting: set once after creation, never on the launch path.  The

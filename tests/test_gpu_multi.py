@@ -59,6 +59,22 @@ def _rank_main(rank, world, port, ret):
             torch.cuda.synchronize()
             got = gg.output(mm).cpu().numpy()
             ok &= rel_l2(got, oracle.matmul_f64(xs.float().cpu().numpy(), wfull)) < 1e-3
+        # --- the same sharded product from host buffers, many products per call (copies-in, kernels and copies-out on
+        # the context's three streams); rank 0 takes the gathered rows.  An odd number of products, twice: the buffer
+        # parity carries over from call to call.
+        ms = [1, 4, 8, 3, 2, 8, 1]
+        xs_t = [torch.from_numpy(make_x(mm, k, seed=40 + i)).bfloat16() for i, mm in enumerate(ms)]
+        xs_h = [xt.view(torch.int16).numpy() for xt in xs_t]
+        ys_h = [np.full((mm, n), np.nan, np.float32) if rank == 0 else None for mm in ms]
+        hb = hq.ops.HostBatch([(xh, w, yh, mm, hq.ops.DT_BF16) for xh, yh, mm in zip(xs_h, ys_h, ms)])
+        for rep in range(2):
+            gg.host_batch(hb)
+            hq.ops.host_sync(ctx)
+            ctx.check_status()
+            if rank == 0:
+                for xt, yh in zip(xs_t, ys_h):
+                    ok &= rel_l2(yh, oracle.matmul_f64(xt.float().numpy(), wfull)) < 1e-3
+                    yh[...] = np.nan
         dist.barrier()
         gg.close()
         # --- a real chain: the gathered output of every product is the next product's activations, no host
