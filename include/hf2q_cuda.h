@@ -248,7 +248,9 @@ HF2Q_API int32_t hf2q_cuda_qmatmul_host_async(hf2q_ctx* ctx, const void* x_host,
  * independent: no item may read another item's output.  A batch that arrives a second time unchanged (same
  * pointers, shapes and types -- a decode loop) is captured into a CUDA graph and replayed from then on: the
  * host buffers are read and written at every call as before, the call itself costs one graph launch
- * (HF2Q_HOST_BATCH_GRAPH=0 in the environment keeps the plain enqueueing). */
+ * (HF2Q_HOST_BATCH_GRAPH=0 in the environment keeps the plain enqueueing).  A batch is recognised by its
+ * pointers, shapes and types alone: host buffers that were freed and allocated again at the same addresses
+ * must be of the same kind (pinned or pageable) as when the batch was first seen. */
 typedef struct hf2q_host_product {
     const void* x_host;   /* [m][k], x_dtype */
     const void* w_dev;    /* device blocks, as for hf2q_cuda_qmatmul */
