@@ -517,6 +517,49 @@ def test_gather_entry_single_rank(gpu_ctx):
     assert lib.hf2q_cuda_gather_supported(h, odd.ptr, 1, 16, 1792, oracle.Q6_K, 0) == 0
 
 
+def test_gather_host_batch_single_rank(gpu_ctx):
+    """hf2q_cuda_qmatmul_gather_host_batch with one rank: host activations in, the products through the gathering
+    mat-vec into the group's two alternating buffers, the rows lifted out by the wait-and-take launch and copied to the
+    host; an item without y_host runs but returns nothing; the buffer parity is the caller's."""
+    import ctypes as C
+    from hf2q_b200.dist import _Gather
+    lib, h = gpu_ctx._lib, gpu_ctx._h
+    specs = [(oracle.Q6_K, 48, 2048, 3), (oracle.Q4_K, 200, 512, 8), (oracle.Q5_K, 64, 1024, 1), (oracle.Q8_0, 96, 256, 4),
+             (oracle.Q4_0, 40, 512, 2)]
+    n_total, max_m = 256, 8
+    buf_bytes = (max_m * n_total * 4 + 255) & ~255
+    ybuf, fbuf = C.c_void_p(), C.c_void_p()
+    hy, hf = (C.c_uint8 * 64)(), (C.c_uint8 * 64)()
+    gpu_ctx._check(lib.hf2q_cuda_ipc_alloc(h, 2 * buf_bytes, C.byref(ybuf), hy))
+    gpu_ctx._check(lib.hf2q_cuda_ipc_alloc(h, 256, C.byref(fbuf), hf))
+    g = _Gather()
+    g.y_all[0], g.flags[0] = ybuf.value, fbuf.value
+    g.n_ranks, g.rank, g.n_total, g.col0, g.wait_previous = 1, 0, n_total, 0, 1
+    raws = [make_quant_weight(t, n, k, seed=70 + i) for i, (t, n, k, m) in enumerate(specs)]
+    ws = [hq.load_quant_weight(gpu_ctx, raw, t, n, k) for raw, (t, n, k, m) in zip(raws, specs)]
+    xs_t = [torch.from_numpy(make_x(m, k, seed=80 + i)).bfloat16() for i, (t, n, k, m) in enumerate(specs)]
+    xs_h = [xt.view(torch.int16).numpy() for xt in xs_t]
+    ys = [np.full((m, n), np.nan, np.float32) if i != 2 else None for i, (t, n, k, m) in enumerate(specs)]
+    batch = hq.ops.HostBatch([(xh, w, y, m, hq.ops.DT_BF16) for xh, w, y, (t, n, k, m) in zip(xs_h, ws, ys, specs)])
+    parity = 0
+    for rep in range(3):
+        gpu_ctx._check(lib.hf2q_cuda_qmatmul_gather_host_batch(h, C.byref(g), buf_bytes, parity, C.cast(batch.array, C.c_void_p), len(batch)))
+        parity ^= len(batch) & 1
+        hq.ops.host_sync(gpu_ctx)
+        gpu_ctx.check_status()
+        for i, (xt, y, raw, (t, n, k, m)) in enumerate(zip(xs_t, ys, raws, specs)):
+            if y is None:
+                continue
+            assert rel_l2(y, _ref(t, raw, xt.float().numpy(), n, k)) < GATE, (rep, t, n, k, m)
+            y[...] = np.nan
+    # argument checks: no group, a product wider than the group's buffer
+    assert lib.hf2q_cuda_qmatmul_gather_host_batch(h, None, buf_bytes, 0, C.cast(batch.array, C.c_void_p), len(batch)) == _lib.ERR_INVALID_ARGUMENT
+    g.n_total = 100
+    assert lib.hf2q_cuda_qmatmul_gather_host_batch(h, C.byref(g), buf_bytes, 0, C.cast(batch.array, C.c_void_p), len(batch)) == _lib.ERR_INVALID_ARGUMENT
+    lib.hf2q_cuda_free(h, ybuf.value)
+    lib.hf2q_cuda_free(h, fbuf.value)
+
+
 @pytest.mark.parametrize("t", TYPES)
 def test_device_dequant_of_golden_blocks_reencodes_to_the_stored_codes(gpu_ctx, golden_dir, t):
     """The reference's quantizers recompute the codes from (x + dmin*m) / (d*sc) with the stored
